@@ -1,0 +1,120 @@
+// Host utilities shared by every kernel file: error text, tensor-map encoding,
+// device queries. The driver's cuTensorMapEncodeTiled is resolved at run time
+// through the runtime API so the library links without libcuda.
+#include "common.cuh"
+
+#include <cudaTypedefs.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+namespace edl {
+
+static thread_local char g_err[512] = {0};
+
+void set_last_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return 0;
+  set_last_error("%s: %s", what, cudaGetErrorString(e));
+  return -1;
+}
+
+static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  }
+  return fn;
+}
+
+static CUtensorMapSwizzle swz(int s) {
+  switch (s) {
+    case 0: return CU_TENSOR_MAP_SWIZZLE_NONE;
+    case 1: return CU_TENSOR_MAP_SWIZZLE_32B;
+    case 2: return CU_TENSOR_MAP_SWIZZLE_64B;
+    default: return CU_TENSOR_MAP_SWIZZLE_128B;
+  }
+}
+
+int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                 uint32_t box_cols, int elem_bytes, int swizzle) {
+  auto fn = encode_fn();
+  if (!fn) {
+    set_last_error("cuTensorMapEncodeTiled is not available from this driver");
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld * elem_bytes) & 15)) {
+    set_last_error("tensor map: base %p / leading dimension %llu not 16-byte aligned", base, (unsigned long long)ld);
+    return -1;
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swz(swizzle), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled failed (%d): rows=%llu cols=%llu ld=%llu box=%ux%u", (int)r,
+                   (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, box_rows, box_cols);
+    return -1;
+  }
+  return 0;
+}
+
+int make_tmap_2d_16b(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                     uint32_t box_rows, uint32_t box_cols) {
+  return make_tmap_2d(map, base, rows, cols, ld, box_rows, box_cols, 2, 3);
+}
+
+int make_tmap_3d_16b(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1,
+                     uint64_t stride2, uint32_t box0, uint32_t box1, uint32_t box2, int swizzle) {
+  auto fn = encode_fn();
+  if (!fn) {
+    set_last_error("cuTensorMapEncodeTiled is not available from this driver");
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((stride1 * 2) & 15) || ((stride2 * 2) & 15)) {
+    set_last_error("tensor map 3d: base/strides not 16-byte aligned");
+    return -1;
+  }
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1 * 2, stride2 * 2};
+  cuuint32_t box[3] = {box0, box1, box2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swz(swizzle), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled(3d) failed (%d)", (int)r);
+    return -1;
+  }
+  return 0;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace edl
+
+EDL_HOST_API const char* edl_last_error() { return edl::g_err; }
+EDL_HOST_API int edl_sm_count() { return edl::sm_count(); }
+EDL_HOST_API int edl_abi_version() { return 1; }

@@ -1,0 +1,356 @@
+// bf16 GEMM on the 5th-generation tensor cores: C[M,N] (+)= op(A) * op(B).
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer  (cp.async.bulk.tensor, 128-byte swizzle, mbarrier tx counts)
+//   warp 1      MMA issuer    (one thread issues tcgen05.mma, accumulators in tensor memory)
+//   warps 2..5  epilogue      (tcgen05.ld -> registers -> bias / accumulate / cast -> global)
+// Two accumulator buffers in tensor memory let the epilogue of tile i overlap the
+// main loop of tile i+1. Either operand may be K-major (its reduction dimension is
+// contiguous in memory) or MN-major (its M or N dimension is contiguous), which
+// covers forward (X W^T), data-gradient (dY W) and weight-gradient (dY^T X) GEMMs
+// of a linear layer without transposing anything in memory.
+//
+// This is the replacement for the reference's einsum -> XLA -> cuBLASLt path
+// (easydel/layers/linears/_linear.py:245-322).
+#include "common.cuh"
+
+namespace edl {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int GEMM_THREADS = 192;
+
+enum GemmFlags : int {
+  GEMM_OUT_F32 = 1,     // C is fp32 (else bf16)
+  GEMM_ACCUMULATE = 2,  // C += A*B (else C = A*B)
+  GEMM_BIAS = 4,        // add bias[N] (bf16) to every row
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  // Groups of 8 M-tiles share each N-tile consecutively so that the B tile and
+  // a small set of A tiles stay in L2 while a wave of CTAs works on them.
+  constexpr int GROUP = 8;
+  int per_group = GROUP * tiles_n;
+  int g = tile / per_group;
+  int first_m = g * GROUP;
+  int gm = min(tiles_m - first_m, GROUP);
+  int r = tile - g * per_group;
+  tm = first_m + (r % gm);
+  tn = r / gm;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 void* __restrict__ Cout, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc,
+                 int flags, int* status) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  const uint32_t full0 = smem_u32(bars);
+  const uint32_t empty0 = full0 + 8 * C::STAGES;
+  const uint32_t tfull0 = empty0 + 8 * C::STAGES;
+  const uint32_t tempty0 = tfull0 + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(tfull0, 1);
+    mbar_init(tfull0 + 8, 1);
+    mbar_init(tempty0, 4);
+    mbar_init(tempty0 + 8, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tma_a);
+    prefetch_tmap(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, status, EDL_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = full0 + 8 * stage;
+          mbar_expect_tx(fb, C::STAGE_BYTES);
+          const uint32_t a_dst = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + C::A_BYTES;
+          if (!A_MN) {
+            tma_load_2d(a_dst, &tma_a, fb, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tma_a, fb, m0 + j * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(b_dst, &tma_b, fb, kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tma_b, fb, n0 + j * 64, kb * BK);
+          }
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, status, EDL_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, status, EDL_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? umma_smem_desc_sw128(a_addr + k * 2048, 8192, 1024)
+                                        : umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
+                                        : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(empty0 + 8 * stage);
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(tfull0 + 8 * acc);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool out_f32 = flags & GEMM_OUT_F32;
+    const bool accum = flags & GEMM_ACCUMULATE;
+    const bool has_bias = (flags & GEMM_BIAS) && bias != nullptr;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, status, EDL_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (has_bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < N) v[j] += __bfloat162float(bias[col0 + j]);
+          }
+          const bool full_chunk = (col0 + 32 <= N);
+          if (out_f32) {
+            float* cp = reinterpret_cast<float*>(Cout) + (long long)row * ldc + col0;
+            if (full_chunk) {
+              if (accum) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                  float4 o = *reinterpret_cast<const float4*>(cp + j);
+                  v[j] += o.x;
+                  v[j + 1] += o.y;
+                  v[j + 2] += o.z;
+                  v[j + 3] += o.w;
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(cp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) cp[j] = accum ? cp[j] + v[j] : v[j];
+            }
+          } else {
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)row * ldc + col0;
+            if (full_chunk) {
+              if (accum) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 o = *reinterpret_cast<const uint4*>(cp + j);
+                  float2 f;
+                  f = unpack_bf16x2(o.x); v[j] += f.x; v[j + 1] += f.y;
+                  f = unpack_bf16x2(o.y); v[j + 2] += f.x; v[j + 3] += f.y;
+                  f = unpack_bf16x2(o.z); v[j + 4] += f.x; v[j + 5] += f.y;
+                  f = unpack_bf16x2(o.w); v[j + 6] += f.x; v[j + 7] += f.y;
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 o;
+                o.x = pack_bf16x2(v[j], v[j + 1]);
+                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(cp + j) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) {
+                float o = accum ? __bfloat162float(cp[j]) + v[j] : v[j];
+                cp[j] = __float2bfloat16(o);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  // Teardown. On the error path give copies still in flight a moment to land
+  // before shared memory is handed back.
+  if (*abort_flag) {
+    long long t0 = clock64();
+    while (clock64() - t0 < 400000) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch(const void* A, const void* B, void* Cout, const void* bias, int M, int N, int K, long long lda,
+           long long ldb, long long ldc, int flags, int* status, cudaStream_t stream, int max_ctas) {
+  using C = Cfg<BN>;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!A_MN)
+    rc = make_tmap_2d_16b(&ta, A, M, K, lda, BM, BK);
+  else
+    rc = make_tmap_2d_16b(&ta, A, K, M, lda, BK, 64);
+  if (rc) return rc;
+  if (!B_MN)
+    rc = make_tmap_2d_16b(&tb, B, N, K, ldb, BN, BK);
+  else
+    rc = make_tmap_2d_16b(&tb, B, K, N, ldb, BK, 64);
+  if (rc) return rc;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
+                   "cudaFuncSetAttribute(gemm)"))
+      return -1;
+    attr_set = true;
+  }
+  int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int ctas = sm_count();
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (tiles < ctas) ctas = tiles;
+  kern<<<ctas, GEMM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, Cout, reinterpret_cast<const __nv_bfloat16*>(bias), M,
+                                                       N, K, ldc, flags, status);
+  return check_cuda(cudaGetLastError(), "gemm launch");
+}
+
+}  // namespace
+}  // namespace edl
+
+// C[M,N] (+)= op(A) * op(B), bf16 inputs, fp32 accumulation.
+//   a_mn = 0: A is an [M,K] row-major matrix (leading dimension lda).
+//   a_mn = 1: A is stored as [K,M] row-major (the caller holds A transposed).
+//   b_mn = 0: B is stored as [N,K] row-major (a torch Linear weight: C = A B^T).
+//   b_mn = 1: B is stored as [K,N] row-major.
+// flags: 1 = fp32 output, 2 = accumulate into C, 4 = add bf16 bias[N].
+// Requirements: all bases 16-byte aligned; lda, ldb multiples of 8; ldc a multiple
+// of 8 (bf16) or 4 (fp32). `status` is a device int that receives a non-zero code
+// if a pipeline wait ran out. Returns 0 on success; edl_last_error() has the text.
+EDL_HOST_API int edl_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                               long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int flags,
+                               int* status, void* stream, int max_ctas, int force_bn) {
+  using namespace edl;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(C) & 15) ||
+      ((flags & GEMM_OUT_F32) ? (ldc & 3) : (ldc & 7))) {
+    set_last_error("edl_gemm_bf16: leading dimensions must keep 16-byte alignment (lda=%lld ldb=%lld ldc=%lld)", lda,
+                   ldb, ldc);
+    return -1;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
+  bool bn128 = (N <= 128) || (tiles256 < sm_count());
+  if (force_bn == 128) bn128 = true;
+  if (force_bn == 256) bn128 = false;
+#define EDL_GEMM_CASE(BN, AM, BMN) \
+  return launch<BN, AM, BMN>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, status, s, max_ctas)
+  if (bn128) {
+    if (!a_mn && !b_mn) EDL_GEMM_CASE(128, false, false);
+    if (!a_mn && b_mn) EDL_GEMM_CASE(128, false, true);
+    if (a_mn && !b_mn) EDL_GEMM_CASE(128, true, false);
+    EDL_GEMM_CASE(128, true, true);
+  } else {
+    if (!a_mn && !b_mn) EDL_GEMM_CASE(256, false, false);
+    if (!a_mn && b_mn) EDL_GEMM_CASE(256, false, true);
+    if (a_mn && !b_mn) EDL_GEMM_CASE(256, true, false);
+    EDL_GEMM_CASE(256, true, true);
+  }
+#undef EDL_GEMM_CASE
+}

@@ -1,0 +1,86 @@
+"""tcgen05 GEMM against an fp32 PyTorch matmul for every operand layout, tile width and epilogue."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    return A @ B
+
+
+def _mk(M, N, K, a_mn, b_mn, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", generator=g).to(torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", generator=g).to(torch.bfloat16)
+    return a, b
+
+
+def _close(out, ref, K):
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    # bf16 output rounding (2^-8 relative) plus accumulation noise
+    assert err <= 1e-2 * scale + 1e-3 * (K ** 0.5), f"max err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_layouts(a_mn, b_mn, bn):
+    from easydel_b200.ops import kernels as K_
+
+    M, N, K = 384, 512, 320
+    a, b = _mk(M, N, K, a_mn, b_mn)
+    out = K_.gemm(a, b, a_mn=a_mn, b_mn=b_mn, force_bn=bn)
+    _close(out, _ref(a, b, a_mn, b_mn), K)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 264, 72), (1, 8, 8), (1000, 1000, 1000), (4096, 4096, 4096),
+                                   (130, 40, 4104)])
+def test_gemm_shapes(M, N, K):
+    from easydel_b200.ops import kernels as K_
+
+    a, b = _mk(M, N, K, False, False, seed=M + N + K)
+    out = K_.gemm(a, b)
+    _close(out, _ref(a, b, False, False), K)
+
+
+def test_gemm_fp32_accumulate_and_bias():
+    from easydel_b200.ops import kernels as K_
+
+    M, N, K = 300, 520, 256
+    a, b = _mk(M, N, K, True, True, seed=3)
+    ref = _ref(a, b, True, True)
+    acc = torch.ones((M, N), device="cuda", dtype=torch.float32)
+    K_.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    K_.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True)
+    assert torch.allclose(acc, 1 + 2 * ref, atol=2e-2, rtol=1e-3)
+    a, b = _mk(M, N, K, False, False, seed=4)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    out = K_.gemm(a, b, bias=bias)
+    _close(out, _ref(a, b, False, False) + bias.float(), K)
+
+
+def test_gemm_strided_views():
+    from easydel_b200.ops import kernels as K_
+
+    big_a = torch.randn(256, 1024, device="cuda").to(torch.bfloat16)
+    big_b = torch.randn(512, 1024, device="cuda").to(torch.bfloat16)
+    a = big_a[:, 128:640]
+    b = big_b[:, 128:640]
+    out_big = torch.zeros(256, 1024, device="cuda", dtype=torch.bfloat16)
+    out = out_big[:, 256:768]
+    K_.gemm(a, b, out=out)
+    _close(out, a.float() @ b.float().t(), 512)
+    assert out_big[:, :256].abs().max().item() == 0 and out_big[:, 768:].abs().max().item() == 0
+
+
+def test_gemm_deterministic():
+    from easydel_b200.ops import kernels as K_
+
+    a, b = _mk(1024, 2048, 512, False, False, seed=9)
+    o1 = K_.gemm(a, b)
+    o2 = K_.gemm(a, b)
+    assert torch.equal(o1, o2)
