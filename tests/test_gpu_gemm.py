@@ -50,7 +50,7 @@ def test_gemm_shapes(M, N, K):
 def test_gemm_fp32_accumulate_and_bias():
     from easydel_b200.ops import kernels as K_
 
-    M, N, K = 300, 520, 256
+    M, N, K = 304, 520, 256
     a, b = _mk(M, N, K, True, True, seed=3)
     ref = _ref(a, b, True, True)
     acc = torch.ones((M, N), device="cuda", dtype=torch.float32)
