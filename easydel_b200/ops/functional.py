@@ -1,0 +1,407 @@
+"""Differentiable ops. CUDA tensors run the sm_100a kernels, CPU tensors the reference math.
+
+Each op is a ``torch.autograd.Function`` over the raw launchers in
+:mod:`easydel_b200.ops.kernels`. Weight gradients of linear layers are
+accumulated straight into ``weight.main_grad`` (an fp32 view of the flat
+gradient buffer owned by the optimizer state) when that attribute exists, so a
+micro-batch loop never materialises per-parameter bf16 gradients.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib, kernels as K, reference as R
+
+
+def _as_2d(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1 or (x2.shape[0] > 1 and x2.stride(0) % 8) or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    return x2
+
+
+# ---------------------------------------------------------------------------- linear
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        x2 = _as_2d(x)
+        y = K.gemm(x2, w, bias=bias)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.x_shape = x.shape
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = _as_2d(dy)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = K.gemm(dy2, w, b_mn=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                K.gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True)
+                w.grad_added_to_main_grad = True
+            else:
+                dw = K.gemm(dy2, x2, a_mn=True, b_mn=True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x @ w.T + bias with ``w`` in torch Linear layout ``[out, in]``."""
+    if _lib.use_kernels(x):
+        if x.dtype != torch.bfloat16:
+            raise TypeError(f"GPU linear expects bf16 activations, got {x.dtype}")
+        return _LinearFn.apply(x, w, bias)
+    return R.linear(x, w, bias)
+
+
+# ---------------------------------------------------------------------------- norms
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, residual, eps, w_offset):
+        y, h, rstd = K.rmsnorm_fwd(x, w, eps, residual=residual, w_offset=w_offset)
+        ctx.save_for_backward(h, w, rstd)
+        ctx.w_offset = w_offset
+        ctx.has_res = residual is not None
+        ctx.set_materialize_grads(False)
+        if residual is not None:
+            return y, h
+        placeholder = x.new_empty(0)
+        ctx.mark_non_differentiable(placeholder)
+        return y, placeholder
+
+    @staticmethod
+    def backward(ctx, dy, dh):
+        h, w, rstd = ctx.saved_tensors
+        mg = getattr(w, "main_grad", None)
+        dres = dh if ctx.has_res else None
+        if dy is None:
+            dy = torch.zeros_like(h)
+        dx, dw = K.rmsnorm_bwd(h, w, dy, rstd, dres=dres, w_offset=ctx.w_offset, dw_out=mg,
+                               accumulate=mg is not None)
+        dwr = None
+        if mg is None:
+            dwr = dw.to(w.dtype)
+        return dx, dwr, (dx if ctx.has_res else None), None, None
+
+
+def rms_norm(x, w, eps: float = 1e-6, w_offset: float = 0.0):
+    if _lib.use_kernels(x):
+        y, _ = _RMSNormFn.apply(x, w, None, eps, w_offset)
+        return y
+    return R.rms_norm(x, w, eps, w_offset)
+
+
+def add_rms_norm(x, residual, w, eps: float = 1e-6, w_offset: float = 0.0):
+    """Returns (rmsnorm(x + residual), x + residual) with the add fused into the norm kernel."""
+    if _lib.use_kernels(x):
+        return _RMSNormFn.apply(x, w, residual, eps, w_offset)
+    h = x + residual
+    return R.rms_norm(h, w, eps, w_offset), h
+
+
+def layer_norm(x, w, b, eps: float = 1e-5):
+    # LayerNorm models (GPT-2/NeoX/OPT/...) are not on a named hot path; torch's kernel serves both devices.
+    return torch.nn.functional.layer_norm(x, (x.shape[-1],), w, b, eps)
+
+
+# ---------------------------------------------------------------------------- activations
+class _GatedActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu, act):
+        ctx.save_for_backward(gu)
+        ctx.act = act
+        return K.gated_act_fwd(gu, act)
+
+    @staticmethod
+    def backward(ctx, dh):
+        (gu,) = ctx.saved_tensors
+        return K.gated_act_bwd(gu, dh, ctx.act), None
+
+
+def gated_act(gu: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """act(gu[..., :F]) * gu[..., F:]."""
+    if _lib.use_kernels(gu) and act in K.ACT_IDS:
+        return _GatedActFn.apply(gu if gu.stride(-1) == 1 else gu.contiguous(), act)
+    return R.gated_act(gu, act)
+
+
+# ---------------------------------------------------------------------------- rotary
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, pos, cos, sin, nheads, head_dim, col0, rot_dim, interleaved):
+        ctx.save_for_backward(pos, cos, sin)
+        ctx.args = (nheads, head_dim, col0, rot_dim, interleaved)
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        K.rope_(x2, pos, cos, sin, nheads, head_dim, col0=col0, rot_dim=rot_dim, interleaved=interleaved)
+        ctx.mark_dirty(x)
+        return x
+
+    @staticmethod
+    def backward(ctx, dx):
+        pos, cos, sin = ctx.saved_tensors
+        nheads, head_dim, col0, rot_dim, interleaved = ctx.args
+        dx = dx.contiguous() if not dx.is_contiguous() else dx.clone()
+        K.rope_(dx.view(-1, dx.shape[-1]), pos, cos, sin, nheads, head_dim, col0=col0, rot_dim=rot_dim,
+                interleaved=interleaved, backward=True)
+        return dx, None, None, None, None, None, None, None, None
+
+
+def rope_packed(qkv: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, nheads: int,
+                head_dim: int, col0: int = 0, rot_dim: int | None = None, interleaved: bool = False):
+    """Rotates the first ``nheads`` heads (starting at column ``col0``) of a packed ``[T, width]`` projection.
+
+    On the GPU the rotation happens in place on ``qkv`` (which must be a fresh, contiguous activation).
+    """
+    if _lib.use_kernels(qkv):
+        if not qkv.is_contiguous():
+            qkv = qkv.contiguous()
+        elif qkv.requires_grad and qkv.is_leaf:
+            qkv = qkv.clone()
+        elif not qkv.requires_grad:
+            qkv = qkv.clone() if qkv._base is not None else qkv
+        return _RopeFn.apply(qkv, pos.reshape(-1), cos, sin, nheads, head_dim, col0, rot_dim, interleaved)
+    T = qkv.reshape(-1, qkv.shape[-1]).shape[0]
+    flat = qkv.reshape(T, -1)
+    seg = flat[:, col0:col0 + nheads * head_dim].reshape(T, nheads, head_dim)
+    rot = R.apply_rope(seg, pos.reshape(-1), cos, sin, rot_dim, interleaved).reshape(T, nheads * head_dim)
+    out = torch.cat([flat[:, :col0], rot, flat[:, col0 + nheads * head_dim:]], dim=-1)
+    return out.view(qkv.shape)
+
+
+# ---------------------------------------------------------------------------- embedding
+class _EmbedFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, table, ids):
+        ctx.save_for_backward(ids)
+        ctx.table = table
+        return K.embed_fwd(table, ids)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        table = ctx.table
+        mg = getattr(table, "main_grad", None)
+        if mg is not None:
+            K.embed_bwd_(mg, dout, ids)
+            table.grad_added_to_main_grad = True
+            return None, None
+        g = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
+        K.embed_bwd_(g, dout, ids)
+        return g.to(table.dtype), None
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    if _lib.use_kernels(table) and table.dtype == torch.bfloat16:
+        return _EmbedFn.apply(table, ids)
+    return torch.nn.functional.embedding(ids, table)
+
+
+# ---------------------------------------------------------------------------- LM head + cross entropy
+class _LinearCEFn(torch.autograd.Function):
+    """Chunked LM-head GEMM + cross-entropy that never holds more than one chunk of logits.
+
+    The gradient of each chunk is produced in the same pass (the CE kernel overwrites the
+    logits with d loss / d logits), then pushed through the two backward GEMMs, so the
+    backward of this node only rescales by the incoming scalar gradient.
+    """
+
+    @staticmethod
+    def forward(ctx, h, w, labels, bias, ignore_index, label_smoothing, z_loss, softcap, chunk, reduction_scale,
+                want_acc):
+        T, H = h.shape
+        V = w.shape[0]
+        dev = h.device
+        valid = (labels != ignore_index)
+        n_valid = valid.sum().to(torch.float32)
+        # gscale tensor = 1/max(n_valid,1) * reduction_scale, consumed on-device by the CE kernel
+        if reduction_scale is None:
+            gs = (1.0 / n_valid.clamp_min(1.0)).reshape(1)
+        else:
+            gs = torch.full((1,), float(reduction_scale), dtype=torch.float32, device=dev)
+        need_grad = torch.is_grad_enabled() and (h.requires_grad or w.requires_grad)
+        losses = torch.empty(T, dtype=torch.float32, device=dev)
+        correct = torch.empty(T, dtype=torch.int32, device=dev) if want_acc else None
+        dh = torch.empty_like(h) if need_grad and h.requires_grad else None
+        mg = getattr(w, "main_grad", None)
+        dw = None
+        if need_grad and w.requires_grad and mg is None:
+            dw = torch.zeros(V, H, dtype=torch.float32, device=dev)
+        for s in range(0, T, chunk):
+            e = min(T, s + chunk)
+            hc = h[s:e]
+            logits = K.gemm(hc, w, bias=bias)
+            l, _, c = K.cross_entropy_(logits, labels[s:e], ignore_index=ignore_index,
+                                       label_smoothing=label_smoothing, z_loss=z_loss, softcap=softcap,
+                                       grad_scale_tensor=gs, write_grad=need_grad, want_correct=want_acc)
+            losses[s:e] = l
+            if want_acc:
+                correct[s:e] = c
+            if need_grad:
+                if dh is not None:
+                    K.gemm(logits, w, b_mn=True, out=dh[s:e])
+                if w.requires_grad:
+                    K.gemm(logits, hc, a_mn=True, b_mn=True, out=mg if mg is not None else dw, accumulate=True)
+        if mg is not None and need_grad and w.requires_grad:
+            w.grad_added_to_main_grad = True
+        loss = losses.sum() * gs[0]
+        ctx.save_for_backward(dh, dw)
+        ctx.w_dtype = w.dtype
+        ctx.mark_non_differentiable(n_valid)
+        acc = None
+        if want_acc:
+            acc = correct.sum().to(torch.float32) / n_valid.clamp_min(1.0)
+            ctx.mark_non_differentiable(acc)
+            return loss, n_valid, acc
+        return loss, n_valid, torch.zeros((), device=dev)
+
+    @staticmethod
+    def backward(ctx, dloss, _dn, _dacc):
+        dh, dw = ctx.saved_tensors
+        gh = gw = None
+        if dh is not None:
+            gh = dh * dloss.to(dh.dtype)
+        if dw is not None:
+            gw = (dw * dloss).to(ctx.w_dtype)
+        return gh, gw, None, None, None, None, None, None, None, None, None
+
+
+def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, *, bias=None,
+                         ignore_index: int = -100, label_smoothing: float = 0.0, z_loss: float = 0.0,
+                         softcap: float = 0.0, chunk_size: int = 2048, reduction_scale: float | None = None,
+                         want_accuracy: bool = False):
+    """Mean (over non-ignored labels) cross-entropy of ``h @ w.T`` without materialising the logits.
+
+    ``h`` is ``[T, H]``, ``labels`` ``[T]`` (already shifted by the caller). Returns
+    ``(loss, n_valid, accuracy)``. With ``reduction_scale`` the sum of token losses is
+    multiplied by that constant instead of ``1 / n_valid``.
+
+    On the GPU with ``w.main_grad`` present the LM-head weight gradient is accumulated
+    during this call, which is exact when the scalar gradient reaching ``loss`` is 1
+    (the trainer folds 1/accumulation into ``reduction_scale``).
+    """
+    h2 = h.reshape(-1, h.shape[-1])
+    lab = labels.reshape(-1)
+    if _lib.use_kernels(h2):
+        if not h2.is_contiguous():
+            h2 = h2.contiguous()
+        return _LinearCEFn.apply(h2, w, lab, bias, ignore_index, label_smoothing, z_loss, softcap, chunk_size,
+                                 reduction_scale, want_accuracy)
+    total = h2.new_zeros((), dtype=torch.float32)
+    correct = h2.new_zeros((), dtype=torch.float32)
+    for s in range(0, h2.shape[0], chunk_size):
+        logits = R.linear(h2[s:s + chunk_size], w, bias)
+        l, _ = R.cross_entropy(logits, lab[s:s + chunk_size], ignore_index=ignore_index,
+                               label_smoothing=label_smoothing, z_loss=z_loss, softcap=softcap)
+        total = total + l.sum()
+        if want_accuracy:
+            zc = logits.float()
+            correct = correct + ((zc.argmax(-1) == lab[s:s + chunk_size]) & (lab[s:s + chunk_size] != ignore_index)
+                                 ).sum()
+    n_valid = (lab != ignore_index).sum().to(torch.float32)
+    scale = (1.0 / n_valid.clamp_min(1.0)) if reduction_scale is None else reduction_scale
+    return total * scale, n_valid, correct / n_valid.clamp_min(1.0)
+
+
+# ---------------------------------------------------------------------------- token log-probs (DPO / GRPO)
+class _LinearLogprobFn(torch.autograd.Function):
+    """log p(label) per token from hidden states and the LM head, chunked; backward recomputes each chunk."""
+
+    @staticmethod
+    def forward(ctx, h, w, labels, bias, ignore_index, temperature, chunk, want_entropy):
+        T = h.shape[0]
+        logp = torch.empty(T, dtype=torch.float32, device=h.device)
+        lse = torch.empty(T, dtype=torch.float32, device=h.device)
+        ent = torch.empty(T, dtype=torch.float32, device=h.device) if want_entropy else None
+        for s in range(0, T, chunk):
+            e = min(T, s + chunk)
+            logits = K.gemm(h[s:e], w, bias=bias)
+            lp, ls, en = K.token_logprob(logits, labels[s:e], ignore_index=ignore_index, temperature=temperature,
+                                         want_entropy=want_entropy)
+            logp[s:e] = lp
+            lse[s:e] = ls
+            if want_entropy:
+                ent[s:e] = en
+        ctx.save_for_backward(h, w, labels, lse, bias)
+        ctx.args = (ignore_index, temperature, chunk)
+        if want_entropy:
+            ctx.mark_non_differentiable(ent)
+            return logp, ent
+        return logp, torch.zeros((), device=h.device)
+
+    @staticmethod
+    def backward(ctx, dlogp, _dent):
+        h, w, labels, lse, bias = ctx.saved_tensors
+        ignore_index, temperature, chunk = ctx.args
+        T, H = h.shape
+        dh = torch.empty_like(h) if ctx.needs_input_grad[0] else None
+        mg = getattr(w, "main_grad", None)
+        dw = None
+        if ctx.needs_input_grad[1] and mg is None:
+            dw = torch.zeros(w.shape, dtype=torch.float32, device=h.device)
+        dlogp = dlogp.contiguous()
+        for s in range(0, T, chunk):
+            e = min(T, s + chunk)
+            logits = K.gemm(h[s:e], w, bias=bias)
+            K.token_logprob_bwd_(logits, labels[s:e], lse[s:e], dlogp[s:e], ignore_index=ignore_index,
+                                 temperature=temperature)
+            if dh is not None:
+                K.gemm(logits, w, b_mn=True, out=dh[s:e])
+            if ctx.needs_input_grad[1]:
+                K.gemm(logits, h[s:e], a_mn=True, b_mn=True, out=mg if mg is not None else dw, accumulate=True)
+        gw = None
+        if dw is not None:
+            gw = dw.to(w.dtype)
+        elif mg is not None and ctx.needs_input_grad[1]:
+            w.grad_added_to_main_grad = True
+        return dh, gw, None, None, None, None, None, None
+
+
+def linear_token_logprob(h, w, labels, *, bias=None, ignore_index: int = -100, temperature: float = 1.0,
+                         chunk_size: int = 2048, want_entropy: bool = False):
+    """Per-token ``log softmax(h @ w.T / temperature)[label]`` (0 where ignored); optional entropy."""
+    shape = labels.shape
+    h2 = h.reshape(-1, h.shape[-1])
+    lab = labels.reshape(-1)
+    if _lib.use_kernels(h2):
+        if not h2.is_contiguous():
+            h2 = h2.contiguous()
+        lp, ent = _LinearLogprobFn.apply(h2, w, lab, bias, ignore_index, temperature, chunk_size, want_entropy)
+        return lp.view(shape), (ent.view(shape) if want_entropy else None)
+    outs, ents = [], []
+    for s in range(0, h2.shape[0], chunk_size):
+        logits = R.linear(h2[s:s + chunk_size], w, bias)
+        outs.append(R.token_logprob(logits, lab[s:s + chunk_size], ignore_index=ignore_index,
+                                    temperature=temperature))
+        if want_entropy:
+            lpa = torch.log_softmax(logits.float() / temperature, -1)
+            ents.append(-(lpa.exp() * lpa).sum(-1))
+    return torch.cat(outs).view(shape), (torch.cat(ents).view(shape) if want_entropy else None)
+
+
+# ---------------------------------------------------------------------------- attention
+def attention(q, k, v, *, causal: bool = True, scale: float | None = None, segment_ids=None,
+              sliding_window: int | None = None, softcap: float = 0.0, sinks=None, cu_seqlens=None):
+    """Softmax attention. q ``[B,T,Hq,D]``, k/v ``[B,T,Hkv,D]`` -> ``[B,T,Hq,D]``.
+
+    CUDA tensors run the tcgen05 flash kernels (imported lazily from :mod:`.attention`).
+    """
+    if _lib.use_kernels(q):
+        from .attention import flash_attention
+
+        return flash_attention(q, k, v, causal=causal, scale=scale, segment_ids=segment_ids,
+                               sliding_window=sliding_window, softcap=softcap, sinks=sinks)
+    return R.attention(q, k, v, causal=causal, scale=scale, segment_ids=segment_ids, sliding_window=sliding_window,
+                       softcap=softcap, sinks=sinks)
+
+
+def default_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)
