@@ -1,0 +1,143 @@
+"""Self-attention layer shared by every decoder family.
+
+One class covers what the reference's ``UnifiedAttention`` does for standard attention
+(easydel/layers/attention/_unified.py:290-340, forward at :1048-1174): fused QKV projection,
+optional QK-norm, rotary embedding, GQA, sliding window, logit soft-cap, attention sinks, ALiBi,
+then the attention operator chosen by the execution mode:
+
+* training / full-sequence forward: flash attention kernels (``ops.functional.attention``);
+* ``generate()`` with a dense cache: the same kernel over the cache contents (queries aligned
+  to the end of the keys);
+* eSurge serving: the paged cache view appends K/V into pages and runs the paged attention
+  kernels (``caching.paged``).
+"""
+
+from __future__ import annotations
+
+import math
+import typing as tp
+
+import torch
+from torch import nn
+
+from ..ops import functional as F
+from .linears import ColumnParallelLinear, RowParallelLinear
+from .norms import LayerNorm, RMSNorm
+from .rotary import get_rope
+
+
+def alibi_slopes(n_heads: int) -> torch.Tensor:
+    def pow2(n):
+        start = 2 ** (-(2 ** -(math.log2(n) - 3)))
+        return [start * (start ** i) for i in range(n)]
+
+    if math.log2(n_heads).is_integer():
+        return torch.tensor(pow2(n_heads), dtype=torch.float32)
+    c = 2 ** math.floor(math.log2(n_heads))
+    return torch.tensor(pow2(c) + pow2(2 * c)[0::2][: n_heads - c], dtype=torch.float32)
+
+
+class Attention(nn.Module):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, *, layer_idx: int = 0,
+                 bias: bool = False, o_bias: bool = False, qk_norm: str | None = None, qk_norm_eps: float = 1e-6,
+                 rope: dict | None = None, sliding_window: int | None = None, softcap: float = 0.0,
+                 scale: float | None = None, use_sinks: bool = False, use_alibi: bool = False, causal: bool = True,
+                 clip_qkv: float | None = None, dtype: torch.dtype = torch.float32, init_std: float = 0.02,
+                 tp_size: int = 1, tp_rank: int = 0, tp_group=None, qk_norm_offset: float = 0.0):
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.hidden_size = hidden_size
+        self.num_heads_global, self.num_kv_heads_global = num_heads, num_kv_heads
+        if num_heads % tp_size:
+            raise ValueError(f"num_heads {num_heads} not divisible by tp {tp_size}")
+        # KV heads are split when there are enough of them, replicated otherwise
+        self.kv_replicated = num_kv_heads % tp_size != 0
+        if self.kv_replicated and tp_size % num_kv_heads:
+            raise ValueError(f"cannot place {num_kv_heads} KV heads on tp={tp_size}")
+        self.num_heads = num_heads // tp_size
+        self.num_kv_heads = max(1, num_kv_heads // tp_size)
+        self.head_dim = head_dim
+        self.tp_size, self.tp_rank = tp_size, tp_rank
+        self.sliding_window = sliding_window
+        self.softcap = softcap
+        self.causal = causal
+        self.clip_qkv = clip_qkv
+        self.scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+        kv_out = num_kv_heads * head_dim if not self.kv_replicated else self.num_kv_heads * head_dim * tp_size
+        self.qkv_proj = ColumnParallelLinear(hidden_size, (num_heads * head_dim, kv_out, kv_out), bias=bias,
+                                             dtype=dtype, init_std=init_std, tp_size=tp_size, tp_rank=tp_rank,
+                                             tp_group=tp_group)
+        self.o_proj = RowParallelLinear(num_heads * head_dim, hidden_size, bias=o_bias, dtype=dtype,
+                                        init_std=init_std, tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group)
+        self.qk_norm = qk_norm
+        if qk_norm == "rms_head":      # per-head RMSNorm over head_dim (Qwen3, Gemma3, OLMo... per-head flavour)
+            self.q_norm = RMSNorm(head_dim, qk_norm_eps, dtype, offset=qk_norm_offset)
+            self.k_norm = RMSNorm(head_dim, qk_norm_eps, dtype, offset=qk_norm_offset)
+        elif qk_norm == "rms_full":    # RMSNorm over the whole projection (OLMo2, Cohere-style full width)
+            self.q_norm = RMSNorm(self.num_heads * head_dim, qk_norm_eps, dtype)
+            self.k_norm = RMSNorm(self.num_kv_heads * head_dim, qk_norm_eps, dtype)
+        elif qk_norm == "layer_head":  # per-head LayerNorm without bias (Cohere, StableLM per-head)
+            self.q_norm = LayerNorm(head_dim, qk_norm_eps, bias=False, dtype=dtype)
+            self.k_norm = LayerNorm(head_dim, qk_norm_eps, bias=False, dtype=dtype)
+        self.rotary = None
+        if rope is not None:
+            self.rotary = get_rope(head_size=head_dim, **rope)
+        self.sinks = nn.Parameter(torch.zeros(self.num_heads, dtype=torch.float32)) if use_sinks else None
+        if use_alibi:
+            sl = alibi_slopes(num_heads)[tp_rank * self.num_heads:(tp_rank + 1) * self.num_heads]
+            self.register_buffer("alibi", sl, persistent=False)
+        else:
+            self.alibi = None
+
+    # ------------------------------------------------------------------
+    def _split(self, qkv: torch.Tensor):
+        B, T, _ = qkv.shape
+        Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        q = qkv[..., : Hq * D].view(B, T, Hq, D)
+        k = qkv[..., Hq * D:(Hq + Hkv) * D].view(B, T, Hkv, D)
+        v = qkv[..., (Hq + Hkv) * D:].view(B, T, Hkv, D)
+        return q, k, v
+
+    def _apply_qk_norm(self, qkv: torch.Tensor) -> torch.Tensor:
+        B, T, W = qkv.shape
+        Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        q, k, v = qkv[..., : Hq * D], qkv[..., Hq * D:(Hq + Hkv) * D], qkv[..., (Hq + Hkv) * D:]
+        if self.qk_norm in ("rms_head", "layer_head"):
+            q = self.q_norm(q.reshape(B, T, Hq, D)).reshape(B, T, Hq * D)
+            k = self.k_norm(k.reshape(B, T, Hkv, D)).reshape(B, T, Hkv * D)
+        else:
+            q = self.q_norm(q.contiguous())
+            k = self.k_norm(k.contiguous())
+        return torch.cat([q, k, v], dim=-1)
+
+    def forward(self, hidden: torch.Tensor, positions: torch.Tensor, *, segment_ids: torch.Tensor | None = None,
+                cache_view=None, attn_meta=None, cu_seqlens=None, max_seqlen=None) -> torch.Tensor:
+        """hidden ``[B,T,H]``; positions ``[B,T]``. Returns ``[B,T,H]``."""
+        B, T, _ = hidden.shape
+        qkv = self.qkv_proj(hidden)
+        if self.clip_qkv is not None:
+            qkv = qkv.clamp(-self.clip_qkv, self.clip_qkv)
+        if self.qk_norm is not None:
+            qkv = self._apply_qk_norm(qkv)
+        if self.rotary is not None:
+            qkv = self.rotary.rotate_packed(qkv, positions, self.num_heads + self.num_kv_heads)
+        q, k, v = self._split(qkv)
+        if cache_view is not None:
+            o = cache_view.attend(self, q, k, v, positions=positions, attn_meta=attn_meta)
+        elif self.alibi is not None:
+            o = self._alibi_attention(q, k, v, segment_ids)
+        else:
+            o = F.attention(q, k, v, causal=self.causal, scale=self.scale, segment_ids=segment_ids,
+                            sliding_window=self.sliding_window, softcap=self.softcap, sinks=self.sinks,
+                            cu_seqlens=cu_seqlens)
+        return self.o_proj(o.reshape(B, T, self.num_heads * self.head_dim))
+
+    def _alibi_attention(self, q, k, v, segment_ids):
+        # ALiBi families (Falcon-RW, MPT, BLOOM-style) are served by the dense oracle path: a
+        # position-dependent bias has no slot in the flash kernels.
+        from ..ops import reference as R
+
+        Tq, Tk = q.shape[1], k.shape[1]
+        rel = (torch.arange(Tk, device=q.device)[None, :] - torch.arange(Tq, device=q.device)[:, None] - (Tk - Tq))
+        bias = self.alibi.to(q.device)[None, :, None, None] * rel[None, None].float()
+        return R.attention(q, k, v, causal=self.causal, scale=self.scale, segment_ids=segment_ids, bias=bias)

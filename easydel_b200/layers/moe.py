@@ -1,0 +1,150 @@
+"""Mixture-of-experts block: router, token permutation, expert FFNs, weighted combine, aux losses.
+
+Behavioural counterpart of ``BaseMoeModule`` (easydel/layers/moe/_moe_module.py:108-1791) and the
+permutation helpers in ``_communication_utils.py:764-963``:
+
+* router logits -> fp32 softmax (or sigmoid) over all experts -> top-k -> optional renormalisation
+  (``TOP_K`` vs ``TOP_K_NDIV``), DeepSeek group-limited selection and score-correction bias;
+* tokens are repeated ``k`` times and sorted by expert (dropless, no capacity), the experts run as
+  one grouped GEMM over the ragged groups, outputs are un-sorted and combined in fp32;
+* load-balancing auxiliary loss and router z-loss are returned for the model to add to the loss.
+
+Expert weights are stacked ``[E, out, in]`` (torch layout per expert); the checkpoint writer
+stores them as the reference's ``(E, in, out)`` kernels. Under expert parallelism each rank
+owns ``E / ep`` experts and ``parallel.ep`` moves tokens between ranks around the grouped GEMM.
+"""
+
+from __future__ import annotations
+
+import typing as tp
+
+import torch
+from torch import nn
+
+from ..ops import functional as F
+from ..ops import grouped as G
+from .linears import ColumnParallelLinear
+from .mlp import GatedMLP
+
+
+class MoELinear(nn.Module):
+    """Stacked expert weights ``[E_local, out, in]`` (ParallelMoELinear, _linear_moe.py:90-542)."""
+
+    def __init__(self, num_experts: int, in_features: int, out_features: int, dtype=torch.float32,
+                 init_std: float = 0.01, parallel_style: str = "column", device=None):
+        super().__init__()
+        self.num_experts, self.in_features, self.out_features = num_experts, in_features, out_features
+        self.parallel_style = parallel_style
+        self.weight = nn.Parameter(torch.empty(num_experts, out_features, in_features, dtype=dtype, device=device))
+        if self.weight.device.type != "meta":
+            nn.init.normal_(self.weight, 0.0, init_std)
+
+    def forward(self, x_sorted: torch.Tensor, group_sizes: torch.Tensor) -> torch.Tensor:
+        return G.grouped_linear(x_sorted, self.weight, group_sizes)
+
+
+def load_balancing_loss(router_probs: torch.Tensor, topk_idx: torch.Tensor, num_experts: int,
+                        attention_mask: torch.Tensor | None = None) -> torch.Tensor:
+    """Switch-style auxiliary loss ``E * sum_e f_e * P_e`` (easydel/infra/loss_utils.py:1760-1892).
+
+    ``router_probs`` ``[T, E]`` fp32 probabilities, ``topk_idx`` ``[T, k]``.
+    """
+    T, k = topk_idx.shape
+    onehot = torch.zeros(T, num_experts, dtype=torch.float32, device=router_probs.device)
+    onehot.scatter_add_(1, topk_idx, torch.ones_like(topk_idx, dtype=torch.float32))
+    if attention_mask is not None:
+        m = attention_mask.reshape(-1, 1).to(torch.float32)
+        denom = m.sum().clamp_min(1.0)
+        tokens_per_expert = (onehot * m).sum(0) / denom
+        prob_per_expert = (router_probs * m).sum(0) / denom
+    else:
+        tokens_per_expert = onehot.mean(0)
+        prob_per_expert = router_probs.mean(0)
+    return num_experts * (tokens_per_expert * prob_per_expert).sum()
+
+
+def router_z_loss(router_logits: torch.Tensor) -> torch.Tensor:
+    return torch.logsumexp(router_logits.float(), dim=-1).pow(2).mean()
+
+
+class MoEBlock(nn.Module):
+    """Router + routed experts (+ optional shared experts)."""
+
+    def __init__(self, hidden_size: int, moe_intermediate_size: int, num_experts: int, top_k: int, *,
+                 act: str = "silu", norm_topk_prob: bool = True, scoring: str = "softmax",
+                 routed_scaling_factor: float = 1.0, n_group: int = 1, topk_group: int = 1,
+                 use_score_bias: bool = False, router_bias: bool = False, shared_intermediate_size: int = 0,
+                 shared_gate: bool = False, dtype=torch.float32, init_std: float = 0.02, expert_init_std: float = 0.01,
+                 ep_size: int = 1, ep_rank: int = 0, ep_group=None, tp_size: int = 1, tp_rank: int = 0,
+                 tp_group=None, router_dtype=None):
+        super().__init__()
+        if num_experts % ep_size:
+            raise ValueError(f"{num_experts} experts not divisible by ep={ep_size}")
+        self.hidden_size, self.num_experts, self.top_k = hidden_size, num_experts, top_k
+        self.act, self.norm_topk_prob, self.scoring = act, norm_topk_prob, scoring
+        self.routed_scaling_factor = routed_scaling_factor
+        self.n_group, self.topk_group = n_group, topk_group
+        self.ep_size, self.ep_rank, self.ep_group = ep_size, ep_rank, ep_group
+        self.num_local_experts = num_experts // ep_size
+        self.gate = ColumnParallelLinear(hidden_size, num_experts, bias=router_bias, dtype=router_dtype or dtype,
+                                         init_std=init_std)
+        self.e_score_correction_bias = nn.Parameter(torch.zeros(num_experts, dtype=torch.float32)) \
+            if use_score_bias else None
+        self.gate_up_proj = MoELinear(self.num_local_experts, hidden_size, 2 * moe_intermediate_size, dtype,
+                                      expert_init_std, "column")
+        self.down_proj = MoELinear(self.num_local_experts, moe_intermediate_size, hidden_size, dtype,
+                                   expert_init_std, "row")
+        self.shared_experts = None
+        self.shared_expert_gate = None
+        if shared_intermediate_size > 0:
+            self.shared_experts = GatedMLP(hidden_size, shared_intermediate_size, act, False, dtype, init_std,
+                                           tp_size, tp_rank, tp_group)
+            if shared_gate:
+                self.shared_expert_gate = ColumnParallelLinear(hidden_size, 1, bias=False, dtype=dtype,
+                                                               init_std=init_std)
+
+    # ------------------------------------------------------------------ routing
+    def route(self, logits: torch.Tensor):
+        """Returns (weights [T,k] fp32, idx [T,k] int64, probs [T,E] fp32)."""
+        lf = logits.float()
+        probs = torch.softmax(lf, dim=-1) if self.scoring == "softmax" else torch.sigmoid(lf)
+        scores = probs
+        if self.e_score_correction_bias is not None:
+            scores = probs + self.e_score_correction_bias
+        if self.n_group > 1:
+            T, E = scores.shape
+            g = scores.view(T, self.n_group, E // self.n_group)
+            if self.e_score_correction_bias is not None:
+                gscore = g.topk(2, dim=-1).values.sum(-1)
+            else:
+                gscore = g.max(-1).values
+            gidx = gscore.topk(self.topk_group, dim=-1).indices
+            gmask = torch.zeros_like(gscore).scatter_(1, gidx, 1.0)
+            scores = (g * gmask[..., None]).masked_fill(gmask[..., None] == 0, float("-inf")
+                                                        if self.e_score_correction_bias is None else 0.0).view(T, E)
+        idx = scores.topk(self.top_k, dim=-1).indices
+        w = probs.gather(-1, idx)
+        if self.norm_topk_prob:
+            w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
+        w = w * self.routed_scaling_factor
+        return w, idx, probs
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, x: torch.Tensor):
+        """x ``[B,T,H]`` -> (y ``[B,T,H]``, router_logits ``[B*T,E]``)."""
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        logits = self.gate(x2)
+        w, idx, _ = self.route(logits)
+        if self.ep_size > 1:
+            from ..parallel import ep as epar
+
+            y = epar.expert_parallel_ffn(self, x2, w, idx)
+        else:
+            y = G.moe_ffn(x2, self.gate_up_proj.weight, self.down_proj.weight, w, idx, self.act)
+        if self.shared_experts is not None:
+            s = self.shared_experts(x2)
+            if self.shared_expert_gate is not None:
+                s = s * torch.sigmoid(self.shared_expert_gate(x2).float()).to(s.dtype)
+            y = y + s
+        return y.view(shape), logits

@@ -1,0 +1,4 @@
+"""Model families. Importing this package registers every family with the registry."""
+
+from . import llama  # noqa: F401
+from .llama import *  # noqa: F401,F403

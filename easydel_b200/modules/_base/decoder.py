@@ -1,0 +1,443 @@
+"""Spec-driven decoder-only transformer shared by the model families.
+
+Each family (``modules/<name>``) maps its Hugging Face style config onto an :class:`ArchSpec`
+(normalisation kind, MLP kind, positional scheme, QK-norm, sliding-window layout, MoE layout,
+soft-caps, tying, residual topology...) and registers thin subclasses of the classes here. The
+layer loop keeps the residual stream and the not-yet-added branch output as a pair so that every
+residual add is fused into the following RMSNorm kernel.
+
+Reference structure being covered: ``LlamaDecoderLayer`` / ``LlamaModel`` / ``LlamaForCausalLM``
+(easydel/modules/llama/modeling_llama.py:165-564) and the task heads in
+easydel/modules/_base/causal_lm_module.py:84-627.
+"""
+
+from __future__ import annotations
+
+import typing as tp
+from dataclasses import dataclass, field
+
+import torch
+from torch import nn
+from torch.utils.checkpoint import checkpoint
+
+from ...infra.base_module import EasyDeLBaseModule
+from ...infra.loss_utils import (LossConfig, LossMetrics, ForSequenceClassificationLoss,
+                                 auxiliary_load_balancing_loss_func, causal_lm_loss_from_hidden)
+from ...infra.modeling_outputs import (BaseModelOutput, CausalLMOutput, MoeCausalLMOutput, MoeModelOutput,
+                                       SequenceClassifierOutput)
+from ...layers.attention import Attention
+from ...layers.embeddings import Embed
+from ...layers.linears import ColumnParallelLinear
+from ...layers.mlp import GatedMLP, PlainMLP
+from ...layers.moe import MoEBlock
+from ...layers.norms import LayerNorm, RMSNorm
+from ...ops import functional as F
+
+
+@dataclass
+class MoESpec:
+    num_experts: int
+    top_k: int
+    intermediate_size: int
+    norm_topk_prob: bool = True
+    scoring: str = "softmax"
+    routed_scaling_factor: float = 1.0
+    n_group: int = 1
+    topk_group: int = 1
+    use_score_bias: bool = False
+    router_bias: bool = False
+    shared_intermediate_size: int = 0
+    shared_gate: bool = False
+    layers: tuple[int, ...] | None = None   # None = every layer
+    aux_loss_coef: float = 0.0
+    expert_init_std: float = 0.01
+
+
+@dataclass
+class ArchSpec:
+    hidden_size: int
+    num_layers: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    intermediate_size: int
+    vocab_size: int
+    max_position: int = 4096
+    norm: str = "rms"                 # rms | layer
+    norm_eps: float = 1e-6
+    norm_offset: float = 0.0          # Gemma: weights stored as (w - 1)
+    norm_bias: bool = True            # LayerNorm only
+    act: str = "silu"
+    mlp: str = "gated"                # gated | plain
+    mlp_bias: bool = False
+    attn_bias: bool = False
+    o_bias: bool = False
+    qk_norm: str | None = None
+    rope: dict | None = None          # kwargs of layers.rotary.get_rope minus head_size; None = no RoPE
+    rope_local: dict | None = None    # separate table for sliding layers (Gemma3)
+    pos_emb: str = "rope"             # rope | learned | alibi | none
+    learned_pos_offset: int = 0
+    tie_embeddings: bool = False
+    embed_scale: float | None = None
+    logit_softcap: float = 0.0
+    attn_softcap: float = 0.0
+    attn_scale: float | None = None
+    sliding_window: int | None = None
+    layer_types: tuple[str, ...] | None = None  # per layer: "full" | "sliding" | "nope" (full, no rope)
+    residual: str = "pre"             # pre | parallel | post (norm applied to the branch output, OLMo2)
+    sandwich_norm: bool = False       # extra norms after attention / MLP outputs (Gemma2/3)
+    shared_parallel_norm: bool = True  # parallel residual with one norm (GPT-J, Phi) vs two (NeoX)
+    use_sinks: bool = False
+    moe: MoESpec | None = None
+    lm_head_bias: bool = False
+    final_norm: bool = True
+    embed_layernorm: bool = False
+    init_std: float = 0.02
+    clip_qkv: float | None = None
+    logit_scale: float | None = None  # Cohere / Granite style multiplier on logits
+    residual_multiplier: float | None = None
+    embedding_multiplier: float | None = None
+
+
+def _norm(spec: ArchSpec, dtype) -> nn.Module:
+    if spec.norm == "rms":
+        return RMSNorm(spec.hidden_size, spec.norm_eps, dtype, offset=spec.norm_offset)
+    return LayerNorm(spec.hidden_size, spec.norm_eps, bias=spec.norm_bias, dtype=dtype)
+
+
+def _tp_of(config) -> tuple[int, int, tp.Any]:
+    mesh = config.mesh
+    if mesh.tp > 1:
+        return mesh.tp, mesh.axis_index("tp"), mesh.get_group("tp")
+    return 1, 0, None
+
+
+def _ep_of(config) -> tuple[int, int, tp.Any]:
+    mesh = config.mesh
+    if mesh.ep > 1:
+        return mesh.ep, mesh.axis_index("ep"), mesh.get_group("ep")
+    return 1, 0, None
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, config, spec: ArchSpec, layer_idx: int, dtype):
+        super().__init__()
+        self.spec, self.layer_idx = spec, layer_idx
+        tp_size, tp_rank, tp_group = _tp_of(config)
+        ltype = spec.layer_types[layer_idx] if spec.layer_types else ("sliding" if spec.sliding_window else "full")
+        window = spec.sliding_window if ltype == "sliding" else None
+        rope = spec.rope if spec.pos_emb == "rope" else None
+        if ltype == "sliding" and spec.rope_local is not None:
+            rope = spec.rope_local
+        if ltype == "nope":
+            rope = None
+        self.self_attn = Attention(
+            spec.hidden_size, spec.num_heads, spec.num_kv_heads, spec.head_dim, layer_idx=layer_idx,
+            bias=spec.attn_bias, o_bias=spec.o_bias, qk_norm=spec.qk_norm, qk_norm_eps=spec.norm_eps, rope=rope,
+            sliding_window=window, softcap=spec.attn_softcap, scale=spec.attn_scale, use_sinks=spec.use_sinks,
+            use_alibi=spec.pos_emb == "alibi", clip_qkv=spec.clip_qkv, dtype=dtype, init_std=spec.init_std,
+            tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group, qk_norm_offset=spec.norm_offset)
+        moe = spec.moe
+        self.is_moe = moe is not None and (moe.layers is None or layer_idx in moe.layers)
+        if self.is_moe:
+            ep_size, ep_rank, ep_group = _ep_of(config)
+            self.mlp = MoEBlock(spec.hidden_size, moe.intermediate_size, moe.num_experts, moe.top_k, act=spec.act,
+                                norm_topk_prob=moe.norm_topk_prob, scoring=moe.scoring,
+                                routed_scaling_factor=moe.routed_scaling_factor, n_group=moe.n_group,
+                                topk_group=moe.topk_group, use_score_bias=moe.use_score_bias,
+                                router_bias=moe.router_bias, shared_intermediate_size=moe.shared_intermediate_size,
+                                shared_gate=moe.shared_gate, dtype=dtype, init_std=spec.init_std,
+                                expert_init_std=moe.expert_init_std, ep_size=ep_size, ep_rank=ep_rank,
+                                ep_group=ep_group, tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group)
+        elif spec.mlp == "gated":
+            self.mlp = GatedMLP(spec.hidden_size, spec.intermediate_size, spec.act, spec.mlp_bias, dtype,
+                                spec.init_std, tp_size, tp_rank, tp_group)
+        else:
+            self.mlp = PlainMLP(spec.hidden_size, spec.intermediate_size, spec.act, spec.mlp_bias, dtype,
+                                spec.init_std, tp_size, tp_rank, tp_group)
+        if spec.residual == "post":
+            self.post_attention_layernorm = _norm(spec, dtype)
+            self.post_feedforward_layernorm = _norm(spec, dtype)
+        else:
+            self.input_layernorm = _norm(spec, dtype)
+            if spec.residual == "pre" or not spec.shared_parallel_norm:
+                self.post_attention_layernorm = _norm(spec, dtype)
+            if spec.sandwich_norm:
+                self.post_attn_out_layernorm = _norm(spec, dtype)
+                self.pre_feedforward_layernorm = _norm(spec, dtype)
+                self.post_feedforward_layernorm = _norm(spec, dtype)
+
+    # The pair (x, pending) means the residual stream is x + pending; `pending` is folded in by the
+    # next fused add+norm. Returns (x, pending, router_logits).
+    def forward(self, x, pending, positions, segment_ids=None, cache_view=None, attn_meta=None):
+        spec = self.spec
+        rl = None
+        fused = spec.norm == "rms" and spec.residual == "pre" and not spec.sandwich_norm \
+            and spec.residual_multiplier is None
+        if fused:
+            if pending is None:
+                h = self.input_layernorm(x)
+            else:
+                h, x = self.input_layernorm.forward_with_residual(pending, x)
+            a = self.self_attn(h, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
+            h, x = self.post_attention_layernorm.forward_with_residual(a, x)
+            m = self.mlp(h)
+            if self.is_moe:
+                m, rl = m
+            return x, m, rl
+        if pending is not None:
+            x = x + pending
+        rm = spec.residual_multiplier or 1.0
+        if spec.residual == "parallel":
+            h = self.input_layernorm(x)
+            a = self.self_attn(h, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
+            h2 = h if spec.shared_parallel_norm else self.post_attention_layernorm(x)
+            m = self.mlp(h2)
+            if self.is_moe:
+                m, rl = m
+            return x + a + m, None, rl
+        if spec.residual == "post":
+            a = self.self_attn(x, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
+            x = x + self.post_attention_layernorm(a)
+            m = self.mlp(x)
+            if self.is_moe:
+                m, rl = m
+            return x + self.post_feedforward_layernorm(m), None, rl
+        h = self.input_layernorm(x)
+        a = self.self_attn(h, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
+        if spec.sandwich_norm:
+            a = self.post_attn_out_layernorm(a)
+        x = x + a * rm
+        h = (self.pre_feedforward_layernorm if spec.sandwich_norm else self.post_attention_layernorm)(x)
+        m = self.mlp(h)
+        if self.is_moe:
+            m, rl = m
+        if spec.sandwich_norm:
+            m = self.post_feedforward_layernorm(m)
+        return x + m * rm, None, rl
+
+
+class DecoderModel(EasyDeLBaseModule):
+    """Embedding -> N decoder layers -> final norm."""
+
+    spec_fn: tp.Callable[[tp.Any], ArchSpec] | None = None
+
+    def __init__(self, config, dtype=torch.bfloat16, param_dtype=None, precision=None, rngs=None):
+        super().__init__(config, dtype, param_dtype, precision, rngs)
+        spec = type(self).spec_fn(config)
+        self.spec = spec
+        pd = self.param_dtype
+        self.embed_tokens = Embed(spec.vocab_size, spec.hidden_size, pd, spec.init_std,
+                                  getattr(config, "pad_token_id", None) if False else None)
+        if spec.pos_emb == "learned":
+            self.embed_positions = Embed(spec.max_position + spec.learned_pos_offset, spec.hidden_size, pd,
+                                         spec.init_std)
+        if spec.embed_layernorm:
+            self.embed_layernorm = _norm(spec, pd)
+        self.layers = nn.ModuleList([DecoderLayer(config, spec, i, pd) for i in range(spec.num_layers)])
+        if spec.final_norm:
+            self.norm = _norm(spec, pd)
+
+    def get_input_embeddings(self):
+        return self.embed_tokens
+
+    def _run_layer(self, layer, x, pending, positions, segment_ids, cache_view, attn_meta, policy):
+        if policy and self.training and torch.is_grad_enabled() and cache_view is None:
+            return checkpoint(layer, x, pending, positions, segment_ids, None, None, use_reentrant=False)
+        return layer(x, pending, positions, segment_ids, cache_view, attn_meta)
+
+    def forward(self, input_ids: torch.Tensor | None = None, attention_mask: torch.Tensor | None = None,
+                position_ids: torch.Tensor | None = None, segment_ids: torch.Tensor | None = None,
+                inputs_embeds: torch.Tensor | None = None, past_key_values=None, cache_metadata=None,
+                output_hidden_states: bool = False, output_router_logits: bool = False, **_):
+        spec = self.spec
+        if inputs_embeds is None:
+            if input_ids.dim() == 1:
+                input_ids = input_ids[None]
+            x = self.embed_tokens(input_ids)
+        else:
+            x = inputs_embeds
+        B, T = x.shape[:2]
+        if x.dtype != self.dtype and x.is_floating_point():
+            x = x.to(self.dtype)
+        if spec.embed_scale is not None:
+            x = x * torch.tensor(spec.embed_scale, dtype=x.dtype, device=x.device)
+        if spec.embedding_multiplier is not None:
+            x = x * spec.embedding_multiplier
+        if position_ids is None:
+            start = 0
+            if past_key_values is not None and hasattr(past_key_values, "seq_len"):
+                start = past_key_values.seq_len()
+            if segment_ids is not None:
+                position_ids = _positions_from_segments(segment_ids)
+            elif attention_mask is not None and past_key_values is None:
+                position_ids = (attention_mask.long().cumsum(-1) - 1).clamp_min(0)
+            else:
+                position_ids = torch.arange(start, start + T, device=x.device)[None].expand(B, T)
+        if position_ids.dim() == 1:
+            position_ids = position_ids[None].expand(B, T)
+        if segment_ids is None and attention_mask is not None and past_key_values is None and T > 1:
+            # padding -> segment 0 (isolated), real tokens -> segment 1
+            if not bool(attention_mask.all()):
+                segment_ids = attention_mask.to(torch.int32)
+        if spec.pos_emb == "learned":
+            x = x + self.embed_positions(position_ids + spec.learned_pos_offset)
+        if spec.embed_layernorm:
+            x = self.embed_layernorm(x)
+        policy = self.gradient_checkpointing_policy() not in ("", "everything_saveable")
+        pending = None
+        all_hidden = [] if output_hidden_states else None
+        router_logits = []
+        for i, layer in enumerate(self.layers):
+            if output_hidden_states:
+                all_hidden.append(x if pending is None else x + pending)
+            view = past_key_values.view(i) if past_key_values is not None else None
+            x, pending, rl = self._run_layer(layer, x, pending, position_ids, segment_ids, view, cache_metadata,
+                                             policy)
+            if rl is not None:
+                router_logits.append(rl)
+        if spec.final_norm:
+            if pending is not None and spec.norm == "rms":
+                x, _ = self.norm.forward_with_residual(pending, x)
+            else:
+                x = self.norm(x if pending is None else x + pending)
+        elif pending is not None:
+            x = x + pending
+        if output_hidden_states:
+            all_hidden.append(x)
+        cls = MoeModelOutput if spec.moe is not None else BaseModelOutput
+        kw = dict(last_hidden_state=x, hidden_states=tuple(all_hidden) if all_hidden else None,
+                  past_key_values=past_key_values)
+        if spec.moe is not None:
+            kw["router_logits"] = tuple(router_logits) if router_logits else None
+        return cls(**kw)
+
+
+def _positions_from_segments(segment_ids: torch.Tensor) -> torch.Tensor:
+    """Positions restart at 0 at every segment boundary of a packed row."""
+    B, T = segment_ids.shape
+    idx = torch.arange(T, device=segment_ids.device)[None].expand(B, T)
+    change = torch.ones_like(segment_ids, dtype=torch.bool)
+    change[:, 1:] = segment_ids[:, 1:] != segment_ids[:, :-1]
+    start = torch.where(change, idx, torch.zeros_like(idx)).cummax(dim=1).values
+    return idx - start
+
+
+class DecoderForCausalLM(EasyDeLBaseModule):
+    """Backbone + LM head. ``apply_lm_head=False`` returns hidden states only (chunked loss, serving)."""
+
+    backbone_cls: type[DecoderModel] = DecoderModel
+    loss_type = "ForCausalLM"
+
+    def __init__(self, config, dtype=torch.bfloat16, param_dtype=None, precision=None, rngs=None):
+        super().__init__(config, dtype, param_dtype, precision, rngs)
+        self.model = type(self).backbone_cls(config, dtype, param_dtype, precision, rngs)
+        spec = self.model.spec
+        self.spec = spec
+        if not spec.tie_embeddings:
+            tp_size, tp_rank, tp_group = 1, 0, None  # vocab-parallel head is set up by parallel.tp when enabled
+            self.lm_head = ColumnParallelLinear(spec.hidden_size, spec.vocab_size, bias=spec.lm_head_bias,
+                                                dtype=self.param_dtype, init_std=spec.init_std)
+        else:
+            self.lm_head = None
+
+    def can_generate(self) -> bool:
+        return True
+
+    def get_input_embeddings(self):
+        return self.model.embed_tokens
+
+    def lm_head_weight(self) -> torch.Tensor:
+        return self.model.embed_tokens.weight if self.lm_head is None else self.lm_head.weight
+
+    def lm_head_bias(self):
+        return None if self.lm_head is None else self.lm_head.bias
+
+    def apply_lm_head(self, hidden: torch.Tensor) -> torch.Tensor:
+        spec = self.spec
+        logits = F.linear(hidden, self.lm_head_weight(), self.lm_head_bias())
+        if spec.logit_scale is not None:
+            logits = logits * spec.logit_scale
+        if spec.logit_softcap:
+            logits = torch.tanh(logits.float() / spec.logit_softcap).mul_(spec.logit_softcap).to(logits.dtype)
+        return logits
+
+    def make_lm_head_fn(self):
+        return self.apply_lm_head
+
+    def forward(self, input_ids=None, attention_mask=None, position_ids=None, segment_ids=None, inputs_embeds=None,
+                past_key_values=None, cache_metadata=None, output_hidden_states=False, output_router_logits=False,
+                apply_lm_head: bool = True, labels: torch.Tensor | None = None, **kw):
+        out = self.model(input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
+                         segment_ids=segment_ids, inputs_embeds=inputs_embeds, past_key_values=past_key_values,
+                         cache_metadata=cache_metadata, output_hidden_states=output_hidden_states,
+                         output_router_logits=output_router_logits)
+        hidden = out.last_hidden_state
+        logits = self.apply_lm_head(hidden) if apply_lm_head else None
+        rl = getattr(out, "router_logits", None)
+        if self.spec.moe is not None:
+            aux = None
+            if rl and self.spec.moe.aux_loss_coef:
+                aux = auxiliary_load_balancing_loss_func(rl, self.spec.moe.num_experts, self.spec.moe.top_k,
+                                                         attention_mask)
+            return MoeCausalLMOutput(logits=logits, last_hidden_state=hidden, hidden_states=out.hidden_states,
+                                     past_key_values=out.past_key_values, router_logits=rl, aux_loss=aux)
+        return CausalLMOutput(logits=logits, last_hidden_state=hidden, hidden_states=out.hidden_states,
+                              past_key_values=out.past_key_values)
+
+    def _compute_task_loss(self, labels, loss_config: LossConfig, loss_scale, call, loss_kwargs):
+        call = dict(call)
+        call["apply_lm_head"] = False
+        attention_mask = call.get("attention_mask")
+        out = self(**call)
+        if attention_mask is not None:
+            labels = torch.where(attention_mask.bool(), labels, torch.full_like(labels, loss_config.ignore_index))
+        spec = self.spec
+        hidden = out.last_hidden_state
+        if spec.logit_scale is not None:
+            hidden = hidden * spec.logit_scale
+        metrics = causal_lm_loss_from_hidden(hidden, self.lm_head_weight(), labels, loss_config,
+                                             lm_head_bias=self.lm_head_bias(), softcap=spec.logit_softcap,
+                                             chunk_size=getattr(self.config, "lmhead_chunksize", None),
+                                             loss_scale=loss_scale, **loss_kwargs)
+        aux = getattr(out, "aux_loss", None)
+        if aux is not None and spec.moe is not None and spec.moe.aux_loss_coef:
+            # the auxiliary loss is added to the training loss (easydel/infra/base_module.py:2791-2793)
+            metrics.loss = metrics.loss + spec.moe.aux_loss_coef * aux * loss_scale
+            metrics.other_metrics = {"aux_loss": aux.detach()}
+        return out, metrics
+
+
+class DecoderForSequenceClassification(EasyDeLBaseModule):
+    backbone_cls: type[DecoderModel] = DecoderModel
+    loss_type = "ForSequenceClassification"
+
+    def __init__(self, config, dtype=torch.bfloat16, param_dtype=None, precision=None, rngs=None):
+        super().__init__(config, dtype, param_dtype, precision, rngs)
+        self.model = type(self).backbone_cls(config, dtype, param_dtype, precision, rngs)
+        self.num_labels = getattr(config, "num_labels", 2)
+        self.score = ColumnParallelLinear(self.model.spec.hidden_size, self.num_labels, bias=False,
+                                          dtype=self.param_dtype, init_std=self.model.spec.init_std)
+
+    def forward(self, input_ids=None, attention_mask=None, position_ids=None, segment_ids=None, inputs_embeds=None,
+                labels=None, **kw):
+        out = self.model(input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
+                         segment_ids=segment_ids, inputs_embeds=inputs_embeds)
+        h = out.last_hidden_state
+        B, T = h.shape[:2]
+        if attention_mask is not None:
+            last = (attention_mask.long() * torch.arange(T, device=h.device)[None]).argmax(-1)
+        elif input_ids is not None and getattr(self.config, "pad_token_id", None) is not None:
+            nonpad = (input_ids != self.config.pad_token_id).long()
+            last = (nonpad * torch.arange(T, device=h.device)[None]).argmax(-1)
+        else:
+            last = torch.full((B,), T - 1, device=h.device, dtype=torch.long)
+        pooled = h[torch.arange(B, device=h.device), last]
+        logits = self.score(pooled)
+        return SequenceClassifierOutput(logits=logits, hidden_states=out.hidden_states)
+
+    def _compute_task_loss(self, labels, loss_config, loss_scale, call, loss_kwargs):
+        out = self(**call)
+        m = ForSequenceClassificationLoss(out.logits, labels, loss_config)
+        m.loss = m.loss * loss_scale
+        return out, m
