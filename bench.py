@@ -1,0 +1,249 @@
+"""Headline benchmark: Llama-3-8B SFT step throughput (tokens/s over all GPUs of one node).
+
+``python bench.py --gpus N --steps K --warmup W`` (launched under ``torch.distributed.run`` for
+N > 1) trains a random-init Llama-3-8B in bf16 with fp32 master weights / AdamW, full activation
+checkpointing and sequence-packed synthetic documents (lengths uniform in [256, 4096], tokens
+uniform in [0, 128256), packed to 8192). Per-GPU work is fixed (8 sequences of 8192 per step, as
+8 micro-batches), so the global batch is ``8 * N`` sequences: 64 at N = 8 (weak scaling).
+
+Two measurements, both through ``easydel_b200.trainers.Trainer``:
+
+* ``value``: K optimizer steps on device-resident batches, CUDA events around the K steps,
+  barrier + synchronize on both sides, max over ranks.
+* ``e2e``: the same K steps driven by ``Trainer.train()`` from pinned host batches; every step
+  copies its batch host->device and reads the loss back device->host.
+
+``--impl reference`` reports whether the unmodified reference can run here.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+SEQ = 8192
+PER_GPU_SEQS = 8
+VOCAB = 128256
+MODEL_NAME = "llama-3-8b"
+
+
+def reference_arm(args) -> None:
+    why = ("reference (EasyDeL, JAX) cannot be installed offline: pip reports build backend 'uv_build' missing, and "
+           "its runtime dependencies jax/jaxlib/flax/optax/eformer/ejkernel are not in the image or wheelhouse")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+
+
+def synth_packed_batches(n_batches: int, per_batch: int, seed: int) -> list[dict]:
+    """First-fit packing of synthetic documents into rows of SEQ tokens (host tensors)."""
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(n_batches):
+        ids = torch.empty(per_batch, SEQ, dtype=torch.int64)
+        seg = torch.zeros(per_batch, SEQ, dtype=torch.int32)
+        for r in range(per_batch):
+            pos, s = 0, 1
+            while pos < SEQ:
+                L = int(torch.randint(256, 4097, (1,), generator=g))
+                L = min(L, SEQ - pos)
+                ids[r, pos:pos + L] = torch.randint(0, VOCAB, (L,), generator=g)
+                seg[r, pos:pos + L] = s
+                pos += L
+                s += 1
+        out.append({"input_ids": ids, "labels": ids.clone(), "segment_ids": seg})
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i",
+                                          str(self.index), "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 4), ("hw_thermal_slowdown", 5), ("sw_thermal_slowdown", 6),
+                              ("sw_power_cap", 7)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=32, help="debug only; the reported config requires 32")
+    ap.add_argument("--doc-mask", action="store_true",
+                    help="mask attention across packed documents (the reference attends across them)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch.distributed as dist
+
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+    from easydel_b200.ops import _lib
+    from easydel_b200.parallel.mesh import init_distributed
+    from easydel_b200.trainers import Trainer, TrainingArguments
+
+    rank, local, world = init_distributed()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+
+    cfg = LlamaConfig(vocab_size=VOCAB, hidden_size=4096, intermediate_size=14336, num_hidden_layers=args.layers,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5,
+                      rope_theta=500000.0, max_position_embeddings=SEQ, tie_word_embeddings=False,
+                      gradient_checkpointing="nothing_saveable", sharding_axis_dims=(1, -1, 1, 1, 1),
+                      lmhead_chunksize=2048)
+    model = LlamaForCausalLM.sequential_init(cfg, dtype=torch.bfloat16, param_dtype=torch.bfloat16, device=dev,
+                                             seed=1234)
+    K, W = args.steps, args.warmup
+    targs = TrainingArguments(model_name="bench", save_directory=None, total_batch_size=PER_GPU_SEQS * world,
+                              gradient_accumulation_steps=PER_GPU_SEQS, learning_rate=1e-5, weight_decay=0.01,
+                              optimizer="adamw", scheduler="none", clip_grad=1.0, max_training_steps=2 * (K + W),
+                              max_length=SEQ, do_last_save=False, resume_if_possible=False, use_wandb=False,
+                              report_metrics=False, progress_bar_type="none", report_steps=1, log_grad_norms=False,
+                              extra_optimizer_kwargs={"b1": 0.9, "b2": 0.95, "eps": 1e-8})
+
+    host_batches = synth_packed_batches(K + W, PER_GPU_SEQS, seed=100 + rank)
+    if not args.doc_mask:
+        for b in host_batches:
+            b.pop("segment_ids")
+    host_batches = [{k: v.pin_memory() for k, v in b.items()} for b in host_batches]
+
+    class _Batches:
+        already_batched = True
+
+        def __len__(self):
+            return len(host_batches)
+
+        def __iter__(self):
+            return iter(host_batches)
+
+    trainer = Trainer(arguments=targs, model=model, dataset_train=_Batches())
+    tokens_per_step = PER_GPU_SEQS * SEQ * world
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------- device-timed: batches already on the device
+    dev_batches = [{k: v.to(dev) for k, v in b.items()} for b in host_batches]
+    for i in range(W):
+        trainer.training_step(dev_batches[i])
+    sync()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        loss, _, _ = trainer.training_step(dev_batches[W + i])
+    e1.record()
+    sync()
+    launches = _lib.launch_count - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = ms.item() / K
+    _lib.check_status()
+    final_loss = float(loss)
+    del dev_batches
+
+    # ---------------- end to end: Trainer.train() from pinned host memory, loss read back every step
+    marks = {}
+
+    def on_end(tr, step):
+        if step == trainer_start + W:
+            sync()
+            marks["t0"] = time.perf_counter()
+
+    trainer_start = trainer.model_state.step
+    trainer.max_training_steps = trainer_start + W + K
+    trainer.arguments.performance_mode = False   # report (and read back) the loss every step
+    trainer.arguments.report_metrics = True
+    trainer.arguments.report_steps = 1
+    trainer.register_hook("on_step_end", on_end)
+    trainer.train()
+    sync()
+    t1 = time.perf_counter()
+    e2e_s = torch.tensor([t1 - marks["t0"]], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
+    e2e_tok_s = tokens_per_step * K / e2e_s.item()
+    h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
+
+    if rank == 0:
+        value = tokens_per_step / (ms_per_step / 1e3)
+        print(json.dumps({
+            "metric": "SFT tokens/sec/box Llama-3-8B", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "config": {"model": MODEL_NAME, "layers": args.layers, "global_batch": PER_GPU_SEQS * world,
+                       "seq_len": SEQ, "micro_batch": 1, "grad_accum": PER_GPU_SEQS,
+                       "parallelism": f"fsdp{world}" if world > 1 else "single",
+                       "activation_checkpointing": "full", "optimizer": "adamw fp32 master+moments",
+                       "attention": "document-masked varlen" if args.doc_mask else
+                       "causal over the whole 8192-token pack (what the reference computes for Llama)",
+                       "l2": "weights (16 GB) and activations stream through every step; working set >> 126 MB L2",
+                       "final_loss": final_loss},
+            "clocks": clocks,
+            "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+        }))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,48 @@
+"""easydel_b200: a Blackwell-native (sm_100a) LLM training and serving framework with EasyDeL's surface."""
+
+__version__ = "0.1.0"
+
+import importlib as _importlib
+import typing as _tp
+
+_LAZY: dict[str, str] = {
+    # infra
+    "EasyDeLBaseConfig": "easydel_b200.infra.base_config", "EasyDeLBaseConfigDict": "easydel_b200.infra.base_config",
+    "PartitionAxis": "easydel_b200.infra.base_config",
+    "EasyDeLBaseModule": "easydel_b200.infra.base_module", "EasyDeLState": "easydel_b200.infra.base_state",
+    "LossConfig": "easydel_b200.infra.loss_utils", "LossMetrics": "easydel_b200.infra.loss_utils",
+    "TaskType": "easydel_b200.infra.factory", "ConfigType": "easydel_b200.infra.factory",
+    "register_config": "easydel_b200.infra.factory", "register_module": "easydel_b200.infra.factory",
+    "get_modules_by_type": "easydel_b200.infra.factory",
+    "EasyDeLOptimizers": "easydel_b200.infra.etils", "EasyDeLSchedulers": "easydel_b200.infra.etils",
+    "EasyDeLGradientCheckPointers": "easydel_b200.infra.etils", "AttentionMechanisms": "easydel_b200.infra.etils",
+    # trainers
+    "TrainingArguments": "easydel_b200.trainers", "Trainer": "easydel_b200.trainers",
+    "BaseTrainer": "easydel_b200.trainers", "TrainerOutput": "easydel_b200.trainers",
+    "LogWatcher": "easydel_b200.trainers",
+    # models
+    "LlamaConfig": "easydel_b200.modules.llama", "LlamaModel": "easydel_b200.modules.llama",
+    "LlamaForCausalLM": "easydel_b200.modules.llama",
+    "LlamaForSequenceClassification": "easydel_b200.modules.llama",
+}
+
+
+def _register_lazy(names: dict[str, str]) -> None:
+    _LAZY.update(names)
+
+
+def __getattr__(name: str) -> _tp.Any:
+    if name in _LAZY:
+        return getattr(_importlib.import_module(_LAZY[name]), name)
+    try:
+        from . import _exports
+
+        if name in _exports.LAZY:
+            return getattr(_importlib.import_module(_exports.LAZY[name]), name)
+    except ImportError:
+        pass
+    raise AttributeError(f"module 'easydel_b200' has no attribute {name!r}")
+
+
+def __dir__():
+    return sorted(list(globals()) + list(_LAZY))

@@ -28,11 +28,12 @@ class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias):
         x2 = _as_2d(x)
-        y = K.gemm(x2, w, bias=bias)
+        y = torch.empty((*x.shape[:-1], w.shape[0]), dtype=x.dtype, device=x.device)
+        K.gemm(x2, w, bias=bias, out=y.view(-1, w.shape[0]))
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.x_shape = x.shape
-        return y.view(*x.shape[:-1], w.shape[0])
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -40,7 +41,8 @@ class _LinearFn(torch.autograd.Function):
         dy2 = _as_2d(dy)
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = K.gemm(dy2, w, b_mn=True).view(ctx.x_shape)
+            dx = torch.empty(ctx.x_shape, dtype=dy.dtype, device=dy.device)
+            K.gemm(dy2, w, b_mn=True, out=dx.view(-1, w.shape[1]))
         if ctx.needs_input_grad[1]:
             mg = getattr(w, "main_grad", None)
             if mg is not None:
@@ -139,11 +141,10 @@ class _RopeFn(torch.autograd.Function):
     def forward(ctx, x, pos, cos, sin, nheads, head_dim, col0, rot_dim, interleaved):
         ctx.save_for_backward(pos, cos, sin)
         ctx.args = (nheads, head_dim, col0, rot_dim, interleaved)
-        shape = x.shape
-        x2 = x.reshape(-1, shape[-1])
-        K.rope_(x2, pos, cos, sin, nheads, head_dim, col0=col0, rot_dim=rot_dim, interleaved=interleaved)
-        ctx.mark_dirty(x)
-        return x
+        y = x.clone(memory_format=torch.contiguous_format)
+        K.rope_(y.view(-1, y.shape[-1]), pos, cos, sin, nheads, head_dim, col0=col0, rot_dim=rot_dim,
+                interleaved=interleaved)
+        return y
 
     @staticmethod
     def backward(ctx, dx):
@@ -159,15 +160,9 @@ def rope_packed(qkv: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: to
                 head_dim: int, col0: int = 0, rot_dim: int | None = None, interleaved: bool = False):
     """Rotates the first ``nheads`` heads (starting at column ``col0``) of a packed ``[T, width]`` projection.
 
-    On the GPU the rotation happens in place on ``qkv`` (which must be a fresh, contiguous activation).
+    Returns a new tensor; the input is left untouched.
     """
     if _lib.use_kernels(qkv):
-        if not qkv.is_contiguous():
-            qkv = qkv.contiguous()
-        elif qkv.requires_grad and qkv.is_leaf:
-            qkv = qkv.clone()
-        elif not qkv.requires_grad:
-            qkv = qkv.clone() if qkv._base is not None else qkv
         return _RopeFn.apply(qkv, pos.reshape(-1), cos, sin, nheads, head_dim, col0, rot_dim, interleaved)
     T = qkv.reshape(-1, qkv.shape[-1]).shape[0]
     flat = qkv.reshape(T, -1)
@@ -216,7 +211,7 @@ class _LinearCEFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, h, w, labels, bias, ignore_index, label_smoothing, z_loss, softcap, chunk, reduction_scale,
-                want_acc):
+                want_acc, grad_enabled):
         T, H = h.shape
         V = w.shape[0]
         dev = h.device
@@ -227,7 +222,7 @@ class _LinearCEFn(torch.autograd.Function):
             gs = (1.0 / n_valid.clamp_min(1.0)).reshape(1)
         else:
             gs = torch.full((1,), float(reduction_scale), dtype=torch.float32, device=dev)
-        need_grad = torch.is_grad_enabled() and (h.requires_grad or w.requires_grad)
+        need_grad = grad_enabled and (h.requires_grad or w.requires_grad)
         losses = torch.empty(T, dtype=torch.float32, device=dev)
         correct = torch.empty(T, dtype=torch.int32, device=dev) if want_acc else None
         dh = torch.empty_like(h) if need_grad and h.requires_grad else None
@@ -271,7 +266,7 @@ class _LinearCEFn(torch.autograd.Function):
             gh = dh * dloss.to(dh.dtype)
         if dw is not None:
             gw = (dw * dloss).to(ctx.w_dtype)
-        return gh, gw, None, None, None, None, None, None, None, None, None
+        return gh, gw, None, None, None, None, None, None, None, None, None, None
 
 
 def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, *, bias=None,
@@ -294,7 +289,7 @@ def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
         if not h2.is_contiguous():
             h2 = h2.contiguous()
         return _LinearCEFn.apply(h2, w, lab, bias, ignore_index, label_smoothing, z_loss, softcap, chunk_size,
-                                 reduction_scale, want_accuracy)
+                                 reduction_scale, want_accuracy, torch.is_grad_enabled())
     total = h2.new_zeros((), dtype=torch.float32)
     correct = h2.new_zeros((), dtype=torch.float32)
     for s in range(0, h2.shape[0], chunk_size):
