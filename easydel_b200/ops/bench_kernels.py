@@ -82,12 +82,83 @@ def bench_gemm(args) -> None:
     _lib.check_status()
 
 
+def bench_attention(args) -> None:
+    from . import attention as A
+
+    pk = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    T, Hq, Hkv, D = args.tokens, 32, 8, 128
+    qkv = torch.randn(1, T, (Hq + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+    q = qkv[..., : Hq * D].view(1, T, Hq, D)
+    k = qkv[..., Hq * D:(Hq + Hkv) * D].view(1, T, Hkv, D)
+    v = qkv[..., (Hq + Hkv) * D:].view(1, T, Hkv, D)
+    do = torch.randn(1, T, Hq, D, device="cuda").to(torch.bfloat16)
+    o, lse = A.attn_fwd(q, k, v, causal=True)
+    ms_f = time_cuda(lambda: A.attn_fwd(q, k, v, causal=True), flush=flush)
+    ms_b = time_cuda(lambda: A.attn_bwd(q, k, v, o, lse, do, causal=True), flush=flush)
+    fl = 4.0 * T * T * D * Hq * 0.5
+    print(f"attention fwd  T={T} Hq={Hq} Hkv={Hkv} D={D} causal: {ms_f:.3f} ms  {fl / ms_f / 1e9:.1f} TFLOP/s "
+          f"({fl / ms_f / 1e9 / pk['tflops']:.2f} of {pk['src']} peak)")
+    print(f"attention bwd  (2.5x fwd FLOPs):                    {ms_b:.3f} ms  {2.5 * fl / ms_b / 1e9:.1f} TFLOP/s "
+          f"({2.5 * fl / ms_b / 1e9 / pk['tflops']:.2f} of {pk['src']} peak)")
+    try:
+        import torch.nn.functional as tF
+
+        qh, kh, vh = (t.transpose(1, 2) for t in (q, k, v))
+        ms_l = time_cuda(lambda: tF.scaled_dot_product_attention(qh, kh, vh, is_causal=True, enable_gqa=True),
+                         flush=flush)
+        print(f"library SDPA fwd:                                   {ms_l:.3f} ms  {fl / ms_l / 1e9:.1f} TFLOP/s")
+    except Exception as e:  # the library baseline is informative only
+        print("library SDPA unavailable:", e)
+    from . import _lib
+
+    _lib.check_status()
+
+
+def bench_layer(args) -> None:
+    """One micro-batch (1 x tokens) forward + backward of a 2-layer Llama-3-8B-shaped model: the
+    launch list of this run under ncu gives the per-kernel time shares of a training step."""
+    from ..infra.base_state import EasyDeLState
+    from ..modules.llama import LlamaConfig, LlamaForCausalLM
+    from ..optimizers import OptimizerFactory, SchedulerConfig
+
+    cfg = LlamaConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=args.layers,
+                      num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-5,
+                      rope_theta=500000.0, max_position_embeddings=args.tokens,
+                      gradient_checkpointing="nothing_saveable", lmhead_chunksize=2048)
+    model = LlamaForCausalLM.sequential_init(cfg, dtype=torch.bfloat16, param_dtype=torch.bfloat16, device="cuda")
+    model.train()
+    tx, _ = OptimizerFactory.create("adamw", SchedulerConfig(None, learning_rate=1e-5), weight_decay=0.01)
+    state = EasyDeLState.create(model=model, tx=tx, init_opt_state=True)
+    ids = torch.randint(0, 128256, (1, args.tokens), device="cuda")
+
+    def step():
+        _, m = model.compute_loss(input_ids=ids, labels=ids)
+        m.loss.backward()
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    step()
+    e.record()
+    torch.cuda.synchronize()
+    state.apply_gradients()
+    torch.cuda.synchronize()
+    from . import _lib
+
+    _lib.check_status()
+    print(f"layers={args.layers} tokens={args.tokens}: fwd+bwd micro-batch {s.elapsed_time(e):.2f} ms")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("what", choices=["gemm"])
+    ap.add_argument("what", choices=["gemm", "attention", "layer"])
     ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=2)
     a = ap.parse_args()
-    {"gemm": bench_gemm}[a.what](a)
+    {"gemm": bench_gemm, "attention": bench_attention, "layer": bench_layer}[a.what](a)
 
 
 if __name__ == "__main__":
