@@ -1,15 +1,19 @@
 // Flash-attention forward on tcgen05 tensor cores (head_dim 64 or 128, bf16, GQA,
 // causal, variable-length batches, sliding window, logit soft-cap, attention sinks).
 //
-// One CTA per (query tile of 128 rows, query head, sequence):
-//   warp 0      TMA producer: Q once, then K/V tiles of 128 keys through a 2-stage ring
-//   warp 1      MMA issuer:   S = Q K^T (both operands K-major in shared memory) and
-//               O += P V (P read from tensor memory, V as an MN-major shared operand)
-//   warps 2..5  softmax: thread i owns query row i; S comes out of tensor memory with
-//               tcgen05.ld, P goes back as packed bf16 with tcgen05.st over the same
-//               columns; O is rescaled in tensor memory only when the running maximum
-//               moved by more than 2^8 (otherwise the stale maximum stays exact).
-// Two S/P buffers let the softmax of tile j overlap the QK^T of tile j+1.
+// One CTA per (block of 256 query rows = two tiles A and B, query head, sequence):
+//   warp 0      TMA producer: both Q tiles once, then K and V tiles of 128 keys through
+//               two independent 2-stage rings (K is released as soon as both QK^T products
+//               of a step are issued, V after both PV products)
+//   warp 1      MMA issuer, software pipelined per key tile j:
+//                   O_A += P_A(j) V(j);  S_A = Q_A K(j+1)^T;  O_B += P_B(j) V(j);  S_B = Q_B K(j+1)^T
+//               so that the softmax of one tile always runs under the two products of the other
+//   warps 2..5  softmax of tile A, warps 6..9 softmax of tile B: thread i owns query row i,
+//               pulls its whole S row (128 fp32) out of tensor memory in one go, finds the row
+//               maximum, exponentiates in registers and writes P back as packed bf16 over the
+//               same tensor-memory columns (the A operand of the PV product). O is rescaled in
+//               tensor memory only when the running maximum moved by more than 2^8.
+// Tensor memory map (512 columns): S_A/P_A [0,128)  S_B/P_B [128,256)  O_A [256,384)  O_B [384,512).
 //
 // Queries, keys and values are read straight out of the packed projection output
 // through 3-D tensor maps (head_dim, heads, tokens), so no transposes are needed.
@@ -20,13 +24,16 @@
 // easydel/operations/kernels/flash_attention.py:82-324 and
 // scaled_dot_product_attention.py:107-254.
 #include "common.cuh"
+#include "tmem_ops.cuh"
 
 namespace edl {
 namespace {
 
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;
 constexpr int BQ = 128;
 constexpr int BKV = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
 
 struct AttnFwdParams {
   __nv_bfloat16* o;      // [tokens, ldo], head h at columns h*D
@@ -46,11 +53,30 @@ struct AttnFwdParams {
 template <int D>
 struct ACfg {
   static constexpr int DCH = D / 64;              // 128-byte chunks along head_dim
-  static constexpr int Q_BYTES = BQ * D * 2;
+  static constexpr int Q_BYTES = BQ * D * 2;      // one query tile
   static constexpr int KV_BYTES = BKV * D * 2;
-  static constexpr int STAGES = 2;
-  static constexpr int SMEM = Q_BYTES + STAGES * 2 * KV_BYTES + 256 + 1024;
+  static constexpr int OFF_K = 2 * Q_BYTES;
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_V + 2 * KV_BYTES;
+  static constexpr int SMEM = OFF_BAR + 256 + 1024;
 };
+
+struct TileRange {
+  int lo, hi;  // key-tile indices [lo, hi) this query tile attends to
+};
+
+__device__ __forceinline__ TileRange tile_range(int q0, int len_q, int len_k, int off, int causal, int window) {
+  TileRange r{0, 0};
+  if (q0 >= len_q) return r;
+  int kv_hi = len_k;
+  if (causal) kv_hi = min(len_k, q0 + BQ + off);
+  int kv_lo = 0;
+  if (window > 0) kv_lo = max(0, q0 + off - window + 1);
+  if (kv_hi <= kv_lo) return r;
+  r.lo = kv_lo / BKV;
+  r.hi = (kv_hi + BKV - 1) / BKV;
+  return r;
+}
 
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -60,21 +86,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t sQ = smem_u32(smem);
-  const uint32_t sK0 = sQ + C::Q_BYTES;
-  const uint32_t sV0 = sK0 + C::STAGES * C::KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::Q_BYTES + C::STAGES * 2 * C::KV_BYTES);
+  const uint32_t sK0 = sQ + C::OFF_K;
+  const uint32_t sV0 = sQ + C::OFF_V;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   const uint32_t b_qfull = smem_u32(bars);
   const uint32_t b_kfull = b_qfull + 8;        // [2]
   const uint32_t b_vfull = b_kfull + 16;       // [2]
-  const uint32_t b_kvempty = b_vfull + 16;     // [2]
-  const uint32_t b_sfull = b_kvempty + 16;     // [2]
-  const uint32_t b_pfull = b_sfull + 16;       // [2]
-  const uint32_t b_odone = b_pfull + 16;       // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  const uint32_t b_kempty = b_vfull + 16;      // [2]
+  const uint32_t b_vempty = b_kempty + 16;     // [2]
+  const uint32_t b_sfull = b_vempty + 16;      // [2] per query tile
+  const uint32_t b_pfull = b_sfull + 16;       // [2] per query tile
+  const uint32_t b_ofinal = b_pfull + 16;      // [2] per query tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal tiles first
+  const int qb = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal blocks first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
 
@@ -82,28 +109,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const int k_start = p.cu_k ? p.cu_k[b] : b * p.Tk;
   const int len_q = p.cu_q ? p.cu_q[b + 1] - q_start : p.Tq;
   const int len_k = p.cu_k ? p.cu_k[b + 1] - k_start : p.Tk;
-  const int q0 = qt * BQ;
-  if (q0 >= len_q) return;
+  const int qblock0 = qb * 2 * BQ;
+  if (qblock0 >= len_q) return;
   const int off = len_k - len_q;  // absolute key position of query row r is r + off
 
-  // key-tile range for this query tile
-  int kv_hi = len_k;
-  if (p.causal) kv_hi = min(len_k, q0 + BQ + off);
-  int kv_lo = 0;
-  if (p.window > 0) kv_lo = max(0, q0 + off - p.window + 1);
-  const int jt0 = kv_lo / BKV;
-  const int n_kv = kv_hi > kv_lo ? (kv_hi + BKV - 1) / BKV - jt0 : 0;
+  const TileRange rgA = tile_range(qblock0, len_q, len_k, off, p.causal, p.window);
+  const TileRange rgB = tile_range(qblock0 + BQ, len_q, len_k, off, p.causal, p.window);
+  const bool anyA = rgA.hi > rgA.lo, anyB = rgB.hi > rgB.lo;
+  int jmin = 0, jmax = 0;
+  if (anyA && anyB) {
+    jmin = min(rgA.lo, rgB.lo);
+    jmax = max(rgA.hi, rgB.hi);
+  } else if (anyA) {
+    jmin = rgA.lo;
+    jmax = rgA.hi;
+  } else if (anyB) {
+    jmin = rgB.lo;
+    jmax = rgB.hi;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(b_qfull, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(b_kfull + 8 * s, 1);
       mbar_init(b_vfull + 8 * s, 1);
-      mbar_init(b_kvempty + 8 * s, 1);
+      mbar_init(b_kempty + 8 * s, 1);
+      mbar_init(b_vempty + 8 * s, 1);
       mbar_init(b_sfull + 8 * s, 1);
       mbar_init(b_pfull + 8 * s, 128);
+      mbar_init(b_ofinal + 8 * s, 1);
     }
-    mbar_init(b_odone, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -115,27 +150,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS0 = tmem_base;             // S/P buffer 0: columns [0,128)
-  const uint32_t tO = tmem_base + 256;        // O: columns [256, 256+D)
 
   if (warp == 0) {
-    if (lane == 0 && n_kv > 0) {
+    if (lane == 0 && jmax > jmin) {
       prefetch_tmap(&tq);
       prefetch_tmap(&tk);
       prefetch_tmap(&tv);
-      mbar_expect_tx(b_qfull, C::Q_BYTES);
+      mbar_expect_tx(b_qfull, 2 * C::Q_BYTES);
 #pragma unroll
-      for (int c = 0; c < C::DCH; ++c) tma_load_3d(sQ + c * (BQ * 128), &tq, b_qfull, c * 64, h, q_start + q0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        if (j >= 2) {
-          if (!mbar_wait(b_kvempty + 8 * s, ((j >> 1) - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_PRODUCER)) break;
-        }
-        const int krow = k_start + (jt0 + j) * BKV;
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int c = 0; c < C::DCH; ++c)
+          tma_load_3d(sQ + t * C::Q_BYTES + c * (BQ * 128), &tq, b_qfull, c * 64, h, q_start + qblock0 + t * BQ);
+      for (int j = jmin; j < jmax; ++j) {
+        const int it = j - jmin;
+        const int s = it & 1;
+        const int krow = k_start + j * BKV;
+        if (it >= 2 &&
+            !mbar_wait(b_kempty + 8 * s, ((it >> 1) - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_PRODUCER))
+          break;
         mbar_expect_tx(b_kfull + 8 * s, C::KV_BYTES);
 #pragma unroll
         for (int c = 0; c < C::DCH; ++c)
           tma_load_3d(sK0 + s * C::KV_BYTES + c * (BKV * 128), &tk, b_kfull + 8 * s, c * 64, hk, krow);
+        if (it >= 2 &&
+            !mbar_wait(b_vempty + 8 * s, ((it >> 1) - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_PRODUCER))
+          break;
         mbar_expect_tx(b_vfull + 8 * s, C::KV_BYTES);
 #pragma unroll
         for (int c = 0; c < C::DCH; ++c)
@@ -143,171 +183,188 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_kv > 0) {
+    if (lane == 0 && jmax > jmin) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(BQ, BKV, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(BQ, D, 0, 1);
       bool ok = mbar_wait(b_qfull, 0, abort_flag, p.status, EDL_TIMEOUT_MMA);
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(b_kfull + 8 * s, (j >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) return false;
-        tc_fence_after();
+      int pv_cnt[2] = {0, 0};
+      auto valid = [&](int t, int j) { return t == 0 ? (j >= rgA.lo && j < rgA.hi) : (j >= rgB.lo && j < rgB.hi); };
+      auto issue_qk = [&](int t, int j) {
+        const int s = (j - jmin) & 1;
         const uint32_t kb = sK0 + s * C::KV_BYTES;
+        const uint32_t qbase = sQ + t * C::Q_BYTES;
 #pragma unroll
         for (int c = 0; c < C::DCH; ++c)
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            uint64_t ad = umma_smem_desc_sw128(sQ + c * (BQ * 128) + k * 32, 16, 1024);
+            uint64_t ad = umma_smem_desc_sw128(qbase + c * (BQ * 128) + k * 32, 16, 1024);
             uint64_t bd = umma_smem_desc_sw128(kb + c * (BKV * 128) + k * 32, 16, 1024);
-            umma_f16_ss(tS0 + s * 128, ad, bd, idesc_qk, (c | k) != 0 ? 1u : 0u);
+            umma_f16_ss(tmem_base + t * 128, ad, bd, idesc_qk, (c | k) != 0 ? 1u : 0u);
           }
-        tc_commit(b_sfull + 8 * s);
-        return true;
+        tc_commit(b_sfull + 8 * t);
       };
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j & 1;
-        if (j + 1 < n_kv) {
-          if (!issue_qk(j + 1)) break;
-        }
-        if (!mbar_wait(b_vfull + 8 * s, (j >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) break;
-        if (!mbar_wait(b_pfull + 8 * s, (j >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) break;
+      auto issue_pv = [&](int t, int j) -> bool {
+        const int s = (j - jmin) & 1;
+        if (!mbar_wait(b_pfull + 8 * t, pv_cnt[t] & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) return false;
         tc_fence_after();
         const uint32_t vb = sV0 + s * C::KV_BYTES;
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
           uint64_t bd = umma_smem_desc_sw128(vb + k * 2048, BKV * 128, 1024);
-          umma_f16_ts(tO, tS0 + s * 128 + k * 8, bd, idesc_pv, (j | k) != 0 ? 1u : 0u);
+          umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, bd, idesc_pv,
+                      (pv_cnt[t] | k) != 0 ? 1u : 0u);
         }
-        tc_commit(b_kvempty + 8 * s);
-        tc_commit(b_odone);
+        ++pv_cnt[t];
+        const bool last = t == 0 ? (j == rgA.hi - 1) : (j == rgB.hi - 1);
+        if (last) tc_commit(b_ofinal + 8 * t);
+        return true;
+      };
+      if (ok) {
+        ok = mbar_wait(b_kfull, 0, abort_flag, p.status, EDL_TIMEOUT_MMA);
+        if (ok) {
+          tc_fence_after();
+          if (valid(0, jmin)) issue_qk(0, jmin);
+          if (valid(1, jmin)) issue_qk(1, jmin);
+          tc_commit(b_kempty);
+        }
+      }
+      for (int j = jmin; j < jmax && ok; ++j) {
+        const int it = j - jmin;
+        const int s = it & 1;
+        const bool more = j + 1 < jmax;
+        if (!mbar_wait(b_vfull + 8 * s, (it >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) break;
+        if (more && !mbar_wait(b_kfull + 8 * (s ^ 1), ((it + 1) >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA))
+          break;
+        tc_fence_after();
+        if (valid(0, j) && !issue_pv(0, j)) break;
+        if (more && valid(0, j + 1)) issue_qk(0, j + 1);
+        if (valid(1, j) && !issue_pv(1, j)) break;
+        tc_commit(b_vempty + 8 * s);
+        if (more) {
+          if (valid(1, j + 1)) issue_qk(1, j + 1);
+          tc_commit(b_kempty + 8 * (s ^ 1));
+        }
       }
     }
   } else {
-    const int q = warp & 3;
+    const int t = (warp - 2) >> 2;          // query tile handled by this softmax group
+    const int q = warp & 3;                 // tensor-memory lane quadrant of this warp
     const int r = q * 32 + lane;            // query row within the tile
+    const int q0 = qblock0 + t * BQ;
     const int qrow = q0 + r;                // row within the sequence
     const int qpos = qrow + off;            // absolute key position of this query
+    const TileRange rg = t == 0 ? rgA : rgB;
     const uint32_t lane_sel = uint32_t(q * 32) << 16;
+    const uint32_t tS = tmem_base + t * 128 + lane_sel;
+    const uint32_t tO = tmem_base + 256 + t * 128 + lane_sel;
+    const uint32_t bs = b_sfull + 8 * t, bp = b_pfull + 8 * t, bo = b_ofinal + 8 * t;
     float m_used = -1e30f;
     float l = 0.f;
-    const float cap2 = p.softcap * 1.4426950408889634f;  // soft-cap in log2 units
+    const float cap2 = p.softcap * LOG2E;   // soft-cap in log2 units
     const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
-    const float scale_nat = p.scale_log2 * 0.6931471805599453f;
+    const float scale_nat = p.scale_log2 * LN2;
+    const bool capped = p.softcap > 0.f;
+    const float mul = capped ? 1.f : p.scale_log2;
     bool alive = true;
-    for (int j = 0; j < n_kv && alive; ++j) {
-      const int s = j & 1;
-      const int kv0 = (jt0 + j) * BKV;
-      if (!mbar_wait(b_sfull + 8 * s, (j >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
+    int n = 0;
+    for (int j = rg.lo; j < rg.hi && alive; ++j, ++n) {
+      const int kv0 = j * BKV;
+      if (!mbar_wait(bs, n & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
         alive = false;
         break;
       }
       tc_fence_after();
-      const uint32_t tS = tS0 + s * 128 + lane_sel;
+      uint32_t a[64], c2[64];
+      tmem_ld_32x32b_x64(tS, a);
+      tmem_ld_32x32b_x64(tS + 64, c2);
+      tc_wait_ld();
       const bool tile_mask = (kv0 + BKV > len_k) || (p.causal && kv0 + BKV - 1 > q0 + off) ||
                              (p.window > 0 && kv0 < q0 + BQ - 1 + off - p.window + 1);
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32b_x32(tS + c * 32, rr);
-        tc_wait_ld();
+      if (capped) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(rr[i]);
-          if (p.softcap > 0.f) v = cap2 * tanhf(v * scale_nat * inv_cap);
-          else v *= p.scale_log2;
-          if (tile_mask) {
-            const int kpos = kv0 + c * 32 + i;
-            const bool ok = (kpos < len_k) && (!p.causal || kpos <= qpos) && (p.window <= 0 || kpos > qpos - p.window);
-            v = ok ? v : -INFINITY;
-          }
-          mx = fmaxf(mx, v);
+        for (int i = 0; i < 64; ++i) {
+          a[i] = __float_as_uint(cap2 * tanhf(__uint_as_float(a[i]) * scale_nat * inv_cap));
+          c2[i] = __float_as_uint(cap2 * tanhf(__uint_as_float(c2[i]) * scale_nat * inv_cap));
         }
       }
-      // lazy rescale (warp-uniform decision: tcgen05.ld/st are warp-wide)
+      if (tile_mask) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const int k0 = kv0 + i, k1 = kv0 + 64 + i;
+          const bool ok0 = (k0 < len_k) && (!p.causal || k0 <= qpos) && (p.window <= 0 || k0 > qpos - p.window);
+          const bool ok1 = (k1 < len_k) && (!p.causal || k1 <= qpos) && (p.window <= 0 || k1 > qpos - p.window);
+          if (!ok0) a[i] = 0xff800000u;   // -inf
+          if (!ok1) c2[i] = 0xff800000u;
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(a[i]), __uint_as_float(c2[i])));
+      mx *= mul;  // mul > 0, so scaling commutes with the maximum
+      // lazy rescale (warp-uniform decision: tcgen05.ld/st are warp-wide). The QK^T product of this
+      // step was issued after the PV product of the previous one, so O is quiescent here.
       const float m_new = fmaxf(m_used, mx);
-      const bool want = m_new > m_used + 8.f;
-      if (__any_sync(0xffffffffu, want)) {
+      if (__any_sync(0xffffffffu, m_new > m_used + 8.f)) {
         const float alpha = exp2f(m_used - m_new);
         l *= alpha;
-        if (j > 0) {
-          if (!mbar_wait(b_odone, (j - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
-            alive = false;
-            break;
-          }
-          tc_fence_after();
+        if (n > 0) {
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
             uint32_t rr[32];
-            tmem_ld_32x32b_x32(tO + lane_sel + c * 32, rr);
+            tmem_ld_32x32b_x32(tO + c * 32, rr);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
-            tmem_st_32x32b_x32(tO + lane_sel + c * 32, rr);
+            tmem_st_32x32b_x32(tO + c * 32, rr);
           }
-          tc_wait_st();
         }
         m_used = m_new;
       }
-      // pass 2: P = exp2(S - m), packed bf16 into the same tensor-memory columns
-#pragma unroll 1
-      for (int c2 = 0; c2 < 2; ++c2) {
+      const float neg_m = -m_used;
+      float l0 = 0.f, l1 = 0.f;
+      {
         uint32_t pk[32];
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = c2 * 2 + cc;
-          uint32_t rr[32];
-          tmem_ld_32x32b_x32(tS + c * 32, rr);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float v0 = __uint_as_float(rr[i]), v1 = __uint_as_float(rr[i + 1]);
-            if (p.softcap > 0.f) {
-              v0 = cap2 * tanhf(v0 * scale_nat * inv_cap);
-              v1 = cap2 * tanhf(v1 * scale_nat * inv_cap);
-            } else {
-              v0 *= p.scale_log2;
-              v1 *= p.scale_log2;
-            }
-            if (tile_mask) {
-              const int kpos = kv0 + c * 32 + i;
-              const bool ok0 = (kpos < len_k) && (!p.causal || kpos <= qpos) && (p.window <= 0 || kpos > qpos - p.window);
-              const bool ok1 = (kpos + 1 < len_k) && (!p.causal || kpos + 1 <= qpos) &&
-                               (p.window <= 0 || kpos + 1 > qpos - p.window);
-              v0 = ok0 ? v0 : -INFINITY;
-              v1 = ok1 ? v1 : -INFINITY;
-            }
-            const float e0 = exp2f(v0 - m_used), e1 = exp2f(v1 - m_used);
-            l += e0 + e1;
-            pk[cc * 16 + i / 2] = pack_bf16x2(e0, e1);
-          }
+        for (int i = 0; i < 64; i += 2) {
+          const float e0 = exp2f(fmaf(__uint_as_float(a[i]), mul, neg_m));
+          const float e1 = exp2f(fmaf(__uint_as_float(a[i + 1]), mul, neg_m));
+          l0 += e0;
+          l1 += e1;
+          pk[i >> 1] = pack_bf16x2(e0, e1);
         }
-        // all lanes of the warp must have read their S columns before any lane overwrites
-        // them: columns [c2*32, c2*32+32) of P alias S columns that were read in pass 1 and,
-        // for c2 == 0, in this very pass (chunks 0,1 cover S columns 0..63 >= P columns 0..31).
-        tmem_st_32x32b_x32(tS + c2 * 32, pk);
+        tmem_st_32x32b_x32(tS, pk);
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          const float e0 = exp2f(fmaf(__uint_as_float(c2[i]), mul, neg_m));
+          const float e1 = exp2f(fmaf(__uint_as_float(c2[i + 1]), mul, neg_m));
+          l0 += e0;
+          l1 += e1;
+          pk[i >> 1] = pack_bf16x2(e0, e1);
+        }
+        tmem_st_32x32b_x32(tS + 32, pk);
       }
+      l += l0 + l1;
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(b_pfull + 8 * s);
+      mbar_arrive(bp);
     }
 
     // epilogue: O / l -> bf16, plus LSE
-    if (n_kv > 0 && alive) {
-      if (!mbar_wait(b_odone, (n_kv - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_EPILOGUE)) alive = false;
+    const bool any = rg.hi > rg.lo;
+    if (any && alive) {
+      if (!mbar_wait(bo, 0, abort_flag, p.status, EDL_TIMEOUT_EPILOGUE)) alive = false;
       tc_fence_after();
     }
-    if (alive) {
-      if (p.sinks) l += exp2f(p.sinks[h] * 1.4426950408889634f - m_used);
+    if (alive && q0 < len_q) {
+      if (p.sinks) l += exp2f(p.sinks[h] * LOG2E - m_used);
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
       const bool row_ok = qrow < len_q;
       __nv_bfloat16* op = p.o + (long long)(q_start + qrow) * p.ldo + (long long)h * D;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t rr[32];
-        if (n_kv > 0) {
-          tmem_ld_32x32b_x32(tO + lane_sel + c * 32, rr);
+        if (any) {
+          tmem_ld_32x32b_x32(tO + c * 32, rr);
           tc_wait_ld();
         } else {
 #pragma unroll
@@ -326,8 +383,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         }
       }
       if (row_ok && p.lse)
-        p.lse[(long long)h * p.total_q + q_start + qrow] =
-            l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        p.lse[(long long)h * p.total_q + q_start + qrow] = l > 0.f ? (m_used + log2f(l)) * LN2 : -INFINITY;
     }
   }
 
@@ -357,7 +413,7 @@ int launch_fwd(const void* q, const void* k, const void* v, long long ldq, long 
       return -1;
     attr_set = true;
   }
-  dim3 grid((p.Tq + BQ - 1) / BQ, p.Hq, p.B);
+  dim3 grid((p.Tq + 2 * BQ - 1) / (2 * BQ), p.Hq, p.B);
   kern<<<grid, ATT_THREADS, C::SMEM, stream>>>(tq, tk, tv, p);
   return check_cuda(cudaGetLastError(), "attn_fwd launch");
 }
