@@ -1,40 +1,44 @@
-// Flash-attention backward on tcgen05 tensor cores.
+// Flash-attention backward on tcgen05 tensor cores, as two pipelined kernels (no atomics,
+// bitwise reproducible):
 //
-// One CTA per (key tile of 128 rows, KV head, sequence). K and V stay resident in
-// shared memory; the CTA walks over every query head of the GQA group and every
-// query tile that can see the key tile, with Q and dO double-buffered through TMA.
-// Per step, five tensor-core products (all 128x128x{128|D}):
-//     S^T  = K Q^T        dP^T = V dO^T                   (operands K-major in smem)
-//     dV  += P^T dO       dK  += dS^T Q                   (A from tensor memory, B MN-major)
-//     dQ   = dS K                                         (A = dS staged in smem, MN-major)
-// Thread i of the four softmax warps owns key row i: it turns S^T / dP^T into
-// P^T = exp2(S^T*c - lse) and dS^T = P^T (dP^T - delta), writes both back to tensor
-// memory as packed bf16 (P^T over S^T, dS^T over dP^T) and dS^T also to shared
-// memory in the 128-byte-swizzled MN-major layout the dQ product reads. dK and dV
-// accumulate in tensor memory over the whole walk and are written once; dQ tiles are
-// added to an fp32 buffer with vector reductions (red.global.add.v4.f32).
+//   attn_bwd_dq_kernel   one CTA per (query tile of 128 rows, query head, sequence), walking the key
+//                        tiles it can see:   S = Q K^T,  dP = dO V^T,  dQ += dS K
+//   attn_bwd_dkv_kernel  one CTA per (key tile of 128 rows, KV head, sequence), walking every query
+//                        head of the GQA group and every query tile that can see the key tile:
+//                        S^T = K Q^T,  dP^T = V dO^T,  dV += P^T dO,  dK += dS^T Q
 //
-// Tensor memory map (512 columns): [0,128) S^T -> P^T -> dQ, [128,256) dP^T -> dS^T,
-// [256,256+D) dK, [384,384+D) dV.
+// Both recompute P = exp2(S*c - lse) from the forward's log-sum-exp and form dS = P (dP - delta)
+// with delta = rowsum(O * dO) from a small pre-pass. Roles in each CTA: warp 0 feeds shared
+// memory through TMA rings, warp 1 issues the MMAs, warps 2..9 do the element-wise work. Each of
+// the four tensor-memory lane quadrants is served by two warps that split the 128 columns of a
+// tile between them; a warp writes its bf16 results (the A operands of the following products)
+// only into the column range it alone has just read, so the two never need to synchronise.
+// The MMA order is software pipelined (products of step t+1 / t+2 are issued before the results
+// of step t are consumed), which keeps the tensor pipe busy while the element-wise warps work.
+//
+// Tensor memory, dQ kernel:   S(even) [0,128)  S(odd) [128,256)  dP -> dS [256,384)  dQ [384,512)
+// Tensor memory, dK/dV kernel: S^T [0,128)  dP^T -> P^T,dS^T [128,256)  dK [256,384)  dV [384,512)
 //
 // Gradient counterpart of the flash kernels behind
 // easydel/operations/kernels/flash_attention.py:82-324 (the reference selects a Triton
 // or XLA backward there, easydel/infra/base_config.py:829).
 #include "common.cuh"
+#include "tmem_ops.cuh"
 
 namespace edl {
 namespace {
 
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;
 constexpr int BT = 128;
+constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnBwdParams {
   const float* lse;     // [Hq, total_q]
   const float* delta;   // [Hq, total_q]
-  float* dq;            // [total_q, Hq, D] fp32, zero-initialised by the caller
+  __nv_bfloat16* dq;    // [total_q, lddq], head at columns h*D
   __nv_bfloat16* dk;    // [total_k, lddk], head at columns hk*D
   __nv_bfloat16* dv;
-  long long lddk, lddv;
+  long long lddq, lddk, lddv;
   const int* cu_q;
   const int* cu_k;
   int B, Tq, Tk, Hq, Hkv, total_q;
@@ -49,44 +53,307 @@ template <int D>
 struct BCfg {
   static constexpr int DCH = D / 64;
   static constexpr int TILE = BT * D * 2;          // one [128, D] bf16 tile
-  static constexpr int OFF_K = 0;
-  static constexpr int OFF_V = TILE;
-  static constexpr int OFF_Q = 2 * TILE;           // 2 stages
-  static constexpr int OFF_DO = 4 * TILE;          // 2 stages
-  static constexpr int OFF_DS = 6 * TILE;          // [128 keys x 128 queries] bf16 = 32 KB
-  static constexpr int OFF_STAT = OFF_DS + BT * BT * 2;  // lse2[128], delta[128] fp32
-  static constexpr int OFF_BAR = OFF_STAT + 1024;
-  static constexpr int SMEM = OFF_BAR + 128 + 1024;
+  static constexpr int OFF_STAT = 7 * TILE;        // 2 x (lse2[128], delta[128]) fp32
+  static constexpr int OFF_BAR = OFF_STAT + 2048;
+  static constexpr int SMEM = OFF_BAR + 256;
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
-}
-__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// A-operand column of the k-th 16-wide reduction step when the 128 reduction columns were
+// written as two 32-column packed pieces at `base` and `base + 64`.
+__device__ __forceinline__ uint32_t split_a(uint32_t base, int kk) {
+  return kk < 4 ? base + kk * 8 : base + 64 + (kk - 4) * 8;
+}
+
+template <int NCOL>
+__device__ __forceinline__ void store_rows_bf16(__nv_bfloat16* dst, const uint32_t (&r)[NCOL], float mul) {
+#pragma unroll
+  for (int x = 0; x < NCOL; x += 8) {
+    uint4 o;
+    o.x = pack_bf16x2(__uint_as_float(r[x]) * mul, __uint_as_float(r[x + 1]) * mul);
+    o.y = pack_bf16x2(__uint_as_float(r[x + 2]) * mul, __uint_as_float(r[x + 3]) * mul);
+    o.z = pack_bf16x2(__uint_as_float(r[x + 4]) * mul, __uint_as_float(r[x + 5]) * mul);
+    o.w = pack_bf16x2(__uint_as_float(r[x + 6]) * mul, __uint_as_float(r[x + 7]) * mul);
+    *reinterpret_cast<uint4*>(dst + x) = o;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// dQ
+// ------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
-                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
-                const AttnBwdParams p) {
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                   const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                   const AttnBwdParams p) {
   using C = BCfg<D>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t sK = sbase + C::OFF_K, sV = sbase + C::OFF_V, sQ0 = sbase + C::OFF_Q, sDO0 = sbase + C::OFF_DO,
-                 sDS = sbase + C::OFF_DS;
-  float* s_lse = reinterpret_cast<float*>(smem + C::OFF_STAT);
-  float* s_delta = s_lse + 128;
+  const uint32_t sQ = sbase, sDO = sbase + C::TILE, sK0 = sbase + 2 * C::TILE, sV0 = sbase + 5 * C::TILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  const uint32_t b_qfull = smem_u32(bars);
+  const uint32_t b_kfull = b_qfull + 8;       // [3]
+  const uint32_t b_kempty = b_kfull + 24;     // [3]
+  const uint32_t b_vfull = b_kempty + 24;     // [2]
+  const uint32_t b_vempty = b_vfull + 16;     // [2]
+  const uint32_t b_sfull = b_vempty + 16;     // [2]
+  const uint32_t b_dpfull = b_sfull + 16;
+  const uint32_t b_dsfull = b_dpfull + 8;
+  const uint32_t b_final = b_dsfull + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q_start = p.cu_q ? p.cu_q[b] : b * p.Tq;
+  const int k_start = p.cu_k ? p.cu_k[b] : b * p.Tk;
+  const int len_q = p.cu_q ? p.cu_q[b + 1] - q_start : p.Tq;
+  const int len_k = p.cu_k ? p.cu_k[b + 1] - k_start : p.Tk;
+  const int q0 = qt * BT;
+  if (q0 >= len_q) return;
+  const int off = len_k - len_q;
+  int kv_hi = len_k;
+  if (p.causal) kv_hi = min(len_k, q0 + BT + off);
+  int kv_lo = 0;
+  if (p.window > 0) kv_lo = max(0, q0 + off - p.window + 1);
+  const int lo = kv_lo / BT;
+  const int n = kv_hi > kv_lo ? (kv_hi + BT - 1) / BT - lo : 0;
+
+  if (threadIdx.x == 0) {
+    if (sbase & 1023) atomicCAS(p.status, 0, EDL_BAD_INDEX);
+    mbar_init(b_qfull, 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(b_kfull + 8 * s, 1);
+      mbar_init(b_kempty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(b_vfull + 8 * s, 1);
+      mbar_init(b_vempty + 8 * s, 1);
+      mbar_init(b_sfull + 8 * s, 1);
+    }
+    mbar_init(b_dpfull, 1);
+    mbar_init(b_dsfull, 256);
+    mbar_init(b_final, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 256, tDQ = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0 && n > 0) {
+      prefetch_tmap(&tk);
+      prefetch_tmap(&tv);
+      mbar_expect_tx(b_qfull, 2 * C::TILE);
+#pragma unroll
+      for (int c = 0; c < C::DCH; ++c) {
+        tma_load_3d(sQ + c * (BT * 128), &tq, b_qfull, c * 64, h, q_start + q0);
+        tma_load_3d(sDO + c * (BT * 128), &tdo, b_qfull, c * 64, h, q_start + q0);
+      }
+      for (int it = 0; it < n; ++it) {
+        const int ks = it % 3, vs = it & 1;
+        const int krow = k_start + (lo + it) * BT;
+        if (it >= 3 && !mbar_wait(b_kempty + 8 * ks, (it / 3 - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_PRODUCER))
+          break;
+        mbar_expect_tx(b_kfull + 8 * ks, C::TILE);
+#pragma unroll
+        for (int c = 0; c < C::DCH; ++c)
+          tma_load_3d(sK0 + ks * C::TILE + c * (BT * 128), &tk, b_kfull + 8 * ks, c * 64, hk, krow);
+        if (it >= 2 && !mbar_wait(b_vempty + 8 * vs, ((it >> 1) - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_PRODUCER))
+          break;
+        mbar_expect_tx(b_vfull + 8 * vs, C::TILE);
+#pragma unroll
+        for (int c = 0; c < C::DCH; ++c)
+          tma_load_3d(sV0 + vs * C::TILE + c * (BT * 128), &tv, b_vfull + 8 * vs, c * 64, hk, krow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t id_kk = umma_idesc_bf16(BT, BT, 0, 0);
+      constexpr uint32_t id_tn = umma_idesc_bf16(BT, D, 0, 1);
+      bool ok = mbar_wait(b_qfull, 0, abort_flag, p.status, EDL_TIMEOUT_MMA);
+      auto issue_s = [&](int it) -> bool {
+        const int ks = it % 3;
+        if (!mbar_wait(b_kfull + 8 * ks, (it / 3) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t kb = sK0 + ks * C::TILE;
+#pragma unroll
+        for (int c = 0; c < C::DCH; ++c)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16_ss(tS + (it & 1) * 128, umma_smem_desc_sw128(sQ + c * (BT * 128) + k * 32, 16, 1024),
+                        umma_smem_desc_sw128(kb + c * (BT * 128) + k * 32, 16, 1024), id_kk, (c | k) != 0 ? 1u : 0u);
+        tc_commit(b_sfull + 8 * (it & 1));
+        return true;
+      };
+      auto issue_dp = [&](int it) -> bool {
+        const int vs = it & 1;
+        if (!mbar_wait(b_vfull + 8 * vs, (it >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t vb = sV0 + vs * C::TILE;
+#pragma unroll
+        for (int c = 0; c < C::DCH; ++c)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f16_ss(tDP, umma_smem_desc_sw128(sDO + c * (BT * 128) + k * 32, 16, 1024),
+                        umma_smem_desc_sw128(vb + c * (BT * 128) + k * 32, 16, 1024), id_kk, (c | k) != 0 ? 1u : 0u);
+        tc_commit(b_dpfull);
+        tc_commit(b_vempty + 8 * vs);
+        return true;
+      };
+      auto issue_dq = [&](int it) -> bool {
+        if (!mbar_wait(b_dsfull, it & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t kb = sK0 + (it % 3) * C::TILE;
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk)
+          umma_f16_ts(tDQ, split_a(tDP, kk), umma_smem_desc_sw128(kb + kk * 2048, BT * 128, 1024), id_tn,
+                      (it | kk) != 0 ? 1u : 0u);
+        tc_commit(b_kempty + 8 * (it % 3));
+        if (it == n - 1) tc_commit(b_final);
+        return true;
+      };
+      if (ok) ok = issue_s(0) && issue_dp(0);
+      if (ok && n > 1) ok = issue_s(1);
+      for (int it = 0; it < n && ok; ++it) {
+        if (!issue_dq(it)) break;
+        if (it + 1 < n && !issue_dp(it + 1)) break;
+        if (it + 2 < n && !issue_s(it + 2)) break;
+      }
+    }
+  } else {
+    const int half = (warp - 2) >> 2;
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;
+    const int qrow = q0 + r;
+    const int qpos = qrow + off;
+    const int cb = half * 64;
+    const uint32_t lane_sel = uint32_t(qd * 32) << 16;
+    const float scale_log2 = p.scale * LOG2E;
+    const bool capped = p.softcap > 0.f;
+    const float inv_cap = capped ? 1.f / p.softcap : 0.f;
+    const float cap2 = p.softcap * LOG2E;
+    float lse2 = 0.f, dl = 0.f;
+    if (qrow < len_q) {
+      const long long idx = (long long)h * p.total_q + q_start + qrow;
+      lse2 = p.lse[idx] * LOG2E;
+      dl = p.delta[idx];
+    }
+    bool alive = true;
+    for (int it = 0; it < n && alive; ++it) {
+      const int kv0 = (lo + it) * BT;
+      if (!mbar_wait(b_sfull + 8 * (it & 1), (it >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
+        alive = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t s[64];
+      tmem_ld_32x32b_x64(tS + (it & 1) * 128 + lane_sel + cb, s);
+      tc_wait_ld();
+      const bool tile_mask = (kv0 + BT > len_k) || (q0 + BT > len_q) || (p.causal && kv0 + BT - 1 > q0 + off) ||
+                             (p.window > 0 && kv0 < q0 + BT - 1 + off - p.window + 1);
+      float pd[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        float sv = __uint_as_float(s[i]);
+        float dcap = 1.f, s2;
+        if (capped) {
+          const float th = tanhf(sv * p.scale * inv_cap);
+          s2 = cap2 * th;
+          dcap = 1.f - th * th;
+        } else {
+          s2 = sv * scale_log2;
+        }
+        float pe = exp2f(s2 - lse2) * dcap;
+        if (tile_mask) {
+          const int kpos = kv0 + cb + i;
+          const bool okm = (kpos < len_k) && (qrow < len_q) && (!p.causal || kpos <= qpos) &&
+                           (p.window <= 0 || kpos > qpos - p.window);
+          pe = okm ? pe : 0.f;
+        }
+        pd[i] = pe;
+      }
+      if (!mbar_wait(b_dpfull, it & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
+        alive = false;
+        break;
+      }
+      tc_fence_after();
+      tmem_ld_32x32b_x64(tDP + lane_sel + cb, s);
+      tc_wait_ld();
+      uint32_t pk[32];
+#pragma unroll
+      for (int i = 0; i < 64; i += 2)
+        pk[i >> 1] = pack_bf16x2(pd[i] * (__uint_as_float(s[i]) - dl), pd[i + 1] * (__uint_as_float(s[i + 1]) - dl));
+      tmem_st_32x32b_x32(tDP + lane_sel + cb, pk);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(b_dsfull);
+    }
+    if (alive && n > 0) {
+      if (!mbar_wait(b_final, 0, abort_flag, p.status, EDL_TIMEOUT_EPILOGUE)) alive = false;
+      tc_fence_after();
+    }
+    if (alive) {
+      constexpr int HC = D / 2;  // columns of dQ handled by this warp
+      uint32_t rr[HC];
+      if (n > 0) {
+        if constexpr (HC == 64) tmem_ld_32x32b_x64(tDQ + lane_sel + half * HC, rr);
+        else tmem_ld_32x32b_x32(tDQ + lane_sel + half * HC, rr);
+        tc_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < HC; ++i) rr[i] = 0u;
+      }
+      if (qrow < len_q)
+        store_rows_bf16<HC>(p.dq + (long long)(q_start + qrow) * p.lddq + (long long)h * D + half * HC, rr, p.scale);
+    }
+  }
+
+  if (*abort_flag) {
+    long long t0 = clock64();
+    while (clock64() - t0 < 400000) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ------------------------------------------------------------------------------------------
+// dK, dV
+// ------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                    const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                    const AttnBwdParams p) {
+  using C = BCfg<D>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t sK = sbase, sV = sbase + C::TILE, sQ0 = sbase + 2 * C::TILE, sDO0 = sbase + 5 * C::TILE;
+  float* s_stat = reinterpret_cast<float*>(smem + C::OFF_STAT);  // [2][lse2 128 | delta 128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   const uint32_t b_kvfull = smem_u32(bars);
-  const uint32_t b_qfull = b_kvfull + 8;     // [2]
-  const uint32_t b_qempty = b_qfull + 16;    // [2]
-  const uint32_t b_sfull = b_qempty + 16;
-  const uint32_t b_pfull = b_sfull + 8;
-  const uint32_t b_dqfull = b_pfull + 8;
-  const uint32_t b_tfree = b_dqfull + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  const uint32_t b_qfull = b_kvfull + 8;      // [3]
+  const uint32_t b_qempty = b_qfull + 24;     // [3]
+  const uint32_t b_dofull = b_qempty + 24;    // [2]
+  const uint32_t b_doempty = b_dofull + 16;   // [2]
+  const uint32_t b_sfull = b_doempty + 16;
+  const uint32_t b_sfree = b_sfull + 8;
+  const uint32_t b_dpfull = b_sfree + 8;
+  const uint32_t b_pfull = b_dpfull + 8;
+  const uint32_t b_final = b_pfull + 8;
+  const uint32_t b_stat = b_final + 8;        // rendezvous of the 256 element-wise threads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -99,24 +366,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const int kv0 = jt * BT;
   if (kv0 >= len_k) return;
   const int off = len_k - len_q;
-
-  // query tiles that can see this key tile
   int i_lo = 0, i_hi = (len_q + BT - 1) / BT;
   if (p.causal) i_lo = max(0, kv0 - off) / BT;
   if (p.window > 0) i_hi = min(i_hi, max(0, kv0 + BT - 1 + p.window - 1 - off) / BT + 1);
   const int n_i = max(0, i_hi - i_lo);
-  const int n_steps = n_i * G;
+  const int n = n_i * G;
 
   if (threadIdx.x == 0) {
+    if (sbase & 1023) atomicCAS(p.status, 0, EDL_BAD_INDEX);
     mbar_init(b_kvfull, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 3; ++s) {
       mbar_init(b_qfull + 8 * s, 1);
       mbar_init(b_qempty + 8 * s, 1);
     }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(b_dofull + 8 * s, 1);
+      mbar_init(b_doempty + 8 * s, 1);
+    }
     mbar_init(b_sfull, 1);
-    mbar_init(b_pfull, 128);
-    mbar_init(b_dqfull, 1);
-    mbar_init(b_tfree, 128);
+    mbar_init(b_sfree, 256);
+    mbar_init(b_dpfull, 1);
+    mbar_init(b_pfull, 256);
+    mbar_init(b_final, 1);
+    mbar_init(b_stat, 256);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -131,7 +403,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDK = tmem_base + 256, tDV = tmem_base + 384;
 
   if (warp == 0) {
-    if (lane == 0 && n_steps > 0) {
+    if (lane == 0 && n > 0) {
       prefetch_tmap(&tq);
       prefetch_tmap(&tdo);
       mbar_expect_tx(b_kvfull, 2 * C::TILE);
@@ -140,218 +412,210 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         tma_load_3d(sK + c * (BT * 128), &tk, b_kvfull, c * 64, hk, k_start + kv0);
         tma_load_3d(sV + c * (BT * 128), &tv, b_kvfull, c * 64, hk, k_start + kv0);
       }
-      for (int t = 0; t < n_steps; ++t) {
-        const int s = t & 1;
-        if (t >= 2) {
-          if (!mbar_wait(b_qempty + 8 * s, ((t >> 1) - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_PRODUCER)) break;
-        }
+      for (int t = 0; t < n; ++t) {
         const int g = t / n_i, i = i_lo + (t - g * n_i);
         const int hq = hk * G + g;
         const int row = q_start + i * BT;
-        mbar_expect_tx(b_qfull + 8 * s, 2 * C::TILE);
+        const int qs = t % 3, ds = t & 1;
+        if (t >= 3 && !mbar_wait(b_qempty + 8 * qs, (t / 3 - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_PRODUCER))
+          break;
+        mbar_expect_tx(b_qfull + 8 * qs, C::TILE);
 #pragma unroll
-        for (int c = 0; c < C::DCH; ++c) {
-          tma_load_3d(sQ0 + s * C::TILE + c * (BT * 128), &tq, b_qfull + 8 * s, c * 64, hq, row);
-          tma_load_3d(sDO0 + s * C::TILE + c * (BT * 128), &tdo, b_qfull + 8 * s, c * 64, hq, row);
-        }
+        for (int c = 0; c < C::DCH; ++c)
+          tma_load_3d(sQ0 + qs * C::TILE + c * (BT * 128), &tq, b_qfull + 8 * qs, c * 64, hq, row);
+        if (t >= 2 && !mbar_wait(b_doempty + 8 * ds, ((t >> 1) - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_PRODUCER))
+          break;
+        mbar_expect_tx(b_dofull + 8 * ds, C::TILE);
+#pragma unroll
+        for (int c = 0; c < C::DCH; ++c)
+          tma_load_3d(sDO0 + ds * C::TILE + c * (BT * 128), &tdo, b_dofull + 8 * ds, c * 64, hq, row);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_steps > 0) {
-      constexpr uint32_t id_kk = umma_idesc_bf16(BT, BT, 0, 0);   // S^T, dP^T
-      constexpr uint32_t id_tn = umma_idesc_bf16(BT, D, 0, 1);    // dV, dK (A in tmem, B MN-major)
-      constexpr uint32_t id_nn = umma_idesc_bf16(BT, D, 1, 1);    // dQ (A, B MN-major)
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t id_kk = umma_idesc_bf16(BT, BT, 0, 0);
+      constexpr uint32_t id_tn = umma_idesc_bf16(BT, D, 0, 1);
       bool ok = mbar_wait(b_kvfull, 0, abort_flag, p.status, EDL_TIMEOUT_MMA);
-      for (int t = 0; t < n_steps && ok; ++t) {
-        const int s = t & 1;
-        const uint32_t sQ = sQ0 + s * C::TILE, sDO = sDO0 + s * C::TILE;
-        if (!mbar_wait(b_qfull + 8 * s, (t >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) break;
-        if (t > 0 && !mbar_wait(b_tfree, (t - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) break;
+      auto issue_st = [&](int t) -> bool {
+        const int qs = t % 3;
+        if (!mbar_wait(b_qfull + 8 * qs, (t / 3) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) return false;
+        if (t > 0 && !mbar_wait(b_sfree, (t - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) return false;
         tc_fence_after();
+        const uint32_t qb = sQ0 + qs * C::TILE;
 #pragma unroll
         for (int c = 0; c < C::DCH; ++c)
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            uint64_t ad = umma_smem_desc_sw128(sK + c * (BT * 128) + k * 32, 16, 1024);
-            uint64_t bd = umma_smem_desc_sw128(sQ + c * (BT * 128) + k * 32, 16, 1024);
-            umma_f16_ss(tS, ad, bd, id_kk, (c | k) != 0 ? 1u : 0u);
-          }
-#pragma unroll
-        for (int c = 0; c < C::DCH; ++c)
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            uint64_t ad = umma_smem_desc_sw128(sV + c * (BT * 128) + k * 32, 16, 1024);
-            uint64_t bd = umma_smem_desc_sw128(sDO + c * (BT * 128) + k * 32, 16, 1024);
-            umma_f16_ss(tDP, ad, bd, id_kk, (c | k) != 0 ? 1u : 0u);
-          }
+          for (int k = 0; k < 4; ++k)
+            umma_f16_ss(tS, umma_smem_desc_sw128(sK + c * (BT * 128) + k * 32, 16, 1024),
+                        umma_smem_desc_sw128(qb + c * (BT * 128) + k * 32, 16, 1024), id_kk, (c | k) != 0 ? 1u : 0u);
         tc_commit(b_sfull);
-        if (!mbar_wait(b_pfull, t & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) break;
+        return true;
+      };
+      auto issue_dpt = [&](int t) -> bool {
+        const int ds = t & 1;
+        if (!mbar_wait(b_dofull + 8 * ds, (t >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) return false;
         tc_fence_after();
+        const uint32_t db = sDO0 + ds * C::TILE;
 #pragma unroll
-        for (int k = 0; k < BT / 16; ++k) {
-          uint64_t bd = umma_smem_desc_sw128(sDO + k * 2048, BT * 128, 1024);
-          umma_f16_ts(tDV, tS + k * 8, bd, id_tn, (t | k) != 0 ? 1u : 0u);
-        }
+        for (int c = 0; c < C::DCH; ++c)
 #pragma unroll
-        for (int k = 0; k < BT / 16; ++k) {
-          uint64_t bd = umma_smem_desc_sw128(sQ + k * 2048, BT * 128, 1024);
-          umma_f16_ts(tDK, tDP + k * 8, bd, id_tn, (t | k) != 0 ? 1u : 0u);
-        }
+          for (int k = 0; k < 4; ++k)
+            umma_f16_ss(tDP, umma_smem_desc_sw128(sV + c * (BT * 128) + k * 32, 16, 1024),
+                        umma_smem_desc_sw128(db + c * (BT * 128) + k * 32, 16, 1024), id_kk, (c | k) != 0 ? 1u : 0u);
+        tc_commit(b_dpfull);
+        return true;
+      };
+      auto issue_dvdk = [&](int t) -> bool {
+        if (!mbar_wait(b_pfull, t & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) return false;
+        tc_fence_after();
+        const uint32_t db = sDO0 + (t & 1) * C::TILE;
+        const uint32_t qb = sQ0 + (t % 3) * C::TILE;
 #pragma unroll
-        for (int k = 0; k < BT / 16; ++k) {
-          uint64_t ad = umma_smem_desc_sw128(sDS + k * 2048, BT * 128, 1024);
-          uint64_t bd = umma_smem_desc_sw128(sK + k * 2048, BT * 128, 1024);
-          umma_f16_ss(tS, ad, bd, id_nn, k != 0 ? 1u : 0u);
-        }
-        tc_commit(b_qempty + 8 * s);
-        tc_commit(b_dqfull);
+        for (int kk = 0; kk < BT / 16; ++kk)
+          umma_f16_ts(tDV, split_a(tDP, kk), umma_smem_desc_sw128(db + kk * 2048, BT * 128, 1024), id_tn,
+                      (t | kk) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk)
+          umma_f16_ts(tDK, split_a(tDP + 32, kk), umma_smem_desc_sw128(qb + kk * 2048, BT * 128, 1024), id_tn,
+                      (t | kk) != 0 ? 1u : 0u);
+        tc_commit(b_qempty + 8 * (t % 3));
+        tc_commit(b_doempty + 8 * (t & 1));
+        if (t == n - 1) tc_commit(b_final);
+        return true;
+      };
+      if (ok) ok = issue_st(0) && issue_dpt(0);
+      if (ok && n > 1) ok = issue_st(1);
+      for (int t = 0; t < n && ok; ++t) {
+        if (!issue_dvdk(t)) break;
+        if (t + 1 < n && !issue_dpt(t + 1)) break;
+        if (t + 2 < n && !issue_st(t + 2)) break;
       }
     }
   } else {
-    const int q4 = warp & 3;
-    const int r = q4 * 32 + lane;  // key row (S^T, dP^T, dK, dV) or query row (dQ) owned by this thread
-    const uint32_t lane_sel = uint32_t(q4 * 32) << 16;
+    const int half = (warp - 2) >> 2;
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;          // key row owned by this thread
     const int kpos = kv0 + r;
-    const float scale_log2 = p.scale * 1.4426950408889634f;
-    const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
-    const float cap2 = p.softcap * 1.4426950408889634f;
-    bool alive = true;
-    for (int t = 0; t < n_steps && alive; ++t) {
+    const int cb = half * 64;              // first query column of this warp's half
+    const int sidx = (warp - 2) * 32 + lane;  // 0..255 among the element-wise threads
+    const uint32_t lane_sel = uint32_t(qd * 32) << 16;
+    const float scale_log2 = p.scale * LOG2E;
+    const bool capped = p.softcap > 0.f;
+    const float inv_cap = capped ? 1.f / p.softcap : 0.f;
+    const float cap2 = p.softcap * LOG2E;
+
+    auto load_stat = [&](int t) -> float {
+      // threads 0..127 fetch lse (log2 units) of query row sidx, threads 128..255 delta of row sidx-128
       const int g = t / n_i, i = i_lo + (t - g * n_i);
       const int hq = hk * G + g;
+      const int qr = i * BT + (sidx & 127);
+      if (qr >= len_q) return 0.f;
+      const long long idx = (long long)hq * p.total_q + q_start + qr;
+      return sidx < 128 ? p.lse[idx] * LOG2E : p.delta[idx];
+    };
+    // Bounded rendezvous (an mbarrier instead of bar.sync, so that an abandoned wait cannot hang the CTA).
+    int stat_phase = 0;
+    bool alive = true;
+    auto rendezvous = [&]() {
+      mbar_arrive(b_stat);
+      if (!mbar_wait(b_stat, stat_phase & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) alive = false;
+      ++stat_phase;
+    };
+    if (n > 0) {
+      s_stat[sidx] = load_stat(0);
+      rendezvous();
+    }
+
+    for (int t = 0; t < n && alive; ++t) {
+      const int g = t / n_i, i = i_lo + (t - g * n_i);
       const int q0 = i * BT;
-      // stage lse (log2 units) and delta for the 128 query columns of this tile
-      {
-        const int qr = q0 + r;
-        float l2 = 0.f, dl = 0.f;
-        if (qr < len_q) {
-          const long long idx = (long long)hq * p.total_q + q_start + qr;
-          l2 = p.lse[idx] * 1.4426950408889634f;
-          dl = p.delta[idx];
-        }
-        softmax_bar();  // previous step's readers are done with s_lse / s_delta
-        s_lse[r] = l2;
-        s_delta[r] = dl;
-        softmax_bar();
-      }
+      const float* st_lse = s_stat + (t & 1) * 256;
+      const float* st_dl = st_lse + 128;
+      const float next_stat = (t + 1 < n) ? load_stat(t + 1) : 0.f;
       if (!mbar_wait(b_sfull, t & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
         alive = false;
         break;
       }
       tc_fence_after();
+      uint32_t s[64];
+      tmem_ld_32x32b_x64(tS + lane_sel + cb, s);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(b_sfree);
       const bool tile_mask = (kv0 + BT > len_k) || (q0 + BT > len_q) || (p.causal && kv0 + BT - 1 > q0 + off) ||
                              (p.window > 0 && kv0 < q0 + BT - 1 + off - p.window + 1);
-#pragma unroll 1
-      for (int c2 = 0; c2 < 2; ++c2) {   // 64 query columns per round
-        uint32_t pk[32], dk_[32];
+      float pd[64];
+      uint32_t pkp[32];
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = c2 * 2 + cc;
-          uint32_t rs[32], rd[32];
-          tmem_ld_32x32b_x32(tS + lane_sel + c * 32, rs);
-          tmem_ld_32x32b_x32(tDP + lane_sel + c * 32, rd);
-          tc_wait_ld();
+      for (int x = 0; x < 64; x += 2) {
+        float pv[2];
 #pragma unroll
-          for (int x = 0; x < 32; x += 2) {
-            float pv[2], dsv[2];
-#pragma unroll
-            for (int y = 0; y < 2; ++y) {
-              const int col = c * 32 + x + y;
-              float sv = __uint_as_float(rs[x + y]);
-              float dcap = 1.f;
-              float s2;
-              if (p.softcap > 0.f) {
-                const float th = tanhf(sv * p.scale * inv_cap);
-                s2 = cap2 * th;
-                dcap = 1.f - th * th;
-              } else {
-                s2 = sv * scale_log2;
-              }
-              float pe = exp2f(s2 - s_lse[col]);
-              if (tile_mask) {
-                const int qpos = q0 + col + off;
-                const bool okm = (kpos < len_k) && (q0 + col < len_q) && (!p.causal || kpos <= qpos) &&
-                                 (p.window <= 0 || kpos > qpos - p.window);
-                pe = okm ? pe : 0.f;
-              }
-              pv[y] = pe;
-              dsv[y] = pe * (__uint_as_float(rd[x + y]) - s_delta[col]) * dcap;
-            }
-            pk[cc * 16 + x / 2] = pack_bf16x2(pv[0], pv[1]);
-            dk_[cc * 16 + x / 2] = pack_bf16x2(dsv[0], dsv[1]);
+        for (int y = 0; y < 2; ++y) {
+          const int col = cb + x + y;
+          float sv = __uint_as_float(s[x + y]);
+          float dcap = 1.f, s2;
+          if (capped) {
+            const float th = tanhf(sv * p.scale * inv_cap);
+            s2 = cap2 * th;
+            dcap = 1.f - th * th;
+          } else {
+            s2 = sv * scale_log2;
           }
+          float pe = exp2f(s2 - st_lse[col]);
+          if (tile_mask) {
+            const int qpos = q0 + col + off;
+            const bool okm = (kpos < len_k) && (q0 + col < len_q) && (!p.causal || kpos <= qpos) &&
+                             (p.window <= 0 || kpos > qpos - p.window);
+            pe = okm ? pe : 0.f;
+          }
+          pv[y] = pe;
+          pd[x + y] = pe * dcap;
         }
-        tmem_st_32x32b_x32(tS + lane_sel + c2 * 32, pk);
-        tmem_st_32x32b_x32(tDP + lane_sel + c2 * 32, dk_);
-        // dS^T row r, query columns [64*c2, 64*c2+64): 8 units of 16 bytes, 128-byte swizzle
-        uint8_t* dsrow = smem + C::OFF_DS + c2 * (BT * 128) + r * 128;
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          uint4 val = make_uint4(dk_[4 * u], dk_[4 * u + 1], dk_[4 * u + 2], dk_[4 * u + 3]);
-          *reinterpret_cast<uint4*>(dsrow + ((u ^ (r & 7)) << 4)) = val;
-        }
+        pkp[x >> 1] = pack_bf16x2(pv[0], pv[1]);
       }
-      tc_wait_st();
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(b_pfull);
-
-      // dQ tile of this step: rows are queries now
-      if (!mbar_wait(b_dqfull, t & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
+      if (!mbar_wait(b_dpfull, t & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
         alive = false;
         break;
       }
       tc_fence_after();
-      const int qrow = q0 + r;
-      float* dqp = p.dq + ((long long)(q_start + qrow) * p.Hq + hq) * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t rr[32];
-        tmem_ld_32x32b_x32(tS + lane_sel + c * 32, rr);
-        tc_wait_ld();
-        if (qrow < len_q) {
+      tmem_ld_32x32b_x64(tDP + lane_sel + cb, s);
+      tc_wait_ld();
+      uint32_t pkd[32];
 #pragma unroll
-          for (int x = 0; x < 32; x += 4)
-            red_add_v4(dqp + c * 32 + x, __uint_as_float(rr[x]) * p.scale, __uint_as_float(rr[x + 1]) * p.scale,
-                       __uint_as_float(rr[x + 2]) * p.scale, __uint_as_float(rr[x + 3]) * p.scale);
-        }
-      }
+      for (int x = 0; x < 64; x += 2)
+        pkd[x >> 1] = pack_bf16x2(pd[x] * (__uint_as_float(s[x]) - st_dl[cb + x]),
+                                  pd[x + 1] * (__uint_as_float(s[x + 1]) - st_dl[cb + x + 1]));
+      tmem_st_32x32b_x32(tDP + lane_sel + cb, pkp);        // P^T piece of this half
+      tmem_st_32x32b_x32(tDP + lane_sel + cb + 32, pkd);   // dS^T piece of this half
+      tc_wait_st();
       tc_fence_before();
-      mbar_arrive(b_tfree);
+      mbar_arrive(b_pfull);
+      if (t + 1 < n) s_stat[((t + 1) & 1) * 256 + sidx] = next_stat;
+      rendezvous();
     }
-
-    // dK, dV
+    if (alive && n > 0) {
+      if (!mbar_wait(b_final, 0, abort_flag, p.status, EDL_TIMEOUT_EPILOGUE)) alive = false;
+      tc_fence_after();
+    }
     if (alive) {
-      const bool row_ok = kpos < len_k;
-      __nv_bfloat16* dkp = p.dk + (long long)(k_start + kpos) * p.lddk + (long long)hk * D;
-      __nv_bfloat16* dvp = p.dv + (long long)(k_start + kpos) * p.lddv + (long long)hk * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t rk[32], rv[32];
-        if (n_steps > 0) {
-          tmem_ld_32x32b_x32(tDK + lane_sel + c * 32, rk);
-          tmem_ld_32x32b_x32(tDV + lane_sel + c * 32, rv);
-          tc_wait_ld();
+      constexpr int HC = D / 2;
+      uint32_t rk[HC], rv[HC];
+      if (n > 0) {
+        if constexpr (HC == 64) {
+          tmem_ld_32x32b_x64(tDK + lane_sel + half * HC, rk);
+          tmem_ld_32x32b_x64(tDV + lane_sel + half * HC, rv);
         } else {
-#pragma unroll
-          for (int x = 0; x < 32; ++x) rk[x] = rv[x] = 0u;
+          tmem_ld_32x32b_x32(tDK + lane_sel + half * HC, rk);
+          tmem_ld_32x32b_x32(tDV + lane_sel + half * HC, rv);
         }
-        if (row_ok) {
+        tc_wait_ld();
+      } else {
 #pragma unroll
-          for (int x = 0; x < 32; x += 8) {
-            uint4 a, bq;
-            a.x = pack_bf16x2(__uint_as_float(rk[x]) * p.scale, __uint_as_float(rk[x + 1]) * p.scale);
-            a.y = pack_bf16x2(__uint_as_float(rk[x + 2]) * p.scale, __uint_as_float(rk[x + 3]) * p.scale);
-            a.z = pack_bf16x2(__uint_as_float(rk[x + 4]) * p.scale, __uint_as_float(rk[x + 5]) * p.scale);
-            a.w = pack_bf16x2(__uint_as_float(rk[x + 6]) * p.scale, __uint_as_float(rk[x + 7]) * p.scale);
-            bq.x = pack_bf16x2(__uint_as_float(rv[x]), __uint_as_float(rv[x + 1]));
-            bq.y = pack_bf16x2(__uint_as_float(rv[x + 2]), __uint_as_float(rv[x + 3]));
-            bq.z = pack_bf16x2(__uint_as_float(rv[x + 4]), __uint_as_float(rv[x + 5]));
-            bq.w = pack_bf16x2(__uint_as_float(rv[x + 6]), __uint_as_float(rv[x + 7]));
-            *reinterpret_cast<uint4*>(dkp + c * 32 + x) = a;
-            *reinterpret_cast<uint4*>(dvp + c * 32 + x) = bq;
-          }
-        }
+        for (int x = 0; x < HC; ++x) rk[x] = rv[x] = 0u;
+      }
+      if (kpos < len_k) {
+        store_rows_bf16<HC>(p.dk + (long long)(k_start + kpos) * p.lddk + (long long)hk * D + half * HC, rk, p.scale);
+        store_rows_bf16<HC>(p.dv + (long long)(k_start + kpos) * p.lddv + (long long)hk * D + half * HC, rv, 1.f);
       }
     }
   }
@@ -397,40 +661,42 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dout, lo
   if (make_tmap_3d_16b(&tk, k, D, p.Hkv, total_k, D, ldk, 64, 1, BT, 3)) return -1;
   if (make_tmap_3d_16b(&tv, v, D, p.Hkv, total_k, D, ldv, 64, 1, BT, 3)) return -1;
   if (make_tmap_3d_16b(&tdo, dout, D, p.Hq, total_q, D, lddo, 64, 1, BT, 3)) return -1;
-  auto kern = attn_bwd_kernel<D>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM),
-                   "cudaFuncSetAttribute(attn_bwd)"))
+    if (check_cuda(cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM),
+                   "cudaFuncSetAttribute(attn_bwd_dq)") ||
+        check_cuda(cudaFuncSetAttribute(attn_bwd_dkv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM),
+                   "cudaFuncSetAttribute(attn_bwd_dkv)"))
       return -1;
     attr_set = true;
   }
-  dim3 grid((p.Tk + BT - 1) / BT, p.Hkv, p.B);
-  kern<<<grid, BWD_THREADS, C::SMEM, stream>>>(tq, tk, tv, tdo, p);
-  return check_cuda(cudaGetLastError(), "attn_bwd launch");
+  dim3 grid_kv((p.Tk + BT - 1) / BT, p.Hkv, p.B);
+  attn_bwd_dkv_kernel<D><<<grid_kv, BWD_THREADS, C::SMEM, stream>>>(tq, tk, tv, tdo, p);
+  if (check_cuda(cudaGetLastError(), "attn_bwd_dkv launch")) return -1;
+  dim3 grid_q((p.Tq + BT - 1) / BT, p.Hq, p.B);
+  attn_bwd_dq_kernel<D><<<grid_q, BWD_THREADS, C::SMEM, stream>>>(tq, tk, tv, tdo, p);
+  return check_cuda(cudaGetLastError(), "attn_bwd_dq launch");
 }
 
 }  // namespace
 }  // namespace edl
 
-// Gradients of edl_attn_fwd. `delta` ([Hq,total_q] fp32) is scratch the caller provides;
-// `dq` is an fp32 [total_q, Hq, D] buffer the caller has zeroed (tiles are added to it);
-// dk/dv are bf16 with row strides lddk/lddv. `reserved` must be null.
+// Gradients of edl_attn_fwd. `delta` ([Hq,total_q] fp32) is scratch the caller provides.
+// dq/dk/dv are bf16 with row strides lddq/lddk/lddv (heads packed inside a row like q/k/v).
 EDL_HOST_API int edl_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                              const float* lse, float* delta, float* dq, void* dk, void* dv, void* reserved,
-                              long long ldq, long long ldk, long long ldv, long long ldo, long long lddo,
+                              const float* lse, float* delta, void* dq, void* dk, void* dv, long long ldq,
+                              long long ldk, long long ldv, long long ldo, long long lddo, long long lddq,
                               long long lddk, long long lddv, const int* cu_q, const int* cu_k, int B, int Tq, int Tk,
                               long long total_q, long long total_k, int Hq, int Hkv, int D, float scale, int causal,
                               int window, float softcap, int* status, void* stream) {
   using namespace edl;
-  (void)reserved;
   if (B <= 0 || total_q <= 0 || total_k <= 0) return 0;
   if (D != 64 && D != 128) {
     set_last_error("edl_attn_bwd: head_dim %d not supported (64 or 128)", D);
     return -1;
   }
-  if ((lddk & 7) || (lddv & 7)) {
-    set_last_error("edl_attn_bwd: dk/dv row strides must be multiples of 8");
+  if ((lddq & 7) || (lddk & 7) || (lddv & 7)) {
+    set_last_error("edl_attn_bwd: dq/dk/dv row strides must be multiples of 8");
     return -1;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -444,9 +710,10 @@ EDL_HOST_API int edl_attn_bwd(const void* q, const void* k, const void* v, const
   AttnBwdParams p;
   p.lse = lse;
   p.delta = delta;
-  p.dq = dq;
+  p.dq = (__nv_bfloat16*)dq;
   p.dk = (__nv_bfloat16*)dk;
   p.dv = (__nv_bfloat16*)dv;
+  p.lddq = lddq;
   p.lddk = lddk;
   p.lddv = lddv;
   p.cu_q = cu_q;

@@ -11,7 +11,7 @@ from . import _lib
 vp, i32, i64, f32 = _lib.vp, _lib.i32, _lib.i64, _lib.f32
 _lib.register("edl_attn_fwd", i32, [vp, vp, vp, vp, vp, i64, i64, i64, i64, vp, vp, i32, i32, i32, i64, i64, i32, i32,
                                     i32, f32, i32, i32, f32, vp, vp, vp])
-_lib.register("edl_attn_bwd", i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64,
+_lib.register("edl_attn_bwd", i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64, i64,
                                     vp, vp, i32, i32, i32, i64, i64, i32, i32, i32, f32, i32, i32, f32, vp, vp])
 
 
@@ -73,18 +73,17 @@ def attn_bwd(q, k, v, o, lse, do, *, causal=True, scale=None, window=0, softcap=
         do = do.contiguous()
     if not o.is_contiguous():
         o = o.contiguous()
-    dq_acc = torch.zeros((total_q, Hq, D), dtype=torch.float32, device=q.device)
+    dq = torch.empty((*q.shape[:-2], Hq, D), dtype=q.dtype, device=q.device) if dq is None else dq
     dk = torch.empty((*k.shape[:-2], Hkv, D), dtype=k.dtype, device=k.device) if dk is None else dk
     dv = torch.empty((*v.shape[:-2], Hkv, D), dtype=v.dtype, device=v.device) if dv is None else dv
     delta = torch.empty((Hq, total_q), dtype=torch.float32, device=q.device)
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     _lib.call("edl_attn_bwd", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
-              delta.data_ptr(), dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), None, q.stride(-3), k.stride(-3),
-              v.stride(-3), o.stride(-3), do.stride(-3), dk.stride(-3), dv.stride(-3), _lib.ptr(cu_q),
+              delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), q.stride(-3), k.stride(-3),
+              v.stride(-3), o.stride(-3), do.stride(-3), dq.stride(-3), dk.stride(-3), dv.stride(-3), _lib.ptr(cu_q),
               _lib.ptr(cu_k), B, Tq, Tk, total_q, total_k, Hq, Hkv, D, float(scale), int(causal), int(window or 0),
               float(softcap or 0.0), _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
-    dq_out = dq_acc.to(q.dtype).view(q.shape) if dq is None else dq.copy_(dq_acc.view(q.shape))
-    return dq_out, dk, dv
+    return dq, dk, dv
 
 
 class _FlashAttnFn(torch.autograd.Function):

@@ -1,0 +1,119 @@
+"""Multi-process (gloo, CPU ranks) tests of the mesh and the sharded optimizer step."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(fn, world, *args, timeout: float = 240.0):
+    """Spawns ``world`` gloo ranks; a rank that never finishes fails the test instead of hanging it."""
+    port = _free_port()
+    ctx = mp.spawn(_entry, args=(fn, world, port, args), nprocs=world, join=False)
+    import time
+
+    deadline = time.time() + timeout
+    while not ctx.join(timeout=1.0):
+        if time.time() > deadline:
+            for p in ctx.processes:
+                if p.is_alive():
+                    p.terminate()
+            raise TimeoutError(f"distributed test did not finish within {timeout}s")
+
+
+def _entry(rank, fn, world, port, args):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    import datetime
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
+    try:
+        fn(rank, world, *args)
+    finally:
+        dist.destroy_process_group()
+
+
+def _tiny(seed):
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+
+    cfg = LlamaConfig(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=32)
+    torch.manual_seed(seed)
+    return LlamaForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32)
+
+
+def _sharded_step_worker(rank, world):
+    from easydel_b200.infra.base_state import EasyDeLState
+    from easydel_b200.optimizers import OptimizerFactory, SchedulerConfig
+
+    model = _tiny(seed=rank)  # different init per rank: the broadcast must make them equal
+    tx, _ = OptimizerFactory.create("adamw", SchedulerConfig(None, learning_rate=1e-2), weight_decay=0.01,
+                                    clip_grad=1.0)
+    state = EasyDeLState.create(model=model, tx=tx, init_opt_state=True)
+    assert state._dist is not None and state.flat.world_size == world
+    g = torch.Generator().manual_seed(7)
+    data = torch.randint(0, 128, (2 * world, 16), generator=g)
+    mine = data[2 * rank:2 * rank + 2]
+    for _ in range(2):
+        _, met = model.compute_loss(input_ids=mine, labels=mine)
+        met.loss.backward()
+        norm = state.apply_gradients()
+    flat_w = state.flat.work.clone()
+    gathered = [torch.empty_like(flat_w) for _ in range(world)]
+    dist.all_gather(gathered, flat_w)
+    for t in gathered:
+        assert torch.equal(t, gathered[0]), "ranks diverged"
+    if rank == 0:
+        # single-process reference on the full batch (mean over ranks == mean over the global batch here)
+        from easydel_b200.parallel.mesh import DeviceMesh
+
+        ref = _tiny(seed=0)
+        ref.config.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), ref.config.sharding_axis_names, rank=0, world_size=1))
+        tx2, _ = OptimizerFactory.create("adamw", SchedulerConfig(None, learning_rate=1e-2), weight_decay=0.01,
+                                         clip_grad=1.0)
+        st2 = EasyDeLState.create(model=ref, tx=tx2, init_opt_state=True)
+        assert st2._dist is None
+        for _ in range(2):
+            for r in range(world):
+                mb = data[2 * r:2 * r + 2]
+                _, met = ref.compute_loss(input_ids=mb, labels=mb, loss_scale=1.0 / world)
+                met.loss.backward()
+            n2 = st2.apply_gradients()
+        a = dict(ref.named_parameters())
+        for n_, p in model.named_parameters():
+            assert torch.allclose(p, a[n_], atol=2e-5), n_
+        assert abs(float(norm) - float(n2)) < 1e-4
+
+
+def _mesh_worker(rank, world):
+    from easydel_b200.parallel.mesh import DeviceMesh
+
+    mesh = DeviceMesh.create((1, -1, 1, 2, 1), ("dp", "fsdp", "ep", "tp", "sp"))
+    assert mesh.shape == {"dp": 1, "fsdp": world // 2, "ep": 1, "tp": 2, "sp": 1}
+    tpg = mesh.get_group("tp")
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t, group=tpg)
+    base = rank - rank % 2
+    assert t.item() == base + base + 1
+    assert mesh.axis_index("tp") == rank % 2 and mesh.axis_index("fsdp") == rank // 2
+    fg = mesh.get_group("fsdp")
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t, group=fg)
+    assert t.item() == sum(r for r in range(world) if r % 2 == rank % 2)
+
+
+def test_mesh_groups_4_ranks():
+    _run(_mesh_worker, 4)
+
+
+def test_sharded_optimizer_matches_single_process():
+    _run(_sharded_step_worker, 2)
