@@ -249,6 +249,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       dl = p.delta[idx];
     }
     bool alive = true;
+    const float neg_lse2 = -lse2;
     for (int it = 0; it < n && alive; ++it) {
       const int kv0 = (lo + it) * BT;
       if (!mbar_wait(b_sfull + 8 * (it & 1), (it >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
@@ -261,26 +262,26 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       tc_wait_ld();
       const bool tile_mask = (kv0 + BT > len_k) || (q0 + BT > len_q) || (p.causal && kv0 + BT - 1 > q0 + off) ||
                              (p.window > 0 && kv0 < q0 + BT - 1 + off - p.window + 1);
+      // pd = P * d(capped score)/d(score); the common (uncapped, unmasked) path is one FMA and one EX2 per element
       float pd[64];
+      if (!capped) {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        float sv = __uint_as_float(s[i]);
-        float dcap = 1.f, s2;
-        if (capped) {
-          const float th = tanhf(sv * p.scale * inv_cap);
-          s2 = cap2 * th;
-          dcap = 1.f - th * th;
-        } else {
-          s2 = sv * scale_log2;
+        for (int i = 0; i < 64; ++i) pd[i] = exp2f(fmaf(__uint_as_float(s[i]), scale_log2, neg_lse2));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float th = tanhf(__uint_as_float(s[i]) * p.scale * inv_cap);
+          pd[i] = exp2f(fmaf(cap2, th, neg_lse2)) * (1.f - th * th);
         }
-        float pe = exp2f(s2 - lse2) * dcap;
-        if (tile_mask) {
+      }
+      if (tile_mask) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
           const int kpos = kv0 + cb + i;
           const bool okm = (kpos < len_k) && (qrow < len_q) && (!p.causal || kpos <= qpos) &&
                            (p.window <= 0 || kpos > qpos - p.window);
-          pe = okm ? pe : 0.f;
+          pd[i] = okm ? pd[i] : 0.f;
         }
-        pd[i] = pe;
       }
       if (!mbar_wait(b_dpfull, it & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
         alive = false;
@@ -544,34 +545,47 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       mbar_arrive(b_sfree);
       const bool tile_mask = (kv0 + BT > len_k) || (q0 + BT > len_q) || (p.causal && kv0 + BT - 1 > q0 + off) ||
                              (p.window > 0 && kv0 < q0 + BT - 1 + off - p.window + 1);
-      float pd[64];
+      // P^T is kept only as packed bf16 (the form the dV product consumes); dS^T is formed from those
+      // rounded values, which keeps the live register set small. lse / delta of the 64 query columns
+      // come from shared memory as 16-byte broadcasts. Common path: one FMA and one EX2 per element.
       uint32_t pkp[32];
+      if (!capped && !tile_mask) {
 #pragma unroll
-      for (int x = 0; x < 64; x += 2) {
-        float pv[2];
+        for (int x = 0; x < 64; x += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(st_lse + cb + x);
+          pkp[x >> 1] = pack_bf16x2(exp2f(fmaf(__uint_as_float(s[x]), scale_log2, -l4.x)),
+                                    exp2f(fmaf(__uint_as_float(s[x + 1]), scale_log2, -l4.y)));
+          pkp[(x >> 1) + 1] = pack_bf16x2(exp2f(fmaf(__uint_as_float(s[x + 2]), scale_log2, -l4.z)),
+                                          exp2f(fmaf(__uint_as_float(s[x + 3]), scale_log2, -l4.w)));
+        }
+      } else {
 #pragma unroll
-        for (int y = 0; y < 2; ++y) {
-          const int col = cb + x + y;
-          float sv = __uint_as_float(s[x + y]);
-          float dcap = 1.f, s2;
-          if (capped) {
-            const float th = tanhf(sv * p.scale * inv_cap);
-            s2 = cap2 * th;
-            dcap = 1.f - th * th;
-          } else {
-            s2 = sv * scale_log2;
-          }
-          float pe = exp2f(s2 - st_lse[col]);
-          if (tile_mask) {
+        for (int x = 0; x < 64; x += 2) {
+          float pv[2];
+#pragma unroll
+          for (int y = 0; y < 2; ++y) {
+            const int col = cb + x + y;
+            float s2 = __uint_as_float(s[x + y]) * scale_log2;
+            float dcap = 1.f;
+            if (capped) {
+              const float th = tanhf(__uint_as_float(s[x + y]) * p.scale * inv_cap);
+              s2 = cap2 * th;
+              dcap = 1.f - th * th;
+            }
+            float pe = exp2f(s2 - st_lse[col]);
             const int qpos = q0 + col + off;
             const bool okm = (kpos < len_k) && (q0 + col < len_q) && (!p.causal || kpos <= qpos) &&
                              (p.window <= 0 || kpos > qpos - p.window);
-            pe = okm ? pe : 0.f;
+            pv[y] = okm ? pe : 0.f;
+            s[x + y] = __float_as_uint(dcap);   // the raw score is no longer needed
           }
-          pv[y] = pe;
-          pd[x + y] = pe * dcap;
+          pkp[x >> 1] = pack_bf16x2(pv[0], pv[1]);
         }
-        pkp[x >> 1] = pack_bf16x2(pv[0], pv[1]);
+      }
+      uint32_t dcp[32];   // soft-cap derivative, packed bf16 (only meaningful when capped)
+      if (capped) {
+#pragma unroll
+        for (int x = 0; x < 64; x += 2) dcp[x >> 1] = pack_bf16x2(__uint_as_float(s[x]), __uint_as_float(s[x + 1]));
       }
       if (!mbar_wait(b_dpfull, t & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
         alive = false;
@@ -582,9 +596,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       tc_wait_ld();
       uint32_t pkd[32];
 #pragma unroll
-      for (int x = 0; x < 64; x += 2)
-        pkd[x >> 1] = pack_bf16x2(pd[x] * (__uint_as_float(s[x]) - st_dl[cb + x]),
-                                  pd[x + 1] * (__uint_as_float(s[x + 1]) - st_dl[cb + x + 1]));
+      for (int x = 0; x < 64; x += 4) {
+        const float4 d4 = *reinterpret_cast<const float4*>(st_dl + cb + x);
+        float2 p0 = unpack_bf16x2(pkp[x >> 1]), p1 = unpack_bf16x2(pkp[(x >> 1) + 1]);
+        if (capped) {
+          const float2 c0 = unpack_bf16x2(dcp[x >> 1]), c1 = unpack_bf16x2(dcp[(x >> 1) + 1]);
+          p0.x *= c0.x; p0.y *= c0.y; p1.x *= c1.x; p1.y *= c1.y;
+        }
+        pkd[x >> 1] = pack_bf16x2(p0.x * (__uint_as_float(s[x]) - d4.x), p0.y * (__uint_as_float(s[x + 1]) - d4.y));
+        pkd[(x >> 1) + 1] =
+            pack_bf16x2(p1.x * (__uint_as_float(s[x + 2]) - d4.z), p1.y * (__uint_as_float(s[x + 3]) - d4.w));
+      }
       tmem_st_32x32b_x32(tDP + lane_sel + cb, pkp);        // P^T piece of this half
       tmem_st_32x32b_x32(tDP + lane_sel + cb + 32, pkd);   // dS^T piece of this half
       tc_wait_st();
@@ -732,3 +754,4 @@ EDL_HOST_API int edl_attn_bwd(const void* q, const void* k, const void* v, const
   if (D == 128) return launch_bwd<128>(q, k, v, dout, ldq, ldk, ldv, lddo, total_q, total_k, p, s);
   return launch_bwd<64>(q, k, v, dout, ldq, ldk, ldv, lddo, total_q, total_k, p, s);
 }
+
