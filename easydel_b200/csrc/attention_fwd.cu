@@ -48,6 +48,12 @@ struct AttnFwdParams {
   int causal;
   int window;            // 0 = off; keys with pos <= qpos - window are masked
   int* status;
+  // paged / packed mode (serving): keys and values live in pages of BKV tokens addressed through a
+  // per-sequence page table, and the `pack` query heads of one KV head share a tile (row = token*pack + head)
+  const int* page_table; // [B, pt_stride] page ids, or null
+  const int* kv_lens;    // [B] keys per sequence (context length including the new tokens), paged mode
+  int pt_stride;
+  int pack;              // query heads per tile row group (1 = one head per CTA)
 };
 
 template <int D>
@@ -65,11 +71,13 @@ struct TileRange {
   int lo, hi;  // key-tile indices [lo, hi) this query tile attends to
 };
 
-__device__ __forceinline__ TileRange tile_range(int q0, int len_q, int len_k, int off, int causal, int window) {
+__device__ __forceinline__ TileRange tile_range(int q0, int tq, int len_q, int len_k, int off, int causal,
+                                                int window) {
+  // q0: first query token of the tile, tq: query tokens per tile
   TileRange r{0, 0};
   if (q0 >= len_q) return r;
   int kv_hi = len_k;
-  if (causal) kv_hi = min(len_k, q0 + BQ + off);
+  if (causal) kv_hi = min(len_k, q0 + tq + off);
   int kv_lo = 0;
   if (window > 0) kv_lo = max(0, q0 + off - window + 1);
   if (kv_hi <= kv_lo) return r;
@@ -102,19 +110,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int hk = h / (p.Hq / p.Hkv);
+  const int b = blockIdx.z;
+  const int pack = p.pack;                       // power of two, divides BQ
+  const int pshift = 31 - __clz(pack);
+  const int TQ = BQ >> pshift;                   // query tokens per tile
+  const int h = blockIdx.y;                      // query head (pack == 1) or KV head (packed)
+  const int hk = pack == 1 ? h / (p.Hq / p.Hkv) : h;
+  const int h_first = pack == 1 ? h : hk * pack; // first query head of this CTA's rows
 
   const int q_start = p.cu_q ? p.cu_q[b] : b * p.Tq;
-  const int k_start = p.cu_k ? p.cu_k[b] : b * p.Tk;
+  const int k_start = p.page_table ? 0 : (p.cu_k ? p.cu_k[b] : b * p.Tk);
   const int len_q = p.cu_q ? p.cu_q[b + 1] - q_start : p.Tq;
-  const int len_k = p.cu_k ? p.cu_k[b + 1] - k_start : p.Tk;
-  const int qblock0 = qb * 2 * BQ;
+  const int len_k = p.kv_lens ? p.kv_lens[b] : (p.cu_k ? p.cu_k[b + 1] - k_start : p.Tk);
+  const int* pt = p.page_table ? p.page_table + (long long)b * p.pt_stride : nullptr;
+  const int qblock0 = qb * 2 * TQ;
   if (qblock0 >= len_q) return;
-  const int off = len_k - len_q;  // absolute key position of query row r is r + off
+  const int off = len_k - len_q;  // absolute key position of query token r is r + off
 
-  const TileRange rgA = tile_range(qblock0, len_q, len_k, off, p.causal, p.window);
-  const TileRange rgB = tile_range(qblock0 + BQ, len_q, len_k, off, p.causal, p.window);
+  const TileRange rgA = tile_range(qblock0, TQ, len_q, len_k, off, p.causal, p.window);
+  const TileRange rgB = tile_range(qblock0 + TQ, TQ, len_q, len_k, off, p.causal, p.window);
   const bool anyA = rgA.hi > rgA.lo, anyB = rgB.hi > rgB.lo;
   int jmin = 0, jmax = 0;
   if (anyA && anyB) {
@@ -161,11 +175,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       for (int t = 0; t < 2; ++t)
 #pragma unroll
         for (int c = 0; c < C::DCH; ++c)
-          tma_load_3d(sQ + t * C::Q_BYTES + c * (BQ * 128), &tq, b_qfull, c * 64, h, q_start + qblock0 + t * BQ);
+          tma_load_3d(sQ + t * C::Q_BYTES + c * (BQ * 128), &tq, b_qfull, c * 64, h_first, q_start + qblock0 + t * TQ);
       for (int j = jmin; j < jmax; ++j) {
         const int it = j - jmin;
         const int s = it & 1;
-        const int krow = k_start + j * BKV;
+        const int krow = pt ? pt[j] * BKV : k_start + j * BKV;
         if (it >= 2 &&
             !mbar_wait(b_kempty + 8 * s, ((it >> 1) - 1) & 1, abort_flag, p.status, EDL_TIMEOUT_PRODUCER))
           break;
@@ -250,8 +264,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const int t = (warp - 2) >> 2;          // query tile handled by this softmax group
     const int q = warp & 3;                 // tensor-memory lane quadrant of this warp
     const int r = q * 32 + lane;            // query row within the tile
-    const int q0 = qblock0 + t * BQ;
-    const int qrow = q0 + r;                // row within the sequence
+    const int q0 = qblock0 + t * TQ;        // first query token of the tile
+    const int qrow = q0 + (r >> pshift);    // query token (within the sequence) of this row
+    const int qhead = h_first + (r & (pack - 1));
     const int qpos = qrow + off;            // absolute key position of this query
     const TileRange rg = t == 0 ? rgA : rgB;
     const uint32_t lane_sel = uint32_t(q * 32) << 16;
@@ -279,7 +294,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tmem_ld_32x32b_x64(tS + 64, c2);
       tc_wait_ld();
       const bool tile_mask = (kv0 + BKV > len_k) || (p.causal && kv0 + BKV - 1 > q0 + off) ||
-                             (p.window > 0 && kv0 < q0 + BQ - 1 + off - p.window + 1);
+                             (p.window > 0 && kv0 < q0 + TQ - 1 + off - p.window + 1);
       if (capped) {
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
@@ -356,10 +371,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tc_fence_after();
     }
     if (alive && q0 < len_q) {
-      if (p.sinks) l += exp2f(p.sinks[h] * LOG2E - m_used);
+      if (p.sinks) l += exp2f(p.sinks[qhead] * LOG2E - m_used);
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
       const bool row_ok = qrow < len_q;
-      __nv_bfloat16* op = p.o + (long long)(q_start + qrow) * p.ldo + (long long)h * D;
+      __nv_bfloat16* op = p.o + (long long)(q_start + qrow) * p.ldo + (long long)qhead * D;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t rr[32];
@@ -383,7 +398,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         }
       }
       if (row_ok && p.lse)
-        p.lse[(long long)h * p.total_q + q_start + qrow] = l > 0.f ? (m_used + log2f(l)) * LN2 : -INFINITY;
+        p.lse[(long long)qhead * p.total_q + q_start + qrow] = l > 0.f ? (m_used + log2f(l)) * LN2 : -INFINITY;
     }
   }
 
@@ -402,7 +417,7 @@ int launch_fwd(const void* q, const void* k, const void* v, long long ldq, long 
                long long total_q, long long total_k, const AttnFwdParams& p, cudaStream_t stream) {
   using C = ACfg<D>;
   CUtensorMap tq, tk, tv;
-  if (make_tmap_3d_16b(&tq, q, D, p.Hq, total_q, D, ldq, 64, 1, BQ, 3)) return -1;
+  if (make_tmap_3d_16b(&tq, q, D, p.Hq, total_q, D, ldq, 64, p.pack, BQ / p.pack, 3)) return -1;
   if (make_tmap_3d_16b(&tk, k, D, p.Hkv, total_k, D, ldk, 64, 1, BKV, 3)) return -1;
   if (make_tmap_3d_16b(&tv, v, D, p.Hkv, total_k, D, ldv, 64, 1, BKV, 3)) return -1;
   auto kern = attn_fwd_kernel<D>;
@@ -413,7 +428,8 @@ int launch_fwd(const void* q, const void* k, const void* v, long long ldq, long 
       return -1;
     attr_set = true;
   }
-  dim3 grid((p.Tq + 2 * BQ - 1) / (2 * BQ), p.Hq, p.B);
+  const int tq_block = 2 * BQ / p.pack;  // query tokens per CTA
+  dim3 grid((p.Tq + tq_block - 1) / tq_block, p.pack == 1 ? p.Hq : p.Hkv, p.B);
   kern<<<grid, ATT_THREADS, C::SMEM, stream>>>(tq, tk, tv, p);
   return check_cuda(cudaGetLastError(), "attn_fwd launch");
 }
@@ -463,7 +479,64 @@ EDL_HOST_API int edl_attn_fwd(const void* q, const void* k, const void* v, void*
   p.causal = causal;
   p.window = window;
   p.status = status;
+  p.page_table = nullptr;
+  p.kv_lens = nullptr;
+  p.pt_stride = 0;
+  p.pack = 1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (D == 128) return launch_fwd<128>(q, k, v, ldq, ldk, ldv, total_q, total_k, p, s);
   return launch_fwd<64>(q, k, v, ldq, ldk, ldv, total_q, total_k, p, s);
+}
+
+// Paged attention for serving (mixed prefill + decode in one launch).
+//   q:        [total_q, ldq] new query tokens of all sequences, concatenated; cu_q [B+1] their offsets
+//   k_pages / v_pages: [num_pages * 128, ld_page] page pools (page size 128 tokens), heads packed in a row;
+//             the new tokens' keys/values must already be written to their pages
+//   page_table [B, pt_stride]: page ids of each sequence in order; kv_lens [B]: keys per sequence
+//             (cached + new). Query token i of a sequence sits at key position kv_len - len_q + i.
+//   max_q:    largest number of new tokens of any sequence (sizes the grid)
+// All query heads of a KV head share one tile (rows = token x head), so one pass over a page
+// serves the whole GQA group. Hq / Hkv must be a power of two <= 128.
+EDL_HOST_API int edl_attn_paged(const void* q, const void* k_pages, const void* v_pages, void* o, long long ldq,
+                                long long ld_page, long long ldo, const int* cu_q, const int* kv_lens,
+                                const int* page_table, int pt_stride, int B, int max_q, long long total_q,
+                                long long num_pages, int Hq, int Hkv, int D, float scale, int causal, int window,
+                                float softcap, const float* sinks, int* status, void* stream) {
+  using namespace edl;
+  if (B <= 0 || max_q <= 0 || total_q <= 0) return 0;
+  const int G = Hq / Hkv;
+  if ((D != 64 && D != 128) || Hq % Hkv || (G & (G - 1)) || G > 128) {
+    set_last_error("edl_attn_paged: unsupported head layout (D=%d, Hq=%d, Hkv=%d)", D, Hq, Hkv);
+    return -1;
+  }
+  if ((ldo & 7) || (reinterpret_cast<uintptr_t>(o) & 15)) {
+    set_last_error("edl_attn_paged: output must be 16-byte aligned with ldo %% 8 == 0");
+    return -1;
+  }
+  AttnFwdParams p;
+  p.o = reinterpret_cast<__nv_bfloat16*>(o);
+  p.ldo = ldo;
+  p.lse = nullptr;
+  p.cu_q = cu_q;
+  p.cu_k = nullptr;
+  p.sinks = sinks;
+  p.B = B;
+  p.Tq = max_q;
+  p.Tk = 0;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.total_q = (int)total_q;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.softcap = softcap;
+  p.causal = causal;
+  p.window = window;
+  p.status = status;
+  p.page_table = page_table;
+  p.kv_lens = kv_lens;
+  p.pt_stride = pt_stride;
+  p.pack = G;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long total_k = num_pages * 128;
+  if (D == 128) return launch_fwd<128>(q, k_pages, v_pages, ldq, ld_page, ld_page, total_q, total_k, p, s);
+  return launch_fwd<64>(q, k_pages, v_pages, ldq, ld_page, ld_page, total_q, total_k, p, s);
 }
