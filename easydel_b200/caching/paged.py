@@ -1,0 +1,96 @@
+"""Paged KV cache for the eSurge engine.
+
+Layout follows the reference's GPU cache (``UnifiedAttentionCache``: separate key and value page
+arrays ``[P, page, Hkv, D]``, easydel/caching/unified_attention/cache.py:465-466); the number of
+pages comes from free HBM x ``hbm_utilization`` like easydel/caching/ragged_page/cache.py:557-559.
+Page size is 128 tokens: one page is exactly one key tile of the paged attention kernel, so a
+tile is fetched with a single TMA load addressed through the page table.
+
+``PagedBatchMeta`` is the per-step device metadata (the reference's ``RaggedPagesMetadata``,
+ragged_page/cache.py:1157-1250): query start offsets, context lengths, page tables, slot mapping.
+"""
+
+from __future__ import annotations
+
+import typing as tp
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import serving as S
+
+PAGE_SIZE = S.PAGE_SIZE
+
+
+@dataclass
+class PagedBatchMeta:
+    cu_q: torch.Tensor           # int32 [B+1] offsets of each sequence's new tokens in the flat token axis
+    kv_lens: torch.Tensor        # int32 [B]   keys per sequence after this step's append
+    page_table: torch.Tensor     # int32 [B, maxP]
+    slot_mapping: torch.Tensor   # int32 [T]   flat page slot of every new token (-1 = padding)
+    max_q: int                   # largest number of new tokens of any sequence
+    num_seqs: int
+    last_token_index: torch.Tensor | None = None  # int32 [B] row of each sequence's last new token
+    request_distribution: tuple[int, int, int] | None = None  # (#decode, #decode+#prefill, #total)
+
+
+class PagedKVCache:
+    def __init__(self, num_layers: int, num_pages: int, num_kv_heads: int, head_dim: int, dtype=torch.bfloat16,
+                 device=None, page_size: int = PAGE_SIZE):
+        if page_size != PAGE_SIZE:
+            raise ValueError(f"the paged attention kernels use pages of {PAGE_SIZE} tokens, got {page_size}")
+        self.num_layers, self.num_pages, self.page_size = num_layers, num_pages, page_size
+        self.num_kv_heads, self.head_dim, self.dtype = num_kv_heads, head_dim, dtype
+        shape = (num_layers, num_pages, page_size, num_kv_heads, head_dim)
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+
+    @staticmethod
+    def bytes_per_page(num_layers: int, num_kv_heads: int, head_dim: int, dtype=torch.bfloat16,
+                       page_size: int = PAGE_SIZE) -> int:
+        return 2 * num_layers * page_size * num_kv_heads * head_dim * torch.empty(0, dtype=dtype).element_size()
+
+    @classmethod
+    def init_for_model(cls, model, num_pages: int | None = None, page_size: int = PAGE_SIZE,
+                       hbm_utilization: float = 0.85, max_model_length: int | None = None, dtype=None, device=None):
+        spec = model.spec
+        device = device or model.device
+        dtype = dtype or getattr(model.config, "kvdtype", None) or model.dtype
+        tp_size = getattr(model.config.mesh, "tp", 1)
+        kvh = max(1, spec.num_kv_heads // tp_size)
+        if num_pages is None:
+            per_page = cls.bytes_per_page(spec.num_layers, kvh, spec.head_dim, dtype, page_size)
+            if torch.device(device).type == "cuda":
+                free, total = torch.cuda.mem_get_info(device)
+                budget = max(0, int(free - (1.0 - hbm_utilization) * total))
+            else:
+                budget = 256 << 20
+            num_pages = max(2, budget // per_page)
+            if max_model_length is not None:
+                # never more than max_num_seqs * pages-per-sequence would need; the engine caps it further
+                pass
+        return cls(spec.num_layers, int(num_pages), kvh, spec.head_dim, dtype, device, page_size)
+
+    def view(self, layer: int) -> "PagedLayerView":
+        return PagedLayerView(self.k[layer], self.v[layer])
+
+    def seq_len(self) -> int:  # the engine passes explicit positions
+        return 0
+
+
+class PagedLayerView:
+    def __init__(self, k_pages: torch.Tensor, v_pages: torch.Tensor):
+        self.k_pages, self.v_pages = k_pages, v_pages
+
+    def attend(self, attn, q, k, v, positions=None, attn_meta: PagedBatchMeta | None = None):
+        """Appends this step's keys/values to their pages, then runs paged attention.
+
+        q ``[1, T, Hq, D]`` / k, v ``[1, T, Hkv, D]`` (all sequences flattened on the token axis)."""
+        meta = attn_meta
+        T = q.shape[1]
+        q3, k3, v3 = q[0], k[0], v[0]
+        S.kv_append(k3, v3, self.k_pages, self.v_pages, meta.slot_mapping)
+        o = S.paged_attention(q3, self.k_pages, self.v_pages, meta.cu_q, meta.kv_lens, meta.page_table, meta.max_q,
+                              scale=attn.scale, causal=True, window=attn.sliding_window or 0, softcap=attn.softcap,
+                              sinks=attn.sinks)
+        return o[None]

@@ -1,0 +1,168 @@
+"""Model runner: turns a ``SchedulerOutput`` into one device step and returns the sampled tokens.
+
+Role of ``eSurgeRunner`` / ``ExecutionManager`` / ``BatchMetadataPreparer`` in the reference
+(easydel/inference/esurge/runners/*): per step one packed host->device upload of the ragged-batch
+metadata, the backbone over the flattened tokens with the paged cache, the LM head on each
+sequence's last position only, the sampler, and one small device->host download of the tokens.
+Instead of ahead-of-time compiled buckets the step is eager kernel launches on persistent,
+fixed-size device buffers (so that decode steps can be replayed from CUDA graphs).
+"""
+
+from __future__ import annotations
+
+import time
+import typing as tp
+
+import numpy as np
+import torch
+
+from ...caching.paged import PAGE_SIZE, PagedBatchMeta, PagedKVCache
+from ...ops import functional as F
+from ...ops import serving as S
+from .scheduler import SchedulerOutput
+
+
+class ModelRunner:
+    def __init__(self, model, cache: PagedKVCache, max_num_seqs: int, max_num_batched_tokens: int,
+                 max_model_len: int):
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.max_num_seqs = max_num_seqs
+        self.max_tokens = max_num_batched_tokens
+        self.max_pages_per_seq = (max_model_len + PAGE_SIZE - 1) // PAGE_SIZE
+        self.vocab = model.spec.vocab_size
+        dev = self.device
+        pin = dev.type == "cuda"
+        B, T, MP = max_num_seqs, max_num_batched_tokens, self.max_pages_per_seq
+        # one packed int32 staging buffer: ids | pos | slots | cu_q | kv_lens | last_idx | page_table
+        self._sizes = [T, T, T, B + 1, B, B, B * MP]
+        total = sum(self._sizes)
+        self._host = torch.zeros(total, dtype=torch.int32, pin_memory=pin)
+        self._dev = torch.zeros(total, dtype=torch.int32, device=dev)
+        self._hviews = self._split(self._host)
+        self._dviews = self._split(self._dev)
+        # per-row sampling parameters (float and int blocks)
+        self._fhost = torch.zeros(6 * B, dtype=torch.float32, pin_memory=pin)
+        self._fdev = torch.zeros(6 * B, dtype=torch.float32, device=dev)
+        self._ihost = torch.zeros(3 * B, dtype=torch.int64, pin_memory=pin)
+        self._idev = torch.zeros(3 * B, dtype=torch.int64, device=dev)
+        self.counts: torch.Tensor | None = None
+        self.timings: dict[str, float] = {"prep": 0.0, "exec": 0.0, "sample": 0.0, "d2h": 0.0, "steps": 0}
+
+    def _split(self, buf: torch.Tensor) -> list[torch.Tensor]:
+        out, o = [], 0
+        for n in self._sizes:
+            out.append(buf[o:o + n])
+            o += n
+        return out
+
+    # ------------------------------------------------------------------
+    def _ensure_counts(self) -> torch.Tensor:
+        if self.counts is None:
+            self.counts = torch.zeros(self.max_num_seqs, self.vocab, dtype=torch.int32, device=self.device)
+        return self.counts
+
+    def reset_slot(self, slot: int, token_ids: tp.Sequence[int] | None = None) -> None:
+        """Clears (and re-seeds) the penalty counts of a slot when a request takes it."""
+        if self.counts is None:
+            return
+        self.counts[slot].zero_()
+        if token_ids:
+            t = torch.tensor(list(token_ids), dtype=torch.int64, device=self.device)
+            self.counts[slot].index_put_((t,), torch.ones_like(t, dtype=torch.int32), accumulate=True)
+
+    @torch.no_grad()
+    def execute(self, out: SchedulerOutput) -> dict[str, int]:
+        """Runs one engine step; returns ``{request_id: sampled token}`` for the requests that sampled."""
+        t0 = time.perf_counter()
+        sched = out.scheduled
+        B = len(sched)
+        T = out.total_tokens
+        if B == 0:
+            return {}
+        if B > self.max_num_seqs or T > self.max_tokens:
+            raise RuntimeError(f"batch of {B} sequences / {T} tokens exceeds the runner's buffers")
+        ids, pos, slots, cu_q, kv_lens, last_idx, table = self._hviews
+        MP = self.max_pages_per_seq
+        ids_np, pos_np, slots_np = ids.numpy(), pos.numpy(), slots.numpy()
+        table_np = table.numpy().reshape(self.max_num_seqs, MP)
+        cu_np, kv_np, last_np = cu_q.numpy(), kv_lens.numpy(), last_idx.numpy()
+        o = 0
+        max_q = 0
+        cu_np[0] = 0
+        any_pen = False
+        any_random = False
+        for b, s in enumerate(sched):
+            req = s.request
+            n, st = s.num_new_tokens, s.start
+            npt = req.num_prompt_tokens
+            if st + n <= npt:
+                toks = req.prompt_token_ids[st:st + n]
+            elif st >= npt:
+                toks = req.output_token_ids[st - npt:st - npt + n]
+            else:
+                toks = req.prompt_token_ids[st:] + req.output_token_ids[:st + n - npt]
+            ids_np[o:o + n] = toks
+            p = np.arange(st, st + n, dtype=np.int32)
+            pos_np[o:o + n] = p
+            pg = np.asarray(req.pages, dtype=np.int32)
+            slots_np[o:o + n] = pg[p // PAGE_SIZE] * PAGE_SIZE + p % PAGE_SIZE
+            table_np[b, :len(pg)] = pg
+            kv_np[b] = st + n
+            o += n
+            cu_np[b + 1] = o
+            last_np[b] = o - 1
+            max_q = max(max_q, n)
+            sp = req.sampling_params
+            any_pen |= sp.needs_penalties
+            any_random |= not sp.is_greedy
+        # one upload of the packed metadata
+        self._dev.copy_(self._host, non_blocking=True)
+        d_ids, d_pos, d_slots, d_cu, d_kv, d_last, d_table = self._dviews
+        meta = PagedBatchMeta(cu_q=d_cu[:B + 1], kv_lens=d_kv[:B], page_table=d_table.view(self.max_num_seqs, MP)[:B],
+                              slot_mapping=d_slots[:T], max_q=max_q, num_seqs=B, last_token_index=d_last[:B],
+                              request_distribution=(out.num_decode, B, B))
+        t1 = time.perf_counter()
+        model = self.model
+        res = model(input_ids=d_ids[:T][None].long(), position_ids=d_pos[:T][None], past_key_values=self.cache,
+                    cache_metadata=meta, apply_lm_head=False)
+        hidden = res.last_hidden_state[0]
+        rows = S.gather_rows(hidden, d_last[:B])
+        logits = model.apply_lm_head(rows)
+        t2 = time.perf_counter()
+        kw = {}
+        if any_random or any_pen:
+            fh, ih = self._fhost.view(6, -1), self._ihost.view(3, -1)
+            for b, s in enumerate(sched):
+                sp = s.request.sampling_params
+                fh[0, b] = 0.0 if sp.is_greedy else sp.temperature
+                fh[1, b], fh[2, b] = sp.top_p, sp.min_p
+                fh[3, b], fh[4, b], fh[5, b] = sp.presence_penalty, sp.frequency_penalty, sp.repetition_penalty
+                ih[0, b] = sp.top_k
+                ih[1, b] = sp.seed if sp.seed is not None else hash(s.request.request_id) & 0x7FFFFFFF
+                ih[2, b] = len(s.request.output_token_ids)
+            self._fdev.copy_(self._fhost, non_blocking=True)
+            self._idev.copy_(self._ihost, non_blocking=True)
+            fd, idv = self._fdev.view(6, -1), self._idev.view(3, -1)
+            kw = dict(temperature=fd[0, :B], top_p=fd[1, :B], min_p=fd[2, :B], top_k=idv[0, :B].to(torch.int32),
+                      seeds=idv[1, :B], steps=idv[2, :B].to(torch.int32))
+            if any_pen:
+                counts = self._ensure_counts()
+                slot_rows = torch.tensor([s.request.slot for s in sched], dtype=torch.int64, device=self.device)
+                kw.update(presence=fd[3, :B], frequency=fd[4, :B], repetition=fd[5, :B],
+                          counts=counts.index_select(0, slot_rows))
+        tokens, _ = S.sample(logits, **kw)
+        if any_pen:
+            S.count_update(self.counts, tokens, torch.tensor([s.request.slot for s in sched], dtype=torch.int32,
+                                                              device=self.device))
+        t3 = time.perf_counter()
+        host_tokens = tokens.cpu().tolist()  # the step's only device->host read
+        t4 = time.perf_counter()
+        tm = self.timings
+        tm["prep"] += t1 - t0
+        tm["exec"] += t2 - t1
+        tm["sample"] += t3 - t2
+        tm["d2h"] += t4 - t3
+        tm["steps"] += 1
+        return {s.request.request_id: host_tokens[b] for b, s in enumerate(sched) if s.samples}
