@@ -1,0 +1,116 @@
+// Small-message all-reduce over NVLink peer memory for tensor-parallel decode steps.
+//
+// One-shot algorithm: every rank has already written its partial result into its own slot of a
+// symmetric buffer (the row-parallel GEMM writes there directly). The kernel raises this rank's
+// flag in every peer's flag array, waits (bounded) until every peer's flag for this call has
+// arrived, then each rank sums all ranks' partials for the whole message and writes the result,
+// optionally fused with a residual add. Two buffer slots alternate between consecutive calls, so
+// a peer that is still reading call n never sees the writes of call n+1; the flag wait of call
+// n+1 proves every peer has finished call n before slot n is written again by call n+2.
+//
+// The reference leaves this all-reduce to XLA -> NCCL (implicit SPMD collectives, see
+// easydel/layers/linears/_linear.py:348-378); decode-time messages of [tokens, hidden] bf16 are
+// latency-bound, which is what the one-shot peer-load form is for.
+#include "common.cuh"
+
+namespace edl {
+namespace {
+
+constexpr int MAX_RANKS = 16;
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys(int* addr, int v) {
+  asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// data.p[r]: rank r's partial (n bf16 elements); flags.p[r]: rank r's flag array (int[MAX_RANKS]).
+__global__ void allreduce_oneshot_kernel(PeerPtrs data, PeerPtrs flags, int nranks, int rank, int epoch,
+                                         __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual,
+                                         long long n, long long spin_limit, int* status) {
+  __shared__ int s_ok;
+  if (blockIdx.x == 0 && threadIdx.x < nranks)
+    st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + rank, epoch);
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const int* mine = reinterpret_cast<const int*>(flags.p[rank]);
+    const long long t0 = clock64();
+    for (int r = 0; r < nranks && ok; ++r) {
+      while (ld_acquire_sys(mine + r) < epoch) {
+        if (clock64() - t0 > spin_limit) {
+          ok = 0;
+          if (status) atomicCAS(status, 0, EDL_TIMEOUT_PEER_FLAG);
+          break;
+        }
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const long long nvec = n / 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = 0; k < nranks; ++k) {
+      const int r = (rank + k) % nranks;
+      const uint4 v = reinterpret_cast<const uint4*>(data.p[r])[i];
+      float2 f;
+      f = unpack_bf16x2(v.x); acc[0] += f.x; acc[1] += f.y;
+      f = unpack_bf16x2(v.y); acc[2] += f.x; acc[3] += f.y;
+      f = unpack_bf16x2(v.z); acc[4] += f.x; acc[5] += f.y;
+      f = unpack_bf16x2(v.w); acc[6] += f.x; acc[7] += f.y;
+    }
+    if (residual) {
+      const uint4 v = reinterpret_cast<const uint4*>(residual)[i];
+      float2 f;
+      f = unpack_bf16x2(v.x); acc[0] += f.x; acc[1] += f.y;
+      f = unpack_bf16x2(v.y); acc[2] += f.x; acc[3] += f.y;
+      f = unpack_bf16x2(v.z); acc[4] += f.x; acc[5] += f.y;
+      f = unpack_bf16x2(v.w); acc[6] += f.x; acc[7] += f.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+}  // namespace
+}  // namespace edl
+
+using namespace edl;
+
+// data_ptrs[r] / flag_ptrs[r]: peer-mapped addresses of rank r's partial and flag array.
+// n: bf16 elements (multiple of 8). epoch: strictly increasing per call on this group.
+// wait_ms: how long to wait for peers before giving up with status EDL_TIMEOUT_PEER_FLAG.
+EDL_HOST_API int edl_allreduce_oneshot(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs,
+                                       int nranks, int rank, int epoch, void* out, const void* residual, long long n,
+                                       int wait_ms, int* status, void* stream) {
+  if (n <= 0) return 0;
+  if (nranks < 1 || nranks > MAX_RANKS || (n & 7)) {
+    set_last_error("edl_allreduce_oneshot: nranks=%d (max %d), n=%lld must be a multiple of 8", nranks, MAX_RANKS, n);
+    return -1;
+  }
+  PeerPtrs d, f;
+  for (int r = 0; r < nranks; ++r) {
+    d.p[r] = reinterpret_cast<void*>(data_ptrs[r]);
+    f.p[r] = reinterpret_cast<void*>(flag_ptrs[r]);
+  }
+  long long blocks = (n / 8 + 255) / 256;
+  long long cap = (long long)sm_count();
+  const long long spin = (long long)(wait_ms > 0 ? wait_ms : 2000) * 2000000LL;
+  allreduce_oneshot_kernel<<<(int)(blocks > cap ? cap : blocks), 256, 0, (cudaStream_t)stream>>>(
+      d, f, nranks, rank, epoch, (__nv_bfloat16*)out, (const __nv_bfloat16*)residual, n, spin, status);
+  return check_cuda(cudaGetLastError(), "allreduce_oneshot launch");
+}

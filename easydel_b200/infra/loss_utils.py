@@ -121,9 +121,7 @@ def causal_lm_loss_from_hidden(hidden: torch.Tensor, lm_head_weight: torch.Tenso
         hidden.reshape(-1, hidden.shape[-1]), lm_head_weight, labels.reshape(-1), bias=lm_head_bias,
         ignore_index=cfg.ignore_index, label_smoothing=cfg.label_smoothing, z_loss=cfg.z_loss, softcap=softcap,
         chunk_size=chunk_size or cfg.chunk_token_size or 2048, reduction_scale=red_scale,
-        want_accuracy=want_accuracy)
-    if red_scale is None and loss_scale != 1.0:
-        loss = loss * loss_scale
+        loss_scale=loss_scale, want_accuracy=want_accuracy)
     return LossMetrics(loss=loss, weight_sum=n_valid, accuracy=acc if want_accuracy else None)
 
 

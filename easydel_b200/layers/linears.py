@@ -95,6 +95,13 @@ class ParallelLinear(nn.Module):
 class ColumnParallelLinear(ParallelLinear):
     parallel_style = "column"
 
+    def forward(self, x: torch.Tensor, w: torch.Tensor | None = None) -> torch.Tensor:
+        if self.tp_size > 1:
+            from ..parallel import tp as tpar
+
+            x = tpar.copy_to_tp(x, self.tp_group)
+        return super().forward(x, w)
+
 
 class RowParallelLinear(ParallelLinear):
     parallel_style = "row"

@@ -211,7 +211,7 @@ class _LinearCEFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, h, w, labels, bias, ignore_index, label_smoothing, z_loss, softcap, chunk, reduction_scale,
-                want_acc, grad_enabled):
+                want_acc, grad_enabled, loss_scale):
         T, H = h.shape
         V = w.shape[0]
         dev = h.device
@@ -219,7 +219,7 @@ class _LinearCEFn(torch.autograd.Function):
         n_valid = valid.sum().to(torch.float32)
         # gscale tensor = 1/max(n_valid,1) * reduction_scale, consumed on-device by the CE kernel
         if reduction_scale is None:
-            gs = (1.0 / n_valid.clamp_min(1.0)).reshape(1)
+            gs = (float(loss_scale) / n_valid.clamp_min(1.0)).reshape(1)
         else:
             gs = torch.full((1,), float(reduction_scale), dtype=torch.float32, device=dev)
         need_grad = grad_enabled and (h.requires_grad or w.requires_grad)
@@ -266,17 +266,19 @@ class _LinearCEFn(torch.autograd.Function):
             gh = dh * dloss.to(dh.dtype)
         if dw is not None:
             gw = (dw * dloss).to(ctx.w_dtype)
-        return gh, gw, None, None, None, None, None, None, None, None, None, None
+        return gh, gw, None, None, None, None, None, None, None, None, None, None, None
 
 
 def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, *, bias=None,
                          ignore_index: int = -100, label_smoothing: float = 0.0, z_loss: float = 0.0,
                          softcap: float = 0.0, chunk_size: int = 2048, reduction_scale: float | None = None,
+                         loss_scale: float = 1.0,
                          want_accuracy: bool = False):
     """Mean (over non-ignored labels) cross-entropy of ``h @ w.T`` without materialising the logits.
 
     ``h`` is ``[T, H]``, ``labels`` ``[T]`` (already shifted by the caller). Returns
-    ``(loss, n_valid, accuracy)``. With ``reduction_scale`` the sum of token losses is
+    ``(loss, n_valid, accuracy)``. ``loss_scale`` multiplies the mean (gradient accumulation passes
+    ``1 / steps`` here so that it is part of the gradients produced inside the op). With ``reduction_scale`` the sum of token losses is
     multiplied by that constant instead of ``1 / n_valid``.
 
     On the GPU with ``w.main_grad`` present the LM-head weight gradient is accumulated
@@ -289,7 +291,7 @@ def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
         if not h2.is_contiguous():
             h2 = h2.contiguous()
         return _LinearCEFn.apply(h2, w, lab, bias, ignore_index, label_smoothing, z_loss, softcap, chunk_size,
-                                 reduction_scale, want_accuracy, torch.is_grad_enabled())
+                                 reduction_scale, want_accuracy, torch.is_grad_enabled(), loss_scale)
     total = h2.new_zeros((), dtype=torch.float32)
     correct = h2.new_zeros((), dtype=torch.float32)
     for s in range(0, h2.shape[0], chunk_size):
@@ -302,7 +304,7 @@ def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
             correct = correct + ((zc.argmax(-1) == lab[s:s + chunk_size]) & (lab[s:s + chunk_size] != ignore_index)
                                  ).sum()
     n_valid = (lab != ignore_index).sum().to(torch.float32)
-    scale = (1.0 / n_valid.clamp_min(1.0)) if reduction_scale is None else reduction_scale
+    scale = (loss_scale / n_valid.clamp_min(1.0)) if reduction_scale is None else reduction_scale
     return total * scale, n_valid, correct / n_valid.clamp_min(1.0)
 
 

@@ -69,8 +69,12 @@ class DistributedFlat:
 
             self.h_work = symm.rendezvous(flat.work, self.group)
             self.h_grad = symm.rendezvous(flat.grad, self.group)
-            self._work_ptrs = (C.c_ulonglong * self.world)(*[int(p) for p in self.h_work.buffer_ptrs])
-            self._grad_ptrs = (C.c_ulonglong * self.world)(*[int(p) for p in self.h_grad.buffer_ptrs])
+            # buffer_ptrs are the bases of the symmetric blocks; a tensor sits at `offset` inside its block
+            wo, go = int(getattr(self.h_work, "offset", 0)), int(getattr(self.h_grad, "offset", 0))
+            self._work_ptrs = (C.c_ulonglong * self.world)(*[int(p) + wo for p in self.h_work.buffer_ptrs])
+            self._grad_ptrs = (C.c_ulonglong * self.world)(*[int(p) + go for p in self.h_grad.buffer_ptrs])
+            if self._work_ptrs[self.rank] != flat.work.data_ptr() or self._grad_ptrs[self.rank] != flat.grad.data_ptr():
+                raise RuntimeError("symmetric-memory handle does not address this rank's own buffers")
 
     # ------------------------------------------------------------------
     def _barrier(self, channel: int = 0) -> None:

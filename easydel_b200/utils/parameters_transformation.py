@@ -274,3 +274,53 @@ class TensorConverter:
 
             return t.detach().cpu().view(torch.int16).numpy().view(ml_dtypes.bfloat16)
         return t.detach().cpu().numpy()
+
+
+def shard_internal_state_for_tp(model, full_state: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """Cuts a full (tensor-parallel size 1) internal state dict down to what this rank's model holds.
+
+    Column-parallel weights keep this rank's rows of every merged output (q / k / v, gate / up), row-parallel
+    weights keep this rank's input columns. When there are fewer KV heads than ranks, every rank keeps the
+    KV head its query heads belong to.
+    """
+    out = {}
+    mods = dict(model.named_modules())
+    for name, t in full_state.items():
+        mod_name, _, leaf = name.rpartition(".")
+        mod = mods.get(mod_name)
+        style = getattr(mod, "parallel_style", None)
+        tp_size = getattr(mod, "tp_size", 1)
+        if mod is None or tp_size == 1 or style not in ("column", "row"):
+            out[name] = t
+            continue
+        r = mod.tp_rank
+        if style == "row":
+            if leaf == "weight":
+                c = t.shape[1] // tp_size
+                out[name] = t[:, r * c:(r + 1) * c]
+            else:
+                out[name] = t
+            continue
+        local = mod.local_out_splits()
+        if len(local) == 1:
+            c = t.shape[0] // tp_size
+            out[name] = t[r * c:(r + 1) * c]
+            continue
+        # merged outputs: infer the full widths from the tensor (q is exact; k / v may be replicated)
+        total_local = sum(local)
+        q_full = local[0] * tp_size
+        rest = (t.shape[0] - q_full) // (len(local) - 1)
+        full_widths = [q_full] + [rest] * (len(local) - 1)
+        pieces, o = [], 0
+        for lw, fw in zip(local, full_widths):
+            chunk = t[o:o + fw]
+            if fw == lw * tp_size:
+                pieces.append(chunk[r * lw:(r + 1) * lw])
+            else:  # fewer KV heads than ranks: pick the head group this rank's queries use
+                n_groups = fw // lw
+                gi = r * n_groups // tp_size
+                pieces.append(chunk[gi * lw:(gi + 1) * lw])
+            o += fw
+        out[name] = torch.cat(pieces, dim=0)
+        assert out[name].shape[0] == total_local
+    return out

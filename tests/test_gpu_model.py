@@ -82,3 +82,30 @@ def test_packed_segments_isolate_documents():
         alone = gpu(input_ids=ids[:, 200:].cuda()).logits.float().cpu()
     assert (lr - lg).abs().max().item() < 0.125
     assert (lg[:, 200:] - alone).abs().max().item() < 0.06
+
+
+def test_micro_batch_accumulation_matches_full_batch():
+    """Gradients accumulated over two half-batches scaled by 1/2 equal the full-batch gradients (LM head included)."""
+    from easydel_b200.infra.base_state import EasyDeLState
+    from easydel_b200.optimizers import OptimizerFactory, SchedulerConfig
+
+    def grads(split):
+        _, gpu = _pair(_cfg())
+        gpu.train()
+        tx, _ = OptimizerFactory.create("adamw", SchedulerConfig(None, learning_rate=1e-3), weight_decay=0.0)
+        st = EasyDeLState.create(model=gpu, tx=tx, init_opt_state=True)
+        ids = torch.randint(0, 2048, (4, 128), generator=torch.Generator().manual_seed(5)).cuda()
+        if split:
+            for i in range(2):
+                _, m = gpu.compute_loss(input_ids=ids[2 * i:2 * i + 2], labels=ids[2 * i:2 * i + 2], loss_scale=0.5)
+                m.loss.backward()
+        else:
+            _, m = gpu.compute_loss(input_ids=ids, labels=ids)
+            m.loss.backward()
+        st.flat.fold_param_grads()
+        return {n: v.clone() for n, v in st.flat.named_views(st.flat.grad)}
+
+    a, b = grads(False), grads(True)
+    for n in a:
+        rel = ((a[n] - b[n]).norm() / (a[n].norm() + 1e-8)).item()
+        assert rel < 0.03, f"{n}: {rel}"

@@ -1,0 +1,155 @@
+"""Two-GPU tests (child processes over NCCL, NVLS disabled): peer-memory all-reduce, tensor-parallel forward,
+sharded optimizer step. Skipped when fewer than two GPUs are visible."""
+
+import os
+import socket
+import time
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, fn, world, port):
+    import datetime
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120),
+                            device_id=torch.device("cuda", rank))
+    try:
+        fn(rank, world)
+        torch.cuda.synchronize()
+        from easydel_b200.ops import _lib
+
+        _lib.check_status()
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(fn, world=2, timeout=300.0):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.spawn(_entry, args=(fn, world, _free_port()), nprocs=world, join=False)
+    deadline = time.time() + timeout
+    while not ctx.join(timeout=1.0):
+        if time.time() > deadline:
+            for p in ctx.processes:
+                if p.is_alive():
+                    p.terminate()
+            raise TimeoutError("multi-GPU test timed out")
+
+
+def _allreduce_worker(rank, world):
+    import torch.distributed as dist
+
+    from easydel_b200.parallel import tp
+
+    g = dist.group.WORLD
+    for step, n in enumerate([8192, 64 * 8192, 4096, 8 * 1024]):
+        x = (torch.randn(n, device="cuda", generator=torch.Generator(device="cuda").manual_seed(10 * step + rank))
+             ).to(torch.bfloat16)
+        ref = x.float().clone()
+        dist.all_reduce(ref, group=g)
+        with torch.no_grad():
+            y = tp.all_reduce(x, g)
+        assert torch.allclose(y.float(), ref, atol=3e-2, rtol=2e-2), (step, (y.float() - ref).abs().max())
+    assert tp._CTX, "the peer-memory path was not used"
+
+
+def _tp_forward_worker(rank, world):
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+    from easydel_b200.parallel.mesh import DeviceMesh
+    from easydel_b200.utils.parameters_transformation import shard_internal_state_for_tp
+
+    kw = dict(vocab_size=2048, hidden_size=512, intermediate_size=1408, num_hidden_layers=2, num_attention_heads=8,
+              num_key_value_heads=2, head_dim=64, max_position_embeddings=512)
+    full_cfg = LlamaConfig(**kw)
+    full_cfg.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), full_cfg.sharding_axis_names, 0, 1))
+    torch.manual_seed(0)
+    full = LlamaForCausalLM(full_cfg, dtype=torch.bfloat16, param_dtype=torch.bfloat16).cuda().eval()
+    cfg = LlamaConfig(sharding_axis_dims=(1, 1, 1, 2, 1), **kw)
+    model = LlamaForCausalLM(cfg, dtype=torch.bfloat16, param_dtype=torch.bfloat16).cuda().eval()
+    assert model.model.layers[0].self_attn.num_heads == 4
+    model.load_state_dict(shard_internal_state_for_tp(model, full.state_dict()))
+    ids = torch.randint(0, 2048, (2, 128), generator=torch.Generator().manual_seed(1)).cuda()
+    with torch.no_grad():
+        a = full(input_ids=ids).logits.float()
+        b = model(input_ids=ids).logits.float()
+    assert (a - b).abs().max().item() < 0.125, (a - b).abs().max()
+    # training path: gradients of a replicated parameter agree with the single-GPU model
+    model.train(), full.train()
+    _, m1 = full.compute_loss(input_ids=ids, labels=ids)
+    _, m2 = model.compute_loss(input_ids=ids, labels=ids)
+    assert abs(float(m1.loss) - float(m2.loss)) < 2e-2
+    m1.loss.backward()
+    m2.loss.backward()
+    g1 = full.model.norm.weight.grad.float()
+    g2 = model.model.norm.weight.grad.float()
+    assert ((g1 - g2).norm() / g1.norm()).item() < 0.05
+
+
+def _dist_optim_worker(rank, world):
+    from easydel_b200.infra.base_state import EasyDeLState
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+    from easydel_b200.optimizers import OptimizerFactory, SchedulerConfig
+    from easydel_b200.parallel.mesh import DeviceMesh
+
+    def mk(seed, single):
+        cfg = LlamaConfig(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                          num_attention_heads=4, num_key_value_heads=2, head_dim=64, max_position_embeddings=256)
+        if single:
+            cfg.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), cfg.sharding_axis_names, 0, 1))
+        torch.manual_seed(seed)
+        return LlamaForCausalLM(cfg, dtype=torch.bfloat16, param_dtype=torch.bfloat16).cuda().train()
+
+    def tx():
+        return OptimizerFactory.create("adamw", SchedulerConfig(None, learning_rate=1e-3), weight_decay=0.01,
+                                       clip_grad=1.0)[0]
+
+    model = mk(rank, False)
+    state = EasyDeLState.create(model=model, tx=tx(), init_opt_state=True)
+    assert state._dist is not None and state._dist.peer
+    data = torch.randint(0, 1024, (2 * world, 64), generator=torch.Generator().manual_seed(3)).cuda()
+    mine = data[2 * rank:2 * rank + 2]
+    for _ in range(2):
+        _, met = model.compute_loss(input_ids=mine, labels=mine)
+        met.loss.backward()
+        norm = state.apply_gradients()
+    ref = mk(0, True)
+    st2 = EasyDeLState.create(model=ref, tx=tx(), init_opt_state=True)
+    for _ in range(2):
+        for r in range(world):
+            mb = data[2 * r:2 * r + 2]
+            _, met = ref.compute_loss(input_ids=mb, labels=mb, loss_scale=1.0 / world)
+            met.loss.backward()
+        n2 = st2.apply_gradients()
+    torch.cuda.synchronize()
+    assert abs(float(norm) - float(n2)) / float(n2) < 2e-2
+    diff = (state.flat.work.float() - st2.flat.work.float()[: state.flat.numel]).abs().max().item()
+    assert diff < 1e-2, diff
+    assert state.flat.grad.abs().max().item() == 0
+
+
+def test_peer_allreduce_matches_nccl():
+    _run(_allreduce_worker)
+
+
+def test_tensor_parallel_forward_and_loss():
+    _run(_tp_forward_worker)
+
+
+def test_sharded_optimizer_peer_kernels():
+    _run(_dist_optim_worker)
