@@ -39,6 +39,27 @@ struct Cfg {
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
+// Grouped (mixture-of-experts) operation. mode 0: plain GEMM.
+// mode 1: the rows of A / C are segments of 128-row tiles, each owned by one expert; tile_expert[] names the
+//         owner, meta[0] is the number of row tiles (read on the device), B holds one matrix per expert stacked
+//         along its row dimension (b_rows_per_expert rows each).
+// mode 2: one GEMM per expert over that expert's slice [offsets[e], offsets[e+1]) of the reduction dimension
+//         (weight gradients); C holds one [M,N] matrix per expert, c_stride elements apart.
+struct GroupInfo {
+  int mode;
+  int num_experts;
+  const int* tile_expert;
+  const int* meta;
+  const int* offsets;
+  int b_rows_per_expert;
+  long long c_stride;
+};
+
+struct TileInfo {
+  int m0, n0, b_row_off, k0, nkb;
+  long long c_off;
+};
+
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   // Groups of 8 M-tiles share each N-tile consecutively so that the B tile and
   // a small set of A tiles stay in L2 while a wave of CTAs works on them.
@@ -52,11 +73,35 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tn = r / gm;
 }
 
+template <int BN>
+__device__ __forceinline__ TileInfo decode_tile(int tile, int tiles_m, int tiles_n, int num_kb, const GroupInfo& g) {
+  TileInfo t;
+  int tm, tn;
+  if (g.mode == 2) {
+    const int per = tiles_m * tiles_n;
+    const int e = tile / per;
+    tile_coords(tile - e * per, tiles_m, tiles_n, tm, tn);
+    t.k0 = g.offsets[e];
+    t.nkb = (g.offsets[e + 1] - t.k0) / BK;
+    t.b_row_off = 0;
+    t.c_off = (long long)e * g.c_stride;
+  } else {
+    tile_coords(tile, tiles_m, tiles_n, tm, tn);
+    t.k0 = 0;
+    t.nkb = num_kb;
+    t.c_off = 0;
+    t.b_row_off = g.mode == 1 ? g.tile_expert[tm] * g.b_rows_per_expert : 0;
+  }
+  t.m0 = tm * BM;
+  t.n0 = tn * BN;
+  return t;
+}
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  void* __restrict__ Cout, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc,
-                 int flags, int* status) {
+                 int flags, int* status, const GroupInfo grp) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -94,9 +139,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (grp.mode == 1) M = grp.meta[0] * BM;  // padded row count lives on the device
   const int tiles_m = (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int num_tiles = tiles_m * tiles_n * (grp.mode == 2 ? grp.num_experts : 1);
   const int num_kb = (K + BK - 1) / BK;
   const uint32_t smem_base = smem_u32(smem);
 
@@ -106,10 +152,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
-        const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const TileInfo ti = decode_tile<BN>(tile, tiles_m, tiles_n, num_kb, grp);
+        const int m0 = ti.m0, n0 = ti.n0;
+        for (int kb = 0; kb < ti.nkb; ++kb) {
+          const int kc = ti.k0 + kb * BK;
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, status, EDL_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
@@ -119,16 +165,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           const uint32_t a_dst = smem_base + stage * C::STAGE_BYTES;
           const uint32_t b_dst = a_dst + C::A_BYTES;
           if (!A_MN) {
-            tma_load_2d(a_dst, &tma_a, fb, kb * BK, m0);
+            tma_load_2d(a_dst, &tma_a, fb, kc, m0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tma_a, fb, m0 + j * 64, kb * BK);
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * 8192, &tma_a, fb, m0 + j * 64, kc);
           }
           if (!B_MN) {
-            tma_load_2d(b_dst, &tma_b, fb, kb * BK, n0);
+            tma_load_2d(b_dst, &tma_b, fb, kc, n0 + ti.b_row_off);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tma_b, fb, n0 + j * 64, kb * BK);
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * 8192, &tma_b, fb, n0 + j * 64, kc + ti.b_row_off);
           }
           if (++stage == C::STAGES) {
             stage = 0;
@@ -146,10 +193,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const TileInfo ti = decode_tile<BN>(tile, tiles_m, tiles_n, num_kb, grp);
+        if (ti.nkb == 0) continue;  // an expert without rows contributes nothing
         if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, status, EDL_TIMEOUT_MMA)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < ti.nkb; ++kb) {
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, status, EDL_TIMEOUT_MMA)) {
             ok = false;
             break;
@@ -184,9 +233,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const bool accum = flags & GEMM_ACCUMULATE;
     const bool has_bias = (flags & GEMM_BIAS) && bias != nullptr;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
-      const int m0 = tm * BM, n0 = tn * BN;
+      const TileInfo ti = decode_tile<BN>(tile, tiles_m, tiles_n, num_kb, grp);
+      if (ti.nkb == 0) continue;
+      const int m0 = ti.m0, n0 = ti.n0;
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, status, EDL_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
@@ -208,7 +257,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
           const bool full_chunk = (col0 + 32 <= N);
           if (out_f32) {
-            float* cp = reinterpret_cast<float*>(Cout) + (long long)row * ldc + col0;
+            float* cp = reinterpret_cast<float*>(Cout) + ti.c_off + (long long)row * ldc + col0;
             if (full_chunk) {
               if (accum) {
 #pragma unroll
@@ -227,7 +276,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               for (int j = 0; j < 32 && col0 + j < N; ++j) cp[j] = accum ? cp[j] + v[j] : v[j];
             }
           } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)row * ldc + col0;
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(Cout) + ti.c_off + (long long)row * ldc + col0;
             if (full_chunk) {
               if (accum) {
 #pragma unroll
@@ -278,21 +327,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
+// a_rows / b_rows: extents of the row (outer) dimension of the A / B tensors in memory, which for grouped
+// operation differ from the logical M / N / K of one product.
 template <int BN, bool A_MN, bool B_MN>
 int launch(const void* A, const void* B, void* Cout, const void* bias, int M, int N, int K, long long lda,
-           long long ldb, long long ldc, int flags, int* status, cudaStream_t stream, int max_ctas) {
+           long long ldb, long long ldc, int flags, int* status, cudaStream_t stream, int max_ctas,
+           const GroupInfo& grp = GroupInfo{0, 1, nullptr, nullptr, nullptr, 0, 0}, long long a_rows = -1,
+           long long b_rows = -1, int max_tiles = -1) {
   using C = Cfg<BN>;
   CUtensorMap ta, tb;
   int rc;
   if (!A_MN)
-    rc = make_tmap_2d_16b(&ta, A, M, K, lda, BM, BK);
+    rc = make_tmap_2d_16b(&ta, A, a_rows >= 0 ? a_rows : M, K, lda, BM, BK);
   else
-    rc = make_tmap_2d_16b(&ta, A, K, M, lda, BK, 64);
+    rc = make_tmap_2d_16b(&ta, A, a_rows >= 0 ? a_rows : K, M, lda, BK, 64);
   if (rc) return rc;
   if (!B_MN)
-    rc = make_tmap_2d_16b(&tb, B, N, K, ldb, BN, BK);
+    rc = make_tmap_2d_16b(&tb, B, b_rows >= 0 ? b_rows : N, K, ldb, BN, BK);
   else
-    rc = make_tmap_2d_16b(&tb, B, K, N, ldb, BK, 64);
+    rc = make_tmap_2d_16b(&tb, B, b_rows >= 0 ? b_rows : K, N, ldb, BK, 64);
   if (rc) return rc;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
@@ -302,12 +355,12 @@ int launch(const void* A, const void* B, void* Cout, const void* bias, int M, in
       return -1;
     attr_set = true;
   }
-  int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int tiles = max_tiles >= 0 ? max_tiles : ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   if (tiles < ctas) ctas = tiles;
   kern<<<ctas, GEMM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, Cout, reinterpret_cast<const __nv_bfloat16*>(bias), M,
-                                                       N, K, ldc, flags, status);
+                                                       N, K, ldc, flags, status, grp);
   return check_cuda(cudaGetLastError(), "gemm launch");
 }
 
@@ -353,4 +406,43 @@ EDL_HOST_API int edl_gemm_bf16(const void* A, const void* B, void* C, const void
     EDL_GEMM_CASE(256, true, true);
   }
 #undef EDL_GEMM_CASE
+}
+
+// Expert (grouped) GEMMs over rows bucketed by edl_moe_route (segments padded to 128 rows).
+//   kind 0  forward:       Y[rows, N]  = X[rows, K] * W[e]^T        W: [E, N, K]
+//   kind 1  data gradient: dX[rows, K] = dY[rows, N] * W[e]         W: [E, N, K]   (pass N = width of dY, K = width of dX)
+//   kind 2  weight gradient: dW[e][N, K] (+)= dY_e^T X_e  over the rows of expert e; fp32 output, flags & 2 accumulates
+// tile_expert / meta / offsets come from edl_moe_route; max_rows is the capacity (multiple of 128) of the row buffers.
+EDL_HOST_API int edl_gemm_grouped(int kind, const void* X, const void* W, void* Y, const void* dYw, int max_rows, int N,
+                                  int K, int E, const int* tile_expert, const int* meta, const int* offsets,
+                                  int flags, int* status, void* stream) {
+  using namespace edl;
+  if (max_rows <= 0 || N <= 0 || K <= 0 || E <= 0) return 0;
+  if ((N & 7) || (K & 7) || (max_rows % 128)) {
+    set_last_error("edl_gemm_grouped: N, K must be multiples of 8 and max_rows a multiple of 128");
+    return -1;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (kind == 0) {
+    GroupInfo g{1, E, tile_expert, meta, nullptr, N, 0};
+    const int tiles = (max_rows / 128) * ((N + 255) / 256);
+    return launch<256, false, false>(X, W, Y, nullptr, max_rows, N, K, K, K, N, flags, status, s, 0, g, max_rows,
+                                     (long long)E * N, tiles);
+  }
+  if (kind == 1) {
+    // A = dY [rows, N] K-major over N; B = W viewed as [E*N (reduction rows), K] MN-major; output dX [rows, K]
+    GroupInfo g{1, E, tile_expert, meta, nullptr, N, 0};
+    const int tiles = (max_rows / 128) * ((K + 255) / 256);
+    return launch<256, false, true>(X, W, Y, nullptr, max_rows, K, N, N, K, K, flags, status, s, 0, g, max_rows,
+                                    (long long)E * N, tiles);
+  }
+  if (kind == 2) {
+    // per expert: dW[e] [N, K] = dY_e^T [N, rows_e] * X_e [rows_e, K]; both operands MN-major over the row buffers
+    GroupInfo g{2, E, nullptr, nullptr, offsets, 0, (long long)N * K};
+    const int tiles = E * ((N + 127) / 128) * ((K + 255) / 256);
+    return launch<256, true, true>(dYw, X, Y, nullptr, N, K, max_rows, N, K, K, flags | GEMM_OUT_F32, status, s, 0, g,
+                                   max_rows, max_rows, tiles);
+  }
+  set_last_error("edl_gemm_grouped: unknown kind %d", kind);
+  return -1;
 }
