@@ -37,6 +37,21 @@ def alibi_slopes(n_heads: int) -> torch.Tensor:
     return torch.tensor(pow2(c) + pow2(2 * c)[0::2][: n_heads - c], dtype=torch.float32)
 
 
+class _PerHeadLayerNorm(nn.Module):
+    """Bias-free LayerNorm over the last axis with a separate scale vector per head."""
+
+    def __init__(self, heads: int, head_dim: int, eps: float, dtype, tp_size: int = 1, tp_rank: int = 0):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(heads, head_dim, dtype=dtype))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:   # [..., heads, head_dim]
+        xf = x.float()
+        mean = xf.mean(-1, keepdim=True)
+        var = (xf - mean).pow(2).mean(-1, keepdim=True)
+        return ((xf - mean) * torch.rsqrt(var + self.eps) * self.weight.float()).to(x.dtype)
+
+
 class Attention(nn.Module):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, *, layer_idx: int = 0,
                  bias: bool = False, o_bias: bool = False, qk_norm: str | None = None, qk_norm_eps: float = 1e-6,
@@ -79,6 +94,10 @@ class Attention(nn.Module):
         elif qk_norm == "layer_head":  # per-head LayerNorm without bias (Cohere, StableLM per-head)
             self.q_norm = LayerNorm(head_dim, qk_norm_eps, bias=False, dtype=dtype)
             self.k_norm = LayerNorm(head_dim, qk_norm_eps, bias=False, dtype=dtype)
+        elif qk_norm == "layer_perhead":  # LayerNorm over head_dim with one scale row per head (Cohere)
+            self.q_norm = _PerHeadLayerNorm(self.num_heads, head_dim, qk_norm_eps, dtype, tp_size, tp_rank)
+            self.k_norm = _PerHeadLayerNorm(self.num_kv_heads, head_dim, qk_norm_eps, dtype,
+                                            1 if self.kv_replicated else tp_size, tp_rank)
         self.rotary = None
         if rope is not None:
             self.rotary = get_rope(head_size=head_dim, **rope)
@@ -102,7 +121,7 @@ class Attention(nn.Module):
         B, T, W = qkv.shape
         Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         q, k, v = qkv[..., : Hq * D], qkv[..., Hq * D:(Hq + Hkv) * D], qkv[..., (Hq + Hkv) * D:]
-        if self.qk_norm in ("rms_head", "layer_head"):
+        if self.qk_norm in ("rms_head", "layer_head", "layer_perhead"):
             q = self.q_norm(q.reshape(B, T, Hq, D)).reshape(B, T, Hq * D)
             k = self.k_norm(k.reshape(B, T, Hkv, D)).reshape(B, T, Hkv * D)
         else:

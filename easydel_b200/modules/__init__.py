@@ -2,3 +2,5 @@
 
 from . import llama  # noqa: F401
 from .llama import *  # noqa: F401,F403
+from . import families  # noqa: F401
+from .families import *  # noqa: F401,F403

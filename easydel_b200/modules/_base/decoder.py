@@ -102,6 +102,9 @@ class ArchSpec:
 def _norm(spec: ArchSpec, dtype) -> nn.Module:
     if spec.norm == "rms":
         return RMSNorm(spec.hidden_size, spec.norm_eps, dtype, offset=spec.norm_offset)
+    if spec.norm == "layer_noparam":
+        return LayerNorm(spec.hidden_size, spec.norm_eps if spec.norm_eps > 1e-6 else 1e-5, dtype=dtype,
+                         elementwise_affine=False)
     return LayerNorm(spec.hidden_size, spec.norm_eps, bias=spec.norm_bias, dtype=dtype)
 
 
@@ -160,7 +163,8 @@ class DecoderLayer(nn.Module):
             self.post_feedforward_layernorm = _norm(spec, dtype)
         else:
             self.input_layernorm = _norm(spec, dtype)
-            if spec.residual == "pre" or not spec.shared_parallel_norm:
+            if (spec.residual == "pre" and not spec.sandwich_norm) or \
+                    (spec.residual == "parallel" and not spec.shared_parallel_norm):
                 self.post_attention_layernorm = _norm(spec, dtype)
             if spec.sandwich_norm:
                 self.post_attn_out_layernorm = _norm(spec, dtype)

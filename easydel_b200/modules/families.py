@@ -1,0 +1,264 @@
+"""Decoder-only text families defined through the spec table (see ``_base/families.py``).
+
+Each block cites the reference directory it covers (easydel/modules/<family>/). Config defaults
+follow the Hugging Face configs of the same ``model_type`` so that ``config.json`` files load
+unchanged.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ._base.decoder import ArchSpec, MoESpec
+from ._base.families import base_spec, define_family, moe_spec, rope_args
+
+_LLAMA_DEFAULTS = dict(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+                       num_attention_heads=32, num_key_value_heads=None, head_dim=None, hidden_act="silu",
+                       max_position_embeddings=4096, initializer_range=0.02, rms_norm_eps=1e-6, use_cache=True,
+                       rope_theta=10000.0, rope_scaling=None, attention_bias=False, attention_dropout=0.0,
+                       mlp_bias=False, tie_word_embeddings=False)
+EXPORTS: dict[str, type] = {}
+
+
+def _d(**kw):
+    d = dict(_LLAMA_DEFAULTS)
+    d.update(kw)
+    return d
+
+
+def _layer_types(c, n):
+    lt = getattr(c, "layer_types", None)
+    if lt:
+        return tuple("sliding" if "sliding" in t else "full" for t in lt)
+    return None
+
+
+# ---- mistral (easydel/modules/mistral) ------------------------------------------------------
+EXPORTS.update(define_family("mistral", _d(sliding_window=4096, rms_norm_eps=1e-6, max_position_embeddings=32768),
+                             lambda c: base_spec(c, sliding_window=getattr(c, "sliding_window", None))))
+
+# ---- qwen2 (easydel/modules/qwen2): biased q/k/v ----------------------------------------------
+EXPORTS.update(define_family(
+    "qwen2", _d(vocab_size=151936, intermediate_size=22016, max_position_embeddings=32768, use_sliding_window=False,
+                sliding_window=4096, max_window_layers=28, layer_types=None),
+    lambda c: base_spec(c, attn_bias=True, o_bias=False,
+                        sliding_window=c.sliding_window if getattr(c, "use_sliding_window", False) else None)))
+
+# ---- qwen3 (easydel/modules/qwen3): per-head QK RMSNorm ---------------------------------------
+EXPORTS.update(define_family(
+    "qwen3", _d(vocab_size=151936, intermediate_size=22016, head_dim=128, max_position_embeddings=32768,
+                use_sliding_window=False, sliding_window=None, layer_types=None),
+    lambda c: base_spec(c, qk_norm="rms_head")))
+
+# ---- seed_oss / smollm3 / granite -----------------------------------------------------------
+EXPORTS.update(define_family("seed_oss", _d(attention_bias=True, attention_out_bias=False, head_dim=128),
+                             lambda c: base_spec(c, attn_bias=c.attention_bias,
+                                                 o_bias=getattr(c, "attention_out_bias", False))))
+
+
+def _smollm3_spec(c):
+    n = c.num_hidden_layers
+    nope = getattr(c, "no_rope_layers", None)
+    if nope is None:
+        interval = getattr(c, "no_rope_layer_interval", 4)
+        nope = [int((i + 1) % interval != 0) for i in range(n)]
+    lt = tuple("full" if nope[i] else "nope" for i in range(n))
+    return base_spec(c, layer_types=lt)
+
+
+EXPORTS.update(define_family("smollm3", _d(no_rope_layers=None, no_rope_layer_interval=4, use_sliding_window=False,
+                                           sliding_window=None, layer_types=None), _smollm3_spec,
+                             class_prefix="SmolLM3"))
+EXPORTS.update(define_family(
+    "granite", _d(embedding_multiplier=1.0, logits_scaling=1.0, residual_multiplier=1.0, attention_multiplier=1.0),
+    lambda c: base_spec(c, embedding_multiplier=c.embedding_multiplier, residual_multiplier=c.residual_multiplier,
+                        attn_scale=c.attention_multiplier, logit_scale=1.0 / c.logits_scaling)))
+
+# ---- gemma family (easydel/modules/gemma, gemma2, gemma3) --------------------------------------
+_GEMMA = _d(vocab_size=256000, hidden_size=3072, intermediate_size=24576, num_hidden_layers=28,
+            num_attention_heads=16, num_key_value_heads=16, head_dim=256, hidden_act="gelu_pytorch_tanh",
+            hidden_activation="gelu_pytorch_tanh", max_position_embeddings=8192, tie_word_embeddings=True)
+
+
+def _gemma_act(c):
+    return getattr(c, "hidden_activation", None) or "gelu_pytorch_tanh"
+
+
+EXPORTS.update(define_family(
+    "gemma", _GEMMA,
+    lambda c: base_spec(c, norm_offset=1.0, act=_gemma_act(c), embed_scale=math.sqrt(c.hidden_size),
+                        tie_embeddings=True)))
+
+
+def _gemma2_spec(c):
+    n = c.num_hidden_layers
+    lt = _layer_types(c, n) or tuple("sliding" if i % 2 == 0 else "full" for i in range(n))
+    return base_spec(c, norm_offset=1.0, act=_gemma_act(c), embed_scale=math.sqrt(c.hidden_size), tie_embeddings=True,
+                     sandwich_norm=True, attn_softcap=c.attn_logit_softcapping or 0.0,
+                     logit_softcap=c.final_logit_softcapping or 0.0, attn_scale=c.query_pre_attn_scalar ** -0.5,
+                     sliding_window=c.sliding_window, layer_types=lt)
+
+
+EXPORTS.update(define_family(
+    "gemma2", dict(_GEMMA, hidden_size=2304, intermediate_size=9216, num_hidden_layers=26, num_attention_heads=8,
+                   num_key_value_heads=4, query_pre_attn_scalar=256, sliding_window=4096, layer_types=None,
+                   final_logit_softcapping=30.0, attn_logit_softcapping=50.0), _gemma2_spec,
+    rules=[("post_attention_layernorm", "post_attn_out_layernorm")]))
+
+
+def _gemma3_spec(c):
+    n = c.num_hidden_layers
+    pat = getattr(c, "sliding_window_pattern", 6) or 6
+    lt = _layer_types(c, n) or tuple("full" if (i + 1) % pat == 0 else "sliding" for i in range(n))
+    hd = c.head_dim
+    glob = rope_args(c, hd)
+    local = dict(glob, base=getattr(c, "rope_local_base_freq", 10000.0), rope_scaling=None)
+    return base_spec(c, norm_offset=1.0, act=_gemma_act(c), embed_scale=math.sqrt(c.hidden_size), tie_embeddings=True,
+                     sandwich_norm=True, qk_norm="rms_head", attn_scale=c.query_pre_attn_scalar ** -0.5,
+                     sliding_window=c.sliding_window, layer_types=lt, rope=glob, rope_local=local,
+                     attn_softcap=getattr(c, "attn_logit_softcapping", None) or 0.0,
+                     logit_softcap=getattr(c, "final_logit_softcapping", None) or 0.0)
+
+
+EXPORTS.update(define_family(
+    "gemma3_text", dict(_GEMMA, vocab_size=262208, hidden_size=2304, intermediate_size=9216, num_hidden_layers=26,
+                        num_attention_heads=8, num_key_value_heads=4, query_pre_attn_scalar=256, sliding_window=4096,
+                        layer_types=None, rope_theta=1000000.0, rope_local_base_freq=10000.0,
+                        sliding_window_pattern=6, max_position_embeddings=131072, final_logit_softcapping=None,
+                        attn_logit_softcapping=None), _gemma3_spec, class_prefix="Gemma3Text",
+    rules=[("post_attention_layernorm", "post_attn_out_layernorm")]))
+
+# ---- phi3 (easydel/modules/phi3): checkpoints already hold fused qkv / gate_up -----------------
+EXPORTS.update(define_family(
+    "phi3", _d(vocab_size=32064, hidden_size=3072, intermediate_size=8192, rms_norm_eps=1e-5, sliding_window=None,
+               original_max_position_embeddings=4096, partial_rotary_factor=1.0, pad_token_id=32000),
+    lambda c: base_spec(c, sliding_window=getattr(c, "sliding_window", None),
+                        rope=rope_args(c, c.hidden_size // c.num_attention_heads,
+                                       partial=getattr(c, "partial_rotary_factor", 1.0))),
+    hf_keeps_fused=("qkv_proj", "gate_up_proj")))
+
+# ---- olmo / olmo2 / olmo3 (easydel/modules/olmo*) ----------------------------------------------
+EXPORTS.update(define_family(
+    "olmo", _d(vocab_size=50304, clip_qkv=None, max_position_embeddings=2048),
+    lambda c: base_spec(c, norm="layer_noparam", clip_qkv=c.clip_qkv)))
+EXPORTS.update(define_family(
+    "olmo2", _d(vocab_size=50304, rms_norm_eps=1e-5, max_position_embeddings=2048),
+    lambda c: base_spec(c, residual="post", qk_norm="rms_full")))
+
+
+def _olmo3_spec(c):
+    n = c.num_hidden_layers
+    lt = _layer_types(c, n) or tuple("sliding" if (i + 1) % 4 else "full" for i in range(n))
+    return base_spec(c, residual="post", qk_norm="rms_full", sliding_window=getattr(c, "sliding_window", None),
+                     layer_types=lt)
+
+
+EXPORTS.update(define_family("olmo3", _d(vocab_size=50304, rms_norm_eps=1e-5, sliding_window=4096, layer_types=None),
+                             _olmo3_spec))
+
+# ---- cohere (easydel/modules/cohere): parallel block, LayerNorm without bias, interleaved RoPE ---
+EXPORTS.update(define_family(
+    "cohere", _d(vocab_size=256000, hidden_size=8192, intermediate_size=22528, num_hidden_layers=40,
+                 num_attention_heads=64, logit_scale=0.0625, layer_norm_eps=1e-5, use_qk_norm=False,
+                 max_position_embeddings=8192, tie_word_embeddings=True),
+    lambda c: base_spec(c, norm="layer", norm_bias=False, norm_eps=c.layer_norm_eps, residual="parallel",
+                        shared_parallel_norm=True, logit_scale=c.logit_scale, tie_embeddings=True,
+                        qk_norm="layer_perhead" if c.use_qk_norm else None,
+                        rope=rope_args(c, c.hidden_size // c.num_attention_heads, neox=False)),
+    layernorm_names=["input_layernorm", "norm"]))
+
+# ---- stablelm (easydel/modules/stablelm): LayerNorm, partial rotary -------------------------------
+EXPORTS.update(define_family(
+    "stablelm", _d(vocab_size=50304, hidden_size=2560, intermediate_size=6912, layer_norm_eps=1e-5,
+                   partial_rotary_factor=0.25, use_qkv_bias=False, qk_layernorm=False, use_parallel_residual=False),
+    lambda c: base_spec(c, norm="layer", norm_eps=c.layer_norm_eps, attn_bias=c.use_qkv_bias, o_bias=False,
+                        rope=rope_args(c, c.hidden_size // c.num_attention_heads, partial=c.partial_rotary_factor)),
+    layernorm_names=["input_layernorm", "post_attention_layernorm", "norm"]))
+
+# ---- starcoder2: LayerNorm + bias, plain GELU MLP ---------------------------------------------------
+EXPORTS.update(define_family(
+    "starcoder2", _d(vocab_size=49152, hidden_size=3072, intermediate_size=12288, num_hidden_layers=30,
+                     num_attention_heads=24, num_key_value_heads=2, hidden_act="gelu_pytorch_tanh", norm_epsilon=1e-5,
+                     use_bias=True, sliding_window=None, tie_word_embeddings=True),
+    lambda c: base_spec(c, norm="layer", norm_eps=c.norm_epsilon, mlp="plain", mlp_bias=c.use_bias,
+                        attn_bias=c.use_bias, o_bias=c.use_bias, sliding_window=c.sliding_window),
+    rules=[("mlp.c_fc", "mlp.fc1"), ("mlp.c_proj", "mlp.fc2")],
+    layernorm_names=["input_layernorm", "post_attention_layernorm", "norm"]))
+
+# ---- glm / glm4 (easydel/modules/glm, glm4): half rotary, interleaved; fused gate_up in checkpoints --
+_GLM = _d(vocab_size=151552, hidden_size=4096, intermediate_size=13696, num_hidden_layers=40, num_attention_heads=32,
+          num_key_value_heads=2, head_dim=128, partial_rotary_factor=0.5, rms_norm_eps=1.5625e-07,
+          attention_bias=True, max_position_embeddings=131072)
+EXPORTS.update(define_family(
+    "glm", _GLM, lambda c: base_spec(c, attn_bias=c.attention_bias, o_bias=False,
+                                     rope=rope_args(c, c.head_dim, partial=c.partial_rotary_factor, neox=False)),
+    hf_keeps_fused=("gate_up_proj",)))
+EXPORTS.update(define_family(
+    "glm4", _GLM, lambda c: base_spec(c, attn_bias=c.attention_bias, o_bias=False, sandwich_norm=True,
+                                      rope=rope_args(c, c.head_dim, partial=c.partial_rotary_factor, neox=False)),
+    hf_keeps_fused=("gate_up_proj",),
+    rules=[("post_self_attn_layernorm", "post_attn_out_layernorm"),
+           ("post_attention_layernorm", "pre_feedforward_layernorm"),
+           ("post_mlp_layernorm", "post_feedforward_layernorm")]))
+
+
+# ---- MoE families --------------------------------------------------------------------------------
+def _mixtral_spec(c):
+    return base_spec(c, sliding_window=getattr(c, "sliding_window", None),
+                     moe=moe_spec(c, num_experts=c.num_local_experts, top_k=c.num_experts_per_tok,
+                                  intermediate=c.intermediate_size, norm_topk=True,
+                                  aux_coef=getattr(c, "router_aux_loss_coef", 0.0)))
+
+
+EXPORTS.update(define_family(
+    "mixtral", _d(intermediate_size=14336, num_key_value_heads=8, num_local_experts=8, num_experts_per_tok=2,
+                  sliding_window=None, router_aux_loss_coef=0.001, output_router_logits=False,
+                  max_position_embeddings=131072, rms_norm_eps=1e-5, rope_theta=1e6),
+    _mixtral_spec,
+    rules=[("block_sparse_moe", "mlp"), (".w1.", ".gate_proj."), (".w3.", ".up_proj."), (".w2.", ".down_proj.")]))
+
+
+def _qwen_moe_layers(c):
+    n = c.num_hidden_layers
+    only = set(getattr(c, "mlp_only_layers", None) or [])
+    step = getattr(c, "decoder_sparse_step", 1) or 1
+    return tuple(i for i in range(n) if i not in only and (i + 1) % step == 0)
+
+
+def _qwen3_moe_spec(c):
+    return base_spec(c, qk_norm="rms_head",
+                     moe=moe_spec(c, num_experts=c.num_experts, top_k=c.num_experts_per_tok,
+                                  intermediate=c.moe_intermediate_size, norm_topk=c.norm_topk_prob,
+                                  layers=_qwen_moe_layers(c), aux_coef=c.router_aux_loss_coef))
+
+
+EXPORTS.update(define_family(
+    "qwen3_moe", _d(vocab_size=151936, hidden_size=2048, intermediate_size=6144, num_hidden_layers=24,
+                    num_attention_heads=32, num_key_value_heads=4, head_dim=128, max_position_embeddings=32768,
+                    decoder_sparse_step=1, moe_intermediate_size=768, num_experts_per_tok=8, num_experts=128,
+                    norm_topk_prob=False, output_router_logits=False, router_aux_loss_coef=0.001,
+                    mlp_only_layers=None, use_sliding_window=False, sliding_window=None),
+    _qwen3_moe_spec, class_prefix="Qwen3Moe"))
+
+
+def _qwen2_moe_spec(c):
+    return base_spec(c, attn_bias=True, o_bias=False,
+                     moe=moe_spec(c, num_experts=c.num_experts, top_k=c.num_experts_per_tok,
+                                  intermediate=c.moe_intermediate_size, norm_topk=c.norm_topk_prob,
+                                  shared=c.shared_expert_intermediate_size, shared_gate=True,
+                                  layers=_qwen_moe_layers(c), aux_coef=c.router_aux_loss_coef))
+
+
+EXPORTS.update(define_family(
+    "qwen2_moe", _d(vocab_size=151936, hidden_size=2048, intermediate_size=5632, num_hidden_layers=24,
+                    num_attention_heads=16, num_key_value_heads=16, max_position_embeddings=32768,
+                    decoder_sparse_step=1, moe_intermediate_size=1408, shared_expert_intermediate_size=5632,
+                    num_experts_per_tok=4, num_experts=60, norm_topk_prob=False, output_router_logits=False,
+                    router_aux_loss_coef=0.001, mlp_only_layers=None, use_sliding_window=False, sliding_window=4096),
+    _qwen2_moe_spec, class_prefix="Qwen2Moe",
+    rules=[("mlp.shared_expert.", "mlp.shared_experts."), ("mlp.shared_expert_gate.", "mlp.shared_expert_gate.")]))
+
+globals().update(EXPORTS)
+__all__ = sorted(EXPORTS)

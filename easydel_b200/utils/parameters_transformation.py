@@ -43,7 +43,7 @@ def internal_to_hf(model, state: dict[str, torch.Tensor] | None = None) -> dict[
         leaf, mod_name = parts[-1], parts[-2] if len(parts) > 1 else ""
         prefix = ".".join(parts[:-2])
         pre = prefix + "." if prefix else ""
-        if mod_name in FUSED_SPLITS and t.dim() <= 2:
+        if mod_name in FUSED_SPLITS and t.dim() <= 2 and mod_name not in getattr(model, "hf_keeps_fused", ()):
             mod = _module_of(model, ".".join(parts[:-1]))
             widths = mod.local_out_splits()
             for sub, chunk in zip(FUSED_SPLITS[mod_name], torch.split(t, list(widths), dim=0)):
@@ -102,7 +102,11 @@ def hf_to_internal(model, hf_state: dict[str, torch.Tensor], strict: bool = True
                 # HF checkpoints with already-fused expert tensors [E, in, 2F] / [E, F, out]
                 fused_key = f"{pre}experts.{mod_name}"
                 if fused_key in hf_state:
-                    out[name] = hf_state[fused_key].transpose(1, 2)
+                    t = hf_state[fused_key]
+                    transposed = getattr(model, "hf_fused_experts_transposed", None)
+                    if transposed is None:
+                        transposed = tuple(t.shape) != tuple(ref.shape)
+                    out[name] = t.transpose(1, 2) if transposed else t
                 else:
                     missing.append(name)
         else:
@@ -215,6 +219,44 @@ def _layernorm_names(model) -> tuple[str, ...]:
         return ()
 
 
+_EXPERT_ALIASES = (("gate_proj", "up_proj", "down_proj"), ("w1", "w3", "w2"))
+
+
+def _adapt_to_hf_module_names(sd: dict[str, torch.Tensor], expected: dict[str, torch.Tensor]):
+    """Checkpoint-format names -> the in-memory names of the installed ``transformers`` version.
+
+    Recent ``transformers`` keeps MoE experts as stacked ``experts.gate_up_proj`` / ``experts.down_proj``
+    tensors (and renames Mixtral's ``block_sparse_moe`` to ``mlp``) while checkpoints on disk keep the
+    per-expert modules; ``from_pretrained`` converts on load, ``load_state_dict`` does not.
+    """
+    out = dict(sd)
+    for key, ref in expected.items():
+        if key in out:
+            continue
+        alt = key.replace(".mlp.", ".block_sparse_moe.")
+        if alt in out:
+            out[key] = out.pop(alt)
+            continue
+        if not (key.endswith("experts.gate_up_proj") or key.endswith("experts.down_proj")):
+            continue
+        base = key.rsplit(".", 1)[0]
+        for prefix in (base, base.replace(".mlp.", ".block_sparse_moe.")):
+            for g, u, d in _EXPERT_ALIASES:
+                if f"{prefix}.0.{d}.weight" not in out:
+                    continue
+                E = ref.shape[0]
+                if key.endswith("gate_up_proj"):
+                    t = torch.stack([torch.cat([out.pop(f"{prefix}.{e}.{g}.weight"),
+                                                out.pop(f"{prefix}.{e}.{u}.weight")], 0) for e in range(E)])
+                else:
+                    t = torch.stack([out.pop(f"{prefix}.{e}.{d}.weight") for e in range(E)])
+                out[key] = t if tuple(t.shape) == tuple(ref.shape) else t.transpose(1, 2).contiguous()
+                break
+            if key in out:
+                break
+    return out
+
+
 class StateDictConverter:
     """Reference-named facade (easydel/utils/parameters_transformation.py:117-700)."""
 
@@ -234,12 +276,19 @@ class ModelConverter:
         import transformers
 
         hf_cfg_cls = transformers.CONFIG_MAPPING[model.config.model_type]
+        hf_defaults = hf_cfg_cls().to_dict()
+        own_keys = set(getattr(model.config, "hf_config_keys", ())) | {"rope_scaling", "head_dim", "rope_theta"}
         cfg_dict = {k: v for k, v in model.config.to_dict().items()
-                    if k in hf_cfg_cls().to_dict() or k in ("rope_scaling", "head_dim")}
+                    if (k in hf_defaults or k in own_keys) and not (v is None and k not in hf_defaults)}
+        spec = getattr(model, "spec", None)
+        if "layer_types" in hf_defaults and spec is not None and spec.layer_types is not None:
+            cfg_dict["layer_types"] = ["sliding_attention" if t == "sliding" else "full_attention"
+                                       for t in spec.layer_types]
         hf_cfg = hf_cfg_cls(**cfg_dict)
         auto = base_hf_auto_class or transformers.AutoModelForCausalLM
         hf_model = auto.from_config(hf_cfg).to(dtype)
         sd = {k: v.detach().to("cpu", dtype) for k, v in internal_to_hf(model).items()}
+        sd = _adapt_to_hf_module_names(sd, hf_model.state_dict())
         missing, unexpected = hf_model.load_state_dict(sd, strict=False)
         bad = [m for m in missing if "rotary" not in m and "inv_freq" not in m and not
                (m == "lm_head.weight" and getattr(hf_cfg, "tie_word_embeddings", False))]
