@@ -4,3 +4,5 @@ from . import llama  # noqa: F401
 from .llama import *  # noqa: F401,F403
 from . import families  # noqa: F401
 from .families import *  # noqa: F401,F403
+from . import families_classic  # noqa: F401
+from .families_classic import *  # noqa: F401,F403

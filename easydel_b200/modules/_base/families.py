@@ -15,6 +15,7 @@ here the shared structure lives in ``decoder.py`` and a family is a page of decl
 
 from __future__ import annotations
 
+import re
 import typing as tp
 
 import torch
@@ -26,7 +27,8 @@ from .decoder import ArchSpec, DecoderForCausalLM, DecoderForSequenceClassificat
 _HF_KEYS = ("pad_token_id", "bos_token_id", "eos_token_id", "tie_word_embeddings")
 
 
-def make_config(model_type: str, defaults: dict, post: tp.Callable | None = None, name: str | None = None):
+def make_config(model_type: str, defaults: dict, post: tp.Callable | None = None, name: str | None = None,
+                attribute_map: dict | None = None):
     defaults = dict(defaults)
 
     class _Config(EasyDeLBaseConfig):
@@ -45,6 +47,8 @@ def make_config(model_type: str, defaults: dict, post: tp.Callable | None = None
             super().__init__(**kw)
 
     _Config.model_type = model_type
+    if attribute_map:
+        _Config.attribute_map = dict(attribute_map)
     _Config.hf_config_keys = tuple(defaults)
     _Config.__name__ = _Config.__qualname__ = name or (model_type.title().replace("_", "") + "Config")
     return register_config(model_type)(_Config)
@@ -82,29 +86,37 @@ def base_spec(c, **over) -> ArchSpec:
 
 
 class _Renamer:
-    """Bidirectional key substitutions: ``rules`` is a list of (hf_fragment, internal_fragment)."""
+    """Bidirectional key substitutions: ``rules`` is a list of (hf_fragment, internal_fragment), or a
+    function of the model returning one.
 
-    def __init__(self, rules: tp.Sequence[tuple[str, str]], tensor_in=None, tensor_out=None):
-        self.rules, self.tensor_in, self.tensor_out = list(rules), tensor_in, tensor_out
+    A key is rewritten in one left-to-right pass; where several fragments match at the same position the
+    one listed first wins, and replaced text is never rescanned, so a specific rule placed before a general
+    one (``model.decoder.final_layer_norm.`` before ``model.decoder.``) behaves the same in both directions.
+    """
+
+    def __init__(self, rules, tensor_in=None, tensor_out=None):
+        self.rules, self.tensor_in, self.tensor_out = rules, tensor_in, tensor_out
+
+    def _table(self, model, inverse: bool):
+        rules = self.rules(model) if callable(self.rules) else self.rules
+        pairs = [(b, a) if inverse else (a, b) for a, b in rules]
+        if not pairs:
+            return None, {}
+        return re.compile("|".join(re.escape(a) for a, _ in pairs)), dict(pairs)
+
+    @staticmethod
+    def _apply(sd, pattern, table):
+        if pattern is None:
+            return dict(sd)
+        return {pattern.sub(lambda m: table[m.group(0)], k): v for k, v in sd.items()}
 
     def to_internal(self, model, sd: dict) -> dict:
         if self.tensor_in is not None:
             sd = self.tensor_in(model, sd)
-        out = {}
-        for k, v in sd.items():
-            for a, b in self.rules:
-                if a in k:
-                    k = k.replace(a, b)
-            out[k] = v
-        return out
+        return self._apply(sd, *self._table(model, False))
 
     def to_hf(self, model, sd: dict) -> dict:
-        out = {}
-        for k, v in sd.items():
-            for a, b in reversed(self.rules):
-                if b in k:
-                    k = k.replace(b, a)
-            out[k] = v
+        out = self._apply(sd, *self._table(model, True))
         if self.tensor_out is not None:
             out = self.tensor_out(model, out)
         return out
@@ -113,9 +125,10 @@ class _Renamer:
 def define_family(model_type: str, defaults: dict, spec_fn: tp.Callable[[tp.Any], ArchSpec], *,
                   class_prefix: str | None = None, rules: tp.Sequence[tuple[str, str]] = (), tensor_in=None,
                   tensor_out=None, config_post=None, hf_keeps_fused: tuple[str, ...] = (),
-                  layernorm_names: list[str] | None = None, with_classifier: bool = True):
+                  layernorm_names: list[str] | None = None, with_classifier: bool = True,
+                  attribute_map: dict | None = None):
     prefix = class_prefix or model_type.title().replace("_", "")
-    cfg = make_config(model_type, defaults, config_post, prefix + "Config")
+    cfg = make_config(model_type, defaults, config_post, prefix + "Config", attribute_map)
     ren = _Renamer(rules, tensor_in, tensor_out) if (rules or tensor_in or tensor_out) else None
 
     def hooks(ns: dict) -> dict:

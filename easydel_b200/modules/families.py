@@ -258,7 +258,7 @@ EXPORTS.update(define_family(
                     num_experts_per_tok=4, num_experts=60, norm_topk_prob=False, output_router_logits=False,
                     router_aux_loss_coef=0.001, mlp_only_layers=None, use_sliding_window=False, sliding_window=4096),
     _qwen2_moe_spec, class_prefix="Qwen2Moe",
-    rules=[("mlp.shared_expert.", "mlp.shared_experts."), ("mlp.shared_expert_gate.", "mlp.shared_expert_gate.")]))
+    rules=[("mlp.shared_expert.", "mlp.shared_experts.")]))
 
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

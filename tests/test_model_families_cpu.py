@@ -35,6 +35,21 @@ CASES = {
     "glm4": dict(head_dim=16, pad_token_id=0),
     "mixtral": dict(num_local_experts=4, num_experts_per_tok=2),
     "qwen3_moe": dict(head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True),
+    "gpt2": dict(_replace=dict(vocab_size=512, n_embd=128, n_layer=3, n_head=8, n_positions=256)),
+    "gpt_neox": dict(_replace=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=3,
+                                   num_attention_heads=8, max_position_embeddings=256, rotary_pct=0.5)),
+    "gptj": dict(_replace=dict(vocab_size=512, n_embd=128, n_layer=3, n_head=8, n_positions=256, rotary_dim=8)),
+    "opt": dict(_replace=dict(vocab_size=512, hidden_size=128, ffn_dim=256, num_hidden_layers=3,
+                              num_attention_heads=8, max_position_embeddings=256)),
+    "phi": dict(),
+    "falcon": dict(_replace=dict(vocab_size=512, hidden_size=128, num_hidden_layers=3, num_attention_heads=8,
+                                 max_position_embeddings=256)),
+    "falcon-new": dict(_replace=dict(vocab_size=512, hidden_size=128, num_hidden_layers=3, num_attention_heads=8,
+                                     num_kv_heads=2, new_decoder_architecture=True, max_position_embeddings=256,
+                                     bias=True), _type="falcon"),
+    "falcon-mha": dict(_replace=dict(vocab_size=512, hidden_size=128, num_hidden_layers=3, num_attention_heads=8,
+                                     multi_query=False, parallel_attn=False, max_position_embeddings=256),
+                       _type="falcon"),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                       shared_expert_intermediate_size=96),
 }
@@ -43,8 +58,11 @@ CASES = {
 def _build(model_type, extra):
     from easydel_b200.infra.factory import TaskType, registry
 
+    extra = dict(extra)
+    model_type = extra.pop("_type", model_type)
+    base = extra.pop("_replace", None)
     cfg_cls = registry.get_config(model_type)
-    cfg = cfg_cls(**{**_COMMON, **extra})
+    cfg = cfg_cls(**({**_COMMON, **extra} if base is None else base))
     reg = registry.get_module_registration(TaskType.CAUSAL_LM, model_type)
     torch.manual_seed(0)
     model = reg.module(cfg, dtype=torch.float32, param_dtype=torch.float32)
