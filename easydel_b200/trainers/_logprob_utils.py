@@ -1,0 +1,74 @@
+"""Token / sequence log-probabilities without materialising ``[tokens, vocab]`` logits.
+
+The preference and RL trainers need ``log pi(y_t | y_<t)`` for given tokens, sometimes with the
+policy entropy. The reference computes them from chunked logits (easydel/trainers/_logprob_utils.py and
+direct_preference_optimization_trainer/_fn.py:63); here the backbone runs once, and the LM head is folded
+into the fused head+log-prob kernel (``ops.functional.linear_token_logprob``), chunked over tokens.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..ops import functional as F
+
+
+def _head(model):
+    w = model.lm_head_weight() if hasattr(model, "lm_head_weight") else None
+    b = model.lm_head_bias() if hasattr(model, "lm_head_bias") else None
+    return w, b
+
+
+def token_logprobs(model, input_ids: torch.Tensor, attention_mask: torch.Tensor | None = None,
+                   loss_mask: torch.Tensor | None = None, *, temperature: float = 1.0, want_entropy: bool = False,
+                   chunk_size: int = 2048, **model_kwargs):
+    """Returns ``(logps [B, T-1], mask [B, T-1] float, entropy or None, model_output)``.
+
+    ``logps[b, t]`` is the log-probability of ``input_ids[b, t+1]``; positions outside ``loss_mask`` (which is
+    aligned with ``input_ids``) or outside ``attention_mask`` are zero.
+    """
+    mask = torch.ones_like(input_ids, dtype=torch.bool) if loss_mask is None else loss_mask.bool()
+    if attention_mask is not None:
+        mask = mask & attention_mask.bool()
+    mask = mask[:, 1:]
+    labels = input_ids[:, 1:].masked_fill(~mask, -100)
+    w, b = _head(model)
+    spec = getattr(model, "spec", None)
+    direct = w is not None and not (spec is not None and spec.logit_softcap)
+    if direct:
+        out = model(input_ids=input_ids, attention_mask=attention_mask, apply_lm_head=False, **model_kwargs)
+        h = out.last_hidden_state[:, :-1]
+        if spec is not None and spec.logit_scale is not None:
+            h = h * spec.logit_scale
+        lp, ent = F.linear_token_logprob(h, w, labels, bias=b, temperature=temperature, chunk_size=chunk_size,
+                                         want_entropy=want_entropy)
+    else:
+        out = model(input_ids=input_ids, attention_mask=attention_mask, **model_kwargs)
+        logits = out.logits[:, :-1].float() / temperature
+        lsm = torch.log_softmax(logits, -1)
+        lp = lsm.gather(-1, labels.clamp_min(0)[..., None])[..., 0]
+        ent = -(lsm.exp() * lsm).sum(-1) if want_entropy else None
+    m = mask.to(lp.dtype)
+    lp = lp * m
+    if ent is not None:
+        ent = ent * m
+    return lp, m, ent, out
+
+
+def sequence_logprobs(model, input_ids, attention_mask=None, loss_mask=None, *, average: bool = False, **kw):
+    """Sum (or mean) of the token log-probabilities over ``loss_mask``: ``[B]``."""
+    lp, m, _, out = token_logprobs(model, input_ids, attention_mask, loss_mask, **kw)
+    s = lp.sum(-1)
+    if average:
+        s = s / m.sum(-1).clamp_min(1.0)
+    return s, m.sum(-1), out
+
+
+def masked_mean(x: torch.Tensor, mask: torch.Tensor, dim=None) -> torch.Tensor:
+    if dim is None:
+        return (x * mask).sum() / mask.sum().clamp_min(1.0)
+    return (x * mask).sum(dim) / mask.sum(dim).clamp_min(1.0)
+
+
+def selective_log_softmax(logits: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    return torch.log_softmax(logits.float(), -1).gather(-1, index[..., None])[..., 0]
