@@ -31,16 +31,28 @@ def _register_lazy(names: dict[str, str]) -> None:
     _LAZY.update(names)
 
 
+# Packages searched (in order) for public names that are not listed above: every model family, trainer,
+# serving class and data helper is reachable as ``easydel_b200.<Name>`` like in the reference's flat namespace.
+_SEARCH = ("modules", "trainers", "inference", "data", "optimizers", "layers", "caching", "parallel", "utils", "elarge")
+
+
 def __getattr__(name: str) -> _tp.Any:
+    if name.startswith("__"):
+        raise AttributeError(name)
     if name in _LAZY:
         return getattr(_importlib.import_module(_LAZY[name]), name)
     try:
-        from . import _exports
-
-        if name in _exports.LAZY:
-            return getattr(_importlib.import_module(_exports.LAZY[name]), name)
-    except ImportError:
-        pass
+        return _importlib.import_module(f"{__name__}.{name}")
+    except ModuleNotFoundError as e:
+        if e.name != f"{__name__}.{name}":
+            raise
+    for pkg in _SEARCH:
+        try:
+            mod = _importlib.import_module(f"{__name__}.{pkg}")
+        except ModuleNotFoundError:
+            continue
+        if name in getattr(mod, "__dict__", {}):
+            return mod.__dict__[name]
     raise AttributeError(f"module 'easydel_b200' has no attribute {name!r}")
 
 

@@ -6,6 +6,24 @@ from .training_configurations import (TrainingArguments, get_trainer_arguments_c
                                       register_trainer, register_trainer_arguments)
 
 register_trainer("base")(Trainer)
+register_trainer("trainer")(Trainer)
 
-__all__ = ["BaseTrainer", "Trainer", "TrainerOutput", "TrainingArguments", "LogWatcher", "StepMetrics",
-           "find_latest_checkpoint", "get_trainer_class", "get_trainer_arguments_class"]
+from .sft import SFTConfig, SFTTrainer  # noqa: E402
+from .preference import (BCOConfig, BCOTrainer, CPOConfig, CPOTrainer, DPOConfig, DPODataCollator,  # noqa: E402
+                         DPOTrainer, KTOConfig, KTOTrainer, ORPOConfig, ORPOTrainer, RewardConfig, RewardTrainer,
+                         dpo_loss)
+from .rl import (GFPOConfig, GFPOTrainer, GRPOConfig, GRPOTrainer, GSPOConfig, GSPOTrainer, RLVRConfig,  # noqa: E402
+                 RLVRTrainer, SDPOConfig, SDPOTrainer, MathVerifier, FormatVerifier, LengthPenaltyVerifier,
+                 CodeExecutionVerifier)
+from .rl_online import (NashMDConfig, NashMDTrainer, PPOConfig, PPOTrainer, XPOConfig, XPOTrainer)  # noqa: E402
+from .distillation import (DistillationConfig, DistillationTrainer, GKDConfig, GKDTrainer,  # noqa: E402
+                           OnPolicyDistillationConfig, OnPolicyDistillationTrainer, SeqKDConfig, SeqKDTrainer,
+                           SparseDistillationConfig, SparseDistillationTrainer)
+from .embedding import EmbeddingConfig, EmbeddingTrainer  # noqa: E402
+from .agentic import (AgenticMoshPitConfig, AgenticMoshPitTrainer, EnvironmentManager, TextEnvironment,  # noqa: E402
+                      ToolEnvironment)
+from .ray_dist import RayDistributedConfig, RayDistributedTrainer  # noqa: E402
+
+register_trainer("ray_dist")(RayDistributedTrainer)
+
+__all__ = [n for n in dir() if not n.startswith("_")]
