@@ -248,6 +248,39 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   return __bfloat1622float2(v);
 }
 
+// Epilogue helper: a warp holds a 32-row block one row per lane, each row 128 bytes as eight 16-byte chunks
+// (64 bf16 or 32 fp32 values). Writing it straight out would make every store instruction touch 32 different rows
+// with 16 bytes each; instead the block goes through a swizzled 4 KB shared-memory stage and leaves as four whole
+// 128-byte row segments per instruction. `gbase` points at (first row, first column) of the block in global
+// memory, `ld_bytes` is the row pitch, rows >= valid_rows and 16-byte chunks >= valid_chunks are skipped.
+// ACC_F32 adds the staged fp32 values to what is in memory (gradient accumulation).
+template <bool ACC_F32>
+__device__ __forceinline__ void store_rows_coalesced(uint8_t* stage, const uint4 (&pk)[8], uint8_t* gbase,
+                                                     long long ld_bytes, int valid_rows, int valid_chunks, int lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = pk[j];
+  __syncwarp();
+  const int ch = lane & 7;
+  const bool col_ok = ch < valid_chunks;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    uint4 v = *reinterpret_cast<const uint4*>(stage + r * 128 + ((ch ^ (r & 7)) << 4));
+    if (col_ok && r < valid_rows) {
+      uint4* g = reinterpret_cast<uint4*>(gbase + r * ld_bytes + ch * 16);
+      if (ACC_F32) {
+        const uint4 o = *g;
+        v.x = __float_as_uint(__uint_as_float(v.x) + __uint_as_float(o.x));
+        v.y = __float_as_uint(__uint_as_float(v.y) + __uint_as_float(o.y));
+        v.z = __float_as_uint(__uint_as_float(v.z) + __uint_as_float(o.z));
+        v.w = __float_as_uint(__uint_as_float(v.w) + __uint_as_float(o.w));
+      }
+      *g = v;
+    }
+  }
+  __syncwarp();
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

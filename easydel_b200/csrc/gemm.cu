@@ -13,6 +13,7 @@
 // This is the replacement for the reference's einsum -> XLA -> cuBLASLt path
 // (easydel/layers/linears/_linear.py:245-322).
 #include "common.cuh"
+#include "tmem_ops.cuh"
 
 namespace edl {
 
@@ -35,7 +36,8 @@ struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int EPI_BYTES = 4 * 4096;  // one 32-row x 128-byte stage per epilogue warp
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES + 1024;
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -112,6 +114,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const uint32_t tempty0 = tfull0 + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES + C::BAR_BYTES;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -240,6 +243,66 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      uint8_t* my_stage = epi_stage + q * 4096;
+      const int valid_rows = M - (m0 + q * 32);  // may be <= 0 or > 32
+      if (!out_f32 && !accum) {
+        // bf16 output: 64 columns per step, staged so that stores cover whole 128-byte row segments
+        __nv_bfloat16* gbase = reinterpret_cast<__nv_bfloat16*>(Cout) + ti.c_off + (long long)(m0 + q * 32) * ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t r[64];
+          tmem_ld_32x32b_x64(t_row + c * 64, r);
+          tc_wait_ld();
+          const int col0 = n0 + c * 64;
+          if (col0 < N && valid_rows > 0) {
+            uint4 pk[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float v[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j * 8 + e]);
+              if (has_bias) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  if (col0 + j * 8 + e < N) v[e] += __bfloat162float(bias[col0 + j * 8 + e]);
+              }
+              pk[j] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                 pack_bf16x2(v[6], v[7]));
+            }
+            store_rows_coalesced<false>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ldc * 2, valid_rows,
+                                        min(8, (N - col0) >> 3), lane);
+          }
+        }
+      } else if (out_f32 && (N & 3) == 0) {
+        // fp32 output (weight gradients, optionally accumulated in place): 32 columns = 128 bytes per row per step
+        float* gbase = reinterpret_cast<float*>(Cout) + ti.c_off + (long long)(m0 + q * 32) * ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, r);
+          tc_wait_ld();
+          const int col0 = n0 + c * 32;
+          if (col0 < N && valid_rows > 0) {
+            uint4 pk[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (has_bias) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  if (col0 + j * 4 + e < N)
+                    r[j * 4 + e] = __float_as_uint(__uint_as_float(r[j * 4 + e]) + __bfloat162float(bias[col0 + j * 4 + e]));
+              }
+              pk[j] = make_uint4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
+            }
+            if (accum)
+              store_rows_coalesced<true>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ldc * 4, valid_rows,
+                                         min(8, (N - col0) >> 2), lane);
+            else
+              store_rows_coalesced<false>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ldc * 4, valid_rows,
+                                          min(8, (N - col0) >> 2), lane);
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -306,6 +369,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             }
           }
         }
+      }
       }
       tc_fence_before();
       __syncwarp();

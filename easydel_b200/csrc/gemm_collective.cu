@@ -8,15 +8,20 @@
 //       sums the staged partials of its own row shard: out[M/n, N] = sum_r partial_r (+ residual).
 //
 //   edl_allgather_gemm : A is sharded by rows across ranks (sequence parallel activations or FSDP weight rows);
-//       C[n*Ms, N] = gather(A) * W^T. A few copier CTAs pull the peers' shards into a local gathered buffer with
-//       bulk asynchronous copies (peer global -> shared -> local global, several hundred KB in flight per CTA) and
-//       publish one counter per 128-row chunk; the GEMM CTAs start on the local shard and reach each remote chunk
-//       after it has landed, reading it from local memory so every byte crosses NVLink once.
+//       C[n*Ms, N] = gather(A) * W^T. One extra warp in every CTA pulls its share of the peers' shards into a local
+//       gathered buffer with bulk asynchronous copies (peer global -> shared -> local global; remote reads are
+//       latency bound per SM, so the copy is spread over all SMs) and publishes one counter per 128-row chunk; the
+//       GEMM warps start on the local shard and reach each remote chunk after it has landed, reading it from local
+//       memory so every byte crosses NVLink once.
+//
+// Output tiles leave through a swizzled shared-memory stage so that each store instruction writes whole 128-byte
+// row segments: peer stores of 16 bytes per row (one row per lane) reached a small fraction of the link rate.
 //
 // All waits (pipeline barriers, chunk counters, peer flags) are bounded and report through the status word.
 // No load in this file uses a cluster-wide broadcast; peers are reached with plain stores, plain loads and
 // CTA-local bulk copies only.
 #include "common.cuh"
+#include "tmem_ops.cuh"
 
 namespace edl {
 namespace {
@@ -24,17 +29,17 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warp 6 all-gather copier
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+constexpr int EPI_BYTES = 4 * 4096;               // per epilogue warp: 32 rows x 128 bytes
+constexpr int PIECE = 8192;                       // bytes per bulk copy
+constexpr int COPY_SLOTS = 2;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + EPI_BYTES + COPY_SLOTS * PIECE + 1024;
 constexpr int TMEM_COLS = 2 * BN;
 constexpr int MAX_RANKS = 8;
-constexpr int PIECE = 32768;                      // bytes per bulk copy
-constexpr int COPY_SLOTS = (STAGES * STAGE_BYTES) / PIECE;  // 6
-constexpr int COPY_AHEAD = COPY_SLOTS - 2;
 
 enum { MODE_RS = 1, MODE_AG = 2 };
 enum { CF_BIAS = 1, CF_RESIDUAL = 2, CF_COPY_OWN = 4 };
@@ -42,7 +47,6 @@ enum { CF_BIAS = 1, CF_RESIDUAL = 2, CF_COPY_OWN = 4 };
 struct CollInfo {
   int mode, nranks, rank, epoch;
   int tiles_per_shard;   // 128-row tiles in one rank's row shard
-  int n_copy;            // AG: copier CTAs (lowest block indices)
   int flags;
   long long spin_limit;  // clock cycles a wait on a peer may take
   void* peer[MAX_RANKS];  // RS: staging base on every rank (this call's slot). AG: A shard base on every rank
@@ -125,11 +129,12 @@ __device__ __forceinline__ Tile decode(int t, int tiles_n, const CollInfo& ci) {
   Tile o;
   const int tps = ci.tiles_per_shard;
   if (ci.mode == MODE_RS) {
-    const int per_shard = tps * tiles_n;
-    const int si = t / per_shard;
+    // Destinations alternate tile by tile, so the peer stores are spread over the whole kernel instead of being
+    // bunched into its first part, and neighbouring tiles share the same B tile.
+    const int si = t % ci.nranks;
     int tm, tn;
-    group_coords(t - si * per_shard, tps, tiles_n, tm, tn);
-    o.dst = (ci.rank + 1 + si) % ci.nranks;  // own shard last
+    group_coords(t / ci.nranks, tps, tiles_n, tm, tn);
+    o.dst = (ci.rank + 1 + si) % ci.nranks;
     o.a_row = (o.dst * tps + tm) * BM;
     o.n0 = tn * BN;
     o.out_row = (long long)(ci.rank * tps + tm) * BM;
@@ -163,20 +168,22 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-  const uint32_t full0 = smem_u32(bars);          // GEMM: STAGES barriers; copier: COPY_SLOTS barriers
-  const uint32_t empty0 = full0 + 8 * 8;
-  const uint32_t tfull0 = empty0 + 8 * 8;
+  const uint32_t full0 = smem_u32(bars);
+  const uint32_t empty0 = full0 + 8 * STAGES;
+  const uint32_t tfull0 = empty0 + 8 * STAGES;
   const uint32_t tempty0 = tfull0 + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  const uint32_t cfull0 = tempty0 + 16;  // copier slots
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + COPY_SLOTS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_stage = smem + STAGES * STAGE_BYTES + 256;
+  uint8_t* copy_stage = epi_stage + EPI_BYTES;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const bool copier = ci.mode == MODE_AG && (int)blockIdx.x < ci.n_copy;
   const uint32_t smem_base = smem_u32(smem);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 8; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
@@ -184,13 +191,14 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     mbar_init(tfull0 + 8, 1);
     mbar_init(tempty0, 4);
     mbar_init(tempty0 + 8, 4);
+    for (int s = 0; s < COPY_SLOTS; ++s) mbar_init(cfull0 + 8 * s, 1);
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tma_a);
     prefetch_tmap(&tma_g);
     prefetch_tmap(&tma_b);
   }
-  if (!copier && warp == 1) {
+  if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
   }
@@ -198,18 +206,24 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   __syncthreads();
   tc_fence_after();
 
-  if (copier) {
-    // ---- all-gather copier: one thread drives a ring of bulk copies -------------------------------------
-    if (threadIdx.x == 0) {
+  const uint32_t tmem_base = *tmem_slot;
+  const int cta = blockIdx.x;
+  const int ncta = gridDim.x;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = ci.nranks * ci.tiles_per_shard * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  const int ppc = (BM * K * 2) / PIECE;  // pieces per 128-row chunk
+
+  if (warp == 6) {
+    // ---- all-gather copier: every CTA moves its share of the peers' rows while its other warps multiply -------
+    if (ci.mode == MODE_AG && lane == 0) {
       const int tps = ci.tiles_per_shard;
-      const int ppc = (BM * K * 2) / PIECE;  // pieces per 128-row chunk
       const int shards = ci.nranks - 1 + ((ci.flags & CF_COPY_OWN) ? 1 : 0);
       const long long total = (long long)shards * tps * ppc;
-      const int c = blockIdx.x;
-      const int my_n = total > c ? (int)((total - c + ci.n_copy - 1) / ci.n_copy) : 0;
+      const int my_n = total > cta ? (int)((total - cta + ncta - 1) / ncta) : 0;
       const long long chunk_bytes = (long long)BM * K * 2;
       auto locate = [&](int j, const uint8_t*& src, uint8_t*& dst, int& chunk) {
-        const long long L = c + (long long)j * ci.n_copy;
+        const long long L = cta + (long long)j * ncta;
         const int si = (int)(L / ((long long)tps * ppc));
         const int rem = (int)(L - (long long)si * tps * ppc);
         const int lt = rem / ppc, p = rem - lt * ppc;
@@ -218,14 +232,15 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         chunk = r * tps + lt;
         dst = reinterpret_cast<uint8_t*>(ci.gathered) + chunk * chunk_bytes + (long long)p * PIECE;
       };
+      const uint32_t cbase = smem_u32(copy_stage);
       auto issue_load = [&](int j) {
         const uint8_t* src;
         uint8_t* dst;
         int chunk;
         locate(j, src, dst, chunk);
         const int slot = j % COPY_SLOTS;
-        mbar_expect_tx(full0 + 8 * slot, PIECE);
-        bulk_g2s(smem_base + slot * PIECE, src, PIECE, full0 + 8 * slot);
+        mbar_expect_tx(cfull0 + 8 * slot, PIECE);
+        bulk_g2s(cbase + slot * PIECE, src, PIECE, cfull0 + 8 * slot);
       };
       auto signal = [&](int j) {
         const uint8_t* src;
@@ -236,12 +251,17 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         __threadfence();
         atom_add_acq_rel_gpu(ci.counters + chunk, 1);
       };
-      for (int j = 0; j < COPY_AHEAD && j < my_n; ++j) issue_load(j);
-      int done = 0;  // pieces whose completion has been published
+      // Slot s holds piece j (j % COPY_SLOTS == s). The load of piece j+1 flies while piece j is stored.
+      if (my_n > 0) issue_load(0);
+      int done = 0;
       bool ok = true;
       for (int i = 0; i < my_n; ++i) {
         const int slot = i % COPY_SLOTS;
-        if (!mbar_wait(full0 + 8 * slot, (i / COPY_SLOTS) & 1, abort_flag, status, EDL_TIMEOUT_PRODUCER)) {
+        if (i + 1 < my_n) {
+          tma_store_wait_read<0>();  // the store that last used the other slot has left shared memory
+          issue_load(i + 1);
+        }
+        if (!mbar_wait(cfull0 + 8 * slot, (i / COPY_SLOTS) & 1, abort_flag, status, EDL_TIMEOUT_PRODUCER)) {
           ok = false;
           break;
         }
@@ -249,215 +269,198 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         uint8_t* dst;
         int chunk;
         locate(i, src, dst, chunk);
-        bulk_s2g(dst, smem_base + slot * PIECE, PIECE);
+        bulk_s2g(dst, cbase + slot * PIECE, PIECE);
         tma_store_commit();
-        tma_store_wait_read<1>();  // stores up to i-1 have left shared memory: the slot of piece i-2 is free
-        if (i + COPY_AHEAD < my_n) issue_load(i + COPY_AHEAD);
-        tma_store_wait<2>();       // stores up to i-2 are complete in global memory
-        for (; done <= i - 2; ++done) signal(done);
+        tma_store_wait<1>();  // stores up to i-1 are complete in global memory
+        for (; done <= i - 1; ++done) signal(done);
       }
       tma_store_wait<0>();
       if (ok)
         for (; done < my_n; ++done) signal(done);
     }
-  } else {
-    const uint32_t tmem_base = *tmem_slot;
-    const int cta = blockIdx.x - (ci.mode == MODE_AG ? ci.n_copy : 0);
-    const int ncta = gridDim.x - (ci.mode == MODE_AG ? ci.n_copy : 0);
-    const int tiles_n = (N + BN - 1) / BN;
-    const int num_tiles = ci.nranks * ci.tiles_per_shard * tiles_n;
-    const int num_kb = (K + BK - 1) / BK;
-    const int ppc = (BM * K * 2) / PIECE;
-
-    if (warp == 0) {
-      if (lane == 0) {
-        int stage = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
-          const Tile ti = decode(tile, tiles_n, ci);
-          if (ti.chunk >= 0) {
-            if (!wait_counter(ci.counters + ti.chunk, ppc, ci.spin_limit, abort_flag, status)) break;
-            fence_proxy_async_all();
+  } else if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
+        const Tile ti = decode(tile, tiles_n, ci);
+        if (ti.chunk >= 0) {
+          if (!wait_counter(ci.counters + ti.chunk, ppc, ci.spin_limit, abort_flag, status)) break;
+          fence_proxy_async_all();
+        }
+        const CUtensorMap* amap = ti.use_gather ? &tma_g : &tma_a;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, status, EDL_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
           }
-          const CUtensorMap* amap = ti.use_gather ? &tma_g : &tma_a;
-          for (int kb = 0; kb < num_kb; ++kb) {
-            if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, status, EDL_TIMEOUT_PRODUCER)) {
-              ok = false;
-              break;
-            }
-            const uint32_t fb = full0 + 8 * stage;
-            mbar_expect_tx(fb, STAGE_BYTES);
-            const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
-            tma_load_2d(a_dst, amap, fb, kb * BK, ti.a_row);
-            tma_load_2d(a_dst + A_BYTES, &tma_b, fb, kb * BK, ti.n0);
-            if (++stage == STAGES) {
-              stage = 0;
-              phase ^= 1;
-            }
+          const uint32_t fb = full0 + 8 * stage;
+          mbar_expect_tx(fb, STAGE_BYTES);
+          const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+          tma_load_2d(a_dst, amap, fb, kb * BK, ti.a_row);
+          tma_load_2d(a_dst + A_BYTES, &tma_b, fb, kb * BK, ti.n0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
           }
         }
       }
-    } else if (warp == 1) {
-      if (lane == 0) {
-        constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, 0);
-        int stage = 0;
-        uint32_t phase = 0;
-        int acc = 0;
-        uint32_t acc_phase = 0;
-        bool ok = true;
-        for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
-          if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, status, EDL_TIMEOUT_MMA)) break;
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + acc * BN;
-          for (int kb = 0; kb < num_kb; ++kb) {
-            if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, status, EDL_TIMEOUT_MMA)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
-            const uint32_t b_addr = a_addr + A_BYTES;
-#pragma unroll
-            for (int k = 0; k < BK / 16; ++k)
-              umma_f16_ss(d_tmem, umma_smem_desc_sw128(a_addr + k * 32, 16, 1024),
-                          umma_smem_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
-            tc_commit(empty0 + 8 * stage);
-            if (++stage == STAGES) {
-              stage = 0;
-              phase ^= 1;
-            }
-          }
-          if (ok) tc_commit(tfull0 + 8 * acc);
-          acc ^= 1;
-          if (acc == 0) acc_phase ^= 1;
-        }
-      }
-    } else {
-      const int q = warp & 3;
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      const bool ag = ci.mode == MODE_AG;
-      const bool has_bias = ag && (ci.flags & CF_BIAS) && ci.bias != nullptr;
-      const int arrivals_per_dst = 4 * ci.tiles_per_shard * tiles_n;
       bool ok = true;
-      for (int tile = cta; tile < num_tiles; tile += ncta) {
-        const Tile ti = decode(tile, tiles_n, ci);
-        // the whole warp takes the same branch: the tensor-memory loads below are warp-collective
-        if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, status, EDL_TIMEOUT_EPILOGUE))) {
-          ok = false;
-          break;
-        }
+      for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
+        if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, status, EDL_TIMEOUT_MMA)) break;
         tc_fence_after();
-        const long long row = ti.out_row + q * 32 + lane;
-        const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
-        __nv_bfloat16* base = ag ? Cout : reinterpret_cast<__nv_bfloat16*>(ci.peer[ti.dst]);
-        const long long ld = ag ? ldc : (long long)N;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_row + c * 32, r);
-          tc_wait_ld();
-          const int col0 = ti.n0 + c * 32;
-          if (col0 < N) {
-            float v[32];
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, status, EDL_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            if (has_bias) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < N) v[j] += __bfloat162float(ci.bias[col0 + j]);
-            }
-            __nv_bfloat16* cp = base + row * ld + col0;
-            if (col0 + 32 <= N) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]);
-                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-                *reinterpret_cast<uint4*>(cp + j) = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) cp[j] = __float2bfloat16(v[j]);
-            }
+          for (int k = 0; k < BK / 16; ++k)
+            umma_f16_ss(d_tmem, umma_smem_desc_sw128(a_addr + k * 32, 16, 1024),
+                        umma_smem_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit(empty0 + 8 * stage);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
           }
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(tempty0 + 8 * acc);
-          if (!ag) {
-            // Publish: when the last warp of the last tile for this destination has stored, raise its flag.
-            __threadfence_system();
-            const int old = atom_add_acq_rel_gpu(ci.counters + ti.dst, 1);
-            if (old == arrivals_per_dst - 1) st_release_sys(ci.flag[ti.dst] + ci.rank, ci.epoch);
-          }
-        }
+        if (ok) tc_commit(tfull0 + 8 * acc);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
+    }
+  } else {
+    const int q = warp & 3;
+    uint8_t* my_stage = epi_stage + q * 4096;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool ag = ci.mode == MODE_AG;
+    const bool has_bias = ag && (ci.flags & CF_BIAS) && ci.bias != nullptr;
+    const int arrivals_per_dst = 4 * ci.tiles_per_shard * tiles_n;
+    bool ok = true;
+    for (int tile = cta; tile < num_tiles; tile += ncta) {
+      const Tile ti = decode(tile, tiles_n, ci);
+      // the whole warp takes the same branch: the tensor-memory loads below are warp-collective
+      if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, status, EDL_TIMEOUT_EPILOGUE))) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+      __nv_bfloat16* base = ag ? Cout : reinterpret_cast<__nv_bfloat16*>(ci.peer[ti.dst]);
+      const long long ld = ag ? ldc : (long long)N;
+      __nv_bfloat16* gbase = base + (ti.out_row + q * 32) * ld;
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c) {
+        uint32_t r[64];
+        tmem_ld_32x32b_x64(t_row + c * 64, r);
+        tc_wait_ld();
+        const int col0 = ti.n0 + c * 64;
+        if (col0 < N) {  // warp-uniform
+          uint4 pk[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j * 8 + e]);
+            if (has_bias) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (col0 + j * 8 + e < N) v[e] += __bfloat162float(ci.bias[col0 + j * 8 + e]);
+            }
+            pk[j] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                               pack_bf16x2(v[6], v[7]));
+          }
+          store_rows_coalesced<false>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ld * 2, 32,
+                                      min(8, (N - col0) >> 3), lane);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(tempty0 + 8 * acc);
+        if (!ag) {
+          // Publish: when the last warp of the last tile for this destination has stored, raise its flag.
+          __threadfence_system();
+          const int old = atom_add_acq_rel_gpu(ci.counters + ti.dst, 1);
+          if (old == arrivals_per_dst - 1) st_release_sys(ci.flag[ti.dst] + ci.rank, ci.epoch);
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
 
-      if (!ag && __all_sync(0xffffffffu, ok && !*abort_flag)) {
-        // ---- reduce this rank's row shard over the partials staged by every source -----------------------
-        bool ready = true;
-        if (lane == 0) {
-          const int* mine = ci.flag[ci.rank];
-          for (int s = 0; s < ci.nranks && ready; ++s) {
-            long long t0 = clock64();
-            uint32_t it = 0;
-            while (ld_acquire_sys(mine + s) < ci.epoch) {
-              if ((++it & 0x3f) == 0 && (*abort_flag || clock64() - t0 > ci.spin_limit)) {
-                if (!*abort_flag) {
-                  *abort_flag = 1;
-                  if (status) atomicCAS(status, 0, EDL_TIMEOUT_PEER_FLAG);
-                }
-                ready = false;
-                break;
+    if (!ag && __all_sync(0xffffffffu, ok && !*abort_flag)) {
+      // ---- reduce this rank's row shard over the partials staged by every source -------------------------
+      bool ready = true;
+      if (lane == 0) {
+        const int* mine = ci.flag[ci.rank];
+        for (int s = 0; s < ci.nranks && ready; ++s) {
+          long long t0 = clock64();
+          uint32_t it = 0;
+          while (ld_acquire_sys(mine + s) < ci.epoch) {
+            if ((++it & 0x3f) == 0 && (*abort_flag || clock64() - t0 > ci.spin_limit)) {
+              if (!*abort_flag) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, EDL_TIMEOUT_PEER_FLAG);
               }
+              ready = false;
+              break;
             }
           }
         }
-        ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
-        if (ready) {
-          const long long rows = (long long)ci.tiles_per_shard * BM;
-          const long long vec_per_row = N / 8;
-          const long long total = rows * vec_per_row;
-          const long long slot_elems = rows * N;
-          const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(ci.peer[ci.rank]);
-          const bool has_res = (ci.flags & CF_RESIDUAL) && ci.residual != nullptr;
-          const bool rs_bias = (ci.flags & CF_BIAS) && ci.bias != nullptr;
-          for (long long v = (long long)cta * 128 + (warp - 2) * 32 + lane; v < total; v += (long long)ncta * 128) {
-            float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int s = 0; s < ci.nranks; ++s) {
-              const uint4 x = __ldcg(reinterpret_cast<const uint4*>(stage + s * slot_elems + v * 8));
-              float2 f;
-              f = unpack_bf16x2(x.x); a[0] += f.x; a[1] += f.y;
-              f = unpack_bf16x2(x.y); a[2] += f.x; a[3] += f.y;
-              f = unpack_bf16x2(x.z); a[4] += f.x; a[5] += f.y;
-              f = unpack_bf16x2(x.w); a[6] += f.x; a[7] += f.y;
-            }
-            if (has_res) {
-              const uint4 x = *reinterpret_cast<const uint4*>(ci.residual + v * 8);
-              float2 f;
-              f = unpack_bf16x2(x.x); a[0] += f.x; a[1] += f.y;
-              f = unpack_bf16x2(x.y); a[2] += f.x; a[3] += f.y;
-              f = unpack_bf16x2(x.z); a[4] += f.x; a[5] += f.y;
-              f = unpack_bf16x2(x.w); a[6] += f.x; a[7] += f.y;
-            }
-            if (rs_bias) {
-              const int col = (int)((v % vec_per_row) * 8);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) a[j] += __bfloat162float(ci.bias[col + j]);
-            }
-            uint4 o;
-            o.x = pack_bf16x2(a[0], a[1]);
-            o.y = pack_bf16x2(a[2], a[3]);
-            o.z = pack_bf16x2(a[4], a[5]);
-            o.w = pack_bf16x2(a[6], a[7]);
-            *reinterpret_cast<uint4*>(Cout + v * 8) = o;
+      }
+      ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+      if (ready) {
+        const long long rows = (long long)ci.tiles_per_shard * BM;
+        const long long vec_per_row = N / 8;
+        const long long total = rows * vec_per_row;
+        const long long slot_elems = rows * N;
+        const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(ci.peer[ci.rank]);
+        const bool has_res = (ci.flags & CF_RESIDUAL) && ci.residual != nullptr;
+        const bool rs_bias = (ci.flags & CF_BIAS) && ci.bias != nullptr;
+        for (long long v = (long long)cta * 128 + (warp - 2) * 32 + lane; v < total; v += (long long)ncta * 128) {
+          float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int s = 0; s < ci.nranks; ++s) {
+            const uint4 x = __ldcg(reinterpret_cast<const uint4*>(stage + s * slot_elems + v * 8));
+            float2 f;
+            f = unpack_bf16x2(x.x); a[0] += f.x; a[1] += f.y;
+            f = unpack_bf16x2(x.y); a[2] += f.x; a[3] += f.y;
+            f = unpack_bf16x2(x.z); a[4] += f.x; a[5] += f.y;
+            f = unpack_bf16x2(x.w); a[6] += f.x; a[7] += f.y;
           }
+          if (has_res) {
+            const uint4 x = *reinterpret_cast<const uint4*>(ci.residual + v * 8);
+            float2 f;
+            f = unpack_bf16x2(x.x); a[0] += f.x; a[1] += f.y;
+            f = unpack_bf16x2(x.y); a[2] += f.x; a[3] += f.y;
+            f = unpack_bf16x2(x.z); a[4] += f.x; a[5] += f.y;
+            f = unpack_bf16x2(x.w); a[6] += f.x; a[7] += f.y;
+          }
+          if (rs_bias) {
+            const int col = (int)((v % vec_per_row) * 8);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[j] += __bfloat162float(ci.bias[col + j]);
+          }
+          uint4 o;
+          o.x = pack_bf16x2(a[0], a[1]);
+          o.y = pack_bf16x2(a[2], a[3]);
+          o.z = pack_bf16x2(a[4], a[5]);
+          o.w = pack_bf16x2(a[6], a[7]);
+          *reinterpret_cast<uint4*>(Cout + v * 8) = o;
         }
       }
     }
@@ -470,7 +473,7 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   }
   tc_fence_before();
   __syncthreads();
-  if (!copier && warp == 1) tmem_dealloc(*tmem_slot, TMEM_COLS);
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 int launch_collective(const CUtensorMap& ta, const CUtensorMap& tg, const CUtensorMap& tb, void* C, int N, int K,
@@ -544,7 +547,7 @@ EDL_HOST_API int edl_gemm_reduce_scatter(const void* A, const void* W, void* out
 //   finished (callers bracket the call with a device barrier over the same symmetric allocation).
 //   gathered: local [nranks * Ms, K]; rows of rank r land at r * Ms (own rows only when copy_own != 0).
 //   C [nranks * Ms, N] (ldc) = gather(A) * W^T (+ bias). counters: nranks * Ms / 128 local ints.
-//   n_copy: CTAs set aside for copying (0 = default of 12).
+//   n_copy is ignored (kept for binary compatibility): every CTA copies with a spare warp.
 EDL_HOST_API int edl_allgather_gemm(void* const* shard_ptrs, const void* W, void* C, const void* bias, void* gathered,
                                     int Ms, int N, int K, long long ldb, long long ldc, int* counters, int nranks,
                                     int rank, int n_copy, int copy_own, int wait_ms, int* status, void* stream) {
@@ -554,9 +557,7 @@ EDL_HOST_API int edl_allgather_gemm(void* const* shard_ptrs, const void* W, void
                    Ms, N, K);
     return -1;
   }
-  if (n_copy <= 0) n_copy = 12;
-  if (nranks == 1 && !copy_own) n_copy = 0;
-  if (n_copy > sm_count() / 2) n_copy = sm_count() / 2;
+  (void)n_copy;
   CUtensorMap ta, tg, tb;
   if (make_tmap_2d_16b(&ta, shard_ptrs[rank], Ms, K, K, BM, BK)) return -1;
   if (make_tmap_2d_16b(&tg, gathered, (uint64_t)nranks * Ms, K, K, BM, BK)) return -1;
@@ -566,7 +567,6 @@ EDL_HOST_API int edl_allgather_gemm(void* const* shard_ptrs, const void* W, void
   ci.nranks = nranks;
   ci.rank = rank;
   ci.tiles_per_shard = Ms / BM;
-  ci.n_copy = n_copy;
   ci.flags = (bias ? CF_BIAS : 0) | (copy_own ? CF_COPY_OWN : 0);
   ci.spin_limit = cycles_for_ms(wait_ms);
   for (int r = 0; r < nranks; ++r) ci.peer[r] = shard_ptrs[r];
