@@ -52,7 +52,8 @@ class PagedKVCache:
 
     @classmethod
     def init_for_model(cls, model, num_pages: int | None = None, page_size: int = PAGE_SIZE,
-                       hbm_utilization: float = 0.85, max_model_length: int | None = None, dtype=None, device=None):
+                       hbm_utilization: float = 0.85, max_model_length: int | None = None, dtype=None, device=None,
+                       max_pages: int | None = None):
         spec = model.spec
         device = device or model.device
         dtype = dtype or getattr(model.config, "kvdtype", None) or model.dtype
@@ -66,9 +67,9 @@ class PagedKVCache:
             else:
                 budget = 256 << 20
             num_pages = max(2, budget // per_page)
-            if max_model_length is not None:
-                # never more than max_num_seqs * pages-per-sequence would need; the engine caps it further
-                pass
+        if max_pages is not None:
+            # never more than max_num_seqs * pages-per-sequence would need
+            num_pages = min(int(num_pages), int(max_pages))
         return cls(spec.num_layers, int(num_pages), kvh, spec.head_dim, dtype, device, page_size)
 
     def view(self, layer: int) -> "PagedLayerView":

@@ -8,6 +8,11 @@
 // a peer that is still reading call n never sees the writes of call n+1; the flag wait of call
 // n+1 proves every peer has finished call n before slot n is written again by call n+2.
 //
+// The call number ("epoch") lives in device memory: every block reads it on entry and the block that finishes
+// last writes it back incremented, so a captured CUDA graph that contains these launches can be replayed (a
+// graph must contain an even number of them, which keeps the slot parity of every launch fixed). All ranks add
+// the partials in rank order, so every rank ends up with bitwise the same sum.
+//
 // The reference leaves this all-reduce to XLA -> NCCL (implicit SPMD collectives, see
 // easydel/layers/linears/_linear.py:348-378); decode-time messages of [tokens, hidden] bf16 are
 // latency-bound, which is what the one-shot peer-load form is for.
@@ -31,10 +36,12 @@ __device__ __forceinline__ int ld_acquire_sys(const int* addr) {
 }
 
 // data.p[r]: rank r's partial (n bf16 elements); flags.p[r]: rank r's flag array (int[MAX_RANKS]).
-__global__ void allreduce_oneshot_kernel(PeerPtrs data, PeerPtrs flags, int nranks, int rank, int epoch,
+// sync[0]: number of calls completed on this group; sync[1]: ticket counter of the running call.
+__global__ void allreduce_oneshot_kernel(PeerPtrs data, PeerPtrs flags, int nranks, int rank, int* sync,
                                          __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual,
                                          long long n, long long spin_limit, int* status) {
   __shared__ int s_ok;
+  const int epoch = *reinterpret_cast<volatile int*>(sync) + 1;
   if (blockIdx.x == 0 && threadIdx.x < nranks)
     st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + rank, epoch);
   if (threadIdx.x == 0) {
@@ -53,16 +60,20 @@ __global__ void allreduce_oneshot_kernel(PeerPtrs data, PeerPtrs flags, int nran
     s_ok = ok;
   }
   __syncthreads();
-  if (!s_ok) return;
-  const long long nvec = n / 8;
+  const long long nvec = s_ok ? n / 8 : 0;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int k = 0; k < nranks; ++k) {
-      const int r = (rank + k) % nranks;
-      const uint4 v = reinterpret_cast<const uint4*>(data.p[r])[i];
+    uint4 part[MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < nranks) part[r] = reinterpret_cast<const uint4*>(data.p[r])[i];
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r >= nranks) break;
+      const uint4 v = part[r];
       float2 f;
       f = unpack_bf16x2(v.x); acc[0] += f.x; acc[1] += f.y;
       f = unpack_bf16x2(v.y); acc[2] += f.x; acc[3] += f.y;
@@ -84,6 +95,16 @@ __global__ void allreduce_oneshot_kernel(PeerPtrs data, PeerPtrs flags, int nran
     o.w = pack_bf16x2(acc[6], acc[7]);
     reinterpret_cast<uint4*>(out)[i] = o;
   }
+  // The last block to get here publishes the new call count (also after a timeout, so that the ranks stay in step).
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(sync + 1, 1) == (int)gridDim.x - 1) {
+      sync[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile int*>(sync) = epoch;
+    }
+  }
 }
 
 }  // namespace
@@ -92,10 +113,10 @@ __global__ void allreduce_oneshot_kernel(PeerPtrs data, PeerPtrs flags, int nran
 using namespace edl;
 
 // data_ptrs[r] / flag_ptrs[r]: peer-mapped addresses of rank r's partial and flag array.
-// n: bf16 elements (multiple of 8). epoch: strictly increasing per call on this group.
+// n: bf16 elements (multiple of 8). sync: two device ints (zero-initialised once per group) holding the call count.
 // wait_ms: how long to wait for peers before giving up with status EDL_TIMEOUT_PEER_FLAG.
 EDL_HOST_API int edl_allreduce_oneshot(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs,
-                                       int nranks, int rank, int epoch, void* out, const void* residual, long long n,
+                                       int nranks, int rank, int* sync, void* out, const void* residual, long long n,
                                        int wait_ms, int* status, void* stream) {
   if (n <= 0) return 0;
   if (nranks < 1 || nranks > MAX_RANKS || (n & 7)) {
@@ -111,6 +132,6 @@ EDL_HOST_API int edl_allreduce_oneshot(const unsigned long long* data_ptrs, cons
   long long cap = (long long)sm_count();
   const long long spin = (long long)(wait_ms > 0 ? wait_ms : 2000) * 2000000LL;
   allreduce_oneshot_kernel<<<(int)(blocks > cap ? cap : blocks), 256, 0, (cudaStream_t)stream>>>(
-      d, f, nranks, rank, epoch, (__nv_bfloat16*)out, (const __nv_bfloat16*)residual, n, spin, status);
+      d, f, nranks, rank, sync, (__nv_bfloat16*)out, (const __nv_bfloat16*)residual, n, spin, status);
   return check_cuda(cudaGetLastError(), "allreduce_oneshot launch");
 }

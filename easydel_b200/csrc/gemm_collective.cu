@@ -432,35 +432,54 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(ci.peer[ci.rank]);
         const bool has_res = (ci.flags & CF_RESIDUAL) && ci.residual != nullptr;
         const bool rs_bias = (ci.flags & CF_BIAS) && ci.bias != nullptr;
-        for (long long v = (long long)cta * 128 + (warp - 2) * 32 + lane; v < total; v += (long long)ncta * 128) {
-          float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int s = 0; s < ci.nranks; ++s) {
-            const uint4 x = __ldcg(reinterpret_cast<const uint4*>(stage + s * slot_elems + v * 8));
-            float2 f;
-            f = unpack_bf16x2(x.x); a[0] += f.x; a[1] += f.y;
-            f = unpack_bf16x2(x.y); a[2] += f.x; a[3] += f.y;
-            f = unpack_bf16x2(x.z); a[4] += f.x; a[5] += f.y;
-            f = unpack_bf16x2(x.w); a[6] += f.x; a[7] += f.y;
-          }
-          if (has_res) {
-            const uint4 x = *reinterpret_cast<const uint4*>(ci.residual + v * 8);
-            float2 f;
-            f = unpack_bf16x2(x.x); a[0] += f.x; a[1] += f.y;
-            f = unpack_bf16x2(x.y); a[2] += f.x; a[3] += f.y;
-            f = unpack_bf16x2(x.z); a[4] += f.x; a[5] += f.y;
-            f = unpack_bf16x2(x.w); a[6] += f.x; a[7] += f.y;
-          }
-          if (rs_bias) {
-            const int col = (int)((v % vec_per_row) * 8);
+        // four independent 16-byte vectors per thread and step keep enough loads in flight to stream from HBM
+        const long long step = (long long)ncta * 128;
+        for (long long v0 = (long long)cta * 128 + (warp - 2) * 32 + lane; v0 < total; v0 += 4 * step) {
+          uint4 x[4][MAX_RANKS];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) a[j] += __bfloat162float(ci.bias[col + j]);
+          for (int u = 0; u < 4; ++u) {
+            const long long v = v0 + u * step;
+            if (v < total) {
+#pragma unroll
+              for (int s = 0; s < MAX_RANKS; ++s)
+                if (s < ci.nranks) x[u][s] = __ldcg(reinterpret_cast<const uint4*>(stage + s * slot_elems + v * 8));
+            }
           }
-          uint4 o;
-          o.x = pack_bf16x2(a[0], a[1]);
-          o.y = pack_bf16x2(a[2], a[3]);
-          o.z = pack_bf16x2(a[4], a[5]);
-          o.w = pack_bf16x2(a[6], a[7]);
-          *reinterpret_cast<uint4*>(Cout + v * 8) = o;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const long long v = v0 + u * step;
+            if (v >= total) break;
+            float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < MAX_RANKS; ++s) {
+              if (s < ci.nranks) {
+                float2 f;
+                f = unpack_bf16x2(x[u][s].x); a[0] += f.x; a[1] += f.y;
+                f = unpack_bf16x2(x[u][s].y); a[2] += f.x; a[3] += f.y;
+                f = unpack_bf16x2(x[u][s].z); a[4] += f.x; a[5] += f.y;
+                f = unpack_bf16x2(x[u][s].w); a[6] += f.x; a[7] += f.y;
+              }
+            }
+            if (has_res) {
+              const uint4 r4 = *reinterpret_cast<const uint4*>(ci.residual + v * 8);
+              float2 f;
+              f = unpack_bf16x2(r4.x); a[0] += f.x; a[1] += f.y;
+              f = unpack_bf16x2(r4.y); a[2] += f.x; a[3] += f.y;
+              f = unpack_bf16x2(r4.z); a[4] += f.x; a[5] += f.y;
+              f = unpack_bf16x2(r4.w); a[6] += f.x; a[7] += f.y;
+            }
+            if (rs_bias) {
+              const int col = (int)((v % vec_per_row) * 8);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) a[j] += __bfloat162float(ci.bias[col + j]);
+            }
+            uint4 o;
+            o.x = pack_bf16x2(a[0], a[1]);
+            o.y = pack_bf16x2(a[2], a[3]);
+            o.z = pack_bf16x2(a[4], a[5]);
+            o.w = pack_bf16x2(a[6], a[7]);
+            *reinterpret_cast<uint4*>(Cout + v * 8) = o;
+          }
         }
       }
     }

@@ -120,10 +120,10 @@ class eSurge:
         self.reserve_tokens = reserve_tokens if reserve_tokens is not None else 1
         self.name = esurge_name or f"esurge-{id(self) & 0xffff:x}"
         pages_cap = max_num_seqs * ((max_model_len + page_size - 1) // page_size) + 1
+        # the page count is settled before anything is allocated: two caches never exist at once
         self.cache = PagedKVCache.init_for_model(model, num_pages=num_pages, page_size=page_size,
-                                                 hbm_utilization=hbm_utilization, max_model_length=max_model_len)
-        if num_pages is None and self.cache.num_pages > pages_cap:
-            self.cache = PagedKVCache.init_for_model(model, num_pages=pages_cap, page_size=page_size)
+                                                 hbm_utilization=hbm_utilization, max_model_length=max_model_len,
+                                                 max_pages=pages_cap if num_pages is None else None)
         self.pool = PagePool(self.cache.num_pages, enable_caching=enable_prefix_caching)
         self.scheduler = Scheduler(SchedulerConfig(max_num_seqs=max_num_seqs,
                                                    max_num_batched_tokens=self.max_num_batched_tokens,

@@ -48,7 +48,20 @@ class ModelRunner:
         self._ihost = torch.zeros(3 * B, dtype=torch.int64, pin_memory=pin)
         self._idev = torch.zeros(3 * B, dtype=torch.int64, device=dev)
         self.counts: torch.Tensor | None = None
-        self.timings: dict[str, float] = {"prep": 0.0, "exec": 0.0, "sample": 0.0, "d2h": 0.0, "steps": 0}
+        self.timings: dict[str, float] = {"prep": 0.0, "exec": 0.0, "sample": 0.0, "d2h": 0.0, "steps": 0,
+                                          "graph_steps": 0}
+        # Decode-only greedy steps are replayed from CUDA graphs, one per power-of-two batch bucket
+        # (the reference compiles (tokens, requests) buckets ahead of time: runners/execution_manager.py:1291-1405).
+        import os
+
+        self.use_graphs = dev.type == "cuda" and os.environ.get("EDL_ESURGE_CUDA_GRAPHS", "1") != "0"
+        self._graphs: dict[int, tuple[tp.Any, torch.Tensor]] = {}
+        self._graph_pool = None
+        self._warm: set[int] = set()
+        self.tp_group = None
+        mesh = getattr(model.config, "mesh", None)
+        if mesh is not None and getattr(mesh, "tp", 1) > 1:
+            self.tp_group = mesh.get_group("tp")
 
     def _split(self, buf: torch.Tensor) -> list[torch.Tensor]:
         out, o = [], 0
@@ -71,6 +84,38 @@ class ModelRunner:
         if token_ids:
             t = torch.tensor(list(token_ids), dtype=torch.int64, device=self.device)
             self.counts[slot].index_put_((t,), torch.ones_like(t, dtype=torch.int32), accumulate=True)
+
+    def _forward(self, B: int, T: int, max_q: int, num_decode: int) -> torch.Tensor:
+        """Backbone over the first ``T`` staged tokens of ``B`` sequences, LM head on each sequence's last row."""
+        d_ids, d_pos, d_slots, d_cu, d_kv, d_last, d_table = self._dviews
+        MP = self.max_pages_per_seq
+        meta = PagedBatchMeta(cu_q=d_cu[:B + 1], kv_lens=d_kv[:B], page_table=d_table.view(self.max_num_seqs, MP)[:B],
+                              slot_mapping=d_slots[:T], max_q=max_q, num_seqs=B, last_token_index=d_last[:B],
+                              request_distribution=(num_decode, B, B))
+        model = self.model
+        res = model(input_ids=d_ids[:T][None].long(), position_ids=d_pos[:T][None], past_key_values=self.cache,
+                    cache_metadata=meta, apply_lm_head=False)
+        rows = S.gather_rows(res.last_hidden_state[0], d_last[:B])
+        return model.apply_lm_head(rows)
+
+    def _decode_step_graphed(self, Bp: int) -> torch.Tensor:
+        """Greedy decode step for ``Bp`` rows: eager the first time (warm-up), captured the second, replayed after."""
+        entry = self._graphs.get(Bp)
+        if entry is not None:
+            entry[0].replay()
+            return entry[1]
+        if Bp not in self._warm:
+            self._warm.add(Bp)
+            return S.sample(self._forward(Bp, Bp, 1, Bp))[0]
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=self._graph_pool):
+            toks = S.sample(self._forward(Bp, Bp, 1, Bp))[0]
+        if self._graph_pool is None:
+            self._graph_pool = g.pool()
+        self._graphs[Bp] = (g, toks)
+        g.replay()
+        return toks
 
     @torch.no_grad()
     def execute(self, out: SchedulerOutput) -> dict[str, int]:
@@ -117,45 +162,56 @@ class ModelRunner:
             sp = req.sampling_params
             any_pen |= sp.needs_penalties
             any_random |= not sp.is_greedy
+        decode_only = max_q == 1 and not any_pen and not any_random
+        Bp = B
+        if self.use_graphs and decode_only:
+            Bp = 1
+            while Bp < B:
+                Bp *= 2
+            Bp = min(Bp, self.max_num_seqs)
+            if Bp > B:   # pad rows: token 0 at position 0 written to the null page, attending to one key
+                ids_np[B:Bp] = 0
+                pos_np[B:Bp] = 0
+                slots_np[B:Bp] = 0
+                table_np[B:Bp, :] = 0
+                kv_np[B:Bp] = 1
+                cu_np[B + 1:Bp + 1] = np.arange(B + 1, Bp + 1, dtype=np.int32)
+                last_np[B:Bp] = np.arange(B, Bp, dtype=np.int32)
         # one upload of the packed metadata
         self._dev.copy_(self._host, non_blocking=True)
-        d_ids, d_pos, d_slots, d_cu, d_kv, d_last, d_table = self._dviews
-        meta = PagedBatchMeta(cu_q=d_cu[:B + 1], kv_lens=d_kv[:B], page_table=d_table.view(self.max_num_seqs, MP)[:B],
-                              slot_mapping=d_slots[:T], max_q=max_q, num_seqs=B, last_token_index=d_last[:B],
-                              request_distribution=(out.num_decode, B, B))
         t1 = time.perf_counter()
-        model = self.model
-        res = model(input_ids=d_ids[:T][None].long(), position_ids=d_pos[:T][None], past_key_values=self.cache,
-                    cache_metadata=meta, apply_lm_head=False)
-        hidden = res.last_hidden_state[0]
-        rows = S.gather_rows(hidden, d_last[:B])
-        logits = model.apply_lm_head(rows)
-        t2 = time.perf_counter()
-        kw = {}
-        if any_random or any_pen:
-            fh, ih = self._fhost.view(6, -1), self._ihost.view(3, -1)
-            for b, s in enumerate(sched):
-                sp = s.request.sampling_params
-                fh[0, b] = 0.0 if sp.is_greedy else sp.temperature
-                fh[1, b], fh[2, b] = sp.top_p, sp.min_p
-                fh[3, b], fh[4, b], fh[5, b] = sp.presence_penalty, sp.frequency_penalty, sp.repetition_penalty
-                ih[0, b] = sp.top_k
-                ih[1, b] = sp.seed if sp.seed is not None else hash(s.request.request_id) & 0x7FFFFFFF
-                ih[2, b] = len(s.request.output_token_ids)
-            self._fdev.copy_(self._fhost, non_blocking=True)
-            self._idev.copy_(self._ihost, non_blocking=True)
-            fd, idv = self._fdev.view(6, -1), self._idev.view(3, -1)
-            kw = dict(temperature=fd[0, :B], top_p=fd[1, :B], min_p=fd[2, :B], top_k=idv[0, :B].to(torch.int32),
-                      seeds=idv[1, :B], steps=idv[2, :B].to(torch.int32))
+        if self.use_graphs and decode_only:
+            tokens = self._decode_step_graphed(Bp)[:B]
+            self.timings["graph_steps"] += 1
+            t2 = time.perf_counter()
+        else:
+            logits = self._forward(B, T, max_q, out.num_decode)
+            t2 = time.perf_counter()
+            kw = {}
+            if any_random or any_pen:
+                fh, ih = self._fhost.view(6, -1), self._ihost.view(3, -1)
+                for b, s in enumerate(sched):
+                    sp = s.request.sampling_params
+                    fh[0, b] = 0.0 if sp.is_greedy else sp.temperature
+                    fh[1, b], fh[2, b] = sp.top_p, sp.min_p
+                    fh[3, b], fh[4, b], fh[5, b] = sp.presence_penalty, sp.frequency_penalty, sp.repetition_penalty
+                    ih[0, b] = sp.top_k
+                    ih[1, b] = sp.seed if sp.seed is not None else hash(s.request.request_id) & 0x7FFFFFFF
+                    ih[2, b] = len(s.request.output_token_ids)
+                self._fdev.copy_(self._fhost, non_blocking=True)
+                self._idev.copy_(self._ihost, non_blocking=True)
+                fd, idv = self._fdev.view(6, -1), self._idev.view(3, -1)
+                kw = dict(temperature=fd[0, :B], top_p=fd[1, :B], min_p=fd[2, :B], top_k=idv[0, :B].to(torch.int32),
+                          seeds=idv[1, :B], steps=idv[2, :B].to(torch.int32))
+                if any_pen:
+                    counts = self._ensure_counts()
+                    slot_rows = torch.tensor([s.request.slot for s in sched], dtype=torch.int64, device=self.device)
+                    kw.update(presence=fd[3, :B], frequency=fd[4, :B], repetition=fd[5, :B],
+                              counts=counts.index_select(0, slot_rows))
+            tokens, _ = S.sample(logits, **kw)
             if any_pen:
-                counts = self._ensure_counts()
-                slot_rows = torch.tensor([s.request.slot for s in sched], dtype=torch.int64, device=self.device)
-                kw.update(presence=fd[3, :B], frequency=fd[4, :B], repetition=fd[5, :B],
-                          counts=counts.index_select(0, slot_rows))
-        tokens, _ = S.sample(logits, **kw)
-        if any_pen:
-            S.count_update(self.counts, tokens, torch.tensor([s.request.slot for s in sched], dtype=torch.int32,
-                                                              device=self.device))
+                S.count_update(self.counts, tokens, torch.tensor([s.request.slot for s in sched], dtype=torch.int32,
+                                                                  device=self.device))
         t3 = time.perf_counter()
         host_tokens = tokens.cpu().tolist()  # the step's only device->host read
         t4 = time.perf_counter()

@@ -21,7 +21,7 @@ import torch.distributed as dist
 
 from ..ops import _lib
 
-_lib.register("edl_allreduce_oneshot", _lib.i32, [_lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.vp,
+_lib.register("edl_allreduce_oneshot", _lib.i32, [_lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.vp, _lib.vp, _lib.vp,
                                                   _lib.i64, _lib.i32, _lib.vp, _lib.vp])
 
 ONE_SHOT_MAX_BYTES = 1 << 20
@@ -48,7 +48,8 @@ class _PeerAllReduce:
             raise RuntimeError("symmetric-memory handle does not address this rank's own buffer")
         self.slot_ptrs = [(C.c_ulonglong * self.world)(*[b + s * max_bytes for b in base]) for s in range(2)]
         self.flag_ptrs = (C.c_ulonglong * self.world)(*[b + 2 * max_bytes for b in base])
-        self.epoch = 0
+        self.epoch = 0          # host-side call count: selects the slot; the kernel keeps its own count in `sync`
+        self.sync = torch.zeros(2, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
@@ -67,7 +68,7 @@ class _PeerAllReduce:
         s = self.epoch & 1
         out = torch.empty_like(partial_in_slot, memory_format=torch.contiguous_format)
         _lib.call("edl_allreduce_oneshot", C.cast(self.slot_ptrs[s], C.c_void_p), C.cast(self.flag_ptrs, C.c_void_p),
-                  self.world, self.rank, self.epoch, out.data_ptr(), _lib.ptr(residual), partial_in_slot.numel(),
+                  self.world, self.rank, self.sync.data_ptr(), out.data_ptr(), _lib.ptr(residual), partial_in_slot.numel(),
                   wait_ms, _lib.status_word(out.device).data_ptr(), _lib.stream_ptr())
         return out
 
