@@ -510,3 +510,67 @@ EDL_HOST_API int edl_gemm_grouped(int kind, const void* X, const void* W, void* 
   set_last_error("edl_gemm_grouped: unknown kind %d", kind);
   return -1;
 }
+
+namespace edl {
+namespace {
+// out[m, n] = sum_s ws[s, m, n] (+ bias[n]), fp32 partials -> bf16.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out,
+                                     const __nv_bfloat16* __restrict__ bias, int M, int N, long long ldc, int splits) {
+  const long long vec_per_row = N / 4;
+  const long long total = (long long)M * vec_per_row;
+  const long long plane = (long long)M * N;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total;
+       v += (long long)gridDim.x * blockDim.x) {
+    const long long m = v / vec_per_row;
+    const int n = (int)(v - m * vec_per_row) * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+      const float4 x = *reinterpret_cast<const float4*>(ws + s * plane + m * N + n);
+      a.x += x.x;
+      a.y += x.y;
+      a.z += x.z;
+      a.w += x.w;
+    }
+    if (bias) {
+      a.x += __bfloat162float(bias[n]);
+      a.y += __bfloat162float(bias[n + 1]);
+      a.z += __bfloat162float(bias[n + 2]);
+      a.w += __bfloat162float(bias[n + 3]);
+    }
+    uint2 o;
+    o.x = pack_bf16x2(a.x, a.y);
+    o.y = pack_bf16x2(a.z, a.w);
+    *reinterpret_cast<uint2*>(out + m * ldc + n) = o;
+  }
+}
+}  // namespace
+}  // namespace edl
+
+// Split-K form of C[M,N] = A[M,K] * B[N,K]^T (+ bias) for skinny problems (decode steps: a few rows against a
+// large weight matrix), where the plain kernel has too few output tiles to keep every SM streaming weights.
+// The K range is cut into `splits` slices, each (tile, slice) pair is one unit of work writing an fp32 partial
+// into `workspace` [splits, M, N]; a second small kernel sums the slices and casts to bf16.
+//   k_offsets: device int[splits + 1], multiples of 64 from 0 to K. N must be a multiple of 8.
+EDL_HOST_API int edl_gemm_splitk(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                                 long long lda, long long ldb, long long ldc, int splits, void* workspace,
+                                 const int* k_offsets, int* status, void* stream) {
+  using namespace edl;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7) || splits < 1) {
+    set_last_error("edl_gemm_splitk: lda, ldb, ldc, N must be multiples of 8 and splits >= 1");
+    return -1;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  GroupInfo g{2, splits, nullptr, nullptr, k_offsets, 0, (long long)M * N};
+  const int tiles = splits * ((M + 127) / 128) * ((N + 127) / 128);
+  int rc = launch<128, false, false>(A, B, workspace, nullptr, M, N, K, lda, ldb, N, GEMM_OUT_F32, status, s, 0, g, M,
+                                     N, tiles);
+  if (rc) return rc;
+  const long long vecs = (long long)M * (N / 4);
+  int blocks = (int)((vecs + 255) / 256);
+  if (blocks > 4 * sm_count()) blocks = 4 * sm_count();
+  splitk_reduce_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float*>(workspace),
+                                              reinterpret_cast<__nv_bfloat16*>(C),
+                                              reinterpret_cast<const __nv_bfloat16*>(bias), M, N, ldc, splits);
+  return check_cuda(cudaGetLastError(), "splitk_reduce launch");
+}

@@ -31,6 +31,7 @@ _SIGS = {
     "edl_sm_count": (i32, []),
     "edl_abi_version": (i32, []),
     "edl_gemm_bf16": (i32, [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i32, i32, vp, vp, i32, i32]),
+    "edl_gemm_splitk": (i32, [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, vp, vp, vp, vp]),
     "edl_rmsnorm_fwd": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32, f32, vp]),
     "edl_rmsnorm_bwd_workspace": (i64, [i32, i32]),
     "edl_rmsnorm_bwd": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, i32, vp]),

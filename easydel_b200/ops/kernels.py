@@ -26,6 +26,44 @@ def _check_bf16_2d(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name}: base pointer / leading dimension must be 16-byte aligned")
 
 
+_SPLITK_OFFSETS: dict[tuple, torch.Tensor] = {}
+_SM_COUNT: dict[int, int] = {}
+
+
+def _splitk_plan(M: int, N: int, K: int, device) -> int:
+    """Number of K slices for a skinny GEMM (1 = use the plain kernel).
+
+    Decode-time linears have a handful of rows and are bound by streaming the weight matrix; with one CTA per
+    128-column tile a 4096-wide projection would occupy 32 of 148 SMs. Slicing K gives every SM a share.
+    """
+    if M > 256 or N % 8 or K % 64 or K < 512:
+        return 1
+    idx = device.index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(device).multi_processor_count
+    sms = _SM_COUNT[idx]
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
+    if tiles * 4 >= sms * 3:
+        return 1
+    kb = K // 64
+    want = min(16, max(2, (2 * sms + tiles - 1) // tiles))
+    best = 1
+    for s in range(2, want + 1):
+        if kb % s == 0 and kb // s >= 2:
+            best = s
+    return best
+
+
+def _splitk_offsets(K: int, splits: int, device) -> torch.Tensor:
+    key = (K, splits, device.index or 0)
+    t = _SPLITK_OFFSETS.get(key)
+    if t is None:
+        step = K // splits
+        t = torch.tensor([i * step for i in range(splits + 1)], dtype=torch.int32, device=device)
+        _SPLITK_OFFSETS[key] = t
+    return t
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
          out_dtype: torch.dtype | None = None, accumulate: bool = False, bias: torch.Tensor | None = None,
          max_ctas: int = 0, force_bn: int = 0) -> torch.Tensor:
@@ -58,6 +96,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     lda = a.stride(0) if a.shape[0] > 1 else a.shape[1]
     ldb = b.stride(0) if b.shape[0] > 1 else b.shape[1]
     ldc = out.stride(0) if out.shape[0] > 1 else out.shape[1]
+    if not (a_mn or b_mn or accumulate or max_ctas or force_bn) and out.dtype == torch.bfloat16:
+        splits = _splitk_plan(M, N, K, a.device)
+        if splits > 1:
+            ws = torch.empty((splits, M, N), dtype=torch.float32, device=a.device)
+            _lib.call("edl_gemm_splitk", a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K, lda, ldb,
+                      ldc, splits, ws.data_ptr(), _splitk_offsets(K, splits, a.device).data_ptr(),
+                      _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+            return out
     _lib.call("edl_gemm_bf16", a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K, lda, ldb, ldc,
               int(a_mn), int(b_mn), flags, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr(), max_ctas,
               force_bn)

@@ -84,3 +84,21 @@ def test_gemm_deterministic():
     o1 = K_.gemm(a, b)
     o2 = K_.gemm(a, b)
     assert torch.equal(o1, o2)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (16, 6144, 4096), (64, 1280, 8192), (256, 4096, 14336),
+                                   (48, 8192, 1024)])
+def test_gemm_skinny_uses_split_k(M, N, K):
+    """Decode-shaped products take the split-K path and agree with the fp32 reference (with and without bias)."""
+    from easydel_b200.ops import kernels as K_
+
+    assert K_._splitk_plan(M, N, K, torch.device("cuda", 0)) > 1
+    torch.manual_seed(M + N)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    for b in (None, bias):
+        out = K_.gemm(a, w, bias=b)
+        ref = a.float() @ w.float().t() + (b.float() if b is not None else 0)
+        err = (out.float() - ref).abs().max() / ref.abs().max()
+        assert err < 1e-2, err
