@@ -497,11 +497,11 @@ EDL_HOST_API int edl_attn_fwd(const void* q, const void* k, const void* v, void*
 //   max_q:    largest number of new tokens of any sequence (sizes the grid)
 // All query heads of a KV head share one tile (rows = token x head), so one pass over a page
 // serves the whole GQA group. Hq / Hkv must be a power of two <= 128.
-EDL_HOST_API int edl_attn_paged(const void* q, const void* k_pages, const void* v_pages, void* o, long long ldq,
-                                long long ld_page, long long ldo, const int* cu_q, const int* kv_lens,
-                                const int* page_table, int pt_stride, int B, int max_q, long long total_q,
-                                long long num_pages, int Hq, int Hkv, int D, float scale, int causal, int window,
-                                float softcap, const float* sinks, int* status, void* stream) {
+static int attn_paged_impl(const void* q, const void* k_pages, const void* v_pages, void* o, float* lse,
+                           long long ldq, long long ld_page, long long ldo, const int* cu_q, const int* kv_lens,
+                           const int* page_table, int pt_stride, int B, int max_q, long long total_q,
+                           long long num_pages, int Hq, int Hkv, int D, float scale, int causal, int window,
+                           float softcap, const float* sinks, int* status, void* stream) {
   using namespace edl;
   if (B <= 0 || max_q <= 0 || total_q <= 0) return 0;
   const int G = Hq / Hkv;
@@ -516,7 +516,7 @@ EDL_HOST_API int edl_attn_paged(const void* q, const void* k_pages, const void* 
   AttnFwdParams p;
   p.o = reinterpret_cast<__nv_bfloat16*>(o);
   p.ldo = ldo;
-  p.lse = nullptr;
+  p.lse = lse;
   p.cu_q = cu_q;
   p.cu_k = nullptr;
   p.sinks = sinks;
@@ -539,4 +539,25 @@ EDL_HOST_API int edl_attn_paged(const void* q, const void* k_pages, const void* 
   const long long total_k = num_pages * 128;
   if (D == 128) return launch_fwd<128>(q, k_pages, v_pages, ldq, ld_page, ld_page, total_q, total_k, p, s);
   return launch_fwd<64>(q, k_pages, v_pages, ldq, ld_page, ld_page, total_q, total_k, p, s);
+}
+
+EDL_HOST_API int edl_attn_paged(const void* q, const void* k_pages, const void* v_pages, void* o, long long ldq,
+                                long long ld_page, long long ldo, const int* cu_q, const int* kv_lens,
+                                const int* page_table, int pt_stride, int B, int max_q, long long total_q,
+                                long long num_pages, int Hq, int Hkv, int D, float scale, int causal, int window,
+                                float softcap, const float* sinks, int* status, void* stream) {
+  return attn_paged_impl(q, k_pages, v_pages, o, nullptr, ldq, ld_page, ldo, cu_q, kv_lens, page_table, pt_stride, B,
+                         max_q, total_q, num_pages, Hq, Hkv, D, scale, causal, window, softcap, sinks, status, stream);
+}
+
+// Same, also writing lse [Hq, total_q] (natural log of the softmax denominator; -inf for a row without keys):
+// the partial results of split-KV decode and of context-parallel attention are merged from (o, lse) pairs.
+EDL_HOST_API int edl_attn_paged_lse(const void* q, const void* k_pages, const void* v_pages, void* o, float* lse,
+                                    long long ldq, long long ld_page, long long ldo, const int* cu_q,
+                                    const int* kv_lens, const int* page_table, int pt_stride, int B, int max_q,
+                                    long long total_q, long long num_pages, int Hq, int Hkv, int D, float scale,
+                                    int causal, int window, float softcap, const float* sinks, int* status,
+                                    void* stream) {
+  return attn_paged_impl(q, k_pages, v_pages, o, lse, ldq, ld_page, ldo, cu_q, kv_lens, page_table, pt_stride, B,
+                         max_q, total_q, num_pages, Hq, Hkv, D, scale, causal, window, softcap, sinks, status, stream);
 }

@@ -1,0 +1,208 @@
+// Weight-only quantised linears: code-book dequantisation and a skinny fused dequant-GEMV.
+//
+// Every supported format (int8, affine 4/8-bit, nf4, mxfp4, nvfp4, mxfp8, nvfp8) is stored the same way:
+//   codes  [N, K * bits / 8] uint8   (4-bit codes: two per byte, low nibble = even k)
+//   scales [N, K / group] bf16       (already decoded from e8m0 / e4m3 where the format uses those)
+//   zeros  [N, K / group] bf16       (affine formats only, else null)
+//   lut    float[1 << bits]          (code -> value before scaling: the format's number system)
+// so that  w[n, k] = lut[code[n, k]] * scales[n, k / group] (+ zeros[n, k / group]).
+//
+//   edl_dequant_bf16 : materialises bf16 weights (prefill / training path, followed by the tcgen05 GEMM).
+//   edl_qgemv        : y[M, N] = x[M, K] * W^T for M <= 8 (decode steps): every warp streams four weight rows of
+//                      packed codes with 16-byte loads, dequantises in registers and keeps M x 4 fp32 accumulators,
+//                      so the weights cross HBM once at 4 or 8 bits per value.
+// Counterpart in the reference: ejkernel quantized_matmul reached from
+// easydel/layers/linears/_linear_quantized.py:1030-1108.
+#include "common.cuh"
+
+namespace edl {
+namespace {
+
+constexpr int QG_THREADS = 256;
+constexpr int QG_ROWS = 4;   // weight rows per warp
+constexpr int QG_MAX_M = 8;
+
+__global__ void dequant_kernel(const uint8_t* __restrict__ codes, const __nv_bfloat16* __restrict__ scales,
+                               const __nv_bfloat16* __restrict__ zeros, const float* __restrict__ lut, int bits,
+                               int N, int K, int group, __nv_bfloat16* __restrict__ out, long long ldo) {
+  __shared__ float s_lut[256];
+  for (int i = threadIdx.x; i < (1 << bits); i += blockDim.x) s_lut[i] = lut[i];
+  __syncthreads();
+  const int per16 = bits == 4 ? 32 : 16;               // weights per 16 bytes of codes
+  const long long vec_per_row = K / per16;
+  const long long total = (long long)N * vec_per_row;
+  const int groups = K / group;
+  const long long row_bytes = (long long)K * bits / 8;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total;
+       v += (long long)gridDim.x * blockDim.x) {
+    const long long n = v / vec_per_row;
+    const int k0 = (int)(v - n * vec_per_row) * per16;
+    const uint4 q = *reinterpret_cast<const uint4*>(codes + n * row_bytes + (long long)k0 * bits / 8);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    __nv_bfloat16* o = out + n * ldo + k0;
+    float sc = 0.f, zr = 0.f;
+    int cur_g = -1;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (i >= per16) break;
+      const int k = k0 + i;
+      const int g = k / group;
+      if (g != cur_g) {
+        cur_g = g;
+        sc = __bfloat162float(scales[n * groups + g]);
+        zr = zeros ? __bfloat162float(zeros[n * groups + g]) : 0.f;
+      }
+      const uint32_t code = bits == 4 ? (w[i >> 3] >> ((i & 7) * 4)) & 0xF : (w[i >> 2] >> ((i & 3) * 8)) & 0xFF;
+      o[i] = __float2bfloat16(s_lut[code] * sc + zr);
+    }
+  }
+}
+
+template <int M>
+__global__ void __launch_bounds__(QG_THREADS)
+qgemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* __restrict__ codes,
+             const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ zeros,
+             const float* __restrict__ lut, int bits, int N, int K, int group, __nv_bfloat16* __restrict__ out,
+             long long ldo, const __nv_bfloat16* __restrict__ bias) {
+  __shared__ float s_lut[256];
+  for (int i = threadIdx.x; i < (1 << bits); i += blockDim.x) s_lut[i] = lut[i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = QG_THREADS / 32;
+  const int per16 = bits == 4 ? 32 : 16;
+  const int groups = K / group;
+  const long long row_bytes = (long long)K * bits / 8;
+  const int nvec = K / per16;
+  for (int n0 = (blockIdx.x * warps + warp) * QG_ROWS; n0 < N; n0 += gridDim.x * warps * QG_ROWS) {
+    float acc[M][QG_ROWS];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int r = 0; r < QG_ROWS; ++r) acc[m][r] = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      const int k0 = v * per16;
+      uint4 q[QG_ROWS];
+#pragma unroll
+      for (int r = 0; r < QG_ROWS; ++r)
+        q[r] = (n0 + r < N) ? *reinterpret_cast<const uint4*>(codes + (long long)(n0 + r) * row_bytes + (long long)k0 * bits / 8)
+                            : make_uint4(0, 0, 0, 0);
+      // a group never straddles a 16-byte code vector when group >= weights per vector (checked on the host)
+      const int g = k0 / group;
+      float sc[QG_ROWS], zr[QG_ROWS];
+#pragma unroll
+      for (int r = 0; r < QG_ROWS; ++r) {
+        const bool ok = n0 + r < N;
+        sc[r] = ok ? __bfloat162float(scales[(long long)(n0 + r) * groups + g]) : 0.f;
+        zr[r] = (ok && zeros) ? __bfloat162float(zeros[(long long)(n0 + r) * groups + g]) : 0.f;
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {          // four 32-bit words of codes = 8 (4-bit) or 4 (8-bit) weights each
+        const int nw = bits == 4 ? 8 : 4;
+        float xv[M][8];
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const __nv_bfloat16* xp = x + m * ldx + k0 + c * nw;
+          if (bits == 4) {
+            const uint4 xx = *reinterpret_cast<const uint4*>(xp);
+            float2 f;
+            f = unpack_bf16x2(xx.x); xv[m][0] = f.x; xv[m][1] = f.y;
+            f = unpack_bf16x2(xx.y); xv[m][2] = f.x; xv[m][3] = f.y;
+            f = unpack_bf16x2(xx.z); xv[m][4] = f.x; xv[m][5] = f.y;
+            f = unpack_bf16x2(xx.w); xv[m][6] = f.x; xv[m][7] = f.y;
+          } else {
+            const uint2 xx = *reinterpret_cast<const uint2*>(xp);
+            float2 f;
+            f = unpack_bf16x2(xx.x); xv[m][0] = f.x; xv[m][1] = f.y;
+            f = unpack_bf16x2(xx.y); xv[m][2] = f.x; xv[m][3] = f.y;
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < QG_ROWS; ++r) {
+          const uint32_t word = c == 0 ? q[r].x : c == 1 ? q[r].y : c == 2 ? q[r].z : q[r].w;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (i >= nw) break;
+            const uint32_t code = bits == 4 ? (word >> (i * 4)) & 0xF : (word >> (i * 8)) & 0xFF;
+            const float wv = s_lut[code] * sc[r] + zr[r];
+#pragma unroll
+            for (int m = 0; m < M; ++m) acc[m][r] += wv * xv[m][i];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int r = 0; r < QG_ROWS; ++r) {
+        float s = warp_sum(acc[m][r]);
+        if (lane == 0 && n0 + r < N) {
+          if (bias) s += __bfloat162float(bias[n0 + r]);
+          out[m * ldo + n0 + r] = __float2bfloat16(s);
+        }
+      }
+  }
+}
+
+}  // namespace
+}  // namespace edl
+
+using namespace edl;
+
+static int check_quant_args(const char* who, int bits, int N, int K, int group) {
+  const int per16 = bits == 4 ? 32 : 16;
+  if ((bits != 4 && bits != 8) || N <= 0 || K <= 0 || group <= 0 || K % per16 || K % group ||
+      (group % per16 && per16 % group)) {
+    set_last_error("%s: bits must be 4 or 8, K a multiple of %d and of the group size (bits=%d K=%d group=%d)", who,
+                   per16, bits, K, group);
+    return -1;
+  }
+  return 0;
+}
+
+EDL_HOST_API int edl_dequant_bf16(const void* codes, const void* scales, const void* zeros, const float* lut, int bits,
+                                  int N, int K, int group, void* out, long long ldo, void* stream) {
+  if (check_quant_args("edl_dequant_bf16", bits, N, K, group)) return -1;
+  const long long total = (long long)N * (K / (bits == 4 ? 32 : 16));
+  long long blocks = (total + 255) / 256, cap = (long long)sm_count() * 8;
+  dequant_kernel<<<(int)(blocks > cap ? cap : blocks), 256, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)codes, (const __nv_bfloat16*)scales, (const __nv_bfloat16*)zeros, lut, bits, N, K, group,
+      (__nv_bfloat16*)out, ldo);
+  return check_cuda(cudaGetLastError(), "dequant launch");
+}
+
+// x [M, K] bf16 (row pitch ldx, multiple of 8), M <= 8; out [M, N] bf16. The group size must be a multiple of the
+// number of weights in one 16-byte code vector (32 for 4-bit, 16 for 8-bit).
+EDL_HOST_API int edl_qgemv(const void* x, long long ldx, const void* codes, const void* scales, const void* zeros,
+                           const float* lut, int bits, int M, int N, int K, int group, void* out, long long ldo,
+                           const void* bias, void* stream) {
+  if (check_quant_args("edl_qgemv", bits, N, K, group)) return -1;
+  const int per16 = bits == 4 ? 32 : 16;
+  if (M < 1 || M > QG_MAX_M || (ldx & 7) || group % per16) {
+    set_last_error("edl_qgemv: M must be in [1, %d], ldx a multiple of 8 and group a multiple of %d", QG_MAX_M, per16);
+    return -1;
+  }
+  const int rows_per_cta = (QG_THREADS / 32) * QG_ROWS;
+  int blocks = (N + rows_per_cta - 1) / rows_per_cta;
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t s = (cudaStream_t)stream;
+#define EDL_QGEMV_CASE(MM)                                                                                          \
+  case MM:                                                                                                          \
+    qgemv_kernel<MM><<<blocks, QG_THREADS, 0, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)codes,             \
+                                                   (const __nv_bfloat16*)scales, (const __nv_bfloat16*)zeros, lut, \
+                                                   bits, N, K, group, (__nv_bfloat16*)out, ldo,                     \
+                                                   (const __nv_bfloat16*)bias);                                     \
+    break;
+  switch (M) {
+    EDL_QGEMV_CASE(1)
+    EDL_QGEMV_CASE(2)
+    EDL_QGEMV_CASE(3)
+    EDL_QGEMV_CASE(4)
+    EDL_QGEMV_CASE(5)
+    EDL_QGEMV_CASE(6)
+    EDL_QGEMV_CASE(7)
+    EDL_QGEMV_CASE(8)
+  }
+#undef EDL_QGEMV_CASE
+  return check_cuda(cudaGetLastError(), "qgemv launch");
+}

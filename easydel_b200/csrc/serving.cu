@@ -108,6 +108,47 @@ sample_kernel(const void* __restrict__ logits, int is_f32, long long ld, int V, 
   const bool greedy = temp <= 0.f || k == 1;
   if (k <= 0 || k > MAX_CAND) k = MAX_CAND;
   const int rounds = greedy ? 1 : k;
+  if (greedy && !pen && !is_f32 && (V & 7) == 0 && (ld & 7) == 0) {
+    // Greedy rows without penalties: one pass of 16-byte loads computes the arg-max and, online, the
+    // log-sum-exp that the reported log-probability needs.
+    const uint4* rowp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(logits) + row * ld);
+    ArgMax best{-INFINITY, 0x7fffffff};
+    float m = -INFINITY, ssum = 0.f;
+    const int nvec = V >> 3;
+    for (int i = threadIdx.x; i < nvec; i += SAMP_THREADS) {
+      const uint4 q = rowp[i];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+      float z[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(w[j]);
+        z[2 * j] = f.x;
+        z[2 * j + 1] = f.y;
+      }
+      float cm = z[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) cm = fmaxf(cm, z[j]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (z[j] > best.v) best = ArgMax{z[j], i * 8 + j};  // ascending index: the first maximum wins
+      if (out_logprob) {
+        const float nm = fmaxf(m, cm);
+        float add = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) add += __expf(z[j] - nm);
+        ssum = ssum * __expf(m - nm) + add;
+        m = nm;
+      }
+    }
+    best = block_argmax(best, red);
+    if (out_logprob) {
+      const float gm = block_max(m, s_lse_parts);
+      const float tot = block_sum(ssum * __expf(m - gm), s_lse_parts);
+      if (threadIdx.x == 0) out_logprob[row] = best.v - (gm + __logf(tot));
+    }
+    if (threadIdx.x == 0) out[row] = best.i;
+    return;
+  }
   // log-sum-exp of the (penalised, temperature-scaled) distribution for the reported log-prob
   float lmax = -INFINITY;
   for (int v = threadIdx.x; v < V; v += SAMP_THREADS) {

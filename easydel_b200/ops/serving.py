@@ -9,6 +9,9 @@ import torch
 from . import _lib
 
 vp, i32, i64, f32 = _lib.vp, _lib.i32, _lib.i64, _lib.f32
+_lib.register("edl_attn_paged_lse", i32, [vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, vp, i32, i32, i32, i64, i64, i32,
+                                          i32, i32, _lib.f32, i32, i32, _lib.f32, vp, vp, vp])
+_lib.register("edl_attn_combine", i32, [vp, i64, vp, i32, i32, i32, i32, vp, vp, vp, vp])
 _lib.register("edl_attn_paged", i32, [vp, vp, vp, vp, i64, i64, i64, vp, vp, vp, i32, i32, i32, i64, i64, i32, i32,
                                       i32, f32, i32, i32, f32, vp, vp, vp])
 _lib.register("edl_paged_kv_append", i32, [vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, i64, vp, vp])
@@ -65,6 +68,66 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         return out
     return paged_attention_reference(q, k_pages, v_pages, cu_q, kv_lens, page_table, scale=scale, causal=causal,
                                      window=window, softcap=softcap, sinks=sinks)
+
+
+def attn_combine(o_parts: torch.Tensor, lse_parts: torch.Tensor, sinks=None, want_lse: bool = False):
+    """Merges ``o_parts [S, R, H, D]`` with ``lse_parts [S, H, R]`` (disjoint key ranges) into ``[R, H, D]``."""
+    S_, R_, H, D = o_parts.shape
+    if o_parts.is_cuda:
+        assert o_parts.stride(3) == 1 and o_parts.stride(2) == D and o_parts.stride(1) == H * D
+        out = torch.empty(R_, H, D, dtype=o_parts.dtype, device=o_parts.device)
+        lse = torch.empty(H, R_, dtype=torch.float32, device=o_parts.device) if want_lse else None
+        _lib.call("edl_attn_combine", o_parts.data_ptr(), o_parts.stride(0), lse_parts.contiguous().data_ptr(), S_, R_,
+                  H, D, _lib.ptr(sinks), out.data_ptr(), _lib.ptr(lse), _lib.stream_ptr())
+        return (out, lse) if want_lse else out
+    l = lse_parts.float().permute(0, 2, 1)                      # [S, R, H]
+    if sinks is not None:
+        l_all = torch.cat([l, sinks.float()[None, None].expand(1, R_, H)], 0)
+    else:
+        l_all = l
+    tot = torch.logsumexp(l_all, 0)                             # [R, H]
+    w = torch.exp(l - tot[None]).nan_to_num(0.0)
+    out = (w[..., None] * o_parts.float()).sum(0).to(o_parts.dtype)
+    return (out, tot.t().contiguous()) if want_lse else out
+
+
+def paged_attention_splitkv(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_lens: torch.Tensor,
+                            page_table: torch.Tensor, num_splits: int, *, scale: float | None = None,
+                            softcap: float = 0.0, sinks=None) -> torch.Tensor:
+    """Decode attention (one query token per sequence) with every sequence's keys cut into ``num_splits`` page
+    ranges that run as independent rows of the paged kernel and are merged by :func:`attn_combine`.
+
+    With few sequences and long contexts the plain kernel has ``B * Hkv`` CTAs walking thousands of keys each;
+    splitting gives the idle SMs work. q ``[B, Hq, D]``; the page table's width is padded to a multiple of
+    ``num_splits`` pages so that each split is a strided view of it.
+    """
+    B, Hq, D = q.shape
+    S_ = int(num_splits)
+    MP = page_table.shape[1]
+    cp = (MP + S_ - 1) // S_
+    if cp * S_ != MP:
+        page_table = torch.nn.functional.pad(page_table, (0, cp * S_ - MP))
+    pt = page_table.contiguous().view(B * S_, cp)
+    chunk = cp * PAGE_SIZE
+    starts = torch.arange(S_, device=q.device, dtype=torch.int32) * chunk
+    lens = (kv_lens.to(torch.int32)[:, None] - starts[None]).clamp(0, chunk).reshape(-1).contiguous()
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        o = paged_attention_reference(q, k_pages, v_pages, torch.arange(B + 1, dtype=torch.int32), kv_lens,
+                                      page_table[:, :MP], scale=scale, causal=True, softcap=softcap, sinks=sinks)
+        return o
+    qr = q.repeat_interleave(S_, 0).contiguous()
+    cu = torch.arange(B * S_ + 1, device=q.device, dtype=torch.int32)
+    o_parts = torch.empty(B * S_, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(Hq, B * S_, dtype=torch.float32, device=q.device)
+    _lib.call("edl_attn_paged_lse", qr.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), o_parts.data_ptr(),
+              lse.data_ptr(), qr.stride(0), k_pages.stride(1), o_parts.stride(0), cu.data_ptr(), lens.data_ptr(),
+              pt.data_ptr(), pt.stride(0), B * S_, 1, B * S_, k_pages.shape[0], Hq, k_pages.shape[2], D, float(scale),
+              1, 0, float(softcap or 0.0), None, _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
+    # [B*S, Hq, D] -> [S, B, Hq, D]; lse [Hq, B*S] -> [S, Hq, B]
+    op = o_parts.view(B, S_, Hq, D).transpose(0, 1).contiguous()
+    lp = lse.view(Hq, B, S_).permute(2, 0, 1).contiguous()
+    return attn_combine(op, lp, sinks)
 
 
 def paged_attention_reference(q, k_pages, v_pages, cu_q, kv_lens, page_table, *, scale=None, causal=True, window=0,

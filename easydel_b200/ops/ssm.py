@@ -1,0 +1,213 @@
+"""State-space and linear-attention recurrences: Mamba-1 selective scan, Mamba-2 SSD, gated delta rule, KDA and
+the ragged causal conv1d in front of them (``csrc/ssm.cu``).
+
+Every op has a PyTorch reference (also its autograd path: training differentiates the reference, chunk by chunk,
+while inference and evaluation call the CUDA recurrences). Sequences are packed on the token axis with
+``cu_seqlens``; ``state`` tensors are fp32 and updated in place.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as tF
+
+from . import _lib
+
+vp, i32, f32 = _lib.vp, _lib.i32, _lib.f32
+_lib.register("edl_selective_scan", i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, vp, vp, vp])
+_lib.register("edl_ssd_scan", i32, [vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp])
+_lib.register("edl_delta_rule", i32, [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp, vp])
+_lib.register("edl_ragged_conv1d", i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp])
+
+
+def _cu(total: int, cu_seqlens, device):
+    if cu_seqlens is None:
+        return torch.tensor([0, total], dtype=torch.int32, device=device)
+    return cu_seqlens.to(device=device, dtype=torch.int32)
+
+
+def _use_kernel(*ts) -> bool:
+    t = ts[0]
+    return t.is_cuda and _lib.available() and not (torch.is_grad_enabled() and any(
+        x is not None and x.requires_grad for x in ts))
+
+
+# ----------------------------------------------------------------------------------------- Mamba-1
+def selective_scan_reference(u, delta, A, B, C, D=None, z=None, dt_bias=None, softplus=True, cu_seqlens=None,
+                             state=None):
+    total, Dm = u.shape
+    N = A.shape[1]
+    cu = _cu(total, cu_seqlens, u.device).tolist()
+    dt = delta.float() + (dt_bias.float() if dt_bias is not None else 0.0)
+    if softplus:
+        dt = tF.softplus(dt)
+    ys = []
+    new_states = []
+    for b in range(len(cu) - 1):
+        h = state[b].float().clone() if state is not None else torch.zeros(Dm, N, device=u.device)
+        for t in range(cu[b], cu[b + 1]):
+            dA = torch.exp(dt[t][:, None] * A.float())
+            h = dA * h + dt[t][:, None] * B[t].float()[None] * u[t].float()[:, None]
+            y = (h * C[t].float()[None]).sum(-1)
+            if D is not None:
+                y = y + D.float() * u[t].float()
+            if z is not None:
+                y = y * tF.silu(z[t].float())
+            ys.append(y)
+        new_states.append(h)
+    if state is not None:
+        with torch.no_grad():
+            state.copy_(torch.stack([s.detach() for s in new_states]))
+    return torch.stack(ys).to(u.dtype)
+
+
+def selective_scan(u, delta, A, B, C, D=None, z=None, dt_bias=None, softplus=True, cu_seqlens=None, state=None):
+    """u, delta, z ``[total, D]``; A ``[D, N]`` (negative); B, C ``[total, N]``; state ``[nseq, D, N]`` fp32."""
+    if _use_kernel(u, delta, A, B, C, D, z) and A.shape[1] in (8, 16, 32, 64) and u.dtype == torch.bfloat16:
+        total, Dm = u.shape
+        cu = _cu(total, cu_seqlens, u.device)
+        y = torch.empty_like(u)
+        c = lambda t: None if t is None else t.contiguous()  # noqa: E731
+        _lib.call("edl_selective_scan", c(u).data_ptr(), c(delta).data_ptr(), A.float().contiguous().data_ptr(),
+                  c(B).data_ptr(), c(C).data_ptr(), _lib.ptr(None if D is None else D.float().contiguous()),
+                  _lib.ptr(c(z)), _lib.ptr(None if dt_bias is None else dt_bias.float().contiguous()), int(softplus),
+                  cu.data_ptr(), cu.numel() - 1, Dm, A.shape[1], _lib.ptr(state), y.data_ptr(), _lib.stream_ptr())
+        return y
+    return selective_scan_reference(u, delta, A, B, C, D, z, dt_bias, softplus, cu_seqlens, state)
+
+
+# ----------------------------------------------------------------------------------------- Mamba-2
+def ssd_scan_reference(x, dt, A, B, C, D=None, dt_bias=None, softplus=True, cu_seqlens=None, state=None):
+    total, H, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    cu = _cu(total, cu_seqlens, x.device).tolist()
+    d = dt.float() + (dt_bias.float() if dt_bias is not None else 0.0)
+    if softplus:
+        d = tF.softplus(d)
+    rep = H // G
+    ys, new_states = [], []
+    for b in range(len(cu) - 1):
+        s = state[b].float().clone() if state is not None else torch.zeros(H, P, N, device=x.device)
+        for t in range(cu[b], cu[b + 1]):
+            decay = torch.exp(d[t] * A.float())                                   # [H]
+            Bt = B[t].float().repeat_interleave(rep, 0)                            # [H, N]
+            Ct = C[t].float().repeat_interleave(rep, 0)
+            s = decay[:, None, None] * s + (d[t][:, None] * x[t].float())[:, :, None] * Bt[:, None, :]
+            y = (s * Ct[:, None, :]).sum(-1)
+            if D is not None:
+                y = y + D.float()[:, None] * x[t].float()
+            ys.append(y)
+        new_states.append(s)
+    if state is not None:
+        with torch.no_grad():
+            state.copy_(torch.stack([s.detach() for s in new_states]))
+    return torch.stack(ys).to(x.dtype)
+
+
+def ssd_scan(x, dt, A, B, C, D=None, dt_bias=None, softplus=True, cu_seqlens=None, state=None):
+    """x ``[total, H, P]``; dt ``[total, H]``; A ``[H]``; B, C ``[total, G, N]``; state ``[nseq, H, P, N]`` fp32."""
+    if _use_kernel(x, dt, A, B, C, D) and B.shape[2] in (16, 32, 64, 128) and x.dtype == torch.bfloat16 \
+            and x.shape[2] <= 256:
+        total, H, P = x.shape
+        cu = _cu(total, cu_seqlens, x.device)
+        y = torch.empty_like(x)
+        _lib.call("edl_ssd_scan", x.contiguous().data_ptr(), dt.contiguous().data_ptr(),
+                  A.float().contiguous().data_ptr(), B.contiguous().data_ptr(), C.contiguous().data_ptr(),
+                  _lib.ptr(None if D is None else D.float().contiguous()),
+                  _lib.ptr(None if dt_bias is None else dt_bias.float().contiguous()), int(softplus), cu.data_ptr(),
+                  cu.numel() - 1, H, P, B.shape[1], B.shape[2], _lib.ptr(state), y.data_ptr(), _lib.stream_ptr())
+        return y
+    return ssd_scan_reference(x, dt, A, B, C, D, dt_bias, softplus, cu_seqlens, state)
+
+
+# ----------------------------------------------------------------------------------------- delta rules
+def delta_rule_reference(q, k, v, g=None, beta=None, scale=None, cu_seqlens=None, state=None):
+    total, H, DK = q.shape
+    DV = v.shape[-1]
+    scale = scale if scale is not None else DK ** -0.5
+    cu = _cu(total, cu_seqlens, q.device).tolist()
+    outs, new_states = [], []
+    for b in range(len(cu) - 1):
+        S = state[b].float().clone() if state is not None else torch.zeros(H, DK, DV, device=q.device)
+        for t in range(cu[b], cu[b + 1]):
+            if g is not None:
+                gt = torch.exp(g[t].float())
+                S = S * (gt[:, :, None] if gt.dim() == 2 else gt[:, None, None])
+            kt, qt, vt = k[t].float(), q[t].float(), v[t].float()
+            r = vt - torch.einsum("hk,hkv->hv", kt, S)
+            if beta is not None:
+                r = r * beta[t].float()[:, None]
+            S = S + kt[:, :, None] * r[:, None, :]
+            outs.append(torch.einsum("hk,hkv->hv", qt, S) * scale)
+        new_states.append(S)
+    if state is not None:
+        with torch.no_grad():
+            state.copy_(torch.stack([s.detach() for s in new_states]))
+    return torch.stack(outs).to(q.dtype)
+
+
+def gated_delta_rule(q, k, v, g=None, beta=None, scale=None, cu_seqlens=None, state=None):
+    """q, k ``[total, H, DK]``; v ``[total, H, DV]``; g ``[total, H]`` log-decay (or ``[total, H, DK]`` for KDA);
+    beta ``[total, H]``; state ``[nseq, H, DK, DV]`` fp32. Returns ``[total, H, DV]``."""
+    DK, DV = q.shape[-1], v.shape[-1]
+    if _use_kernel(q, k, v, g, beta) and DK in (32, 64, 128) and DV <= 256 and q.dtype == torch.bfloat16:
+        total, H, _ = q.shape
+        cu = _cu(total, cu_seqlens, q.device)
+        o = torch.empty(total, H, DV, dtype=q.dtype, device=q.device)
+        per_channel = int(g is not None and g.dim() == 3)
+        _lib.call("edl_delta_rule", q.contiguous().data_ptr(), k.contiguous().data_ptr(), v.contiguous().data_ptr(),
+                  _lib.ptr(None if g is None else g.float().contiguous()),
+                  _lib.ptr(None if beta is None else beta.to(torch.bfloat16).contiguous()), per_channel,
+                  cu.data_ptr(), cu.numel() - 1, H, DK, DV, float(scale if scale is not None else DK ** -0.5),
+                  _lib.ptr(state), o.data_ptr(), _lib.stream_ptr())
+        return o
+    return delta_rule_reference(q, k, v, g, beta, scale, cu_seqlens, state)
+
+
+kda = gated_delta_rule   # kernel delta attention: the same recurrence with a per-channel gate ``g [total, H, DK]``
+
+
+# ----------------------------------------------------------------------------------------- conv1d
+def ragged_conv1d_reference(x, w, bias=None, cu_seqlens=None, activation: str | None = "silu", conv_state=None):
+    total, Cn = x.shape
+    W = w.shape[1]
+    cu = _cu(total, cu_seqlens, x.device).tolist()
+    outs = []
+    for b in range(len(cu) - 1):
+        seg = x[cu[b]:cu[b + 1]].float()
+        left = conv_state[b].float() if conv_state is not None else torch.zeros(W - 1, Cn, device=x.device)
+        padded = torch.cat([left, seg], 0)
+        y = sum(padded[j:j + seg.shape[0]] * w[:, j].float()[None] for j in range(W))
+        if bias is not None:
+            y = y + bias.float()
+        outs.append(tF.silu(y) if activation in ("silu", "swish") else y)
+        if conv_state is not None and seg.shape[0]:
+            with torch.no_grad():
+                conv_state[b].copy_(padded[-(W - 1):].to(conv_state.dtype))
+    return torch.cat(outs).to(x.dtype)
+
+
+def ragged_conv1d(x, w, bias=None, cu_seqlens=None, activation: str | None = "silu", conv_state=None):
+    """Depth-wise causal conv over packed sequences. x ``[total, C]``; w ``[C, W]``; conv_state ``[nseq, W-1, C]``
+    holds the rows before each sequence and receives its last ``W-1`` rows."""
+    if _use_kernel(x, w, bias) and x.dtype == torch.bfloat16:
+        total, Cn = x.shape
+        cu = _cu(total, cu_seqlens, x.device)
+        lens = (cu[1:] - cu[:-1]).long()
+        seq_of = torch.repeat_interleave(torch.arange(cu.numel() - 1, device=x.device, dtype=torch.int32), lens)
+        y = torch.empty_like(x)
+        xs = x.contiguous()
+        _lib.call("edl_ragged_conv1d", xs.data_ptr(), w.to(torch.bfloat16).contiguous().data_ptr(),
+                  _lib.ptr(None if bias is None else bias.to(torch.bfloat16).contiguous()), cu.data_ptr(),
+                  seq_of.contiguous().data_ptr(), total, Cn, w.shape[1],
+                  int(activation in ("silu", "swish")), _lib.ptr(conv_state), y.data_ptr(), _lib.stream_ptr())
+        if conv_state is not None:
+            W = w.shape[1]
+            with torch.no_grad():     # roll the window: last W-1 rows of (old state ++ sequence)
+                cul = cu.tolist()
+                for b in range(len(cul) - 1):
+                    seg = xs[cul[b]:cul[b + 1]]
+                    if seg.shape[0]:
+                        conv_state[b].copy_(torch.cat([conv_state[b], seg], 0)[-(W - 1):])
+        return y
+    return ragged_conv1d_reference(x, w, bias, cu_seqlens, activation, conv_state)

@@ -105,3 +105,50 @@ def test_sampler_greedy_penalties_and_topk():
     a, _ = S.sample(logits, temperature=temp, top_k=topk, seeds=seeds, steps=steps)
     b, _ = S.sample(logits, temperature=temp, top_k=topk, seeds=seeds, steps=steps)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("splits", [2, 4, 7])
+def test_split_kv_decode_matches_unsplit(splits):
+    """Long contexts cut into page ranges and merged by log-sum-exp give the same output as one pass."""
+    from easydel_b200.ops import serving as S
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    B, Hq, Hkv, D, P = 3, 8, 2, 128, 64
+    k_pages = torch.randn(P, 128, Hkv, D, device=dev, dtype=torch.bfloat16)
+    v_pages = torch.randn(P, 128, Hkv, D, device=dev, dtype=torch.bfloat16)
+    kv_lens = torch.tensor([2000, 130, 901], dtype=torch.int32, device=dev)
+    table = torch.zeros(B, 16, dtype=torch.int32, device=dev)
+    perm = torch.randperm(P - 1, device=dev)[:48].to(torch.int32) + 1
+    table[:, :16] = perm.view(3, 16)
+    q = torch.randn(B, Hq, D, device=dev, dtype=torch.bfloat16)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
+    sinks = torch.randn(Hq, device=dev)
+    for sk in (None, sinks):
+        ref = S.paged_attention_reference(q, k_pages, v_pages, cu, kv_lens, table, causal=True, sinks=sk)
+        got = S.paged_attention_splitkv(q, k_pages, v_pages, kv_lens, table, splits, sinks=sk)
+        assert (got.float() - ref.float()).abs().max() < 2e-2
+
+
+def test_attn_combine_matches_reference():
+    from easydel_b200.ops import serving as S
+
+    torch.manual_seed(1)
+    o = torch.randn(3, 5, 4, 64, device="cuda", dtype=torch.bfloat16)
+    lse = torch.randn(3, 4, 5, device="cuda")
+    lse[1, :, 2] = float("-inf")
+    got, l = S.attn_combine(o, lse, want_lse=True)
+    ref, lr = S.attn_combine(o.cpu(), lse.cpu(), want_lse=True)
+    assert (got.float().cpu() - ref.float()).abs().max() < 2e-2 and (l.cpu() - lr).abs().max() < 1e-4
+
+
+def test_greedy_sampler_fast_path_matches_argmax():
+    from easydel_b200.ops import serving as S
+
+    torch.manual_seed(2)
+    logits = torch.randn(37, 128256, device="cuda", dtype=torch.bfloat16)
+    tok, lp = S.sample(logits, want_logprob=True)
+    ref = logits.float().argmax(-1)
+    assert torch.equal(tok.long(), ref)
+    ref_lp = torch.log_softmax(logits.float(), -1).gather(-1, ref[:, None])[:, 0]
+    assert (lp - ref_lp).abs().max() < 1e-3

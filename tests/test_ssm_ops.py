@@ -1,0 +1,94 @@
+"""Recurrent ops: the CUDA scans agree with the step-by-step PyTorch recurrences, including carried state."""
+
+import pytest
+import torch
+
+from easydel_b200.ops import ssm
+
+
+def _close(a, b, tol=3e-2):
+    return (a.float() - b.float()).abs().max() <= tol * b.float().abs().max().clamp_min(1.0)
+
+
+def test_references_carry_state_across_calls():
+    torch.manual_seed(0)
+    T, D, N = 12, 6, 4
+    u, delta = torch.randn(T, D), torch.randn(T, D)
+    A = -torch.rand(D, N)
+    B, C = torch.randn(T, N), torch.randn(T, N)
+    full = ssm.selective_scan_reference(u, delta, A, B, C)
+    st = torch.zeros(1, D, N)
+    a = ssm.selective_scan_reference(u[:7], delta[:7], A, B[:7], C[:7], state=st)
+    b = ssm.selective_scan_reference(u[7:], delta[7:], A, B[7:], C[7:], state=st)
+    assert torch.allclose(torch.cat([a, b]), full, atol=1e-5)
+    q, k, v = torch.randn(T, 2, 8), torch.randn(T, 2, 8), torch.randn(T, 2, 5)
+    g, beta = -torch.rand(T, 2), torch.rand(T, 2)
+    full = ssm.delta_rule_reference(q, k, v, g, beta)
+    st = torch.zeros(1, 2, 8, 5)
+    parts = torch.cat([ssm.delta_rule_reference(q[:5], k[:5], v[:5], g[:5], beta[:5], state=st),
+                       ssm.delta_rule_reference(q[5:], k[5:], v[5:], g[5:], beta[5:], state=st)])
+    assert torch.allclose(parts, full, atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_selective_scan_cuda():
+    torch.manual_seed(1)
+    dev, T, D, N = "cuda", 70, 192, 16
+    cu = torch.tensor([0, 30, 70], dtype=torch.int32, device=dev)
+    bf = lambda *s: torch.randn(*s, device=dev).to(torch.bfloat16)  # noqa: E731
+    u, delta, z, B, C = bf(T, D), bf(T, D), bf(T, D), bf(T, N), bf(T, N)
+    A, Dv, bias = -torch.rand(D, N, device=dev), torch.randn(D, device=dev), torch.randn(D, device=dev)
+    s1, s2 = torch.zeros(2, D, N, device=dev), torch.zeros(2, D, N, device=dev)
+    with torch.no_grad():
+        got = ssm.selective_scan(u, delta, A, B, C, Dv, z, bias, True, cu, s1)
+        ref = ssm.selective_scan_reference(u, delta, A, B, C, Dv, z, bias, True, cu, s2)
+    assert _close(got, ref) and _close(s1, s2)
+
+
+@pytest.mark.gpu
+def test_ssd_scan_cuda():
+    torch.manual_seed(2)
+    dev, T, H, P, G, N = "cuda", 40, 4, 64, 2, 128
+    cu = torch.tensor([0, 17, 40], dtype=torch.int32, device=dev)
+    bf = lambda *s: torch.randn(*s, device=dev).to(torch.bfloat16)  # noqa: E731
+    x, dt, B, C = bf(T, H, P), bf(T, H), bf(T, G, N) * 0.3, bf(T, G, N) * 0.3
+    A, Dv = -torch.rand(H, device=dev), torch.randn(H, device=dev)
+    s1, s2 = torch.zeros(2, H, P, N, device=dev), torch.zeros(2, H, P, N, device=dev)
+    with torch.no_grad():
+        got = ssm.ssd_scan(x, dt, A, B, C, Dv, None, True, cu, s1)
+        ref = ssm.ssd_scan_reference(x, dt, A, B, C, Dv, None, True, cu, s2)
+    assert _close(got, ref) and _close(s1, s2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("DK,DV,kda", [(128, 128, False), (64, 96, False), (128, 128, True), (128, 256, False)])
+def test_delta_rule_cuda(DK, DV, kda):
+    torch.manual_seed(3)
+    dev, T, H = "cuda", 33, 3
+    cu = torch.tensor([0, 13, 33], dtype=torch.int32, device=dev)
+    q = torch.nn.functional.normalize(torch.randn(T, H, DK, device=dev), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(torch.randn(T, H, DK, device=dev), dim=-1).to(torch.bfloat16)
+    v = torch.randn(T, H, DV, device=dev).to(torch.bfloat16)
+    g = -torch.rand(T, H, DK, device=dev) if kda else -torch.rand(T, H, device=dev)
+    beta = torch.rand(T, H, device=dev).to(torch.bfloat16)
+    s1, s2 = torch.zeros(2, H, DK, DV, device=dev), torch.zeros(2, H, DK, DV, device=dev)
+    with torch.no_grad():
+        got = ssm.gated_delta_rule(q, k, v, g, beta, None, cu, s1)
+        ref = ssm.delta_rule_reference(q, k, v, g, beta, None, cu, s2)
+    assert _close(got, ref) and _close(s1, s2)
+
+
+@pytest.mark.gpu
+def test_ragged_conv1d_cuda():
+    torch.manual_seed(4)
+    dev, T, Cn, W = "cuda", 50, 96, 4
+    cu = torch.tensor([0, 3, 20, 50], dtype=torch.int32, device=dev)
+    x = torch.randn(T, Cn, device=dev).to(torch.bfloat16)
+    w = torch.randn(Cn, W, device=dev).to(torch.bfloat16)
+    b = torch.randn(Cn, device=dev).to(torch.bfloat16)
+    c1 = torch.randn(3, W - 1, Cn, device=dev).to(torch.bfloat16)
+    c2 = c1.clone()
+    with torch.no_grad():
+        got = ssm.ragged_conv1d(x, w, b, cu, "silu", c1)
+        ref = ssm.ragged_conv1d_reference(x, w, b, cu, "silu", c2)
+    assert _close(got, ref) and torch.equal(c1, c2)
