@@ -135,3 +135,82 @@ EDL_HOST_API int edl_allreduce_oneshot(const unsigned long long* data_ptrs, cons
       d, f, nranks, rank, sync, (__nv_bfloat16*)out, (const __nv_bfloat16*)residual, n, spin, status);
   return check_cuda(cudaGetLastError(), "allreduce_oneshot launch");
 }
+
+// ---- peer-memory all-gather / reduce-scatter used by expert parallelism -----------------------------------------
+// Both read the peers' symmetric buffers with plain 16-byte loads (every rank's data is complete before the launch:
+// the callers put a device-side barrier in front). The reduce adds in rank order, so all ranks round identically.
+namespace edl {
+namespace {
+
+__global__ void peer_gather_kernel(PeerPtrs src, int nranks, long long vecs_per_rank, uint4* __restrict__ out) {
+  const long long total = vecs_per_rank * nranks;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / vecs_per_rank);
+    out[i] = reinterpret_cast<const uint4*>(src.p[r])[i - r * vecs_per_rank];
+  }
+}
+
+__global__ void peer_reduce_bf16_kernel(PeerPtrs src, int nranks, long long offset_vecs, long long nvec,
+                                        uint4* __restrict__ out) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    uint4 part[MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < nranks) part[r] = reinterpret_cast<const uint4*>(src.p[r])[offset_vecs + i];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r >= nranks) break;
+      float2 f;
+      f = unpack_bf16x2(part[r].x); acc[0] += f.x; acc[1] += f.y;
+      f = unpack_bf16x2(part[r].y); acc[2] += f.x; acc[3] += f.y;
+      f = unpack_bf16x2(part[r].z); acc[4] += f.x; acc[5] += f.y;
+      f = unpack_bf16x2(part[r].w); acc[6] += f.x; acc[7] += f.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    out[i] = o;
+  }
+}
+
+}  // namespace
+}  // namespace edl
+
+// out[r * bytes_per_rank ...] = bytes_per_rank bytes at ptrs[r] (bytes_per_rank a multiple of 16).
+EDL_HOST_API int edl_peer_gather(const unsigned long long* ptrs, int nranks, long long bytes_per_rank, void* out,
+                                 void* stream) {
+  if (bytes_per_rank <= 0) return 0;
+  if (nranks < 1 || nranks > MAX_RANKS || (bytes_per_rank & 15)) {
+    set_last_error("edl_peer_gather: nranks=%d, bytes_per_rank=%lld must be a multiple of 16", nranks, bytes_per_rank);
+    return -1;
+  }
+  PeerPtrs p;
+  for (int r = 0; r < nranks; ++r) p.p[r] = reinterpret_cast<void*>(ptrs[r]);
+  const long long vecs = bytes_per_rank / 16;
+  long long blocks = (vecs * nranks + 255) / 256, cap = (long long)sm_count() * 4;
+  peer_gather_kernel<<<(int)(blocks > cap ? cap : blocks), 256, 0, (cudaStream_t)stream>>>(p, nranks, vecs,
+                                                                                          (uint4*)out);
+  return check_cuda(cudaGetLastError(), "peer_gather launch");
+}
+
+// out[i] = sum_r ptrs[r][offset + i] over bf16 elements (offset and count multiples of 8), fp32 accumulation.
+EDL_HOST_API int edl_peer_reduce_bf16(const unsigned long long* ptrs, int nranks, long long offset, long long count,
+                                      void* out, void* stream) {
+  if (count <= 0) return 0;
+  if (nranks < 1 || nranks > MAX_RANKS || (offset & 7) || (count & 7)) {
+    set_last_error("edl_peer_reduce_bf16: offset / count must be multiples of 8 elements");
+    return -1;
+  }
+  PeerPtrs p;
+  for (int r = 0; r < nranks; ++r) p.p[r] = reinterpret_cast<void*>(ptrs[r]);
+  const long long nvec = count / 8;
+  long long blocks = (nvec + 255) / 256, cap = (long long)sm_count() * 4;
+  peer_reduce_bf16_kernel<<<(int)(blocks > cap ? cap : blocks), 256, 0, (cudaStream_t)stream>>>(p, nranks, offset / 8,
+                                                                                               nvec, (uint4*)out);
+  return check_cuda(cudaGetLastError(), "peer_reduce launch");
+}

@@ -117,3 +117,37 @@ def test_mesh_groups_4_ranks():
 
 def test_sharded_optimizer_matches_single_process():
     _run(_sharded_step_worker, 2)
+
+
+def _ep_worker(rank, world):
+    """Expert-parallel MoE block (2 ranks x 2 local experts) equals the single-rank block on each rank's tokens,
+    in outputs and in gradients of inputs, router weights and expert weights."""
+    from easydel_b200.layers.moe import MoEBlock
+
+    torch.manual_seed(0)
+    H, F, E, k, T = 16, 32, 4, 2, 6
+    full = MoEBlock(H, F, E, k, dtype=torch.float32)
+    ep = MoEBlock(H, F, E, k, dtype=torch.float32, ep_size=world, ep_rank=rank, ep_group=dist.group.WORLD)
+    El = E // world
+    with torch.no_grad():
+        ep.gate.weight.copy_(full.gate.weight)
+        ep.gate_up_proj.weight.copy_(full.gate_up_proj.weight[rank * El:(rank + 1) * El])
+        ep.down_proj.weight.copy_(full.down_proj.weight[rank * El:(rank + 1) * El])
+    xs = torch.randn(world, 1, T, H)
+    x_full = xs.reshape(1, world * T, H).clone().requires_grad_(True)
+    y_full, _ = full(x_full)
+    y_full.square().sum().backward()
+    x = xs[rank].clone().requires_grad_(True)
+    y, _ = ep(x)
+    y.square().sum().backward()
+    assert torch.allclose(y, y_full[:, rank * T:(rank + 1) * T], atol=1e-5)
+    assert torch.allclose(x.grad, x_full.grad[:, rank * T:(rank + 1) * T], atol=1e-5)
+    assert torch.allclose(ep.gate_up_proj.weight.grad, full.gate_up_proj.weight.grad[rank * El:(rank + 1) * El],
+                          atol=1e-5)
+    g = ep.gate.weight.grad.clone()
+    dist.all_reduce(g)     # the router is replicated: its gradient is the sum over ranks
+    assert torch.allclose(g, full.gate.weight.grad, atol=1e-5)
+
+
+def test_expert_parallel_block_matches_single_rank():
+    _run(_ep_worker, 2)
