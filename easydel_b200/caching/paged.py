@@ -32,6 +32,7 @@ class PagedBatchMeta:
     num_seqs: int
     last_token_index: torch.Tensor | None = None  # int32 [B] row of each sequence's last new token
     request_distribution: tuple[int, int, int] | None = None  # (#decode, #decode+#prefill, #total)
+    num_splits: int = 1          # decode-only steps: cut every sequence's keys into this many page ranges
 
 
 class PagedKVCache:
@@ -91,6 +92,10 @@ class PagedLayerView:
         T = q.shape[1]
         q3, k3, v3 = q[0], k[0], v[0]
         S.kv_append(k3, v3, self.k_pages, self.v_pages, meta.slot_mapping)
+        if meta.num_splits > 1 and meta.max_q == 1 and not attn.sliding_window and q3.is_cuda:
+            o = S.paged_attention_splitkv(q3, self.k_pages, self.v_pages, meta.kv_lens, meta.page_table,
+                                          meta.num_splits, scale=attn.scale, softcap=attn.softcap, sinks=attn.sinks)
+            return o[None]
         o = S.paged_attention(q3, self.k_pages, self.v_pages, meta.cu_q, meta.kv_lens, meta.page_table, meta.max_q,
                               scale=attn.scale, causal=True, window=attn.sliding_window or 0, softcap=attn.softcap,
                               sinks=attn.sinks)

@@ -58,6 +58,7 @@ class ModelRunner:
         self._graphs: dict[int, tuple[tp.Any, torch.Tensor]] = {}
         self._graph_pool = None
         self._warm: set[int] = set()
+        self._sms = torch.cuda.get_device_properties(dev).multi_processor_count if dev.type == "cuda" else 1
         self.tp_group = None
         mesh = getattr(model.config, "mesh", None)
         if mesh is not None and getattr(mesh, "tp", 1) > 1:
@@ -85,13 +86,23 @@ class ModelRunner:
             t = torch.tensor(list(token_ids), dtype=torch.int64, device=self.device)
             self.counts[slot].index_put_((t,), torch.ones_like(t, dtype=torch.int32), accumulate=True)
 
+    def _decode_splits(self, B: int) -> int:
+        """Key-range splits for a decode step of ``B`` rows: enough (row, kv-head, split) units to fill the SMs."""
+        if self.device.type != "cuda" or self.max_pages_per_seq < 8:
+            return 1
+        units = B * max(1, self.cache.num_kv_heads)
+        if units * 2 > self._sms:
+            return 1
+        return int(min(8, self.max_pages_per_seq // 4, max(1, self._sms // units)))
+
     def _forward(self, B: int, T: int, max_q: int, num_decode: int) -> torch.Tensor:
         """Backbone over the first ``T`` staged tokens of ``B`` sequences, LM head on each sequence's last row."""
         d_ids, d_pos, d_slots, d_cu, d_kv, d_last, d_table = self._dviews
         MP = self.max_pages_per_seq
         meta = PagedBatchMeta(cu_q=d_cu[:B + 1], kv_lens=d_kv[:B], page_table=d_table.view(self.max_num_seqs, MP)[:B],
                               slot_mapping=d_slots[:T], max_q=max_q, num_seqs=B, last_token_index=d_last[:B],
-                              request_distribution=(num_decode, B, B))
+                              request_distribution=(num_decode, B, B),
+                              num_splits=self._decode_splits(B) if (max_q == 1 and T == B) else 1)
         model = self.model
         res = model(input_ids=d_ids[:T][None].long(), position_ids=d_pos[:T][None], past_key_values=self.cache,
                     cache_metadata=meta, apply_lm_head=False)
