@@ -6,3 +6,5 @@ from . import families  # noqa: F401
 from .families import *  # noqa: F401,F403
 from . import families_classic  # noqa: F401
 from .families_classic import *  # noqa: F401,F403
+from . import mamba  # noqa: F401
+from .mamba import *  # noqa: F401,F403

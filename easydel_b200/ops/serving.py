@@ -74,10 +74,10 @@ def attn_combine(o_parts: torch.Tensor, lse_parts: torch.Tensor, sinks=None, wan
     """Merges ``o_parts [S, R, H, D]`` with ``lse_parts [S, H, R]`` (disjoint key ranges) into ``[R, H, D]``."""
     S_, R_, H, D = o_parts.shape
     if o_parts.is_cuda:
-        assert o_parts.stride(3) == 1 and o_parts.stride(2) == D and o_parts.stride(1) == H * D
+        o_parts = o_parts.contiguous()      # strides of size-1 dimensions are arbitrary: pass the dense pitch
         out = torch.empty(R_, H, D, dtype=o_parts.dtype, device=o_parts.device)
         lse = torch.empty(H, R_, dtype=torch.float32, device=o_parts.device) if want_lse else None
-        _lib.call("edl_attn_combine", o_parts.data_ptr(), o_parts.stride(0), lse_parts.contiguous().data_ptr(), S_, R_,
+        _lib.call("edl_attn_combine", o_parts.data_ptr(), R_ * H * D, lse_parts.contiguous().data_ptr(), S_, R_,
                   H, D, _lib.ptr(sinks), out.data_ptr(), _lib.ptr(lse), _lib.stream_ptr())
         return (out, lse) if want_lse else out
     l = lse_parts.float().permute(0, 2, 1)                      # [S, R, H]
