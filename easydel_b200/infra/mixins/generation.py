@@ -18,6 +18,12 @@ class EasyGenerationMixin:
     def init_cache(self, batch_size: int, max_length: int, dtype=None, device=None, **_):
         from ...caching.transformer import TransformerCache
 
+        spec = getattr(self, "spec", None)
+        if spec is not None and getattr(spec, "mla", None) is not None:
+            from ...layers.mla import MLACache
+
+            return MLACache(spec.num_layers, batch_size, max_length, spec.mla["kv_lora_rank"],
+                            spec.mla["qk_rope_head_dim"], dtype or self.dtype, device or self.device)
         return TransformerCache.init_for_model(self, batch_size, max_length, dtype=dtype, device=device)
 
     def init_ragged_pages(self, num_pages: int | None = None, page_size: int = 128, hbm_utilization: float = 0.85,

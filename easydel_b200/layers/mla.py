@@ -1,0 +1,128 @@
+"""Multi-head latent attention (DeepSeek-V2 / V3; easydel/layers/attention MLA paths and modules/deepseek_v3).
+
+Keys and values are generated from a low-rank latent ``c_kv`` (``kv_lora_rank`` wide) plus one rotary key shared by
+all heads; queries optionally go through their own low-rank bottleneck. The generation cache stores only the
+normalised latent and the rotary key per token (:class:`MLACache`), and the per-head keys / values are re-expanded
+from it. Query / key heads are ``qk_nope + qk_rope`` wide while value heads are ``v_head_dim`` wide; the flash
+kernels here handle equal widths of 64 or 128, so the score and value products of this layer run through the dense
+attention reference (library matmuls) — an MLA kernel is open work.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from ..ops import functional as F
+from ..ops import reference as R
+from .linears import ColumnParallelLinear, RowParallelLinear
+from .norms import RMSNorm
+from .rotary import get_rope
+
+
+class MLACache:
+    def __init__(self, num_layers: int, batch: int, max_len: int, kv_lora_rank: int, rope_dim: int,
+                 dtype=torch.bfloat16, device=None):
+        self.latent = torch.zeros(num_layers, batch, max_len, kv_lora_rank, dtype=dtype, device=device)
+        self.k_rope = torch.zeros(num_layers, batch, max_len, rope_dim, dtype=dtype, device=device)
+        self.length, self.max_len = 0, max_len
+
+    def seq_len(self) -> int:
+        return self.length
+
+    def advance(self, n: int) -> None:
+        self.length += n
+
+    def view(self, layer: int):
+        return _MLAView(self, layer)
+
+    def reorder(self, index: torch.Tensor) -> None:
+        self.latent = self.latent.index_select(1, index)
+        self.k_rope = self.k_rope.index_select(1, index)
+
+
+class _MLAView:
+    def __init__(self, cache: MLACache, layer: int):
+        self.cache, self.layer = cache, layer
+
+    def update(self, latent: torch.Tensor, k_rope: torch.Tensor):
+        c = self.cache
+        T = latent.shape[1]
+        s, e = c.length, c.length + T
+        if e > c.max_len:
+            raise ValueError(f"MLA cache overflow: {e} > {c.max_len}")
+        c.latent[self.layer, :, s:e] = latent
+        c.k_rope[self.layer, :, s:e] = k_rope
+        return c.latent[self.layer, :, :e], c.k_rope[self.layer, :, :e]
+
+
+class MLAttention(nn.Module):
+    def __init__(self, hidden_size: int, num_heads: int, *, q_lora_rank: int | None, kv_lora_rank: int,
+                 qk_nope_head_dim: int, qk_rope_head_dim: int, v_head_dim: int, rope: dict, rope_interleave: bool = True,
+                 norm_eps: float = 1e-6, bias: bool = False, scale: float | None = None, layer_idx: int = 0,
+                 dtype=torch.bfloat16, init_std: float = 0.02, tp_size: int = 1, tp_rank: int = 0, tp_group=None):
+        super().__init__()
+        self.H, self.nope, self.rope_dim, self.vd = num_heads // tp_size, qk_nope_head_dim, qk_rope_head_dim, v_head_dim
+        self.qk_dim = qk_nope_head_dim + qk_rope_head_dim
+        self.kv_lora_rank, self.layer_idx, self.interleave = kv_lora_rank, layer_idx, rope_interleave
+        self.scale = scale if scale is not None else self.qk_dim ** -0.5
+        self.sliding_window, self.softcap, self.sinks = None, 0.0, None
+        kw = dict(dtype=dtype, init_std=init_std)
+        if q_lora_rank:
+            self.q_a_proj = ColumnParallelLinear(hidden_size, q_lora_rank, bias=bias, **kw)
+            self.q_a_layernorm = RMSNorm(q_lora_rank, norm_eps, dtype)
+            self.q_b_proj = ColumnParallelLinear(q_lora_rank, num_heads * self.qk_dim, bias=False, tp_size=tp_size,
+                                                 tp_rank=tp_rank, tp_group=tp_group, **kw)
+            self.q_proj = None
+        else:
+            self.q_proj = ColumnParallelLinear(hidden_size, num_heads * self.qk_dim, bias=False, tp_size=tp_size,
+                                               tp_rank=tp_rank, tp_group=tp_group, **kw)
+        self.kv_a_proj_with_mqa = ColumnParallelLinear(hidden_size, kv_lora_rank + qk_rope_head_dim, bias=bias, **kw)
+        self.kv_a_layernorm = RMSNorm(kv_lora_rank, norm_eps, dtype)
+        self.kv_b_proj = ColumnParallelLinear(kv_lora_rank, num_heads * (qk_nope_head_dim + v_head_dim), bias=False,
+                                              tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group, **kw)
+        self.o_proj = RowParallelLinear(num_heads * v_head_dim, hidden_size, bias=bias, tp_size=tp_size,
+                                        tp_rank=tp_rank, tp_group=tp_group, **kw)
+        self.rotary = get_rope(head_size=qk_rope_head_dim, **rope)
+
+    def _rope(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """x ``[B, T, h, rope_dim]``. Checkpoints with ``rope_interleave`` store pairs interleaved: de-interleave,
+        then rotate in the half-split layout (what the Hugging Face implementation does)."""
+        if self.interleave:
+            B, T, h, d = x.shape
+            x = x.view(B, T, h, d // 2, 2).transpose(-1, -2).reshape(B, T, h, d)
+        cos, sin = self.rotary.tables(x.device)
+        B, T, h, d = x.shape
+        pos = positions.reshape(-1) if positions.numel() == B * T else positions.expand(B, T).reshape(-1)
+        return R.apply_rope(x.reshape(B * T, h, d), pos, cos, sin, d, False).view(B, T, h, d)
+
+    def forward(self, hidden, positions, *, segment_ids=None, cache_view=None, attn_meta=None, **_):
+        B, T, _ = hidden.shape
+        if self.q_proj is None:
+            q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(hidden)))
+        else:
+            q = self.q_proj(hidden)
+        q = q.view(B, T, self.H, self.qk_dim)
+        q_nope, q_rope = q[..., : self.nope], q[..., self.nope:]
+        ckv = self.kv_a_proj_with_mqa(hidden)
+        latent = self.kv_a_layernorm(ckv[..., : self.kv_lora_rank].contiguous())
+        k_rope = self._rope(ckv[..., self.kv_lora_rank:].reshape(B, T, 1, self.rope_dim), positions)[:, :, 0]
+        q_rope = self._rope(q_rope, positions)
+        kv_seg = None
+        if cache_view is not None:
+            if not hasattr(cache_view, "update"):
+                raise TypeError("latent attention needs an MLACache (model.init_cache builds one)")
+            latent, k_rope = cache_view.update(latent, k_rope)
+            if attn_meta is not None and attn_meta.get("kv_segment_ids") is not None:
+                kv_seg = attn_meta["kv_segment_ids"][:, : latent.shape[1]]
+        Tk = latent.shape[1]
+        kv = self.kv_b_proj(latent).view(B, Tk, self.H, self.nope + self.vd)
+        k = torch.cat([kv[..., : self.nope], k_rope[:, :, None, :].expand(B, Tk, self.H, self.rope_dim)], -1)
+        v = kv[..., self.nope:]
+        qf = torch.cat([q_nope, q_rope], -1)
+        if kv_seg is not None:
+            o = R.attention(qf, k, v, causal=True, scale=self.scale, segment_ids=kv_seg[:, Tk - T:],
+                            kv_segment_ids=kv_seg)
+        else:
+            o = R.attention(qf, k, v, causal=True, scale=self.scale, segment_ids=segment_ids)
+        return self.o_proj(o.reshape(B, T, self.H * self.vd).to(hidden.dtype))

@@ -120,8 +120,10 @@ class MoEBlock(nn.Module):
                 gscore = g.max(-1).values
             gidx = gscore.topk(self.topk_group, dim=-1).indices
             gmask = torch.zeros_like(gscore).scatter_(1, gidx, 1.0)
-            scores = (g * gmask[..., None]).masked_fill(gmask[..., None] == 0, float("-inf")
-                                                        if self.e_score_correction_bias is None else 0.0).view(T, E)
+            # experts of the groups that lost are out of the race: -inf for softmax scores, 0 for the
+            # bias-corrected sigmoid scores (DeepSeek-V3 convention)
+            fill = float("-inf") if self.e_score_correction_bias is None else 0.0
+            scores = torch.where(gmask[..., None] > 0, g, torch.full_like(g, fill)).view(T, E)
         idx = scores.topk(self.top_k, dim=-1).indices
         w = probs.gather(-1, idx)
         if self.norm_topk_prob:

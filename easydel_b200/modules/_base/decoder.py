@@ -97,6 +97,7 @@ class ArchSpec:
     logit_scale: float | None = None  # Cohere / Granite style multiplier on logits
     residual_multiplier: float | None = None
     embedding_multiplier: float | None = None
+    mla: dict | None = None           # kwargs of layers.mla.MLAttention: latent attention instead of MHA / GQA
 
 
 def _norm(spec: ArchSpec, dtype) -> nn.Module:
@@ -134,14 +135,30 @@ class DecoderLayer(nn.Module):
             rope = spec.rope_local
         if ltype == "nope":
             rope = None
-        self.self_attn = Attention(
+        if spec.mla is not None:
+            from ...layers.mla import MLAttention
+
+            self.self_attn = MLAttention(spec.hidden_size, spec.num_heads, rope=spec.rope, norm_eps=spec.norm_eps,
+                                         bias=spec.attn_bias, layer_idx=layer_idx, dtype=dtype,
+                                         init_std=spec.init_std, tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group,
+                                         **spec.mla)
+        else:
+            self.self_attn = self._mha(spec, layer_idx, dtype, rope, window, tp_size, tp_rank, tp_group)
+        moe = spec.moe
+        self.is_moe = moe is not None and (moe.layers is None or layer_idx in moe.layers)
+        self._build_mlp(config, spec, layer_idx, dtype, tp_size, tp_rank, tp_group)
+
+    @staticmethod
+    def _mha(spec, layer_idx, dtype, rope, window, tp_size, tp_rank, tp_group):
+        return Attention(
             spec.hidden_size, spec.num_heads, spec.num_kv_heads, spec.head_dim, layer_idx=layer_idx,
             bias=spec.attn_bias, o_bias=spec.o_bias, qk_norm=spec.qk_norm, qk_norm_eps=spec.norm_eps, rope=rope,
             sliding_window=window, softcap=spec.attn_softcap, scale=spec.attn_scale, use_sinks=spec.use_sinks,
             use_alibi=spec.pos_emb == "alibi", clip_qkv=spec.clip_qkv, dtype=dtype, init_std=spec.init_std,
             tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group, qk_norm_offset=spec.norm_offset)
+
+    def _build_mlp(self, config, spec, layer_idx, dtype, tp_size, tp_rank, tp_group):
         moe = spec.moe
-        self.is_moe = moe is not None and (moe.layers is None or layer_idx in moe.layers)
         if self.is_moe:
             ep_size, ep_rank, ep_group = _ep_of(config)
             self.mlp = MoEBlock(spec.hidden_size, moe.intermediate_size, moe.num_experts, moe.top_k, act=spec.act,

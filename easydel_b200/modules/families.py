@@ -262,3 +262,114 @@ EXPORTS.update(define_family(
 
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)
+
+
+# ---- cohere2 (easydel/modules/cohere2): sliding layers rotate, every fourth (global) layer has no positions ----
+def _cohere2_spec(c):
+    n = c.num_hidden_layers
+    pat = getattr(c, "sliding_window_pattern", 4) or 4
+    lt = getattr(c, "layer_types", None)
+    if lt:
+        types = tuple("sliding" if "sliding" in t else "nope" for t in lt)
+    else:
+        types = tuple("nope" if (i + 1) % pat == 0 else "sliding" for i in range(n))
+    return base_spec(c, norm="layer", norm_bias=False, norm_eps=c.layer_norm_eps, residual="parallel",
+                     shared_parallel_norm=True, logit_scale=c.logit_scale, tie_embeddings=True,
+                     sliding_window=c.sliding_window, layer_types=types,
+                     rope=rope_args(c, c.hidden_size // c.num_attention_heads, neox=False))
+
+
+EXPORTS.update(define_family(
+    "cohere2", _d(vocab_size=256000, hidden_size=8192, intermediate_size=22528, num_hidden_layers=40,
+                  num_attention_heads=64, logit_scale=0.0625, layer_norm_eps=1e-5, sliding_window=4096,
+                  sliding_window_pattern=4, layer_types=None, max_position_embeddings=8192, tie_word_embeddings=True),
+    _cohere2_spec, layernorm_names=["input_layernorm", "norm"]))
+
+
+# ---- deepseek_v2 / deepseek_v3 (easydel/modules/deepseek_v2, deepseek_v3): latent attention + routed experts ------
+def _yarn_mscale(scale: float, mscale: float) -> float:
+    return 1.0 if scale <= 1 else 0.1 * mscale * math.log(scale) + 1.0
+
+
+def _mla_args(c) -> dict:
+    qk = c.qk_nope_head_dim + c.qk_rope_head_dim
+    scale = qk ** -0.5
+    rs = getattr(c, "rope_scaling", None)
+    if isinstance(rs, dict) and rs.get("mscale_all_dim"):
+        scale = scale * _yarn_mscale(rs.get("factor", 1.0), rs["mscale_all_dim"]) ** 2
+    return dict(q_lora_rank=c.q_lora_rank, kv_lora_rank=c.kv_lora_rank, qk_nope_head_dim=c.qk_nope_head_dim,
+                qk_rope_head_dim=c.qk_rope_head_dim, v_head_dim=c.v_head_dim, scale=scale,
+                rope_interleave=getattr(c, "rope_interleave", True))
+
+
+def _dense_then_moe(c, freq_attr="moe_layer_freq"):
+    n = c.num_hidden_layers
+    freq = getattr(c, freq_attr, 1) or 1
+    return tuple(i for i in range(n) if i >= c.first_k_dense_replace and i % freq == 0)
+
+
+def _deepseek_v3_spec(c):
+    return base_spec(
+        c, head_dim=c.qk_rope_head_dim, rope=rope_args(c, c.qk_rope_head_dim), mla=_mla_args(c),
+        moe=moe_spec(c, num_experts=c.n_routed_experts, top_k=c.num_experts_per_tok,
+                     intermediate=c.moe_intermediate_size, norm_topk=c.norm_topk_prob,
+                     shared=c.moe_intermediate_size * (c.n_shared_experts or 0), layers=_dense_then_moe(c),
+                     scoring="sigmoid", routed_scaling_factor=c.routed_scaling_factor, n_group=c.n_group,
+                     topk_group=c.topk_group, use_score_bias=True))
+
+
+_DSV3 = _d(vocab_size=129280, hidden_size=7168, intermediate_size=18432, moe_intermediate_size=2048,
+           num_hidden_layers=61, num_attention_heads=128, num_key_value_heads=128, n_shared_experts=1,
+           n_routed_experts=256, routed_scaling_factor=2.5, kv_lora_rank=512, q_lora_rank=1536, qk_rope_head_dim=64,
+           v_head_dim=128, qk_nope_head_dim=128, n_group=8, topk_group=4, num_experts_per_tok=8,
+           first_k_dense_replace=3, norm_topk_prob=True, rope_interleave=True, moe_layer_freq=1,
+           max_position_embeddings=4096)
+_DSV3.pop("head_dim", None)
+EXPORTS.update(define_family(
+    "deepseek_v3", _DSV3, _deepseek_v3_spec, class_prefix="DeepseekV3",
+    rules=[("mlp.gate.e_score_correction_bias", "mlp.e_score_correction_bias")], with_classifier=False))
+
+
+def _deepseek_v2_spec(c):
+    grouped = getattr(c, "topk_method", "greedy") == "group_limited_greedy"
+    return base_spec(
+        c, head_dim=c.qk_rope_head_dim, rope=rope_args(c, c.qk_rope_head_dim), mla=_mla_args(c),
+        moe=moe_spec(c, num_experts=c.n_routed_experts, top_k=c.num_experts_per_tok,
+                     intermediate=c.moe_intermediate_size, norm_topk=c.norm_topk_prob,
+                     shared=c.moe_intermediate_size * (c.n_shared_experts or 0), layers=_dense_then_moe(c),
+                     scoring="softmax", routed_scaling_factor=c.routed_scaling_factor,
+                     n_group=c.n_group if grouped else 1, topk_group=c.topk_group if grouped else 1))
+
+
+_DSV2 = dict(_DSV3, vocab_size=102400, hidden_size=4096, intermediate_size=11008, moe_intermediate_size=1407,
+             num_hidden_layers=30, num_attention_heads=32, num_key_value_heads=32, n_shared_experts=2,
+             n_routed_experts=64, routed_scaling_factor=1.0, topk_method="greedy", n_group=1, topk_group=1,
+             num_experts_per_tok=6, first_k_dense_replace=1, norm_topk_prob=False, max_position_embeddings=2048)
+EXPORTS.update(define_family("deepseek_v2", _DSV2, _deepseek_v2_spec, class_prefix="DeepseekV2",
+                             with_classifier=False))
+
+
+# ---- glm4_moe (easydel/modules/glm4_moe): GQA with partial rotary + DeepSeek-style routed experts -------------------
+def _glm4_moe_spec(c):
+    return base_spec(
+        c, attn_bias=c.attention_bias, o_bias=False, qk_norm="rms_head" if c.use_qk_norm else None,
+        rope=rope_args(c, c.head_dim, partial=c.partial_rotary_factor),
+        moe=moe_spec(c, num_experts=c.n_routed_experts, top_k=c.num_experts_per_tok,
+                     intermediate=c.moe_intermediate_size, norm_topk=c.norm_topk_prob,
+                     shared=c.moe_intermediate_size * (c.n_shared_experts or 0),
+                     layers=tuple(range(c.first_k_dense_replace, c.num_hidden_layers)), scoring="sigmoid",
+                     routed_scaling_factor=c.routed_scaling_factor, n_group=c.n_group, topk_group=c.topk_group,
+                     use_score_bias=True))
+
+
+EXPORTS.update(define_family(
+    "glm4_moe", _d(vocab_size=151552, hidden_size=4096, intermediate_size=10944, num_hidden_layers=46,
+                   num_attention_heads=96, num_key_value_heads=8, head_dim=128, partial_rotary_factor=0.5,
+                   rms_norm_eps=1e-5, attention_bias=False, moe_intermediate_size=1408, num_experts_per_tok=8,
+                   n_shared_experts=1, n_routed_experts=128, routed_scaling_factor=1.0, n_group=1, topk_group=1,
+                   first_k_dense_replace=1, norm_topk_prob=True, use_qk_norm=False, max_position_embeddings=131072),
+    _glm4_moe_spec, class_prefix="Glm4Moe",
+    rules=[("mlp.gate.e_score_correction_bias", "mlp.e_score_correction_bias")], with_classifier=False))
+
+globals().update(EXPORTS)
+__all__ = sorted(EXPORTS)

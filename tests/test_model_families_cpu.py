@@ -50,6 +50,22 @@ CASES = {
     "falcon-mha": dict(_replace=dict(vocab_size=512, hidden_size=128, num_hidden_layers=3, num_attention_heads=8,
                                      multi_query=False, parallel_attn=False, max_position_embeddings=256),
                        _type="falcon"),
+    "cohere2": dict(sliding_window=32, sliding_window_pattern=2, logit_scale=0.25),
+    "deepseek_v3": dict(_replace=dict(vocab_size=512, hidden_size=128, intermediate_size=256, moe_intermediate_size=64,
+                                      num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=8,
+                                      n_shared_experts=1, n_routed_experts=8, kv_lora_rank=32, q_lora_rank=48,
+                                      qk_rope_head_dim=16, v_head_dim=24, qk_nope_head_dim=32, n_group=4,
+                                      topk_group=2, num_experts_per_tok=3, first_k_dense_replace=1,
+                                      max_position_embeddings=256)),
+    "deepseek_v2": dict(_replace=dict(vocab_size=512, hidden_size=128, intermediate_size=256, moe_intermediate_size=64,
+                                      num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=8,
+                                      n_shared_experts=2, n_routed_experts=8, kv_lora_rank=32, q_lora_rank=None,
+                                      qk_rope_head_dim=16, v_head_dim=24, qk_nope_head_dim=32,
+                                      num_experts_per_tok=3, first_k_dense_replace=1, max_position_embeddings=256)),
+    "glm4_moe": dict(_replace=dict(vocab_size=512, hidden_size=128, intermediate_size=256, moe_intermediate_size=64,
+                                   num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=16,
+                                   n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1, use_qk_norm=True,
+                                   first_k_dense_replace=1, max_position_embeddings=256, pad_token_id=0)),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                       shared_expert_intermediate_size=96),
 }
