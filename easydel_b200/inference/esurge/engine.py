@@ -255,6 +255,7 @@ class eSurge:
             for s in out.scheduled:
                 if s.request.slot < 0:
                     s.request.slot = self._free_slots.pop()
+                    self.runner._slot_npages[s.request.slot] = 0   # the slot's page mirror belongs to a new request
                     if s.request.sampling_params.needs_penalties:
                         self.runner._ensure_counts()
                         self.runner.reset_slot(s.request.slot, s.request.all_token_ids)

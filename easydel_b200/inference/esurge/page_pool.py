@@ -34,12 +34,30 @@ def hash_page_tokens(parent_hash: bytes | None, tokens: tp.Sequence[int], extra_
 
 
 def hash_request_pages(tokens: tp.Sequence[int], page_size: int, extra_keys: tp.Any = None) -> list[bytes]:
-    """Chained hashes of every *full* page of a token list."""
+    """Chained hashes of every *full* page of a token list (native 128-bit mixer when the library is built,
+    keyed BLAKE2b otherwise; one process always uses the same one)."""
+    if _NATIVE is not None:
+        extra = 0 if extra_keys is None else int.from_bytes(
+            hashlib.blake2b(repr(extra_keys).encode(), digest_size=8).digest(), "little")
+        return _NATIVE.hash_pages(tokens, page_size, _SEED_INT, extra)
     out, parent = [], None
     for i in range(0, len(tokens) - len(tokens) % page_size, page_size):
         parent = hash_page_tokens(parent, tokens[i:i + page_size], extra_keys)
         out.append(parent)
     return out
+
+
+def _pick_native():
+    try:
+        from ...data import _native
+
+        return _native if _native.available() else None
+    except Exception:
+        return None
+
+
+_NATIVE = _pick_native()
+_SEED_INT = int.from_bytes(hashlib.blake2b(_seed(), digest_size=8).digest(), "little")
 
 
 @dataclass

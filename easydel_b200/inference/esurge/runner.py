@@ -47,6 +47,15 @@ class ModelRunner:
         self._fdev = torch.zeros(6 * B, dtype=torch.float32, device=dev)
         self._ihost = torch.zeros(3 * B, dtype=torch.int64, pin_memory=pin)
         self._idev = torch.zeros(3 * B, dtype=torch.int64, device=dev)
+        # host mirror of every slot's page list, so that decode steps are filled without per-request slicing
+        self._slot_pages = np.zeros((B, MP), dtype=np.int32)
+        self._slot_npages = np.zeros(B, dtype=np.int32)
+        try:
+            from ...data import _native
+
+            self._native = _native._lib()
+        except Exception:
+            self._native = None
         self.counts: torch.Tensor | None = None
         self.timings: dict[str, float] = {"prep": 0.0, "exec": 0.0, "sample": 0.0, "d2h": 0.0, "steps": 0,
                                           "graph_steps": 0}
@@ -149,7 +158,36 @@ class ModelRunner:
         cu_np[0] = 0
         any_pen = False
         any_random = False
-        for b, s in enumerate(sched):
+        fast = all(s.num_new_tokens == 1 and s.start >= s.request.num_prompt_tokens for s in sched)
+        if fast:
+            # Decode-only step: vectorised fill from the per-slot page mirror (one short Python pass per field).
+            sp_pages, sp_n = self._slot_pages, self._slot_npages
+            slot_idx = np.fromiter((s.request.slot for s in sched), dtype=np.int64, count=B)
+            for s in sched:   # pages only grow by one every 128 tokens: this loop rarely copies anything
+                req = s.request
+                n_pg = len(req.pages)
+                if sp_n[req.slot] != n_pg:
+                    sp_pages[req.slot, :n_pg] = req.pages
+                    sp_n[req.slot] = n_pg
+                sp = req.sampling_params
+                any_pen |= sp.needs_penalties
+                any_random |= not sp.is_greedy
+            p = np.fromiter((s.start for s in sched), dtype=np.int32, count=B)
+            ids_np[:B] = np.fromiter((s.request.output_token_ids[-1] for s in sched), dtype=np.int32, count=B)
+            pos_np[:B] = p
+            if self._native is not None:     # one C++ pass over the rows (csrc/host_native.cu)
+                self._native.edl_host_fill_decode(slot_idx.ctypes.data, p.ctypes.data, B, sp_pages.ctypes.data, MP,
+                                                  PAGE_SIZE, slots_np.ctypes.data, table_np.ctypes.data,
+                                                  kv_np.ctypes.data, cu_np.ctypes.data, last_np.ctypes.data)
+            else:
+                rows = sp_pages[slot_idx]
+                slots_np[:B] = rows[np.arange(B), p >> 7] * PAGE_SIZE + (p & (PAGE_SIZE - 1))
+                table_np[:B] = rows
+                kv_np[:B] = p + 1
+                cu_np[:B + 1] = np.arange(B + 1, dtype=np.int32)
+                last_np[:B] = np.arange(B, dtype=np.int32)
+            max_q = 1
+        for b, s in enumerate(sched if not fast else ()):
             req = s.request
             n, st = s.num_new_tokens, s.start
             npt = req.num_prompt_tokens
@@ -165,6 +203,9 @@ class ModelRunner:
             pg = np.asarray(req.pages, dtype=np.int32)
             slots_np[o:o + n] = pg[p // PAGE_SIZE] * PAGE_SIZE + p % PAGE_SIZE
             table_np[b, :len(pg)] = pg
+            if req.slot >= 0:
+                self._slot_pages[req.slot, :len(pg)] = pg
+                self._slot_npages[req.slot] = len(pg)
             kv_np[b] = st + n
             o += n
             cu_np[b + 1] = o

@@ -1,0 +1,100 @@
+"""Runs one kernel a handful of times on a small, L2-exceeding case so that it can be captured by a profiler.
+
+    python -m easydel_b200.ops.profile_case gemm          # 4096 x 6144 x 4096 bf16 (151 MB of operands + output)
+    python -m easydel_b200.ops.profile_case gemm_wgrad    # fp32-accumulating weight gradient, MN-major operands
+    python -m easydel_b200.ops.profile_case attn_fwd      # 8192 tokens, 32 / 8 heads, D = 128, causal
+    python -m easydel_b200.ops.profile_case attn_bwd
+    python -m easydel_b200.ops.profile_case gemm_rs       # one-rank form of the GEMM -> reduce-scatter kernel
+    python -m easydel_b200.ops.profile_case ag_gemm       # one-rank form of the all-gather -> GEMM kernel
+    python -m easydel_b200.ops.profile_case qgemv         # 4-bit fused dequant-GEMV, 4 rows x 14336 x 4096
+    python -m easydel_b200.ops.profile_case adamw         # fused AdamW over 256M parameters
+
+Prints the CUDA-event time of the last launch. Everything held on the device stays below 4 GB.
+"""
+
+from __future__ import annotations
+
+import sys
+
+import torch
+
+
+def main() -> None:
+    what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    from . import kernels as K
+
+    bf = lambda *s: torch.randn(*s, device=dev, dtype=torch.bfloat16)  # noqa: E731
+    if what == "gemm":
+        a, w = bf(4096, 4096), bf(6144, 4096)
+        out = torch.empty(4096, 6144, device=dev, dtype=torch.bfloat16)
+        fn = lambda: K.gemm(a, w, out=out)  # noqa: E731
+        work = 2.0 * 4096 * 6144 * 4096
+    elif what == "gemm_wgrad":
+        dy, x = bf(8192, 4096), bf(8192, 4096)
+        out = torch.zeros(4096, 4096, device=dev, dtype=torch.float32)
+        fn = lambda: K.gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True)  # noqa: E731
+        work = 2.0 * 8192 * 4096 * 4096
+    elif what in ("attn_fwd", "attn_bwd"):
+        from . import attention as A
+
+        q, k, v = bf(1, 8192, 32, 128), bf(1, 8192, 8, 128), bf(1, 8192, 8, 128)
+        o, lse = A.attn_fwd(q, k, v, causal=True)
+        do = bf(1, 8192, 32, 128)
+        if what == "attn_fwd":
+            fn = lambda: A.attn_fwd(q, k, v, causal=True)  # noqa: E731
+            work = 4.0 * 8192 * 8192 * 32 * 128 / 2
+        else:
+            fn = lambda: A.attn_bwd(q, k, v, o, lse, do, causal=True)  # noqa: E731
+            work = 10.0 * 8192 * 8192 * 32 * 128 / 2
+    elif what == "gemm_rs":
+        from ..parallel.fused import GemmReduceScatter
+
+        a, w = bf(4096, 4096), bf(4096, 4096)
+        op = GemmReduceScatter(None, 4096, 4096, dev)
+        fn = lambda: op(a, w)  # noqa: E731
+        work = 2.0 * 4096 * 4096 * 4096
+    elif what == "ag_gemm":
+        from ..parallel.fused import AllGatherGemm
+
+        a, w = bf(4096, 4096), bf(4096, 4096)
+        op = AllGatherGemm(None, 4096, 4096, dev)
+        fn = lambda: op(a, w)  # noqa: E731
+        work = 2.0 * 4096 * 4096 * 4096
+    elif what == "qgemv":
+        from ..layers.quantization import quantize, quantized_matmul
+
+        q = quantize(bf(14336, 4096) * 0.05, "nf4")
+        x = bf(4, 4096)
+        fn = lambda: quantized_matmul(x, q)  # noqa: E731
+        work = 14336 * 4096 * 0.5 + 14336 * 64 * 2      # bytes: the roofline of this kernel is HBM
+    elif what == "adamw":
+        n = 256 << 20
+        p, g = torch.zeros(n, device=dev), torch.randn(n, device=dev)
+        m, v2 = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        w16 = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: K.adamw_(p, w16, m, v2, g, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.01,  # noqa: E731
+                              step=3)
+        work = n * (4 * 4 + 3 * 4 + 2)
+    else:
+        raise SystemExit(f"unknown case {what!r}")
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    unit = "GB/s" if what in ("qgemv", "adamw") else "TFLOP/s"
+    rate = work / ms / 1e6 if unit == "GB/s" else work / ms / 1e9
+    from . import _lib
+
+    _lib.check_status(dev)
+    print(f"{what}: {ms:.3f} ms, {rate:.1f} {unit}")
+
+
+if __name__ == "__main__":
+    main()
