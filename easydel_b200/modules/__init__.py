@@ -8,3 +8,4 @@ from . import families_classic  # noqa: F401
 from .families_classic import *  # noqa: F401,F403
 from . import mamba  # noqa: F401
 from .mamba import *  # noqa: F401,F403
+from .auto import *  # noqa: F401,F403
