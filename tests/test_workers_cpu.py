@@ -58,3 +58,40 @@ def test_prometheus_exporter_and_provisioning(tmp_path):
     assert "[m]" in RichConsoleMonitor(eng).line()
     files = eSurgeMonitoringServer(eng, prometheus_port=9191).write_provisioning(str(tmp_path))
     assert "esurge" in open(files["prometheus"]).read() and "panels" in open(files["grafana"]).read()
+
+
+def test_distributed_controller_handshake_step_and_failure_detection():
+    """Host-side failure detection: a wrong fingerprint, a diverging worker and a silent worker are all reported."""
+    import socket
+
+    import pytest
+
+    from easydel_b200.inference.esurge.distributed import (DistributedController, WorkerControlServer, canonical_hash,
+                                                           sampled_digest)
+
+    def ep():
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            return f"tcp://127.0.0.1:{s.getsockname()[1]}"
+
+    assert canonical_hash({"b": 1, "a": [1.0, 2]}) == canonical_hash({"a": [1.0, 2], "b": 1})
+    e1, e2 = ep(), ep()
+    good = WorkerControlServer(e1, "fp", step_fn=lambda d: {"r0": d["token"]}).start()
+    bad = WorkerControlServer(e2, "fp", step_fn=lambda d: {"r0": d["token"] + 1}).start()
+    try:
+        ctl = DistributedController([e1], "fp", timeout_ms=2000)
+        ctl.handshake()
+        ctl.broadcast_step({"token": 7}, {"r0": 7})
+        assert ctl.health()[0]["steps"] == 1
+        with pytest.raises(RuntimeError, match="fingerprint"):
+            DistributedController([e1], "other", timeout_ms=2000).handshake()
+        with pytest.raises(RuntimeError, match="diverged"):
+            DistributedController([e2], "fp", timeout_ms=2000).broadcast_step({"token": 7}, {"r0": 7})
+        silent = DistributedController([ep()], "fp", timeout_ms=300)      # nobody listens there
+        with pytest.raises(TimeoutError):
+            silent.handshake()
+        assert silent.health()[0]["ok"] is False
+        assert sampled_digest({"a": 1}) != sampled_digest({"a": 2})
+    finally:
+        good.stop()
+        bad.stop()
