@@ -19,7 +19,7 @@ namespace edl {
 namespace {
 
 constexpr int QG_THREADS = 256;
-constexpr int QG_ROWS = 4;   // weight rows per warp
+constexpr int QG_ROWS = 2;   // weight rows per warp and pass
 constexpr int QG_MAX_M = 8;
 
 __global__ void dequant_kernel(const uint8_t* __restrict__ codes, const __nv_bfloat16* __restrict__ scales,
@@ -58,14 +58,19 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ codes, const __nv_bfl
   }
 }
 
+// Persistent, prefetching form: the grid is two CTAs per SM; every warp walks row groups of QG_ROWS weight rows.
+// For 4-bit codes one shared-memory lookup per code byte yields two dequantised values (a 256-entry table of value
+// pairs built from the 16-entry code book); the group scale (and zero point) is applied once per 16-byte vector to
+// the partial dot product instead of to every weight:  sum_k (lut[c_k] s + z) x_k = s * sum lut[c_k] x_k + z * sum x_k.
 template <int M>
 __global__ void __launch_bounds__(QG_THREADS)
 qgemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* __restrict__ codes,
              const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ zeros,
              const float* __restrict__ lut, int bits, int N, int K, int group, __nv_bfloat16* __restrict__ out,
              long long ldo, const __nv_bfloat16* __restrict__ bias) {
-  __shared__ float s_lut[256];
-  for (int i = threadIdx.x; i < (1 << bits); i += blockDim.x) s_lut[i] = lut[i];
+  __shared__ float2 s_pair[256];   // 4-bit: (low nibble value, high nibble value); 8-bit: (value, unused)
+  for (int i = threadIdx.x; i < 256; i += blockDim.x)
+    s_pair[i] = bits == 4 ? make_float2(lut[i & 15], lut[i >> 4]) : make_float2(lut[i], 0.f);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = QG_THREADS / 32;
@@ -73,62 +78,81 @@ qgemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* 
   const int groups = K / group;
   const long long row_bytes = (long long)K * bits / 8;
   const int nvec = K / per16;
-  for (int n0 = (blockIdx.x * warps + warp) * QG_ROWS; n0 < N; n0 += gridDim.x * warps * QG_ROWS) {
+  const int n_groups_rows = (N + QG_ROWS - 1) / QG_ROWS;
+  for (int rg = blockIdx.x * warps + warp; rg < n_groups_rows; rg += gridDim.x * warps) {
+    const int n0 = rg * QG_ROWS;
     float acc[M][QG_ROWS];
 #pragma unroll
     for (int m = 0; m < M; ++m)
 #pragma unroll
       for (int r = 0; r < QG_ROWS; ++r) acc[m][r] = 0.f;
-    for (int v = lane; v < nvec; v += 32) {
-      const int k0 = v * per16;
-      uint4 q[QG_ROWS];
+    uint4 q[QG_ROWS], qn[QG_ROWS];
+    auto load_codes = [&](int v, uint4 (&dst)[QG_ROWS]) {
 #pragma unroll
       for (int r = 0; r < QG_ROWS; ++r)
-        q[r] = (n0 + r < N) ? *reinterpret_cast<const uint4*>(codes + (long long)(n0 + r) * row_bytes + (long long)k0 * bits / 8)
-                            : make_uint4(0, 0, 0, 0);
-      // a group never straddles a 16-byte code vector when group >= weights per vector (checked on the host)
+        dst[r] = (n0 + r < N && v < nvec)
+                     ? __ldg(reinterpret_cast<const uint4*>(codes + (long long)(n0 + r) * row_bytes + (long long)v * 16))
+                     : make_uint4(0, 0, 0, 0);
+    };
+    load_codes(lane, q);
+    for (int v = lane; v < nvec; v += 32) {
+      load_codes(v + 32, qn);                 // prefetch the next vector of every row while this one is consumed
+      const int k0 = v * per16;
       const int g = k0 / group;
-      float sc[QG_ROWS], zr[QG_ROWS];
+      float part[M][QG_ROWS], xsum[M];
 #pragma unroll
-      for (int r = 0; r < QG_ROWS; ++r) {
-        const bool ok = n0 + r < N;
-        sc[r] = ok ? __bfloat162float(scales[(long long)(n0 + r) * groups + g]) : 0.f;
-        zr[r] = (ok && zeros) ? __bfloat162float(zeros[(long long)(n0 + r) * groups + g]) : 0.f;
+      for (int m = 0; m < M; ++m) {
+        xsum[m] = 0.f;
+#pragma unroll
+        for (int r = 0; r < QG_ROWS; ++r) part[m][r] = 0.f;
       }
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {          // four 32-bit words of codes = 8 (4-bit) or 4 (8-bit) weights each
-        const int nw = bits == 4 ? 8 : 4;
+      for (int c = 0; c < 4; ++c) {           // one 32-bit word of codes per row: 8 (4-bit) or 4 (8-bit) weights
         float xv[M][8];
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          const __nv_bfloat16* xp = x + m * ldx + k0 + c * nw;
           if (bits == 4) {
-            const uint4 xx = *reinterpret_cast<const uint4*>(xp);
+            const uint4 xx = *reinterpret_cast<const uint4*>(x + m * ldx + k0 + c * 8);
             float2 f;
             f = unpack_bf16x2(xx.x); xv[m][0] = f.x; xv[m][1] = f.y;
             f = unpack_bf16x2(xx.y); xv[m][2] = f.x; xv[m][3] = f.y;
             f = unpack_bf16x2(xx.z); xv[m][4] = f.x; xv[m][5] = f.y;
             f = unpack_bf16x2(xx.w); xv[m][6] = f.x; xv[m][7] = f.y;
+            xsum[m] += (xv[m][0] + xv[m][1]) + (xv[m][2] + xv[m][3]) + (xv[m][4] + xv[m][5]) + (xv[m][6] + xv[m][7]);
           } else {
-            const uint2 xx = *reinterpret_cast<const uint2*>(xp);
+            const uint2 xx = *reinterpret_cast<const uint2*>(x + m * ldx + k0 + c * 4);
             float2 f;
             f = unpack_bf16x2(xx.x); xv[m][0] = f.x; xv[m][1] = f.y;
             f = unpack_bf16x2(xx.y); xv[m][2] = f.x; xv[m][3] = f.y;
+            xsum[m] += (xv[m][0] + xv[m][1]) + (xv[m][2] + xv[m][3]);
           }
         }
 #pragma unroll
         for (int r = 0; r < QG_ROWS; ++r) {
           const uint32_t word = c == 0 ? q[r].x : c == 1 ? q[r].y : c == 2 ? q[r].z : q[r].w;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (i >= nw) break;
-            const uint32_t code = bits == 4 ? (word >> (i * 4)) & 0xF : (word >> (i * 8)) & 0xFF;
-            const float wv = s_lut[code] * sc[r] + zr[r];
+          for (int bb = 0; bb < 4; ++bb) {
+            const float2 w2 = s_pair[(word >> (8 * bb)) & 0xFF];
+            if (bits == 4) {
 #pragma unroll
-            for (int m = 0; m < M; ++m) acc[m][r] += wv * xv[m][i];
+              for (int m = 0; m < M; ++m) part[m][r] += w2.x * xv[m][2 * bb] + w2.y * xv[m][2 * bb + 1];
+            } else {
+#pragma unroll
+              for (int m = 0; m < M; ++m) part[m][r] += w2.x * xv[m][bb];
+            }
           }
         }
       }
+#pragma unroll
+      for (int r = 0; r < QG_ROWS; ++r) {
+        const bool ok = n0 + r < N;
+        const float sc = ok ? __bfloat162float(scales[(long long)(n0 + r) * groups + g]) : 0.f;
+        const float zr = (ok && zeros) ? __bfloat162float(zeros[(long long)(n0 + r) * groups + g]) : 0.f;
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[m][r] += sc * part[m][r] + zr * xsum[m];
+      }
+#pragma unroll
+      for (int r = 0; r < QG_ROWS; ++r) q[r] = qn[r];
     }
 #pragma unroll
     for (int m = 0; m < M; ++m)
@@ -183,7 +207,7 @@ EDL_HOST_API int edl_qgemv(const void* x, long long ldx, const void* codes, cons
   }
   const int rows_per_cta = (QG_THREADS / 32) * QG_ROWS;
   int blocks = (N + rows_per_cta - 1) / rows_per_cta;
-  const int cap = sm_count() * 8;
+  const int cap = sm_count() * 2;   // persistent: warps loop over row groups
   if (blocks > cap) blocks = cap;
   cudaStream_t s = (cudaStream_t)stream;
 #define EDL_QGEMV_CASE(MM)                                                                                          \

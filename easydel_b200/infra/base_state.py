@@ -85,6 +85,12 @@ class EasyDeLState:
         flat.fold_param_grads()
         self.step += 1
         lr = tx.lr_at(self.step - 1)
+        ep_group, ep = self._expert_parallel()
+        if ep > 1:
+            # replicated parameters: sum over the ranks' different tokens; then everything is the gradient of the
+            # sum of the per-rank mean losses, so one factor 1/ep turns it into the global mean
+            flat.sync_replicated_grads(ep_group)
+            grad_scale = grad_scale / ep
         if self._dist is not None:
             norm = self._dist.step(tx, step=self.step, lr=lr, grad_scale=grad_scale, zero_grad=zero_grad)
             self.last_grad_norm = norm
@@ -98,6 +104,15 @@ class EasyDeLState:
                 self._sumsq = torch.zeros(1, dtype=torch.float32, device=g.device)
             self._sumsq.zero_()
             K.sumsq_(self._sumsq, g)
+            if ep > 1:   # every rank must clip with the same global norm: add the other ranks' expert gradients
+                import torch.distributed as dist
+
+                rep = torch.zeros_like(self._sumsq)
+                for lo, hi in flat.replicated_ranges():
+                    K.sumsq_(rep, flat.grad[lo:hi])
+                local_experts = self._sumsq - rep
+                dist.all_reduce(local_experts, group=ep_group)
+                self._sumsq.copy_(rep + local_experts)
             norm, coef, skip = K.clip_coef(self._sumsq, grad_scale, tx.clip_grad or 0.0)
         else:
             norm = g.float().norm() * grad_scale
@@ -111,6 +126,12 @@ class EasyDeLState:
                       gscale_tensor=coef, skip_tensor=skip, decay=decay, zero_grad=zero_grad)
         self.last_grad_norm = norm
         return norm
+
+    def _expert_parallel(self):
+        mesh = getattr(getattr(self.model, "config", None), "mesh", None)
+        if mesh is None or getattr(mesh, "ep", 1) <= 1:
+            return None, 1
+        return mesh.get_group("ep"), mesh.ep
 
     def zero_grad(self) -> None:
         if self.flat is not None:

@@ -94,6 +94,9 @@ class MoEBlock(nn.Module):
                                       expert_init_std, "column")
         self.down_proj = MoELinear(self.num_local_experts, moe_intermediate_size, hidden_size, dtype,
                                    expert_init_std, "row")
+        if ep_size > 1:   # these weights differ per rank: their gradients are not summed over the group
+            self.gate_up_proj.weight._ep_local = True
+            self.down_proj.weight._ep_local = True
         self.shared_experts = None
         self.shared_expert_gate = None
         if shared_intermediate_size > 0:

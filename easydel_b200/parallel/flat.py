@@ -105,6 +105,28 @@ class FlatParams:
                 runs.append((lo, hi, decay))
         return runs
 
+    def replicated_ranges(self) -> list[tuple[int, int]]:
+        """Maximal runs of the flat buffer that hold parameters replicated across the expert-parallel group
+        (everything except the per-rank expert weights, which are tagged ``_ep_local`` by the MoE block)."""
+        runs: list[tuple[int, int]] = []
+        for i, (n, o, sz, _, _) in enumerate(self.entries):
+            if getattr(self.params[n], "_ep_local", False):
+                continue
+            end = self.entries[i + 1][1] if i + 1 < len(self.entries) else self.numel
+            if runs and runs[-1][1] == o:
+                runs[-1] = (runs[-1][0], end)
+            else:
+                runs.append((o, end))
+        return runs
+
+    def sync_replicated_grads(self, group) -> None:
+        """Sums the gradients of the replicated parameters over the expert-parallel group (each rank saw different
+        tokens); expert weights already received every token's contribution through the token exchange."""
+        import torch.distributed as dist
+
+        for lo, hi in self.replicated_ranges():
+            dist.all_reduce(self.grad[lo:hi], group=group)
+
     def zero_grad(self) -> None:
         self.grad.zero_()
 

@@ -151,3 +151,47 @@ def _ep_worker(rank, world):
 
 def test_expert_parallel_block_matches_single_rank():
     _run(_ep_worker, 2)
+
+
+def _ep_step_worker(rank, world):
+    """One optimizer step of an expert-parallel model equals the single-rank step on the union of the data."""
+    from easydel_b200.infra.base_state import EasyDeLState
+    from easydel_b200.modules.families import Qwen3MoeConfig, Qwen3MoeForCausalLM
+    from easydel_b200.optimizers import OptimizerFactory, SchedulerConfig
+    from easydel_b200.parallel.mesh import DeviceMesh
+
+    kw = dict(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=8, moe_intermediate_size=16, num_experts=4, num_experts_per_tok=2,
+              norm_topk_prob=True, router_aux_loss_coef=0.0, max_position_embeddings=32)
+    full_cfg = Qwen3MoeConfig(**kw)
+    full_cfg.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), full_cfg.sharding_axis_names, 0, 1))
+    torch.manual_seed(0)
+    full = Qwen3MoeForCausalLM(full_cfg, dtype=torch.float32, param_dtype=torch.float32)
+    cfg = Qwen3MoeConfig(sharding_axis_dims=(1, 1, world, 1, 1), **kw)
+    model = Qwen3MoeForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32)
+    El = 4 // world
+    sd = {}
+    for k, v in full.state_dict().items():
+        sd[k] = v[rank * El:(rank + 1) * El].clone() if (v.dim() == 3 and v.shape[0] == 4) else v.clone()
+    model.load_state_dict(sd)
+    ids = torch.randint(0, 64, (world, 2, 16), generator=torch.Generator().manual_seed(5))
+
+    def step(m, batch):
+        tx, _ = OptimizerFactory.create("adamw", SchedulerConfig(None, learning_rate=1e-2), weight_decay=0.0,
+                                        clip_grad=0.5)
+        st = EasyDeLState.create(model=m, tx=tx, init_opt_state=True)
+        _, met = m.compute_loss(input_ids=batch, labels=batch)
+        met.loss.backward()
+        return st.apply_gradients()
+
+    n_full = step(full, ids.reshape(world * 2, 16))
+    n_ep = step(model, ids[rank])
+    assert abs(float(n_full) - float(n_ep)) < 1e-4 * max(1.0, float(n_full)), (float(n_full), float(n_ep))
+    ref = full.state_dict()
+    for k, v in model.state_dict().items():
+        want = ref[k][rank * El:(rank + 1) * El] if (ref[k].dim() == 3 and ref[k].shape[0] == 4) else ref[k]
+        assert torch.allclose(v, want, atol=2e-5), k
+
+
+def test_expert_parallel_training_step_matches_single_rank():
+    _run(_ep_step_worker, 2)
