@@ -11,3 +11,6 @@ from .mamba import *  # noqa: F401,F403
 from .auto import *  # noqa: F401,F403
 from . import roberta  # noqa: F401
 from .roberta import *  # noqa: F401,F403
+from . import vision, llava  # noqa: F401
+from .vision import *  # noqa: F401,F403
+from .llava import *  # noqa: F401,F403

@@ -1,0 +1,98 @@
+"""LLaVA (CLIP tower + projector + Llama), the SigLIP tower and RoBERTa against Hugging Face on CPU."""
+
+import torch
+import transformers
+
+from easydel_b200.utils.parameters_transformation import hf_to_internal, internal_to_hf
+
+VKW = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4, image_size=28,
+           patch_size=14)
+TKW = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+           num_key_value_heads=2)
+
+
+def _jitter(model):
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.05)
+
+
+def test_llava_matches_hf_trains_and_generates():
+    from easydel_b200.modules.llava import LlavaConfig, LlavaForConditionalGeneration
+
+    cfg = LlavaConfig(vision_config=dict(model_type="clip_vision_model", **VKW),
+                      text_config=dict(model_type="llama", **TKW), image_token_index=127)
+    torch.manual_seed(0)
+    m = LlavaForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.LlavaForConditionalGeneration(transformers.LlavaConfig(
+        vision_config=transformers.CLIPVisionConfig(**VKW), text_config=transformers.LlamaConfig(**TKW),
+        image_token_index=127)).float().eval()
+    missing, unexpected = hf.load_state_dict(internal_to_hf(m), strict=False)
+    assert not unexpected and all("position_ids" in x for x in missing), (missing, unexpected)
+    ids = torch.randint(0, 120, (2, 12))
+    ids[:, 2:6] = 127
+    pix = torch.randn(2, 3, 28, 28)
+    with torch.no_grad():
+        a, b = m(input_ids=ids, pixel_values=pix).logits, hf(input_ids=ids, pixel_values=pix).logits
+    assert (a - b).abs().max() < 2e-4
+    back = hf_to_internal(m, hf.state_dict())
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    _, met = m.compute_loss(input_ids=ids, pixel_values=pix, labels=ids)
+    met.loss.backward()
+    assert torch.isfinite(met.loss)
+    # incremental decoding: image features enter with the prompt only
+    cache = m.init_cache(2, 16)
+    with torch.no_grad():
+        o1 = m(input_ids=ids[:, :10], pixel_values=pix, past_key_values=cache).logits
+        cache.advance(10)
+        o2 = m(input_ids=ids[:, 10:11], past_key_values=cache).logits
+    assert (o2[:, 0] - a[:, 10]).abs().max() < 2e-4 and (o1 - a[:, :10]).abs().max() < 2e-4
+
+
+def test_siglip_tower_matches_hf():
+    from easydel_b200.modules.vision import SiglipVisionConfig, SiglipVisionModel
+
+    kw = dict(VKW, patch_size=14)
+    m = SiglipVisionModel(SiglipVisionConfig(**kw), dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf_cfg = transformers.SiglipVisionConfig(**kw, vision_use_head=False) if "vision_use_head" in \
+        transformers.SiglipVisionConfig().to_dict() else transformers.SiglipVisionConfig(**kw)
+    hf = transformers.SiglipVisionModel(hf_cfg).float().eval()
+    missing, unexpected = hf.load_state_dict(internal_to_hf(m), strict=False)
+    assert not unexpected and all("head" in x or "position_ids" in x for x in missing), (missing, unexpected)
+    pix = torch.randn(2, 3, 28, 28)
+    with torch.no_grad():
+        a = m(pix).last_hidden_state
+        b = hf(pixel_values=pix).last_hidden_state
+    assert (a - b).abs().max() < 2e-4
+
+
+def test_roberta_heads_match_hf():
+    from easydel_b200.modules.roberta import RobertaConfig, RobertaForMaskedLM, RobertaForSequenceClassification
+
+    kw = dict(vocab_size=128, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+              max_position_embeddings=40, type_vocab_size=1)
+    ids = torch.randint(3, 128, (2, 12))
+    ids[1, 8:] = 1
+    att = (ids != 1).long()
+    m = RobertaForMaskedLM(RobertaConfig(**kw), dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.RobertaForMaskedLM(transformers.RobertaConfig(**kw)).float().eval()
+    sd = internal_to_hf(m)
+    sd["lm_head.decoder.weight"], sd["lm_head.decoder.bias"] = sd["roberta.embeddings.word_embeddings.weight"], \
+        sd["lm_head.bias"]
+    missing, unexpected = hf.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected
+    with torch.no_grad():
+        a, b = m(input_ids=ids, attention_mask=att).logits, hf(input_ids=ids, attention_mask=att).logits
+    assert (a - b)[att.bool()].abs().max() < 2e-3
+    c = RobertaForSequenceClassification(RobertaConfig(num_labels=3, **kw), dtype=torch.float32,
+                                         param_dtype=torch.float32).eval()
+    hfc = transformers.RobertaForSequenceClassification(transformers.RobertaConfig(num_labels=3, **kw)).float().eval()
+    missing, unexpected = hfc.load_state_dict(internal_to_hf(c), strict=False)
+    assert not missing and not unexpected
+    with torch.no_grad():
+        assert (c(input_ids=ids, attention_mask=att).logits - hfc(input_ids=ids, attention_mask=att).logits
+                ).abs().max() < 2e-3
