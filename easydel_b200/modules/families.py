@@ -371,5 +371,25 @@ EXPORTS.update(define_family(
     _glm4_moe_spec, class_prefix="Glm4Moe",
     rules=[("mlp.gate.e_score_correction_bias", "mlp.e_score_correction_bias")], with_classifier=False))
 
+
+
+# ---- exaone4 (easydel/modules/exaone4): post-norm blocks, per-head QK norm, local layers rotate / global layers do not
+def _exaone4_spec(c):
+    n = c.num_hidden_layers
+    if c.sliding_window:
+        lt = getattr(c, "layer_types", None)
+        pat = getattr(c, "sliding_window_pattern", 4) or 4
+        types = tuple(("sliding" if "sliding" in t else "nope") for t in lt) if lt else \
+            tuple("nope" if (i + 1) % pat == 0 else "sliding" for i in range(n))
+    else:
+        types = None
+    return base_spec(c, residual="post", qk_norm="rms_head", sliding_window=c.sliding_window, layer_types=types)
+
+
+EXPORTS.update(define_family(
+    "exaone4", _d(vocab_size=102400, hidden_size=4096, intermediate_size=16384, rms_norm_eps=1e-5,
+                  sliding_window=4096, sliding_window_pattern=4, layer_types=None, max_position_embeddings=2048),
+    _exaone4_spec))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

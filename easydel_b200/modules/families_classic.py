@@ -247,5 +247,36 @@ EXPORTS.update(define_family(
     rules=_falcon_rules,
     tensor_in=_falcon_qkv(True), tensor_out=_falcon_qkv(False), hf_keeps_fused=("qkv_proj",), layernorm_names=_LN))
 
+
+
+# ---- mpt (easydel/modules/mosaic_mpt): ALiBi, bias-free LayerNorm and linears, fused Wqkv stored as q | k | v ------
+def _mpt_spec(c) -> ArchSpec:
+    ac = c.attn_config if isinstance(c.attn_config, dict) else c.attn_config.to_dict()
+    return ArchSpec(hidden_size=c.d_model, num_layers=c.n_layers, num_heads=c.n_heads, num_kv_heads=c.n_heads,
+                    head_dim=c.d_model // c.n_heads, intermediate_size=int(c.expansion_ratio * c.d_model),
+                    vocab_size=c.vocab_size, max_position=c.max_seq_len, norm="layer", norm_bias=not c.no_bias,
+                    norm_eps=c.layer_norm_epsilon, act="gelu", mlp="plain", mlp_bias=not c.no_bias,
+                    attn_bias=not c.no_bias, o_bias=not c.no_bias, rope=None,
+                    pos_emb="alibi" if ac.get("alibi", True) else "learned", tie_embeddings=True,
+                    init_std=c.initializer_range, clip_qkv=ac.get("clip_qkv"), attn_scale=ac.get("softmax_scale"))
+
+
+EXPORTS.update(define_family(
+    "mpt", dict(d_model=2048, n_heads=16, n_layers=24, expansion_ratio=4, max_seq_len=2048, vocab_size=50368,
+                resid_pdrop=0.0, layer_norm_epsilon=1e-5, emb_pdrop=0.0, learned_pos_emb=True,
+                attn_config={"alibi": True, "clip_qkv": None, "softmax_scale": None, "qk_ln": False,
+                             "attn_pdrop": 0, "alibi_bias_max": 8}, init_device="cpu", logit_scale=None,
+                no_bias=True, verbose=0, embedding_fraction=1.0, norm_type="low_precision_layernorm",
+                use_cache=False, initializer_range=0.02, tie_word_embeddings=True),
+    _mpt_spec, class_prefix="Mpt",
+    rules=[("transformer.wte.", "model.embed_tokens."), ("transformer.wpe.", "model.embed_positions."),
+           ("transformer.norm_f.", "model.norm."), ("transformer.blocks.", "model.layers."),
+           (".norm_1.", ".input_layernorm."), (".norm_2.", ".post_attention_layernorm."),
+           (".attn.Wqkv.", ".self_attn.qkv_proj."), (".attn.out_proj.", ".self_attn.o_proj."),
+           (".ffn.up_proj.", ".mlp.fc1."), (".ffn.down_proj.", ".mlp.fc2.")],
+    hf_keeps_fused=("qkv_proj",), layernorm_names=_LN,
+    attribute_map={"hidden_size": "d_model", "num_attention_heads": "n_heads", "num_hidden_layers": "n_layers",
+                   "max_position_embeddings": "max_seq_len"}))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

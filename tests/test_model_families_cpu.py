@@ -66,6 +66,8 @@ CASES = {
                                    num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=16,
                                    n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1, use_qk_norm=True,
                                    first_k_dense_replace=1, max_position_embeddings=256, pad_token_id=0)),
+    "exaone4": dict(sliding_window=32, sliding_window_pattern=2, head_dim=16),
+    "mpt": dict(_replace=dict(d_model=128, n_heads=8, n_layers=3, max_seq_len=256, vocab_size=512)),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                       shared_expert_intermediate_size=96),
 }
