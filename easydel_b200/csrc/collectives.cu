@@ -214,3 +214,143 @@ EDL_HOST_API int edl_peer_reduce_bf16(const unsigned long long* ptrs, int nranks
                                                                                                nvec, (uint4*)out);
   return check_cuda(cudaGetLastError(), "peer_reduce launch");
 }
+
+// ---- one-shot all-reduce fused with the residual add and the RMSNorm that follow a row-parallel linear -----------
+// Every rank's partial [rows, width] sits in its symmetric slot. One CTA owns a row at a time: it sums the peers'
+// partials in rank order, adds the residual stream, writes the new residual stream, reduces the row's sum of squares
+// and writes the normalised row times (weight + w_offset). Flags, call counter and slot rules are those of the plain
+// one-shot kernel above. width must be a multiple of 8 and at most 16384.
+namespace edl {
+namespace {
+
+constexpr int ARN_THREADS = 256;
+constexpr int ARN_MAX_VEC = 8;   // uint4 vectors per thread: width <= 256 * 8 * 8 = 16384
+
+__global__ void __launch_bounds__(ARN_THREADS)
+allreduce_add_rmsnorm_kernel(PeerPtrs data, PeerPtrs flags, int nranks, int rank, int* sync,
+                             const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ weight,
+                             float eps, float w_offset, __nv_bfloat16* __restrict__ x_out,
+                             __nv_bfloat16* __restrict__ h_out, int rows, int width, long long spin_limit,
+                             int* status) {
+  __shared__ int s_ok;
+  __shared__ float red[32];
+  const int epoch = *reinterpret_cast<volatile int*>(sync) + 1;
+  if (blockIdx.x == 0 && threadIdx.x < nranks)
+    st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + rank, epoch);
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    const int* mine = reinterpret_cast<const int*>(flags.p[rank]);
+    const long long t0 = clock64();
+    for (int r = 0; r < nranks && ok; ++r) {
+      while (ld_acquire_sys(mine + r) < epoch) {
+        if (clock64() - t0 > spin_limit) {
+          ok = 0;
+          if (status) atomicCAS(status, 0, EDL_TIMEOUT_PEER_FLAG);
+          break;
+        }
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  const int vec_per_row = width / 8;
+  if (s_ok) {
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+      float v[ARN_MAX_VEC][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < ARN_MAX_VEC; ++j) {
+        const int c = threadIdx.x + j * ARN_THREADS;
+        if (c >= vec_per_row) break;
+        const long long off = (long long)row * vec_per_row + c;
+        uint4 part[MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < nranks) part[r] = reinterpret_cast<const uint4*>(data.p[r])[off];
+        const uint4 rs = reinterpret_cast<const uint4*>(residual)[off];
+        float2 f;
+        f = unpack_bf16x2(rs.x); v[j][0] = f.x; v[j][1] = f.y;
+        f = unpack_bf16x2(rs.y); v[j][2] = f.x; v[j][3] = f.y;
+        f = unpack_bf16x2(rs.z); v[j][4] = f.x; v[j][5] = f.y;
+        f = unpack_bf16x2(rs.w); v[j][6] = f.x; v[j][7] = f.y;
+        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) {
+          if (r >= nranks) break;
+          f = unpack_bf16x2(part[r].x); a[0] += f.x; a[1] += f.y;
+          f = unpack_bf16x2(part[r].y); a[2] += f.x; a[3] += f.y;
+          f = unpack_bf16x2(part[r].z); a[4] += f.x; a[5] += f.y;
+          f = unpack_bf16x2(part[r].w); a[6] += f.x; a[7] += f.y;
+        }
+        // the sum of the partials is rounded to bf16 before it joins the residual stream, as the unfused
+        // sequence (all-reduce to bf16, then add) does
+        uint4 o;
+        uint32_t* ow = &o.x;
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const float2 y = unpack_bf16x2(pack_bf16x2(a[e], a[e + 1]));
+          const uint32_t packed = pack_bf16x2(v[j][e] + y.x, v[j][e + 1] + y.y);
+          ow[e >> 1] = packed;
+          const float2 z = unpack_bf16x2(packed);
+          v[j][e] = z.x;
+          v[j][e + 1] = z.y;
+          ss += z.x * z.x + z.y * z.y;
+        }
+        reinterpret_cast<uint4*>(x_out)[off] = o;
+      }
+      ss = block_sum(ss, red);
+      const float rstd = rsqrtf(ss / (float)width + eps);
+#pragma unroll
+      for (int j = 0; j < ARN_MAX_VEC; ++j) {
+        const int c = threadIdx.x + j * ARN_THREADS;
+        if (c >= vec_per_row) break;
+        const uint4 wv = reinterpret_cast<const uint4*>(weight)[c];
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        uint4 o;
+        uint32_t* ow = &o.x;
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const float2 w2 = unpack_bf16x2(ww[e >> 1]);
+          ow[e >> 1] = pack_bf16x2(v[j][e] * rstd * (w2.x + w_offset), v[j][e + 1] * rstd * (w2.y + w_offset));
+        }
+        reinterpret_cast<uint4*>(h_out)[(long long)row * vec_per_row + c] = o;
+      }
+      __syncthreads();
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(sync + 1, 1) == (int)gridDim.x - 1) {
+      sync[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile int*>(sync) = epoch;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace edl
+
+EDL_HOST_API int edl_allreduce_add_rmsnorm(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs,
+                                           int nranks, int rank, int* sync, const void* residual, const void* weight,
+                                           float eps, float w_offset, void* x_out, void* h_out, int rows, int width,
+                                           int wait_ms, int* status, void* stream) {
+  if (rows <= 0) return 0;
+  if (nranks < 1 || nranks > MAX_RANKS || (width & 7) || width > ARN_THREADS * ARN_MAX_VEC * 8) {
+    set_last_error("edl_allreduce_add_rmsnorm: nranks=%d, width=%d must be a multiple of 8 and <= %d", nranks, width,
+                   ARN_THREADS * ARN_MAX_VEC * 8);
+    return -1;
+  }
+  PeerPtrs d, f;
+  for (int r = 0; r < nranks; ++r) {
+    d.p[r] = reinterpret_cast<void*>(data_ptrs[r]);
+    f.p[r] = reinterpret_cast<void*>(flag_ptrs[r]);
+  }
+  int blocks = rows < sm_count() * 2 ? rows : sm_count() * 2;
+  const long long spin = (long long)(wait_ms > 0 ? wait_ms : 2000) * 2000000LL;
+  allreduce_add_rmsnorm_kernel<<<blocks, ARN_THREADS, 0, (cudaStream_t)stream>>>(
+      d, f, nranks, rank, sync, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)weight, eps, w_offset,
+      (__nv_bfloat16*)x_out, (__nv_bfloat16*)h_out, rows, width, spin, status);
+  return check_cuda(cudaGetLastError(), "allreduce_add_rmsnorm launch");
+}

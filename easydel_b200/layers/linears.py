@@ -105,13 +105,16 @@ class ColumnParallelLinear(ParallelLinear):
 
 class RowParallelLinear(ParallelLinear):
     parallel_style = "row"
+    # When set (by a decoder layer whose next operation is the fused residual-add + RMSNorm), small inference
+    # products return a ``parallel.tp.PendingReduce`` so that the all-reduce is fused into that norm.
+    defer_reduce = False
 
-    def forward(self, x: torch.Tensor, w: torch.Tensor | None = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, w: torch.Tensor | None = None):
         if self.tp_size > 1:
             from ..parallel import tp as tpar
 
             return tpar.row_parallel_linear(x, self.weight if w is None else w, self.bias, self.tp_group,
-                                            scale=self.scale)
+                                            scale=self.scale, defer=self.defer_reduce)
         return super().forward(x, w)
 
 

@@ -25,8 +25,11 @@ class RMSNorm(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return F.rms_norm(x, self.weight, self.eps, self.offset)
 
-    def forward_with_residual(self, x: torch.Tensor, residual: torch.Tensor):
-        """Returns (norm(x + residual), x + residual) from one kernel."""
+    def forward_with_residual(self, x, residual: torch.Tensor):
+        """Returns (norm(x + residual), x + residual) from one kernel. ``x`` may be a pending tensor-parallel
+        reduction, in which case the sum over ranks happens in the same kernel."""
+        if hasattr(x, "add_rms_norm"):
+            return x.add_rms_norm(residual, self.weight, self.eps, self.offset)
         return F.add_rms_norm(x, residual, self.weight, self.eps, self.offset)
 
     def extra_repr(self) -> str:

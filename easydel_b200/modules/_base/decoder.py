@@ -109,6 +109,11 @@ def _norm(spec: ArchSpec, dtype) -> nn.Module:
     return LayerNorm(spec.hidden_size, spec.norm_eps, bias=spec.norm_bias, dtype=dtype)
 
 
+def _resolve(x):
+    """Tensor-parallel products may arrive as pending reductions (see ``parallel.tp.PendingReduce``)."""
+    return x.resolve() if hasattr(x, "resolve") else x
+
+
 def _tp_of(config) -> tuple[int, int, tp.Any]:
     mesh = config.mesh
     if mesh.tp > 1:
@@ -147,6 +152,13 @@ class DecoderLayer(nn.Module):
         moe = spec.moe
         self.is_moe = moe is not None and (moe.layers is None or layer_idx in moe.layers)
         self._build_mlp(config, spec, layer_idx, dtype, tp_size, tp_rank, tp_group)
+        fused = spec.norm == "rms" and spec.residual == "pre" and not spec.sandwich_norm \
+            and spec.residual_multiplier is None
+        if fused and tp_size > 1 and spec.mla is None:
+            # both branch outputs feed a fused add+norm: let it also do the tensor-parallel sum
+            self.self_attn.o_proj.defer_reduce = True
+            if not self.is_moe:
+                (self.mlp.down_proj if hasattr(self.mlp, "down_proj") else self.mlp.fc2).defer_reduce = True
 
     @staticmethod
     def _mha(spec, layer_idx, dtype, rope, window, tp_size, tp_rank, tp_group):
@@ -207,7 +219,7 @@ class DecoderLayer(nn.Module):
                 m, rl = m
             return x, m, rl
         if pending is not None:
-            x = x + pending
+            x = x + _resolve(pending)
         rm = spec.residual_multiplier or 1.0
         if spec.residual == "parallel":
             h = self.input_layernorm(x)
@@ -311,6 +323,7 @@ class DecoderModel(EasyDeLBaseModule):
         router_logits = []
         for i, layer in enumerate(self.layers):
             if output_hidden_states:
+                pending = _resolve(pending)
                 all_hidden.append(x if pending is None else x + pending)
             view = past_key_values.view(i) if past_key_values is not None else None
             x, pending, rl = self._run_layer(layer, x, pending, position_ids, segment_ids, view, cache_metadata,
@@ -321,9 +334,9 @@ class DecoderModel(EasyDeLBaseModule):
             if pending is not None and spec.norm == "rms":
                 x, _ = self.norm.forward_with_residual(pending, x)
             else:
-                x = self.norm(x if pending is None else x + pending)
+                x = self.norm(x if pending is None else x + _resolve(pending))
         elif pending is not None:
-            x = x + pending
+            x = x + _resolve(pending)
         if output_hidden_states:
             all_hidden.append(x)
         cls = MoeModelOutput if spec.moe is not None else BaseModelOutput

@@ -24,6 +24,10 @@ from ..ops import _lib
 _lib.register("edl_allreduce_oneshot", _lib.i32, [_lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.vp, _lib.vp, _lib.vp,
                                                   _lib.i64, _lib.i32, _lib.vp, _lib.vp])
 
+_lib.register("edl_allreduce_add_rmsnorm", _lib.i32, [_lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.vp, _lib.vp, _lib.vp,
+                                                      _lib.f32, _lib.f32, _lib.vp, _lib.vp, _lib.i32, _lib.i32,
+                                                      _lib.i32, _lib.vp, _lib.vp])
+
 ONE_SHOT_MAX_BYTES = 1 << 20
 _FLAG_BYTES = 256
 
@@ -71,6 +75,52 @@ class _PeerAllReduce:
                   self.world, self.rank, self.sync.data_ptr(), out.data_ptr(), _lib.ptr(residual), partial_in_slot.numel(),
                   wait_ms, _lib.status_word(out.device).data_ptr(), _lib.stream_ptr())
         return out
+
+
+class PendingReduce:
+    """A row-parallel product whose partial sums still sit in the symmetric slot.
+
+    The consumer either calls :meth:`add_rms_norm` (one kernel: sum over ranks + residual add + RMSNorm) or
+    :meth:`resolve` (the plain one-shot all-reduce). Exactly one of them must be called, and before the next
+    row-parallel product of the same group is formed.
+    """
+
+    def __init__(self, ctx: "_PeerAllReduce", slot: torch.Tensor, shape, bias=None, scale=None):
+        self.ctx, self.slot, self.shape, self.bias, self.scale = ctx, slot, tuple(shape), bias, scale
+        self.dtype, self.device = slot.dtype, slot.device
+
+    def resolve(self) -> torch.Tensor:
+        y = self.ctx.reduce(self.slot).view(self.shape)
+        if self.bias is not None:
+            y = y + self.bias
+        return y if self.scale is None else y * self.scale
+
+    def add_rms_norm(self, residual: torch.Tensor, weight: torch.Tensor, eps: float, w_offset: float = 0.0):
+        """Returns ``(rmsnorm(residual + sum) * (weight + w_offset), residual + sum)``."""
+        if self.bias is not None or self.scale is not None or residual.dtype != torch.bfloat16 \
+                or weight.dtype != torch.bfloat16 or self.shape[-1] > 16384:
+            y = self.resolve()
+            from ..ops import functional as F
+
+            return F.add_rms_norm(y, residual, weight, eps, w_offset)
+        c = self.ctx
+        c.epoch += 1
+        s = c.epoch & 1
+        res = residual.contiguous()
+        x_out = torch.empty_like(res)
+        h_out = torch.empty_like(res)
+        width = self.shape[-1]
+        rows = res.numel() // width
+        _lib.call("edl_allreduce_add_rmsnorm", C.cast(c.slot_ptrs[s], C.c_void_p), C.cast(c.flag_ptrs, C.c_void_p),
+                  c.world, c.rank, c.sync.data_ptr(), res.data_ptr(), weight.data_ptr(), float(eps), float(w_offset),
+                  x_out.data_ptr(), h_out.data_ptr(), rows, width, 2000, _lib.status_word(res.device).data_ptr(),
+                  _lib.stream_ptr())
+        return h_out.view(residual.shape), x_out.view(residual.shape)
+
+
+def resolve(x):
+    """Materialises a :class:`PendingReduce`; passes tensors (and ``None``) through."""
+    return x.resolve() if isinstance(x, PendingReduce) else x
 
 
 _CTX: dict[int, _PeerAllReduce] = {}
@@ -135,7 +185,7 @@ def copy_to_tp(x: torch.Tensor, group) -> torch.Tensor:
     return _CopyToTP.apply(x, group)
 
 
-def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, bias, group, scale=None) -> torch.Tensor:
+def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, bias, group, scale=None, defer: bool = False):
     """``all_reduce(x_local @ w_local.T) + bias``. In inference the GEMM writes into the symmetric slot."""
     from ..ops import functional as F
     from ..ops import kernels as K
@@ -149,6 +199,8 @@ def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, bias, group, scale=Non
                 x2 = x2.contiguous()
             slot = ctx.slot_tensor((x2.shape[0], w.shape[0]), x.dtype)
             K.gemm(x2, w, out=slot)
+            if defer:
+                return PendingReduce(ctx, slot, (*x.shape[:-1], w.shape[0]), bias, scale)
             y = ctx.reduce(slot).view(*x.shape[:-1], w.shape[0])
             if bias is not None:
                 y = y + bias

@@ -67,6 +67,27 @@ def _allreduce_worker(rank, world):
             y = tp.all_reduce(x, g)
         assert torch.allclose(y.float(), ref, atol=3e-2, rtol=2e-2), (step, (y.float() - ref).abs().max())
     assert tp._CTX, "the peer-memory path was not used"
+    # row-parallel product whose reduction is fused with the residual add and the RMSNorm that follow it
+    torch.manual_seed(7)          # same weights / inputs on every rank, then each rank keeps its K slice
+    H, Kf, R = 1024, 512, 24
+    x_full = torch.randn(R, Kf, device="cuda").to(torch.bfloat16)
+    w_full = (torch.randn(H, Kf, device="cuda") * 0.05).to(torch.bfloat16)
+    res = torch.randn(R, H, device="cuda").to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16)
+    ks = Kf // world
+    xs, ws = x_full[:, rank * ks:(rank + 1) * ks].contiguous(), w_full[:, rank * ks:(rank + 1) * ks].contiguous()
+    with torch.no_grad():
+        for it in range(3):
+            pend = tp.row_parallel_linear(xs, ws, None, g, defer=True)
+            assert isinstance(pend, tp.PendingReduce)
+            h, xn = pend.add_rms_norm(res, nw, 1e-5)
+            y = x_full.float() @ w_full.float().t()
+            xr = res.float() + y
+            hr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * nw.float()
+            assert (xn.float() - xr).abs().max() < 6e-2 * xr.abs().max(), it
+            assert (h.float() - hr).abs().max() < 6e-2 * hr.abs().max(), it
+            plain = tp.row_parallel_linear(xs, ws, None, g)       # keeps the call count even
+            assert (plain.float() - y).abs().max() < 6e-2 * y.abs().max()
 
 
 def _tp_forward_worker(rank, world):
