@@ -24,6 +24,9 @@ _LAZY: dict[str, str] = {
     "LlamaConfig": "easydel_b200.modules.llama", "LlamaModel": "easydel_b200.modules.llama",
     "LlamaForCausalLM": "easydel_b200.modules.llama",
     "LlamaForSequenceClassification": "easydel_b200.modules.llama",
+    # speech
+    "vWhisperInference": "easydel_b200.inference.vwhisper",
+    "vWhisperInferenceConfig": "easydel_b200.inference.vwhisper",
 }
 
 

@@ -14,3 +14,5 @@ from .roberta import *  # noqa: F401,F403
 from . import vision, llava  # noqa: F401
 from .vision import *  # noqa: F401,F403
 from .llava import *  # noqa: F401,F403
+from . import whisper  # noqa: F401
+from .whisper import *  # noqa: F401,F403
