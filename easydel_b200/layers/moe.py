@@ -31,13 +31,14 @@ class MoELinear(nn.Module):
     """Stacked expert weights ``[E_local, out, in]`` (ParallelMoELinear, _linear_moe.py:90-542)."""
 
     def __init__(self, num_experts: int, in_features: int, out_features: int, dtype=torch.float32,
-                 init_std: float = 0.01, parallel_style: str = "column", device=None):
+                 init_std: float = 0.01, parallel_style: str = "column", device=None, bias: bool = False):
         super().__init__()
         self.num_experts, self.in_features, self.out_features = num_experts, in_features, out_features
         self.parallel_style = parallel_style
         self.weight = nn.Parameter(torch.empty(num_experts, out_features, in_features, dtype=dtype, device=device))
         if self.weight.device.type != "meta":
             nn.init.normal_(self.weight, 0.0, init_std)
+        self.bias = nn.Parameter(torch.zeros(num_experts, out_features, dtype=dtype, device=device)) if bias else None
 
     def forward(self, x_sorted: torch.Tensor, group_sizes: torch.Tensor) -> torch.Tensor:
         return G.grouped_linear(x_sorted, self.weight, group_sizes)
@@ -76,7 +77,7 @@ class MoEBlock(nn.Module):
                  use_score_bias: bool = False, router_bias: bool = False, shared_intermediate_size: int = 0,
                  shared_gate: bool = False, dtype=torch.float32, init_std: float = 0.02, expert_init_std: float = 0.01,
                  ep_size: int = 1, ep_rank: int = 0, ep_group=None, tp_size: int = 1, tp_rank: int = 0,
-                 tp_group=None, router_dtype=None):
+                 tp_group=None, router_dtype=None, expert_bias: bool = False):
         super().__init__()
         if num_experts % ep_size:
             raise ValueError(f"{num_experts} experts not divisible by ep={ep_size}")
@@ -91,12 +92,14 @@ class MoEBlock(nn.Module):
         self.e_score_correction_bias = nn.Parameter(torch.zeros(num_experts, dtype=torch.float32)) \
             if use_score_bias else None
         self.gate_up_proj = MoELinear(self.num_local_experts, hidden_size, 2 * moe_intermediate_size, dtype,
-                                      expert_init_std, "column")
+                                      expert_init_std, "column", bias=expert_bias)
         self.down_proj = MoELinear(self.num_local_experts, moe_intermediate_size, hidden_size, dtype,
-                                   expert_init_std, "row")
+                                   expert_init_std, "row", bias=expert_bias)
         if ep_size > 1:   # these weights differ per rank: their gradients are not summed over the group
-            self.gate_up_proj.weight._ep_local = True
-            self.down_proj.weight._ep_local = True
+            for lin in (self.gate_up_proj, self.down_proj):
+                lin.weight._ep_local = True
+                if lin.bias is not None:
+                    lin.bias._ep_local = True
         self.shared_experts = None
         self.shared_expert_gate = None
         if shared_intermediate_size > 0:
@@ -146,7 +149,8 @@ class MoEBlock(nn.Module):
 
             y = epar.expert_parallel_ffn(self, x2, w, idx)
         else:
-            y = G.moe_ffn(x2, self.gate_up_proj.weight, self.down_proj.weight, w, idx, self.act)
+            y = G.moe_ffn(x2, self.gate_up_proj.weight, self.down_proj.weight, w, idx, self.act,
+                          b_gate_up=self.gate_up_proj.bias, b_down=self.down_proj.bias)
         if self.shared_experts is not None:
             s = self.shared_experts(x2)
             if self.shared_expert_gate is not None:

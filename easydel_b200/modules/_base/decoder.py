@@ -51,6 +51,8 @@ class MoESpec:
     layers: tuple[int, ...] | None = None   # None = every layer
     aux_loss_coef: float = 0.0
     expert_init_std: float = 0.01
+    expert_bias: bool = False         # per-expert biases on both expert projections (GPT-OSS)
+    expert_act: str | None = None     # gated activation of the experts when it differs from the dense MLP's
 
 
 @dataclass
@@ -173,7 +175,8 @@ class DecoderLayer(nn.Module):
         moe = spec.moe
         if self.is_moe:
             ep_size, ep_rank, ep_group = _ep_of(config)
-            self.mlp = MoEBlock(spec.hidden_size, moe.intermediate_size, moe.num_experts, moe.top_k, act=spec.act,
+            self.mlp = MoEBlock(spec.hidden_size, moe.intermediate_size, moe.num_experts, moe.top_k,
+                                act=moe.expert_act or spec.act, expert_bias=moe.expert_bias,
                                 norm_topk_prob=moe.norm_topk_prob, scoring=moe.scoring,
                                 routed_scaling_factor=moe.routed_scaling_factor, n_group=moe.n_group,
                                 topk_group=moe.topk_group, use_score_bias=moe.use_score_bias,

@@ -391,5 +391,71 @@ EXPORTS.update(define_family(
                   sliding_window=4096, sliding_window_pattern=4, layer_types=None, max_position_embeddings=2048),
     _exaone4_spec))
 
+
+
+# ---- gpt_oss (easydel/modules/gpt_oss): attention sinks, alternating sliding / full layers, YaRN; top-k router with
+# ---- bias; experts with biases and the clamped x*sigmoid(1.702x) gate. Hugging Face stores the expert tensors as
+# ---- [E, in, 2F] with gate / up columns interleaved; here they are [E, 2F, in] with the gate rows first.
+def _gpt_oss_spec(c):
+    n = c.num_hidden_layers
+    lt = _layer_types(c, n) or tuple("sliding" if i % 2 == 0 else "full" for i in range(n))
+    return base_spec(c, use_sinks=True, attn_bias=True, o_bias=True, sliding_window=c.sliding_window, layer_types=lt,
+                     moe=moe_spec(c, num_experts=c.num_local_experts, top_k=c.num_experts_per_tok,
+                                  intermediate=c.intermediate_size, norm_topk=True, router_bias=True,
+                                  expert_bias=True, expert_act="gptoss_swiglu",
+                                  aux_coef=getattr(c, "router_aux_loss_coef", 0.0)))
+
+
+def _gpt_oss_in(model, sd):
+    out = {}
+    for k, t in sd.items():
+        if k.endswith("mlp.experts.gate_up_proj"):
+            w = t.transpose(1, 2)                                    # [E, 2F, in], rows interleaved
+            out[k[:-len("experts.gate_up_proj")] + "gate_up_proj.weight"] = torch.cat([w[:, 0::2], w[:, 1::2]], 1)
+        elif k.endswith("mlp.experts.gate_up_proj_bias"):
+            out[k[:-len("experts.gate_up_proj_bias")] + "gate_up_proj.bias"] = torch.cat([t[:, 0::2], t[:, 1::2]], 1)
+        elif k.endswith("mlp.experts.down_proj"):
+            out[k[:-len("experts.down_proj")] + "down_proj.weight"] = t.transpose(1, 2)
+        elif k.endswith("mlp.experts.down_proj_bias"):
+            out[k[:-len("experts.down_proj_bias")] + "down_proj.bias"] = t
+        else:
+            out[k] = t
+    return out
+
+
+def _interleave(gate, up, dim):
+    return torch.stack([gate, up], dim + 1).flatten(dim, dim + 1)
+
+
+def _gpt_oss_out(model, sd):
+    out = {}
+    for k, t in sd.items():
+        if k.endswith("mlp.gate_up_proj.weight"):
+            f = t.shape[1] // 2
+            out[k[:-len("gate_up_proj.weight")] + "experts.gate_up_proj"] = \
+                _interleave(t[:, :f], t[:, f:], 1).transpose(1, 2).contiguous()
+        elif k.endswith("mlp.gate_up_proj.bias"):
+            f = t.shape[1] // 2
+            out[k[:-len("gate_up_proj.bias")] + "experts.gate_up_proj_bias"] = _interleave(t[:, :f], t[:, f:], 1)
+        elif k.endswith("mlp.down_proj.weight") and t.dim() == 3:
+            out[k[:-len("down_proj.weight")] + "experts.down_proj"] = t.transpose(1, 2).contiguous()
+        elif k.endswith("mlp.down_proj.bias") and t.dim() == 2:
+            out[k[:-len("down_proj.bias")] + "experts.down_proj_bias"] = t
+        else:
+            out[k] = t
+    return out
+
+
+EXPORTS.update(define_family(
+    "gpt_oss", _d(vocab_size=201088, hidden_size=2880, intermediate_size=2880, num_hidden_layers=36,
+                  num_attention_heads=64, num_key_value_heads=8, head_dim=64, num_local_experts=128,
+                  num_experts_per_tok=4, sliding_window=128, rms_norm_eps=1e-5, attention_bias=True,
+                  rope_theta=150000.0, max_position_embeddings=131072, initial_context_length=4096, layer_types=None,
+                  router_aux_loss_coef=0.9, output_router_logits=False,
+                  rope_scaling={"rope_type": "yarn", "factor": 32.0, "beta_fast": 32.0, "beta_slow": 1.0,
+                                "truncate": False, "original_max_position_embeddings": 4096}),
+    _gpt_oss_spec, class_prefix="GptOss", rules=[("mlp.router.", "mlp.gate.")], tensor_in=_gpt_oss_in,
+    tensor_out=_gpt_oss_out, hf_keeps_fused=("experts",)))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

@@ -152,6 +152,79 @@ def moe_ffn(x, w_gate_up, w_down, topk_w, topk_idx, act: str = "silu", expert_of
     return _MoEFFN.apply(x, w_gate_up, w_down, topk_w, topk_idx, act, expert_offset)
 
 
+class _GatherFn(torch.autograd.Function):
+    """Rows of ``x`` copied into the expert-sorted, 128-row-padded layout of a :class:`Routing`."""
+
+    @staticmethod
+    def forward(ctx, x, r):
+        ctx.r, ctx.shape = r, x.shape
+        return r.gather(x.contiguous())
+
+    @staticmethod
+    def backward(ctx, dxs):
+        r = ctx.r
+        T, H = ctx.shape
+        dxs = dxs.contiguous()
+        dx = torch.empty(T, H, dtype=dxs.dtype, device=dxs.device)
+        _lib.call("edl_moe_gather_bwd", dxs.data_ptr(), r.slot_pos.data_ptr(), dx.data_ptr(), T, r.k, H,
+                  _lib.stream_ptr())
+        return dx, None
+
+
+class _GroupedLinearFn(torch.autograd.Function):
+    """``ys = xs @ w[expert of row].T`` over the padded layout, with data and weight gradients."""
+
+    @staticmethod
+    def forward(ctx, xs, w, r):
+        ctx.r = r
+        ctx.save_for_backward(xs, w)
+        return _grouped_fwd(r, xs, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xs, w = ctx.saved_tensors
+        r = ctx.r
+        dy = dy.contiguous()
+        dxs = _grouped_dgrad(r, dy, w) if ctx.needs_input_grad[0] else None
+        gw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                _grouped_wgrad(r, dy, xs, mg, True)
+                w.grad_added_to_main_grad = True
+            else:
+                buf = torch.zeros(w.shape, dtype=torch.float32, device=dy.device)
+                _grouped_wgrad(r, dy, xs, buf, False)
+                gw = buf.to(w.dtype)
+        return dxs, gw, None
+
+
+def moe_ffn_composed(x, w_gate_up, w_down, topk_w, topk_idx, act, b_gate_up=None, b_down=None,
+                     expert_offset: int = 0):
+    """Expert FFN with per-expert biases and / or a gated activation outside the fused set: the two grouped GEMMs
+    run on the tensor cores, the bias adds, the activation and the weighted combine are elementwise torch ops."""
+    from . import functional as F
+
+    T, H = x.shape
+    k = topk_idx.shape[1]
+    E = w_gate_up.shape[0]
+    r = Routing(topk_idx, E, expert_offset)
+    xs = _GatherFn.apply(x, r)
+    # expert of every padded row; tiles past the used range hold arbitrary ids and are never read back
+    row_e = r.tile_expert.long().clamp(0, E - 1).repeat_interleave(128)
+    h = _GroupedLinearFn.apply(xs, w_gate_up, r)
+    if b_gate_up is not None:
+        h = h + b_gate_up[row_e]
+    a = F.gated_act(h, act)
+    ys = _GroupedLinearFn.apply(a.contiguous(), w_down, r)
+    if b_down is not None:
+        ys = ys + b_down[row_e]
+    pos = r.slot_pos.long()
+    valid = (pos >= 0).view(T, k)
+    picked = ys[pos.clamp_min(0)].view(T, k, H).float()
+    return (picked * (topk_w.float() * valid)[..., None]).sum(1).to(x.dtype)
+
+
 def grouped_linear(x_sorted, w, group_sizes):
     """Grouped linear over rows already sorted by expert with explicit sizes (API parity with
     ``grouped_matmul(x, w, group_sizes)``): re-buckets through the routing tables."""

@@ -45,8 +45,21 @@ def layer_norm(x, w, b, eps):
                         eps).to(x.dtype)
 
 
+def _gptoss_swiglu(g, u, alpha: float = 1.702, limit: float = 7.0):
+    """GPT-OSS expert activation: clamped gate through x*sigmoid(alpha x), clamped linear branch offset by one."""
+    g = g.clamp(max=limit)
+    u = u.clamp(min=-limit, max=limit)
+    return (u + 1) * (g * torch.sigmoid(g * alpha))
+
+
+# gated activations that are not of the form act(gate) * up
+GATED_FNS = {"gptoss_swiglu": _gptoss_swiglu}
+
+
 def gated_act(gu, act: str = "silu"):
     g, u = gu.chunk(2, dim=-1)
+    if act in GATED_FNS:
+        return GATED_FNS[act](g, u)
     return ACT2FN[act](g) * u
 
 

@@ -158,14 +158,16 @@ def expert_parallel_ffn(block, x: torch.Tensor, topk_w: torch.Tensor, topk_idx: 
     w_all = all_gather_tokens(topk_w.to(torch.float32).contiguous(), group).to(topk_w.dtype)
     idx_all = _ag_raw(topk_idx.to(torch.int32).contiguous(), group).long()
     offset = block.ep_rank * block.num_local_experts
-    if _lib.use_kernels(x_all):
-        y_part = G.moe_ffn(x_all, block.gate_up_proj.weight, block.down_proj.weight, w_all, idx_all, block.act,
-                           expert_offset=offset)
-    else:   # reference path: pairs owned by other ranks get weight zero
-        from ..ops import grouped
+    from ..ops import grouped
 
+    b_gu, b_d = block.gate_up_proj.bias, block.down_proj.bias
+    if _lib.use_kernels(x_all):
+        y_part = grouped.moe_ffn(x_all, block.gate_up_proj.weight, block.down_proj.weight, w_all, idx_all, block.act,
+                                 expert_offset=offset, b_gate_up=b_gu, b_down=b_d)
+    else:   # reference path: pairs owned by other ranks get weight zero
         local = idx_all - offset
         mine = (local >= 0) & (local < block.num_local_experts)
         y_part = grouped.moe_ffn(x_all, block.gate_up_proj.weight, block.down_proj.weight,
-                                 w_all * mine.to(w_all.dtype), local.clamp(0, block.num_local_experts - 1), block.act)
+                                 w_all * mine.to(w_all.dtype), local.clamp(0, block.num_local_experts - 1), block.act,
+                                 b_gate_up=b_gu, b_down=b_d)
     return reduce_scatter_tokens(y_part.contiguous(), group)

@@ -43,12 +43,14 @@ def internal_to_hf(model, state: dict[str, torch.Tensor] | None = None) -> dict[
         leaf, mod_name = parts[-1], parts[-2] if len(parts) > 1 else ""
         prefix = ".".join(parts[:-2])
         pre = prefix + "." if prefix else ""
-        if mod_name in FUSED_SPLITS and t.dim() <= 2 and mod_name not in getattr(model, "hf_keeps_fused", ()):
+        if mod_name in FUSED_SPLITS and t.dim() <= 2 and mod_name not in getattr(model, "hf_keeps_fused", ()) and \
+                hasattr(_module_of(model, ".".join(parts[:-1])), "local_out_splits"):
             mod = _module_of(model, ".".join(parts[:-1]))
             widths = mod.local_out_splits()
             for sub, chunk in zip(FUSED_SPLITS[mod_name], torch.split(t, list(widths), dim=0)):
                 out[f"{pre}{sub}.{leaf}"] = chunk
-        elif t.dim() == 3 and mod_name in ("gate_up_proj", "down_proj") and leaf == "weight":
+        elif t.dim() == 3 and mod_name in ("gate_up_proj", "down_proj") and leaf == "weight" and \
+                "experts" not in getattr(model, "hf_keeps_fused", ()):
             E = t.shape[0]
             if mod_name == "gate_up_proj":
                 F = t.shape[1] // 2

@@ -60,3 +60,26 @@ def test_moe_main_grad_accumulation_and_empty_experts():
     rel = ((wd.main_grad - 2 * wdr.grad).norm() / (2 * wdr.grad).norm()).item()
     assert rel < 0.05, rel
     assert wgu.main_grad[3:].abs().max().item() == 0
+
+
+def test_moe_ffn_with_expert_biases_and_gptoss_gate():
+    """Composed path: grouped GEMMs on the tensor cores + per-expert biases + the clamped GPT-OSS gate, against the
+    CPU composition of the same op in fp32."""
+    from easydel_b200.ops import grouped
+
+    T, H, Fd, E, k = 300, 256, 384, 8, 2
+    x, wgu, wd, w, idx = _setup(T, H, Fd, E, k, seed=5)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    bgu = (torch.randn(E, 2 * Fd, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    bd = (torch.randn(E, H, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    cpu = [t.detach().float().cpu().requires_grad_(True) for t in (x, wgu, wd, w, bgu, bd)]
+    ref = grouped.moe_ffn(cpu[0], cpu[1], cpu[2], cpu[3], idx.cpu(), "gptoss_swiglu", b_gate_up=cpu[4], b_down=cpu[5])
+    dy = torch.randn_like(ref)
+    ref.backward(dy)
+    dev = [t.detach().clone().requires_grad_(True) for t in (x, wgu, wd, w, bgu, bd)]
+    y = grouped.moe_ffn(dev[0], dev[1], dev[2], dev[3], idx, "gptoss_swiglu", b_gate_up=dev[4], b_down=dev[5])
+    assert torch.allclose(y.float().cpu(), ref.detach(), atol=4e-2, rtol=4e-2), (y.float().cpu() - ref).abs().max()
+    y.backward(dy.cuda().to(y.dtype))
+    for a, b, name in zip(dev, cpu, ("dx", "dW_gate_up", "dW_down", "dw", "db_gate_up", "db_down")):
+        rel = ((a.grad.float().cpu() - b.grad).norm() / (b.grad.norm() + 1e-8)).item()
+        assert rel < 0.05, f"{name}: {rel}"

@@ -68,6 +68,9 @@ CASES = {
                                    first_k_dense_replace=1, max_position_embeddings=256, pad_token_id=0)),
     "exaone4": dict(sliding_window=32, sliding_window_pattern=2, head_dim=16),
     "mpt": dict(_replace=dict(d_model=128, n_heads=8, n_layers=3, max_seq_len=256, vocab_size=512)),
+    "gpt_oss": dict(head_dim=16, num_local_experts=4, num_experts_per_tok=2, sliding_window=16, intermediate_size=64,
+                    rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0,
+                                  "truncate": False, "original_max_position_embeddings": 64}),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                       shared_expert_intermediate_size=96),
 }
