@@ -19,13 +19,20 @@ class TransformerCache:
         self.v = torch.zeros_like(self.k)
         self.length = 0
         self.max_len = max_len
+        self.linear: dict[int, object] = {}     # layer -> recurrent state of a linear-attention layer (hybrids)
 
     @classmethod
     def init_for_model(cls, model, batch_size: int, max_length: int, dtype=None, device=None):
         spec = model.spec
         tp_size = getattr(model.config.mesh, "tp", 1)
-        return cls(spec.num_layers, batch_size, max_length, max(1, spec.num_kv_heads // tp_size), spec.head_dim,
-                   dtype or model.dtype, device or model.device)
+        cache = cls(spec.num_layers, batch_size, max_length, max(1, spec.num_kv_heads // tp_size), spec.head_dim,
+                    dtype or model.dtype, device or model.device)
+        layers = getattr(getattr(model, "model", model), "layers", ())
+        for i, layer in enumerate(layers):
+            mixer = getattr(layer, "linear_attn", None)
+            if mixer is not None:
+                cache.linear[i] = mixer.make_state(batch_size, dtype or model.dtype, device or model.device)
+        return cache
 
     def seq_len(self) -> int:
         return self.length
@@ -40,11 +47,17 @@ class TransformerCache:
         """Beam search: re-gathers the batch rows."""
         self.k = self.k.index_select(1, index)
         self.v = self.v.index_select(1, index)
+        for st in self.linear.values():
+            st.reorder(index)
 
 
 class TransformerCacheView:
     def __init__(self, cache: TransformerCache, layer: int):
         self.cache, self.layer = cache, layer
+
+    @property
+    def linear_state(self):
+        return self.cache.linear.get(self.layer)
 
     def attend(self, attn, q, k, v, positions=None, attn_meta=None):
         c = self.cache

@@ -58,9 +58,13 @@ class Attention(nn.Module):
                  rope: dict | None = None, sliding_window: int | None = None, softcap: float = 0.0,
                  scale: float | None = None, use_sinks: bool = False, use_alibi: bool = False, causal: bool = True,
                  clip_qkv: float | None = None, dtype: torch.dtype = torch.float32, init_std: float = 0.02,
-                 tp_size: int = 1, tp_rank: int = 0, tp_group=None, qk_norm_offset: float = 0.0):
+                 tp_size: int = 1, tp_rank: int = 0, tp_group=None, qk_norm_offset: float = 0.0,
+                 output_gate: bool = False):
         super().__init__()
         self.layer_idx = layer_idx
+        # Qwen3-Next: the query projection also emits a per-channel gate ([q (D) | gate (D)] per head); the
+        # attention output is multiplied by sigmoid(gate) before the output projection
+        self.output_gate = output_gate
         self.hidden_size = hidden_size
         self.num_heads_global, self.num_kv_heads_global = num_heads, num_kv_heads
         if num_heads % tp_size:
@@ -79,7 +83,8 @@ class Attention(nn.Module):
         self.clip_qkv = clip_qkv
         self.scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
         kv_out = num_kv_heads * head_dim if not self.kv_replicated else self.num_kv_heads * head_dim * tp_size
-        self.qkv_proj = ColumnParallelLinear(hidden_size, (num_heads * head_dim, kv_out, kv_out), bias=bias,
+        self.qkv_proj = ColumnParallelLinear(hidden_size, (num_heads * head_dim * (2 if output_gate else 1), kv_out,
+                                                           kv_out), bias=bias,
                                              dtype=dtype, init_std=init_std, tp_size=tp_size, tp_rank=tp_rank,
                                              tp_group=tp_group)
         self.o_proj = RowParallelLinear(num_heads * head_dim, hidden_size, bias=o_bias, dtype=dtype,
@@ -134,6 +139,12 @@ class Attention(nn.Module):
         """hidden ``[B,T,H]``; positions ``[B,T]``. Returns ``[B,T,H]``."""
         B, T, _ = hidden.shape
         qkv = self.qkv_proj(hidden)
+        gate = None
+        if self.output_gate:
+            Hq, D = self.num_heads, self.head_dim
+            qg = qkv[..., : 2 * Hq * D].view(B, T, Hq, 2 * D)
+            gate = qg[..., D:].reshape(B, T, Hq * D)
+            qkv = torch.cat([qg[..., :D].reshape(B, T, Hq * D), qkv[..., 2 * Hq * D:]], dim=-1)
         if self.clip_qkv is not None:
             qkv = qkv.clamp(-self.clip_qkv, self.clip_qkv)
         if self.qk_norm is not None:
@@ -149,7 +160,10 @@ class Attention(nn.Module):
             o = F.attention(q, k, v, causal=self.causal, scale=self.scale, segment_ids=segment_ids,
                             sliding_window=self.sliding_window, softcap=self.softcap, sinks=self.sinks,
                             cu_seqlens=cu_seqlens)
-        return self.o_proj(o.reshape(B, T, self.num_heads * self.head_dim))
+        o = o.reshape(B, T, self.num_heads * self.head_dim)
+        if gate is not None:
+            o = o * torch.sigmoid(gate)
+        return self.o_proj(o)
 
     def _alibi_attention(self, q, k, v, segment_ids):
         # ALiBi families (Falcon-RW, MPT, BLOOM-style) are served by the dense oracle path: a

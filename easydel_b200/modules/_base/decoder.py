@@ -100,6 +100,8 @@ class ArchSpec:
     residual_multiplier: float | None = None
     embedding_multiplier: float | None = None
     mla: dict | None = None           # kwargs of layers.mla.MLAttention: latent attention instead of MHA / GQA
+    linear_attn: dict | None = None   # kwargs of layers.linear_attention.GatedDeltaNet for layers of type "linear"
+    attn_output_gate: bool = False    # sigmoid gate on the attention output, emitted by the query projection
 
 
 def _norm(spec: ArchSpec, dtype) -> nn.Module:
@@ -142,7 +144,13 @@ class DecoderLayer(nn.Module):
             rope = spec.rope_local
         if ltype == "nope":
             rope = None
-        if spec.mla is not None:
+        self.is_linear = ltype == "linear"
+        if self.is_linear:
+            from ...layers.linear_attention import GatedDeltaNet
+
+            self.linear_attn = GatedDeltaNet(spec.hidden_size, layer_idx=layer_idx, dtype=dtype,
+                                             init_std=spec.init_std, norm_eps=spec.norm_eps, **spec.linear_attn)
+        elif spec.mla is not None:
             from ...layers.mla import MLAttention
 
             self.self_attn = MLAttention(spec.hidden_size, spec.num_heads, rope=spec.rope, norm_eps=spec.norm_eps,
@@ -156,7 +164,7 @@ class DecoderLayer(nn.Module):
         self._build_mlp(config, spec, layer_idx, dtype, tp_size, tp_rank, tp_group)
         fused = spec.norm == "rms" and spec.residual == "pre" and not spec.sandwich_norm \
             and spec.residual_multiplier is None
-        if fused and tp_size > 1 and spec.mla is None:
+        if fused and tp_size > 1 and spec.mla is None and not self.is_linear:
             # both branch outputs feed a fused add+norm: let it also do the tensor-parallel sum
             self.self_attn.o_proj.defer_reduce = True
             if not self.is_moe:
@@ -169,7 +177,8 @@ class DecoderLayer(nn.Module):
             bias=spec.attn_bias, o_bias=spec.o_bias, qk_norm=spec.qk_norm, qk_norm_eps=spec.norm_eps, rope=rope,
             sliding_window=window, softcap=spec.attn_softcap, scale=spec.attn_scale, use_sinks=spec.use_sinks,
             use_alibi=spec.pos_emb == "alibi", clip_qkv=spec.clip_qkv, dtype=dtype, init_std=spec.init_std,
-            tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group, qk_norm_offset=spec.norm_offset)
+            tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group, qk_norm_offset=spec.norm_offset,
+            output_gate=spec.attn_output_gate)
 
     def _build_mlp(self, config, spec, layer_idx, dtype, tp_size, tp_rank, tp_group):
         moe = spec.moe
@@ -205,6 +214,12 @@ class DecoderLayer(nn.Module):
 
     # The pair (x, pending) means the residual stream is x + pending; `pending` is folded in by the
     # next fused add+norm. Returns (x, pending, router_logits).
+    def _mix(self, h, positions, segment_ids, cache_view, attn_meta):
+        if self.is_linear:
+            return self.linear_attn(h, segment_ids=segment_ids,
+                                    state=None if cache_view is None else cache_view.linear_state)
+        return self.self_attn(h, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
+
     def forward(self, x, pending, positions, segment_ids=None, cache_view=None, attn_meta=None):
         spec = self.spec
         rl = None
@@ -215,7 +230,7 @@ class DecoderLayer(nn.Module):
                 h = self.input_layernorm(x)
             else:
                 h, x = self.input_layernorm.forward_with_residual(pending, x)
-            a = self.self_attn(h, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
+            a = self._mix(h, positions, segment_ids, cache_view, attn_meta)
             h, x = self.post_attention_layernorm.forward_with_residual(a, x)
             m = self.mlp(h)
             if self.is_moe:
@@ -226,21 +241,21 @@ class DecoderLayer(nn.Module):
         rm = spec.residual_multiplier or 1.0
         if spec.residual == "parallel":
             h = self.input_layernorm(x)
-            a = self.self_attn(h, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
+            a = self._mix(h, positions, segment_ids, cache_view, attn_meta)
             h2 = h if spec.shared_parallel_norm else self.post_attention_layernorm(x)
             m = self.mlp(h2)
             if self.is_moe:
                 m, rl = m
             return x + a + m, None, rl
         if spec.residual == "post":
-            a = self.self_attn(x, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
+            a = self._mix(x, positions, segment_ids, cache_view, attn_meta)
             x = x + self.post_attention_layernorm(a)
             m = self.mlp(x)
             if self.is_moe:
                 m, rl = m
             return x + self.post_feedforward_layernorm(m), None, rl
         h = self.input_layernorm(x)
-        a = self.self_attn(h, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
+        a = self._mix(h, positions, segment_ids, cache_view, attn_meta)
         if spec.sandwich_norm:
             a = self.post_attn_out_layernorm(a)
         x = x + a * rm

@@ -457,5 +457,42 @@ EXPORTS.update(define_family(
     _gpt_oss_spec, class_prefix="GptOss", rules=[("mlp.router.", "mlp.gate.")], tensor_in=_gpt_oss_in,
     tensor_out=_gpt_oss_out, hf_keeps_fused=("experts",)))
 
+
+
+# ---- qwen3_next (easydel/modules/qwen3_next): three Gated-DeltaNet layers per gated full-attention layer, (1 + w)
+# ---- RMSNorm, rotary on a quarter of the head, MoE with a gated shared expert ----
+def _qwen3_next_spec(c):
+    n = c.num_hidden_layers
+    lt = getattr(c, "layer_types", None)
+    interval = getattr(c, "full_attention_interval", 4) or 4
+    types = tuple("linear" if "linear" in t else "full" for t in lt) if lt else \
+        tuple("full" if (i + 1) % interval == 0 else "linear" for i in range(n))
+    hd = c.head_dim
+    params = getattr(c, "rope_parameters", None) or {}
+    partial = getattr(c, "partial_rotary_factor", None) or params.get("partial_rotary_factor", 0.25)
+    moe = None
+    if c.num_experts > 0:
+        moe = moe_spec(c, num_experts=c.num_experts, top_k=c.num_experts_per_tok,
+                       intermediate=c.moe_intermediate_size, norm_topk=c.norm_topk_prob,
+                       shared=c.shared_expert_intermediate_size, shared_gate=True, layers=_qwen_moe_layers(c),
+                       aux_coef=c.router_aux_loss_coef)
+    return base_spec(c, qk_norm="rms_head", norm_offset=1.0, layer_types=types, attn_output_gate=True,
+                     rope=rope_args(c, hd, partial=partial),
+                     linear_attn=dict(num_k_heads=c.linear_num_key_heads, num_v_heads=c.linear_num_value_heads,
+                                      head_k_dim=c.linear_key_head_dim, head_v_dim=c.linear_value_head_dim,
+                                      conv_kernel=c.linear_conv_kernel_dim), moe=moe)
+
+
+EXPORTS.update(define_family(
+    "qwen3_next", _d(vocab_size=151936, hidden_size=2048, intermediate_size=5632, num_hidden_layers=48,
+                     num_attention_heads=16, num_key_value_heads=2, head_dim=256, partial_rotary_factor=0.25,
+                     max_position_embeddings=32768, rope_theta=10000000.0, linear_conv_kernel_dim=4,
+                     linear_key_head_dim=128, linear_value_head_dim=128, linear_num_key_heads=16,
+                     linear_num_value_heads=32, decoder_sparse_step=1, moe_intermediate_size=512,
+                     shared_expert_intermediate_size=512, num_experts_per_tok=10, num_experts=512,
+                     norm_topk_prob=True, output_router_logits=False, router_aux_loss_coef=0.001,
+                     mlp_only_layers=None, layer_types=None, full_attention_interval=4),
+    _qwen3_next_spec, class_prefix="Qwen3Next", rules=[("mlp.shared_expert.", "mlp.shared_experts.")]))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

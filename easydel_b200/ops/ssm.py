@@ -146,9 +146,56 @@ def delta_rule_reference(q, k, v, g=None, beta=None, scale=None, cu_seqlens=None
     return torch.stack(outs).to(q.dtype)
 
 
+def delta_rule_chunked(q, k, v, g=None, beta=None, scale=None, cu_seqlens=None, state=None, chunk: int = 64):
+    """The gated delta rule in chunk-parallel form: differentiable, matmul-bound (the training path).
+
+    Inside a chunk with cumulative log-decay ``c_t`` the per-token updates ``u_t = beta_t (v_t - k_t^T e^{g_t} S_{t-1})``
+    satisfy ``(I + A) U = beta * (V - e^{c} K S_0)`` with the strictly lower-triangular
+    ``A[t,s] = beta_t e^{c_t - c_s} (k_t . k_s)``; one triangular solve per chunk replaces the token loop, then
+    ``o_t = scale (e^{c_t} q_t^T S_0 + sum_{s<=t} e^{c_t - c_s} (q_t . k_s) u_s)`` and
+    ``S_C = e^{c_C} S_0 + sum_s e^{c_C - c_s} k_s u_s^T``. Every exponent is <= 0. Scalar-per-head gates only.
+    """
+    total, H, DK = q.shape
+    DV = v.shape[-1]
+    scale = scale if scale is not None else DK ** -0.5
+    cu = _cu(total, cu_seqlens, q.device).tolist()
+    outs, new_states = [], []
+    for b in range(len(cu) - 1):
+        s0, s1 = cu[b], cu[b + 1]
+        S = state[b].float() if state is not None else torch.zeros(H, DK, DV, device=q.device)
+        for c0 in range(s0, s1, chunk):
+            c1 = min(c0 + chunk, s1)
+            n = c1 - c0
+            qc, kc, vc = (t[c0:c1].float().transpose(0, 1) for t in (q, k, v))          # [H, n, D]
+            bc = beta[c0:c1].float().t() if beta is not None else torch.ones(H, n, device=q.device)
+            cum = torch.cumsum(g[c0:c1].float().t(), -1) if g is not None else torch.zeros(H, n, device=q.device)
+            diff = cum[:, :, None] - cum[:, None, :]                                     # c_t - c_s
+            tri = torch.ones(n, n, device=q.device, dtype=torch.bool).tril()
+            decay = torch.where(tri, diff, torch.full_like(diff, -float("inf"))).exp()   # 0 above the diagonal
+            kk = kc @ kc.transpose(1, 2)
+            A = (bc[:, :, None] * decay * kk).tril(-1)
+            rhs = bc[:, :, None] * (vc - cum.exp()[:, :, None] * (kc @ S))
+            eye = torch.eye(n, device=q.device)
+            U = torch.linalg.solve_triangular(eye + A, rhs, upper=False)
+            o = cum.exp()[:, :, None] * (qc @ S) + (decay * (qc @ kc.transpose(1, 2))) @ U
+            outs.append((o * scale).transpose(0, 1))
+            tail = (cum[:, -1:] - cum).exp()                                             # e^{c_C - c_s}
+            S = cum[:, -1].exp()[:, None, None] * S + (kc * tail[:, :, None]).transpose(1, 2) @ U
+        new_states.append(S)
+    if state is not None:
+        with torch.no_grad():
+            state.copy_(torch.stack([x.detach() for x in new_states]))
+    if not outs:
+        return q.new_zeros(0, H, DV)
+    return torch.cat(outs).to(q.dtype)
+
+
 def gated_delta_rule(q, k, v, g=None, beta=None, scale=None, cu_seqlens=None, state=None):
     """q, k ``[total, H, DK]``; v ``[total, H, DV]``; g ``[total, H]`` log-decay (or ``[total, H, DK]`` for KDA);
-    beta ``[total, H]``; state ``[nseq, H, DK, DV]`` fp32. Returns ``[total, H, DV]``."""
+    beta ``[total, H]``; state ``[nseq, H, DK, DV]`` fp32. Returns ``[total, H, DV]``.
+
+    Inference on the GPU runs the recurrent kernel; anything that needs gradients (or long CPU inputs) with a
+    per-head gate goes through :func:`delta_rule_chunked`."""
     DK, DV = q.shape[-1], v.shape[-1]
     if _use_kernel(q, k, v, g, beta) and DK in (32, 64, 128) and DV <= 256 and q.dtype == torch.bfloat16:
         total, H, _ = q.shape
@@ -161,6 +208,8 @@ def gated_delta_rule(q, k, v, g=None, beta=None, scale=None, cu_seqlens=None, st
                   cu.data_ptr(), cu.numel() - 1, H, DK, DV, float(scale if scale is not None else DK ** -0.5),
                   _lib.ptr(state), o.data_ptr(), _lib.stream_ptr())
         return o
+    if (g is None or g.dim() == 2) and q.shape[0] > 16:
+        return delta_rule_chunked(q, k, v, g, beta, scale, cu_seqlens, state)
     return delta_rule_reference(q, k, v, g, beta, scale, cu_seqlens, state)
 
 

@@ -284,8 +284,8 @@ class ModelConverter:
                     if (k in hf_defaults or k in own_keys) and not (v is None and k not in hf_defaults)}
         spec = getattr(model, "spec", None)
         if "layer_types" in hf_defaults and spec is not None and spec.layer_types is not None:
-            cfg_dict["layer_types"] = ["sliding_attention" if t == "sliding" else "full_attention"
-                                       for t in spec.layer_types]
+            cfg_dict["layer_types"] = [{"sliding": "sliding_attention", "linear": "linear_attention"}.get(
+                t, "full_attention") for t in spec.layer_types]
         hf_cfg = hf_cfg_cls(**cfg_dict)
         auto = base_hf_auto_class or transformers.AutoModelForCausalLM
         hf_model = auto.from_config(hf_cfg).to(dtype)

@@ -71,6 +71,10 @@ CASES = {
     "gpt_oss": dict(head_dim=16, num_local_experts=4, num_experts_per_tok=2, sliding_window=16, intermediate_size=64,
                     rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0,
                                   "truncate": False, "original_max_position_embeddings": 64}),
+    "qwen3_next": dict(head_dim=16, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=8,
+                       linear_value_head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=24,
+                       shared_expert_intermediate_size=48,
+                       layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"]),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                       shared_expert_intermediate_size=96),
 }
@@ -110,3 +114,22 @@ def test_family_matches_hf(model_type):
     back = hf_to_internal(model, hf.state_dict(), strict=True)
     for k, v in model.state_dict().items():
         assert torch.equal(back[k].to(v.dtype), v), k
+
+
+def test_qwen3_next_incremental_decoding_matches_full_forward():
+    """Hybrid cache: KV pages for the full-attention layers, convolution window + recurrent state for the
+    Gated-DeltaNet layers; prefill + single-token steps reproduce the logits of one full forward."""
+    torch.manual_seed(0)
+    m = _build("qwen3_next", CASES["qwen3_next"])
+    ids = torch.randint(0, 512, (2, 12))
+    with torch.no_grad():
+        full = m(input_ids=ids).logits
+        cache = m.init_cache(2, 16)
+        assert set(cache.linear) == {0, 1, 2}
+        o = m(input_ids=ids[:, :9], past_key_values=cache).logits
+        cache.advance(9)
+        assert (o - full[:, :9]).abs().max() < 2e-4
+        for t in range(9, 12):
+            o = m(input_ids=ids[:, t:t + 1], past_key_values=cache).logits
+            cache.advance(1)
+            assert (o[:, 0] - full[:, t]).abs().max() < 2e-4
