@@ -77,6 +77,16 @@ class TransformerCacheView:
             return R.attention(q, kk, vv, causal=True, scale=attn.scale, segment_ids=seg_k[:, s:e],
                                kv_segment_ids=seg_k, sliding_window=attn.sliding_window, softcap=attn.softcap,
                                sinks=attn.sinks)
+        chunk = getattr(attn, "chunk_size", None)
+        if chunk and e > chunk:
+            # block-diagonal causal attention over the cache: keys outside the query's block are masked out
+            from ..ops import reference as R
+
+            qpos = torch.arange(s, e, device=q.device)
+            kpos = torch.arange(e, device=q.device)
+            bias = torch.where((qpos[:, None] // chunk) == (kpos[None, :] // chunk), 0.0, float("-inf"))
+            return R.attention(q, kk, vv, causal=True, scale=attn.scale, softcap=attn.softcap, sinks=attn.sinks,
+                               bias=bias[None, None])
         if kk.shape[0] > 1 and e < c.max_len:
             kk, vv = kk.contiguous(), vv.contiguous()  # the kernels want equally spaced token rows
         return F.attention(q, kk, vv, causal=True, scale=attn.scale, sliding_window=attn.sliding_window,

@@ -59,9 +59,13 @@ class Attention(nn.Module):
                  scale: float | None = None, use_sinks: bool = False, use_alibi: bool = False, causal: bool = True,
                  clip_qkv: float | None = None, dtype: torch.dtype = torch.float32, init_std: float = 0.02,
                  tp_size: int = 1, tp_rank: int = 0, tp_group=None, qk_norm_offset: float = 0.0,
-                 output_gate: bool = False):
+                 output_gate: bool = False, chunk_size: int | None = None,
+                 temp_tuning: tuple[float, float] | None = None):
         super().__init__()
         self.layer_idx = layer_idx
+        # Llama-4: attention restricted to blocks of ``chunk_size`` positions (rotary layers); position-dependent
+        # query temperature ``log1p(floor((pos + 1) / floor_scale)) * attn_scale + 1`` (layers without rotary)
+        self.chunk_size, self.temp_tuning = chunk_size, temp_tuning
         # Qwen3-Next: the query projection also emits a per-channel gate ([q (D) | gate (D)] per head); the
         # attention output is multiplied by sigmoid(gate) before the output projection
         self.output_gate = output_gate
@@ -89,7 +93,7 @@ class Attention(nn.Module):
                                              tp_group=tp_group)
         self.o_proj = RowParallelLinear(num_heads * head_dim, hidden_size, bias=o_bias, dtype=dtype,
                                         init_std=init_std, tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group)
-        self.qk_norm = qk_norm
+        self.qk_norm, self.qk_norm_eps = qk_norm, qk_norm_eps
         if qk_norm == "rms_head":      # per-head RMSNorm over head_dim (Qwen3, Gemma3, OLMo... per-head flavour)
             self.q_norm = RMSNorm(head_dim, qk_norm_eps, dtype, offset=qk_norm_offset)
             self.k_norm = RMSNorm(head_dim, qk_norm_eps, dtype, offset=qk_norm_offset)
@@ -147,11 +151,24 @@ class Attention(nn.Module):
             qkv = torch.cat([qg[..., :D].reshape(B, T, Hq * D), qkv[..., 2 * Hq * D:]], dim=-1)
         if self.clip_qkv is not None:
             qkv = qkv.clamp(-self.clip_qkv, self.clip_qkv)
-        if self.qk_norm is not None:
+        if self.qk_norm is not None and self.qk_norm != "l2_post_rope":
             qkv = self._apply_qk_norm(qkv)
         if self.rotary is not None:
             qkv = self.rotary.rotate_packed(qkv, positions, self.num_heads + self.num_kv_heads)
         q, k, v = self._split(qkv)
+        if self.qk_norm == "l2_post_rope":      # weightless RMS normalisation of every head, after the rotation
+            q = (q.float() * torch.rsqrt(q.float().pow(2).mean(-1, keepdim=True) + self.qk_norm_eps)).to(v.dtype)
+            k = (k.float() * torch.rsqrt(k.float().pow(2).mean(-1, keepdim=True) + self.qk_norm_eps)).to(v.dtype)
+        if self.temp_tuning is not None:
+            a_scale, floor_scale = self.temp_tuning
+            t = torch.log1p(torch.floor((positions.float() + 1.0) / floor_scale)) * a_scale + 1.0
+            q = (q * t[..., None, None]).to(v.dtype)
+        if self.chunk_size and cache_view is None and T > 1:
+            # a block-diagonal causal mask is a segment mask: (document, position // chunk) names the segment
+            blocks = positions // self.chunk_size
+            base = segment_ids.long() if segment_ids is not None else torch.ones_like(blocks)
+            if int(blocks.max()) > 0:
+                segment_ids = (base * (int(blocks.max()) + 1) + blocks).to(torch.int32) * (base != 0)
         if cache_view is not None:
             o = cache_view.attend(self, q, k, v, positions=positions, attn_meta=attn_meta)
         elif self.alibi is not None:

@@ -77,8 +77,10 @@ class MoEBlock(nn.Module):
                  use_score_bias: bool = False, router_bias: bool = False, shared_intermediate_size: int = 0,
                  shared_gate: bool = False, dtype=torch.float32, init_std: float = 0.02, expert_init_std: float = 0.01,
                  ep_size: int = 1, ep_rank: int = 0, ep_group=None, tp_size: int = 1, tp_rank: int = 0,
-                 tp_group=None, router_dtype=None, expert_bias: bool = False):
+                 tp_group=None, router_dtype=None, expert_bias: bool = False, scale_input: bool = False):
         super().__init__()
+        # Llama-4: the routing score multiplies the expert's input instead of its output
+        self.scale_input = scale_input
         if num_experts % ep_size:
             raise ValueError(f"{num_experts} experts not divisible by ep={ep_size}")
         self.hidden_size, self.num_experts, self.top_k = hidden_size, num_experts, top_k
@@ -144,7 +146,19 @@ class MoEBlock(nn.Module):
         x2 = x.reshape(-1, shape[-1])
         logits = self.gate(x2)
         w, idx, _ = self.route(logits)
-        if self.ep_size > 1:
+        if self.scale_input:
+            T, k = idx.shape
+            x_in = (x2[:, None, :] * w[..., None].to(x2.dtype)).reshape(T * k, -1)
+            one = torch.ones(T * k, 1, dtype=w.dtype, device=w.device)
+            if self.ep_size > 1:
+                from ..parallel import ep as epar
+
+                y = epar.expert_parallel_ffn(self, x_in, one, idx.reshape(T * k, 1))
+            else:
+                y = G.moe_ffn(x_in, self.gate_up_proj.weight, self.down_proj.weight, one, idx.reshape(T * k, 1),
+                              self.act, b_gate_up=self.gate_up_proj.bias, b_down=self.down_proj.bias)
+            y = y.view(T, k, -1).sum(1)
+        elif self.ep_size > 1:
             from ..parallel import ep as epar
 
             y = epar.expert_parallel_ffn(self, x2, w, idx)

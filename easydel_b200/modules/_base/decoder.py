@@ -53,6 +53,7 @@ class MoESpec:
     expert_init_std: float = 0.01
     expert_bias: bool = False         # per-expert biases on both expert projections (GPT-OSS)
     expert_act: str | None = None     # gated activation of the experts when it differs from the dense MLP's
+    scale_input: bool = False         # routing score applied to the experts' input (Llama-4)
 
 
 @dataclass
@@ -102,6 +103,9 @@ class ArchSpec:
     mla: dict | None = None           # kwargs of layers.mla.MLAttention: latent attention instead of MHA / GQA
     linear_attn: dict | None = None   # kwargs of layers.linear_attention.GatedDeltaNet for layers of type "linear"
     attn_output_gate: bool = False    # sigmoid gate on the attention output, emitted by the query projection
+    attn_chunk_size: int | None = None  # block-diagonal attention on the rotary layers of a rope / nope mix (Llama-4)
+    attn_temp_tuning: tuple[float, float] | None = None  # (attn_scale, floor_scale) on the layers without rotary
+    qk_norm_rope_only: bool = False   # QK norm only on layers that rotate
 
 
 def _norm(spec: ArchSpec, dtype) -> nn.Module:
@@ -172,9 +176,12 @@ class DecoderLayer(nn.Module):
 
     @staticmethod
     def _mha(spec, layer_idx, dtype, rope, window, tp_size, tp_rank, tp_group):
+        qk_norm = spec.qk_norm if (rope is not None or not spec.qk_norm_rope_only) else None
         return Attention(
             spec.hidden_size, spec.num_heads, spec.num_kv_heads, spec.head_dim, layer_idx=layer_idx,
-            bias=spec.attn_bias, o_bias=spec.o_bias, qk_norm=spec.qk_norm, qk_norm_eps=spec.norm_eps, rope=rope,
+            bias=spec.attn_bias, o_bias=spec.o_bias, qk_norm=qk_norm, qk_norm_eps=spec.norm_eps, rope=rope,
+            chunk_size=spec.attn_chunk_size if rope is not None else None,
+            temp_tuning=spec.attn_temp_tuning if rope is None else None,
             sliding_window=window, softcap=spec.attn_softcap, scale=spec.attn_scale, use_sinks=spec.use_sinks,
             use_alibi=spec.pos_emb == "alibi", clip_qkv=spec.clip_qkv, dtype=dtype, init_std=spec.init_std,
             tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group, qk_norm_offset=spec.norm_offset,
@@ -186,6 +193,7 @@ class DecoderLayer(nn.Module):
             ep_size, ep_rank, ep_group = _ep_of(config)
             self.mlp = MoEBlock(spec.hidden_size, moe.intermediate_size, moe.num_experts, moe.top_k,
                                 act=moe.expert_act or spec.act, expert_bias=moe.expert_bias,
+                                scale_input=moe.scale_input,
                                 norm_topk_prob=moe.norm_topk_prob, scoring=moe.scoring,
                                 routed_scaling_factor=moe.routed_scaling_factor, n_group=moe.n_group,
                                 topk_group=moe.topk_group, use_score_bias=moe.use_score_bias,

@@ -494,5 +494,65 @@ EXPORTS.update(define_family(
                      mlp_only_layers=None, layer_types=None, full_attention_interval=4),
     _qwen3_next_spec, class_prefix="Qwen3Next", rules=[("mlp.shared_expert.", "mlp.shared_experts.")]))
 
+
+
+# ---- llama4 text (easydel/modules/llama4): rotary layers attend inside 8192-token blocks and L2-normalise q / k,
+# ---- every fourth layer has no positions and a length-dependent query temperature; top-1 sigmoid router whose score
+# ---- scales the expert input; a shared expert beside the routed ones. Expert tensors are stored [E, in, out].
+def _llama4_spec(c):
+    n = c.num_hidden_layers
+    nope = getattr(c, "no_rope_layers", None) or [int((i + 1) % 4 != 0) for i in range(n)]
+    types = tuple("full" if r else "nope" for r in nope)
+    step = getattr(c, "interleave_moe_layer_step", 1) or 1
+    moe_layers = getattr(c, "moe_layers", None)
+    if moe_layers is None:
+        moe_layers = list(range(step - 1, n, step))
+    return base_spec(c, intermediate_size=c.intermediate_size_mlp, layer_types=types,
+                     rope=rope_args(c, c.head_dim, neox=False),
+                     qk_norm="l2_post_rope" if c.use_qk_norm else None, qk_norm_rope_only=True,
+                     attn_chunk_size=c.attention_chunk_size,
+                     attn_temp_tuning=(c.attn_scale, c.floor_scale) if c.attn_temperature_tuning else None,
+                     moe=moe_spec(c, num_experts=c.num_local_experts, top_k=c.num_experts_per_tok,
+                                  intermediate=c.intermediate_size, norm_topk=False, scoring="sigmoid",
+                                  shared=c.intermediate_size, layers=tuple(moe_layers), scale_input=True,
+                                  aux_coef=getattr(c, "router_aux_loss_coef", 0.0)))
+
+
+def _fused_experts_in(model, sd):
+    """``...experts.gate_up_proj`` [E, in, 2F] / ``...experts.down_proj`` [E, F, out] -> stacked ``.weight`` [E, out, in]."""
+    out = {}
+    for k, t in sd.items():
+        if k.endswith(".experts.gate_up_proj") or k.endswith(".experts.down_proj"):
+            head, leaf = k.rsplit(".experts.", 1)
+            out[f"{head}.{leaf}.weight"] = t.transpose(1, 2)
+        else:
+            out[k] = t
+    return out
+
+
+def _fused_experts_out(model, sd):
+    out = {}
+    for k, t in sd.items():
+        if t.dim() == 3 and (k.endswith(".gate_up_proj.weight") or k.endswith(".down_proj.weight")):
+            head, leaf, _ = k.rsplit(".", 2)
+            out[f"{head}.experts.{leaf}"] = t.transpose(1, 2).contiguous()
+        else:
+            out[k] = t
+    return out
+
+
+EXPORTS.update(define_family(
+    "llama4_text", _d(vocab_size=202048, hidden_size=5120, intermediate_size=8192, intermediate_size_mlp=16384,
+                      num_hidden_layers=48, num_attention_heads=40, num_key_value_heads=8, head_dim=128,
+                      rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=131072, num_experts_per_tok=1,
+                      num_local_experts=16, moe_layers=None, interleave_moe_layer_step=1, use_qk_norm=True,
+                      output_router_logits=False, router_aux_loss_coef=0.001, router_jitter_noise=0.0,
+                      no_rope_layers=None, no_rope_layer_interval=4, attention_chunk_size=8192,
+                      attn_temperature_tuning=True, floor_scale=8192, attn_scale=0.1, layer_types=None),
+    _llama4_spec, class_prefix="Llama4Text",
+    rules=[("feed_forward.router.", "mlp.gate."), ("feed_forward.shared_expert.", "mlp.shared_experts."),
+           ("feed_forward.", "mlp.")],
+    tensor_in=_fused_experts_in, tensor_out=_fused_experts_out, hf_keeps_fused=("experts",)))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

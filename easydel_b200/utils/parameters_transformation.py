@@ -283,7 +283,9 @@ class ModelConverter:
         cfg_dict = {k: v for k, v in model.config.to_dict().items()
                     if (k in hf_defaults or k in own_keys) and not (v is None and k not in hf_defaults)}
         spec = getattr(model, "spec", None)
-        if "layer_types" in hf_defaults and spec is not None and spec.layer_types is not None:
+        if getattr(model.config, "layer_types", None):
+            cfg_dict["layer_types"] = list(model.config.layer_types)      # the family's own vocabulary
+        elif "layer_types" in hf_defaults and spec is not None and spec.layer_types is not None:
             cfg_dict["layer_types"] = [{"sliding": "sliding_attention", "linear": "linear_attention"}.get(
                 t, "full_attention") for t in spec.layer_types]
         hf_cfg = hf_cfg_cls(**cfg_dict)

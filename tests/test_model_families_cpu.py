@@ -75,6 +75,11 @@ CASES = {
                        linear_value_head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=24,
                        shared_expert_intermediate_size=48,
                        layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"]),
+    "llama4_text": dict(head_dim=16, intermediate_size=48, intermediate_size_mlp=96, num_local_experts=4,
+                        num_experts_per_tok=1, attention_chunk_size=32, floor_scale=16, attn_scale=0.3,
+                        no_rope_layers=[1, 1, 1, 0], moe_layers=[0, 2, 3],
+                        layer_types=["chunked_attention", "chunked_attention", "chunked_attention",
+                                     "full_attention"]),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                       shared_expert_intermediate_size=96),
 }
@@ -116,20 +121,24 @@ def test_family_matches_hf(model_type):
         assert torch.equal(back[k].to(v.dtype), v), k
 
 
-def test_qwen3_next_incremental_decoding_matches_full_forward():
-    """Hybrid cache: KV pages for the full-attention layers, convolution window + recurrent state for the
-    Gated-DeltaNet layers; prefill + single-token steps reproduce the logits of one full forward."""
+@pytest.mark.parametrize("model_type", ["qwen3_next", "llama4_text", "gpt_oss"])
+def test_incremental_decoding_matches_full_forward(model_type):
+    """Prefill + single-token steps through the dense cache reproduce one full forward: hybrid state for the
+    Gated-DeltaNet layers (qwen3_next), block-diagonal attention across a block boundary (llama4), sinks with
+    sliding windows (gpt_oss)."""
     torch.manual_seed(0)
-    m = _build("qwen3_next", CASES["qwen3_next"])
-    ids = torch.randint(0, 512, (2, 12))
+    m = _build(model_type, CASES[model_type])
+    n, pre = 40, 30
+    ids = torch.randint(0, 512, (2, n))
     with torch.no_grad():
         full = m(input_ids=ids).logits
-        cache = m.init_cache(2, 16)
-        assert set(cache.linear) == {0, 1, 2}
-        o = m(input_ids=ids[:, :9], past_key_values=cache).logits
-        cache.advance(9)
-        assert (o - full[:, :9]).abs().max() < 2e-4
-        for t in range(9, 12):
+        cache = m.init_cache(2, 48)
+        if model_type == "qwen3_next":
+            assert set(cache.linear) == {0, 1, 2}
+        o = m(input_ids=ids[:, :pre], past_key_values=cache).logits
+        cache.advance(pre)
+        assert (o - full[:, :pre]).abs().max() < 3e-4
+        for t in range(pre, n):
             o = m(input_ids=ids[:, t:t + 1], past_key_values=cache).logits
             cache.advance(1)
-            assert (o[:, 0] - full[:, t]).abs().max() < 2e-4
+            assert (o[:, 0] - full[:, t]).abs().max() < 3e-4, t
