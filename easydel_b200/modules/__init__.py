@@ -16,3 +16,6 @@ from .vision import *  # noqa: F401,F403
 from .llava import *  # noqa: F401,F403
 from . import whisper  # noqa: F401
 from .whisper import *  # noqa: F401,F403
+from . import gemma3, aya_vision  # noqa: F401
+from .gemma3 import *  # noqa: F401,F403
+from .aya_vision import *  # noqa: F401,F403

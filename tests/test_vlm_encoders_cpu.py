@@ -96,3 +96,57 @@ def test_roberta_heads_match_hf():
     with torch.no_grad():
         assert (c(input_ids=ids, attention_mask=att).logits - hfc(input_ids=ids, attention_mask=att).logits
                 ).abs().max() < 2e-3
+
+
+SV = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, image_size=28,
+          patch_size=7)
+
+
+def _check_vlm(m, hf, ids, pix, tol=3e-4):
+    missing, unexpected = hf.load_state_dict(internal_to_hf(m), strict=False)
+    assert not unexpected and all("position_ids" in x or ".head." in x or x == "lm_head.weight" for x in missing), (missing, unexpected)
+    with torch.no_grad():
+        a, b = m(input_ids=ids, pixel_values=pix).logits, hf(input_ids=ids, pixel_values=pix).logits
+    assert (a - b).abs().max() < tol * max(1.0, float(b.abs().max())), (a - b).abs().max()
+    back = hf_to_internal(m, {k: v for k, v in hf.state_dict().items() if k != "lm_head.weight" or
+                              not hf.config.tie_word_embeddings})
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    _, met = m.compute_loss(input_ids=ids, pixel_values=pix, labels=ids)
+    met.loss.backward()
+    assert torch.isfinite(met.loss)
+
+
+def test_gemma3_multimodal_matches_hf():
+    from easydel_b200.modules.gemma3 import Gemma3Config, Gemma3ForConditionalGeneration
+
+    tkw = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=8, sliding_window=16, query_pre_attn_scalar=8)
+    cfg = Gemma3Config(vision_config=dict(model_type="siglip_vision_model", **SV),
+                       text_config=dict(model_type="gemma3_text", **tkw), mm_tokens_per_image=4, image_token_index=127)
+    torch.manual_seed(0)
+    m = Gemma3ForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.Gemma3ForConditionalGeneration(transformers.Gemma3Config(
+        vision_config=transformers.SiglipVisionConfig(**SV), text_config=transformers.Gemma3TextConfig(**tkw),
+        mm_tokens_per_image=4, image_token_index=127)).float().eval()
+    ids = torch.randint(0, 120, (2, 12))
+    ids[:, 2:6] = 127
+    _check_vlm(m, hf, ids, torch.randn(2, 3, 28, 28))
+
+
+def test_aya_vision_matches_hf():
+    from easydel_b200.modules.aya_vision import AyaVisionConfig, AyaVisionForConditionalGeneration
+
+    tkw = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, sliding_window=16, sliding_window_pattern=2, logit_scale=0.5)
+    cfg = AyaVisionConfig(vision_config=dict(model_type="siglip_vision_model", **SV),
+                          text_config=dict(model_type="cohere2", **tkw), downsample_factor=2, image_token_index=127)
+    torch.manual_seed(0)
+    m = AyaVisionForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.AyaVisionForConditionalGeneration(transformers.AyaVisionConfig(
+        vision_config=transformers.SiglipVisionConfig(**SV), text_config=transformers.Cohere2Config(**tkw),
+        downsample_factor=2, image_token_index=127)).float().eval()
+    ids = torch.randint(0, 120, (2, 12))
+    ids[:, 2:6] = 127        # 4x4 patches folded 2x2 -> 4 image tokens
+    _check_vlm(m, hf, ids, torch.randn(2, 3, 28, 28))
