@@ -109,7 +109,9 @@ class eSurge:
                  truncate_mode: str = "left", silent_mode: bool = True, sharding_axis_dims=(1, 1, 1, -1, 1),
                  **unused):
         self.model = model.eval() if hasattr(model, "eval") else model
-        self.tokenizer = tokenizer if tokenizer is not None else processor
+        self.tokenizer = tokenizer if tokenizer is not None else getattr(processor, "tokenizer", processor)
+        self.processor = processor
+        self._mm = None
         self.max_model_len, self.max_num_seqs = max_model_len, max_num_seqs
         if max_num_batched_tokens is None:
             # the reference's GPU default: min(max(2048, max_num_seqs), max_model_len)
@@ -196,12 +198,28 @@ class eSurge:
             return list(prompt["prompt_token_ids"]), prompt.get("prompt")
         return [int(t) for t in prompt], None
 
+    @property
+    def multimodal(self):
+        """The image front end (vision tower runs, feature cache); built on first use for models that have a tower."""
+        if self._mm is None and hasattr(self.model, "get_image_features"):
+            from .multimodal import MultiModalManager
+
+            self._mm = MultiModalManager(self.model, tokenizer=self.tokenizer, processor=self.processor)
+        return self._mm
+
     def add_request(self, prompt, sampling_params: SamplingParams | None = None, request_id: str | None = None,
-                    priority: int = 0) -> str:
+                    priority: int = 0, images: tp.Sequence[tp.Any] | None = None) -> str:
         sp = sampling_params or SamplingParams()
         ids, text = self._tokenize(prompt)
         if not ids:
             raise ValueError("empty prompt")
+        mm_embeds, mm_hash = [], None
+        if images:
+            if self.multimodal is None:
+                raise ValueError("this model has no vision tower: images cannot be served")
+            ids, mm_embeds, mm_hash = self.multimodal.prepare(ids, images)
+            if len(ids) > self.max_model_len - self.reserve_tokens:
+                raise ValueError(f"prompt with images has {len(ids)} tokens; max_model_len is {self.max_model_len}")
         limit = self.max_model_len - self.reserve_tokens
         want = len(ids) + (sp.max_tokens or 0)
         if len(ids) > limit or want > self.max_model_len:
@@ -218,7 +236,8 @@ class eSurge:
             if sp.max_tokens is not None and len(ids) + sp.max_tokens > self.max_model_len:
                 sp = sp.clone(max_tokens=max(1, self.max_model_len - len(ids)))
         rid = request_id or f"req-{next(self._ids)}"
-        req = EngineRequest(rid, ids, sp, eos_token_id=self.eos_token_id, priority=priority)
+        req = EngineRequest(rid, ids, sp, eos_token_id=self.eos_token_id, priority=priority, mm_embeds=mm_embeds,
+                            mm_hash=mm_hash)
         tr = _Tracked(req, text, IncrementalDetokenizer(self.tokenizer if sp.detokenize else None,
                                                         sp.skip_special_tokens))
         with self._work:
@@ -354,14 +373,20 @@ class eSurge:
             num_cached_tokens=req.num_cached_tokens)
 
     def generate(self, prompts, sampling_params: SamplingParams | list[SamplingParams] | None = None,
-                 request_id: str | list[str] | None = None, use_tqdm: bool = False) -> list[RequestOutput]:
-        """Blocking batch generation. Works with or without the background thread."""
+                 request_id: str | list[str] | None = None, use_tqdm: bool = False,
+                 images: list | None = None) -> list[RequestOutput]:
+        """Blocking batch generation. Works with or without the background thread. ``images``: the images of the
+        prompt (or one list per prompt), one per image placeholder token."""
         single = isinstance(prompts, str) or (isinstance(prompts, (list, tuple)) and prompts
                                               and isinstance(prompts[0], int))
         plist = [prompts] if single else list(prompts)
         sps = sampling_params if isinstance(sampling_params, list) else [sampling_params] * len(plist)
         rids = request_id if isinstance(request_id, list) else [request_id] * len(plist)
-        ids = [self.add_request(p, sp, rid) for p, sp, rid in zip(plist, sps, rids)]
+        if images is None:
+            imgs = [None] * len(plist)
+        else:
+            imgs = [images] if single else list(images)
+        ids = [self.add_request(p, sp, rid, images=im) for p, sp, rid, im in zip(plist, sps, rids, imgs)]
         self._drive(lambda: all(self._tracked[i].finished for i in ids))
         outs = [self._snapshot(self._tracked.pop(i), True) for i in ids]
         return outs
@@ -374,10 +399,10 @@ class eSurge:
             elif self.step() == 0 and not self.scheduler.has_unfinished():
                 break
 
-    def stream(self, prompt, sampling_params: SamplingParams | None = None, request_id: str | None = None
-               ) -> tp.Iterator[RequestOutput]:
+    def stream(self, prompt, sampling_params: SamplingParams | None = None, request_id: str | None = None,
+               images: list | None = None) -> tp.Iterator[RequestOutput]:
         """Yields a ``RequestOutput`` whenever new tokens arrive (``delta_text`` holds the increment)."""
-        rid = self.add_request(prompt, sampling_params, request_id)
+        rid = self.add_request(prompt, sampling_params, request_id, images=images)
         tr = self._tracked[rid]
         background = self._thread is not None and self._thread.is_alive()
         try:
@@ -401,12 +426,17 @@ class eSurge:
              stream: bool = False, chat_template: str | None = None, **template_kwargs):
         if self.tokenizer is None:
             raise ValueError("chat() needs a tokenizer with a chat template")
+        images = None
+        if self.multimodal is not None:
+            images, _ = self.multimodal.extract_media_from_messages(messages)
+            if images:
+                messages = self.multimodal.normalize_messages(messages)
         prompt = self.tokenizer.apply_chat_template(messages, tools=tools, tokenize=False,
                                                     add_generation_prompt=True, chat_template=chat_template,
                                                     **template_kwargs)
         if stream:
-            return self.stream(prompt, sampling_params)
-        return self.generate(prompt, sampling_params)[0]
+            return self.stream(prompt, sampling_params, images=images or None)
+        return self.generate(prompt, sampling_params, images=images or None)[0]
 
     def get_metrics_summary(self) -> dict:
         m = self.metrics.summary()

@@ -1,0 +1,353 @@
+"""Images in the serving engine (easydel/inference/esurge/multimodal/{manager,cache,types}.py).
+
+* :class:`MultiModalManager` turns the images of a request (PIL images, arrays, paths, ``data:`` URLs inside OpenAI
+  chat messages) into normalised pixel tensors at one of a few fixed resolutions (so the vision tower only ever sees
+  a handful of shapes), runs the model's vision tower + projector once per distinct image, and rewrites the prompt so
+  that every image placeholder token is repeated once per image feature row.
+* :class:`VisionEncoderCache` keeps projected image features on the device under a byte budget, keyed by a hash of
+  the pixels: a repeated image (multi-turn chat, shared system image) costs no tower forward.
+* The engine stores ``(offset, features)`` on the request; the runner embeds the step's tokens and overwrites the
+  placeholder rows that fall inside the scheduled range (chunked prefill splits an image across steps without any
+  special handling). The feature hashes join the page hashes so that prefix caching never matches two prompts that
+  differ only in their images.
+"""
+
+from __future__ import annotations
+
+import base64
+import hashlib
+import io
+import typing as tp
+from collections import OrderedDict
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+CLIP_MEAN, CLIP_STD = (0.48145466, 0.4578275, 0.40821073), (0.26862954, 0.26130258, 0.27577711)
+HALF_MEAN, HALF_STD = (0.5, 0.5, 0.5), (0.5, 0.5, 0.5)
+
+
+@dataclass
+class PlaceholderRange:
+    offset: int
+    length: int
+
+    @property
+    def end(self) -> int:
+        return self.offset + self.length
+
+
+@dataclass
+class MultiModalFeature:
+    mm_hash: str
+    modality: str = "image"
+    pixel_values: torch.Tensor | None = None           # [3, H, W], dropped once the embeddings exist
+    embeddings: torch.Tensor | None = None             # [rows, hidden] on the model's device
+    placeholder: PlaceholderRange | None = None
+
+    @classmethod
+    def from_image(cls, pixel_values: torch.Tensor) -> "MultiModalFeature":
+        return cls(mm_hash=hash_pixels(pixel_values), pixel_values=pixel_values)
+
+    @property
+    def has_cached_embeddings(self) -> bool:
+        return self.embeddings is not None
+
+    def clear_pixel_values(self) -> None:
+        self.pixel_values = None
+
+
+@dataclass
+class BatchedMultiModalInputs:
+    """Images of several requests stacked for one tower forward."""
+
+    pixel_values: torch.Tensor | None = None
+    request_index: list[int] = field(default_factory=list)
+
+    @classmethod
+    def from_features(cls, per_request: list[list[MultiModalFeature]]) -> "BatchedMultiModalInputs":
+        px, idx = [], []
+        for r, feats in enumerate(per_request):
+            for f in feats:
+                if f.pixel_values is not None:
+                    px.append(f.pixel_values)
+                    idx.append(r)
+        return cls(torch.stack(px) if px else None, idx)
+
+    @property
+    def has_images(self) -> bool:
+        return self.pixel_values is not None
+
+    @property
+    def num_images(self) -> int:
+        return len(self.request_index)
+
+    def get_request_image_count(self, request_idx: int) -> int:
+        return sum(1 for r in self.request_index if r == request_idx)
+
+
+def hash_pixels(pixel_values: torch.Tensor | np.ndarray) -> str:
+    a = pixel_values.detach().cpu().contiguous().numpy() if isinstance(pixel_values, torch.Tensor) else \
+        np.ascontiguousarray(pixel_values)
+    h = hashlib.blake2b(digest_size=16)
+    h.update(str(a.shape).encode())
+    h.update(str(a.dtype).encode())
+    h.update(a.tobytes())
+    return h.hexdigest()
+
+
+class VisionEncoderCache:
+    """LRU over projected image features with a byte budget."""
+
+    def __init__(self, capacity_mb: int = 1024):
+        self.capacity = int(capacity_mb) << 20
+        self._items: OrderedDict[str, torch.Tensor] = OrderedDict()
+        self._bytes = 0
+        self.hits = self.misses = 0
+
+    compute_hash = staticmethod(hash_pixels)
+
+    def get(self, key: str) -> torch.Tensor | None:
+        t = self._items.get(key)
+        if t is None:
+            self.misses += 1
+            return None
+        self._items.move_to_end(key)
+        self.hits += 1
+        return t
+
+    def put(self, key: str, embeddings: torch.Tensor) -> None:
+        n = embeddings.numel() * embeddings.element_size()
+        if n > self.capacity:
+            return
+        old = self._items.pop(key, None)
+        if old is not None:
+            self._bytes -= old.numel() * old.element_size()
+        while self._items and self._bytes + n > self.capacity:
+            _, ev = self._items.popitem(last=False)
+            self._bytes -= ev.numel() * ev.element_size()
+        self._items[key] = embeddings
+        self._bytes += n
+
+    def contains(self, key: str) -> bool:
+        return key in self._items
+
+    def clear(self) -> None:
+        self._items.clear()
+        self._bytes = 0
+
+    def __len__(self) -> int:
+        return len(self._items)
+
+    @property
+    def size_mb(self) -> float:
+        return self._bytes / (1 << 20)
+
+    @property
+    def hit_rate(self) -> float:
+        n = self.hits + self.misses
+        return self.hits / n if n else 0.0
+
+    def get_stats(self) -> dict:
+        return {"entries": len(self), "size_mb": self.size_mb, "capacity_mb": self.capacity / (1 << 20),
+                "hits": self.hits, "misses": self.misses, "hit_rate": self.hit_rate}
+
+
+class MultiModalManager:
+    def __init__(self, model, tokenizer=None, processor=None, resolution_buckets: list[tuple[int, int]] | None = None,
+                 cache_capacity_mb: int = 1024, enable_cache: bool = True, max_batch_images: int = 16):
+        self.model, self.tokenizer, self.processor = model, tokenizer, processor
+        self.cache = VisionEncoderCache(cache_capacity_mb) if enable_cache else None
+        self.max_batch_images = max_batch_images
+        cfg = model.config
+        self.vision_config = getattr(cfg, "vision_config", None)
+        self.image_token_id = getattr(cfg, "image_token_index", getattr(cfg, "image_token_id", None))
+        size = getattr(self.vision_config, "image_size", 224)
+        # fixed-size towers accept exactly one resolution; others snap to the closest bucket
+        self.buckets = resolution_buckets or [(size, size)]
+        vt = getattr(self.vision_config, "model_type", "")
+        self.mean, self.std = (HALF_MEAN, HALF_STD) if "siglip" in vt else (CLIP_MEAN, CLIP_STD)
+        ip = getattr(processor, "image_processor", None)
+        if ip is not None and getattr(ip, "image_mean", None) is not None:
+            self.mean, self.std = tuple(ip.image_mean), tuple(ip.image_std)
+
+    # ------------------------------------------------------------------ pixels
+    def resize_to_bucket(self, image):
+        from PIL import Image
+
+        w, h = image.size
+        ar = w / max(h, 1)
+        bw, bh = min(self.buckets, key=lambda b: (abs(b[0] / b[1] - ar), abs(b[0] * b[1] - w * h)))
+        if (w, h) == (bw, bh):
+            return image
+        return image.resize((bw, bh), Image.BICUBIC)
+
+    def _to_pil(self, img):
+        from PIL import Image
+
+        if isinstance(img, Image.Image):
+            return img.convert("RGB")
+        if isinstance(img, (bytes, bytearray)):
+            return Image.open(io.BytesIO(bytes(img))).convert("RGB")
+        if isinstance(img, str):
+            if img.startswith("data:"):
+                return Image.open(io.BytesIO(base64.b64decode(img.split(",", 1)[1]))).convert("RGB")
+            if img.startswith(("http://", "https://")):
+                import requests
+
+                return Image.open(io.BytesIO(requests.get(img, timeout=30).content)).convert("RGB")
+            return Image.open(img).convert("RGB")
+        if isinstance(img, torch.Tensor):
+            img = img.detach().cpu().numpy()
+        a = np.asarray(img)
+        if a.ndim == 3 and a.shape[0] in (1, 3) and a.shape[-1] not in (1, 3):
+            a = a.transpose(1, 2, 0)
+        if a.dtype != np.uint8:
+            a = (np.clip(a, 0.0, 1.0) * 255).astype(np.uint8) if a.max() <= 1.0 else a.astype(np.uint8)
+        return Image.fromarray(a).convert("RGB")
+
+    def _normalize_rgb(self, rgb: np.ndarray) -> np.ndarray:
+        x = rgb.astype(np.float32) / 255.0
+        return (x - np.asarray(self.mean, np.float32)) / np.asarray(self.std, np.float32)
+
+    def process_images(self, images: tp.Sequence[tp.Any]) -> list[torch.Tensor]:
+        """-> one ``[3, H, W]`` fp32 tensor per image (resolutions may differ across buckets)."""
+        out = []
+        for img in images:
+            pil = self.resize_to_bucket(self._to_pil(img))
+            out.append(torch.from_numpy(self._normalize_rgb(np.asarray(pil)).transpose(2, 0, 1).copy()))
+        return out
+
+    # ------------------------------------------------------------------ messages
+    @staticmethod
+    def extract_media_from_messages(messages: list[dict]) -> tuple[list[tp.Any], list[tp.Any]]:
+        """OpenAI-style content parts -> (images, videos) in order of appearance."""
+        images, videos = [], []
+        for m in messages:
+            content = m.get("content")
+            if not isinstance(content, list):
+                continue
+            for part in content:
+                if not isinstance(part, dict):
+                    continue
+                kind = part.get("type")
+                if kind in ("image", "input_image"):
+                    src = part.get("image", part.get("url", part.get("image_url")))
+                    if src is not None:
+                        images.append(src["url"] if isinstance(src, dict) else src)
+                elif kind == "image_url":
+                    src = part.get("image_url")
+                    images.append(src["url"] if isinstance(src, dict) else src)
+                elif kind in ("video", "video_url"):
+                    src = part.get("video", part.get("video_url"))
+                    videos.append(src["url"] if isinstance(src, dict) else src)
+        return images, videos
+
+    def normalize_messages(self, messages: list[dict], placeholder: str | None = None) -> list[dict]:
+        """Flattens content parts to text for chat templates that know nothing about images: every image part
+        becomes the placeholder token's text."""
+        ph = placeholder or self._placeholder_text() or "<image>"
+        out = []
+        for m in messages:
+            content = m.get("content")
+            if isinstance(content, list):
+                text = "".join(ph if (isinstance(p, dict) and p.get("type") in ("image", "image_url", "input_image"))
+                               else (p.get("text", "") if isinstance(p, dict) else str(p)) for p in content)
+                m = dict(m, content=text)
+            out.append(m)
+        return out
+
+    def _placeholder_text(self) -> str | None:
+        if self.tokenizer is None or self.image_token_id is None:
+            return None
+        try:
+            return self.tokenizer.convert_ids_to_tokens(int(self.image_token_id))
+        except Exception:
+            return None
+
+    # ------------------------------------------------------------------ features
+    @torch.no_grad()
+    def process_images_to_features(self, images: tp.Sequence[tp.Any]) -> list[MultiModalFeature]:
+        feats = [MultiModalFeature.from_image(p) for p in self.process_images(images)]
+        todo: dict[str, MultiModalFeature] = {}
+        for f in feats:
+            hit = self.cache.get(f.mm_hash) if self.cache is not None else None
+            if hit is not None:
+                f.embeddings = hit
+            else:
+                todo.setdefault(f.mm_hash, f)
+        dev = next(self.model.parameters()).device
+        pending = list(todo.values())
+        # one tower forward per resolution bucket and chunk of images
+        by_shape: dict[tuple, list[MultiModalFeature]] = {}
+        for f in pending:
+            by_shape.setdefault(tuple(f.pixel_values.shape), []).append(f)
+        for group in by_shape.values():
+            for i in range(0, len(group), self.max_batch_images):
+                chunk = group[i:i + self.max_batch_images]
+                px = torch.stack([f.pixel_values for f in chunk]).to(dev, self.model.dtype)
+                emb = self.model.get_image_features(px)
+                emb = emb.reshape(len(chunk), -1, emb.shape[-1])
+                for f, e in zip(chunk, emb):
+                    f.embeddings = e.contiguous()
+                    if self.cache is not None:
+                        self.cache.put(f.mm_hash, f.embeddings)
+        for f in feats:
+            if f.embeddings is None:
+                f.embeddings = todo[f.mm_hash].embeddings
+            f.clear_pixel_values()
+        return feats
+
+    def expand_placeholders(self, token_ids: tp.Sequence[int], feats: list[MultiModalFeature]) -> list[int]:
+        """Repeats the i-th image placeholder once per row of the i-th feature and records where it landed.
+        A run of placeholders already as long as the feature (a processor expanded it) is left as it is."""
+        ph = self.image_token_id
+        out: list[int] = []
+        k, i, n = 0, 0, len(token_ids)
+        while i < n:
+            t = token_ids[i]
+            if t != ph:
+                out.append(t)
+                i += 1
+                continue
+            j = i
+            while j < n and token_ids[j] == ph:
+                j += 1
+            run = j - i
+            while run > 0:
+                if k >= len(feats):
+                    raise ValueError("more image placeholders in the prompt than images in the request")
+                rows = feats[k].embeddings.shape[0]
+                take = rows if run >= rows else 1
+                feats[k].placeholder = PlaceholderRange(len(out), rows)
+                out.extend([ph] * rows)
+                run -= take
+                k += 1
+            i = j
+        if k != len(feats):
+            raise ValueError(f"{len(feats)} images for {k} image placeholders in the prompt")
+        return out
+
+    def prepare(self, token_ids: tp.Sequence[int], images: tp.Sequence[tp.Any]):
+        """-> (expanded token ids, [(offset, embeddings)], extra hash key) for ``eSurge.add_request``."""
+        feats = self.process_images_to_features(images)
+        ids = self.expand_placeholders(list(token_ids), feats)
+        return ids, [(f.placeholder.offset, f.embeddings) for f in feats], tuple(f.mm_hash for f in feats)
+
+    def tokenize_multimodal(self, messages: list[dict], images: tp.Sequence[tp.Any] | None = None, **template_kw):
+        if self.tokenizer is None:
+            raise ValueError("tokenize_multimodal needs a tokenizer with a chat template")
+        if images is None:
+            images, _ = self.extract_media_from_messages(messages)
+        text = self.tokenizer.apply_chat_template(self.normalize_messages(messages), tokenize=False,
+                                                  add_generation_prompt=True, **template_kw)
+        ids = self.tokenizer(text, add_special_tokens=False)["input_ids"]
+        return self.prepare(ids, images)
+
+    def clear_cache(self) -> None:
+        if self.cache is not None:
+            self.cache.clear()
+
+    def get_cache_stats(self) -> dict | None:
+        return None if self.cache is None else self.cache.get_stats()

@@ -26,6 +26,8 @@ class ModelRunner:
     def __init__(self, model, cache: PagedKVCache, max_num_seqs: int, max_num_batched_tokens: int,
                  max_model_len: int):
         self.model = model
+        # a vision-language wrapper is served through its language model; image rows arrive as embeddings
+        self._lm = getattr(model, "language_model", model)
         self.cache = cache
         self.device = model.device
         self.max_num_seqs = max_num_seqs
@@ -104,17 +106,25 @@ class ModelRunner:
             return 1
         return int(min(8, self.max_pages_per_seq // 4, max(1, self._sms // units)))
 
-    def _forward(self, B: int, T: int, max_q: int, num_decode: int) -> torch.Tensor:
-        """Backbone over the first ``T`` staged tokens of ``B`` sequences, LM head on each sequence's last row."""
+    def _forward(self, B: int, T: int, max_q: int, num_decode: int, mm_rows=None) -> torch.Tensor:
+        """Backbone over the first ``T`` staged tokens of ``B`` sequences, LM head on each sequence's last row.
+        ``mm_rows``: ``[(first staged row, features [n, hidden])]`` to write over the token embeddings."""
         d_ids, d_pos, d_slots, d_cu, d_kv, d_last, d_table = self._dviews
         MP = self.max_pages_per_seq
         meta = PagedBatchMeta(cu_q=d_cu[:B + 1], kv_lens=d_kv[:B], page_table=d_table.view(self.max_num_seqs, MP)[:B],
                               slot_mapping=d_slots[:T], max_q=max_q, num_seqs=B, last_token_index=d_last[:B],
                               request_distribution=(num_decode, B, B),
                               num_splits=self._decode_splits(B) if (max_q == 1 and T == B) else 1)
-        model = self.model
-        res = model(input_ids=d_ids[:T][None].long(), position_ids=d_pos[:T][None], past_key_values=self.cache,
-                    cache_metadata=meta, apply_lm_head=False)
+        model = self._lm
+        if mm_rows:
+            emb = model.get_input_embeddings()(d_ids[:T].long())
+            for row0, feats in mm_rows:
+                emb[row0:row0 + feats.shape[0]] = feats.to(emb.dtype)
+            res = model(inputs_embeds=emb[None], position_ids=d_pos[:T][None], past_key_values=self.cache,
+                        cache_metadata=meta, apply_lm_head=False)
+        else:
+            res = model(input_ids=d_ids[:T][None].long(), position_ids=d_pos[:T][None], past_key_values=self.cache,
+                        cache_metadata=meta, apply_lm_head=False)
         rows = S.gather_rows(res.last_hidden_state[0], d_last[:B])
         return model.apply_lm_head(rows)
 
@@ -158,6 +168,7 @@ class ModelRunner:
         cu_np[0] = 0
         any_pen = False
         any_random = False
+        mm_rows = []
         fast = all(s.num_new_tokens == 1 and s.start >= s.request.num_prompt_tokens for s in sched)
         if fast:
             # Decode-only step: vectorised fill from the per-slot page mirror (one short Python pass per field).
@@ -198,6 +209,11 @@ class ModelRunner:
             else:
                 toks = req.prompt_token_ids[st:] + req.output_token_ids[:st + n - npt]
             ids_np[o:o + n] = toks
+            for off, feats in req.mm_embeds:
+                # the part of this image that falls inside [st, st + n): chunked prefill may split an image
+                a, z = max(off, st), min(off + feats.shape[0], st + n)
+                if a < z:
+                    mm_rows.append((o + a - st, feats[a - off:z - off]))
             p = np.arange(st, st + n, dtype=np.int32)
             pos_np[o:o + n] = p
             pg = np.asarray(req.pages, dtype=np.int32)
@@ -237,7 +253,7 @@ class ModelRunner:
             self.timings["graph_steps"] += 1
             t2 = time.perf_counter()
         else:
-            logits = self._forward(B, T, max_q, out.num_decode)
+            logits = self._forward(B, T, max_q, out.num_decode, mm_rows)
             t2 = time.perf_counter()
             kw = {}
             if any_random or any_pen:

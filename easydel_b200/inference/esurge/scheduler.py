@@ -61,6 +61,9 @@ class EngineRequest:
     finish_time: float | None = None
     num_preemptions: int = 0
     stop_reason: tp.Any = None
+    # images: (offset of the first placeholder token in the prompt, projected features [rows, hidden] on the device)
+    mm_embeds: list = field(default_factory=list)
+    mm_hash: tp.Any = None                # joins the page hashes: same tokens + other images = other pages
 
     @property
     def all_token_ids(self) -> list[int]:
@@ -178,7 +181,7 @@ class Scheduler:
     def _admit_with_prefix(self, req: EngineRequest) -> None:
         """Shares the cached full pages that match the request's token prefix."""
         tokens = req.all_token_ids
-        req.page_hashes = hash_request_pages(tokens, self.page_size)
+        req.page_hashes = hash_request_pages(tokens, self.page_size, req.mm_hash)
         # never serve the whole request from cache: the last token must be recomputed to produce logits
         usable = req.page_hashes[: max(0, (len(tokens) - 1) // self.page_size)]
         hit = self.pool.lookup(usable)
@@ -198,7 +201,7 @@ class Scheduler:
             return
         tokens = req.all_token_ids
         if len(req.page_hashes) < full:
-            req.page_hashes = hash_request_pages(tokens[: full * self.page_size], self.page_size)
+            req.page_hashes = hash_request_pages(tokens[: full * self.page_size], self.page_size, req.mm_hash)
         for i in range(req.num_registered_pages, full):
             self.pool.register(req.pages[i], req.page_hashes[i])
         req.num_registered_pages = full

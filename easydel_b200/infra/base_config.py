@@ -323,7 +323,7 @@ class EasyDeLBaseConfig(PretrainedConfig):
     @property
     def mesh(self):
         """The process-group mesh built from ``sharding_axis_dims`` (created lazily, cached)."""
-        if self._mesh is None:
+        if self.__dict__.get("_mesh") is None:
             from ..parallel.mesh import DeviceMesh
 
             self._mesh = DeviceMesh.from_config(self)

@@ -32,6 +32,9 @@ class VLMConfig(EasyDeLBaseConfig):
 
     vision_default, text_default = "clip_vision_model", "llama"
 
+    def __init__(self, **kw):   # explicit: the config base class generates a constructor for classes without one
+        super().__init__(**kw)
+
     def _init_parts(self, vision_config, text_config, image_token_index, kw):
         self.vision_config = build_sub_config(vision_config, self.vision_default)
         self.text_config = build_sub_config(text_config, self.text_default)

@@ -1,0 +1,92 @@
+"""Images through the serving engine on CPU: resolution buckets, feature cache, placeholder expansion, chunked
+prefill across an image, and engine output equal to the model's own greedy decoding."""
+
+import numpy as np
+import torch
+
+from easydel_b200.inference import SamplingParams
+from easydel_b200.inference.esurge import eSurge
+from easydel_b200.inference.esurge.multimodal import MultiModalManager, VisionEncoderCache
+from easydel_b200.modules.llava import LlavaConfig, LlavaForConditionalGeneration
+
+IMG = 127
+
+
+def _model():
+    torch.manual_seed(0)
+    cfg = LlavaConfig(
+        vision_config=dict(model_type="clip_vision_model", hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                           num_attention_heads=4, image_size=28, patch_size=14),
+        text_config=dict(model_type="llama", vocab_size=128, hidden_size=32, intermediate_size=64,
+                         num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         max_position_embeddings=512, eos_token_id=126),
+        image_token_index=IMG, vision_feature_layer=-1)
+    return LlavaForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+
+
+def _image(seed, size=(40, 30)):
+    return (np.random.default_rng(seed).random((size[1], size[0], 3)) * 255).astype(np.uint8)
+
+
+def test_feature_cache_lru_and_budget():
+    c = VisionEncoderCache(capacity_mb=1)
+    a = torch.zeros(64, 1024)            # 256 KiB each
+    for i in range(5):
+        c.put(f"k{i}", a + i)
+    assert len(c) == 4 and not c.contains("k0") and c.size_mb <= 1.0
+    assert c.get("k1") is not None and c.get("k0") is None
+    c.put("k5", a)                       # k2 is now the oldest
+    assert not c.contains("k2") and c.contains("k1")
+    assert c.get_stats()["hits"] == 1 and c.get_stats()["misses"] == 1
+    c.put("huge", torch.zeros(1024, 1024))
+    assert not c.contains("huge")
+
+
+def test_manager_buckets_placeholders_and_cache():
+    m = _model()
+    mgr = MultiModalManager(m)
+    px = mgr.process_images([_image(0), _image(1, (28, 28))])
+    assert all(p.shape == (3, 28, 28) for p in px)
+    ids, embeds, key = mgr.prepare([5, IMG, 6, IMG, 7], [_image(0), _image(1)])
+    rows = embeds[0][1].shape[0]
+    assert rows == 4 and ids == [5] + [IMG] * 4 + [6] + [IMG] * 4 + [7]
+    assert [o for o, _ in embeds] == [1, 6] and len(set(key)) == 2
+    before = mgr.get_cache_stats()["misses"]
+    ids2, embeds2, key2 = mgr.prepare([IMG] * 4 + [9], [_image(0)])     # an already expanded run, a cached image
+    assert ids2 == [IMG] * 4 + [9] and key2[0] == key[0]
+    assert mgr.get_cache_stats()["misses"] == before and torch.equal(embeds2[0][1], embeds[0][1])
+    msgs = [{"role": "user", "content": [{"type": "text", "text": "look: "},
+                                          {"type": "image_url", "image_url": {"url": "data:image/png;base64,AAAA"}},
+                                          {"type": "image", "image": _image(3)}]}]
+    images, videos = mgr.extract_media_from_messages(msgs)
+    assert len(images) == 2 and not videos and images[0].startswith("data:")
+    assert mgr.normalize_messages(msgs, "<image>")[0]["content"] == "look: <image><image>"
+
+
+def _greedy(m, ids, images, n, mgr):
+    full_ids, embeds, _ = mgr.prepare(ids, images)
+    toks = list(full_ids)
+    for _ in range(n):
+        t = torch.tensor([toks])
+        emb = m.get_input_embeddings()(t)
+        for off, f in embeds:
+            emb[0, off:off + f.shape[0]] = f
+        with torch.no_grad():
+            nxt = int(m.language_model(inputs_embeds=emb).logits[0, -1].argmax())
+        toks.append(nxt)
+    return toks[len(full_ids):]
+
+
+def test_engine_serves_images_like_the_model_even_across_prefill_chunks():
+    m = _model()
+    prompt = [3, 4, IMG, 9, 10, 11, IMG, 12]
+    imgs = [_image(0), _image(1)]
+    for budget in (64, 5):       # 5 tokens per step: both images are split across engine steps
+        eng = eSurge(m, max_model_len=256, max_num_seqs=2, max_num_batched_tokens=budget, num_pages=8)
+        want = _greedy(m, prompt, imgs, 6, eng.multimodal)
+        out = eng.generate(prompt, SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True), images=imgs)[0]
+        assert list(out.outputs[0].token_ids) == want, (budget, out.outputs[0].token_ids, want)
+    # other images behind the same tokens do not hit the prefix cache of the first request
+    other = eng.generate(prompt, SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True),
+                         images=[_image(5), _image(6)])[0]
+    assert list(other.outputs[0].token_ids) == _greedy(m, prompt, [_image(5), _image(6)], 6, eng.multimodal)
