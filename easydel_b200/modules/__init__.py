@@ -8,6 +8,8 @@ from . import families_classic  # noqa: F401
 from .families_classic import *  # noqa: F401,F403
 from . import mamba  # noqa: F401
 from .mamba import *  # noqa: F401,F403
+from . import families_extra  # noqa: F401
+from .families_extra import *  # noqa: F401,F403
 from .auto import *  # noqa: F401,F403
 from . import roberta  # noqa: F401
 from .roberta import *  # noqa: F401,F403

@@ -1,0 +1,123 @@
+"""Decoder families whose checkpoints ship with their own modelling code rather than a ``transformers`` class:
+InternLM2, EXAONE-3, Grok-1 (easydel/modules/{internlm2,exaone,grok_1}). Same spec-driven decoder; the blocks below
+are the name tables and the layout hooks of their checkpoints.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ._base.families import base_spec, define_family, moe_spec
+
+EXPORTS: dict[str, type] = {}
+
+_LLAMA = dict(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+              num_attention_heads=32, num_key_value_heads=None, head_dim=None, hidden_act="silu",
+              max_position_embeddings=4096, initializer_range=0.02, rms_norm_eps=1e-6, use_cache=True,
+              rope_theta=10000.0, rope_scaling=None, attention_bias=False, tie_word_embeddings=False)
+
+
+def _d(**kw):
+    d = dict(_LLAMA)
+    d.update(kw)
+    return d
+
+
+# ---- internlm2 (easydel/modules/internlm2): one ``wqkv`` matrix laid out per KV group as
+# ---- [q_0 .. q_{g-1} | k | v] (g = query heads per KV head), MLP named w1 (gate) / w3 (up) / w2 (down) ----
+def _internlm2_geometry(model):
+    s = model.spec
+    return s.num_heads, s.num_kv_heads, s.head_dim
+
+
+def _internlm2_in(model, sd):
+    hq, hkv, d = _internlm2_geometry(model)
+    g = hq // hkv
+    out = {}
+    for k, t in sd.items():
+        if ".attention.wqkv." in k:
+            x = t.view(hkv, g + 2, d, *t.shape[1:])
+            q = x[:, :g].reshape(hq * d, *t.shape[1:])
+            kk = x[:, g].reshape(hkv * d, *t.shape[1:])
+            v = x[:, g + 1].reshape(hkv * d, *t.shape[1:])
+            out[k] = torch.cat([q, kk, v], 0)
+        else:
+            out[k] = t
+    return out
+
+
+def _internlm2_out(model, sd):
+    hq, hkv, d = _internlm2_geometry(model)
+    g = hq // hkv
+    out = {}
+    for k, t in sd.items():
+        if ".attention.wqkv." in k:
+            q, kk, v = torch.split(t, [hq * d, hkv * d, hkv * d], 0)
+            x = torch.cat([q.view(hkv, g, d, *t.shape[1:]), kk.view(hkv, 1, d, *t.shape[1:]),
+                           v.view(hkv, 1, d, *t.shape[1:])], 1)
+            out[k] = x.reshape(-1, *t.shape[1:]).contiguous()
+        else:
+            out[k] = t
+    return out
+
+
+EXPORTS.update(define_family(
+    "internlm2", _d(vocab_size=103168, bias=True, pad_token_id=0, bos_token_id=1, eos_token_id=2),
+    lambda c: base_spec(c, attn_bias=getattr(c, "bias", False), o_bias=getattr(c, "bias", False)),
+    class_prefix="InternLM2",
+    rules=[("model.tok_embeddings.", "model.embed_tokens."), ("output.", "lm_head."),
+           (".attention.wqkv.", ".self_attn.qkv_proj."), (".attention.wo.", ".self_attn.o_proj."),
+           (".attention_norm.", ".input_layernorm."), (".ffn_norm.", ".post_attention_layernorm."),
+           (".feed_forward.w1.", ".mlp.gate_proj."), (".feed_forward.w3.", ".mlp.up_proj."),
+           (".feed_forward.w2.", ".mlp.down_proj.")],
+    tensor_in=_internlm2_in, tensor_out=_internlm2_out, hf_keeps_fused=("qkv_proj",)))
+
+
+# ---- exaone 3 (easydel/modules/exaone): Llama block under GPT-2 style names ----
+def _exaone_post(c):
+    if getattr(c, "num_hidden_layers", None) is None:
+        c.num_hidden_layers = c.num_layers
+    c.num_layers = c.num_hidden_layers
+    c.rms_norm_eps = c.layer_norm_epsilon
+    c.hidden_act = c.activation_function
+
+
+EXPORTS.update(define_family(
+    "exaone", dict(vocab_size=102400, hidden_size=2048, intermediate_size=14336, num_layers=32,
+                   num_hidden_layers=None, num_attention_heads=32, num_key_value_heads=8, head_dim=None,
+                   activation_function="silu", max_position_embeddings=2048, initializer_range=0.02,
+                   layer_norm_epsilon=1e-5, use_cache=True, embed_dropout=0.0, attention_dropout=0.0,
+                   rope_theta=10000.0, rope_scaling=None, tie_word_embeddings=False, bos_token_id=1, eos_token_id=2),
+    lambda c: base_spec(c, norm_eps=c.layer_norm_epsilon, act=c.activation_function),
+    config_post=_exaone_post, class_prefix="Exaone",
+    rules=[("transformer.wte.", "model.embed_tokens."), ("transformer.ln_f.", "model.norm."),
+           ("transformer.h.", "model.layers."), (".attn.attention.out_proj.", ".self_attn.o_proj."),
+           (".attn.attention.", ".self_attn."), (".ln_1.", ".input_layernorm."),
+           (".ln_2.", ".post_attention_layernorm."), (".mlp.c_fc_0.", ".mlp.gate_proj."),
+           (".mlp.c_fc_1.", ".mlp.up_proj."), (".mlp.c_proj.", ".mlp.down_proj.")]))
+
+
+# ---- grok-1 (easydel/modules/grok_1): norms before and after both branches, tanh-capped attention logits with a
+# ---- fixed multiplier, GELU-gated experts (linear = gate, linear_v = up, linear_1 = down), scaled embeddings / logits
+EXPORTS.update(define_family(
+    "grok-1", _d(vocab_size=131072, hidden_size=6144, intermediate_size=32768, num_hidden_layers=64,
+                 num_attention_heads=48, num_key_value_heads=8, attn_output_multiplier=0.08838834764831845,
+                 max_attn_value=30.0, max_position_embeddings=8192, embedding_multiplier_scale=78.38367176906169,
+                 output_multiplier_scale=0.5773502691896257, rms_norm_eps=1e-5, num_experts_per_tok=2,
+                 num_experts=8, output_router_logits=False, router_aux_loss_coef=0.001, hidden_act="gelu"),
+    lambda c: base_spec(c, sandwich_norm=True, act="gelu_new", attn_scale=c.attn_output_multiplier,
+                        attn_softcap=c.max_attn_value, embedding_multiplier=c.embedding_multiplier_scale,
+                        logit_scale=c.output_multiplier_scale,
+                        moe=moe_spec(c, num_experts=c.num_experts, top_k=c.num_experts_per_tok,
+                                     intermediate=c.intermediate_size, norm_topk=True,
+                                     aux_coef=c.router_aux_loss_coef)),
+    class_prefix="Grok1",
+    rules=[(".attn.", ".self_attn."), (".pre_attn_norm.", ".input_layernorm."),
+           (".post_attn_norm.", ".post_attn_out_layernorm."), (".pre_moe_norm.", ".pre_feedforward_layernorm."),
+           (".post_moe_norm.", ".post_feedforward_layernorm."), (".moe_block.gate.", ".mlp.gate."),
+           (".moe_block.experts.", ".mlp.experts."), (".linear_v.", ".up_proj."), (".linear_1.", ".down_proj."),
+           (".linear.", ".gate_proj.")],
+    with_classifier=False))
+
+globals().update(EXPORTS)
+__all__ = sorted(EXPORTS)

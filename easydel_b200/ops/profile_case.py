@@ -65,10 +65,23 @@ def main() -> None:
     elif what == "qgemv":
         from ..layers.quantization import quantize, quantized_matmul
 
-        q = quantize(bf(14336, 4096) * 0.05, "nf4")
+        # a launch is a few microseconds: 32 launches over 8 different weight matrices (250 MB, twice the L2) are
+        # captured in one CUDA graph, so that neither the host nor the L2 decides the number
+        qs = [quantize(bf(14336, 4096) * 0.05, "nf4") for _ in range(8)]
         x = bf(4, 4096)
-        fn = lambda: quantized_matmul(x, q)  # noqa: E731
-        work = 14336 * 4096 * 0.5 + 14336 * 64 * 2      # bytes: the roofline of this kernel is HBM
+        graphed = 32
+
+        def many():
+            for i in range(graphed):
+                quantized_matmul(x, qs[i % 8])
+
+        many()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            many()
+        fn = g.replay
+        work = graphed * (14336 * 4096 * 0.5 + 14336 * 64 * 2)     # bytes: the roofline of this kernel is HBM
     elif what == "adamw":
         n = 256 << 20
         p, g = torch.zeros(n, device=dev), torch.randn(n, device=dev)

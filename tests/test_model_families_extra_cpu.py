@@ -1,0 +1,109 @@
+"""Families without a ``transformers`` class: exported checkpoints are re-read with independent code (the documented
+tensor layout + the Hugging Face Llama block they are equivalent to) and must give the same logits."""
+
+import torch
+import transformers
+
+import easydel_b200.modules as M
+from easydel_b200.utils.parameters_transformation import hf_to_internal, internal_to_hf
+
+KW = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_attention_heads=4, num_key_value_heads=2,
+          max_position_embeddings=64)
+
+
+def _llama(sd, bias, eps):
+    cfg = transformers.LlamaConfig(**KW, num_hidden_layers=2, attention_bias=bias, rms_norm_eps=eps)
+    hf = transformers.LlamaForCausalLM(cfg).float().eval()
+    missing, unexpected = hf.load_state_dict(sd, strict=False)
+    assert not unexpected and not [m for m in missing if "rotary" not in m], (missing, unexpected)
+    return hf
+
+
+def _jitter(m):
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn(p.shape, generator=g) * 0.1)
+    return m.eval()
+
+
+def test_internlm2_grouped_wqkv_layout():
+    torch.manual_seed(0)
+    m = _jitter(M.InternLM2ForCausalLM(M.InternLM2Config(**KW, num_hidden_layers=2, bias=True), dtype=torch.float32,
+                                       param_dtype=torch.float32))
+    sd = internal_to_hf(m)
+    hq, hkv, d = 4, 2, 16
+    g = hq // hkv
+    llama = {}
+    for k, t in sd.items():
+        k2 = (k.replace("model.tok_embeddings", "model.embed_tokens").replace("output.", "lm_head.")
+              .replace("attention_norm", "input_layernorm").replace("ffn_norm", "post_attention_layernorm")
+              .replace("feed_forward.w1", "mlp.gate_proj").replace("feed_forward.w3", "mlp.up_proj")
+              .replace("feed_forward.w2", "mlp.down_proj").replace("attention.wo", "self_attn.o_proj"))
+        if "attention.wqkv" in k:
+            x = t.view(hkv, g + 2, d, -1) if t.dim() == 2 else t.view(hkv, g + 2, d)
+            tail = k.rsplit(".", 1)[1]
+            base = k.split("attention.wqkv")[0] + "self_attn."
+            llama[base + "q_proj." + tail] = x[:, :g].reshape(hq * d, *t.shape[1:])
+            llama[base + "k_proj." + tail] = x[:, g].reshape(hkv * d, *t.shape[1:])
+            llama[base + "v_proj." + tail] = x[:, g + 1].reshape(hkv * d, *t.shape[1:])
+        else:
+            llama[k2] = t
+    hf = _llama(llama, True, 1e-6)
+    ids = torch.randint(0, 128, (2, 24))
+    with torch.no_grad():
+        assert (m(input_ids=ids).logits - hf(input_ids=ids).logits).abs().max() < 2e-4
+    back = hf_to_internal(m, sd)
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+
+
+def test_exaone_is_llama_under_other_names():
+    torch.manual_seed(0)
+    kw = dict(KW)
+    m = _jitter(M.ExaoneForCausalLM(M.ExaoneConfig(**kw, num_layers=2), dtype=torch.float32,
+                                    param_dtype=torch.float32))
+    assert m.config.num_hidden_layers == 2
+    sd = internal_to_hf(m)
+    ren = [("transformer.wte", "model.embed_tokens"), ("transformer.ln_f", "model.norm"),
+           ("transformer.h.", "model.layers."), ("attn.attention.out_proj", "self_attn.o_proj"),
+           ("attn.attention.", "self_attn."), ("ln_1", "input_layernorm"), ("ln_2", "post_attention_layernorm"),
+           ("mlp.c_fc_0", "mlp.gate_proj"), ("mlp.c_fc_1", "mlp.up_proj"), ("mlp.c_proj", "mlp.down_proj")]
+    llama = {}
+    for k, t in sd.items():
+        for a, b in ren:
+            k = k.replace(a, b)
+        llama[k] = t
+    hf = _llama(llama, False, 1e-5)
+    ids = torch.randint(0, 128, (2, 24))
+    with torch.no_grad():
+        assert (m(input_ids=ids).logits - hf(input_ids=ids).logits).abs().max() < 2e-4
+    back = hf_to_internal(m, sd)
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+
+
+def test_grok1_block_structure_and_names():
+    torch.manual_seed(0)
+    cfg = M.Grok1Config(**KW, num_hidden_layers=2, num_experts=4, num_experts_per_tok=2, max_attn_value=5.0,
+                        attn_output_multiplier=0.2, embedding_multiplier_scale=3.0, output_multiplier_scale=0.5)
+    m = _jitter(M.Grok1ForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32))
+    sd = internal_to_hf(m)
+    for frag in ("layers.0.attn.q_proj", "pre_attn_norm", "post_attn_norm", "pre_moe_norm", "post_moe_norm",
+                 "moe_block.gate", "moe_block.experts.3.linear.", "experts.0.linear_v.", "experts.0.linear_1."):
+        assert any(frag in k for k in sd), frag
+    back = hf_to_internal(m, sd)
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    # one layer by hand: x + post(attn(pre(x))) then x + post(moe(pre(x))), logits scaled
+    ids = torch.randint(0, 128, (1, 10))
+    out = m(input_ids=ids, output_hidden_states=True)
+    layer = m.model.layers[0]
+    x = out.hidden_states[0]
+    pos = torch.arange(10)[None]
+    a = layer.post_attn_out_layernorm(layer.self_attn(layer.input_layernorm(x), pos))
+    x1 = x + a
+    mo, _ = layer.mlp(layer.pre_feedforward_layernorm(x1))
+    x2 = x1 + layer.post_feedforward_layernorm(mo)
+    assert (x2 - out.hidden_states[1]).abs().max() < 1e-5
+    assert (x - m.model.embed_tokens(ids) * 3.0).abs().max() < 1e-6
+    assert layer.self_attn.softcap == 5.0 and abs(layer.self_attn.scale - 0.2) < 1e-9
+    assert torch.allclose(out.logits, m.lm_head(out.last_hidden_state) * 0.5, atol=1e-5)
