@@ -56,18 +56,18 @@ class SiglipVisionConfig(_VisionConfigBase):
 
 
 class _EncoderLayer(nn.Module):
-    def __init__(self, c, idx, dtype):
+    def __init__(self, c, idx, dtype, causal: bool = False):
         super().__init__()
         hd = c.hidden_size // c.num_attention_heads
         self.layer_norm1 = LayerNorm(c.hidden_size, c.layer_norm_eps, dtype=dtype)
         self.self_attn = Attention(c.hidden_size, c.num_attention_heads, c.num_attention_heads, hd, layer_idx=idx,
-                                   bias=True, o_bias=True, rope=None, causal=False, dtype=dtype,
+                                   bias=True, o_bias=True, rope=None, causal=causal, dtype=dtype,
                                    init_std=c.initializer_range)
         self.layer_norm2 = LayerNorm(c.hidden_size, c.layer_norm_eps, dtype=dtype)
         self.mlp = PlainMLP(c.hidden_size, c.intermediate_size, c.hidden_act, True, dtype, c.initializer_range)
 
-    def forward(self, x, pos):
-        x = x + self.self_attn(self.layer_norm1(x), pos)
+    def forward(self, x, pos, segment_ids=None):
+        x = x + self.self_attn(self.layer_norm1(x), pos, segment_ids=segment_ids)
         return x + self.mlp(self.layer_norm2(x))
 
 

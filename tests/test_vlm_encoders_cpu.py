@@ -150,3 +150,43 @@ def test_aya_vision_matches_hf():
     ids = torch.randint(0, 120, (2, 12))
     ids[:, 2:6] = 127        # 4x4 patches folded 2x2 -> 4 image tokens
     _check_vlm(m, hf, ids, torch.randn(2, 3, 28, 28))
+
+
+def _dual(ours_cls, cfg_cls, hf_cls, hf_cfg_cls, extra=None, text_extra=None):
+    V = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, image_size=28,
+             patch_size=14)
+    T = dict(vocab_size=99, hidden_size=24, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4,
+             max_position_embeddings=16, eos_token_id=98, **(text_extra or {}))
+    kw = dict(extra or {})
+    torch.manual_seed(0)
+    m = ours_cls(cfg_cls(text_config=dict(T), vision_config=dict(V), **kw), dtype=torch.float32,
+                 param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = hf_cls(hf_cfg_cls(text_config=dict(T), vision_config=dict(V), **kw)).float().eval()
+    missing, unexpected = hf.load_state_dict(internal_to_hf(m), strict=False)
+    assert not unexpected and all("position_ids" in x for x in missing), (missing, unexpected)
+    ids = torch.randint(0, 97, (3, 10))
+    ids[:, -1] = 98
+    ids[0, 6] = 98          # an earlier end-of-text token: CLIP pools there
+    pix = torch.randn(3, 3, 28, 28)
+    with torch.no_grad():
+        a, b = m(input_ids=ids, pixel_values=pix, return_loss=True), hf(input_ids=ids, pixel_values=pix,
+                                                                         return_loss=True)
+    assert (a.logits_per_text - b.logits_per_text).abs().max() < 2e-4
+    assert (a.image_embeds - b.image_embeds).abs().max() < 2e-5
+    assert abs(float(a.loss) - float(b.loss)) < 2e-4
+    back = hf_to_internal(m, hf.state_dict())
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+
+
+def test_clip_dual_tower_matches_hf():
+    from easydel_b200.modules.vision import CLIPConfig, CLIPModel
+
+    _dual(CLIPModel, CLIPConfig, transformers.CLIPModel, transformers.CLIPConfig, dict(projection_dim=20))
+
+
+def test_siglip_dual_tower_matches_hf():
+    from easydel_b200.modules.vision import SiglipConfig, SiglipModel
+
+    _dual(SiglipModel, SiglipConfig, transformers.SiglipModel, transformers.SiglipConfig,
+          text_extra=dict(projection_size=32))
