@@ -58,3 +58,24 @@ def test_build_model_trainer_and_train(tmp_path):
     eng = e.set_esurge(max_model_len=128, max_num_seqs=2).build_esurge()
     res = eng.generate([3, 4, 5], None)
     assert len(res[0].outputs[0].token_ids) > 0
+
+
+def test_cluster_config_generator(tmp_path):
+    import importlib.util
+    import pathlib
+
+    import yaml
+
+    path = pathlib.Path(__file__).resolve().parents[1] / "autoscale" / "generate_cluster_configs.py"
+    spec = importlib.util.spec_from_file_location("generate_cluster_configs", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    files = mod.generate("sft", 4, "img", "missing.yaml", "train", tmp_path)
+    ray = yaml.safe_load(files["ray"].read_text())
+    assert ray["max_workers"] == 3 and ray["available_node_types"]["b200_worker"]["resources"]["GPU"] == 8
+    docs = list(yaml.safe_load_all(files["k8s"].read_text()))
+    sts = [d for d in docs if d["kind"] == "StatefulSet"][0]
+    assert sts["spec"]["replicas"] == 4
+    args = sts["spec"]["template"]["spec"]["containers"][0]["args"][0]
+    assert "--nnodes=4" in args and "--nproc-per-node=8" in args and "--master-addr=sft-0.sft" in args
+    assert "#SBATCH --nodes=4" in files["slurm"].read_text()
