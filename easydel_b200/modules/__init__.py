@@ -21,3 +21,6 @@ from .whisper import *  # noqa: F401,F403
 from . import gemma3, aya_vision  # noqa: F401
 from .gemma3 import *  # noqa: F401,F403
 from .aya_vision import *  # noqa: F401,F403
+from . import pixtral, mistral3  # noqa: F401
+from .pixtral import *  # noqa: F401,F403
+from .mistral3 import *  # noqa: F401,F403

@@ -190,3 +190,37 @@ def test_siglip_dual_tower_matches_hf():
 
     _dual(SiglipModel, SiglipConfig, transformers.SiglipModel, transformers.SiglipConfig,
           text_extra=dict(projection_size=32))
+
+
+def test_mistral3_pixtral_matches_hf_with_images_of_two_sizes():
+    from easydel_b200.modules.mistral3 import Mistral3Config, Mistral3ForConditionalGeneration
+
+    V = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, image_size=56,
+             patch_size=7, head_dim=8)
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=8)
+    cfg = Mistral3Config(vision_config=dict(model_type="pixtral", **V), text_config=dict(model_type="mistral", **T),
+                         image_token_index=127, spatial_merge_size=2)
+    torch.manual_seed(0)
+    m = Mistral3ForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.Mistral3ForConditionalGeneration(transformers.Mistral3Config(
+        vision_config=transformers.PixtralVisionConfig(**V), text_config=transformers.MistralConfig(**T),
+        image_token_index=127, spatial_merge_size=2, tie_word_embeddings=False)).float().eval()
+    missing, unexpected = hf.load_state_dict(internal_to_hf(m), strict=False)
+    assert not unexpected and not missing, (missing, unexpected)
+    # image 0: 28 x 56 pixels -> 4 x 8 patches -> 2 x 4 merged rows; image 1: 56 x 28 -> 8 x 4 -> 4 x 2
+    pix = torch.randn(2, 3, 56, 56)
+    sizes = torch.tensor([[28, 56], [56, 28]])
+    ids = torch.randint(0, 120, (1, 24))
+    ids[0, 2:10] = 127
+    ids[0, 12:20] = 127
+    with torch.no_grad():
+        a = m(input_ids=ids, pixel_values=pix, image_sizes=sizes).logits
+        b = hf(input_ids=ids, pixel_values=pix, image_sizes=sizes).logits
+    assert (a - b).abs().max() < 3e-4, (a - b).abs().max()
+    back = hf_to_internal(m, hf.state_dict())
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    _, met = m.compute_loss(input_ids=ids, pixel_values=pix, image_sizes=sizes, labels=ids)
+    met.loss.backward()
+    assert torch.isfinite(met.loss)
