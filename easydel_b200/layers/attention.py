@@ -153,9 +153,15 @@ class Attention(nn.Module):
             qkv = qkv.clamp(-self.clip_qkv, self.clip_qkv)
         if self.qk_norm is not None and self.qk_norm != "l2_post_rope":
             qkv = self._apply_qk_norm(qkv)
-        if self.rotary is not None:
-            qkv = self.rotary.rotate_packed(qkv, positions, self.num_heads + self.num_kv_heads)
-        q, k, v = self._split(qkv)
+        if self.rotary is not None and positions.dim() == 3:
+            # three position streams (temporal, height, width) share the frequency axis by sections
+            q, k, v = self._split(qkv)
+            q, k = self.rotary(positions, q, k)
+            positions = positions[0]
+        else:
+            if self.rotary is not None:
+                qkv = self.rotary.rotate_packed(qkv, positions, self.num_heads + self.num_kv_heads)
+            q, k, v = self._split(qkv)
         if self.qk_norm == "l2_post_rope":      # weightless RMS normalisation of every head, after the rotation
             q = (q.float() * torch.rsqrt(q.float().pow(2).mean(-1, keepdim=True) + self.qk_norm_eps)).to(v.dtype)
             k = (k.float() * torch.rsqrt(k.float().pow(2).mean(-1, keepdim=True) + self.qk_norm_eps)).to(v.dtype)

@@ -24,3 +24,5 @@ from .aya_vision import *  # noqa: F401,F403
 from . import pixtral, mistral3  # noqa: F401
 from .pixtral import *  # noqa: F401,F403
 from .mistral3 import *  # noqa: F401,F403
+from . import qwen2_vl  # noqa: F401
+from .qwen2_vl import *  # noqa: F401,F403

@@ -63,7 +63,8 @@ def rope_args(c, head_dim: int, partial: float = 1.0, neox: bool = True, theta_a
         theta = theta or params.get("rope_theta")
         if scaling is None and params.get("rope_type", "default") != "default":
             scaling = {k: v for k, v in params.items() if k != "rope_theta"}
-    if isinstance(scaling, dict) and (scaling.get("rope_type") or scaling.get("type")) in (None, "default"):
+    if isinstance(scaling, dict) and (scaling.get("rope_type") or scaling.get("type")) in (None, "default") \
+            and not scaling.get("mrope_section"):
         scaling = None
     return dict(rotary_dim=head_dim, max_position=c.max_position_embeddings, base=theta or 10000.0,
                 is_neox_style=neox, rope_scaling=scaling, partial_rotary_factor=partial)

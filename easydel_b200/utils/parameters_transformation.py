@@ -43,7 +43,10 @@ def internal_to_hf(model, state: dict[str, torch.Tensor] | None = None) -> dict[
         leaf, mod_name = parts[-1], parts[-2] if len(parts) > 1 else ""
         prefix = ".".join(parts[:-2])
         pre = prefix + "." if prefix else ""
-        if mod_name in FUSED_SPLITS and t.dim() <= 2 and mod_name not in getattr(model, "hf_keeps_fused", ()) and \
+        keeps = getattr(model, "hf_keeps_fused", ())
+        # entries with a dot are parameter-name prefixes (a sub-model whose checkpoints keep the fused matrix)
+        kept = mod_name in keeps or any("." in e and name.startswith(e) for e in keeps)
+        if mod_name in FUSED_SPLITS and t.dim() <= 2 and not kept and \
                 hasattr(_module_of(model, ".".join(parts[:-1])), "local_out_splits"):
             mod = _module_of(model, ".".join(parts[:-1]))
             widths = mod.local_out_splits()

@@ -224,3 +224,42 @@ def test_mistral3_pixtral_matches_hf_with_images_of_two_sizes():
     _, met = m.compute_loss(input_ids=ids, pixel_values=pix, image_sizes=sizes, labels=ids)
     met.loss.backward()
     assert torch.isfinite(met.loss)
+
+
+def test_qwen2_vl_matches_hf_and_decodes_incrementally():
+    from easydel_b200.modules.qwen2_vl import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+
+    V = dict(depth=2, embed_dim=32, hidden_size=32, mlp_ratio=2, num_heads=4, in_channels=3, patch_size=7,
+             spatial_merge_size=2, temporal_patch_size=2)
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, rope_scaling={"type": "mrope", "mrope_section": [1, 1, 2]})
+    cfg = Qwen2VLConfig(vision_config=dict(V), text_config=dict(T), image_token_id=127)
+    torch.manual_seed(0)
+    m = Qwen2VLForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.Qwen2VLForConditionalGeneration(transformers.Qwen2VLConfig(
+        vision_config=dict(V), text_config=dict(T), image_token_id=127, video_token_id=126,
+        vision_start_token_id=125)).float().eval()
+    missing, unexpected = hf.load_state_dict(internal_to_hf(m), strict=False)
+    assert not unexpected and not missing, (missing, unexpected)
+    # two images: 4 x 8 patches -> 2 x 4 = 8 tokens, and 4 x 4 patches -> 2 x 2 = 4 tokens
+    grid = torch.tensor([[1, 4, 8], [1, 4, 4]])
+    pix = torch.randn(int((grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * 7 * 7)
+    ids = torch.randint(0, 120, (1, 24))
+    ids[0, 2:10] = 127
+    ids[0, 13:17] = 127
+    with torch.no_grad():
+        a = m(input_ids=ids, pixel_values=pix, image_grid_thw=grid).logits
+        b = hf(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=(ids == 127).long()).logits
+    assert (a - b).abs().max() < 3e-4, (a - b).abs().max()
+    back = hf_to_internal(m, hf.state_dict())
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    _, met = m.compute_loss(input_ids=ids, pixel_values=pix, image_grid_thw=grid, labels=ids)
+    met.loss.backward()
+    assert torch.isfinite(met.loss)
+    cache = m.init_cache(1, 32)
+    with torch.no_grad():
+        o1 = m(input_ids=ids[:, :20], pixel_values=pix, image_grid_thw=grid, past_key_values=cache).logits
+        cache.advance(20)
+        o2 = m(input_ids=ids[:, 20:21], past_key_values=cache).logits
+    assert (o1 - a[:, :20]).abs().max() < 3e-4 and (o2[:, 0] - a[:, 20]).abs().max() < 3e-4
