@@ -77,8 +77,10 @@ class MoEBlock(nn.Module):
                  use_score_bias: bool = False, router_bias: bool = False, shared_intermediate_size: int = 0,
                  shared_gate: bool = False, dtype=torch.float32, init_std: float = 0.02, expert_init_std: float = 0.01,
                  ep_size: int = 1, ep_rank: int = 0, ep_group=None, tp_size: int = 1, tp_rank: int = 0,
-                 tp_group=None, router_dtype=None, expert_bias: bool = False, scale_input: bool = False):
+                 tp_group=None, router_dtype=None, expert_bias: bool = False, scale_input: bool = False,
+                 router_jitter_eps: float = 0.01):
         super().__init__()
+        self.router_jitter_eps = router_jitter_eps
         # Llama-4: the routing score multiplies the expert's input instead of its output
         self.scale_input = scale_input
         if num_experts % ep_size:
@@ -112,9 +114,28 @@ class MoEBlock(nn.Module):
                                                                init_std=init_std)
 
     # ------------------------------------------------------------------ routing
+    def _route_sparsemixer(self, lf: torch.Tensor):
+        """Phi-3.5-MoE routing (deterministic form): experts are picked one after the other by arg-max; the weight
+        of each pick is its softmax probability among the experts whose logit lies within a relative margin
+        ``2 * jitter_eps`` of that pick's logit (earlier picks excluded)."""
+        eps = self.router_jitter_eps
+        scores = lf
+        ws, ids = [], []
+        for _ in range(self.top_k):
+            top, ind = scores.max(dim=-1, keepdim=True)
+            factor = lf.abs().clamp(min=top)
+            drop = ((top - lf) / factor) > (2 * eps)
+            gates = torch.softmax(scores.masked_fill(drop, float("-inf")), dim=-1)
+            ws.append(gates.gather(-1, ind))
+            ids.append(ind)
+            scores = scores.scatter(-1, ind, float("-inf"))
+        return torch.cat(ws, -1), torch.cat(ids, -1), torch.softmax(lf, dim=-1)
+
     def route(self, logits: torch.Tensor):
         """Returns (weights [T,k] fp32, idx [T,k] int64, probs [T,E] fp32)."""
         lf = logits.float()
+        if self.scoring == "sparsemixer":
+            return self._route_sparsemixer(lf)
         probs = torch.softmax(lf, dim=-1) if self.scoring == "softmax" else torch.sigmoid(lf)
         scores = probs
         if self.e_score_correction_bias is not None:

@@ -54,6 +54,7 @@ class MoESpec:
     expert_bias: bool = False         # per-expert biases on both expert projections (GPT-OSS)
     expert_act: str | None = None     # gated activation of the experts when it differs from the dense MLP's
     scale_input: bool = False         # routing score applied to the experts' input (Llama-4)
+    router_jitter_eps: float = 0.01   # margin of the sparsemixer routing (Phi-3.5-MoE)
 
 
 @dataclass
@@ -193,7 +194,7 @@ class DecoderLayer(nn.Module):
             ep_size, ep_rank, ep_group = _ep_of(config)
             self.mlp = MoEBlock(spec.hidden_size, moe.intermediate_size, moe.num_experts, moe.top_k,
                                 act=moe.expert_act or spec.act, expert_bias=moe.expert_bias,
-                                scale_input=moe.scale_input,
+                                scale_input=moe.scale_input, router_jitter_eps=moe.router_jitter_eps,
                                 norm_topk_prob=moe.norm_topk_prob, scoring=moe.scoring,
                                 routed_scaling_factor=moe.routed_scaling_factor, n_group=moe.n_group,
                                 topk_group=moe.topk_group, use_score_bias=moe.use_score_bias,

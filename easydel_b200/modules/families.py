@@ -554,5 +554,24 @@ EXPORTS.update(define_family(
            ("feed_forward.", "mlp.")],
     tensor_in=_fused_experts_in, tensor_out=_fused_experts_out, hf_keeps_fused=("experts",)))
 
+
+
+# ---- phimoe (easydel/modules/phimoe): Mixtral block with LayerNorm (weights + biases) and sparsemixer routing ----
+def _phimoe_spec(c):
+    return base_spec(c, norm="layer", norm_bias=True, norm_eps=c.rms_norm_eps,
+                     sliding_window=getattr(c, "sliding_window", None), lm_head_bias=getattr(c, "lm_head_bias", False),
+                     moe=moe_spec(c, num_experts=c.num_local_experts, top_k=c.num_experts_per_tok,
+                                  intermediate=c.intermediate_size, norm_topk=False, scoring="sparsemixer",
+                                  router_jitter_eps=c.router_jitter_noise, aux_coef=c.router_aux_loss_coef))
+
+
+EXPORTS.update(define_family(
+    "phimoe", _d(vocab_size=32064, hidden_size=4096, intermediate_size=6400, num_hidden_layers=32,
+                 num_attention_heads=32, num_key_value_heads=8, max_position_embeddings=131072, rms_norm_eps=1e-5,
+                 rope_theta=1000000.0, sliding_window=None, num_experts_per_tok=2, num_local_experts=16,
+                 output_router_logits=False, router_aux_loss_coef=0.001, router_jitter_noise=0.01,
+                 input_jitter_noise=0.0, attention_bias=False, lm_head_bias=False),
+    _phimoe_spec, class_prefix="Phimoe", rules=[("mlp.router.", "mlp.gate.")]))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

@@ -80,6 +80,7 @@ CASES = {
                         no_rope_layers=[1, 1, 1, 0], moe_layers=[0, 2, 3],
                         layer_types=["chunked_attention", "chunked_attention", "chunked_attention",
                                      "full_attention"]),
+    "phimoe": dict(num_local_experts=4, num_experts_per_tok=2, intermediate_size=96, router_jitter_noise=0.05),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                       shared_expert_intermediate_size=96),
 }
