@@ -107,6 +107,8 @@ class ArchSpec:
     attn_chunk_size: int | None = None  # block-diagonal attention on the rotary layers of a rope / nope mix (Llama-4)
     attn_temp_tuning: tuple[float, float] | None = None  # (attn_scale, floor_scale) on the layers without rotary
     qk_norm_rope_only: bool = False   # QK norm only on layers that rotate
+    residual_mlp: bool = False        # Arctic: MoE layers add a dense hidden-sized MLP branch after attention while
+                                      # the experts read the layer input (norm of x, not of x + attention)
 
 
 def _norm(spec: ArchSpec, dtype) -> nn.Module:
@@ -208,6 +210,11 @@ class DecoderLayer(nn.Module):
         else:
             self.mlp = PlainMLP(spec.hidden_size, spec.intermediate_size, spec.act, spec.mlp_bias, dtype,
                                 spec.init_std, tp_size, tp_rank, tp_group)
+        self.has_residual_mlp = bool(spec.residual_mlp and self.is_moe)
+        if self.has_residual_mlp:
+            self.residual_layernorm = _norm(spec, dtype)
+            self.residual_mlp = GatedMLP(spec.hidden_size, spec.hidden_size, spec.act, False, dtype, spec.init_std,
+                                         tp_size, tp_rank, tp_group)
         if spec.residual == "post":
             self.post_attention_layernorm = _norm(spec, dtype)
             self.post_feedforward_layernorm = _norm(spec, dtype)
@@ -233,7 +240,14 @@ class DecoderLayer(nn.Module):
         spec = self.spec
         rl = None
         fused = spec.norm == "rms" and spec.residual == "pre" and not spec.sandwich_norm \
-            and spec.residual_multiplier is None
+            and spec.residual_multiplier is None and not self.has_residual_mlp
+        if self.has_residual_mlp:
+            if pending is not None:
+                x = x + _resolve(pending)
+            x1 = x + self._mix(self.input_layernorm(x), positions, segment_ids, cache_view, attn_meta)
+            r = x1 + self.residual_mlp(self.residual_layernorm(x1))
+            m, rl = self.mlp(self.post_attention_layernorm(x))
+            return r + m, None, rl
         if fused:
             if pending is None:
                 h = self.input_layernorm(x)

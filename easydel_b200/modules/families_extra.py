@@ -5,6 +5,8 @@ are the name tables and the layout hooks of their checkpoints.
 
 from __future__ import annotations
 
+import re
+
 import torch
 
 from ._base.families import base_spec, define_family, moe_spec
@@ -117,6 +119,34 @@ EXPORTS.update(define_family(
            (".post_moe_norm.", ".post_feedforward_layernorm."), (".moe_block.gate.", ".mlp.gate."),
            (".moe_block.experts.", ".mlp.experts."), (".linear_v.", ".up_proj."), (".linear_1.", ".down_proj."),
            (".linear.", ".gate_proj.")],
+    with_classifier=False))
+
+
+
+# ---- arctic (easydel/modules/arctic): every ``moe_layer_frequency``-th layer holds experts; there the attention
+# ---- output feeds a dense hidden-sized residual MLP while the experts read the layer input in parallel ----
+def _arctic_spec(c):
+    n, f = c.num_hidden_layers, max(1, c.moe_layer_frequency)
+    return base_spec(c, sliding_window=getattr(c, "sliding_window", None),
+                     residual_mlp=bool(c.parallel_attn_mlp_res),
+                     moe=moe_spec(c, num_experts=c.num_local_experts, top_k=c.num_experts_per_tok,
+                                  intermediate=c.intermediate_size, norm_topk=True,
+                                  layers=tuple(i for i in range(n) if (i + 1) % f == 0),
+                                  aux_coef=c.router_aux_loss_coef))
+
+
+EXPORTS.update(define_family(
+    "arctic", _d(vocab_size=32000, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                 num_attention_heads=32, num_key_value_heads=None, rms_norm_eps=1e-5, rope_theta=1e6,
+                 sliding_window=None, num_experts_per_tok=1, num_local_experts=8, router_aux_loss_coef=0.001,
+                 moe_layer_frequency=2, parallel_attn_mlp_res=False, moe_train_capacity_factor=1,
+                 moe_eval_capacity_factor=1, moe_min_capacity=0, moe_token_dropping=True),
+    _arctic_spec, class_prefix="Arctic",
+    rules=[(".block_sparse_moe", ".mlp"), (".w1.", ".gate_proj."), (".w3.", ".up_proj."), (".w2.", ".down_proj.")],
+    # dense layers keep their MLP one level deeper (block_sparse_moe.mlp.w1) than the experts of the sparse ones
+    tensor_in=lambda model, sd: {k.replace(".block_sparse_moe.mlp.", ".block_sparse_moe."): v for k, v in sd.items()},
+    tensor_out=lambda model, sd: {re.sub(r"\.block_sparse_moe\.(w[123])\.", r".block_sparse_moe.mlp.\1.", k): v
+                                  for k, v in sd.items()},
     with_classifier=False))
 
 globals().update(EXPORTS)

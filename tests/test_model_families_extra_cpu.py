@@ -107,3 +107,30 @@ def test_grok1_block_structure_and_names():
     assert (x - m.model.embed_tokens(ids) * 3.0).abs().max() < 1e-6
     assert layer.self_attn.softcap == 5.0 and abs(layer.self_attn.scale - 0.2) < 1e-9
     assert torch.allclose(out.logits, m.lm_head(out.last_hidden_state) * 0.5, atol=1e-5)
+
+
+def test_arctic_parallel_residual_mlp_and_names():
+    torch.manual_seed(0)
+    cfg = M.ArcticConfig(**KW, num_hidden_layers=2, num_local_experts=4, num_experts_per_tok=2, moe_layer_frequency=2,
+                         parallel_attn_mlp_res=True)
+    m = _jitter(M.ArcticForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32))
+    l0, l1 = m.model.layers
+    assert not l0.is_moe and l1.is_moe and l1.has_residual_mlp and not l0.has_residual_mlp
+    assert l1.residual_mlp.down_proj.weight.shape == (64, 64)
+    sd = internal_to_hf(m)
+    for frag in ("layers.0.block_sparse_moe.mlp.w1.", "layers.1.block_sparse_moe.gate.",
+                 "layers.1.block_sparse_moe.experts.3.w2.", "layers.1.residual_mlp.w3.", "layers.1.residual_layernorm."):
+        assert any(frag in k for k in sd), frag
+    back = hf_to_internal(m, sd)
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    ids = torch.randint(0, 128, (1, 10))
+    out = m(input_ids=ids, output_hidden_states=True)
+    x = out.hidden_states[1]
+    pos = torch.arange(10)[None]
+    x1 = x + l1.self_attn(l1.input_layernorm(x), pos)
+    want = x1 + l1.residual_mlp(l1.residual_layernorm(x1)) + l1.mlp(l1.post_attention_layernorm(x))[0]
+    raw, _, _ = l1(x, None, pos)
+    assert (raw - want).abs().max() < 1e-5
+    _, met = m.compute_loss(input_ids=ids, labels=ids)
+    met.loss.backward()
+    assert l1.residual_mlp.gate_up_proj.weight.grad.abs().sum() > 0
