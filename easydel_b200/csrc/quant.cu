@@ -8,8 +8,8 @@
 // so that  w[n, k] = lut[code[n, k]] * scales[n, k / group] (+ zeros[n, k / group]).
 //
 //   edl_dequant_bf16 : materialises bf16 weights (prefill / training path, followed by the tcgen05 GEMM).
-//   edl_qgemv        : y[M, N] = x[M, K] * W^T for M <= 8 (decode steps): every warp streams four weight rows of
-//                      packed codes with 16-byte loads, dequantises in registers and keeps M x 4 fp32 accumulators,
+//   edl_qgemv        : y[M, N] = x[M, K] * W^T for M <= 8 (decode steps): every warp streams two weight rows of
+//                      packed codes with 16-byte loads, dequantises through a conflict-free shared-memory code book and keeps M x 2 fp32 accumulators,
 //                      so the weights cross HBM once at 4 or 8 bits per value.
 // Counterpart in the reference: ejkernel quantized_matmul reached from
 // easydel/layers/linears/_linear_quantized.py:1030-1108.
@@ -59,18 +59,22 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ codes, const __nv_bfl
 }
 
 // Persistent, prefetching form: the grid is two CTAs per SM; every warp walks row groups of QG_ROWS weight rows.
-// For 4-bit codes one shared-memory lookup per code byte yields two dequantised values (a 256-entry table of value
-// pairs built from the 16-entry code book); the group scale (and zero point) is applied once per 16-byte vector to
-// the partial dot product instead of to every weight:  sum_k (lut[c_k] s + z) x_k = s * sum lut[c_k] x_k + z * sum x_k.
+// The code book lives in shared memory once per lane (entry e of lane l at word e * 32 + l), so that a lookup with
+// 32 unrelated codes still touches 32 different banks. For 4-bit codes one lookup per code byte yields both nibbles'
+// values as a bf16 pair (256 entries x 32 lanes x 4 bytes = 32 KB); 8-bit codes look up one fp32 value. The group
+// scale (and zero point) is applied once per 16-byte vector to the partial dot product instead of to every weight:
+//   sum_k (lut[c_k] s + z) x_k = s * sum lut[c_k] x_k + z * sum x_k.
 template <int M>
 __global__ void __launch_bounds__(QG_THREADS)
 qgemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* __restrict__ codes,
              const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ zeros,
              const float* __restrict__ lut, int bits, int N, int K, int group, __nv_bfloat16* __restrict__ out,
              long long ldo, const __nv_bfloat16* __restrict__ bias) {
-  __shared__ float2 s_pair[256];   // 4-bit: (low nibble value, high nibble value); 8-bit: (value, unused)
-  for (int i = threadIdx.x; i < 256; i += blockDim.x)
-    s_pair[i] = bits == 4 ? make_float2(lut[i & 15], lut[i >> 4]) : make_float2(lut[i], 0.f);
+  __shared__ uint32_t s_tab[256 * 32];
+  for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
+    const int e = i >> 5;
+    s_tab[i] = bits == 4 ? pack_bf16x2(lut[e & 15], lut[e >> 4]) : __float_as_uint(lut[e]);
+  }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = QG_THREADS / 32;
@@ -132,13 +136,15 @@ qgemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* 
           const uint32_t word = c == 0 ? q[r].x : c == 1 ? q[r].y : c == 2 ? q[r].z : q[r].w;
 #pragma unroll
           for (int bb = 0; bb < 4; ++bb) {
-            const float2 w2 = s_pair[(word >> (8 * bb)) & 0xFF];
+            const uint32_t t = s_tab[(((word >> (8 * bb)) & 0xFF) << 5) + lane];
             if (bits == 4) {
+              const float lo = __uint_as_float(t << 16), hi = __uint_as_float(t & 0xFFFF0000u);
 #pragma unroll
-              for (int m = 0; m < M; ++m) part[m][r] += w2.x * xv[m][2 * bb] + w2.y * xv[m][2 * bb + 1];
+              for (int m = 0; m < M; ++m) part[m][r] += lo * xv[m][2 * bb] + hi * xv[m][2 * bb + 1];
             } else {
+              const float w = __uint_as_float(t);
 #pragma unroll
-              for (int m = 0; m < M; ++m) part[m][r] += w2.x * xv[m][bb];
+              for (int m = 0; m < M; ++m) part[m][r] += w * xv[m][bb];
             }
           }
         }
