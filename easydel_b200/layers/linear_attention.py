@@ -31,17 +31,23 @@ class LinearAttentionState:
 class GatedDeltaNet(nn.Module):
     def __init__(self, hidden_size: int, num_k_heads: int, num_v_heads: int, head_k_dim: int, head_v_dim: int,
                  conv_kernel: int = 4, norm_eps: float = 1e-6, layer_idx: int = 0, dtype=torch.float32,
-                 init_std: float = 0.02):
+                 init_std: float = 0.02, layout: str = "grouped"):
+        """``layout="grouped"``: two fused projections ordered per key head (Qwen3-Next checkpoints);
+        ``"flat"``: four projections ``[q | k | v]``, ``z``, ``b``, ``a`` in plain head order (Qwen3.5)."""
         super().__init__()
+        self.layout = layout
         self.hk, self.hv, self.dk, self.dv = num_k_heads, num_v_heads, head_k_dim, head_v_dim
         self.rep = num_v_heads // num_k_heads
         self.key_dim, self.value_dim = head_k_dim * num_k_heads, head_v_dim * num_v_heads
         self.conv_dim = 2 * self.key_dim + self.value_dim
         self.conv_kernel, self.eps, self.layer_idx = conv_kernel, norm_eps, layer_idx
-        self.in_proj_qkvz = ColumnParallelLinear(hidden_size, 2 * self.key_dim + 2 * self.value_dim, bias=False,
-                                                 dtype=dtype, init_std=init_std)
-        self.in_proj_ba = ColumnParallelLinear(hidden_size, 2 * num_v_heads, bias=False, dtype=dtype,
-                                               init_std=init_std)
+        lin = lambda o: ColumnParallelLinear(hidden_size, o, bias=False, dtype=dtype, init_std=init_std)  # noqa: E731
+        if layout == "grouped":
+            self.in_proj_qkvz = lin(2 * self.key_dim + 2 * self.value_dim)
+            self.in_proj_ba = lin(2 * num_v_heads)
+        else:
+            self.in_proj_qkv, self.in_proj_z = lin(2 * self.key_dim + self.value_dim), lin(self.value_dim)
+            self.in_proj_b, self.in_proj_a = lin(num_v_heads), lin(num_v_heads)
         self.conv1d = nn.Conv1d(self.conv_dim, self.conv_dim, conv_kernel, groups=self.conv_dim, bias=False,
                                 padding=conv_kernel - 1, dtype=dtype)
         self.dt_bias = nn.Parameter(torch.ones(num_v_heads, dtype=dtype))
@@ -68,7 +74,12 @@ class GatedDeltaNet(nn.Module):
         """hidden ``[B, T, H]``. ``segment_ids`` ``[B, T]`` restart the recurrence at packed-document boundaries (0 =
         padding, which then forms its own segment). ``state``: a :class:`LinearAttentionState` for incremental use."""
         B, T, _ = hidden.shape
-        q, k, v, z, b, a = self._split(self.in_proj_qkvz(hidden), self.in_proj_ba(hidden))
+        if self.layout == "grouped":
+            q, k, v, z, b, a = self._split(self.in_proj_qkvz(hidden), self.in_proj_ba(hidden))
+        else:
+            q, k, v = torch.split(self.in_proj_qkv(hidden), [self.key_dim, self.key_dim, self.value_dim], dim=-1)
+            z = self.in_proj_z(hidden).view(B, T, self.hv, self.dv)
+            b, a = self.in_proj_b(hidden), self.in_proj_a(hidden)
         mixed = torch.cat([q, k, v], -1).reshape(B * T, self.conv_dim)
         if segment_ids is not None and state is None:
             from ..ops.attention import segment_ids_to_cu_seqlens

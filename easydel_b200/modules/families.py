@@ -573,5 +573,49 @@ EXPORTS.update(define_family(
                  input_jitter_noise=0.0, attention_bias=False, lm_head_bias=False),
     _phimoe_spec, class_prefix="Phimoe", rules=[("mlp.router.", "mlp.gate.")]))
 
+
+
+# ---- glm4_moe_lite (easydel/modules/glm4_moe_lite): the DeepSeek-V3 block (latent attention, sigmoid-scored experts
+# ---- with a score-correction bias, one shared expert) at GLM sizes ----
+_GLM4_LITE = dict(_DSV3, vocab_size=154880, hidden_size=2048, intermediate_size=10240, moe_intermediate_size=1536,
+                  num_hidden_layers=47, num_attention_heads=20, num_key_value_heads=20, n_shared_experts=1,
+                  n_routed_experts=64, routed_scaling_factor=1.8, kv_lora_rank=512, q_lora_rank=768,
+                  qk_rope_head_dim=64, v_head_dim=256, qk_nope_head_dim=192, n_group=1, topk_group=1,
+                  num_experts_per_tok=4, first_k_dense_replace=1, norm_topk_prob=True, rope_interleave=True,
+                  max_position_embeddings=202752, rms_norm_eps=1e-5, mlp_layer_types=None)
+EXPORTS.update(define_family(
+    "glm4_moe_lite", _GLM4_LITE, _deepseek_v3_spec, class_prefix="Glm4MoeLite",
+    rules=[("mlp.gate.e_score_correction_bias", "mlp.e_score_correction_bias")], with_classifier=False))
+
+
+
+# ---- qwen3_5 text (easydel/modules/qwen3_5): the Qwen3-Next hybrid with a dense MLP and un-grouped DeltaNet
+# ---- projections; text-only inputs give all three rotary streams the same position, i.e. plain partial rotary ----
+def _qwen3_5_spec(c):
+    spec = _qwen3_next_spec(c)
+    spec.linear_attn = dict(spec.linear_attn, layout="flat")
+    return spec
+
+
+EXPORTS.update(define_family(
+    "qwen3_5_text", _d(vocab_size=248320, hidden_size=4096, intermediate_size=12288, num_hidden_layers=32,
+                       num_attention_heads=16, num_key_value_heads=4, head_dim=256, partial_rotary_factor=0.25,
+                       max_position_embeddings=32768, rope_theta=10000000.0, linear_conv_kernel_dim=4,
+                       linear_key_head_dim=128, linear_value_head_dim=128, linear_num_key_heads=16,
+                       linear_num_value_heads=32, num_experts=0, layer_types=None, full_attention_interval=4),
+    _qwen3_5_spec, class_prefix="Qwen3_5Text"))
+
+
+EXPORTS.update(define_family(
+    "qwen3_5_moe_text", _d(vocab_size=248320, hidden_size=2048, intermediate_size=5632, num_hidden_layers=40,
+                           num_attention_heads=16, num_key_value_heads=2, head_dim=256, partial_rotary_factor=0.25,
+                           max_position_embeddings=32768, rope_theta=10000000.0, linear_conv_kernel_dim=4,
+                           linear_key_head_dim=128, linear_value_head_dim=128, linear_num_key_heads=16,
+                           linear_num_value_heads=32, decoder_sparse_step=1, moe_intermediate_size=512,
+                           shared_expert_intermediate_size=512, num_experts_per_tok=8, num_experts=256,
+                           norm_topk_prob=True, output_router_logits=False, router_aux_loss_coef=0.001,
+                           mlp_only_layers=None, layer_types=None, full_attention_interval=4),
+    _qwen3_5_spec, class_prefix="Qwen3_5MoeText", rules=[("mlp.shared_expert.", "mlp.shared_experts.")]))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

@@ -62,6 +62,12 @@ CASES = {
                                       n_shared_experts=2, n_routed_experts=8, kv_lora_rank=32, q_lora_rank=None,
                                       qk_rope_head_dim=16, v_head_dim=24, qk_nope_head_dim=32,
                                       num_experts_per_tok=3, first_k_dense_replace=1, max_position_embeddings=256)),
+    "glm4_moe_lite": dict(_replace=dict(vocab_size=512, hidden_size=128, intermediate_size=256,
+                                        moe_intermediate_size=64, num_hidden_layers=3, num_attention_heads=8,
+                                        num_key_value_heads=8, n_shared_experts=1, n_routed_experts=8,
+                                        kv_lora_rank=32, q_lora_rank=48, qk_rope_head_dim=16, v_head_dim=24,
+                                        qk_nope_head_dim=32, num_experts_per_tok=3, first_k_dense_replace=1,
+                                        max_position_embeddings=256, pad_token_id=0)),
     "glm4_moe": dict(_replace=dict(vocab_size=512, hidden_size=128, intermediate_size=256, moe_intermediate_size=64,
                                    num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=16,
                                    n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1, use_qk_norm=True,
@@ -81,6 +87,14 @@ CASES = {
                         layer_types=["chunked_attention", "chunked_attention", "chunked_attention",
                                      "full_attention"]),
     "phimoe": dict(num_local_experts=4, num_experts_per_tok=2, intermediate_size=96, router_jitter_noise=0.05),
+    "qwen3_5_text": dict(head_dim=16, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=8,
+                         linear_value_head_dim=16,
+                         layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"]),
+    "qwen3_5_moe_text": dict(head_dim=16, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=8,
+                             linear_value_head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=24,
+                             shared_expert_intermediate_size=48,
+                             layer_types=["linear_attention", "linear_attention", "linear_attention",
+                                          "full_attention"]),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                       shared_expert_intermediate_size=96),
 }
