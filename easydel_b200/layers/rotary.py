@@ -219,6 +219,14 @@ class MultiModalRotaryEmbedding(RotaryEmbedding):
         """positions3 ``[3, T]`` -> per-token cos/sin ``[T, rot/2]`` assembled section-wise."""
         cos, sin = self.tables(positions3.device)
         sec = self.rope.mrope_section or [self.rotary_dim // 2]
+        if self.rope.mrope_interleaved and positions3.shape[0] == 3:
+            # frequencies cycle through the streams (T H W T H W ... T T): H owns 1, 4, 7, ... below 3 * sec[1],
+            # W owns 2, 5, 8, ... below 3 * sec[2], the temporal stream keeps the rest
+            c, s = cos[positions3[0]].clone(), sin[positions3[0]].clone()
+            for dim, off in ((1, 1), (2, 2)):
+                idx = slice(off, sec[dim] * 3, 3)
+                c[:, idx], s[:, idx] = cos[positions3[dim]][:, idx], sin[positions3[dim]][:, idx]
+            return c, s
         outs_c, outs_s, start = [], [], 0
         for i, n in enumerate(sec):
             p = positions3[i % positions3.shape[0]]

@@ -26,3 +26,5 @@ from .pixtral import *  # noqa: F401,F403
 from .mistral3 import *  # noqa: F401,F403
 from . import qwen2_vl  # noqa: F401
 from .qwen2_vl import *  # noqa: F401,F403
+from . import qwen3_vl  # noqa: F401
+from .qwen3_vl import *  # noqa: F401,F403

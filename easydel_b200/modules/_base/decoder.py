@@ -323,7 +323,10 @@ class DecoderModel(EasyDeLBaseModule):
     def forward(self, input_ids: torch.Tensor | None = None, attention_mask: torch.Tensor | None = None,
                 position_ids: torch.Tensor | None = None, segment_ids: torch.Tensor | None = None,
                 inputs_embeds: torch.Tensor | None = None, past_key_values=None, cache_metadata=None,
-                output_hidden_states: bool = False, output_router_logits: bool = False, **_):
+                output_hidden_states: bool = False, output_router_logits: bool = False,
+                deepstack_embeds: tp.Sequence[torch.Tensor] | None = None, **_):
+        """``deepstack_embeds[i]`` ``[B, T, H]`` (zeros outside image positions) is added to the residual stream
+        after layer ``i`` (Qwen3-VL feeds intermediate vision features to the first decoder layers)."""
         spec = self.spec
         if inputs_embeds is None:
             if input_ids.dim() == 1:
@@ -371,6 +374,8 @@ class DecoderModel(EasyDeLBaseModule):
                                              policy)
             if rl is not None:
                 router_logits.append(rl)
+            if deepstack_embeds is not None and i < len(deepstack_embeds):
+                x = x + deepstack_embeds[i].to(x.dtype)
         if spec.final_norm:
             if pending is not None and spec.norm == "rms":
                 x, _ = self.norm.forward_with_residual(pending, x)
@@ -446,7 +451,7 @@ class DecoderForCausalLM(EasyDeLBaseModule):
         out = self.model(input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
                          segment_ids=segment_ids, inputs_embeds=inputs_embeds, past_key_values=past_key_values,
                          cache_metadata=cache_metadata, output_hidden_states=output_hidden_states,
-                         output_router_logits=output_router_logits)
+                         output_router_logits=output_router_logits, deepstack_embeds=kw.get("deepstack_embeds"))
         hidden = out.last_hidden_state
         logits = self.apply_lm_head(hidden) if apply_lm_head else None
         rl = getattr(out, "router_logits", None)

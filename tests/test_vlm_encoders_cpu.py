@@ -263,3 +263,67 @@ def test_qwen2_vl_matches_hf_and_decodes_incrementally():
         cache.advance(20)
         o2 = m(input_ids=ids[:, 20:21], past_key_values=cache).logits
     assert (o1 - a[:, :20]).abs().max() < 3e-4 and (o2[:, 0] - a[:, 20]).abs().max() < 3e-4
+
+
+def test_qwen3_vl_deepstack_matches_hf():
+    from easydel_b200.modules.qwen3_vl import Qwen3VLConfig, Qwen3VLForConditionalGeneration
+
+    V = dict(depth=3, hidden_size=32, intermediate_size=64, num_heads=4, in_channels=3, patch_size=7,
+             spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=32, num_position_embeddings=36,
+             deepstack_visual_indexes=[0, 1])
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=8,
+             rope_scaling={"rope_type": "default", "mrope_section": [2, 1, 1], "mrope_interleaved": True})
+    cfg = Qwen3VLConfig(vision_config=dict(V), text_config=dict(T), image_token_id=127)
+    torch.manual_seed(0)
+    m = Qwen3VLForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.Qwen3VLForConditionalGeneration(transformers.Qwen3VLConfig(
+        vision_config=dict(V), text_config=dict(T), image_token_id=127, video_token_id=126,
+        vision_start_token_id=125)).float().eval()
+    missing, unexpected = hf.load_state_dict(internal_to_hf(m), strict=False)
+    assert not unexpected and not missing, (missing, unexpected)
+    grid = torch.tensor([[1, 4, 8], [1, 4, 4]])
+    pix = torch.randn(int((grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * 7 * 7)
+    ids = torch.randint(0, 120, (1, 24))
+    ids[0, 2:10] = 127
+    ids[0, 13:17] = 127
+    with torch.no_grad():
+        a = m(input_ids=ids, pixel_values=pix, image_grid_thw=grid).logits
+        b = hf(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=(ids == 127).long()).logits
+    assert (a - b).abs().max() < 3e-4, (a - b).abs().max()
+    back = hf_to_internal(m, hf.state_dict())
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    _, met = m.compute_loss(input_ids=ids, pixel_values=pix, image_grid_thw=grid, labels=ids)
+    met.loss.backward()
+    assert torch.isfinite(met.loss) and m.visual.deepstack_merger_list[0].linear_fc1.weight.grad.abs().sum() > 0
+
+
+def test_qwen3_vl_moe_matches_hf():
+    from easydel_b200.modules.qwen3_vl import Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration
+    from easydel_b200.utils.parameters_transformation import _adapt_to_hf_module_names
+
+    V = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=4, in_channels=3, patch_size=7,
+             spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=32, num_position_embeddings=36,
+             deepstack_visual_indexes=[0])
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=8, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=24,
+             rope_scaling={"rope_type": "default", "mrope_section": [2, 1, 1], "mrope_interleaved": True})
+    cfg = Qwen3VLMoeConfig(vision_config=dict(V), text_config=dict(T), image_token_id=127)
+    torch.manual_seed(0)
+    m = Qwen3VLMoeForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.Qwen3VLMoeForConditionalGeneration(transformers.Qwen3VLMoeConfig(
+        vision_config=dict(V), text_config=dict(T), image_token_id=127, video_token_id=126,
+        vision_start_token_id=125)).float().eval()
+    sd = _adapt_to_hf_module_names(internal_to_hf(m), hf.state_dict())
+    missing, unexpected = hf.load_state_dict(sd, strict=False)
+    assert not unexpected and not missing, (missing, unexpected)
+    grid = torch.tensor([[1, 4, 4]])
+    pix = torch.randn(16, 3 * 2 * 7 * 7)
+    ids = torch.randint(0, 120, (1, 12))
+    ids[0, 3:7] = 127
+    with torch.no_grad():
+        a = m(input_ids=ids, pixel_values=pix, image_grid_thw=grid).logits
+        b = hf(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=(ids == 127).long()).logits
+    assert (a - b).abs().max() < 3e-4, (a - b).abs().max()
