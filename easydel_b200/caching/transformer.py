@@ -29,7 +29,7 @@ class TransformerCache:
                     dtype or model.dtype, device or model.device)
         layers = getattr(getattr(model, "model", model), "layers", ())
         for i, layer in enumerate(layers):
-            mixer = getattr(layer, "linear_attn", None)
+            mixer = getattr(layer, "linear_attn", None) or getattr(layer, "mamba", None)
             if mixer is not None:
                 cache.linear[i] = mixer.make_state(batch_size, dtype or model.dtype, device or model.device)
         return cache

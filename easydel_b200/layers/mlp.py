@@ -25,8 +25,17 @@ class GatedMLP(nn.Module):
         self.down_proj = RowParallelLinear(intermediate_size, hidden_size, bias=bias, dtype=dtype, init_std=init_std,
                                            tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group)
 
+    # fixed muP multipliers on the gate pre-activation and on the output (Falcon-H1); 1.0 elsewhere
+    gate_multiplier: float = 1.0
+    down_multiplier: float = 1.0
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(F.gated_act(self.gate_up_proj(x), self.act))
+        gu = self.gate_up_proj(x)
+        if self.gate_multiplier != 1.0:
+            half = gu.shape[-1] // 2
+            gu = torch.cat([gu[..., :half] * self.gate_multiplier, gu[..., half:]], dim=-1)
+        y = self.down_proj(F.gated_act(gu, self.act))
+        return y if self.down_multiplier == 1.0 else y * self.down_multiplier
 
 
 class PlainMLP(nn.Module):

@@ -107,6 +107,9 @@ class ArchSpec:
     attn_chunk_size: int | None = None  # block-diagonal attention on the rotary layers of a rope / nope mix (Llama-4)
     attn_temp_tuning: tuple[float, float] | None = None  # (attn_scale, floor_scale) on the layers without rotary
     qk_norm_rope_only: bool = False   # QK norm only on layers that rotate
+    ssm_branch: dict | None = None    # kwargs of layers.ssm_branch.SSDMixer: a Mamba-2 mixer beside attention (Falcon-H1)
+    branch_multipliers: tuple[float, float, float] = (1.0, 1.0, 1.0)  # attention input, attention output, SSM output
+    mlp_multipliers: tuple[float, float] = (1.0, 1.0)                  # gate pre-activation, MLP output
     residual_mlp: bool = False        # Arctic: MoE layers add a dense hidden-sized MLP branch after attention while
                                       # the experts read the layer input (norm of x, not of x + attention)
 
@@ -166,12 +169,19 @@ class DecoderLayer(nn.Module):
                                          **spec.mla)
         else:
             self.self_attn = self._mha(spec, layer_idx, dtype, rope, window, tp_size, tp_rank, tp_group)
+        if spec.ssm_branch is not None:
+            from ...layers.ssm_branch import SSDMixer
+
+            self.mamba = SSDMixer(spec.hidden_size, layer_idx=layer_idx, dtype=dtype, init_std=spec.init_std,
+                                  norm_eps=spec.norm_eps, **spec.ssm_branch)
         moe = spec.moe
         self.is_moe = moe is not None and (moe.layers is None or layer_idx in moe.layers)
         self._build_mlp(config, spec, layer_idx, dtype, tp_size, tp_rank, tp_group)
+        if spec.mlp_multipliers != (1.0, 1.0) and hasattr(self.mlp, "gate_multiplier"):
+            self.mlp.gate_multiplier, self.mlp.down_multiplier = spec.mlp_multipliers
         fused = spec.norm == "rms" and spec.residual == "pre" and not spec.sandwich_norm \
             and spec.residual_multiplier is None
-        if fused and tp_size > 1 and spec.mla is None and not self.is_linear:
+        if fused and tp_size > 1 and spec.mla is None and not self.is_linear and spec.ssm_branch is None:
             # both branch outputs feed a fused add+norm: let it also do the tensor-parallel sum
             self.self_attn.o_proj.defer_reduce = True
             if not self.is_moe:
@@ -234,6 +244,12 @@ class DecoderLayer(nn.Module):
         if self.is_linear:
             return self.linear_attn(h, segment_ids=segment_ids,
                                     state=None if cache_view is None else cache_view.linear_state)
+        if self.spec.ssm_branch is not None:
+            a_in, a_out, s_out = self.spec.branch_multipliers
+            m = self.mamba(h, segment_ids=segment_ids, state=None if cache_view is None else cache_view.linear_state)
+            a = self.self_attn(h * a_in if a_in != 1.0 else h, positions, segment_ids=segment_ids,
+                               cache_view=cache_view, attn_meta=attn_meta)
+            return m * s_out + a * a_out
         return self.self_attn(h, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
 
     def forward(self, x, pending, positions, segment_ids=None, cache_view=None, attn_meta=None):

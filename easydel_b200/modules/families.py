@@ -617,5 +617,37 @@ EXPORTS.update(define_family(
                            mlp_only_layers=None, layer_types=None, full_attention_interval=4),
     _qwen3_5_spec, class_prefix="Qwen3_5MoeText", rules=[("mlp.shared_expert.", "mlp.shared_experts.")]))
 
+
+
+# ---- falcon_h1 (easydel/modules/falcon_h1): every block runs attention and a Mamba-2 mixer side by side on the same
+# ---- normalised input and sums them; fixed muP multipliers sit on embeddings, keys, both branches, the MLP and logits
+def _falcon_h1_spec(c):
+    hd = getattr(c, "head_dim", None) or c.hidden_size // c.num_attention_heads
+    d_ssm = c.mamba_d_ssm if c.mamba_d_ssm is not None else int(c.mamba_expand * c.hidden_size)
+    return base_spec(
+        c, head_dim=hd, attn_scale=c.key_multiplier / math.sqrt(hd), embedding_multiplier=c.embedding_multiplier,
+        logit_scale=c.lm_head_multiplier, mlp_bias=c.mlp_bias, attn_bias=c.attention_bias, o_bias=c.attention_bias,
+        branch_multipliers=(c.attention_in_multiplier, c.attention_out_multiplier, c.ssm_out_multiplier),
+        mlp_multipliers=tuple(c.mlp_multipliers),
+        ssm_branch=dict(d_ssm=d_ssm, num_heads=c.mamba_n_heads, head_dim=c.mamba_d_head, n_groups=c.mamba_n_groups,
+                        d_state=c.mamba_d_state, d_conv=c.mamba_d_conv, conv_bias=c.mamba_conv_bias,
+                        proj_bias=c.mamba_proj_bias, rms_norm=c.mamba_rms_norm,
+                        norm_before_gate=c.mamba_norm_before_gate, multipliers=tuple(c.ssm_multipliers),
+                        in_multiplier=c.ssm_in_multiplier))
+
+
+EXPORTS.update(define_family(
+    "falcon_h1", _d(vocab_size=128000, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                    num_attention_heads=32, num_key_value_heads=8, max_position_embeddings=8192, rms_norm_eps=1e-5,
+                    rope_theta=100000.0, mamba_d_ssm=1024, mamba_n_heads=128, mamba_d_head=64, mamba_n_groups=1,
+                    mamba_d_state=256, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=256, mamba_conv_bias=True,
+                    mamba_proj_bias=False, mamba_norm_before_gate=True, mamba_rms_norm=False, projectors_bias=False,
+                    lm_head_multiplier=1.0, embedding_multiplier=1.0, mlp_multipliers=[1.0, 1.0], key_multiplier=1.0,
+                    attention_out_multiplier=1.0, attention_in_multiplier=1.0, ssm_multipliers=[1.0] * 5,
+                    ssm_in_multiplier=1.0, ssm_out_multiplier=1.0, mlp_bias=False),
+    _falcon_h1_spec, class_prefix="FalconH1",
+    rules=[(".feed_forward.", ".mlp."), (".pre_ff_layernorm.", ".post_attention_layernorm."),
+           ("model.final_layernorm.", "model.norm.")], with_classifier=False))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

@@ -95,6 +95,11 @@ CASES = {
                              shared_expert_intermediate_size=48,
                              layer_types=["linear_attention", "linear_attention", "linear_attention",
                                           "full_attention"]),
+    "falcon_h1": dict(mamba_d_ssm=64, mamba_n_heads=4, mamba_d_head=16, mamba_n_groups=2, mamba_d_state=8,
+                      mamba_chunk_size=8, key_multiplier=0.7, attention_in_multiplier=1.3,
+                      attention_out_multiplier=0.8, ssm_out_multiplier=0.6, ssm_in_multiplier=1.2,
+                      ssm_multipliers=[0.5, 1.5, 0.7, 1.1, 0.9], mlp_multipliers=[0.8, 1.25],
+                      embedding_multiplier=2.0, lm_head_multiplier=0.5, mamba_rms_norm=True),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                       shared_expert_intermediate_size=96),
 }
@@ -136,7 +141,7 @@ def test_family_matches_hf(model_type):
         assert torch.equal(back[k].to(v.dtype), v), k
 
 
-@pytest.mark.parametrize("model_type", ["qwen3_next", "llama4_text", "gpt_oss"])
+@pytest.mark.parametrize("model_type", ["qwen3_next", "llama4_text", "gpt_oss", "falcon_h1"])
 def test_incremental_decoding_matches_full_forward(model_type):
     """Prefill + single-token steps through the dense cache reproduce one full forward: hybrid state for the
     Gated-DeltaNet layers (qwen3_next), block-diagonal attention across a block boundary (llama4), sinks with
