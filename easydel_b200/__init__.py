@@ -24,6 +24,16 @@ _LAZY: dict[str, str] = {
     "LlamaConfig": "easydel_b200.modules.llama", "LlamaModel": "easydel_b200.modules.llama",
     "LlamaForCausalLM": "easydel_b200.modules.llama",
     "LlamaForSequenceClassification": "easydel_b200.modules.llama",
+    # serving
+    "eSurge": "easydel_b200.inference.esurge", "eSurgeApiServer": "easydel_b200.inference.esurge.server",
+    "InferenceApiRouter": "easydel_b200.inference.oai_proxies",
+    "ToolParserManager": "easydel_b200.inference.tools.parsers",
+    "eSurgeLMEvalAdapter": "easydel_b200.inference.evaluations.esurge_eval",
+    "MultiModalManager": "easydel_b200.inference.esurge.multimodal",
+    # quantisation
+    "EasyDeLQuantizationConfig": "easydel_b200.layers.quantization",
+    "QuantizationType": "easydel_b200.layers.quantization", "EasyQuantizer": "easydel_b200.layers.quantization",
+    "TurboQuantConfig": "easydel_b200.layers.turboquant", "TurboQuantConstants": "easydel_b200.layers.turboquant",
     # speech
     "vWhisperInference": "easydel_b200.inference.vwhisper",
     "vWhisperInferenceConfig": "easydel_b200.inference.vwhisper",

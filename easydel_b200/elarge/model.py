@@ -171,6 +171,13 @@ class eLargeModel:
     def set_mixture(self, informs: list[dict], **kw) -> "eLargeModel":
         return self.update("mixture", informs=informs, **kw)
 
+    def add_dataset(self, data_files, type: str | None = None, content_field: str = "text", weight: float = 1.0,  # noqa: A002
+                    **kw) -> "eLargeModel":
+        """Appends one source to ``mixture.informs`` (fluent form of the YAML list)."""
+        informs = list(self.config["mixture"].get("informs") or [])
+        informs.append(dict(data_files=data_files, type=type, content_field=content_field, weight=weight, **kw))
+        return self.update("mixture", informs=informs)
+
     def set_eval(self, tasks: list[str], **kw) -> "eLargeModel":
         return self.update("eval", tasks=tasks, **kw)
 
@@ -318,6 +325,12 @@ class eLargeModel:
             with open(ev["output_path"], "w") as f:
                 json.dump(res, f, indent=2, default=str)
         return res
+
+    def run_benchmarks(self, tasks: list[str] | None = None, tokenizer=None, **kw) -> dict:
+        """lm-eval tasks through the serving engine; ``tasks`` / keyword overrides replace the ``eval`` section's."""
+        if tasks is not None or kw:
+            self.update("eval", **({"tasks": tasks} if tasks is not None else {}), **kw)
+        return self.eval(tokenizer)
 
     def __repr__(self):
         m = self.config["model"]

@@ -177,6 +177,45 @@ class eSurge:
             self._paused = False
             self._work.notify_all()
 
+    def start_monitoring(self, prometheus_port: int = 9090, console: bool = False, update_interval: float = 1.0):
+        """Starts the Prometheus exporter (and optionally the console monitor) for this engine."""
+        from .monitoring import eSurgeMonitoringServer
+
+        if getattr(self, "_monitor", None) is None:
+            self._monitor = eSurgeMonitoringServer(self, prometheus_port=prometheus_port, console=console)
+            self._monitor.start(update_interval)
+        return {"prometheus": f"http://0.0.0.0:{prometheus_port}/metrics"}
+
+    def stop_monitoring(self) -> None:
+        mon = getattr(self, "_monitor", None)
+        if mon is not None:
+            mon.stop()
+            self._monitor = None
+
+    def start_profiling(self, output_dir: str = "esurge_profile", record_shapes: bool = False) -> None:
+        """Records engine steps with the torch profiler (CPU + CUDA activities) until :meth:`stop_profiling`
+        (easydel/inference/esurge/mixins/lifecycle.py:723-815)."""
+        if getattr(self, "_profiler", None) is not None:
+            raise RuntimeError("profiling is already running")
+        acts = [torch.profiler.ProfilerActivity.CPU]
+        if torch.cuda.is_available():
+            acts.append(torch.profiler.ProfilerActivity.CUDA)
+        self._profile_dir = output_dir
+        self._profiler = torch.profiler.profile(activities=acts, record_shapes=record_shapes)
+        self._profiler.__enter__()
+
+    def stop_profiling(self) -> str | None:
+        """Stops the profiler and writes a Chrome trace; returns its path."""
+        prof = getattr(self, "_profiler", None)
+        if prof is None:
+            return None
+        prof.__exit__(None, None, None)
+        self._profiler = None
+        os.makedirs(self._profile_dir, exist_ok=True)
+        path = os.path.join(self._profile_dir, f"{self.name}-{int(time.time())}.json")
+        prof.export_chrome_trace(path)
+        return path
+
     def update_model_weights(self, model=None, state_dict: dict | None = None) -> None:
         """Swaps in new weights (RL trainers refresh the policy between rollouts). Cached prefixes are dropped."""
         with self._lock:

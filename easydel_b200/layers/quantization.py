@@ -10,6 +10,8 @@ decode steps (up to 8 rows) run the fused dequant-GEMV, larger batches dequantis
 
 from __future__ import annotations
 
+import enum
+
 import ctypes as C
 import re
 import typing as tp
@@ -69,6 +71,20 @@ class EasyDeLQuantizationConfig:
 
 
 QuantizationConfig = EasyDeLQuantizationConfig
+
+
+class QuantizationType(str, enum.Enum):
+    """The weight formats of :data:`FORMATS` under the reference's enum name."""
+
+    INT8 = "int8"
+    A8BIT = "a8bit"
+    A4BIT = "a4bit"
+    AFFINE = "affine"
+    NF4 = "nf4"
+    MXFP4 = "mxfp4"
+    NVFP4 = "nvfp4"
+    MXFP8 = "mxfp8"
+    NVFP8 = "nvfp8"
 
 
 def _lut_tensor(spec: dict, device) -> torch.Tensor:

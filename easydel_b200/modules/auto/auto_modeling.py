@@ -110,3 +110,8 @@ for _suffix, _task in _TASKS.items():
     globals()[f"AutoEasyDeLModel{_suffix}"] = _mk(f"AutoEasyDeLModel{_suffix}", _task, BaseAutoEasyModel)
     globals()[f"AutoState{_suffix}"] = _mk(f"AutoState{_suffix}", _task, BaseAutoEasyState)
     __all__ += [f"AutoEasyDeLModel{_suffix}", f"AutoState{_suffix}"]
+
+# the reference's spelling of the any-to-any auto class
+AutoEasyDeLAnyToAnyModel = globals()["AutoEasyDeLModelForAnyToAny"]
+AutoStateAnyToAnyModel = globals()["AutoStateForAnyToAny"]
+__all__ += ["AutoEasyDeLAnyToAnyModel", "AutoStateAnyToAnyModel"]

@@ -108,3 +108,15 @@ def test_sampling_with_seed_is_reproducible():
     a = eng.generate([list(range(1, 10))], sp)[0].outputs[0].token_ids
     b = eng.generate([list(range(1, 10))], sp)[0].outputs[0].token_ids
     assert a == b and len(a) == 8
+
+
+def test_engine_profiling_and_monitoring_hooks(tmp_path):
+    eng = eSurge(_model(), max_model_len=128, max_num_seqs=2, num_pages=8)
+    eng.start_profiling(str(tmp_path))
+    eng.generate([1, 2, 3], SamplingParams(max_tokens=3, temperature=0.0, ignore_eos=True))
+    path = eng.stop_profiling()
+    assert path and path.endswith(".json") and (tmp_path / path.split("/")[-1]).exists()
+    assert eng.stop_profiling() is None
+    info = eng.start_monitoring(prometheus_port=0)
+    assert "prometheus" in info
+    eng.stop_monitoring()
