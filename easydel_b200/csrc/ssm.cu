@@ -182,6 +182,40 @@ __global__ void ragged_conv1d_kernel(const __nv_bfloat16* __restrict__ x, const 
   }
 }
 
+// ---- RWKV-4 WKV: out_t = (sum_{s<t} e^{-(t-1-s) w + k_s} v_s + e^{u + k_t} v_t) / (same with v = 1), w = exp(decay) ---
+// One thread per (sequence, channel); the running numerator / denominator are kept relative to a running maximum
+// exponent so that nothing overflows. state [nseq, 3, C] fp32 = (numerator, denominator, max exponent).
+__global__ void wkv4_kernel(const float* __restrict__ decay, const float* __restrict__ first,
+                            const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                            const int* __restrict__ cu, int C, float* __restrict__ state,
+                            __nv_bfloat16* __restrict__ out) {
+  const int b = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float w = -__expf(decay[c]), u = first[c];
+  float num = 0.f, den = 0.f, mx = -1e38f;
+  if (state) {
+    const float* st = state + (long long)b * 3 * C;
+    num = st[c]; den = st[C + c]; mx = st[2 * C + c];
+  }
+  for (int t = cu[b]; t < cu[b + 1]; ++t) {
+    const float kt = __bfloat162float(k[(long long)t * C + c]);
+    const float vt = __bfloat162float(v[(long long)t * C + c]);
+    float m = fmaxf(mx, kt + u);
+    float e1 = __expf(mx - m), e2 = __expf(kt + u - m);
+    out[(long long)t * C + c] = __float2bfloat16((e1 * num + e2 * vt) / (e1 * den + e2));
+    m = fmaxf(mx + w, kt);
+    e1 = __expf(mx + w - m); e2 = __expf(kt - m);
+    num = e1 * num + e2 * vt;
+    den = e1 * den + e2;
+    mx = m;
+  }
+  if (state) {
+    float* st = state + (long long)b * 3 * C;
+    st[c] = num; st[C + c] = den; st[2 * C + c] = mx;
+  }
+}
+
 }  // namespace
 }  // namespace edl
 
@@ -287,4 +321,14 @@ EDL_HOST_API int edl_ragged_conv1d(const void* x, const void* w, const void* bia
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, cu, seq_of_token, total, C, W, act,
       (const __nv_bfloat16*)conv_state, (__nv_bfloat16*)y);
   return check_cuda(cudaGetLastError(), "ragged_conv1d launch");
+}
+
+// k, v [total, C] bf16 packed by cu_seqlens; decay, first [C] fp32; state [nseq, 3, C] fp32 or null; out [total, C].
+EDL_HOST_API int edl_wkv4(const float* decay, const float* first, const void* k, const void* v, const int* cu,
+                          int nseq, int C, float* state, void* out, void* stream) {
+  if (nseq <= 0 || C <= 0) return 0;
+  dim3 grid((C + 127) / 128, nseq);
+  wkv4_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(decay, first, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+                                                      cu, C, state, (__nv_bfloat16*)out);
+  return check_cuda(cudaGetLastError(), "wkv4 launch");
 }

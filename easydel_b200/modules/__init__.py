@@ -28,3 +28,5 @@ from . import qwen2_vl  # noqa: F401
 from .qwen2_vl import *  # noqa: F401,F403
 from . import qwen3_vl  # noqa: F401
 from .qwen3_vl import *  # noqa: F401,F403
+from . import rwkv  # noqa: F401
+from .rwkv import *  # noqa: F401,F403

@@ -18,6 +18,7 @@ _lib.register("edl_selective_scan", i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, v
 _lib.register("edl_ssd_scan", i32, [vp, vp, vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, vp])
 _lib.register("edl_delta_rule", i32, [vp, vp, vp, vp, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp, vp])
 _lib.register("edl_ragged_conv1d", i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp, vp])
+_lib.register("edl_wkv4", i32, [vp, vp, vp, vp, vp, i32, i32, vp, vp, vp])
 
 
 def _cu(total: int, cu_seqlens, device):
@@ -260,3 +261,46 @@ def ragged_conv1d(x, w, bias=None, cu_seqlens=None, activation: str | None = "si
                         conv_state[b].copy_(torch.cat([conv_state[b], seg], 0)[-(W - 1):])
         return y
     return ragged_conv1d_reference(x, w, bias, cu_seqlens, activation, conv_state)
+
+
+# ----------------------------------------------------------------------------------------- RWKV-4 WKV
+def wkv4_reference(time_decay, time_first, k, v, cu_seqlens=None, state=None):
+    total, Cn = k.shape
+    cu = _cu(total, cu_seqlens, k.device).tolist()
+    w = -torch.exp(time_decay.float())
+    u = time_first.float()
+    outs, new_states = [], []
+    for b in range(len(cu) - 1):
+        if state is not None:
+            num, den, mx = state[b, 0].float(), state[b, 1].float(), state[b, 2].float()
+        else:
+            num = torch.zeros(Cn, device=k.device)
+            den = torch.zeros(Cn, device=k.device)
+            mx = torch.full((Cn,), -1e38, device=k.device)
+        for t in range(cu[b], cu[b + 1]):
+            kt, vt = k[t].float(), v[t].float()
+            m = torch.maximum(mx, kt + u)
+            e1, e2 = torch.exp(mx - m), torch.exp(kt + u - m)
+            outs.append((e1 * num + e2 * vt) / (e1 * den + e2))
+            m = torch.maximum(mx + w, kt)
+            e1, e2 = torch.exp(mx + w - m), torch.exp(kt - m)
+            num, den, mx = e1 * num + e2 * vt, e1 * den + e2, m
+        new_states.append(torch.stack([num, den, mx]))
+    if state is not None:
+        with torch.no_grad():
+            state.copy_(torch.stack([s.detach() for s in new_states]))
+    return torch.stack(outs).to(k.dtype) if outs else k.new_zeros(0, Cn)
+
+
+def wkv4(time_decay, time_first, k, v, cu_seqlens=None, state=None):
+    """RWKV-4 time mixing. k, v ``[total, C]``; time_decay / time_first ``[C]``; state ``[nseq, 3, C]`` fp32
+    (numerator, denominator, running max exponent), updated in place. Returns ``[total, C]``."""
+    if _use_kernel(k, v, time_decay, time_first) and k.dtype == torch.bfloat16:
+        total, Cn = k.shape
+        cu = _cu(total, cu_seqlens, k.device)
+        out = torch.empty_like(k)
+        _lib.call("edl_wkv4", time_decay.float().contiguous().data_ptr(), time_first.float().contiguous().data_ptr(),
+                  k.contiguous().data_ptr(), v.contiguous().data_ptr(), cu.data_ptr(), cu.numel() - 1, Cn,
+                  _lib.ptr(state), out.data_ptr(), _lib.stream_ptr())
+        return out
+    return wkv4_reference(time_decay, time_first, k, v, cu_seqlens, state)

@@ -92,3 +92,26 @@ def test_ragged_conv1d_cuda():
         got = ssm.ragged_conv1d(x, w, b, cu, "silu", c1)
         ref = ssm.ragged_conv1d_reference(x, w, b, cu, "silu", c2)
     assert _close(got, ref) and torch.equal(c1, c2)
+
+
+@pytest.mark.gpu
+def test_wkv4_kernel_matches_reference_with_state():
+    from easydel_b200.ops import ssm
+
+    torch.manual_seed(0)
+    C = 200
+    cu = torch.tensor([0, 37, 100], dtype=torch.int32, device="cuda")
+    k = torch.randn(100, C, device="cuda").to(torch.bfloat16)
+    v = torch.randn(100, C, device="cuda").to(torch.bfloat16)
+    decay, first = torch.randn(C, device="cuda") * 0.5 - 1.0, torch.randn(C, device="cuda") * 0.5
+    st = torch.zeros(2, 3, C, device="cuda")
+    st[:, 2] = -1e38
+    st_ref = st.clone()
+    out = ssm.wkv4(decay, first, k, v, cu, st)
+    ref = ssm.wkv4_reference(decay, first, k.float(), v.float(), cu, st_ref)
+    assert (out.float() - ref).abs().max() < 2e-2
+    assert (st[:, :2] - st_ref[:, :2]).abs().max() < 1e-3 * max(1.0, float(st_ref[:, :2].abs().max()))
+    # a second call continues from the state
+    out2 = ssm.wkv4(decay, first, k, v, cu, st)
+    ref2 = ssm.wkv4_reference(decay, first, k.float(), v.float(), cu, st_ref)
+    assert (out2.float() - ref2).abs().max() < 2e-2
