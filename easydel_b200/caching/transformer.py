@@ -30,6 +30,8 @@ class TransformerCache:
         layers = getattr(getattr(model, "model", model), "layers", ())
         for i, layer in enumerate(layers):
             mixer = getattr(layer, "linear_attn", None) or getattr(layer, "mamba", None)
+            if mixer is None and hasattr(getattr(layer, "self_attn", None), "make_state"):
+                mixer = layer.self_attn
             if mixer is not None:
                 cache.linear[i] = mixer.make_state(batch_size, dtype or model.dtype, device or model.device)
         return cache

@@ -107,6 +107,9 @@ class ArchSpec:
     attn_chunk_size: int | None = None  # block-diagonal attention on the rotary layers of a rope / nope mix (Llama-4)
     attn_temp_tuning: tuple[float, float] | None = None  # (attn_scale, floor_scale) on the layers without rotary
     qk_norm_rope_only: bool = False   # QK norm only on layers that rotate
+    lightning: dict | None = None     # kwargs of layers.lightning_attention.LightningAttention for "lightning" layers
+    normed_residual: dict | None = None  # MiniMax: the branch input (after the norm) is the residual, combined as
+                                      # alpha * normed + beta * branch; keys attn / lightning / mlp -> (alpha, beta)
     ssm_branch: dict | None = None    # kwargs of layers.ssm_branch.SSDMixer: a Mamba-2 mixer beside attention (Falcon-H1)
     branch_multipliers: tuple[float, float, float] = (1.0, 1.0, 1.0)  # attention input, attention output, SSM output
     mlp_multipliers: tuple[float, float] = (1.0, 1.0)                  # gate pre-activation, MLP output
@@ -154,8 +157,15 @@ class DecoderLayer(nn.Module):
             rope = spec.rope_local
         if ltype == "nope":
             rope = None
-        self.is_linear = ltype == "linear"
-        if self.is_linear:
+        self.is_linear = ltype in ("linear", "lightning")
+        self.ltype = ltype
+        if ltype == "lightning":
+            from ...layers.lightning_attention import LightningAttention
+
+            self.self_attn = LightningAttention(spec.hidden_size, spec.num_heads, spec.head_dim, spec.num_layers,
+                                                act=spec.act, layer_idx=layer_idx,
+                                                dtype=dtype, init_std=spec.init_std, **spec.lightning)
+        elif self.is_linear:
             from ...layers.linear_attention import GatedDeltaNet
 
             self.linear_attn = GatedDeltaNet(spec.hidden_size, layer_idx=layer_idx, dtype=dtype,
@@ -181,7 +191,8 @@ class DecoderLayer(nn.Module):
             self.mlp.gate_multiplier, self.mlp.down_multiplier = spec.mlp_multipliers
         fused = spec.norm == "rms" and spec.residual == "pre" and not spec.sandwich_norm \
             and spec.residual_multiplier is None
-        if fused and tp_size > 1 and spec.mla is None and not self.is_linear and spec.ssm_branch is None:
+        if fused and tp_size > 1 and spec.mla is None and not self.is_linear and spec.ssm_branch is None \
+                and spec.normed_residual is None:
             # both branch outputs feed a fused add+norm: let it also do the tensor-parallel sum
             self.self_attn.o_proj.defer_reduce = True
             if not self.is_moe:
@@ -241,6 +252,9 @@ class DecoderLayer(nn.Module):
     # The pair (x, pending) means the residual stream is x + pending; `pending` is folded in by the
     # next fused add+norm. Returns (x, pending, router_logits).
     def _mix(self, h, positions, segment_ids, cache_view, attn_meta):
+        if self.ltype == "lightning":
+            return self.self_attn(h, segment_ids=segment_ids,
+                                  state=None if cache_view is None else cache_view.linear_state)
         if self.is_linear:
             return self.linear_attn(h, segment_ids=segment_ids,
                                     state=None if cache_view is None else cache_view.linear_state)
@@ -257,6 +271,19 @@ class DecoderLayer(nn.Module):
         rl = None
         fused = spec.norm == "rms" and spec.residual == "pre" and not spec.sandwich_norm \
             and spec.residual_multiplier is None and not self.has_residual_mlp
+        if spec.normed_residual is not None:
+            if pending is not None:
+                x = x + _resolve(pending)
+            nr = spec.normed_residual
+            a_a, b_a = nr["lightning" if self.ltype == "lightning" else "attn"]
+            a_m, b_m = nr["mlp"]
+            h = self.input_layernorm(x)
+            x = h * a_a + self._mix(h, positions, segment_ids, cache_view, attn_meta) * b_a
+            h = self.post_attention_layernorm(x)
+            m = self.mlp(h)
+            if self.is_moe:
+                m, rl = m
+            return h * a_m + m * b_m, None, rl
         if self.has_residual_mlp:
             if pending is not None:
                 x = x + _resolve(pending)

@@ -649,5 +649,33 @@ EXPORTS.update(define_family(
     rules=[(".feed_forward.", ".mlp."), (".pre_ff_layernorm.", ".post_attention_layernorm."),
            ("model.final_layernorm.", "model.norm.")], with_classifier=False))
 
+
+
+# ---- minimax (easydel/modules/minimax): lightning (decayed linear) attention layers interleaved with softmax layers,
+# ---- experts in every layer, and residual branches that start from the *normalised* input with fixed alpha / beta ----
+def _minimax_spec(c):
+    n = c.num_hidden_layers
+    lt = getattr(c, "layer_types", None)
+    types = tuple("lightning" if "linear" in t else "full" for t in lt) if lt else \
+        tuple("full" if (i + 1) % 2 == 0 else "lightning" for i in range(n))
+    return base_spec(c, layer_types=types, lightning=dict(block_size=c.block_size),
+                     normed_residual=dict(attn=(c.full_attn_alpha_factor, c.full_attn_beta_factor),
+                                          lightning=(c.linear_attn_alpha_factor, c.linear_attn_beta_factor),
+                                          mlp=(c.mlp_alpha_factor, c.mlp_beta_factor)),
+                     moe=moe_spec(c, num_experts=c.num_local_experts, top_k=c.num_experts_per_tok,
+                                  intermediate=c.intermediate_size, norm_topk=True,
+                                  aux_coef=c.router_aux_loss_coef))
+
+
+EXPORTS.update(define_family(
+    "minimax", _d(vocab_size=32000, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,
+                  num_attention_heads=32, num_key_value_heads=8, head_dim=None, max_position_embeddings=4096 * 32,
+                  rms_norm_eps=1e-5, rope_theta=1e6, sliding_window=None, num_experts_per_tok=2, num_local_experts=8,
+                  output_router_logits=False, router_aux_loss_coef=0.001, router_jitter_noise=0.0, layer_types=None,
+                  block_size=256, full_attn_alpha_factor=1, full_attn_beta_factor=1, linear_attn_alpha_factor=1,
+                  linear_attn_beta_factor=1, mlp_alpha_factor=1, mlp_beta_factor=1),
+    _minimax_spec, class_prefix="MiniMax", rules=[(".self_attn.qkv_proj.", ".self_attn.lqkv.")],
+    with_classifier=False))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

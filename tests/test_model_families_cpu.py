@@ -100,6 +100,10 @@ CASES = {
                       attention_out_multiplier=0.8, ssm_out_multiplier=0.6, ssm_in_multiplier=1.2,
                       ssm_multipliers=[0.5, 1.5, 0.7, 1.1, 0.9], mlp_multipliers=[0.8, 1.25],
                       embedding_multiplier=2.0, lm_head_multiplier=0.5, mamba_rms_norm=True),
+    "minimax": dict(head_dim=16, num_local_experts=4, num_experts_per_tok=2, intermediate_size=96, block_size=16,
+                    layer_types=["linear_attention", "full_attention", "linear_attention", "full_attention"],
+                    full_attn_alpha_factor=1.5, full_attn_beta_factor=0.8, linear_attn_alpha_factor=1.2,
+                    linear_attn_beta_factor=0.9, mlp_alpha_factor=1.1, mlp_beta_factor=0.7),
     "qwen2_moe": dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                       shared_expert_intermediate_size=96),
 }
@@ -141,7 +145,7 @@ def test_family_matches_hf(model_type):
         assert torch.equal(back[k].to(v.dtype), v), k
 
 
-@pytest.mark.parametrize("model_type", ["qwen3_next", "llama4_text", "gpt_oss", "falcon_h1"])
+@pytest.mark.parametrize("model_type", ["qwen3_next", "llama4_text", "gpt_oss", "falcon_h1", "minimax"])
 def test_incremental_decoding_matches_full_forward(model_type):
     """Prefill + single-token steps through the dense cache reproduce one full forward: hybrid state for the
     Gated-DeltaNet layers (qwen3_next), block-diagonal attention across a block boundary (llama4), sinks with
