@@ -149,5 +149,76 @@ EXPORTS.update(define_family(
                                   for k, v in sd.items()},
     with_classifier=False))
 
+
+
+# ---- dbrx (easydel/modules/dbrx): fused clipped ``Wqkv``, bias-free LayerNorm, 16 experts of which 4 fire, stored
+# ---- as three [E * F, H] matrices (w1 gate, v1 up, w2 down with the output dimension last) ----
+def _dbrx_post(c):
+    a = dict(kv_n_heads=1, clip_qkv=None, rope_theta=10000.0, attn_pdrop=0.0)
+    a.update(c.attn_config or {})
+    f = dict(ffn_hidden_size=3584, moe_num_experts=4, moe_top_k=1, moe_jitter_eps=None, moe_loss_weight=0.01,
+             moe_normalize_expert_weights=1.0, ffn_act_fn={"name": "silu"}, hidden_size=c.d_model)
+    f.update(c.ffn_config or {})
+    c.attn_config, c.ffn_config = a, f
+    c.hidden_size, c.num_attention_heads, c.num_hidden_layers = c.d_model, c.n_heads, c.n_layers
+    c.num_key_value_heads, c.max_position_embeddings = a["kv_n_heads"], c.max_seq_len
+    c.rope_theta, c.intermediate_size = a["rope_theta"], f["ffn_hidden_size"]
+
+
+def _dbrx_spec(c):
+    f = c.ffn_config
+    if f.get("moe_normalize_expert_weights") not in (None, 1, 1.0):
+        raise ValueError("only L1-normalised (or un-normalised) expert weights are supported")
+    return base_spec(c, norm="layer", norm_bias=False, norm_eps=1e-5, clip_qkv=c.attn_config.get("clip_qkv"),
+                     act=f.get("ffn_act_fn", {}).get("name", "silu"),
+                     moe=moe_spec(c, num_experts=f["moe_num_experts"], top_k=f["moe_top_k"],
+                                  intermediate=f["ffn_hidden_size"],
+                                  norm_topk=f.get("moe_normalize_expert_weights") is not None,
+                                  aux_coef=f.get("moe_loss_weight", 0.0)))
+
+
+def _dbrx_in(model, sd):
+    e, fdim = model.spec.moe.num_experts, model.spec.moe.intermediate_size
+    out, parts = {}, {}
+    for k, t in sd.items():
+        if k.endswith((".ffn.experts.mlp.w1", ".ffn.experts.mlp.v1", ".ffn.experts.mlp.w2")):
+            parts.setdefault(k.rsplit(".", 1)[0], {})[k.rsplit(".", 1)[1]] = t.view(e, fdim, -1)
+        else:
+            out[k] = t
+    for base, p in parts.items():
+        pre = base[:-len("experts.mlp")]
+        out[pre + "gate_up_proj.weight"] = torch.cat([p["w1"], p["v1"]], 1)
+        out[pre + "down_proj.weight"] = p["w2"].transpose(1, 2)
+    return out
+
+
+def _dbrx_out(model, sd):
+    out = {}
+    for k, t in sd.items():
+        if t.dim() == 3 and k.endswith(".ffn.gate_up_proj.weight"):
+            f = t.shape[1] // 2
+            pre = k[:-len("gate_up_proj.weight")] + "experts.mlp."
+            out[pre + "w1"] = t[:, :f].reshape(-1, t.shape[2]).contiguous()
+            out[pre + "v1"] = t[:, f:].reshape(-1, t.shape[2]).contiguous()
+        elif t.dim() == 3 and k.endswith(".ffn.down_proj.weight"):
+            out[k[:-len("down_proj.weight")] + "experts.mlp.w2"] = t.transpose(1, 2).reshape(-1, t.shape[1]).contiguous()
+        else:
+            out[k] = t
+    return out
+
+
+EXPORTS.update(define_family(
+    "dbrx", dict(d_model=2048, n_heads=16, n_layers=24, max_seq_len=2048, vocab_size=32000, resid_pdrop=0.0,
+                 emb_pdrop=0.0, attn_config=None, ffn_config=None, use_cache=True, initializer_range=0.02,
+                 output_router_logits=False, tie_word_embeddings=False),
+    _dbrx_spec, config_post=_dbrx_post, class_prefix="Dbrx",
+    rules=[("transformer.wte.", "model.embed_tokens."), ("transformer.norm_f.", "model.norm."),
+           ("transformer.blocks.", "model.layers."), (".norm_attn_norm.norm_1.", ".input_layernorm."),
+           (".norm_attn_norm.norm_2.", ".post_attention_layernorm."),
+           (".norm_attn_norm.attn.Wqkv.", ".self_attn.qkv_proj."),
+           (".norm_attn_norm.attn.out_proj.", ".self_attn.o_proj."), (".ffn.router.layer.", ".mlp.gate."),
+           (".ffn.", ".mlp.")],
+    tensor_in=_dbrx_in, tensor_out=_dbrx_out, hf_keeps_fused=("qkv_proj", "experts"), with_classifier=False))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

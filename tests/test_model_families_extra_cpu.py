@@ -134,3 +134,38 @@ def test_arctic_parallel_residual_mlp_and_names():
     _, met = m.compute_loss(input_ids=ids, labels=ids)
     met.loss.backward()
     assert l1.residual_mlp.gate_up_proj.weight.grad.abs().sum() > 0
+
+
+def test_dbrx_nested_config_fused_qkv_and_expert_layout():
+    """The exported w1 / v1 / w2 matrices ([E * F, H] each) reproduce the block's expert output when used the way the
+    original implementation uses them: ``silu(x w1_e^T) * (x v1_e^T)`` then ``@ w2_e``."""
+    torch.manual_seed(0)
+    cfg = M.DbrxConfig(d_model=64, n_heads=4, n_layers=2, max_seq_len=64, vocab_size=128,
+                       attn_config=dict(kv_n_heads=2, clip_qkv=0.5, rope_theta=5000.0),
+                       ffn_config=dict(ffn_hidden_size=96, moe_num_experts=4, moe_top_k=2))
+    assert cfg.hidden_size == 64 and cfg.num_key_value_heads == 2 and cfg.intermediate_size == 96
+    m = _jitter(M.DbrxForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32))
+    sd = internal_to_hf(m)
+    assert sd["transformer.blocks.0.norm_attn_norm.attn.Wqkv.weight"].shape == (64 + 2 * 32, 64)
+    assert sd["transformer.blocks.0.ffn.experts.mlp.w1"].shape == (4 * 96, 64)
+    assert "transformer.blocks.1.norm_attn_norm.norm_2.weight" in sd and "transformer.blocks.0.ffn.router.layer.weight" in sd
+    back = hf_to_internal(m, sd)
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    layer = m.model.layers[0]
+    assert layer.self_attn.clip_qkv == 0.5 and layer.input_layernorm.bias is None
+    x = torch.randn(5, 64)
+    got, logits = layer.mlp(x[None])
+    p = torch.softmax(logits.float(), -1)
+    w, idx = p.topk(2, -1)
+    w = w / w.sum(-1, keepdim=True)
+    w1, v1, w2 = (sd[f"transformer.blocks.0.ffn.experts.mlp.{n}"].view(4, 96, 64) for n in ("w1", "v1", "w2"))
+    want = torch.zeros(5, 64)
+    for t in range(5):
+        for s in range(2):
+            e = int(idx[t, s])
+            h = torch.nn.functional.silu(x[t] @ w1[e].t()) * (x[t] @ v1[e].t())
+            want[t] += w[t, s] * (h @ w2[e])
+    assert (got[0] - want).abs().max() < 1e-5
+    ids = torch.randint(0, 128, (1, 12))
+    _, met = m.compute_loss(input_ids=ids, labels=ids)
+    assert torch.isfinite(met.loss)
