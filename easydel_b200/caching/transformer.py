@@ -67,9 +67,12 @@ class TransformerCacheView:
         s, e = c.length, c.length + T
         if e > c.max_len:
             raise ValueError(f"KV cache overflow: {e} > {c.max_len}")
-        c.k[self.layer, :, s:e] = k
-        c.v[self.layer, :, s:e] = v
-        kk, vv = c.k[self.layer, :, :e], c.v[self.layer, :, :e]
+        hk = k.shape[2]          # layers may use fewer KV heads than the widest one the cache was sized for
+        c.k[self.layer, :, s:e, :hk] = k
+        c.v[self.layer, :, s:e, :hk] = v
+        kk, vv = c.k[self.layer, :, :e, :hk], c.v[self.layer, :, :e, :hk]
+        if hk != c.k.shape[3]:
+            kk, vv = kk.contiguous(), vv.contiguous()
         seg = None
         if attn_meta is not None and attn_meta.get("kv_segment_ids") is not None:
             # left padding: padded positions carry segment 0

@@ -107,6 +107,7 @@ class ArchSpec:
     attn_chunk_size: int | None = None  # block-diagonal attention on the rotary layers of a rope / nope mix (Llama-4)
     attn_temp_tuning: tuple[float, float] | None = None  # (attn_scale, floor_scale) on the layers without rotary
     qk_norm_rope_only: bool = False   # QK norm only on layers that rotate
+    per_layer: tuple | None = None    # one dict of field overrides per layer (OpenELM scales heads / FFN by depth)
     lightning: dict | None = None     # kwargs of layers.lightning_attention.LightningAttention for "lightning" layers
     normed_residual: dict | None = None  # MiniMax: the branch input (after the norm) is the residual, combined as
                                       # alpha * normed + beta * branch; keys attn / lightning / mlp -> (alpha, beta)
@@ -351,7 +352,14 @@ class DecoderModel(EasyDeLBaseModule):
                                          spec.init_std)
         if spec.embed_layernorm:
             self.embed_layernorm = _norm(spec, pd)
-        self.layers = nn.ModuleList([DecoderLayer(config, spec, i, pd) for i in range(spec.num_layers)])
+        import dataclasses
+
+        def layer_spec(i):
+            if spec.per_layer is None:
+                return spec
+            return dataclasses.replace(spec, per_layer=None, **spec.per_layer[i])
+
+        self.layers = nn.ModuleList([DecoderLayer(config, layer_spec(i), i, pd) for i in range(spec.num_layers)])
         if spec.final_norm:
             self.norm = _norm(spec, pd)
 

@@ -220,5 +220,58 @@ EXPORTS.update(define_family(
            (".ffn.", ".mlp.")],
     tensor_in=_dbrx_in, tensor_out=_dbrx_out, hf_keeps_fused=("qkv_proj", "experts"), with_classifier=False))
 
+
+
+# ---- openelm (easydel/modules/openelm): layer-wise scaling -- the number of heads and the FFN width grow with depth;
+# ---- fused ``qkv_proj`` and ``proj_1`` (gate | up) in the checkpoints, per-head QK RMSNorm, tied output layer ----
+def make_divisible(v, divisor=8, min_value=None):
+    divisor = divisor or 8
+    min_value = min_value or divisor
+    new_v = max(min_value, int(v + divisor / 2) // divisor * divisor)
+    return new_v + divisor if new_v < 0.9 * v else new_v
+
+
+def _linspace(a, b, n):
+    return [round(a + (b - a) * i / max(n - 1, 1), 2) for i in range(n)]
+
+
+def _openelm_post(c):
+    n = c.num_transformer_layers
+    qm = c.qkv_multipliers
+    qms = [qm] * n if isinstance(qm, (int, float)) else _linspace(qm[0], qm[1], n)
+    heads = [int(make_divisible(c.model_dim * m, divisor=c.head_dim * c.num_gqa_groups)) // c.head_dim for m in qms]
+    c.num_query_heads, c.num_kv_heads = heads, [h // c.num_gqa_groups for h in heads]
+    fm = c.ffn_multipliers
+    c.ffn_multipliers = [fm] * n if isinstance(fm, (int, float)) else \
+        (_linspace(fm[0], fm[1], n) if len(fm) == 2 else list(fm))
+    c.hidden_size, c.num_hidden_layers, c.max_position_embeddings = c.model_dim, n, c.max_context_length
+    c.num_attention_heads, c.num_key_value_heads = max(heads), max(c.num_kv_heads)
+    c.intermediate_size = max(int(make_divisible(m * c.model_dim, c.ffn_dim_divisor)) for m in c.ffn_multipliers)
+    c.rope_theta = c.rope_freq_constant
+
+
+def _openelm_spec(c):
+    per = tuple(dict(num_heads=q, num_kv_heads=k,
+                     intermediate_size=int(make_divisible(m * c.model_dim, c.ffn_dim_divisor)))
+                for q, k, m in zip(c.num_query_heads, c.num_kv_heads, c.ffn_multipliers))
+    return base_spec(c, norm_eps=1e-6, act=c.activation_fn_name, mlp="gated" if c.ffn_with_glu else "plain",
+                     qk_norm="rms_head" if c.normalize_qk_projections else None,
+                     tie_embeddings=c.share_input_output_layers, per_layer=per)
+
+
+EXPORTS.update(define_family(
+    "openelm", dict(vocab_size=32000, max_context_length=2048, num_transformer_layers=12, model_dim=2048, head_dim=128,
+                    qkv_multipliers=1.0, num_gqa_groups=1, ffn_multipliers=4.0, ffn_with_glu=True, ffn_dim_divisor=256,
+                    activation_fn_name="swish", normalization_layer_name="rms_norm", normalize_qk_projections=False,
+                    share_input_output_layers=False, rope_freq_constant=10000, rope_max_length=4096,
+                    initializer_range=0.02, use_cache=True, rope_scaling=None),
+    _openelm_spec, config_post=_openelm_post, class_prefix="OpenELM",
+    rules=[("transformer.token_embeddings.", "model.embed_tokens."), ("transformer.norm.", "model.norm."),
+           ("transformer.layers.", "model.layers."), (".attn.out_proj.", ".self_attn.o_proj."),
+           (".attn.", ".self_attn."), (".attn_norm.", ".input_layernorm."),
+           (".ffn_norm.", ".post_attention_layernorm."), (".ffn.proj_1.", ".mlp.gate_up_proj."),
+           (".ffn.proj_2.", ".mlp.down_proj.")],
+    hf_keeps_fused=("qkv_proj", "gate_up_proj"), with_classifier=False))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

@@ -169,3 +169,32 @@ def test_dbrx_nested_config_fused_qkv_and_expert_layout():
     ids = torch.randint(0, 128, (1, 12))
     _, met = m.compute_loss(input_ids=ids, labels=ids)
     assert torch.isfinite(met.loss)
+
+
+def test_openelm_layerwise_scaling_shapes_names_and_decoding():
+    torch.manual_seed(0)
+    cfg = M.OpenELMConfig(vocab_size=128, max_context_length=64, num_transformer_layers=3, model_dim=64, head_dim=16,
+                          qkv_multipliers=[0.5, 1.0], num_gqa_groups=2, ffn_multipliers=[0.5, 2.0], ffn_dim_divisor=16,
+                          normalize_qk_projections=True, share_input_output_layers=True)
+    assert cfg.num_query_heads == [2, 4, 4] and cfg.num_kv_heads == [1, 2, 2]
+    m = _jitter(M.OpenELMForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32))
+    widths = [l.mlp.down_proj.weight.shape[1] for l in m.model.layers]
+    assert widths == [32, 80, 128] and [l.self_attn.num_heads for l in m.model.layers] == [2, 4, 4]
+    sd = internal_to_hf(m)
+    assert sd["transformer.layers.0.attn.qkv_proj.weight"].shape == ((2 + 2 * 1) * 16, 64)
+    assert sd["transformer.layers.2.ffn.proj_1.weight"].shape == (256, 64)
+    assert "transformer.layers.1.attn.q_norm.weight" in sd and "lm_head.weight" not in sd
+    back = hf_to_internal(m, sd)
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    ids = torch.randint(0, 128, (2, 14))
+    with torch.no_grad():
+        full = m(input_ids=ids).logits
+        cache = m.init_cache(2, 16)
+        o = m(input_ids=ids[:, :10], past_key_values=cache).logits
+        cache.advance(10)
+        assert (o - full[:, :10]).abs().max() < 2e-4
+        o = m(input_ids=ids[:, 10:11], past_key_values=cache).logits
+        assert (o[:, 0] - full[:, 10]).abs().max() < 2e-4
+    _, met = m.compute_loss(input_ids=ids, labels=ids)
+    met.loss.backward()
+    assert torch.isfinite(met.loss)
