@@ -22,8 +22,13 @@ class EasyGenerationMixin:
         if spec is not None and getattr(spec, "mla", None) is not None:
             from ...layers.mla import MLACache
 
-            return MLACache(spec.num_layers, batch_size, max_length, spec.mla["kv_lora_rank"],
-                            spec.mla["qk_rope_head_dim"], dtype or self.dtype, device or self.device)
+            cache = MLACache(spec.num_layers, batch_size, max_length, spec.mla["kv_lora_rank"],
+                             spec.mla["qk_rope_head_dim"], dtype or self.dtype, device or self.device)
+            for i, layer in enumerate(getattr(getattr(self, "model", self), "layers", ())):
+                mixer = getattr(layer, "linear_attn", None)
+                if mixer is not None:     # hybrids: recurrent state of the linear-attention layers
+                    cache.linear[i] = mixer.make_state(batch_size, dtype or self.dtype, device or self.device)
+            return cache
         return TransformerCache.init_for_model(self, batch_size, max_length, dtype=dtype, device=device)
 
     def init_ragged_pages(self, num_pages: int | None = None, page_size: int = 128, hbm_utilization: float = 0.85,

@@ -106,3 +106,75 @@ class GatedDeltaNet(nn.Module):
         of = (self.norm.weight.float() * of).to(hidden.dtype).float() * torch.nn.functional.silu(
             z.reshape(B * T, self.hv, self.dv).float())
         return self.out_proj(of.to(hidden.dtype).reshape(B, T, self.value_dim))
+
+
+class KDAState:
+    """Convolution windows of q, k, v and the recurrent state of one batch of sequences."""
+
+    def __init__(self, batch, key_dim, value_dim, conv_width, heads, dk, dv, dtype, device):
+        z = lambda c: torch.zeros(batch, conv_width - 1, c, dtype=dtype, device=device)  # noqa: E731
+        self.q_conv, self.k_conv, self.v_conv = z(key_dim), z(key_dim), z(value_dim)
+        self.recurrent = torch.zeros(batch, heads, dk, dv, dtype=torch.float32, device=device)
+
+    def reorder(self, index):
+        for n in ("q_conv", "k_conv", "v_conv", "recurrent"):
+            setattr(self, n, getattr(self, n).index_select(0, index))
+
+
+class KimiDeltaAttention(nn.Module):
+    """Kimi delta attention (easydel/modules/kimi_linear/modeling_kimi_linear.py:830-1150): separate q / k / v
+    projections each followed by its own depth-wise causal convolution + SiLU, the gated delta rule with a per-head
+    decay ``-exp(A_log) softplus(f_b(silu(f_a x)) + dt_bias)`` (easydel/operations/kernels/kda.py:78-98) and update
+    gate ``sigmoid(b x)``, L2-normalised q / k, then a per-head RMSNorm gated by ``silu(g_b(silu(g_a x)))``."""
+
+    def __init__(self, hidden_size: int, num_heads: int, head_k_dim: int = 128, head_v_dim: int = 128,
+                 d_conv: int = 4, gate_low_rank_dim: int = 128, norm_eps: float = 1e-6, layer_idx: int = 0,
+                 dtype=torch.float32, init_std: float = 0.02):
+        super().__init__()
+        self.h, self.dk, self.dv, self.W, self.eps = num_heads, head_k_dim, head_v_dim, d_conv, norm_eps
+        self.key_dim, self.value_dim = num_heads * head_k_dim, num_heads * head_v_dim
+        lin = lambda i, o: ColumnParallelLinear(i, o, bias=False, dtype=dtype, init_std=init_std)  # noqa: E731
+        self.q_proj, self.k_proj, self.v_proj = lin(hidden_size, self.key_dim), lin(hidden_size, self.key_dim), \
+            lin(hidden_size, self.value_dim)
+        conv = lambda c: nn.Conv1d(c, c, d_conv, groups=c, bias=False, padding=d_conv - 1, dtype=dtype)  # noqa: E731
+        self.q_conv1d, self.k_conv1d, self.v_conv1d = conv(self.key_dim), conv(self.key_dim), conv(self.value_dim)
+        self.f_a_proj, self.f_b_proj = lin(hidden_size, gate_low_rank_dim), lin(gate_low_rank_dim, num_heads)
+        self.b_proj = lin(hidden_size, num_heads)
+        self.g_a_proj, self.g_b_proj = lin(hidden_size, gate_low_rank_dim), lin(gate_low_rank_dim, self.value_dim)
+        self.A_log = nn.Parameter(torch.log(torch.empty(num_heads).uniform_(1.0, 16.0)).to(dtype))
+        self.dt_bias = nn.Parameter(torch.zeros(num_heads, dtype=dtype))
+        self.o_norm = nn.Module()
+        self.o_norm.weight = nn.Parameter(torch.ones(head_v_dim, dtype=dtype))
+        self.o_proj = RowParallelLinear(self.value_dim, hidden_size, bias=False, dtype=dtype, init_std=init_std)
+
+    def make_state(self, batch, dtype, device) -> KDAState:
+        return KDAState(batch, self.key_dim, self.value_dim, self.W, self.h, self.dk, self.dv, dtype, device)
+
+    def forward(self, hidden, segment_ids=None, state: KDAState | None = None):
+        B, T, _ = hidden.shape
+        if segment_ids is not None and state is None:
+            from ..ops.attention import segment_ids_to_cu_seqlens
+
+            cu, _ = segment_ids_to_cu_seqlens(segment_ids)
+        else:
+            cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=hidden.device)
+
+        def conv(x, mod, st):
+            return ssm.ragged_conv1d(x.reshape(B * T, -1), mod.weight.squeeze(1), None, cu, "silu", st)
+
+        q = conv(self.q_proj(hidden), self.q_conv1d, None if state is None else state.q_conv)
+        k = conv(self.k_proj(hidden), self.k_conv1d, None if state is None else state.k_conv)
+        v = conv(self.v_proj(hidden), self.v_conv1d, None if state is None else state.v_conv)
+        q = torch.nn.functional.normalize(q.view(B * T, self.h, self.dk).float(), dim=-1, eps=1e-6)
+        k = torch.nn.functional.normalize(k.view(B * T, self.h, self.dk).float(), dim=-1, eps=1e-6)
+        v = v.view(B * T, self.h, self.dv)
+        gate = self.f_b_proj(torch.nn.functional.silu(self.f_a_proj(hidden))).reshape(B * T, self.h)
+        g = -self.A_log.float().exp() * torch.nn.functional.softplus(gate.float() + self.dt_bias.float())
+        beta = torch.sigmoid(self.b_proj(hidden).reshape(B * T, self.h).float())
+        o = ssm.gated_delta_rule(q.to(v.dtype), k.to(v.dtype), v, g, beta, None, cu,
+                                 None if state is None else state.recurrent)
+        og = self.g_b_proj(torch.nn.functional.silu(self.g_a_proj(hidden))).reshape(B * T, self.h, self.dv)
+        of = o.float()
+        of = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + self.eps) * self.o_norm.weight.float()
+        of = of * torch.nn.functional.silu(og.float())
+        return self.o_proj(of.to(hidden.dtype).reshape(B, T, self.value_dim))

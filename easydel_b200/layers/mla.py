@@ -26,6 +26,7 @@ class MLACache:
         self.latent = torch.zeros(num_layers, batch, max_len, kv_lora_rank, dtype=dtype, device=device)
         self.k_rope = torch.zeros(num_layers, batch, max_len, rope_dim, dtype=dtype, device=device)
         self.length, self.max_len = 0, max_len
+        self.linear: dict[int, object] = {}     # layer -> recurrent state of a linear-attention layer (hybrids)
 
     def seq_len(self) -> int:
         return self.length
@@ -39,11 +40,17 @@ class MLACache:
     def reorder(self, index: torch.Tensor) -> None:
         self.latent = self.latent.index_select(1, index)
         self.k_rope = self.k_rope.index_select(1, index)
+        for st in self.linear.values():
+            st.reorder(index)
 
 
 class _MLAView:
     def __init__(self, cache: MLACache, layer: int):
         self.cache, self.layer = cache, layer
+
+    @property
+    def linear_state(self):
+        return self.cache.linear.get(self.layer)
 
     def update(self, latent: torch.Tensor, k_rope: torch.Tensor):
         c = self.cache
@@ -60,8 +67,10 @@ class MLAttention(nn.Module):
     def __init__(self, hidden_size: int, num_heads: int, *, q_lora_rank: int | None, kv_lora_rank: int,
                  qk_nope_head_dim: int, qk_rope_head_dim: int, v_head_dim: int, rope: dict, rope_interleave: bool = True,
                  norm_eps: float = 1e-6, bias: bool = False, scale: float | None = None, layer_idx: int = 0,
-                 dtype=torch.bfloat16, init_std: float = 0.02, tp_size: int = 1, tp_rank: int = 0, tp_group=None):
+                 dtype=torch.bfloat16, init_std: float = 0.02, tp_size: int = 1, tp_rank: int = 0, tp_group=None,
+                 use_rope: bool = True):
         super().__init__()
+        self.use_rope = use_rope        # Kimi-Linear's latent layers carry no positions (``mla_use_nope``)
         self.H, self.nope, self.rope_dim, self.vd = num_heads // tp_size, qk_nope_head_dim, qk_rope_head_dim, v_head_dim
         self.qk_dim = qk_nope_head_dim + qk_rope_head_dim
         self.kv_lora_rank, self.layer_idx, self.interleave = kv_lora_rank, layer_idx, rope_interleave
@@ -88,6 +97,8 @@ class MLAttention(nn.Module):
     def _rope(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """x ``[B, T, h, rope_dim]``. Checkpoints with ``rope_interleave`` store pairs interleaved: de-interleave,
         then rotate in the half-split layout (what the Hugging Face implementation does)."""
+        if not self.use_rope:
+            return x
         if self.interleave:
             B, T, h, d = x.shape
             x = x.view(B, T, h, d // 2, 2).transpose(-1, -2).reshape(B, T, h, d)

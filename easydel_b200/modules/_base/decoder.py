@@ -158,7 +158,7 @@ class DecoderLayer(nn.Module):
             rope = spec.rope_local
         if ltype == "nope":
             rope = None
-        self.is_linear = ltype in ("linear", "lightning")
+        self.is_linear = ltype in ("linear", "lightning", "kda")
         self.ltype = ltype
         if ltype == "lightning":
             from ...layers.lightning_attention import LightningAttention
@@ -166,6 +166,11 @@ class DecoderLayer(nn.Module):
             self.self_attn = LightningAttention(spec.hidden_size, spec.num_heads, spec.head_dim, spec.num_layers,
                                                 act=spec.act, layer_idx=layer_idx,
                                                 dtype=dtype, init_std=spec.init_std, **spec.lightning)
+        elif ltype == "kda":
+            from ...layers.linear_attention import KimiDeltaAttention
+
+            self.linear_attn = KimiDeltaAttention(spec.hidden_size, layer_idx=layer_idx, dtype=dtype,
+                                                  init_std=spec.init_std, norm_eps=spec.norm_eps, **spec.linear_attn)
         elif self.is_linear:
             from ...layers.linear_attention import GatedDeltaNet
 

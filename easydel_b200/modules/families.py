@@ -8,6 +8,7 @@ unchanged.
 from __future__ import annotations
 
 import math
+import re
 
 import torch
 
@@ -675,6 +676,59 @@ EXPORTS.update(define_family(
                   block_size=256, full_attn_alpha_factor=1, full_attn_beta_factor=1, linear_attn_alpha_factor=1,
                   linear_attn_beta_factor=1, mlp_alpha_factor=1, mlp_beta_factor=1),
     _minimax_spec, class_prefix="MiniMax", rules=[(".self_attn.qkv_proj.", ".self_attn.lqkv.")],
+    with_classifier=False))
+
+
+
+# ---- kimi_linear (easydel/modules/kimi_linear): Kimi delta attention layers (1-indexed ``kda_layers``) between latent
+# ---- (MLA) attention layers without positions, DeepSeek-V3 style sigmoid-routed experts with shared experts ----
+def _kimi_linear_spec(c):
+    n = c.num_hidden_layers
+    la = c.linear_attn_config or {}
+    kda = set(la.get("kda_layers") or [])
+    types = tuple("kda" if (i + 1) in kda else "full" for i in range(n))
+    moe = None
+    if c.num_experts:
+        layers = tuple(i for i in range(n) if i >= c.first_k_dense_replace and i % (c.moe_layer_freq or 1) == 0)
+        grouped = bool(c.use_grouped_topk)
+        moe = moe_spec(c, num_experts=c.num_experts, top_k=c.num_experts_per_token,
+                       intermediate=c.moe_intermediate_size, norm_topk=c.moe_renormalize,
+                       shared=c.moe_intermediate_size * (c.num_shared_experts or 0), layers=layers,
+                       scoring="sigmoid" if c.moe_router_activation_func == "sigmoid" else "softmax",
+                       routed_scaling_factor=c.routed_scaling_factor, n_group=c.num_expert_group if grouped else 1,
+                       topk_group=c.topk_group if grouped else 1, use_score_bias=True)
+    mla = dict(_mla_args(c), use_rope=not c.mla_use_nope)
+    return base_spec(c, head_dim=c.qk_rope_head_dim, rope=rope_args(c, c.qk_rope_head_dim), mla=mla, moe=moe,
+                     layer_types=types,
+                     linear_attn=dict(num_heads=la.get("num_heads", c.num_attention_heads),
+                                      head_k_dim=la.get("head_k_dim", la.get("head_dim", 128)),
+                                      head_v_dim=la.get("head_v_dim", la.get("head_dim", 128)),
+                                      d_conv=la.get("short_conv_kernel_size", la.get("d_conv", 4)),
+                                      gate_low_rank_dim=la.get("gate_low_rank_dim", 128)))
+
+
+_KIMI = _d(vocab_size=163840, hidden_size=2304, intermediate_size=9216, num_hidden_layers=27, num_attention_heads=32,
+           num_key_value_heads=32, rms_norm_eps=1e-5, q_lora_rank=None, kv_lora_rank=512, qk_nope_head_dim=128,
+           qk_rope_head_dim=64, v_head_dim=128, mla_use_nope=True, num_experts=256, num_experts_per_token=8,
+           moe_renormalize=True, num_shared_experts=1, routed_scaling_factor=2.446, moe_router_activation_func="sigmoid",
+           moe_intermediate_size=1024, first_k_dense_replace=1, moe_layer_freq=1, use_grouped_topk=True,
+           num_expert_group=1, topk_group=1, num_nextn_predict_layers=0, max_position_embeddings=1048576,
+           linear_attn_config=None, rope_interleave=True)
+_KIMI.pop("head_dim", None)
+_KIMI_W = {"w1": "gate_proj", "w3": "up_proj", "w2": "down_proj"}
+_KIMI_P = {v: k for k, v in _KIMI_W.items()}
+_KIMI_IN = re.compile(r"\.experts\.(\d+)\.(w[123])\.")
+_KIMI_DENSE = re.compile(r"\.block_sparse_moe\.(gate_proj|up_proj|down_proj)\.")   # dense layers keep ``mlp``
+_KIMI_OUT = re.compile(r"\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.")
+EXPORTS.update(define_family(
+    "kimi_linear", _KIMI, _kimi_linear_spec, class_prefix="KimiLinear",
+    rules=[(".block_sparse_moe.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
+           (".block_sparse_moe", ".mlp")],
+    # routed experts are stored as experts.N.w1 / w3 / w2 (gate / up / down); shared and dense MLPs use the long names
+    tensor_in=lambda model, sd: {_KIMI_IN.sub(lambda m: f".experts.{m.group(1)}.{_KIMI_W[m.group(2)]}.", k): v
+                                 for k, v in sd.items()},
+    tensor_out=lambda model, sd: {_KIMI_DENSE.sub(r".mlp.\1.", _KIMI_OUT.sub(
+        lambda m: f".experts.{m.group(1)}.{_KIMI_P[m.group(2)]}.", k)): v for k, v in sd.items()},
     with_classifier=False))
 
 globals().update(EXPORTS)

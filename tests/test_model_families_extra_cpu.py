@@ -198,3 +198,42 @@ def test_openelm_layerwise_scaling_shapes_names_and_decoding():
     _, met = m.compute_loss(input_ids=ids, labels=ids)
     met.loss.backward()
     assert torch.isfinite(met.loss)
+
+
+def test_kimi_linear_hybrid_of_delta_attention_and_latent_attention():
+    torch.manual_seed(0)
+    cfg = M.KimiLinearConfig(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=4,
+                             num_attention_heads=4, num_key_value_heads=4, kv_lora_rank=16, qk_nope_head_dim=16,
+                             qk_rope_head_dim=8, v_head_dim=16, num_experts=4, num_experts_per_token=2,
+                             moe_intermediate_size=32, num_shared_experts=1, first_k_dense_replace=1,
+                             max_position_embeddings=64,
+                             linear_attn_config=dict(kda_layers=[1, 2, 3], full_attn_layers=[4], num_heads=4,
+                                                     head_dim=16, short_conv_kernel_size=4, gate_low_rank_dim=8))
+    m = _jitter(M.KimiLinearForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32))
+    kinds = [type(getattr(l, "linear_attn", l.self_attn if hasattr(l, "self_attn") else None)).__name__
+             for l in m.model.layers]
+    assert kinds == ["KimiDeltaAttention"] * 3 + ["MLAttention"]
+    assert not m.model.layers[3].self_attn.use_rope and [l.is_moe for l in m.model.layers] == [False, True, True, True]
+    sd = internal_to_hf(m)
+    for frag in ("layers.0.linear_attn.q_conv1d.weight", "layers.1.linear_attn.f_b_proj.weight",
+                 "layers.3.self_attn.kv_a_proj_with_mqa.weight", "layers.1.block_sparse_moe.gate.weight",
+                 "layers.2.block_sparse_moe.gate.e_score_correction_bias", "layers.1.block_sparse_moe.experts.0.w1.",
+                 "layers.1.block_sparse_moe.shared_experts.down_proj.", "layers.0.mlp.gate_proj.weight"):
+        assert any(frag in k for k in sd), frag
+    back = hf_to_internal(m, sd)
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    ids = torch.randint(0, 128, (2, 14))
+    with torch.no_grad():
+        full = m(input_ids=ids).logits
+        cache = m.init_cache(2, 16)
+        assert set(cache.linear) == {0, 1, 2}
+        o = m(input_ids=ids[:, :9], past_key_values=cache).logits
+        cache.advance(9)
+        assert (o - full[:, :9]).abs().max() < 3e-4
+        for t in range(9, 14):
+            o = m(input_ids=ids[:, t:t + 1], past_key_values=cache).logits
+            cache.advance(1)
+            assert (o[:, 0] - full[:, t]).abs().max() < 3e-4, t
+    _, met = m.compute_loss(input_ids=ids, labels=ids)
+    met.loss.backward()
+    assert torch.isfinite(met.loss) and m.model.layers[0].linear_attn.A_log.grad is not None
