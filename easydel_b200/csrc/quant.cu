@@ -19,7 +19,8 @@ namespace edl {
 namespace {
 
 constexpr int QG_THREADS = 256;
-constexpr int QG_ROWS = 2;   // weight rows per warp and pass
+constexpr int QG_ROWS = 4;     // weight rows per warp and pass (they share every activation load)
+constexpr int QG_UNROLL = 2;   // code words per lane and row in flight
 constexpr int QG_MAX_M = 8;
 
 __global__ void dequant_kernel(const uint8_t* __restrict__ codes, const __nv_bfloat16* __restrict__ scales,
@@ -58,107 +59,103 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ codes, const __nv_bfl
   }
 }
 
-// Persistent, prefetching form: the grid is two CTAs per SM; every warp walks row groups of QG_ROWS weight rows.
+// Persistent form: the grid is two CTAs per SM; every warp walks row groups of QG_ROWS weight rows. Inside a row
+// group the 32 lanes take consecutive 32-bit code words (8 weights at 4 bits, 4 at 8 bits), so one warp instruction
+// reads 128 contiguous bytes of codes per row and 512 (256) contiguous bytes of each activation row: every global
+// access is fully coalesced and an activation vector is loaded once for all QG_ROWS rows. QG_UNROLL words per lane
+// are in flight at a time.
 // The code book lives in shared memory once per lane (entry e of lane l at word e * 32 + l), so that a lookup with
 // 32 unrelated codes still touches 32 different banks. For 4-bit codes one lookup per code byte yields both nibbles'
 // values as a bf16 pair (256 entries x 32 lanes x 4 bytes = 32 KB); 8-bit codes look up one fp32 value. The group
-// scale (and zero point) is applied once per 16-byte vector to the partial dot product instead of to every weight:
+// scale (and zero point) is applied once per code word to the partial dot product instead of to every weight:
 //   sum_k (lut[c_k] s + z) x_k = s * sum lut[c_k] x_k + z * sum x_k.
-template <int M>
+template <int M, int BITS>
 __global__ void __launch_bounds__(QG_THREADS)
 qgemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* __restrict__ codes,
              const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ zeros,
-             const float* __restrict__ lut, int bits, int N, int K, int group, __nv_bfloat16* __restrict__ out,
+             const float* __restrict__ lut, int N, int K, int group, __nv_bfloat16* __restrict__ out,
              long long ldo, const __nv_bfloat16* __restrict__ bias) {
+  constexpr int WPW = 32 / BITS;             // weights per 32-bit code word
   __shared__ uint32_t s_tab[256 * 32];
   for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
     const int e = i >> 5;
-    s_tab[i] = bits == 4 ? pack_bf16x2(lut[e & 15], lut[e >> 4]) : __float_as_uint(lut[e]);
+    s_tab[i] = BITS == 4 ? pack_bf16x2(lut[e & 15], lut[e >> 4]) : __float_as_uint(lut[e]);
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = QG_THREADS / 32;
-  const int per16 = bits == 4 ? 32 : 16;
   const int groups = K / group;
-  const long long row_bytes = (long long)K * bits / 8;
-  const int nvec = K / per16;
-  const int n_groups_rows = (N + QG_ROWS - 1) / QG_ROWS;
-  for (int rg = blockIdx.x * warps + warp; rg < n_groups_rows; rg += gridDim.x * warps) {
+  const int nwords = K / WPW;                // code words per row
+  const int n_row_groups = (N + QG_ROWS - 1) / QG_ROWS;
+  const uint32_t* __restrict__ words = reinterpret_cast<const uint32_t*>(codes);
+  for (int rg = blockIdx.x * warps + warp; rg < n_row_groups; rg += gridDim.x * warps) {
     const int n0 = rg * QG_ROWS;
     float acc[M][QG_ROWS];
 #pragma unroll
     for (int m = 0; m < M; ++m)
 #pragma unroll
       for (int r = 0; r < QG_ROWS; ++r) acc[m][r] = 0.f;
-    uint4 q[QG_ROWS], qn[QG_ROWS];
-    auto load_codes = [&](int v, uint4 (&dst)[QG_ROWS]) {
+    for (int w0 = lane; w0 < nwords; w0 += 32 * QG_UNROLL) {
+      uint32_t cw[QG_UNROLL][QG_ROWS];
 #pragma unroll
-      for (int r = 0; r < QG_ROWS; ++r)
-        dst[r] = (n0 + r < N && v < nvec)
-                     ? __ldg(reinterpret_cast<const uint4*>(codes + (long long)(n0 + r) * row_bytes + (long long)v * 16))
-                     : make_uint4(0, 0, 0, 0);
-    };
-    load_codes(lane, q);
-    for (int v = lane; v < nvec; v += 32) {
-      load_codes(v + 32, qn);                 // prefetch the next vector of every row while this one is consumed
-      const int k0 = v * per16;
-      const int g = k0 / group;
-      float part[M][QG_ROWS], xsum[M];
+      for (int u = 0; u < QG_UNROLL; ++u)
 #pragma unroll
-      for (int m = 0; m < M; ++m) {
-        xsum[m] = 0.f;
+        for (int r = 0; r < QG_ROWS; ++r) {
+          const int w = w0 + 32 * u;
+          cw[u][r] = (w < nwords && n0 + r < N) ? __ldg(words + (long long)(n0 + r) * nwords + w) : 0u;
+        }
 #pragma unroll
-        for (int r = 0; r < QG_ROWS; ++r) part[m][r] = 0.f;
-      }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {           // one 32-bit word of codes per row: 8 (4-bit) or 4 (8-bit) weights
-        float xv[M][8];
+      for (int u = 0; u < QG_UNROLL; ++u) {
+        const int w = w0 + 32 * u;
+        if (w >= nwords) break;
+        const int k0 = w * WPW;
+        const int g = k0 / group;
+        float xv[M][WPW], xsum[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          if (bits == 4) {
-            const uint4 xx = *reinterpret_cast<const uint4*>(x + m * ldx + k0 + c * 8);
-            float2 f;
+          float2 f;
+          if (BITS == 4) {
+            const uint4 xx = *reinterpret_cast<const uint4*>(x + m * ldx + k0);
             f = unpack_bf16x2(xx.x); xv[m][0] = f.x; xv[m][1] = f.y;
             f = unpack_bf16x2(xx.y); xv[m][2] = f.x; xv[m][3] = f.y;
-            f = unpack_bf16x2(xx.z); xv[m][4] = f.x; xv[m][5] = f.y;
-            f = unpack_bf16x2(xx.w); xv[m][6] = f.x; xv[m][7] = f.y;
-            xsum[m] += (xv[m][0] + xv[m][1]) + (xv[m][2] + xv[m][3]) + (xv[m][4] + xv[m][5]) + (xv[m][6] + xv[m][7]);
+            f = unpack_bf16x2(xx.z); xv[m][WPW - 4] = f.x; xv[m][WPW - 3] = f.y;
+            f = unpack_bf16x2(xx.w); xv[m][WPW - 2] = f.x; xv[m][WPW - 1] = f.y;
           } else {
-            const uint2 xx = *reinterpret_cast<const uint2*>(x + m * ldx + k0 + c * 4);
-            float2 f;
+            const uint2 xx = *reinterpret_cast<const uint2*>(x + m * ldx + k0);
             f = unpack_bf16x2(xx.x); xv[m][0] = f.x; xv[m][1] = f.y;
             f = unpack_bf16x2(xx.y); xv[m][2] = f.x; xv[m][3] = f.y;
-            xsum[m] += (xv[m][0] + xv[m][1]) + (xv[m][2] + xv[m][3]);
           }
+          float t = 0.f;
+#pragma unroll
+          for (int i = 0; i < WPW; ++i) t += xv[m][i];
+          xsum[m] = t;
         }
 #pragma unroll
         for (int r = 0; r < QG_ROWS; ++r) {
-          const uint32_t word = c == 0 ? q[r].x : c == 1 ? q[r].y : c == 2 ? q[r].z : q[r].w;
+          const uint32_t word = cw[u][r];
+          float part[M];
+#pragma unroll
+          for (int m = 0; m < M; ++m) part[m] = 0.f;
 #pragma unroll
           for (int bb = 0; bb < 4; ++bb) {
             const uint32_t t = s_tab[(((word >> (8 * bb)) & 0xFF) << 5) + lane];
-            if (bits == 4) {
+            if (BITS == 4) {
               const float lo = __uint_as_float(t << 16), hi = __uint_as_float(t & 0xFFFF0000u);
 #pragma unroll
-              for (int m = 0; m < M; ++m) part[m][r] += lo * xv[m][2 * bb] + hi * xv[m][2 * bb + 1];
+              for (int m = 0; m < M; ++m) part[m] += lo * xv[m][(2 * bb) % WPW] + hi * xv[m][(2 * bb + 1) % WPW];
             } else {
-              const float w = __uint_as_float(t);
+              const float wv = __uint_as_float(t);
 #pragma unroll
-              for (int m = 0; m < M; ++m) part[m][r] += w * xv[m][bb];
+              for (int m = 0; m < M; ++m) part[m] += wv * xv[m][bb % WPW];
             }
           }
+          const bool ok = n0 + r < N;
+          const float sc = ok ? __bfloat162float(scales[(long long)(n0 + r) * groups + g]) : 0.f;
+          const float zr = (ok && zeros) ? __bfloat162float(zeros[(long long)(n0 + r) * groups + g]) : 0.f;
+#pragma unroll
+          for (int m = 0; m < M; ++m) acc[m][r] += sc * part[m] + zr * xsum[m];
         }
       }
-#pragma unroll
-      for (int r = 0; r < QG_ROWS; ++r) {
-        const bool ok = n0 + r < N;
-        const float sc = ok ? __bfloat162float(scales[(long long)(n0 + r) * groups + g]) : 0.f;
-        const float zr = (ok && zeros) ? __bfloat162float(zeros[(long long)(n0 + r) * groups + g]) : 0.f;
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[m][r] += sc * part[m][r] + zr * xsum[m];
-      }
-#pragma unroll
-      for (int r = 0; r < QG_ROWS; ++r) q[r] = qn[r];
     }
 #pragma unroll
     for (int m = 0; m < M; ++m)
@@ -216,12 +213,14 @@ EDL_HOST_API int edl_qgemv(const void* x, long long ldx, const void* codes, cons
   const int cap = sm_count() * 2;   // persistent: warps loop over row groups
   if (blocks > cap) blocks = cap;
   cudaStream_t s = (cudaStream_t)stream;
+#define EDL_QGEMV_LAUNCH(MM, BB)                                                                                    \
+  qgemv_kernel<MM, BB><<<blocks, QG_THREADS, 0, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)codes,           \
+                                                     (const __nv_bfloat16*)scales, (const __nv_bfloat16*)zeros,     \
+                                                     lut, N, K, group, (__nv_bfloat16*)out, ldo,                    \
+                                                     (const __nv_bfloat16*)bias)
 #define EDL_QGEMV_CASE(MM)                                                                                          \
   case MM:                                                                                                          \
-    qgemv_kernel<MM><<<blocks, QG_THREADS, 0, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)codes,             \
-                                                   (const __nv_bfloat16*)scales, (const __nv_bfloat16*)zeros, lut, \
-                                                   bits, N, K, group, (__nv_bfloat16*)out, ldo,                     \
-                                                   (const __nv_bfloat16*)bias);                                     \
+    if (bits == 4) EDL_QGEMV_LAUNCH(MM, 4); else EDL_QGEMV_LAUNCH(MM, 8);                                           \
     break;
   switch (M) {
     EDL_QGEMV_CASE(1)
@@ -233,6 +232,7 @@ EDL_HOST_API int edl_qgemv(const void* x, long long ldx, const void* codes, cons
     EDL_QGEMV_CASE(7)
     EDL_QGEMV_CASE(8)
   }
+#undef EDL_QGEMV_LAUNCH
 #undef EDL_QGEMV_CASE
   return check_cuda(cudaGetLastError(), "qgemv launch");
 }
