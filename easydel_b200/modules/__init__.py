@@ -30,3 +30,5 @@ from . import qwen3_vl  # noqa: F401
 from .qwen3_vl import *  # noqa: F401,F403
 from . import rwkv  # noqa: F401
 from .rwkv import *  # noqa: F401,F403
+from . import glm4v  # noqa: F401
+from .glm4v import *  # noqa: F401,F403

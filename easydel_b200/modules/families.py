@@ -731,5 +731,26 @@ EXPORTS.update(define_family(
         lambda m: f".experts.{m.group(1)}.{_KIMI_P[m.group(2)]}.", k)): v for k, v in sd.items()},
     with_classifier=False))
 
+
+
+# ---- glm4v_text (the language half of easydel/modules/glm4v, glm46v): the GLM-4 block with QKV biases always on and
+# ---- the rotary fraction / three-stream sections carried in the rope parameters ----
+def _glm4v_text_spec(c):
+    rp = getattr(c, "rope_parameters", None) or getattr(c, "rope_scaling", None) or {}
+    partial = getattr(c, "partial_rotary_factor", None) or rp.get("partial_rotary_factor", 1.0)
+    hd = c.hidden_size // c.num_attention_heads
+    return base_spec(c, head_dim=hd, attn_bias=True, o_bias=False, sandwich_norm=True,
+                     rope=rope_args(c, hd, partial=partial, neox=False))
+
+
+EXPORTS.update(define_family(
+    "glm4v_text", _d(vocab_size=151552, hidden_size=4096, intermediate_size=13696, num_hidden_layers=40,
+                     num_attention_heads=32, num_key_value_heads=2, rms_norm_eps=1e-5, max_position_embeddings=32768,
+                     partial_rotary_factor=None),
+    _glm4v_text_spec, class_prefix="Glm4vText", hf_keeps_fused=("gate_up_proj",),
+    rules=[("post_self_attn_layernorm", "post_attn_out_layernorm"),
+           ("post_attention_layernorm", "pre_feedforward_layernorm"),
+           ("post_mlp_layernorm", "post_feedforward_layernorm")], with_classifier=False))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

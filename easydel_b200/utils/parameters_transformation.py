@@ -44,8 +44,10 @@ def internal_to_hf(model, state: dict[str, torch.Tensor] | None = None) -> dict[
         prefix = ".".join(parts[:-2])
         pre = prefix + "." if prefix else ""
         keeps = getattr(model, "hf_keeps_fused", ())
-        # entries with a dot are parameter-name prefixes (a sub-model whose checkpoints keep the fused matrix)
-        kept = mod_name in keeps or any("." in e and name.startswith(e) for e in keeps)
+        # "prefix." keeps every fused matrix under that parameter-name prefix, "prefix.:module" only that module's
+        kept = mod_name in keeps or any(
+            (":" in e and name.startswith(e.split(":")[0]) and mod_name == e.split(":")[1])
+            or (":" not in e and "." in e and name.startswith(e)) for e in keeps)
         if mod_name in FUSED_SPLITS and t.dim() <= 2 and not kept and \
                 hasattr(_module_of(model, ".".join(parts[:-1])), "local_out_splits"):
             mod = _module_of(model, ".".join(parts[:-1]))

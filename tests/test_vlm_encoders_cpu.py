@@ -327,3 +327,61 @@ def test_qwen3_vl_moe_matches_hf():
         a = m(input_ids=ids, pixel_values=pix, image_grid_thw=grid).logits
         b = hf(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=(ids == 127).long()).logits
     assert (a - b).abs().max() < 3e-4, (a - b).abs().max()
+
+
+def test_glm4v_matches_hf():
+    from easydel_b200.modules.glm4v import Glm4vConfig, Glm4vForConditionalGeneration
+
+    V = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=4, in_channels=3, patch_size=7,
+             spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=32, image_size=56)
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2,
+             rope_scaling={"rope_type": "default", "mrope_section": [1, 1, 2], "partial_rotary_factor": 1.0})
+    cfg = Glm4vConfig(vision_config=dict(V), text_config=dict(T), image_token_id=127)
+    torch.manual_seed(0)
+    m = Glm4vForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.Glm4vForConditionalGeneration(transformers.Glm4vConfig(
+        vision_config=dict(V), text_config=dict(T), image_token_id=127, video_token_id=126)).float().eval()
+    missing, unexpected = hf.load_state_dict(internal_to_hf(m), strict=False)
+    assert not unexpected and not missing, (missing, unexpected)
+    grid = torch.tensor([[1, 4, 8], [1, 4, 4]])
+    pix = torch.randn(int((grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * 7 * 7)
+    ids = torch.randint(0, 120, (1, 24))
+    ids[0, 2:10] = 127
+    ids[0, 13:17] = 127
+    with torch.no_grad():
+        a = m(input_ids=ids, pixel_values=pix, image_grid_thw=grid).logits
+        b = hf(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=(ids == 127).long()).logits
+    assert (a - b).abs().max() < 3e-4, (a - b).abs().max()
+    back = hf_to_internal(m, hf.state_dict())
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+
+
+def test_glm4v_moe_matches_hf():
+    from easydel_b200.modules.glm4v import Glm4vMoeConfig, Glm4vMoeForConditionalGeneration
+    from easydel_b200.utils.parameters_transformation import _adapt_to_hf_module_names
+
+    V = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=4, in_channels=3, patch_size=7,
+             spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=32, image_size=56)
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=8, moe_intermediate_size=24, n_routed_experts=4, num_experts_per_tok=2,
+             n_shared_experts=1, first_k_dense_replace=1, partial_rotary_factor=0.5, attention_bias=True,
+             rope_scaling={"rope_type": "default", "mrope_section": [1, 1]}, pad_token_id=0)
+    cfg = Glm4vMoeConfig(vision_config=dict(V), text_config=dict(T), image_token_id=127)
+    torch.manual_seed(0)
+    m = Glm4vMoeForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.Glm4vMoeForConditionalGeneration(transformers.Glm4vMoeConfig(
+        vision_config=dict(V), text_config=dict(T), image_token_id=127, video_token_id=126)).float().eval()
+    sd = _adapt_to_hf_module_names(internal_to_hf(m), hf.state_dict())
+    missing, unexpected = hf.load_state_dict(sd, strict=False)
+    assert not unexpected and not missing, (missing, unexpected)
+    grid = torch.tensor([[1, 4, 4]])
+    pix = torch.randn(16, 3 * 2 * 7 * 7)
+    ids = torch.randint(1, 120, (1, 12))
+    ids[0, 3:7] = 127
+    with torch.no_grad():
+        a = m(input_ids=ids, pixel_values=pix, image_grid_thw=grid).logits
+        b = hf(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=(ids == 127).long()).logits
+    assert (a - b).abs().max() < 3e-4, (a - b).abs().max()
