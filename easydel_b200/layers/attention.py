@@ -60,8 +60,12 @@ class Attention(nn.Module):
                  clip_qkv: float | None = None, dtype: torch.dtype = torch.float32, init_std: float = 0.02,
                  tp_size: int = 1, tp_rank: int = 0, tp_group=None, qk_norm_offset: float = 0.0,
                  output_gate: bool = False, chunk_size: int | None = None,
-                 temp_tuning: tuple[float, float] | None = None):
+                 temp_tuning: tuple[float, float] | None = None, head_scale_init: float | None = None):
         super().__init__()
+        # GIDD: one learned multiplier per query head on top of ``scale`` (with L2-normalised q / k it is the whole
+        # temperature of the head)
+        self.head_scale = None if head_scale_init is None else nn.Parameter(
+            torch.full((num_heads // tp_size,), float(head_scale_init), dtype=dtype))
         self.layer_idx = layer_idx
         # Llama-4: attention restricted to blocks of ``chunk_size`` positions (rotary layers); position-dependent
         # query temperature ``log1p(floor((pos + 1) / floor_scale)) * attn_scale + 1`` (layers without rotary)
@@ -143,6 +147,12 @@ class Attention(nn.Module):
         """hidden ``[B,T,H]``; positions ``[B,T]``. Returns ``[B,T,H]``."""
         B, T, _ = hidden.shape
         qkv = self.qkv_proj(hidden)
+        if self.qk_norm == "l2_full":     # q and k are normalised over the whole projection (all heads together)
+            Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+            q, k, v = qkv[..., : Hq * D].float(), qkv[..., Hq * D:(Hq + Hkv) * D].float(), qkv[..., (Hq + Hkv) * D:]
+            q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + self.qk_norm_eps)
+            k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + self.qk_norm_eps)
+            qkv = torch.cat([q.to(v.dtype), k.to(v.dtype), v], dim=-1)
         gate = None
         if self.output_gate:
             Hq, D = self.num_heads, self.head_dim
@@ -151,7 +161,7 @@ class Attention(nn.Module):
             qkv = torch.cat([qg[..., :D].reshape(B, T, Hq * D), qkv[..., 2 * Hq * D:]], dim=-1)
         if self.clip_qkv is not None:
             qkv = qkv.clamp(-self.clip_qkv, self.clip_qkv)
-        if self.qk_norm is not None and self.qk_norm != "l2_post_rope":
+        if self.qk_norm is not None and self.qk_norm not in ("l2_post_rope", "l2_full"):
             qkv = self._apply_qk_norm(qkv)
         if self.rotary is not None and positions.dim() == 3:
             # three position streams (temporal, height, width) share the frequency axis by sections
@@ -162,6 +172,8 @@ class Attention(nn.Module):
             if self.rotary is not None:
                 qkv = self.rotary.rotate_packed(qkv, positions, self.num_heads + self.num_kv_heads)
             q, k, v = self._split(qkv)
+        if self.head_scale is not None:
+            q = (q * self.head_scale.to(q.dtype)[None, None, :, None])
         if self.qk_norm == "l2_post_rope":      # weightless RMS normalisation of every head, after the rotation
             q = (q.float() * torch.rsqrt(q.float().pow(2).mean(-1, keepdim=True) + self.qk_norm_eps)).to(v.dtype)
             k = (k.float() * torch.rsqrt(k.float().pow(2).mean(-1, keepdim=True) + self.qk_norm_eps)).to(v.dtype)

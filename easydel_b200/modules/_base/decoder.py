@@ -107,6 +107,9 @@ class ArchSpec:
     attn_chunk_size: int | None = None  # block-diagonal attention on the rotary layers of a rope / nope mix (Llama-4)
     attn_temp_tuning: tuple[float, float] | None = None  # (attn_scale, floor_scale) on the layers without rotary
     qk_norm_rope_only: bool = False   # QK norm only on layers that rotate
+    causal: bool = True               # False: bidirectional blocks (diffusion language models)
+    attn_head_scale_init: float | None = None  # learned per-head query multiplier (GIDD)
+    qk_norm_eps: float | None = None  # epsilon of the QK norm when it differs from the block norms'
     per_layer: tuple | None = None    # one dict of field overrides per layer (OpenELM scales heads / FFN by depth)
     lightning: dict | None = None     # kwargs of layers.lightning_attention.LightningAttention for "lightning" layers
     normed_residual: dict | None = None  # MiniMax: the branch input (after the norm) is the residual, combined as
@@ -209,7 +212,9 @@ class DecoderLayer(nn.Module):
         qk_norm = spec.qk_norm if (rope is not None or not spec.qk_norm_rope_only) else None
         return Attention(
             spec.hidden_size, spec.num_heads, spec.num_kv_heads, spec.head_dim, layer_idx=layer_idx,
-            bias=spec.attn_bias, o_bias=spec.o_bias, qk_norm=qk_norm, qk_norm_eps=spec.norm_eps, rope=rope,
+            bias=spec.attn_bias, o_bias=spec.o_bias, qk_norm=qk_norm,
+            qk_norm_eps=spec.qk_norm_eps if spec.qk_norm_eps is not None else spec.norm_eps, rope=rope,
+            causal=spec.causal, head_scale_init=spec.attn_head_scale_init,
             chunk_size=spec.attn_chunk_size if rope is not None else None,
             temp_tuning=spec.attn_temp_tuning if rope is None else None,
             sliding_window=window, softcap=spec.attn_softcap, scale=spec.attn_scale, use_sinks=spec.use_sinks,

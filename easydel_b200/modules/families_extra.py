@@ -273,5 +273,57 @@ EXPORTS.update(define_family(
            (".ffn.proj_2.", ".mlp.down_proj.")],
     hf_keeps_fused=("qkv_proj", "gate_up_proj"), with_classifier=False))
 
+
+
+# ---- gidd (easydel/modules/gidd): a bidirectional diffusion language model. (1 + w) RMSNorm, squared-ReLU MLP without
+# ---- gate, residual branches scaled by ``resid_scale``; q and k are L2-normalised over the whole projection and each
+# ---- head has a learned temperature ``qk_scale`` (initialised to 2 log(max positions)) instead of 1 / sqrt(d) ----
+def _gidd_spec(c):
+    import math as _m
+
+    qk = bool(c.use_qk_norm)
+    return base_spec(c, norm_offset=1.0, mlp="plain", act="relu2", mlp_bias=c.mlp_bias, causal=False,
+                     residual_multiplier=c.resid_scale, qk_norm="l2_full" if qk else None, qk_norm_eps=c.qk_norm_eps,
+                     attn_scale=1.0 if qk else None,
+                     attn_head_scale_init=2 * _m.log(c.max_position_embeddings) if qk else None)
+
+
+_GIDD = define_family(
+    "gidd", _d(vocab_size=131072, hidden_size=768, intermediate_size=3072, num_hidden_layers=12,
+               num_attention_heads=12, max_position_embeddings=1024, rms_norm_eps=1e-6, rope_theta=10000.0,
+               init_scale=0.4, emb_init_scale=0.1, head_init_scale=0.0, resid_scale=4.0, use_qk_norm=True,
+               qk_norm_eps=1e-6, mlp_bias=False, tie_word_embeddings=False),
+    _gidd_spec, class_prefix="Gidd",
+    rules=[(".mlp.up_proj.", ".mlp.fc1."), (".mlp.down_proj.", ".mlp.fc2."), (".self_attn.qk_scale", ".self_attn.head_scale")],
+    tensor_in=lambda model, sd: {k: (v.reshape(-1) if k.endswith(".self_attn.qk_scale") else v) for k, v in sd.items()},
+    tensor_out=lambda model, sd: {k: (v.reshape(1, 1, -1, 1) if k.endswith(".self_attn.qk_scale") else v)
+                                  for k, v in sd.items()},
+    with_classifier=False)
+
+
+class GiddForDiffusionLM(_GIDD["GiddForCausalLM"]):
+    """Denoising head: logits for every position from the bidirectional backbone; the loss is cross-entropy at the
+    positions whose label is not ``ignore_index`` (the noised tokens), without the next-token shift."""
+
+    loss_type = "ForDiffusionLM"
+
+    def _compute_task_loss(self, labels, loss_config, loss_scale, call, loss_kwargs):
+        from ..infra.loss_utils import LossMetrics
+
+        call = {k: v for k, v in call.items() if k not in ("noise_mask", "log_snr")}
+        out = self(**call)
+        lg = out.logits.float()
+        loss = torch.nn.functional.cross_entropy(lg.reshape(-1, lg.shape[-1]), labels.reshape(-1),
+                                                 ignore_index=loss_config.ignore_index)
+        return out, LossMetrics(loss=loss * loss_scale)
+
+
+from ..infra.factory import TaskType as _TaskType, register_module as _register_module  # noqa: E402
+
+GiddForDiffusionLM = _register_module(_TaskType.DIFFUSION_LM, config=_GIDD["GiddConfig"], model_type="gidd")(
+    GiddForDiffusionLM)
+_GIDD["GiddForDiffusionLM"] = GiddForDiffusionLM
+EXPORTS.update(_GIDD)
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

@@ -237,3 +237,45 @@ def test_kimi_linear_hybrid_of_delta_attention_and_latent_attention():
     _, met = m.compute_loss(input_ids=ids, labels=ids)
     met.loss.backward()
     assert torch.isfinite(met.loss) and m.model.layers[0].linear_attn.A_log.grad is not None
+
+
+def test_gidd_bidirectional_diffusion_lm():
+    torch.manual_seed(0)
+    cfg = M.GiddConfig(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                       num_attention_heads=4, max_position_embeddings=64, resid_scale=2.0)
+    m = _jitter(M.GiddForDiffusionLM(cfg, dtype=torch.float32, param_dtype=torch.float32))
+    att = m.model.layers[0].self_attn
+    assert not att.causal and att.scale == 1.0
+    assert abs(float(att.head_scale.mean()) - 2 * torch.log(torch.tensor(64.0)).item()) < 0.5
+    sd = internal_to_hf(m)
+    assert sd["model.layers.0.self_attn.qk_scale"].shape == (1, 1, 4, 1) and "model.layers.1.mlp.up_proj.weight" in sd
+    back = hf_to_internal(m, sd)
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    ids = torch.randint(0, 128, (1, 10))
+    with torch.no_grad():
+        a = m(input_ids=ids).logits
+        ids2 = ids.clone()
+        ids2[0, -1] = (ids2[0, -1] + 1) % 128
+        b = m(input_ids=ids2).logits
+    assert (a[0, 0] - b[0, 0]).abs().max() > 1e-6        # a later token changes an earlier position: not causal
+    # one block by hand: q, k normalised over the whole projection, per-head temperature, residual scale
+    layer = m.model.layers[0]
+    x = m.model.embed_tokens(ids)
+    h = layer.input_layernorm(x)
+    qkv = att.qkv_proj(h)
+    q, k, v = qkv[..., :64], qkv[..., 64:128], qkv[..., 128:]
+    q = q / (q.pow(2).sum(-1, keepdim=True) + 1e-6).sqrt()
+    k = k / (k.pow(2).sum(-1, keepdim=True) + 1e-6).sqrt()
+    q, k = att.rotary(torch.arange(10)[None], q.view(1, 10, 4, 16), k.view(1, 10, 4, 16))
+    s = torch.einsum("bqhd,bkhd->bhqk", q * att.head_scale[None, None, :, None], k)
+    o = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), v.view(1, 10, 4, 16)).reshape(1, 10, 64)
+    x1 = x + 2.0 * att.o_proj(o)
+    want = x1 + 2.0 * layer.mlp.fc2(torch.relu(layer.mlp.fc1(layer.post_attention_layernorm(x1))).square())
+    got, _, _ = layer(x, None, torch.arange(10)[None])
+    assert (got - want).abs().max() < 1e-4
+    labels = torch.full_like(ids, -100)
+    labels[0, 3], labels[0, 7] = 5, 9
+    _, met = m.compute_loss(input_ids=ids, labels=labels)
+    with torch.no_grad():
+        ref = torch.nn.functional.cross_entropy(a[0, [3, 7]].float(), torch.tensor([5, 9]))
+    assert abs(float(met.loss) - float(ref)) < 1e-5
