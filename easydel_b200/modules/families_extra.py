@@ -325,5 +325,73 @@ GiddForDiffusionLM = _register_module(_TaskType.DIFFUSION_LM, config=_GIDD["Gidd
 _GIDD["GiddForDiffusionLM"] = GiddForDiffusionLM
 EXPORTS.update(_GIDD)
 
+
+
+# ---- xerxes (easydel/modules/xerxes): Gemma-2 style block (norms before and after both branches, scaled embeddings,
+# ---- every ``window_pattern``-th layer global, the others sliding) with optional per-head QK norm and experts; with
+# ---- QK norm on and neither experts nor ``xe_mlpnorm`` it degenerates to the plain pre-norm block ----
+def _xerxes_plain(c) -> bool:
+    return bool(c.xe_kvnorm and not c.xe_moe and not c.xe_mlpnorm)
+
+
+def _xerxes_spec(c):
+    import math as _m
+
+    n = c.num_hidden_layers
+    types = None
+    if c.window_pattern:
+        types = tuple("sliding" if (i + 1) % c.window_pattern else "full" for i in range(n))
+    moe = None
+    if c.xe_moe:
+        moe = moe_spec(c, num_experts=c.num_local_experts, top_k=c.num_experts_per_tok,
+                       intermediate=c.intermediate_size, norm_topk=True)
+    return base_spec(c, sandwich_norm=not _xerxes_plain(c), qk_norm="rms_head" if c.xe_kvnorm else None,
+                     act="silu" if c.swish_run else "gelu_new", layer_types=types, sliding_window=c.sliding_window,
+                     embed_scale=1.0 if (c.xe_kvnorm and not c.xe_mlpnorm) else _m.sqrt(c.hidden_size), moe=moe,
+                     tie_embeddings=getattr(c, "tie_word_embeddings", False))
+
+
+def _sandwich_rules(model):
+    plain = not model.spec.sandwich_norm if hasattr(model, "spec") else False
+    return [] if plain else [(".post_attention_layernorm.", ".post_attn_out_layernorm.")]
+
+
+EXPORTS.update(define_family(
+    "xerxes", _d(vocab_size=256128, hidden_size=4096, intermediate_size=16384, num_hidden_layers=32,
+                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=16384,
+                 rms_norm_eps=1e-6, num_local_experts=8, num_experts_per_tok=2, swish_run=False, xe_moe=False,
+                 xe_kvnorm=False, xe_mlpnorm=False, window_pattern=None, sliding_window=4096),
+    _xerxes_spec, class_prefix="Xerxes", rules=_sandwich_rules))
+
+
+# ---- xerxes2 (easydel/modules/xerxes2): latent (MLA) attention inside the same four-norm block, Qwen-style experts ----
+def _xerxes2_spec(c):
+    qk = c.qk_nope_head_dim + c.qk_rope_head_dim
+    moe = None
+    if c.num_experts:
+        only = set(c.mlp_only_layers or [])
+        step = c.decoder_sparse_step or 1
+        layers = tuple(i for i in range(c.num_hidden_layers) if i not in only and (i + 1) % step == 0)
+        moe = moe_spec(c, num_experts=c.num_experts, top_k=c.num_experts_per_tok,
+                       intermediate=c.moe_intermediate_size, norm_topk=c.norm_topk_prob, layers=layers,
+                       aux_coef=c.router_aux_loss_coef)
+    from .families import rope_args as _rope_args
+
+    return base_spec(c, head_dim=c.qk_rope_head_dim, rope=_rope_args(c, c.qk_rope_head_dim), sandwich_norm=True,
+                     mla=dict(q_lora_rank=c.q_lora_dim, kv_lora_rank=c.kv_lora_dim,
+                              qk_nope_head_dim=c.qk_nope_head_dim, qk_rope_head_dim=c.qk_rope_head_dim,
+                              v_head_dim=c.vhead_dim, scale=qk ** -0.5, rope_interleave=False), moe=moe)
+
+
+_X2 = _d(vocab_size=256128, hidden_size=4096, intermediate_size=16384, moe_intermediate_size=8192,
+         decoder_sparse_step=1, num_experts=8, num_experts_per_tok=2, norm_topk_prob=False,
+         output_router_logits=False, router_aux_loss_coef=0.001, num_hidden_layers=32, num_attention_heads=32,
+         max_position_embeddings=16384, rms_norm_eps=1e-6, q_lora_dim=1536, kv_lora_dim=512, qk_rope_head_dim=64,
+         qk_nope_head_dim=128, vhead_dim=128, mlp_only_layers=None)
+_X2.pop("head_dim", None)
+EXPORTS.update(define_family("xerxes2", _X2, _xerxes2_spec, class_prefix="Xerxes2",
+                             rules=[(".post_attention_layernorm.", ".post_attn_out_layernorm.")],
+                             with_classifier=False))
+
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)

@@ -279,3 +279,49 @@ def test_gidd_bidirectional_diffusion_lm():
     with torch.no_grad():
         ref = torch.nn.functional.cross_entropy(a[0, [3, 7]].float(), torch.tensor([5, 9]))
     assert abs(float(met.loss) - float(ref)) < 1e-5
+
+
+def test_xerxes_block_variants_and_xerxes2_latent_attention():
+    torch.manual_seed(0)
+    ids = torch.randint(0, 128, (2, 12))
+    # four-norm block with a sliding / global pattern
+    m = _jitter(M.XerxesForCausalLM(M.XerxesConfig(**KW, num_hidden_layers=2, head_dim=16, window_pattern=2,
+                                                   sliding_window=4), dtype=torch.float32,
+                                    param_dtype=torch.float32))
+    l0, l1 = m.model.layers
+    assert l0.self_attn.sliding_window == 4 and l1.self_attn.sliding_window is None
+    sd = internal_to_hf(m)
+    assert {"model.layers.0.post_attention_layernorm.weight", "model.layers.0.pre_feedforward_layernorm.weight",
+            "model.layers.0.post_feedforward_layernorm.weight"} <= set(sd)
+    back = hf_to_internal(m, sd)
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    x = m.model.embed_tokens(ids) * 8.0            # sqrt(64)
+    pos = torch.arange(12)[None].expand(2, 12)
+    x1 = x + l0.post_attn_out_layernorm(l0.self_attn(l0.input_layernorm(x), pos))
+    want = x1 + l0.post_feedforward_layernorm(l0.mlp(l0.pre_feedforward_layernorm(x1)))
+    out = m(input_ids=ids, output_hidden_states=True)
+    assert (out.hidden_states[1] - want).abs().max() < 1e-4
+    # QK norm without experts: the plain pre-norm block, unscaled embeddings
+    p = M.XerxesForCausalLM(M.XerxesConfig(**KW, num_hidden_layers=1, head_dim=16, xe_kvnorm=True), dtype=torch.float32,
+                            param_dtype=torch.float32)
+    assert not p.spec.sandwich_norm and p.spec.embed_scale == 1.0 and hasattr(p.model.layers[0].self_attn, "q_norm")
+    assert "model.layers.0.post_attention_layernorm.weight" in internal_to_hf(p)
+    # xerxes2: latent attention + four norms + experts every layer
+    c2 = M.Xerxes2Config(vocab_size=128, hidden_size=64, intermediate_size=96, moe_intermediate_size=32,
+                         num_hidden_layers=2, num_attention_heads=4, max_position_embeddings=64, num_experts=4,
+                         num_experts_per_tok=2, q_lora_dim=24, kv_lora_dim=16, qk_rope_head_dim=8,
+                         qk_nope_head_dim=16, vhead_dim=16, mlp_only_layers=[0])
+    m2 = _jitter(M.Xerxes2ForCausalLM(c2, dtype=torch.float32, param_dtype=torch.float32))
+    assert type(m2.model.layers[0].self_attn).__name__ == "MLAttention"
+    assert [l.is_moe for l in m2.model.layers] == [False, True]
+    sd2 = internal_to_hf(m2)
+    assert "model.layers.1.self_attn.kv_a_proj_with_mqa.weight" in sd2 and "model.layers.1.mlp.gate.weight" in sd2
+    back = hf_to_internal(m2, sd2)
+    assert all(torch.equal(back[k], v) for k, v in m2.state_dict().items())
+    with torch.no_grad():
+        full = m2(input_ids=ids).logits
+        cache = m2.init_cache(2, 16)
+        o = m2(input_ids=ids[:, :8], past_key_values=cache).logits
+        cache.advance(8)
+        o2 = m2(input_ids=ids[:, 8:9], past_key_values=cache).logits
+    assert (o - full[:, :8]).abs().max() < 3e-4 and (o2[:, 0] - full[:, 8]).abs().max() < 3e-4
