@@ -8,8 +8,8 @@
 // so that  w[n, k] = lut[code[n, k]] * scales[n, k / group] (+ zeros[n, k / group]).
 //
 //   edl_dequant_bf16 : materialises bf16 weights (prefill / training path, followed by the tcgen05 GEMM).
-//   edl_qgemv        : y[M, N] = x[M, K] * W^T for M <= 8 (decode steps): every warp streams two weight rows of
-//                      packed codes with 16-byte loads, dequantises through a conflict-free shared-memory code book and keeps M x 2 fp32 accumulators,
+//   edl_qgemv        : y[M, N] = x[M, K] * W^T for M <= 8 (decode steps): every warp streams four weight rows of
+//                      packed codes with 16-byte loads, dequantises through a conflict-free shared-memory code book and keeps M x 4 packed fp32 accumulators,
 //                      so the weights cross HBM once at 4 or 8 bits per value.
 // Counterpart in the reference: ejkernel quantized_matmul reached from
 // easydel/layers/linears/_linear_quantized.py:1030-1108.
@@ -61,25 +61,31 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ codes, const __nv_bfl
 
 // Persistent form: the grid is two CTAs per SM; every warp walks row groups of QG_ROWS weight rows. Inside a row
 // group the 32 lanes take consecutive 32-bit code words (8 weights at 4 bits, 4 at 8 bits), so one warp instruction
-// reads 128 contiguous bytes of codes per row and 512 (256) contiguous bytes of each activation row: every global
-// access is fully coalesced and an activation vector is loaded once for all QG_ROWS rows. QG_UNROLL words per lane
-// are in flight at a time.
-// The code book lives in shared memory once per lane (entry e of lane l at word e * 32 + l), so that a lookup with
-// 32 unrelated codes still touches 32 different banks. For 4-bit codes one lookup per code byte yields both nibbles'
-// values as a bf16 pair (256 entries x 32 lanes x 4 bytes = 32 KB); 8-bit codes look up one fp32 value. The group
-// scale (and zero point) is applied once per code word to the partial dot product instead of to every weight:
-//   sum_k (lut[c_k] s + z) x_k = s * sum lut[c_k] x_k + z * sum x_k.
-template <int M, int BITS>
-__global__ void __launch_bounds__(QG_THREADS)
-qgemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* __restrict__ codes,
+// reads 128 contiguous bytes of codes per row and the matching contiguous fp32 activations: every global access is
+// coalesced and an activation vector is loaded once for all QG_ROWS rows.
+// The kernel is bound by instruction issue, not by HBM, so the inner loop is built to be short:
+//  * activations arrive as fp32 (the caller converts the few rows once), so nothing is unpacked per weight;
+//  * the code book lives in shared memory once per lane (entry e of lane l at e * 32 + l: 32 unrelated codes still
+//    hit 32 different banks); a 4-bit entry is indexed by a whole code BYTE and holds both nibbles' values as an fp32
+//    pair, fetched with one 8-byte load whose address is one byte-permute (code byte moved to bits 8..15) plus one add;
+//  * the pair multiplies two neighbouring activations with one packed fp32x2 FMA (fma.rn.f32x2);
+//  * the group scale is applied once per code word to the partial sums, and the zero point (affine formats only, a
+//    template flag) through the running sum of the activations:
+//      sum_k (lut[c_k] s + z) x_k = s * sum lut[c_k] x_k + z * sum x_k.
+template <int M, int BITS, bool HAS_ZERO>
+__global__ void __launch_bounds__(QG_THREADS, (M <= 4 ? 2 : 1))
+qgemv_kernel(const float* __restrict__ x, long long ldx, const uint8_t* __restrict__ codes,
              const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ zeros,
              const float* __restrict__ lut, int N, int K, int group, __nv_bfloat16* __restrict__ out,
              long long ldo, const __nv_bfloat16* __restrict__ bias) {
   constexpr int WPW = 32 / BITS;             // weights per 32-bit code word
-  __shared__ uint32_t s_tab[256 * 32];
+  extern __shared__ __align__(16) unsigned char s_raw[];
+  float2* s_pair = reinterpret_cast<float2*>(s_raw);     // 4-bit: [256][32] (low nibble value, high nibble value)
+  float* s_val = reinterpret_cast<float*>(s_raw);        // 8-bit: [256][32]
   for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
     const int e = i >> 5;
-    s_tab[i] = BITS == 4 ? pack_bf16x2(lut[e & 15], lut[e >> 4]) : __float_as_uint(lut[e]);
+    if (BITS == 4) s_pair[i] = make_float2(lut[e & 15], lut[e >> 4]);
+    else s_val[i] = lut[e];
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,13 +94,19 @@ qgemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* 
   const int nwords = K / WPW;                // code words per row
   const int n_row_groups = (N + QG_ROWS - 1) / QG_ROWS;
   const uint32_t* __restrict__ words = reinterpret_cast<const uint32_t*>(codes);
+  // shared-window address of this lane's column of the table; entry e sits (e << 8) bytes further (4-bit) or (e << 7)
+  const uint32_t tab = static_cast<uint32_t>(__cvta_generic_to_shared(s_raw)) + lane * (BITS == 4 ? 8 : 4);
   for (int rg = blockIdx.x * warps + warp; rg < n_row_groups; rg += gridDim.x * warps) {
     const int n0 = rg * QG_ROWS;
-    float acc[M][QG_ROWS];
+    float2 acc[M][QG_ROWS];
+    float zacc[HAS_ZERO ? M : 1][HAS_ZERO ? QG_ROWS : 1];
 #pragma unroll
     for (int m = 0; m < M; ++m)
 #pragma unroll
-      for (int r = 0; r < QG_ROWS; ++r) acc[m][r] = 0.f;
+      for (int r = 0; r < QG_ROWS; ++r) {
+        acc[m][r] = make_float2(0.f, 0.f);
+        if (HAS_ZERO) zacc[m][r] = 0.f;
+      }
     for (int w0 = lane; w0 < nwords; w0 += 32 * QG_UNROLL) {
       uint32_t cw[QG_UNROLL][QG_ROWS];
 #pragma unroll
@@ -110,50 +122,60 @@ qgemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* 
         if (w >= nwords) break;
         const int k0 = w * WPW;
         const int g = k0 / group;
-        float xv[M][WPW], xsum[M];
+        float2 xv[M][4];                    // 4-bit: four activation pairs; 8-bit: two pairs (four values)
+        float xsum[M];
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-          float2 f;
+          const float4 a = __ldg(reinterpret_cast<const float4*>(x + m * ldx + k0));
+          xv[m][0] = make_float2(a.x, a.y);
+          xv[m][1] = make_float2(a.z, a.w);
           if (BITS == 4) {
-            const uint4 xx = *reinterpret_cast<const uint4*>(x + m * ldx + k0);
-            f = unpack_bf16x2(xx.x); xv[m][0] = f.x; xv[m][1] = f.y;
-            f = unpack_bf16x2(xx.y); xv[m][2] = f.x; xv[m][3] = f.y;
-            f = unpack_bf16x2(xx.z); xv[m][WPW - 4] = f.x; xv[m][WPW - 3] = f.y;
-            f = unpack_bf16x2(xx.w); xv[m][WPW - 2] = f.x; xv[m][WPW - 1] = f.y;
-          } else {
-            const uint2 xx = *reinterpret_cast<const uint2*>(x + m * ldx + k0);
-            f = unpack_bf16x2(xx.x); xv[m][0] = f.x; xv[m][1] = f.y;
-            f = unpack_bf16x2(xx.y); xv[m][2] = f.x; xv[m][3] = f.y;
+            const float4 b = __ldg(reinterpret_cast<const float4*>(x + m * ldx + k0 + 4));
+            xv[m][2] = make_float2(b.x, b.y);
+            xv[m][3] = make_float2(b.z, b.w);
           }
-          float t = 0.f;
-#pragma unroll
-          for (int i = 0; i < WPW; ++i) t += xv[m][i];
-          xsum[m] = t;
+          if (HAS_ZERO) {
+            float t = (a.x + a.y) + (a.z + a.w);
+            if (BITS == 4) t += (xv[m][2].x + xv[m][2].y) + (xv[m][3].x + xv[m][3].y);
+            xsum[m] = t;
+          }
         }
 #pragma unroll
         for (int r = 0; r < QG_ROWS; ++r) {
           const uint32_t word = cw[u][r];
-          float part[M];
+          float2 part[M];
 #pragma unroll
-          for (int m = 0; m < M; ++m) part[m] = 0.f;
+          for (int m = 0; m < M; ++m) part[m] = make_float2(0.f, 0.f);
 #pragma unroll
           for (int bb = 0; bb < 4; ++bb) {
-            const uint32_t t = s_tab[(((word >> (8 * bb)) & 0xFF) << 5) + lane];
             if (BITS == 4) {
-              const float lo = __uint_as_float(t << 16), hi = __uint_as_float(t & 0xFFFF0000u);
+              // code byte bb moved to bits 8..15 = its offset in the lane's table column
+              const uint32_t addr = tab + __byte_perm(word, 0u, 0x4404u | (bb << 4));
+              float2 wv;
+              asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(wv.x), "=f"(wv.y) : "r"(addr));
 #pragma unroll
-              for (int m = 0; m < M; ++m) part[m] += lo * xv[m][(2 * bb) % WPW] + hi * xv[m][(2 * bb + 1) % WPW];
+              for (int m = 0; m < M; ++m) part[m] = __ffma2_rn(wv, xv[m][bb], part[m]);
             } else {
-              const float wv = __uint_as_float(t);
+              const uint32_t addr = tab + (__byte_perm(word, 0u, 0x4404u | (bb << 4)) >> 1);
+              float wv;
+              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(wv) : "r"(addr));
 #pragma unroll
-              for (int m = 0; m < M; ++m) part[m] += wv * xv[m][bb % WPW];
+              for (int m = 0; m < M; ++m) {
+                const float xs = (bb & 1) ? xv[m][bb >> 1].y : xv[m][bb >> 1].x;
+                part[m].x = fmaf(wv, xs, part[m].x);
+              }
             }
           }
           const bool ok = n0 + r < N;
           const float sc = ok ? __bfloat162float(scales[(long long)(n0 + r) * groups + g]) : 0.f;
-          const float zr = (ok && zeros) ? __bfloat162float(zeros[(long long)(n0 + r) * groups + g]) : 0.f;
+          const float2 sc2 = make_float2(sc, sc);
 #pragma unroll
-          for (int m = 0; m < M; ++m) acc[m][r] += sc * part[m] + zr * xsum[m];
+          for (int m = 0; m < M; ++m) acc[m][r] = __ffma2_rn(sc2, part[m], acc[m][r]);
+          if (HAS_ZERO) {
+            const float zr = ok ? __bfloat162float(zeros[(long long)(n0 + r) * groups + g]) : 0.f;
+#pragma unroll
+            for (int m = 0; m < M; ++m) zacc[m][r] = fmaf(zr, xsum[m], zacc[m][r]);
+          }
         }
       }
     }
@@ -161,7 +183,7 @@ qgemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const uint8_t* 
     for (int m = 0; m < M; ++m)
 #pragma unroll
       for (int r = 0; r < QG_ROWS; ++r) {
-        float s = warp_sum(acc[m][r]);
+        float s = warp_sum(acc[m][r].x + acc[m][r].y + (HAS_ZERO ? zacc[m][r] : 0.f));
         if (lane == 0 && n0 + r < N) {
           if (bias) s += __bfloat162float(bias[n0 + r]);
           out[m * ldo + n0 + r] = __float2bfloat16(s);
@@ -197,15 +219,15 @@ EDL_HOST_API int edl_dequant_bf16(const void* codes, const void* scales, const v
   return check_cuda(cudaGetLastError(), "dequant launch");
 }
 
-// x [M, K] bf16 (row pitch ldx, multiple of 8), M <= 8; out [M, N] bf16. The group size must be a multiple of the
+// x [M, K] fp32 (row pitch ldx, multiple of 4), M <= 8; out [M, N] bf16. The group size must be a multiple of the
 // number of weights in one 16-byte code vector (32 for 4-bit, 16 for 8-bit).
 EDL_HOST_API int edl_qgemv(const void* x, long long ldx, const void* codes, const void* scales, const void* zeros,
                            const float* lut, int bits, int M, int N, int K, int group, void* out, long long ldo,
                            const void* bias, void* stream) {
   if (check_quant_args("edl_qgemv", bits, N, K, group)) return -1;
   const int per16 = bits == 4 ? 32 : 16;
-  if (M < 1 || M > QG_MAX_M || (ldx & 7) || group % per16) {
-    set_last_error("edl_qgemv: M must be in [1, %d], ldx a multiple of 8 and group a multiple of %d", QG_MAX_M, per16);
+  if (M < 1 || M > QG_MAX_M || (ldx & 3) || group % per16) {
+    set_last_error("edl_qgemv: M must be in [1, %d], ldx a multiple of 4 and group a multiple of %d", QG_MAX_M, per16);
     return -1;
   }
   const int rows_per_cta = (QG_THREADS / 32) * QG_ROWS;
@@ -213,14 +235,19 @@ EDL_HOST_API int edl_qgemv(const void* x, long long ldx, const void* codes, cons
   const int cap = sm_count() * 2;   // persistent: warps loop over row groups
   if (blocks > cap) blocks = cap;
   cudaStream_t s = (cudaStream_t)stream;
-#define EDL_QGEMV_LAUNCH(MM, BB)                                                                                    \
-  qgemv_kernel<MM, BB><<<blocks, QG_THREADS, 0, s>>>((const __nv_bfloat16*)x, ldx, (const uint8_t*)codes,           \
-                                                     (const __nv_bfloat16*)scales, (const __nv_bfloat16*)zeros,     \
-                                                     lut, N, K, group, (__nv_bfloat16*)out, ldo,                    \
-                                                     (const __nv_bfloat16*)bias)
+  const int smem = 256 * 32 * (bits == 4 ? 8 : 4);
+#define EDL_QGEMV_LAUNCH(MM, BB, ZZ)                                                                                \
+  do {                                                                                                              \
+    auto kern = qgemv_kernel<MM, BB, ZZ>;                                                                           \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);                                  \
+    kern<<<blocks, QG_THREADS, smem, s>>>((const float*)x, ldx, (const uint8_t*)codes, (const __nv_bfloat16*)scales, \
+                                          (const __nv_bfloat16*)zeros, lut, N, K, group, (__nv_bfloat16*)out, ldo,  \
+                                          (const __nv_bfloat16*)bias);                                              \
+  } while (0)
 #define EDL_QGEMV_CASE(MM)                                                                                          \
   case MM:                                                                                                          \
-    if (bits == 4) EDL_QGEMV_LAUNCH(MM, 4); else EDL_QGEMV_LAUNCH(MM, 8);                                           \
+    if (bits == 4) { if (zeros) EDL_QGEMV_LAUNCH(MM, 4, true); else EDL_QGEMV_LAUNCH(MM, 4, false); }               \
+    else { if (zeros) EDL_QGEMV_LAUNCH(MM, 8, true); else EDL_QGEMV_LAUNCH(MM, 8, false); }                         \
     break;
   switch (M) {
     EDL_QGEMV_CASE(1)

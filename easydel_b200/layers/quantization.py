@@ -200,10 +200,9 @@ def quantized_matmul(x: torch.Tensor, q: QuantizedTensor, bias: torch.Tensor | N
     per16 = 32 if q.bits == 4 else 16
     if x2.is_cuda and _lib.available() and x2.dtype == torch.bfloat16:
         if M <= 8 and q.group % per16 == 0:
-            if x2.stride(1) != 1 or x2.stride(0) % 8:
-                x2 = x2.contiguous()
+            x32 = x2.float().contiguous()     # the kernel reads fp32 activations (a few rows: converted once)
             out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
-            _lib.call("edl_qgemv", x2.data_ptr(), x2.stride(0) if M > 1 else K, q.codes.data_ptr(),
+            _lib.call("edl_qgemv", x32.data_ptr(), K, q.codes.data_ptr(),
                       q.scales.data_ptr(), _lib.ptr(q.zeros), q.lut.data_ptr(), q.bits, M, N, K, q.group,
                       out.data_ptr(), N, _lib.ptr(bias), _lib.stream_ptr())
             return out.view(*x.shape[:-1], N)

@@ -7,6 +7,7 @@
     python -m easydel_b200.ops.profile_case gemm_rs       # one-rank form of the GEMM -> reduce-scatter kernel
     python -m easydel_b200.ops.profile_case ag_gemm       # one-rank form of the all-gather -> GEMM kernel
     python -m easydel_b200.ops.profile_case qgemv         # 4-bit fused dequant-GEMV, 4 rows x 14336 x 4096
+    python -m easydel_b200.ops.profile_case qgemv_plain   # the same kernel as single launches (profiler captures)
     python -m easydel_b200.ops.profile_case adamw         # fused AdamW over 256M parameters
 
 Prints the CUDA-event time of the last launch. Everything held on the device stays below 4 GB.
@@ -62,6 +63,13 @@ def main() -> None:
         op = AllGatherGemm(None, 4096, 4096, dev)
         fn = lambda: op(a, w)  # noqa: E731
         work = 2.0 * 4096 * 4096 * 4096
+    elif what == "qgemv_plain":      # single launches (for a profiler capture); timing is host-bound, see "qgemv"
+        from ..layers.quantization import quantize, quantized_matmul
+
+        q1 = quantize(bf(14336, 4096) * 0.05, "nf4")
+        x = bf(4, 4096)
+        fn = lambda: quantized_matmul(x, q1)  # noqa: E731
+        work = 14336 * 4096 * 0.5 + 14336 * 64 * 2
     elif what == "qgemv":
         from ..layers.quantization import quantize, quantized_matmul
 
@@ -101,7 +109,7 @@ def main() -> None:
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
-    unit = "GB/s" if what in ("qgemv", "adamw") else "TFLOP/s"
+    unit = "GB/s" if what in ("qgemv", "qgemv_plain", "adamw") else "TFLOP/s"
     rate = work / ms / 1e6 if unit == "GB/s" else work / ms / 1e9
     from . import _lib
 
