@@ -27,6 +27,7 @@ class MLACache:
         self.k_rope = torch.zeros(num_layers, batch, max_len, rope_dim, dtype=dtype, device=device)
         self.length, self.max_len = 0, max_len
         self.linear: dict[int, object] = {}     # layer -> recurrent state of a linear-attention layer (hybrids)
+        self.index_keys: dict[int, torch.Tensor] = {}   # layer -> keys of the sparse-attention scorer seen so far
 
     def seq_len(self) -> int:
         return self.length
@@ -68,8 +69,11 @@ class MLAttention(nn.Module):
                  qk_nope_head_dim: int, qk_rope_head_dim: int, v_head_dim: int, rope: dict, rope_interleave: bool = True,
                  norm_eps: float = 1e-6, bias: bool = False, scale: float | None = None, layer_idx: int = 0,
                  dtype=torch.bfloat16, init_std: float = 0.02, tp_size: int = 1, tp_rank: int = 0, tp_group=None,
-                 use_rope: bool = True):
+                 use_rope: bool = True, indexer: dict | None = None):
         super().__init__()
+        # DeepSeek sparse attention (GLM-MoE-DSA): a light scorer ranks the keys of every query and attention runs
+        # over the ``topk`` best ones only; kwargs: n_heads, head_dim, topk
+        self.indexer_cfg = indexer
         self.use_rope = use_rope        # Kimi-Linear's latent layers carry no positions (``mla_use_nope``)
         self.H, self.nope, self.rope_dim, self.vd = num_heads // tp_size, qk_nope_head_dim, qk_rope_head_dim, v_head_dim
         self.qk_dim = qk_nope_head_dim + qk_rope_head_dim
@@ -93,6 +97,48 @@ class MLAttention(nn.Module):
         self.o_proj = RowParallelLinear(num_heads * v_head_dim, hidden_size, bias=bias, tp_size=tp_size,
                                         tp_rank=tp_rank, tp_group=tp_group, **kw)
         self.rotary = get_rope(head_size=qk_rope_head_dim, **rope)
+        if indexer is not None:
+            from .norms import LayerNorm
+
+            ih, idim = indexer["n_heads"], indexer["head_dim"]
+            self.indexer = nn.Module()
+            self.indexer.wq_b = ColumnParallelLinear(q_lora_rank, ih * idim, bias=False, **kw)
+            self.indexer.wk = ColumnParallelLinear(hidden_size, idim, bias=False, **kw)
+            self.indexer.k_norm = LayerNorm(idim, 1e-6, dtype=dtype)
+            self.indexer.weights_proj = ColumnParallelLinear(hidden_size, ih, bias=False, **kw)
+
+    def _index_bias(self, hidden, q_resid, positions, cache_view, Tk):
+        """Additive mask ``[B, 1, T, Tk]``: 0 at the ``topk`` keys the scorer ranks highest for each query (among
+        the causally visible ones), -inf elsewhere. Score: ``sum_h w_h relu(q_h . k) / sqrt(d)`` with rotary
+        (half-split layout) on the first ``rope_dim`` channels of the scorer's own q / k."""
+        cfg = self.indexer_cfg
+        B, T, _ = hidden.shape
+        ih, idim, rd = cfg["n_heads"], cfg["head_dim"], self.rope_dim
+        cos, sin = self.rotary.tables(hidden.device)
+        pos = positions.reshape(-1) if positions.numel() == B * T else positions.expand(B, T).reshape(-1)
+
+        def rot(x):       # x [B, T, h, idim]
+            h = x.shape[2]
+            xr = R.apply_rope(x[..., :rd].reshape(B * T, h, rd), pos, cos, sin, rd, False).view(B, T, h, rd)
+            return torch.cat([xr, x[..., rd:]], -1)
+
+        q = rot(self.indexer.wq_b(q_resid).view(B, T, ih, idim))
+        k = rot(self.indexer.k_norm(self.indexer.wk(hidden))[:, :, None, :])[:, :, 0]
+        if cache_view is not None:
+            store = cache_view.cache.index_keys
+            prev = store.get(cache_view.layer)
+            k = k if prev is None or T > 1 and cache_view.cache.length == 0 else torch.cat([prev, k], 1)
+            store[cache_view.layer] = k
+        w = self.indexer.weights_proj(hidden).float() * ih ** -0.5
+        sc = torch.relu(torch.einsum("bshd,btd->bsht", q.float(), k.float()) * idim ** -0.5)
+        score = torch.einsum("bsht,bsh->bst", sc, w)
+        qpos = torch.arange(Tk - T, Tk, device=hidden.device)[:, None]
+        visible = torch.arange(Tk, device=hidden.device)[None, :] <= qpos
+        score = score.masked_fill(~visible[None], float("-inf"))
+        top = score.topk(min(cfg["topk"], Tk), dim=-1).indices
+        bias = torch.full((B, T, Tk), float("-inf"), device=hidden.device)
+        bias.scatter_(-1, top, 0.0)
+        return bias[:, None]
 
     def _rope(self, x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """x ``[B, T, h, rope_dim]``. Checkpoints with ``rope_interleave`` store pairs interleaved: de-interleave,
@@ -109,8 +155,10 @@ class MLAttention(nn.Module):
 
     def forward(self, hidden, positions, *, segment_ids=None, cache_view=None, attn_meta=None, **_):
         B, T, _ = hidden.shape
+        q_resid = None
         if self.q_proj is None:
-            q = self.q_b_proj(self.q_a_layernorm(self.q_a_proj(hidden)))
+            q_resid = self.q_a_layernorm(self.q_a_proj(hidden))
+            q = self.q_b_proj(q_resid)
         else:
             q = self.q_proj(hidden)
         q = q.view(B, T, self.H, self.qk_dim)
@@ -131,6 +179,10 @@ class MLAttention(nn.Module):
         k = torch.cat([kv[..., : self.nope], k_rope[:, :, None, :].expand(B, Tk, self.H, self.rope_dim)], -1)
         v = kv[..., self.nope:]
         qf = torch.cat([q_nope, q_rope], -1)
+        if self.indexer_cfg is not None:
+            bias = self._index_bias(hidden, q_resid, positions, cache_view, Tk)
+            o = R.attention(qf, k, v, causal=True, scale=self.scale, bias=bias)
+            return self.o_proj(o.reshape(B, T, self.H * self.vd).to(hidden.dtype))
         if kv_seg is not None:
             o = R.attention(qf, k, v, causal=True, scale=self.scale, segment_ids=kv_seg[:, Tk - T:],
                             kv_segment_ids=kv_seg)

@@ -305,6 +305,9 @@ def _mla_args(c) -> dict:
 
 def _dense_then_moe(c, freq_attr="moe_layer_freq"):
     n = c.num_hidden_layers
+    kinds = getattr(c, "mlp_layer_types", None)
+    if kinds:       # explicit per-layer list ("dense" / "sparse")
+        return tuple(i for i, k in enumerate(kinds) if k == "sparse")
     freq = getattr(c, freq_attr, 1) or 1
     return tuple(i for i in range(n) if i >= c.first_k_dense_replace and i % freq == 0)
 
@@ -751,6 +754,28 @@ EXPORTS.update(define_family(
     rules=[("post_self_attn_layernorm", "post_attn_out_layernorm"),
            ("post_attention_layernorm", "pre_feedforward_layernorm"),
            ("post_mlp_layernorm", "post_feedforward_layernorm")], with_classifier=False))
+
+
+
+# ---- glm_moe_dsa (easydel/modules/glm_moe_dsa): the GLM-4-MoE-Lite block whose latent attention only looks at the
+# ---- ``index_topk`` keys a small scorer (own projections, ReLU-weighted multi-head dot products) ranks highest ----
+def _glm_moe_dsa_spec(c):
+    spec = _deepseek_v3_spec(c)
+    # rotary pairs are stored half-split in these checkpoints (no de-interleaving as in DeepSeek-V3)
+    spec.mla = dict(spec.mla, rope_interleave=False,
+                    indexer=dict(n_heads=c.index_n_heads, head_dim=c.index_head_dim, topk=c.index_topk))
+    return spec
+
+
+EXPORTS.update(define_family(
+    "glm_moe_dsa", dict(_GLM4_LITE, vocab_size=154880, hidden_size=6144, intermediate_size=12288,
+                        moe_intermediate_size=2048, num_hidden_layers=78, num_attention_heads=64,
+                        num_key_value_heads=64, n_routed_experts=256, routed_scaling_factor=2.5, kv_lora_rank=512,
+                        q_lora_rank=2048, qk_rope_head_dim=64, v_head_dim=256, qk_nope_head_dim=192,
+                        num_experts_per_tok=8, first_k_dense_replace=3, index_topk=2048, index_head_dim=128,
+                        index_n_heads=32),
+    _glm_moe_dsa_spec, class_prefix="GlmMoeDsa",
+    rules=[("mlp.gate.e_score_correction_bias", "mlp.e_score_correction_bias")], with_classifier=False))
 
 globals().update(EXPORTS)
 __all__ = sorted(EXPORTS)
