@@ -32,5 +32,7 @@ from . import rwkv  # noqa: F401
 from .rwkv import *  # noqa: F401,F403
 from . import glm4v  # noqa: F401
 from .glm4v import *  # noqa: F401,F403
+from . import gemma4  # noqa: F401
+from .gemma4 import *  # noqa: F401,F403
 from . import kimi_vl  # noqa: F401
 from .kimi_vl import *  # noqa: F401,F403
