@@ -414,3 +414,262 @@ class Gemma4ForCausalLM(EasyDeLBaseModule):
 
     def hf_rename_out(self, sd):
         return dict(sd)
+
+
+# =====================================================================================================================
+# Vision tower and the multimodal model (easydel/modules/gemma4/modeling_gemma4.py:239-1000, 2826-3367)
+# =====================================================================================================================
+from .._base.families import _Renamer  # noqa: E402
+from .._base.vlm import OUTER_RULES, VLMConfig, VLMForConditionalGeneration  # noqa: E402
+
+
+@register_config("gemma4_vision")
+class Gemma4VisionConfig(EasyDeLBaseConfig):
+    model_type = "gemma4_vision"
+    hf_config_keys = ("hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+                      "num_key_value_heads", "head_dim", "hidden_activation", "rms_norm_eps", "rope_parameters",
+                      "pooling_kernel_size", "patch_size", "position_embedding_size", "use_clipped_linears",
+                      "standardize")
+
+    def __init__(self, hidden_size=768, intermediate_size=3072, num_hidden_layers=16, num_attention_heads=12,
+                 num_key_value_heads=12, head_dim=64, hidden_activation="gelu_pytorch_tanh", rms_norm_eps=1e-6,
+                 max_position_embeddings=131_072, rope_parameters=None, pooling_kernel_size=3, patch_size=16,
+                 position_embedding_size=10 * 1024, use_clipped_linears=False, standardize=False,
+                 initializer_range=0.02, **kw):
+        self.hidden_size, self.intermediate_size, self.num_hidden_layers = hidden_size, intermediate_size, \
+            num_hidden_layers
+        self.num_attention_heads, self.num_key_value_heads, self.head_dim = num_attention_heads, \
+            num_key_value_heads, head_dim
+        self.hidden_activation, self.rms_norm_eps = hidden_activation, rms_norm_eps
+        self.max_position_embeddings = max_position_embeddings
+        self.rope_parameters = rope_parameters or {"rope_type": "default", "rope_theta": 100.0}
+        self.pooling_kernel_size, self.patch_size = pooling_kernel_size, patch_size
+        self.position_embedding_size, self.use_clipped_linears = position_embedding_size, use_clipped_linears
+        self.standardize, self.initializer_range = standardize, initializer_range
+        super().__init__(**kw)
+
+
+@register_config("gemma4")
+class Gemma4Config(VLMConfig):
+    model_type = "gemma4"
+    vision_default, text_default = "gemma4_vision", "gemma4_text"
+
+    def __init__(self, text_config=None, vision_config=None, audio_config=None, boi_token_id=255_999,
+                 eoi_token_id=258_882, image_token_id=258_880, video_token_id=258_884, boa_token_id=256_000,
+                 eoa_token_index=258_883, audio_token_id=258_881, **kw):
+        if isinstance(vision_config, dict):
+            vision_config = dict(vision_config, model_type="gemma4_vision")
+        if isinstance(text_config, dict):
+            text_config = dict(text_config, model_type="gemma4_text")
+        kw.setdefault("tie_word_embeddings", True)
+        kw = self._init_parts(vision_config, text_config, image_token_id, kw)
+        self.audio_config = audio_config          # kept for round trips; the audio tower is not built
+        self.boi_token_id, self.eoi_token_id, self.image_token_id = boi_token_id, eoi_token_id, image_token_id
+        self.video_token_id, self.boa_token_id, self.eoa_token_index = video_token_id, boa_token_id, eoa_token_index
+        self.audio_token_id = audio_token_id
+        super().__init__(**kw)
+
+
+class _ClippableLinear(nn.Module):
+    """Bias-free linear whose input and output may be clamped to stored ranges (quantisation-aware checkpoints)."""
+
+    def __init__(self, c: Gemma4VisionConfig, d_in, d_out, dtype):
+        super().__init__()
+        self.clip = c.use_clipped_linears
+        self.linear = nn.Linear(d_in, d_out, bias=False, dtype=dtype)
+        if self.clip:
+            for n, v in (("input_min", -float("inf")), ("input_max", float("inf")), ("output_min", -float("inf")),
+                         ("output_max", float("inf"))):
+                self.register_buffer(n, torch.tensor(v))
+
+    def forward(self, x):
+        if self.clip:
+            x = torch.clamp(x, self.input_min, self.input_max)
+        y = F.linear(x, self.linear.weight)
+        return torch.clamp(y, self.output_min, self.output_max) if self.clip else y
+
+
+class _VisionAttention(nn.Module):
+    def __init__(self, c: Gemma4VisionConfig, dtype):
+        super().__init__()
+        H, hd = c.hidden_size, c.head_dim
+        self.heads, self.kv_heads, self.head_dim, self.eps = c.num_attention_heads, c.num_key_value_heads, hd, \
+            c.rms_norm_eps
+        self.q_proj = _ClippableLinear(c, H, self.heads * hd, dtype)
+        self.k_proj = _ClippableLinear(c, H, self.kv_heads * hd, dtype)
+        self.v_proj = _ClippableLinear(c, H, self.kv_heads * hd, dtype)
+        self.o_proj = _ClippableLinear(c, self.heads * hd, H, dtype)
+        self.q_norm, self.k_norm = RMSNorm(hd, c.rms_norm_eps, dtype), RMSNorm(hd, c.rms_norm_eps, dtype)
+
+    @staticmethod
+    def _rope2d(x, cos, sin):
+        # the head splits in two halves: the first turns with the patch column, the second with the row
+        h = x.shape[-1] // 2
+        q = h // 2
+        a = R.rotate(x[..., :h].float(), cos[..., :q], sin[..., :q])
+        b = R.rotate(x[..., h:].float(), cos[..., q:], sin[..., q:])
+        return torch.cat([a, b], -1).to(x.dtype)
+
+    def forward(self, x, cos, sin, seg):
+        B, T, _ = x.shape
+        q = self._rope2d(self.q_norm(self.q_proj(x).view(B, T, self.heads, self.head_dim)), cos, sin)
+        k = self._rope2d(self.k_norm(self.k_proj(x).view(B, T, self.kv_heads, self.head_dim)), cos, sin)
+        v = self.v_proj(x).view(B, T, self.kv_heads, self.head_dim)
+        v = (v.float() * torch.rsqrt(v.float().pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype)
+        o = F.attention(q, k, v, causal=False, scale=1.0, segment_ids=seg)
+        return self.o_proj(o.reshape(B, T, -1))
+
+
+class _VisionMLP(nn.Module):
+    def __init__(self, c: Gemma4VisionConfig, dtype):
+        super().__init__()
+        self.act = c.hidden_activation
+        self.gate_proj = _ClippableLinear(c, c.hidden_size, c.intermediate_size, dtype)
+        self.up_proj = _ClippableLinear(c, c.hidden_size, c.intermediate_size, dtype)
+        self.down_proj = _ClippableLinear(c, c.intermediate_size, c.hidden_size, dtype)
+
+    def forward(self, x):
+        return self.down_proj(R.ACT2FN[self.act](self.gate_proj(x)) * self.up_proj(x))
+
+
+class _VisionLayer(nn.Module):
+    def __init__(self, c: Gemma4VisionConfig, dtype):
+        super().__init__()
+        self.self_attn, self.mlp = _VisionAttention(c, dtype), _VisionMLP(c, dtype)
+        for n in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm",
+                  "post_feedforward_layernorm"):
+            setattr(self, n, RMSNorm(c.hidden_size, c.rms_norm_eps, dtype))
+
+    def forward(self, x, cos, sin, seg):
+        x = x + self.post_attention_layernorm(self.self_attn(self.input_layernorm(x), cos, sin, seg))
+        return x + self.post_feedforward_layernorm(self.mlp(self.pre_feedforward_layernorm(x)))
+
+
+class Gemma4VisionModel(nn.Module):
+    """``pixel_values`` ``[B, patches, 3 * P * P]`` in ``[0, 1]`` and ``pixel_position_ids`` ``[B, patches, 2]`` (x, y;
+    ``-1`` marks padding) -> soft tokens ``[n_valid, hidden]``: the patches are encoded, averaged over
+    ``k x k`` neighbourhoods of the grid (``k = pooling_kernel_size``) and scaled by ``sqrt(hidden)``."""
+
+    def __init__(self, c: Gemma4VisionConfig, dtype):
+        super().__init__()
+        self.cfg = c
+        self.patch_embedder = nn.Module()
+        self.patch_embedder.input_proj = nn.Linear(3 * c.patch_size ** 2, c.hidden_size, bias=False, dtype=dtype)
+        self.patch_embedder.position_embedding_table = nn.Parameter(
+            torch.randn(2, c.position_embedding_size, c.hidden_size, dtype=dtype) * c.initializer_range)
+        self.encoder = nn.Module()
+        self.encoder.layers = nn.ModuleList([_VisionLayer(c, dtype) for _ in range(c.num_hidden_layers)])
+        sp = c.head_dim // 2
+        self.register_buffer("inv_freq", 1.0 / (c.rope_parameters["rope_theta"] ** (
+            torch.arange(0, sp, 2, dtype=torch.float32) / sp)), persistent=False)
+        if c.standardize:
+            self.register_buffer("std_bias", torch.zeros(c.hidden_size))
+            self.register_buffer("std_scale", torch.ones(c.hidden_size))
+
+    def forward(self, pixel_values, pixel_position_ids):
+        c = self.cfg
+        pad = (pixel_position_ids == -1).all(-1)
+        pos = pixel_position_ids.clamp(min=0)
+        tab = self.patch_embedder.position_embedding_table
+        w = self.patch_embedder.input_proj.weight
+        x = F.linear((2 * (pixel_values - 0.5)).to(w.dtype), w)
+        pe = tab[0][pos[..., 0]] + tab[1][pos[..., 1]]
+        x = x + torch.where(pad[..., None], torch.zeros_like(pe), pe)
+        ang = pixel_position_ids[..., None].float() * self.inv_freq            # [B, T, 2, hd/4]
+        cos, sin = ang.cos().flatten(-2)[:, :, None], ang.sin().flatten(-2)[:, :, None]
+        seg = (~pad).to(torch.int32)
+        for layer in self.encoder.layers:
+            x = layer(x, cos, sin, seg)
+        x = x.masked_fill(pad[..., None], 0.0)
+        T = x.shape[1]
+        length = T // (c.pooling_kernel_size ** 2)
+        valid = ~pad
+        if length != T:
+            k = int((T // length) ** 0.5)
+            if k * k * length != T:
+                raise ValueError(f"cannot pool {T} patches to {length} soft tokens")
+            max_x = pos[..., 0].max(-1, keepdim=True)[0] + 1
+            cell = torch.div(pos, k, rounding_mode="floor")
+            cell = cell[..., 0] + (max_x // k) * cell[..., 1]
+            wts = torch.nn.functional.one_hot(cell.long(), length).float() / (k * k)
+            x = (wts.transpose(1, 2) @ x.float()).to(x.dtype)
+            valid = ~(wts == 0).all(1)
+        x = (x * c.hidden_size ** 0.5)[valid]
+        if c.standardize:
+            x = (x - self.std_bias) * self.std_scale
+        return x
+
+
+class _MultimodalEmbedder(nn.Module):
+    def __init__(self, d_in, d_out, eps, dtype):
+        super().__init__()
+        self.eps = eps
+        self.embedding_projection = nn.Linear(d_in, d_out, bias=False, dtype=dtype)
+
+    def forward(self, x):
+        xf = x.float()
+        return F.linear((xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype),
+                        self.embedding_projection.weight)
+
+
+@register_module(TaskType.IMAGE_TEXT_TO_TEXT, config=Gemma4Config, model_type="gemma4")
+class Gemma4ForConditionalGeneration(VLMForConditionalGeneration):
+    """Image soft tokens replace the ``image_token_id`` embeddings. The per-layer inputs are looked up with the
+    placeholder positions set to the padding id, before the merge."""
+
+    outer_rules = [*OUTER_RULES, ("model.embed_vision.", "embed_vision.")]
+    ignored_prefixes = ("model.audio_tower.", "model.embed_audio.")
+    image_kwargs = ("image_position_ids",)
+
+    def __init__(self, config, dtype=torch.bfloat16, param_dtype=None, precision=None, rngs=None):
+        super().__init__(config, dtype, param_dtype, precision, rngs)
+        self.vision_tower = Gemma4VisionModel(config.vision_config, self.param_dtype)
+        self.embed_vision = _MultimodalEmbedder(config.vision_config.hidden_size, config.text_config.hidden_size,
+                                                config.vision_config.rms_norm_eps, self.param_dtype)
+        self.language_model = self.build_language_model(config, dtype, param_dtype, precision, rngs)
+
+    def _vision_renamer(self):
+        return _Renamer([])
+
+    def get_image_features(self, pixel_values, image_position_ids=None, **kw):
+        if image_position_ids is None:
+            raise ValueError("Gemma-4 needs image_position_ids ([B, patches, 2]) with pixel_values")
+        return self.embed_vision(self.vision_tower(pixel_values, image_position_ids))
+
+    def _mm_mask(self, input_ids):
+        c = self.config
+        return (input_ids == c.image_token_id) | (input_ids == c.video_token_id) | (input_ids == c.audio_token_id)
+
+    def embed_text(self, input_ids):
+        ids = input_ids.masked_fill(self._mm_mask(input_ids), self.config.text_config.pad_token_id or 0)
+        return self.language_model.model.embed(ids)
+
+    def _per_layer(self, input_ids):
+        tm = self.language_model.model
+        if not self.config.text_config.hidden_size_per_layer_input:
+            return None
+        ids = input_ids.masked_fill(self._mm_mask(input_ids), self.config.text_config.pad_token_id or 0)
+        P = self.config.text_config.hidden_size_per_layer_input
+        e = tm.embed_tokens_per_layer(ids) * torch.tensor(P ** 0.5, dtype=tm.embed_tokens_per_layer.weight.dtype)
+        return e.view(*ids.shape, self.config.text_config.num_hidden_layers, P)
+
+    def forward(self, input_ids=None, pixel_values=None, attention_mask=None, position_ids=None, inputs_embeds=None,
+                past_key_values=None, image_features=None, **kw):
+        extra = {k: kw.pop(k) for k in self.image_kwargs if k in kw}
+        if inputs_embeds is None:
+            first = past_key_values is None or past_key_values.seq_len() == 0
+            inputs_embeds = self.merge_embeddings(input_ids, pixel_values if first else None,
+                                                  image_features if first else None, **extra)
+            kw.setdefault("per_layer_inputs", self._per_layer(input_ids))
+        return self.language_model(inputs_embeds=inputs_embeds, attention_mask=attention_mask,
+                                   position_ids=position_ids, past_key_values=past_key_values, **kw)
+
+    def _compute_task_loss(self, labels, loss_config: LossConfig, loss_scale, call, loss_kwargs):
+        call = dict(call)
+        ids = call.pop("input_ids")
+        extra = {k: call.pop(k) for k in self.image_kwargs if k in call}
+        call["inputs_embeds"] = self.merge_embeddings(ids, call.pop("pixel_values", None),
+                                                      call.pop("image_features", None), **extra)
+        call["per_layer_inputs"] = self._per_layer(ids)
+        labels = labels.masked_fill(self._mm_mask(ids), loss_config.ignore_index)
+        return self.language_model._compute_task_loss(labels, loss_config, loss_scale, call, loss_kwargs)

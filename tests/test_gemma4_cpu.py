@@ -73,3 +73,58 @@ def test_borrowing_layers_hold_no_keys_and_model_trains_and_generates():
     m.eval()
     out = m.generate(ids[:, :5], max_new_tokens=4)
     assert out.sequences.shape == (2, 9)
+
+
+def test_multimodal_matches_hf_with_padded_patches():
+    IMG = 150
+    text = dict(BASE, num_kv_shared_layers=3)
+    vis = dict(hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=2,
+               head_dim=16, pooling_kernel_size=2, patch_size=4, position_embedding_size=64)
+    torch.manual_seed(0)
+    hf_cfg = transformers.Gemma4Config(text_config=dict(text), vision_config=dict(vis), image_token_id=IMG,
+                                       video_token_id=151, audio_token_id=152)
+    hf_cfg._attn_implementation = "eager"
+    hf_cfg.text_config._attn_implementation = "eager"
+    hf_cfg.vision_config._attn_implementation = "eager"
+    hf = transformers.Gemma4ForConditionalGeneration(hf_cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.dim() == 1 or "position_embedding_table" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    from easydel_b200.modules.gemma4 import Gemma4Config, Gemma4ForConditionalGeneration
+
+    m = Gemma4ForConditionalGeneration(Gemma4Config(text_config=dict(text), vision_config=dict(vis),
+                                                    image_token_id=IMG, video_token_id=151, audio_token_id=152),
+                                       dtype=torch.float32).eval()
+    m.load_state_dict(hf_to_internal(m, hf.state_dict()))
+    # image 0: 4 x 6 patches; image 1: 4 x 4 patches plus 8 padding patches; pooled 2 x 2 -> 6 and 4 soft tokens
+    def grid(w, h, n):
+        xy = torch.stack(torch.meshgrid(torch.arange(w), torch.arange(h), indexing="xy"), -1).reshape(-1, 2)
+        return torch.cat([xy, -torch.ones(n - xy.shape[0], 2, dtype=torch.long)])
+    pos = torch.stack([grid(6, 4, 24), grid(4, 4, 24)])
+    pix = torch.rand(2, 24, 48)
+    pix[1, 16:] = 0
+    ids = torch.randint(1, 140, (1, 24))
+    ids[0, 2:8] = IMG
+    ids[0, 11:15] = IMG
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=pix, image_position_ids=pos).logits
+        feats = m.get_image_features(pix, image_position_ids=pos)
+        assert feats.shape == (10, 48)
+        ref_feats = hf.model.get_image_features(pix, pos, return_dict=True).pooler_output
+        torch.testing.assert_close(feats, ref_feats, atol=2e-4, rtol=2e-4)
+        got = m(input_ids=ids, pixel_values=pix, image_position_ids=pos).logits
+        torch.testing.assert_close(got, want, atol=4e-4, rtol=4e-4)
+        cache = m.init_cache(1, 32)
+        m(input_ids=ids[:, :20], pixel_values=pix, image_position_ids=pos, past_key_values=cache)
+        cache.advance(20)
+        nxt = m(input_ids=ids[:, 20:], past_key_values=cache).logits
+        torch.testing.assert_close(nxt, want[:, 20:], atol=4e-4, rtol=4e-4)
+    m.train()
+    _, met = m.compute_loss(input_ids=ids, labels=ids, pixel_values=pix, image_position_ids=pos)
+    met.loss.backward()
+    assert m.vision_tower.encoder.layers[0].self_attn.q_proj.linear.weight.grad.abs().sum() > 0
+    back = internal_to_hf(m)
+    ref = hf.state_dict()
+    for k, v in back.items():
+        assert torch.equal(ref[k], v), k
