@@ -34,5 +34,7 @@ from . import glm4v  # noqa: F401
 from .glm4v import *  # noqa: F401,F403
 from . import gemma4  # noqa: F401
 from .gemma4 import *  # noqa: F401,F403
+from . import qwen3_omni_moe  # noqa: F401
+from .qwen3_omni_moe import *  # noqa: F401,F403
 from . import kimi_vl  # noqa: F401
 from .kimi_vl import *  # noqa: F401,F403
