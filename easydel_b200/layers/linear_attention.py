@@ -16,6 +16,12 @@ from ..ops import ssm
 from .linears import ColumnParallelLinear, RowParallelLinear
 
 
+def _l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """``x / sqrt(sum(x^2) + eps)`` in fp32: the epsilon sits inside the root, which matters for small activations."""
+    xf = x.float()
+    return xf * torch.rsqrt(xf.pow(2).sum(-1, keepdim=True) + eps)
+
+
 class LinearAttentionState:
     """Per-layer state of one batch of sequences."""
 
@@ -90,8 +96,7 @@ class GatedDeltaNet(nn.Module):
         w = self.conv1d.weight.squeeze(1)
         mixed = ssm.ragged_conv1d(mixed, w, None, cu, "silu", None if state is None else state.conv)
         q, k, v = torch.split(mixed, [self.key_dim, self.key_dim, self.value_dim], dim=-1)
-        q = torch.nn.functional.normalize(q.reshape(B * T, self.hk, self.dk).float(), dim=-1, eps=1e-6)
-        k = torch.nn.functional.normalize(k.reshape(B * T, self.hk, self.dk).float(), dim=-1, eps=1e-6)
+        q, k = _l2norm(q.reshape(B * T, self.hk, self.dk)), _l2norm(k.reshape(B * T, self.hk, self.dk))
         if self.rep > 1:
             q, k = q.repeat_interleave(self.rep, 1), k.repeat_interleave(self.rep, 1)
         v = v.reshape(B * T, self.hv, self.dv)
@@ -165,8 +170,7 @@ class KimiDeltaAttention(nn.Module):
         q = conv(self.q_proj(hidden), self.q_conv1d, None if state is None else state.q_conv)
         k = conv(self.k_proj(hidden), self.k_conv1d, None if state is None else state.k_conv)
         v = conv(self.v_proj(hidden), self.v_conv1d, None if state is None else state.v_conv)
-        q = torch.nn.functional.normalize(q.view(B * T, self.h, self.dk).float(), dim=-1, eps=1e-6)
-        k = torch.nn.functional.normalize(k.view(B * T, self.h, self.dk).float(), dim=-1, eps=1e-6)
+        q, k = _l2norm(q.view(B * T, self.h, self.dk)), _l2norm(k.view(B * T, self.h, self.dk))
         v = v.view(B * T, self.h, self.dv)
         gate = self.f_b_proj(torch.nn.functional.silu(self.f_a_proj(hidden))).reshape(B * T, self.h)
         g = -self.A_log.float().exp() * torch.nn.functional.softplus(gate.float() + self.dt_bias.float())

@@ -25,7 +25,7 @@ from ..ops import _lib
 _lib.register("edl_dequant_bf16", _lib.i32, [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32,
                                              _lib.vp, _lib.i64, _lib.vp])
 _lib.register("edl_qgemv", _lib.i32, [_lib.vp, _lib.i64, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32,
-                                      _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.i64, _lib.vp, _lib.vp])
+                                      _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.i64, _lib.vp, _lib.vp, _lib.vp])
 
 _NF4 = [-1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453, -0.28444138169288635,
         -0.18477343022823334, -0.09105003625154495, 0.0, 0.07958029955625534, 0.16093020141124725,
@@ -204,7 +204,7 @@ def quantized_matmul(x: torch.Tensor, q: QuantizedTensor, bias: torch.Tensor | N
             out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
             _lib.call("edl_qgemv", x32.data_ptr(), K, q.codes.data_ptr(),
                       q.scales.data_ptr(), _lib.ptr(q.zeros), q.lut.data_ptr(), q.bits, M, N, K, q.group,
-                      out.data_ptr(), N, _lib.ptr(bias), _lib.stream_ptr())
+                      out.data_ptr(), N, _lib.ptr(bias), _lib.status_word(x.device).data_ptr(), _lib.stream_ptr())
             return out.view(*x.shape[:-1], N)
         from ..ops import functional as F
 

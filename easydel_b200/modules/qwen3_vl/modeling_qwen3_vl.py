@@ -247,3 +247,66 @@ class Qwen3VLMoeConfig(Qwen3VLConfig):
 @register_module(TaskType.IMAGE_TEXT_TO_TEXT, config=Qwen3VLMoeConfig, model_type="qwen3_vl_moe")
 class Qwen3VLMoeForConditionalGeneration(Qwen3VLForConditionalGeneration):
     pass
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Qwen3.5 (easydel/modules/qwen3_5, easydel/modules/qwen3_5_moe): the same vision tower without DeepStack in front
+# of the hybrid gated-DeltaNet / attention language models; attention layers rotate a quarter of each head with the
+# interleaved three-stream positions, DeltaNet layers take no positions.
+# ---------------------------------------------------------------------------------------------------------------------
+@register_config("qwen3_5_vision")
+class Qwen3_5VisionConfig(Qwen3VLVisionConfig):
+    model_type = "qwen3_5_vision"
+
+    def __init__(self, **kw):
+        kw.setdefault("deepstack_visual_indexes", ())
+        super().__init__(**kw)
+
+
+def _qwen3_5_text_dict(text_config, model_type):
+    text_config = dict(text_config, model_type=model_type)
+    rp = text_config.pop("rope_parameters", None)
+    if rp:      # one dict in the published configs: base, rotated fraction and the three-stream sections
+        rp = dict(rp)
+        text_config.setdefault("rope_theta", rp.pop("rope_theta", 10000000.0))
+        text_config.setdefault("partial_rotary_factor", rp.pop("partial_rotary_factor", 0.25))
+        text_config.setdefault("rope_scaling", rp)
+    return text_config
+
+
+@register_config("qwen3_5")
+class Qwen3_5Config(Qwen3VLConfig):
+    model_type = "qwen3_5"
+    vision_default, text_default = "qwen3_5_vision", "qwen3_5_text"
+
+    def __init__(self, vision_config=None, text_config=None, image_token_id=248056, video_token_id=248057,
+                 vision_start_token_id=248053, vision_end_token_id=248054, **kw):
+        if isinstance(vision_config, dict):
+            vision_config = Qwen3_5VisionConfig(**{k: v for k, v in vision_config.items() if k != "model_type"})
+        if isinstance(text_config, dict):
+            from ...infra.factory import registry
+
+            text_config = registry.get_config(self.text_default)(
+                **{k: v for k, v in _qwen3_5_text_dict(text_config, self.text_default).items() if k != "model_type"})
+        super().__init__(vision_config=vision_config, text_config=text_config, image_token_id=image_token_id,
+                         video_token_id=video_token_id, vision_start_token_id=vision_start_token_id,
+                         vision_end_token_id=vision_end_token_id, **kw)
+
+
+@register_config("qwen3_5_moe")
+class Qwen3_5MoeConfig(Qwen3_5Config):
+    model_type = "qwen3_5_moe"
+    vision_default, text_default = "qwen3_5_vision", "qwen3_5_moe_text"
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+
+
+@register_module(TaskType.IMAGE_TEXT_TO_TEXT, config=Qwen3_5Config, model_type="qwen3_5")
+class Qwen3_5ForConditionalGeneration(Qwen3VLForConditionalGeneration):
+    pass
+
+
+@register_module(TaskType.IMAGE_TEXT_TO_TEXT, config=Qwen3_5MoeConfig, model_type="qwen3_5_moe")
+class Qwen3_5MoeForConditionalGeneration(Qwen3VLForConditionalGeneration):
+    pass

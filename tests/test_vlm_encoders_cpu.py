@@ -1,5 +1,6 @@
 """LLaVA (CLIP tower + projector + Llama), the SigLIP tower and RoBERTa against Hugging Face on CPU."""
 
+import pytest
 import torch
 import transformers
 
@@ -385,3 +386,41 @@ def test_glm4v_moe_matches_hf():
         a = m(input_ids=ids, pixel_values=pix, image_grid_thw=grid).logits
         b = hf(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=(ids == 127).long()).logits
     assert (a - b).abs().max() < 3e-4, (a - b).abs().max()
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_qwen3_5_hybrid_vlm_matches_hf(moe):
+    from easydel_b200.modules.qwen3_vl import (Qwen3_5Config, Qwen3_5ForConditionalGeneration, Qwen3_5MoeConfig,
+                                               Qwen3_5MoeForConditionalGeneration)
+    from easydel_b200.utils.parameters_transformation import _adapt_to_hf_module_names
+
+    V = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=4, in_channels=3, patch_size=7,
+             spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=32, num_position_embeddings=36)
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=4, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=16, linear_num_value_heads=4, linear_num_key_heads=2,
+             linear_key_head_dim=8, linear_value_head_dim=16,
+             layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"],
+             rope_parameters=dict(rope_type="default", rope_theta=1e6, partial_rotary_factor=0.5,
+                                  mrope_section=[2, 1, 1], mrope_interleaved=True))
+    if moe:
+        T.update(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=24, shared_expert_intermediate_size=48)
+    ours_cfg, ours_cls = (Qwen3_5MoeConfig, Qwen3_5MoeForConditionalGeneration) if moe else \
+        (Qwen3_5Config, Qwen3_5ForConditionalGeneration)
+    hf_cfg_cls, hf_cls = (transformers.Qwen3_5MoeConfig, transformers.Qwen3_5MoeForConditionalGeneration) if moe \
+        else (transformers.Qwen3_5Config, transformers.Qwen3_5ForConditionalGeneration)
+    torch.manual_seed(0)
+    hf = hf_cls(hf_cfg_cls(vision_config=dict(V), text_config=dict(T), image_token_id=127, video_token_id=126,
+                           vision_start_token_id=125)).float().eval()
+    m = ours_cls(ours_cfg(vision_config=dict(V), text_config=dict(T), image_token_id=127), dtype=torch.float32,
+                 param_dtype=torch.float32).eval()
+    m.load_state_dict(hf_to_internal(m, hf.state_dict()))
+    grid = torch.tensor([[1, 4, 4]])
+    pix = torch.randn(16, 3 * 2 * 7 * 7)
+    ids = torch.randint(0, 120, (1, 14))
+    ids[0, 3:7] = 127
+    with torch.no_grad():
+        a = m(input_ids=ids, pixel_values=pix, image_grid_thw=grid).logits
+        b = hf(input_ids=ids, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=(ids == 127).long()).logits
+    assert (a - b).abs().max() < 3e-4, (a - b).abs().max()
+    sd = _adapt_to_hf_module_names(internal_to_hf(m), hf.state_dict())
+    assert set(sd) == set(hf.state_dict())
