@@ -187,5 +187,7 @@ class MLAttention(nn.Module):
             o = R.attention(qf, k, v, causal=True, scale=self.scale, segment_ids=kv_seg[:, Tk - T:],
                             kv_segment_ids=kv_seg)
         else:
-            o = R.attention(qf, k, v, causal=True, scale=self.scale, segment_ids=segment_ids)
+            # 192-wide keys with 128-wide values are outside the flash kernels: the dispatcher picks the fused
+            # library attention for them on a GPU and the dense form on CPU
+            o = F.attention(qf, k, v, causal=True, scale=self.scale, segment_ids=segment_ids)
         return self.o_proj(o.reshape(B, T, self.H * self.vd).to(hidden.dtype))

@@ -385,6 +385,41 @@ def linear_token_logprob(h, w, labels, *, bias=None, ignore_index: int = -100, t
 
 
 # ---------------------------------------------------------------------------- attention
+def _library_attention(q, k, v, causal, scale, segment_ids, sliding_window, softcap, sinks):
+    """Shapes outside the flash kernels (head_dim above 128, value width different from the key width, fp32 / fp16
+    inputs): the fused attention of the tensor library with an explicit mask; logit caps and sinks, which it has no
+    slot for, use the dense fp32 form."""
+    if (softcap and softcap > 0) or sinks is not None:
+        return R.attention(q, k, v, causal=causal, scale=scale, segment_ids=segment_ids,
+                           sliding_window=sliding_window, softcap=softcap, sinks=sinks)
+    B, Tq, Hq, _ = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    mask, dead = None, None
+    windowed = sliding_window is not None and sliding_window > 0
+    if segment_ids is not None or windowed or (causal and Tq != Tk):
+        qpos = torch.arange(Tq, device=q.device)[:, None] + (Tk - Tq)
+        kpos = torch.arange(Tk, device=q.device)[None, :]
+        m = torch.ones(Tq, Tk, dtype=torch.bool, device=q.device)
+        if causal:
+            m &= kpos <= qpos
+        if windowed:
+            m &= kpos > qpos - sliding_window
+        mask = m[None, None]
+        if segment_ids is not None:
+            seg = segment_ids
+            mask = mask & (seg[:, None, :, None] == seg[:, None, None, :]) & (seg[:, None, None, :] != 0)
+            dead = ~mask.any(-1, keepdim=True)              # padding queries: give them one key, zero the row after
+            mask = mask | (dead & (kpos == 0)[None, None])
+    if Hq != Hkv:
+        k, v = k.repeat_interleave(Hq // Hkv, dim=2), v.repeat_interleave(Hq // Hkv, dim=2)
+    o = torch.nn.functional.scaled_dot_product_attention(
+        q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask,
+        is_causal=causal and mask is None, scale=scale).transpose(1, 2)
+    if dead is not None:
+        o = o.masked_fill(dead.transpose(1, 2), 0.0)
+    return o
+
+
 def attention(q, k, v, *, causal: bool = True, scale: float | None = None, segment_ids=None,
               sliding_window: int | None = None, softcap: float = 0.0, sinks=None, cu_seqlens=None):
     """Softmax attention. q ``[B,T,Hq,D]``, k/v ``[B,T,Hkv,D]`` -> ``[B,T,Hq,D]``.
@@ -394,8 +429,18 @@ def attention(q, k, v, *, causal: bool = True, scale: float | None = None, segme
     if _lib.use_kernels(q):
         from .attention import flash_attention
 
-        return flash_attention(q, k, v, causal=causal, scale=scale, segment_ids=segment_ids,
-                               sliding_window=sliding_window, softcap=softcap, sinks=sinks)
+        D = q.shape[-1]
+        if q.dtype == k.dtype == v.dtype == torch.bfloat16 and v.shape[-1] == D and D <= 128:
+            if D not in (64, 128):
+                # zero columns change neither the scores nor the kept output columns
+                pad = (64 if D < 64 else 128) - D
+                scale = scale if scale is not None else 1.0 / math.sqrt(D)
+                q, k, v = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
+                return flash_attention(q, k, v, causal=causal, scale=scale, segment_ids=segment_ids,
+                                       sliding_window=sliding_window, softcap=softcap, sinks=sinks)[..., :D]
+            return flash_attention(q, k, v, causal=causal, scale=scale, segment_ids=segment_ids,
+                                   sliding_window=sliding_window, softcap=softcap, sinks=sinks)
+        return _library_attention(q, k, v, causal, scale, segment_ids, sliding_window, softcap, sinks)
     return R.attention(q, k, v, causal=causal, scale=scale, segment_ids=segment_ids, sliding_window=sliding_window,
                        softcap=softcap, sinks=sinks)
 
