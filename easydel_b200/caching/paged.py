@@ -37,14 +37,16 @@ class PagedBatchMeta:
 
 class PagedKVCache:
     def __init__(self, num_layers: int, num_pages: int, num_kv_heads: int, head_dim: int, dtype=torch.bfloat16,
-                 device=None, page_size: int = PAGE_SIZE):
+                 device=None, page_size: int = PAGE_SIZE, latent: bool = False):
         if page_size != PAGE_SIZE:
             raise ValueError(f"the paged attention kernels use pages of {PAGE_SIZE} tokens, got {page_size}")
         self.num_layers, self.num_pages, self.page_size = num_layers, num_pages, page_size
         self.num_kv_heads, self.head_dim, self.dtype = num_kv_heads, head_dim, dtype
         shape = (num_layers, num_pages, page_size, num_kv_heads, head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        # latent attention stores one row per token (compressed keys/values + the shared rotary key): no value pool
+        self.latent = latent
+        self.v = self.k if latent else torch.zeros(shape, dtype=dtype, device=device)
 
     @staticmethod
     def bytes_per_page(num_layers: int, num_kv_heads: int, head_dim: int, dtype=torch.bfloat16,
@@ -60,8 +62,12 @@ class PagedKVCache:
         dtype = dtype or getattr(model.config, "kvdtype", None) or model.dtype
         tp_size = getattr(model.config.mesh, "tp", 1)
         kvh = max(1, spec.num_kv_heads // tp_size)
+        latent = getattr(spec, "mla", None) is not None
+        head_dim = spec.head_dim
+        if latent:
+            kvh, head_dim = 1, spec.mla["kv_lora_rank"] + spec.mla["qk_rope_head_dim"]
         if num_pages is None:
-            per_page = cls.bytes_per_page(spec.num_layers, kvh, spec.head_dim, dtype, page_size)
+            per_page = cls.bytes_per_page(spec.num_layers, kvh, head_dim, dtype, page_size) // (2 if latent else 1)
             if torch.device(device).type == "cuda":
                 free, total = torch.cuda.mem_get_info(device)
                 budget = max(0, int(free - (1.0 - hbm_utilization) * total))
@@ -71,9 +77,11 @@ class PagedKVCache:
         if max_pages is not None:
             # never more than max_num_seqs * pages-per-sequence would need
             num_pages = min(int(num_pages), int(max_pages))
-        return cls(spec.num_layers, int(num_pages), kvh, spec.head_dim, dtype, device, page_size)
+        return cls(spec.num_layers, int(num_pages), kvh, head_dim, dtype, device, page_size, latent=latent)
 
-    def view(self, layer: int) -> "PagedLayerView":
+    def view(self, layer: int):
+        if self.latent:
+            return PagedLatentView(self.k[layer])
         return PagedLayerView(self.k[layer], self.v[layer])
 
     def seq_len(self) -> int:  # the engine passes explicit positions
@@ -100,3 +108,56 @@ class PagedLayerView:
                               scale=attn.scale, causal=True, window=attn.sliding_window or 0, softcap=attn.softcap,
                               sinks=attn.sinks)
         return o[None]
+
+
+class PagedLatentView:
+    """Pages of latent-attention rows ``[compressed kv | rotary key]`` (one per token, shared by all heads).
+
+    Attention runs in the absorbed form: the key up-projection is folded into the query and the value up-projection
+    is applied after the weighted sum, so the cache is read as it is stored and never expanded per head. The pages
+    of the scheduled sequences are gathered through the page table; the products are batched matrix multiplies.
+    """
+
+    def __init__(self, pages: torch.Tensor):
+        self.pages = pages                  # [P, page, 1, kv_lora_rank + rope_dim]
+
+    def attend_latent(self, mla, q_nope, q_rope, latent, k_rope, meta: PagedBatchMeta):
+        """q_nope ``[1,T,H,nope]``, q_rope ``[1,T,H,rope]`` (rotated), latent ``[1,T,L]`` (normalised), k_rope
+        ``[1,T,rope]`` (rotated) -> ``[1,T,H,v_head_dim]``."""
+        T, H, L = q_nope.shape[1], q_nope.shape[2], latent.shape[-1]
+        new = torch.cat([latent[0], k_rope[0]], -1).to(self.pages.dtype)[:, None, :].contiguous()
+        S.kv_append(new, new, self.pages, self.pages, meta.slot_mapping)
+        w = mla.kv_b_proj.weight.view(H, mla.nope + mla.vd, L)
+        w_uk, w_uv = w[:, : mla.nope], w[:, mla.nope:]
+        q = torch.cat([torch.einsum("thn,hnl->thl", q_nope[0], w_uk.to(q_nope.dtype)), q_rope[0]], -1)   # [T,H,L+R]
+        B = meta.num_seqs
+        table = meta.page_table[:B].long().clamp_min(0)
+        kv = self.pages[table].reshape(B, -1, self.pages.shape[-1])                                       # [B,Tk,L+R]
+        Tk = kv.shape[1]
+        kv_lens = meta.kv_lens[:B].long()
+        if meta.max_q == 1 and T >= B:        # decode: row b is sequence b (rows past B are padding)
+            qb = q[:B, None]
+            qpos = (kv_lens - 1)[:, None]
+            lens = None
+        else:
+            cu = meta.cu_q.tolist()
+            lens = [cu[b + 1] - cu[b] for b in range(B)]
+            qb = q.new_zeros(B, meta.max_q, H, q.shape[-1])
+            for b, n in enumerate(lens):
+                qb[b, :n] = q[cu[b]:cu[b + 1]]
+            qpos = kv_lens[:, None] - torch.tensor(lens, device=q.device)[:, None] + \
+                torch.arange(meta.max_q, device=q.device)[None]
+        kpos = torch.arange(Tk, device=q.device)
+        mask = (kpos[None, None, :] <= qpos[:, :, None]) & (kpos[None, None, :] < kv_lens[:, None, None])
+        s = torch.einsum("bqhw,bkw->bhqk", qb, kv.to(qb.dtype)).float() * mla.scale
+        s = s.masked_fill(~mask[:, None], float("-inf"))
+        p = torch.nan_to_num(torch.softmax(s, -1), nan=0.0).to(qb.dtype)
+        o = torch.einsum("bhqk,bkl->bqhl", p, kv[..., :L].to(qb.dtype))
+        o = torch.einsum("bqhl,hvl->bqhv", o, w_uv.to(qb.dtype))                                           # [B,Tq,H,vd]
+        out = q.new_zeros(T, H, mla.vd)
+        if lens is None:
+            out[:B] = o[:, 0]
+        else:
+            for b, n in enumerate(lens):
+                out[cu[b]:cu[b + 1]] = o[b, :n]
+        return out[None]

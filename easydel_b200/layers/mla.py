@@ -168,6 +168,11 @@ class MLAttention(nn.Module):
         k_rope = self._rope(ckv[..., self.kv_lora_rank:].reshape(B, T, 1, self.rope_dim), positions)[:, :, 0]
         q_rope = self._rope(q_rope, positions)
         kv_seg = None
+        if cache_view is not None and hasattr(cache_view, "attend_latent"):      # paged serving cache
+            if self.indexer_cfg is not None:
+                raise NotImplementedError("sparse-index latent attention is not wired into the paged serving cache")
+            o = cache_view.attend_latent(self, q_nope, q_rope, latent, k_rope, attn_meta)
+            return self.o_proj(o.reshape(B, T, self.H * self.vd).to(hidden.dtype))
         if cache_view is not None:
             if not hasattr(cache_view, "update"):
                 raise TypeError("latent attention needs an MLACache (model.init_cache builds one)")

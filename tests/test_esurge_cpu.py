@@ -120,3 +120,25 @@ def test_engine_profiling_and_monitoring_hooks(tmp_path):
     info = eng.start_monitoring(prometheus_port=0)
     assert "prometheus" in info
     eng.stop_monitoring()
+
+
+def test_latent_attention_models_are_served_from_latent_pages():
+    """DeepSeek-style latent attention: the paged cache holds one compressed row per token and the engine's greedy
+    continuations equal ``model.generate`` for prompts of different lengths scheduled together."""
+    from easydel_b200.infra.factory import TaskType, registry
+
+    torch.manual_seed(0)
+    cfg = registry.get_config("deepseek_v3")(
+        vocab_size=128, hidden_size=48, intermediate_size=64, moe_intermediate_size=32, num_hidden_layers=2,
+        num_attention_heads=4, num_key_value_heads=4, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=8,
+        qk_rope_head_dim=8, v_head_dim=8, n_routed_experts=4, n_shared_experts=1, num_experts_per_tok=2, n_group=2,
+        topk_group=1, first_k_dense_replace=1, max_position_embeddings=512)
+    model = registry.get_module_registration(TaskType.CAUSAL_LM, "deepseek_v3").module(cfg, dtype=torch.float32).eval()
+    eng = eSurge(model, max_model_len=256, max_num_seqs=4, num_pages=8)
+    assert eng.runner.cache.latent and eng.runner.cache.k.shape[-2:] == (1, 24)
+    assert eng.runner.cache.v is eng.runner.cache.k
+    prompts = [[5, 9, 2, 77, 31], list(range(3, 40)), [1, 2]]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=6, temperature=0.0))
+    for p, o in zip(prompts, outs):
+        want = model.generate(torch.tensor([p]), max_new_tokens=6).sequences[0, len(p):].tolist()
+        assert o.outputs[0].token_ids == want
