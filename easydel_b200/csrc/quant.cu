@@ -15,6 +15,8 @@
 // easydel/layers/linears/_linear_quantized.py:1030-1108.
 #include "common.cuh"
 
+#include <stdlib.h>
+
 namespace edl {
 namespace {
 
@@ -192,6 +194,230 @@ qgemv_kernel(const float* __restrict__ x, long long ldx, const uint8_t* __restri
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Staged form of the same product. The kernel above keeps at most QG_UNROLL * QG_ROWS 4-byte loads per lane in
+// flight, which leaves it bound by global-load latency well below the copy bandwidth. Here the codes (and their
+// scales and zero points) of QG_ROWS rows x QS chunk words travel into shared memory with bulk asynchronous copies
+// that complete on an mbarrier, two slots per warp, so every SM keeps ~100 KB of weight bytes in flight while the
+// lanes dequantise the slot that has landed. Every warp is its own producer and consumer: lane 0 issues the copies
+// of item t + 2 into the slot the warp has just finished reading, so no cross-warp hand-off exists. All waits are
+// bounded; a warp that gives up records EDL_TIMEOUT_PRODUCER, and every warp waits (bounded) for its own copies
+// still in flight before the CTA leaves.
+// One CTA per SM; M <= 4 runs 16 warps with 1 KB row chunks, M > 4 runs 8 warps with 2 KB row chunks.
+constexpr int QS_SLOTS = 2;
+constexpr int QS_X_CHUNK_WORDS = 128;   // row chunk when the activations also live in shared memory
+constexpr int QS_X_MAX_BYTES = 64 * 1024;
+template <int M> struct QsShape {
+  static constexpr int THREADS = M <= 4 ? 512 : 256;
+  static constexpr int CHUNK_WORDS = M <= 4 ? 256 : 512;
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+template <int M, int BITS, bool HAS_ZERO, bool X_SMEM>
+__global__ void __launch_bounds__(QsShape<M>::THREADS, 1)
+qgemv_staged_kernel(const float* __restrict__ x, long long ldx, const uint8_t* __restrict__ codes,
+                    const __nv_bfloat16* __restrict__ scales, const __nv_bfloat16* __restrict__ zeros,
+                    const float* __restrict__ lut, int N, int K, int group, __nv_bfloat16* __restrict__ out,
+                    long long ldo, const __nv_bfloat16* __restrict__ bias, int sc_pitch, int* status) {
+  constexpr int WPW = 32 / BITS;
+  constexpr int THREADS = QsShape<M>::THREADS;
+  constexpr int CW = X_SMEM ? QS_X_CHUNK_WORDS : QsShape<M>::CHUNK_WORDS;
+  constexpr int WARPS = THREADS / 32;
+  constexpr int TABLE_BYTES = 256 * 32 * (BITS == 4 ? 8 : 4);
+  constexpr int PLANES = BITS == 4 ? 2 : 1;   // float4 pieces of activations per code word
+  extern __shared__ __align__(128) unsigned char s_raw[];
+  float2* s_pair = reinterpret_cast<float2*>(s_raw);
+  float* s_val = reinterpret_cast<float*>(s_raw);
+  // [table][WARPS * QS_SLOTS mbarriers][abort word, padded to 128 bytes][activations, if staged][ring]
+  uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_raw + TABLE_BYTES);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_raw + TABLE_BYTES + WARPS * QS_SLOTS * 8);
+  float4* s_x = reinterpret_cast<float4*>(s_raw + TABLE_BYTES + WARPS * QS_SLOTS * 8 + 128);
+  unsigned char* s_ring = reinterpret_cast<unsigned char*>(s_x) + (X_SMEM ? (size_t)M * K * 4 : 0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // slot = QG_ROWS code rows of CW words, then QG_ROWS scale rows of sc_pitch bytes, then the zero points
+  const int slot_bytes = QG_ROWS * (CW * 4 + sc_pitch * (HAS_ZERO ? 2 : 1));
+  for (int i = threadIdx.x; i < 256 * 32; i += THREADS) {
+    const int e = i >> 5;
+    if (BITS == 4) s_pair[i] = make_float2(lut[e & 15], lut[e >> 4]);
+    else s_val[i] = lut[e];
+  }
+  const int nwords = K / WPW;
+  if (X_SMEM) {
+    // piece p of word w of row m sits at ((m * PLANES + p) * nwords + w): the lanes of a warp read consecutive 16-byte
+    // pieces, so every activation load is conflict-free
+    for (int i = threadIdx.x; i < M * PLANES * nwords; i += THREADS) {
+      const int w = i % nwords, mp = i / nwords;
+      const int m = mp / PLANES, pp = mp - m * PLANES;
+      s_x[i] = __ldg(reinterpret_cast<const float4*>(x + m * ldx + w * WPW + pp * 4));
+    }
+  }
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    for (int i = 0; i < WARPS * QS_SLOTS; ++i) mbar_init(smem_u32(s_bar + i), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  const int groups = K / group;
+  const long long row_bytes = (long long)nwords * 4;
+  const int chunks = (nwords + CW - 1) / CW;
+  const int gpc = CW * WPW / group;                     // groups per full chunk
+  const int n_row_groups = (N + QG_ROWS - 1) / QG_ROWS;
+  const int first_rg = blockIdx.x * WARPS + warp, rg_stride = gridDim.x * WARPS;
+  const int my_rgs = first_rg < n_row_groups ? (n_row_groups - first_rg + rg_stride - 1) / rg_stride : 0;
+  const int items = my_rgs * chunks;
+  const uint32_t tab = smem_u32(s_raw) + lane * (BITS == 4 ? 8 : 4);
+  unsigned char* my_ring = s_ring + (size_t)warp * QS_SLOTS * slot_bytes;
+  const uint32_t my_bar = smem_u32(s_bar + warp * QS_SLOTS);
+
+  auto issue = [&](int t) {                             // lane 0 only
+    const int j = t / chunks, c = t - j * chunks;
+    const int n0 = (first_rg + j * rg_stride) * QG_ROWS;
+    const int rows = min(QG_ROWS, N - n0);
+    const int cw = min(CW, nwords - c * CW);
+    const uint32_t cb = cw * 4, sb = (cw * WPW / group) * 2;
+    const int slot = t % QS_SLOTS;
+    const uint32_t bar = my_bar + slot * 8;
+    const uint32_t base = smem_u32(my_ring + (size_t)slot * slot_bytes);
+    mbar_expect_tx(bar, rows * (cb + sb * (HAS_ZERO ? 2 : 1)));
+    for (int r = 0; r < rows; ++r) {
+      bulk_load(base + r * CW * 4, codes + (n0 + r) * row_bytes + (long long)c * CW * 4, cb, bar);
+      bulk_load(base + QG_ROWS * CW * 4 + r * sc_pitch, scales + (long long)(n0 + r) * groups + c * gpc, sb, bar);
+      if (HAS_ZERO)
+        bulk_load(base + QG_ROWS * (CW * 4 + sc_pitch) + r * sc_pitch, zeros + (long long)(n0 + r) * groups + c * gpc,
+                  sb, bar);
+    }
+  };
+
+  int issued = 0;
+  if (lane == 0)
+    for (; issued < items && issued < QS_SLOTS; ++issued) issue(issued);
+  issued = __shfl_sync(0xffffffffu, issued, 0);
+
+  float2 acc[M][QG_ROWS];
+  float zacc[HAS_ZERO ? M : 1][HAS_ZERO ? QG_ROWS : 1];
+  int t = 0;
+  bool ok = true;
+  for (; t < items; ++t) {
+    const int j = t / chunks, c = t - j * chunks;
+    const int n0 = (first_rg + j * rg_stride) * QG_ROWS;
+    const int slot = t % QS_SLOTS;
+    if (c == 0) {
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int r = 0; r < QG_ROWS; ++r) {
+          acc[m][r] = make_float2(0.f, 0.f);
+          if (HAS_ZERO) zacc[m][r] = 0.f;
+        }
+    }
+    ok = mbar_wait(my_bar + slot * 8, (t / QS_SLOTS) & 1, s_abort, status, EDL_TIMEOUT_PRODUCER);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    const unsigned char* sl = my_ring + (size_t)slot * slot_bytes;
+    const uint32_t* s_words = reinterpret_cast<const uint32_t*>(sl);
+    const __nv_bfloat16* s_sc = reinterpret_cast<const __nv_bfloat16*>(sl + QG_ROWS * CW * 4);
+    const __nv_bfloat16* s_zr = reinterpret_cast<const __nv_bfloat16*>(sl + QG_ROWS * (CW * 4 + sc_pitch));
+    const int cw = min(CW, nwords - c * CW);
+    const int rows = min(QG_ROWS, N - n0);
+#pragma unroll 2
+    for (int wi = lane; wi < cw; wi += 32) {
+      const int k0 = (c * CW + wi) * WPW;
+      const int gl = wi * WPW / group;                 // group inside the chunk
+      float2 xv[M][4];
+      float xsum[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const float4 a = X_SMEM ? s_x[(m * PLANES) * nwords + c * CW + wi]
+                                : __ldg(reinterpret_cast<const float4*>(x + m * ldx + k0));
+        xv[m][0] = make_float2(a.x, a.y);
+        xv[m][1] = make_float2(a.z, a.w);
+        if (BITS == 4) {
+          const float4 b = X_SMEM ? s_x[(m * PLANES + 1) * nwords + c * CW + wi]
+                                  : __ldg(reinterpret_cast<const float4*>(x + m * ldx + k0 + 4));
+          xv[m][2] = make_float2(b.x, b.y);
+          xv[m][3] = make_float2(b.z, b.w);
+        }
+        if (HAS_ZERO) {
+          float s = (a.x + a.y) + (a.z + a.w);
+          if (BITS == 4) s += (xv[m][2].x + xv[m][2].y) + (xv[m][3].x + xv[m][3].y);
+          xsum[m] = s;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < QG_ROWS; ++r) {
+        const bool live = r < rows;
+        const uint32_t word = live ? s_words[r * CW + wi] : 0u;
+        float2 part[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) part[m] = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int bb = 0; bb < 4; ++bb) {
+          if (BITS == 4) {
+            const uint32_t addr = tab + __byte_perm(word, 0u, 0x4404u | (bb << 4));
+            float2 wv;
+            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(wv.x), "=f"(wv.y) : "r"(addr));
+#pragma unroll
+            for (int m = 0; m < M; ++m) part[m] = __ffma2_rn(wv, xv[m][bb], part[m]);
+          } else {
+            const uint32_t addr = tab + (__byte_perm(word, 0u, 0x4404u | (bb << 4)) >> 1);
+            float wv;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(wv) : "r"(addr));
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+              const float xs = (bb & 1) ? xv[m][bb >> 1].y : xv[m][bb >> 1].x;
+              part[m].x = fmaf(wv, xs, part[m].x);
+            }
+          }
+        }
+        const float sc = live ? __bfloat162float(s_sc[r * (sc_pitch / 2) + gl]) : 0.f;
+        const float2 sc2 = make_float2(sc, sc);
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[m][r] = __ffma2_rn(sc2, part[m], acc[m][r]);
+        if (HAS_ZERO) {
+          const float zr = live ? __bfloat162float(s_zr[r * (sc_pitch / 2) + gl]) : 0.f;
+#pragma unroll
+          for (int m = 0; m < M; ++m) zacc[m][r] = fmaf(zr, xsum[m], zacc[m][r]);
+        }
+      }
+    }
+    // the slot is free once every lane has read it; the next copy into it is an async-proxy write
+    __syncwarp();
+    if (lane == 0 && t + QS_SLOTS < items) {
+      fence_proxy_async_smem();
+      issue(t + QS_SLOTS);
+    }
+    if (c == chunks - 1) {
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int r = 0; r < QG_ROWS; ++r) {
+          float s = warp_sum(acc[m][r].x + acc[m][r].y + (HAS_ZERO ? zacc[m][r] : 0.f));
+          if (lane == 0 && n0 + r < N) {
+            if (bias) s += __bfloat162float(bias[n0 + r]);
+            out[m * ldo + n0 + r] = __float2bfloat16(s);
+          }
+        }
+    }
+  }
+  if (!ok && lane == 0) {
+    // copies issued for items t .. min(items, t + QS_SLOTS) - 1 may still land: give each a short, bounded wait
+    const int last = min(items, t + QS_SLOTS);
+    for (int u = t; u < last; ++u) {
+      const uint32_t bar = my_bar + (u % QS_SLOTS) * 8;
+      const long long t0 = clock64();
+      while (!mbar_try_wait(bar, (u / QS_SLOTS) & 1) && clock64() - t0 < 20000000LL) {
+      }
+    }
+  }
+}
+
 }  // namespace
 }  // namespace edl
 
@@ -223,18 +449,78 @@ EDL_HOST_API int edl_dequant_bf16(const void* codes, const void* scales, const v
 // number of weights in one 16-byte code vector (32 for 4-bit, 16 for 8-bit).
 EDL_HOST_API int edl_qgemv(const void* x, long long ldx, const void* codes, const void* scales, const void* zeros,
                            const float* lut, int bits, int M, int N, int K, int group, void* out, long long ldo,
-                           const void* bias, void* stream) {
+                           const void* bias, int* status, void* stream) {
   if (check_quant_args("edl_qgemv", bits, N, K, group)) return -1;
   const int per16 = bits == 4 ? 32 : 16;
   if (M < 1 || M > QG_MAX_M || (ldx & 3) || group % per16) {
     set_last_error("edl_qgemv: M must be in [1, %d], ldx a multiple of 4 and group a multiple of %d", QG_MAX_M, per16);
     return -1;
   }
+  cudaStream_t s = (cudaStream_t)stream;
+  // Staged form when the bulk copies can be issued: 16-byte aligned sources and whole 16-byte scale pieces. Small
+  // activation blocks (M * K * 4 <= 64 KB) are staged in shared memory as well, with a shorter row chunk.
+  if (status && !getenv("EDL_QGEMV_DIRECT")) {
+    const int wpw = 32 / bits, groups = K / group;
+    const int threads = M <= 4 ? 512 : 256, warps = threads / 32;
+    const int table = 256 * 32 * (bits == 4 ? 8 : 4);
+    const uintptr_t align = (uintptr_t)codes | (uintptr_t)scales | (uintptr_t)(zeros ? zeros : codes);
+    auto plan = [&](int cw, long long x_bytes, int* sc_pitch) -> long long {
+      const int chunk_w = cw * wpw;
+      const int gpc = chunk_w % group == 0 ? chunk_w / group : 0;
+      if (gpc == 0 || gpc % 8 || groups % 8 || (align & 15)) return -1;
+      *sc_pitch = gpc * 2;
+      return table + warps * QS_SLOTS * 8 + 128 + x_bytes +
+             (long long)warps * QS_SLOTS * QG_ROWS * (cw * 4 + *sc_pitch * (zeros ? 2 : 1));
+    };
+    int sc_pitch = 0;
+    const long long x_bytes = (long long)M * K * 4;
+    bool x_smem = x_bytes <= QS_X_MAX_BYTES && !getenv("EDL_QGEMV_X_GLOBAL");
+    long long smem_staged = x_smem ? plan(QS_X_CHUNK_WORDS, x_bytes, &sc_pitch) : -1;
+    if (smem_staged < 0 || smem_staged > 227 * 1024) {
+      x_smem = false;
+      smem_staged = plan(M <= 4 ? 256 : 512, 0, &sc_pitch);
+    }
+    if (smem_staged > 0 && smem_staged <= 227 * 1024) {
+      const int rows_per_cta = warps * QG_ROWS;
+      int blocks = (N + rows_per_cta - 1) / rows_per_cta;
+      if (blocks > sm_count()) blocks = sm_count();
+#define EDL_QGEMV_STAGED(MM, BB, ZZ, XX)                                                                             \
+  do {                                                                                                               \
+    auto kern = qgemv_staged_kernel<MM, BB, ZZ, XX>;                                                                 \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_staged);                       \
+    kern<<<blocks, threads, (size_t)smem_staged, s>>>(                                                               \
+        (const float*)x, ldx, (const uint8_t*)codes, (const __nv_bfloat16*)scales, (const __nv_bfloat16*)zeros, lut, \
+        N, K, group, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)bias, sc_pitch, status);                        \
+  } while (0)
+#define EDL_QGEMV_STAGED_Z(MM, BB, ZZ)                                                                               \
+  do {                                                                                                               \
+    if (x_smem) EDL_QGEMV_STAGED(MM, BB, ZZ, true); else EDL_QGEMV_STAGED(MM, BB, ZZ, false);                        \
+  } while (0)
+#define EDL_QGEMV_STAGED_CASE(MM)                                                                                    \
+  case MM:                                                                                                           \
+    if (bits == 4) { if (zeros) EDL_QGEMV_STAGED_Z(MM, 4, true); else EDL_QGEMV_STAGED_Z(MM, 4, false); }            \
+    else { if (zeros) EDL_QGEMV_STAGED_Z(MM, 8, true); else EDL_QGEMV_STAGED_Z(MM, 8, false); }                      \
+    break;
+      switch (M) {
+        EDL_QGEMV_STAGED_CASE(1)
+        EDL_QGEMV_STAGED_CASE(2)
+        EDL_QGEMV_STAGED_CASE(3)
+        EDL_QGEMV_STAGED_CASE(4)
+        EDL_QGEMV_STAGED_CASE(5)
+        EDL_QGEMV_STAGED_CASE(6)
+        EDL_QGEMV_STAGED_CASE(7)
+        EDL_QGEMV_STAGED_CASE(8)
+      }
+#undef EDL_QGEMV_STAGED
+#undef EDL_QGEMV_STAGED_Z
+#undef EDL_QGEMV_STAGED_CASE
+      return check_cuda(cudaGetLastError(), "qgemv staged launch");
+    }
+  }
   const int rows_per_cta = (QG_THREADS / 32) * QG_ROWS;
   int blocks = (N + rows_per_cta - 1) / rows_per_cta;
   const int cap = sm_count() * 2;   // persistent: warps loop over row groups
   if (blocks > cap) blocks = cap;
-  cudaStream_t s = (cudaStream_t)stream;
   const int smem = 256 * 32 * (bits == 4 ? 8 : 4);
 #define EDL_QGEMV_LAUNCH(MM, BB, ZZ)                                                                                \
   do {                                                                                                              \
