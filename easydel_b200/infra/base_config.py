@@ -317,6 +317,10 @@ class EasyDeLBaseConfig(PretrainedConfig):
             warnings.warn("`kv_cache_quantization_config` and `use_sharded_kv_caching` can't be used together "
                           "at the moment.", stacklevel=1)
         self._mesh = None
+        rp = kwargs.get("rope_parameters")
+        if isinstance(rp, dict) and rp.get("rope_theta") is not None and "rope_theta" in self.__dict__:
+            # newer checkpoint configs keep the rotary base inside ``rope_parameters`` and have no top-level field
+            self.rope_theta = rp["rope_theta"]
         super().__init__(**kwargs)
 
     # ------------------------------------------------------------------ mesh

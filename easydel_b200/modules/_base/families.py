@@ -33,6 +33,18 @@ def make_config(model_type: str, defaults: dict, post: tp.Callable | None = None
 
     class _Config(EasyDeLBaseConfig):
         def __init__(self, **kw):
+            rp = kw.get("rope_parameters")
+            if isinstance(rp, dict) and "rope_type" in rp or isinstance(rp, dict) and "rope_theta" in rp:
+                # newer checkpoints keep the base frequency, the rotated fraction and the scaling recipe in one
+                # dict; spread it over the fields the specs read unless those were given explicitly
+                rest = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
+                if "rope_theta" in rp:
+                    kw.setdefault("rope_theta", rp["rope_theta"])
+                if "partial_rotary_factor" in rp and "partial_rotary_factor" in defaults:
+                    kw.setdefault("partial_rotary_factor", rp["partial_rotary_factor"])
+                if kw.get("rope_scaling") is None and (rest.get("rope_type", "default") != "default"
+                                                       or rest.get("mrope_section")):
+                    kw["rope_scaling"] = rest
             for k, v in defaults.items():
                 if k in _HF_KEYS:
                     kw.setdefault(k, v)

@@ -142,27 +142,33 @@ class Qwen2VLVisionTransformer(nn.Module):
         return y
 
 
-def mrope_positions(input_ids, image_token_id, grid_thw, merge: int, attention_mask=None):
-    """-> ``[3, B, T]`` positions and the per-row offset ``max(position) + 1 - length`` decoding continues from."""
+def mrope_positions(input_ids, image_token_id, grid_thw, merge: int, attention_mask=None, video_token_id=None,
+                    video_grid_thw=None):
+    """-> ``[3, B, T]`` positions and the per-row offset ``max(position) + 1 - length`` decoding continues from.
+
+    Image and video placeholder runs take their grids from ``grid_thw`` / ``video_grid_thw`` in order of appearance;
+    a video's temporal index advances once per temporal patch."""
     B, T = input_ids.shape
     pos = torch.zeros(3, B, T, dtype=torch.long, device=input_ids.device)
     deltas = []
-    grids = iter(grid_thw.tolist()) if grid_thw is not None else iter(())
+    grids = {image_token_id: iter(grid_thw.tolist()) if grid_thw is not None else iter(())}
+    if video_token_id is not None and video_grid_thw is not None:
+        grids[video_token_id] = iter(video_grid_thw.tolist())
     for b in range(B):
         keep = attention_mask[b].bool() if attention_mask is not None else torch.ones(T, dtype=torch.bool,
                                                                                         device=input_ids.device)
         ids = input_ids[b][keep].tolist()
         chunks, cur, i, n = [], 0, 0, len(ids)
         while i < n:
-            if ids[i] != image_token_id:
+            if ids[i] not in grids:
                 j = i
-                while j < n and ids[j] != image_token_id:
+                while j < n and ids[j] not in grids:
                     j += 1
                 chunks.append(torch.arange(cur, cur + j - i)[None].expand(3, -1))
                 cur += j - i
                 i = j
             else:
-                t, h, w = next(grids)
+                t, h, w = next(grids[ids[i]])
                 gh, gw = h // merge, w // merge
                 ti = torch.arange(t)[:, None, None].expand(t, gh, gw).reshape(-1)
                 hi = torch.arange(gh)[None, :, None].expand(t, gh, gw).reshape(-1)
@@ -178,7 +184,6 @@ def mrope_positions(input_ids, image_token_id, grid_thw, merge: int, attention_m
 
 @register_module(TaskType.IMAGE_TEXT_TO_TEXT, config=Qwen2VLConfig, model_type="qwen2_vl")
 class Qwen2VLForConditionalGeneration(VLMForConditionalGeneration):
-    image_kwargs = ("image_grid_thw",)
     ignored_prefixes = ()
     outer_rules = [("model.visual.", "visual."), ("model.language_model.", "language_model.model."),
                    ("lm_head.", "language_model.lm_head.")]
@@ -207,14 +212,35 @@ class Qwen2VLForConditionalGeneration(VLMForConditionalGeneration):
     def get_image_features(self, pixel_values, image_grid_thw=None, **_):
         return self.visual(pixel_values, image_grid_thw)
 
+    def get_video_features(self, pixel_values_videos, video_grid_thw=None, **_):
+        """Videos go through the same tower: a grid with more than one temporal patch."""
+        return self.get_image_features(pixel_values_videos, image_grid_thw=video_grid_thw)
+
+    def merge_embeddings(self, input_ids, pixel_values=None, image_features=None, pixel_values_videos=None,
+                         video_grid_thw=None, **kw):
+        emb = super().merge_embeddings(input_ids, pixel_values, image_features, **kw)
+        if pixel_values_videos is not None:
+            feats = self.get_video_features(pixel_values_videos, video_grid_thw)
+            mask = input_ids == self.config.video_token_id
+            if int(mask.sum()) != feats.shape[0]:
+                raise ValueError(f"{int(mask.sum())} video placeholder tokens for {feats.shape[0]} video feature rows")
+            emb = emb.clone()
+            emb[mask] = feats.to(emb.dtype)
+        return emb
+
+    image_kwargs = ("image_grid_thw", "pixel_values_videos", "video_grid_thw")
+
     def forward(self, input_ids=None, pixel_values=None, attention_mask=None, position_ids=None, inputs_embeds=None,
-                past_key_values=None, image_grid_thw=None, **kw):
+                past_key_values=None, image_grid_thw=None, pixel_values_videos=None, video_grid_thw=None, **kw):
         first = past_key_values is None or past_key_values.seq_len() == 0
+        if first and pixel_values_videos is not None:
+            kw.update(pixel_values_videos=pixel_values_videos, video_grid_thw=video_grid_thw)
         if position_ids is None and input_ids is not None:
             if first:
                 position_ids, self.rope_deltas = mrope_positions(
                     input_ids, self.config.image_token_id, image_grid_thw if pixel_values is not None else None,
-                    self.config.vision_config.spatial_merge_size, attention_mask)
+                    self.config.vision_config.spatial_merge_size, attention_mask, self.config.video_token_id,
+                    video_grid_thw if pixel_values_videos is not None else None)
             else:       # decoding: all three streams continue from the prompt's last position
                 B, T = input_ids.shape
                 start = past_key_values.seq_len()
@@ -232,5 +258,7 @@ class Qwen2VLForConditionalGeneration(VLMForConditionalGeneration):
             call["position_ids"], _ = mrope_positions(
                 call["input_ids"], self.config.image_token_id,
                 call.get("image_grid_thw") if call.get("pixel_values") is not None else None,
-                self.config.vision_config.spatial_merge_size, call.get("attention_mask"))
+                self.config.vision_config.spatial_merge_size, call.get("attention_mask"), self.config.video_token_id,
+                call.get("video_grid_thw") if call.get("pixel_values_videos") is not None else None)
+        labels = labels.masked_fill(call["input_ids"] == self.config.video_token_id, loss_config.ignore_index)
         return super()._compute_task_loss(labels, loss_config, loss_scale, call, loss_kwargs)

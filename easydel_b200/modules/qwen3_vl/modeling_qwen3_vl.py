@@ -50,7 +50,8 @@ class Qwen3VLConfig(VLMConfig):
             vision_config = dict(vision_config, model_type="qwen3_vl_vision")
         if isinstance(text_config, dict):
             text_config = dict(text_config, model_type=self.text_default)
-            text_config.setdefault("rope_theta", 5000000.0)
+            inner = text_config.get("rope_parameters") or text_config.get("rope_scaling") or {}
+            text_config.setdefault("rope_theta", inner.get("rope_theta", 5000000.0))
             if self.text_default == "qwen3_moe":
                 text_config.setdefault("norm_topk_prob", True)
         kw = self._init_parts(vision_config, text_config, image_token_id, kw)
@@ -177,35 +178,56 @@ class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
     def get_image_features(self, pixel_values, image_grid_thw=None, **_):
         return self.visual(pixel_values, image_grid_thw)[0]
 
-    def _merge(self, input_ids, pixel_values, image_grid_thw):
+    def _merge(self, input_ids, pixel_values, image_grid_thw, pixel_values_videos=None, video_grid_thw=None):
         emb = self.embed_text(input_ids)
-        if pixel_values is None:
+        if pixel_values is None and pixel_values_videos is None:
             return emb, None
-        feats, deep = self.visual(pixel_values, image_grid_thw)
-        mask = input_ids == self.config.image_token_id
-        if int(mask.sum()) != feats.shape[0]:
-            raise ValueError(f"{int(mask.sum())} image placeholder tokens for {feats.shape[0]} image feature rows")
         emb = emb.clone()
-        emb[mask] = feats.to(emb.dtype)
-        stacks = []
-        for d in deep:
-            z = torch.zeros_like(emb)
-            z[mask] = d.to(emb.dtype)
-            stacks.append(z)
+        stacks = None
+        for px, grid, tok, what in ((pixel_values, image_grid_thw, self.config.image_token_id, "image"),
+                                    (pixel_values_videos, video_grid_thw, self.config.video_token_id, "video")):
+            if px is None:
+                continue
+            feats, deep = self.visual(px, grid)
+            mask = input_ids == tok
+            if int(mask.sum()) != feats.shape[0]:
+                raise ValueError(f"{int(mask.sum())} {what} placeholder tokens for {feats.shape[0]} feature rows")
+            emb[mask] = feats.to(emb.dtype)
+            if stacks is None:
+                stacks = [torch.zeros_like(emb) for _ in deep]
+            for z, d in zip(stacks, deep):
+                z[mask] = d.to(emb.dtype)
         return emb, stacks
 
+    @staticmethod
+    def _frame_grids(video_grid_thw):
+        """Every frame group of a video is its own placeholder run (timestamps sit between them): one ``(1, h, w)``
+        grid per temporal patch."""
+        if video_grid_thw is None:
+            return None
+        g = torch.repeat_interleave(video_grid_thw, video_grid_thw[:, 0], dim=0).clone()
+        g[:, 0] = 1
+        return g
+
+    def _positions(self, input_ids, pixel_values, image_grid_thw, pixel_values_videos, video_grid_thw,
+                   attention_mask):
+        return mrope_positions(
+            input_ids, self.config.image_token_id, image_grid_thw if pixel_values is not None else None,
+            self.config.vision_config.spatial_merge_size, attention_mask, self.config.video_token_id,
+            self._frame_grids(video_grid_thw) if pixel_values_videos is not None else None)
+
     def forward(self, input_ids=None, pixel_values=None, attention_mask=None, position_ids=None, inputs_embeds=None,
-                past_key_values=None, image_grid_thw=None, **kw):
+                past_key_values=None, image_grid_thw=None, pixel_values_videos=None, video_grid_thw=None, **kw):
         first = past_key_values is None or past_key_values.seq_len() == 0
         if inputs_embeds is None:
-            inputs_embeds, stacks = self._merge(input_ids, pixel_values if first else None, image_grid_thw)
+            inputs_embeds, stacks = self._merge(input_ids, pixel_values if first else None, image_grid_thw,
+                                                pixel_values_videos if first else None, video_grid_thw)
             if stacks:
                 kw["deepstack_embeds"] = stacks
         if position_ids is None and input_ids is not None:
             if first:
-                position_ids, self.rope_deltas = mrope_positions(
-                    input_ids, self.config.image_token_id, image_grid_thw if pixel_values is not None else None,
-                    self.config.vision_config.spatial_merge_size, attention_mask)
+                position_ids, self.rope_deltas = self._positions(input_ids, pixel_values, image_grid_thw,
+                                                                 pixel_values_videos, video_grid_thw, attention_mask)
             else:
                 B, T = input_ids.shape
                 start = past_key_values.seq_len()
@@ -219,17 +241,16 @@ class Qwen3VLForConditionalGeneration(Qwen2VLForConditionalGeneration):
     def _compute_task_loss(self, labels, loss_config, loss_scale, call, loss_kwargs):
         call = dict(call)
         ids = call.pop("input_ids")
-        grid = call.pop("image_grid_thw", None)
-        pix = call.pop("pixel_values", None)
+        grid, pix = call.pop("image_grid_thw", None), call.pop("pixel_values", None)
+        vgrid, vpix = call.pop("video_grid_thw", None), call.pop("pixel_values_videos", None)
         if call.get("position_ids") is None:
-            call["position_ids"], _ = mrope_positions(ids, self.config.image_token_id, grid if pix is not None else
-                                                      None, self.config.vision_config.spatial_merge_size,
-                                                      call.get("attention_mask"))
-        emb, stacks = self._merge(ids, pix, grid)
+            call["position_ids"], _ = self._positions(ids, pix, grid, vpix, vgrid, call.get("attention_mask"))
+        emb, stacks = self._merge(ids, pix, grid, vpix, vgrid)
         if stacks:
             call["deepstack_embeds"] = stacks
         call["inputs_embeds"] = emb
-        labels = labels.masked_fill(ids == self.config.image_token_id, loss_config.ignore_index)
+        labels = labels.masked_fill((ids == self.config.image_token_id) | (ids == self.config.video_token_id),
+                                    loss_config.ignore_index)
         return self.language_model._compute_task_loss(labels, loss_config, loss_scale, call, loss_kwargs)
 
 

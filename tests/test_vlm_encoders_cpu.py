@@ -424,3 +424,63 @@ def test_qwen3_5_hybrid_vlm_matches_hf(moe):
     assert (a - b).abs().max() < 3e-4, (a - b).abs().max()
     sd = _adapt_to_hf_module_names(internal_to_hf(m), hf.state_dict())
     assert set(sd) == set(hf.state_dict())
+
+
+def test_qwen2_vl_video_matches_hf():
+    from easydel_b200.modules.qwen2_vl import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+
+    V = dict(depth=2, embed_dim=32, hidden_size=32, num_heads=4, in_channels=3, patch_size=7, spatial_merge_size=2,
+             temporal_patch_size=2, mlp_ratio=2)
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, rope_scaling={"type": "mrope", "mrope_section": [1, 1, 2]})
+    torch.manual_seed(0)
+    hf = transformers.Qwen2VLForConditionalGeneration(transformers.Qwen2VLConfig(
+        vision_config=dict(V), text_config=dict(T), image_token_id=127, video_token_id=126,
+        vision_start_token_id=125)).float().eval()
+    m = Qwen2VLForConditionalGeneration(Qwen2VLConfig(vision_config=dict(V), text_config=dict(T), image_token_id=127,
+                                                      video_token_id=126), dtype=torch.float32,
+                                        param_dtype=torch.float32).eval()
+    m.load_state_dict(hf_to_internal(m, hf.state_dict()))
+    vgrid = torch.tensor([[2, 4, 4]])                 # two temporal patches of a 4 x 4 patch grid -> 8 tokens
+    vpix = torch.randn(32, 3 * 2 * 7 * 7)
+    igrid = torch.tensor([[1, 4, 4]])
+    ipix = torch.randn(16, 3 * 2 * 7 * 7)
+    ids = torch.randint(0, 120, (1, 26))
+    ids[0, 2:10] = 126
+    ids[0, 14:18] = 127
+    kw = dict(input_ids=ids, pixel_values=ipix, image_grid_thw=igrid, pixel_values_videos=vpix, video_grid_thw=vgrid)
+    with torch.no_grad():
+        a = m(**kw).logits
+        b = hf(mm_token_type_ids=(ids == 127).long() + 2 * (ids == 126).long(), **kw).logits
+    assert (a - b).abs().max() < 1e-3, (a - b).abs().max()
+    _, met = m.compute_loss(labels=ids, **kw)
+    assert torch.isfinite(met.loss)
+
+
+def test_qwen3_vl_video_frames_match_hf():
+    from easydel_b200.modules.qwen3_vl import Qwen3VLConfig, Qwen3VLForConditionalGeneration
+
+    V = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=4, in_channels=3, patch_size=7,
+             spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=32, num_position_embeddings=36,
+             deepstack_visual_indexes=[0])
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, head_dim=8,
+             rope_scaling={"rope_type": "default", "mrope_section": [2, 1, 1], "mrope_interleaved": True})
+    torch.manual_seed(0)
+    hf = transformers.Qwen3VLForConditionalGeneration(transformers.Qwen3VLConfig(
+        vision_config=dict(V), text_config=dict(T), image_token_id=127, video_token_id=126,
+        vision_start_token_id=125)).float().eval()
+    m = Qwen3VLForConditionalGeneration(Qwen3VLConfig(vision_config=dict(V), text_config=dict(T), image_token_id=127,
+                                                      video_token_id=126), dtype=torch.float32,
+                                        param_dtype=torch.float32).eval()
+    m.load_state_dict(hf_to_internal(m, hf.state_dict()))
+    vgrid = torch.tensor([[2, 4, 4]])
+    vpix = torch.randn(32, 3 * 2 * 7 * 7)
+    ids = torch.randint(0, 120, (1, 20))
+    ids[0, 3:7] = 126          # first frame group
+    ids[0, 9:13] = 126         # second one, after its timestamp text
+    kw = dict(input_ids=ids, pixel_values_videos=vpix, video_grid_thw=vgrid)
+    with torch.no_grad():
+        a = m(**kw).logits
+        b = hf(mm_token_type_ids=2 * (ids == 126).long(), **kw).logits
+    assert (a - b).abs().max() < 1e-3, (a - b).abs().max()
