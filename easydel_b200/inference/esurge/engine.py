@@ -247,16 +247,17 @@ class eSurge:
         return self._mm
 
     def add_request(self, prompt, sampling_params: SamplingParams | None = None, request_id: str | None = None,
-                    priority: int = 0, images: tp.Sequence[tp.Any] | None = None) -> str:
+                    priority: int = 0, images: tp.Sequence[tp.Any] | None = None,
+                    videos: tp.Sequence[tp.Any] | None = None) -> str:
         sp = sampling_params or SamplingParams()
         ids, text = self._tokenize(prompt)
         if not ids:
             raise ValueError("empty prompt")
         mm_embeds, mm_hash = [], None
-        if images:
+        if images or videos:
             if self.multimodal is None:
                 raise ValueError("this model has no vision tower: images cannot be served")
-            ids, mm_embeds, mm_hash = self.multimodal.prepare(ids, images)
+            ids, mm_embeds, mm_hash = self.multimodal.prepare(ids, images, videos)
             if len(ids) > self.max_model_len - self.reserve_tokens:
                 raise ValueError(f"prompt with images has {len(ids)} tokens; max_model_len is {self.max_model_len}")
         limit = self.max_model_len - self.reserve_tokens

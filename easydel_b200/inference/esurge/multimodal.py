@@ -171,6 +171,13 @@ class MultiModalManager:
         ip = getattr(processor, "image_processor", None)
         if ip is not None and getattr(ip, "image_mean", None) is not None:
             self.mean, self.std = tuple(ip.image_mean), tuple(ip.image_std)
+        self.video_token_id = getattr(cfg, "video_token_id", None)
+        # towers that take flattened [temporal x patch x patch] pixel blocks plus a (t, h, w) grid per item
+        vc = self.vision_config
+        self.flat_patch = all(hasattr(vc, k) for k in ("spatial_merge_size", "temporal_patch_size", "patch_size"))
+        if self.flat_patch and resolution_buckets is None:
+            unit = vc.patch_size * vc.spatial_merge_size
+            self.buckets = [(unit * a, unit * b) for a, b in ((8, 8), (12, 8), (8, 12), (16, 16), (24, 16), (16, 24))]
 
     # ------------------------------------------------------------------ pixels
     def resize_to_bucket(self, image):
@@ -217,6 +224,36 @@ class MultiModalManager:
         for img in images:
             pil = self.resize_to_bucket(self._to_pil(img))
             out.append(torch.from_numpy(self._normalize_rgb(np.asarray(pil)).transpose(2, 0, 1).copy()))
+        return out
+
+    def patchify(self, frames: torch.Tensor) -> tuple[torch.Tensor, tuple[int, int, int]]:
+        """``[T, 3, H, W]`` normalised frames -> (``[t * h * w, 3 * tp * P * P]`` rows ordered merge block by merge
+        block, ``(t, h, w)`` grid in patches). A frame count that is not a multiple of the temporal patch repeats the
+        last frame (a still image is one temporal patch of identical frames)."""
+        vc = self.vision_config
+        P, tp, m = vc.patch_size, vc.temporal_patch_size, vc.spatial_merge_size
+        T, C, H, W = frames.shape
+        if T % tp:
+            frames = torch.cat([frames, frames[-1:].expand(tp - T % tp, C, H, W)])
+        gt, gh, gw = frames.shape[0] // tp, H // P, W // P
+        if H % (P * m) or W % (P * m):
+            raise ValueError(f"frame size {H}x{W} is not a multiple of patch {P} x merge {m}")
+        x = frames.reshape(gt, tp, C, gh // m, m, P, gw // m, m, P)
+        x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8).reshape(gt * gh * gw, C * tp * P * P)
+        return x.contiguous(), (gt, gh, gw)
+
+    def process_videos(self, videos: tp.Sequence[tp.Any], max_frames: int = 32) -> list[torch.Tensor]:
+        """Each video (``[T, H, W, 3]`` / ``[T, 3, H, W]`` array, or a list of frames) -> ``[T', 3, H, W]`` fp32:
+        at most ``max_frames`` frames sampled uniformly, all resized to one resolution bucket."""
+        out = []
+        for v in videos:
+            if isinstance(v, torch.Tensor):
+                v = v.detach().cpu().numpy()
+            frames = list(v) if not isinstance(v, (list, tuple)) else list(v)
+            if len(frames) > max_frames:
+                idx = np.linspace(0, len(frames) - 1, max_frames).round().astype(int)
+                frames = [frames[i] for i in idx]
+            out.append(torch.stack(self.process_images(frames)))
         return out
 
     # ------------------------------------------------------------------ messages
@@ -279,6 +316,10 @@ class MultiModalManager:
                 todo.setdefault(f.mm_hash, f)
         dev = next(self.model.parameters()).device
         pending = list(todo.values())
+        if self.flat_patch:
+            for f in pending:
+                self._encode_flat(f, dev)
+            pending = []
         # one tower forward per resolution bucket and chunk of images
         by_shape: dict[tuple, list[MultiModalFeature]] = {}
         for f in pending:
@@ -299,41 +340,90 @@ class MultiModalManager:
             f.clear_pixel_values()
         return feats
 
-    def expand_placeholders(self, token_ids: tp.Sequence[int], feats: list[MultiModalFeature]) -> list[int]:
-        """Repeats the i-th image placeholder once per row of the i-th feature and records where it landed.
+    def _encode_flat(self, f: MultiModalFeature, dev) -> None:
+        frames = f.pixel_values if f.pixel_values.dim() == 4 else f.pixel_values[None]
+        rows, grid = self.patchify(frames)
+        grid_t = torch.tensor([grid], device=dev)
+        fn = self.model.get_video_features if (f.modality == "video" and hasattr(self.model, "get_video_features")) \
+            else self.model.get_image_features
+        key = "video_grid_thw" if fn.__name__ == "get_video_features" else "image_grid_thw"
+        f.embeddings = fn(rows.to(dev, self.model.dtype), **{key: grid_t}).contiguous()
+        if self.cache is not None:
+            self.cache.put(f.mm_hash, f.embeddings)
+
+    @torch.no_grad()
+    def process_videos_to_features(self, videos: tp.Sequence[tp.Any]) -> list[MultiModalFeature]:
+        if not self.flat_patch:
+            raise ValueError("this model's vision tower takes single images; pass the frames as images")
+        dev = next(self.model.parameters()).device
+        feats = []
+        for frames in self.process_videos(videos):
+            f = MultiModalFeature(mm_hash=hash_pixels(frames), modality="video", pixel_values=frames)
+            hit = self.cache.get(f.mm_hash) if self.cache is not None else None
+            if hit is not None:
+                f.embeddings = hit
+            else:
+                self._encode_flat(f, dev)
+            f.clear_pixel_values()
+            feats.append(f)
+        return feats
+
+    def expand_placeholders(self, token_ids: tp.Sequence[int], feats: list[MultiModalFeature],
+                            placeholder_id: int | None = None) -> list[int]:
+        """Repeats the i-th placeholder once per row of the i-th feature and records where it landed.
         A run of placeholders already as long as the feature (a processor expanded it) is left as it is."""
-        ph = self.image_token_id
+        ph = self.image_token_id if placeholder_id is None else placeholder_id
+        return self._expand(token_ids, {ph: feats})
+
+    @staticmethod
+    def _expand(token_ids: tp.Sequence[int], by_token: dict[int, list[MultiModalFeature]]) -> list[int]:
         out: list[int] = []
-        k, i, n = 0, 0, len(token_ids)
+        used = {ph: 0 for ph in by_token}
+        i, n = 0, len(token_ids)
         while i < n:
             t = token_ids[i]
-            if t != ph:
+            if t not in by_token:
                 out.append(t)
                 i += 1
                 continue
+            feats = by_token[t]
             j = i
-            while j < n and token_ids[j] == ph:
+            while j < n and token_ids[j] == t:
                 j += 1
             run = j - i
             while run > 0:
+                k = used[t]
                 if k >= len(feats):
-                    raise ValueError("more image placeholders in the prompt than images in the request")
+                    raise ValueError("more media placeholders in the prompt than media items in the request")
                 rows = feats[k].embeddings.shape[0]
                 take = rows if run >= rows else 1
                 feats[k].placeholder = PlaceholderRange(len(out), rows)
-                out.extend([ph] * rows)
+                out.extend([t] * rows)
                 run -= take
-                k += 1
+                used[t] = k + 1
             i = j
-        if k != len(feats):
-            raise ValueError(f"{len(feats)} images for {k} image placeholders in the prompt")
+        for ph, feats in by_token.items():
+            if used[ph] != len(feats):
+                raise ValueError(f"{len(feats)} media items for {used[ph]} placeholders of token {ph} in the prompt")
         return out
 
-    def prepare(self, token_ids: tp.Sequence[int], images: tp.Sequence[tp.Any]):
-        """-> (expanded token ids, [(offset, embeddings)], extra hash key) for ``eSurge.add_request``."""
-        feats = self.process_images_to_features(images)
-        ids = self.expand_placeholders(list(token_ids), feats)
-        return ids, [(f.placeholder.offset, f.embeddings) for f in feats], tuple(f.mm_hash for f in feats)
+    def prepare(self, token_ids: tp.Sequence[int], images: tp.Sequence[tp.Any] | None = None,
+                videos: tp.Sequence[tp.Any] | None = None):
+        """-> (expanded token ids, [(offset, embeddings)], extra hash key) for ``eSurge.add_request``.
+
+        The engine numbers all tokens of a request consecutively; models whose rotary embedding gives vision tokens
+        grid positions (three position streams) therefore see the text after an image later than in
+        ``model.generate``, which computes the grid positions."""
+        feats = self.process_images_to_features(images) if images else []
+        vfeats = self.process_videos_to_features(videos) if videos else []
+        by_token = {}
+        if feats:
+            by_token[self.image_token_id] = feats
+        if vfeats:
+            by_token[self.video_token_id] = vfeats
+        ids = self._expand(list(token_ids), by_token) if by_token else list(token_ids)
+        allf = sorted(feats + vfeats, key=lambda f: f.placeholder.offset)
+        return ids, [(f.placeholder.offset, f.embeddings) for f in allf], tuple(f.mm_hash for f in allf)
 
     def tokenize_multimodal(self, messages: list[dict], images: tp.Sequence[tp.Any] | None = None, **template_kw):
         if self.tokenizer is None:

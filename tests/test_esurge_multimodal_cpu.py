@@ -90,3 +90,38 @@ def test_engine_serves_images_like_the_model_even_across_prefill_chunks():
     other = eng.generate(prompt, SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True),
                          images=[_image(5), _image(6)])[0]
     assert list(other.outputs[0].token_ids) == _greedy(m, prompt, [_image(5), _image(6)], 6, eng.multimodal)
+
+
+def test_flat_patch_tower_images_and_videos_expand_in_one_pass():
+    """Qwen-VL style towers: the manager cuts frames into merge-block-ordered patch rows with a (t, h, w) grid; image
+    and video placeholders are expanded together and the rows equal a direct call of the tower."""
+    import numpy as np
+
+    from easydel_b200.modules.qwen2_vl import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+
+    V = dict(depth=1, embed_dim=32, hidden_size=32, num_heads=4, in_channels=3, patch_size=4, spatial_merge_size=2,
+             temporal_patch_size=2, mlp_ratio=2)
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4,
+             num_key_value_heads=2, rope_scaling={"type": "mrope", "mrope_section": [1, 1, 2]})
+    torch.manual_seed(0)
+    model = Qwen2VLForConditionalGeneration(Qwen2VLConfig(vision_config=V, text_config=T, image_token_id=127,
+                                                          video_token_id=126), dtype=torch.float32).eval()
+    mgr = MultiModalManager(model, resolution_buckets=[(16, 16)])
+    assert mgr.flat_patch
+    rng = np.random.default_rng(0)
+    image = rng.integers(0, 255, (16, 16, 3), dtype=np.uint8)
+    video = rng.integers(0, 255, (3, 16, 16, 3), dtype=np.uint8)      # 3 frames -> 2 temporal patches
+    ids, embeds, key = mgr.prepare([5, 126, 6, 127, 7], images=[image], videos=[video])
+    assert ids == [5] + [126] * 8 + [6] + [127] * 4 + [7]
+    assert [o for o, _ in embeds] == [1, 10] and [e.shape for _, e in embeds] == [(8, 32), (4, 32)]
+    frames = torch.stack(mgr.process_images(list(video)))
+    rows, grid = mgr.patchify(frames)
+    assert grid == (2, 4, 4) and rows.shape == (32, 3 * 2 * 16)
+    # block order: the first four rows are the 2 x 2 merge block at the top-left of the first temporal patch
+    want = torch.stack([frames[0:2, :, 0:4, 0:4], frames[0:2, :, 0:4, 4:8], frames[0:2, :, 4:8, 0:4],
+                        frames[0:2, :, 4:8, 4:8]]).permute(0, 2, 1, 3, 4).reshape(4, -1)
+    torch.testing.assert_close(rows[:4], want)
+    with torch.no_grad():
+        direct = model.get_video_features(rows, video_grid_thw=torch.tensor([grid]))
+    torch.testing.assert_close(embeds[0][1], direct)
+    assert len(key) == 2
