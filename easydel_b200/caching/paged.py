@@ -33,6 +33,7 @@ class PagedBatchMeta:
     last_token_index: torch.Tensor | None = None  # int32 [B] row of each sequence's last new token
     request_distribution: tuple[int, int, int] | None = None  # (#decode, #decode+#prefill, #total)
     num_splits: int = 1          # decode-only steps: cut every sequence's keys into this many page ranges
+    seq_slots: torch.Tensor | None = None   # int64 [B] engine slot of every sequence (recurrent-state pools)
 
 
 class PagedKVCache:
@@ -47,6 +48,24 @@ class PagedKVCache:
         # latent attention stores one row per token (compressed keys/values + the shared rotary key): no value pool
         self.latent = latent
         self.v = self.k if latent else torch.zeros(shape, dtype=dtype, device=device)
+        # hybrids: layer -> recurrent state with one row per engine slot; ``step_meta`` is the running step's batch
+        self.linear: dict[int, object] = {}
+        self.step_meta: PagedBatchMeta | None = None
+
+    def add_state_pools(self, model, num_slots: int) -> None:
+        layers = getattr(getattr(model, "model", model), "layers", ())
+        for i, layer in enumerate(layers):
+            mixer = getattr(layer, "linear_attn", None) or getattr(layer, "mamba", None)
+            if mixer is None and hasattr(getattr(layer, "self_attn", None), "make_state"):
+                mixer = layer.self_attn
+            if mixer is not None:
+                self.linear[i] = mixer.make_state(num_slots, self.dtype, self.k.device)
+
+    def reset_slot_state(self, slot: int) -> None:
+        for st in self.linear.values():
+            for v in vars(st).values():
+                if isinstance(v, torch.Tensor):
+                    v[slot].zero_()
 
     @staticmethod
     def bytes_per_page(num_layers: int, num_kv_heads: int, head_dim: int, dtype=torch.bfloat16,
@@ -80,15 +99,37 @@ class PagedKVCache:
         return cls(spec.num_layers, int(num_pages), kvh, head_dim, dtype, device, page_size, latent=latent)
 
     def view(self, layer: int):
-        if self.latent:
-            return PagedLatentView(self.k[layer])
-        return PagedLayerView(self.k[layer], self.v[layer])
+        view = PagedLatentView(self.k[layer]) if self.latent else PagedLayerView(self.k[layer], self.v[layer])
+        pool = self.linear.get(layer)
+        view.linear_state = None if pool is None else PagedLinearState(pool, self.step_meta)
+        return view
 
     def seq_len(self) -> int:  # the engine passes explicit positions
         return 0
 
 
+class PagedLinearState:
+    """The recurrent state rows of the sequences scheduled in this step, gathered from the per-slot pool; ``cu`` gives
+    the layers the ragged sequence bounds on the flat token axis. ``commit`` scatters the rows back."""
+
+    def __init__(self, pool, meta: PagedBatchMeta):
+        if meta is None or meta.seq_slots is None:
+            raise RuntimeError("recurrent layers need the step's slot ids (PagedKVCache.step_meta.seq_slots)")
+        self._pool, self._slots = pool, meta.seq_slots
+        self.cu = meta.cu_q
+        for name, v in vars(pool).items():
+            if isinstance(v, torch.Tensor):
+                setattr(self, name, v.index_select(0, self._slots))
+
+    def commit(self) -> None:
+        for name, v in vars(self._pool).items():
+            if isinstance(v, torch.Tensor):
+                v.index_copy_(0, self._slots, getattr(self, name).to(v.dtype))
+
+
 class PagedLayerView:
+    linear_state = None
+
     def __init__(self, k_pages: torch.Tensor, v_pages: torch.Tensor):
         self.k_pages, self.v_pages = k_pages, v_pages
 
@@ -117,6 +158,8 @@ class PagedLatentView:
     is applied after the weighted sum, so the cache is read as it is stored and never expanded per head. The pages
     of the scheduled sequences are gathered through the page table; the products are batched matrix multiplies.
     """
+
+    linear_state = None
 
     def __init__(self, pages: torch.Tensor):
         self.pages = pages                  # [P, page, 1, kv_lora_rank + rope_dim]

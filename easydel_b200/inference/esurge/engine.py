@@ -126,6 +126,11 @@ class eSurge:
         self.cache = PagedKVCache.init_for_model(model, num_pages=num_pages, page_size=page_size,
                                                  hbm_utilization=hbm_utilization, max_model_length=max_model_len,
                                                  max_pages=pages_cap if num_pages is None else None)
+        # hybrids: one recurrent-state row per engine slot (the last row belongs to the padding rows of a batch
+        # bucket). A cached prefix has no recurrent state to resume from, so prefix caching is off for them.
+        self.cache.add_state_pools(getattr(model, "language_model", model), max_num_seqs + 1)
+        if self.cache.linear:
+            enable_prefix_caching = False
         self.pool = PagePool(self.cache.num_pages, enable_caching=enable_prefix_caching)
         self.scheduler = Scheduler(SchedulerConfig(max_num_seqs=max_num_seqs,
                                                    max_num_batched_tokens=self.max_num_batched_tokens,
@@ -315,6 +320,7 @@ class eSurge:
                 if s.request.slot < 0:
                     s.request.slot = self._free_slots.pop()
                     self.runner._slot_npages[s.request.slot] = 0   # the slot's page mirror belongs to a new request
+                    self.cache.reset_slot_state(s.request.slot)
                     if s.request.sampling_params.needs_penalties:
                         self.runner._ensure_counts()
                         self.runner.reset_slot(s.request.slot, s.request.all_token_ids)

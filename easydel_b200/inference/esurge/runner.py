@@ -66,6 +66,7 @@ class ModelRunner:
         import os
 
         self.use_graphs = dev.type == "cuda" and os.environ.get("EDL_ESURGE_CUDA_GRAPHS", "1") != "0"
+        self._seq_slots = torch.zeros(max_num_seqs, dtype=torch.int64, device=dev)
         self._graphs: dict[int, tuple[tp.Any, torch.Tensor]] = {}
         self._graph_pool = None
         self._warm: set[int] = set()
@@ -114,7 +115,9 @@ class ModelRunner:
         meta = PagedBatchMeta(cu_q=d_cu[:B + 1], kv_lens=d_kv[:B], page_table=d_table.view(self.max_num_seqs, MP)[:B],
                               slot_mapping=d_slots[:T], max_q=max_q, num_seqs=B, last_token_index=d_last[:B],
                               request_distribution=(num_decode, B, B),
-                              num_splits=self._decode_splits(B) if (max_q == 1 and T == B) else 1)
+                              num_splits=self._decode_splits(B) if (max_q == 1 and T == B) else 1,
+                              seq_slots=self._seq_slots[:B] if self.cache.linear else None)
+        self.cache.step_meta = meta
         model = self._lm
         if mm_rows:
             emb = model.get_input_embeddings()(d_ids[:T].long())
@@ -245,6 +248,10 @@ class ModelRunner:
                 kv_np[B:Bp] = 1
                 cu_np[B + 1:Bp + 1] = np.arange(B + 1, Bp + 1, dtype=np.int32)
                 last_np[B:Bp] = np.arange(B, Bp, dtype=np.int32)
+        if self.cache.linear:
+            # recurrent-state rows of the scheduled sequences; padding rows of a batch bucket share the spare row
+            sl = [s.request.slot for s in sched] + [self.max_num_seqs] * (Bp - B)
+            self._seq_slots[:Bp].copy_(torch.tensor(sl, dtype=torch.int64), non_blocking=True)
         # one upload of the packed metadata
         self._dev.copy_(self._host, non_blocking=True)
         t1 = time.perf_counter()

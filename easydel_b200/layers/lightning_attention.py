@@ -61,7 +61,9 @@ class LightningAttention(nn.Module):
 
             cu, _ = segment_ids_to_cu_seqlens(segment_ids)
         else:
-            cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=hidden.device)
+            cu = getattr(state, "cu", None)       # a serving state names its own (ragged) sequence bounds
+            if cu is None:
+                cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=hidden.device)
         ones = torch.ones(B * T, self.h, dtype=v.dtype, device=v.device)
         o = ssm.ssd_scan(v.contiguous(), ones, -self.slope_rate.view(-1).float(), k.contiguous(), q.contiguous(),
                          None, None, False, cu, None if state is None else state.kv)

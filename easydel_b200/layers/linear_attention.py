@@ -92,7 +92,9 @@ class GatedDeltaNet(nn.Module):
 
             cu, _ = segment_ids_to_cu_seqlens(segment_ids)
         else:
-            cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=hidden.device)
+            cu = getattr(state, "cu", None)       # a serving state names its own (ragged) sequence bounds
+            if cu is None:
+                cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=hidden.device)
         w = self.conv1d.weight.squeeze(1)
         mixed = ssm.ragged_conv1d(mixed, w, None, cu, "silu", None if state is None else state.conv)
         q, k, v = torch.split(mixed, [self.key_dim, self.key_dim, self.value_dim], dim=-1)
@@ -162,7 +164,9 @@ class KimiDeltaAttention(nn.Module):
 
             cu, _ = segment_ids_to_cu_seqlens(segment_ids)
         else:
-            cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=hidden.device)
+            cu = getattr(state, "cu", None)       # a serving state names its own (ragged) sequence bounds
+            if cu is None:
+                cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=hidden.device)
 
         def conv(x, mod, st):
             return ssm.ragged_conv1d(x.reshape(B * T, -1), mod.weight.squeeze(1), None, cu, "silu", st)

@@ -78,7 +78,9 @@ class SSDMixer(nn.Module):
 
             cu, _ = segment_ids_to_cu_seqlens(segment_ids)
         else:
-            cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=h.device)
+            cu = getattr(state, "cu", None)       # a serving state names its own (ragged) sequence bounds
+            if cu is None:
+                cu = torch.arange(0, (B + 1) * T, T, dtype=torch.int32, device=h.device)
         xbc = ssm.ragged_conv1d(xbc.reshape(B * T, self.conv_dim), self.conv1d.weight[:, 0, :], self.conv1d.bias, cu,
                                 "silu", None if state is None else state.conv)
         x, Bm, Cm = xbc[:, :I], xbc[:, I:I + G * N], xbc[:, I + G * N:]

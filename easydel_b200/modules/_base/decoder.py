@@ -263,18 +263,23 @@ class DecoderLayer(nn.Module):
     # The pair (x, pending) means the residual stream is x + pending; `pending` is folded in by the
     # next fused add+norm. Returns (x, pending, router_logits).
     def _mix(self, h, positions, segment_ids, cache_view, attn_meta):
-        if self.ltype == "lightning":
-            return self.self_attn(h, segment_ids=segment_ids,
-                                  state=None if cache_view is None else cache_view.linear_state)
-        if self.is_linear:
-            return self.linear_attn(h, segment_ids=segment_ids,
-                                    state=None if cache_view is None else cache_view.linear_state)
-        if self.spec.ssm_branch is not None:
-            a_in, a_out, s_out = self.spec.branch_multipliers
-            m = self.mamba(h, segment_ids=segment_ids, state=None if cache_view is None else cache_view.linear_state)
-            a = self.self_attn(h * a_in if a_in != 1.0 else h, positions, segment_ids=segment_ids,
-                               cache_view=cache_view, attn_meta=attn_meta)
-            return m * s_out + a * a_out
+        state = None
+        if cache_view is not None and (self.ltype == "lightning" or self.is_linear or self.spec.ssm_branch is not None):
+            state = cache_view.linear_state
+        try:
+            if self.ltype == "lightning":
+                return self.self_attn(h, segment_ids=segment_ids, state=state)
+            if self.is_linear:
+                return self.linear_attn(h, segment_ids=segment_ids, state=state)
+            if self.spec.ssm_branch is not None:
+                a_in, a_out, s_out = self.spec.branch_multipliers
+                m = self.mamba(h, segment_ids=segment_ids, state=state)
+                a = self.self_attn(h * a_in if a_in != 1.0 else h, positions, segment_ids=segment_ids,
+                                   cache_view=cache_view, attn_meta=attn_meta)
+                return m * s_out + a * a_out
+        finally:
+            if hasattr(state, "commit"):      # serving: write the scheduled sequences' states back to their slots
+                state.commit()
         return self.self_attn(h, positions, segment_ids=segment_ids, cache_view=cache_view, attn_meta=attn_meta)
 
     def forward(self, x, pending, positions, segment_ids=None, cache_view=None, attn_meta=None):

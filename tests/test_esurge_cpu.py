@@ -1,5 +1,6 @@
 """eSurge on CPU: page pool / prefix cache, scheduler policy, and engine output equal to plain generate()."""
 
+import pytest
 import torch
 
 from easydel_b200.inference import SamplingParams
@@ -142,3 +143,24 @@ def test_latent_attention_models_are_served_from_latent_pages():
     for p, o in zip(prompts, outs):
         want = model.generate(torch.tensor([p]), max_new_tokens=6).sequences[0, len(p):].tolist()
         assert o.outputs[0].token_ids == want
+
+
+@pytest.mark.parametrize("family", ["qwen3_next", "falcon_h1", "minimax"])
+def test_hybrid_recurrent_models_are_served_with_per_slot_states(family):
+    """Linear-attention / state-space layers keep one state row per engine slot; a ragged step gathers the rows of
+    the scheduled sequences, the layer walks the sequence bounds, and the rows are scattered back."""
+    import test_model_families_cpu as fam
+
+    torch.manual_seed(0)
+    model = fam._build(family, fam.CASES[family])
+    model = (model[0] if isinstance(model, tuple) else model).eval()
+    eng = eSurge(model, max_model_len=256, max_num_seqs=4, num_pages=8)
+    assert eng.cache.linear and not eng.pool.enable_caching
+    prompts = [[5, 9, 2, 77, 31], list(range(3, 40)), [8, 1]]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=5, temperature=0.0))
+    for p, o in zip(prompts, outs):
+        want = model.generate(torch.tensor([p]), max_new_tokens=5).sequences[0, len(p):].tolist()
+        assert o.outputs[0].token_ids == want
+    # a slot taken by a new request starts from a zero state
+    again = eng.generate([prompts[1]], SamplingParams(max_tokens=5, temperature=0.0))[0]
+    assert again.outputs[0].token_ids == outs[1].outputs[0].token_ids
