@@ -141,6 +141,8 @@ class PagedLayerView:
         T = q.shape[1]
         q3, k3, v3 = q[0], k[0], v[0]
         S.kv_append(k3, v3, self.k_pages, self.v_pages, meta.slot_mapping)
+        if getattr(attn, "chunk_size", None):
+            return self._attend_chunked(attn, q3, meta)[None]
         if meta.num_splits > 1 and meta.max_q == 1 and not attn.sliding_window and q3.is_cuda:
             o = S.paged_attention_splitkv(q3, self.k_pages, self.v_pages, meta.kv_lens, meta.page_table,
                                           meta.num_splits, scale=attn.scale, softcap=attn.softcap, sinks=attn.sinks)
@@ -149,6 +151,49 @@ class PagedLayerView:
                               scale=attn.scale, causal=True, window=attn.sliding_window or 0, softcap=attn.softcap,
                               sinks=attn.sinks)
         return o[None]
+
+
+def _pad_queries(q, meta: PagedBatchMeta):
+    """Flat ``[T, H, D]`` queries -> (``[B, max_q, H, D]``, query positions ``[B, max_q]``, row lengths or None)."""
+    B, T = meta.num_seqs, q.shape[0]
+    kv_lens = meta.kv_lens[:B].long()
+    if meta.max_q == 1 and T >= B:
+        return q[:B, None], (kv_lens - 1)[:, None], None, None
+    cu = meta.cu_q.tolist()
+    lens = [cu[b + 1] - cu[b] for b in range(B)]
+    qb = q.new_zeros(B, meta.max_q, *q.shape[1:])
+    for b, n in enumerate(lens):
+        qb[b, :n] = q[cu[b]:cu[b + 1]]
+    qpos = kv_lens[:, None] - torch.tensor(lens, device=q.device)[:, None] + \
+        torch.arange(meta.max_q, device=q.device)[None]
+    return qb, qpos, lens, cu
+
+
+def _attend_chunked(self, attn, q3, meta: PagedBatchMeta):
+    """Block-diagonal causal attention (keys outside the query's block of ``chunk_size`` positions are masked): the
+    pages of the scheduled sequences are gathered and the dense form runs per sequence row."""
+    from ..ops import reference as R
+
+    B = meta.num_seqs
+    table = meta.page_table[:B].long().clamp_min(0)
+    kk = self.k_pages[table].reshape(B, -1, *self.k_pages.shape[2:])
+    vv = self.v_pages[table].reshape(B, -1, *self.v_pages.shape[2:])
+    qb, qpos, lens, cu = _pad_queries(q3, meta)
+    kpos = torch.arange(kk.shape[1], device=q3.device)
+    ok = (kpos[None, None, :] <= qpos[:, :, None]) & (kpos[None, None, :] < meta.kv_lens[:B].long()[:, None, None]) \
+        & ((kpos[None, None, :] // attn.chunk_size) == (qpos[:, :, None] // attn.chunk_size))
+    bias = torch.where(ok, 0.0, float("-inf"))[:, None]
+    o = R.attention(qb, kk, vv, causal=False, scale=attn.scale, softcap=attn.softcap, sinks=attn.sinks, bias=bias)
+    out = q3.new_zeros(q3.shape[0], *o.shape[2:])
+    if lens is None:
+        out[:B] = o[:, 0]
+    else:
+        for b, n in enumerate(lens):
+            out[cu[b]:cu[b + 1]] = o[b, :n]
+    return out
+
+
+PagedLayerView._attend_chunked = _attend_chunked
 
 
 class PagedLatentView:

@@ -145,7 +145,7 @@ def test_latent_attention_models_are_served_from_latent_pages():
         assert o.outputs[0].token_ids == want
 
 
-@pytest.mark.parametrize("family", ["qwen3_next", "falcon_h1", "minimax"])
+@pytest.mark.parametrize("family", ["qwen3_next", "falcon_h1", "minimax", "llama4_text"])
 def test_hybrid_recurrent_models_are_served_with_per_slot_states(family):
     """Linear-attention / state-space layers keep one state row per engine slot; a ragged step gathers the rows of
     the scheduled sequences, the layer walks the sequence bounds, and the rows are scattered back."""
@@ -155,7 +155,8 @@ def test_hybrid_recurrent_models_are_served_with_per_slot_states(family):
     model = fam._build(family, fam.CASES[family])
     model = (model[0] if isinstance(model, tuple) else model).eval()
     eng = eSurge(model, max_model_len=256, max_num_seqs=4, num_pages=8)
-    assert eng.cache.linear and not eng.pool.enable_caching
+    if family != "llama4_text":     # (Llama-4 is here for its block-diagonal attention over the pages)
+        assert eng.cache.linear and not eng.pool.enable_caching
     prompts = [[5, 9, 2, 77, 31], list(range(3, 40)), [8, 1]]
     outs = eng.generate(prompts, SamplingParams(max_tokens=5, temperature=0.0))
     for p, o in zip(prompts, outs):
