@@ -418,6 +418,205 @@ qgemv_staged_kernel(const float* __restrict__ x, long long ldx, const uint8_t* _
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core form for 4-bit codes. The <= 8 activation rows are the n dimension of mma.m16n8k16: a warp owns a tile
+// of 16 weight rows, dequantises code bytes to bf16 pairs through the byte-indexed table (one table word is one
+// A-fragment register: the byte holds two consecutive k of one row) and issues one mma per 16 x 16 block of weights,
+// so the multiply-adds leave the FMA pipe. The k reduction happens inside the mma; every group's partial product is
+// scaled into fp32 accumulators in the mma's D layout, which is also the layout of the output ([row, token]).
+// Staging is the same as above: per-warp two-slot rings filled by bulk copies on mbarriers (16 rows x 64 code words
+// and their scales per item, fetched as tiled TMA boxes with the 128-byte swizzle so that the eight rows of a
+// fragment load hit different banks), activations as bf16 in shared memory with a padded row pitch, group sums of the activations for the zero
+// points. One CTA of eight warps per SM.
+constexpr int QM_THREADS = 256;
+constexpr int QM_WARPS = QM_THREADS / 32;
+constexpr int QM_ROWS = 16;
+constexpr int QM_CW = 64;                       // code words per row and item (512 weights)
+constexpr int QM_CODE_BYTES = QM_ROWS * QM_CW * 4;   // 4 KB of codes per item: two boxes of 16 rows x 128 bytes
+constexpr int QM_TABLE_BYTES = 256 * 256;       // entry e at e * 256 + lane * 4
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool HAS_ZERO>
+__global__ void __launch_bounds__(QM_THREADS, 1)
+qgemv_mma_kernel(const float* __restrict__ x, long long ldx, int M, const __grid_constant__ CUtensorMap map_codes,
+                 const __grid_constant__ CUtensorMap map_sc, const __grid_constant__ CUtensorMap map_zr,
+                 const float* __restrict__ lut, int N, int K, int group, __nv_bfloat16* __restrict__ out,
+                 long long ldo, const __nv_bfloat16* __restrict__ bias, int* status) {
+  extern __shared__ __align__(128) unsigned char s_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int groups = K / group, nwords = K / 8;
+  const int xp = K + 8;                                   // activation row pitch in elements
+  const int gpc = QM_CW * 8 / group;                      // groups per item
+  const int sc_pitch = gpc * 2;                           // bytes (a multiple of 16: checked by the host)
+  // slot: two 128-byte-swizzled boxes of 16 rows x 32 code words, then the scale (and zero-point) boxes; slots start
+  // on 1024-byte boundaries, which the swizzle pattern needs
+  const int slot_bytes = (QM_CODE_BYTES + QM_ROWS * sc_pitch * (HAS_ZERO ? 2 : 1) + 1023) & ~1023;
+  uint32_t* s_tab = reinterpret_cast<uint32_t*>(s_raw);
+  uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_raw + QM_TABLE_BYTES);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(s_raw + QM_TABLE_BYTES + QM_WARPS * QS_SLOTS * 8);
+  __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(s_raw + QM_TABLE_BYTES + QM_WARPS * QS_SLOTS * 8 + 128);
+  float* s_xsum = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(s_x) + (size_t)8 * xp * 2);
+  unsigned char* s_ring = reinterpret_cast<unsigned char*>(s_xsum) + (HAS_ZERO ? (size_t)groups * 8 * 4 : 0);
+  s_ring += (1024 - (smem_u32(s_ring) & 1023)) & 1023;
+
+  __shared__ float s_lut[16];
+  if (threadIdx.x < 16) s_lut[threadIdx.x] = lut[threadIdx.x];
+  // activations: fp32 rows in global memory -> bf16 rows of pitch K + 8 (rows past M and the pad columns are zero)
+  for (int i = threadIdx.x; i < 8 * (xp / 4); i += QM_THREADS) {
+    const int m = i / (xp / 4), k = (i - m * (xp / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (m < M && k < K) v = __ldg(reinterpret_cast<const float4*>(x + m * ldx + k));
+    __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(s_x + m * xp + k);
+    dst[0] = __floats2bfloat162_rn(v.x, v.y);
+    dst[1] = __floats2bfloat162_rn(v.z, v.w);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 256 * 32; i += QM_THREADS) {
+    const int e = i >> 5, l = i & 31;
+    const __nv_bfloat162 pr = __floats2bfloat162_rn(s_lut[e & 15], s_lut[e >> 4]);
+    s_tab[e * 64 + l] = *reinterpret_cast<const uint32_t*>(&pr);
+  }
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    for (int i = 0; i < QM_WARPS * QS_SLOTS; ++i) mbar_init(smem_u32(s_bar + i), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (HAS_ZERO) {
+    for (int i = threadIdx.x; i < groups * 8; i += QM_THREADS) {
+      const int gi = i >> 3, m = i & 7;
+      float a = 0.f;
+      for (int k = 0; k < group; ++k) a += __bfloat162float(s_x[m * xp + gi * group + k]);
+      s_xsum[i] = a;
+    }
+    __syncthreads();
+  }
+
+  const int chunks = nwords / QM_CW;
+  const int n_tiles = (N + QM_ROWS - 1) / QM_ROWS;
+  const int first = blockIdx.x * QM_WARPS + warp, stride = gridDim.x * QM_WARPS;
+  const int my_tiles = first < n_tiles ? (n_tiles - first + stride - 1) / stride : 0;
+  const int items = my_tiles * chunks;
+  unsigned char* my_ring = s_ring + (size_t)warp * QS_SLOTS * slot_bytes;
+  const uint32_t my_bar = smem_u32(s_bar + warp * QS_SLOTS);
+  const uint32_t sel = 0x4404u | (t << 4);
+  const int gsteps = group / 16;                          // mma steps per group
+
+  auto issue = [&](int it) {                              // lane 0 only: three or four tiled copies per item
+    const int j = it / chunks, c = it - j * chunks;
+    const int n0 = (first + j * stride) * QM_ROWS;
+    const int slot = it % QS_SLOTS;
+    const uint32_t bar = my_bar + slot * 8;
+    const uint32_t base = smem_u32(my_ring + (size_t)slot * slot_bytes);
+    // rows past N are filled with zeros by the copy engine and count towards the byte total like the others
+    mbar_expect_tx(bar, QM_CODE_BYTES + QM_ROWS * sc_pitch * (HAS_ZERO ? 2 : 1));
+    tma_load_2d(base, &map_codes, bar, c * QM_CW, n0);
+    tma_load_2d(base + QM_CODE_BYTES / 2, &map_codes, bar, c * QM_CW + QM_CW / 2, n0);
+    tma_load_2d(base + QM_CODE_BYTES, &map_sc, bar, c * gpc, n0);
+    if (HAS_ZERO) tma_load_2d(base + QM_CODE_BYTES + QM_ROWS * sc_pitch, &map_zr, bar, c * gpc, n0);
+  };
+
+  int issued = 0;
+  if (lane == 0)
+    for (; issued < items && issued < QS_SLOTS; ++issued) issue(issued);
+
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  int it = 0;
+  bool ok = true;
+  for (; it < items; ++it) {
+    const int j = it / chunks, c = it - j * chunks;
+    const int n0 = (first + j * stride) * QM_ROWS;
+    const int slot = it % QS_SLOTS;
+    if (c == 0) acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+    ok = mbar_wait(my_bar + slot * 8, (it / QS_SLOTS) & 1, s_abort, status, EDL_TIMEOUT_PRODUCER);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    const unsigned char* sl = my_ring + (size_t)slot * slot_bytes;
+    const __nv_bfloat16* s_sc = reinterpret_cast<const __nv_bfloat16*>(sl + QM_CODE_BYTES);
+    const __nv_bfloat16* s_zr = reinterpret_cast<const __nv_bfloat16*>(sl + QM_CODE_BYTES + QM_ROWS * sc_pitch);
+    const unsigned char* c_lo = sl + g * 128;              // row g of a box; row g + 8 sits 1024 bytes further
+    const unsigned char* c_hi = c_lo + 8 * 128;
+    const unsigned char* t_base = s_raw + lane * 4;
+    const unsigned char* x_base = reinterpret_cast<const unsigned char*>(s_x) + ((g * xp + c * QM_CW * 8 + 2 * t) << 1);
+    // one mma step: 16 k of the 16 rows = two code words per row; plain shared loads so that the compiler may
+    // schedule the loads of several steps ahead of the mma chain
+    auto step = [&](float (&d)[4], int s) {
+      // byte s * 8 of the row: box s / 16, 16-byte piece (s / 2) % 8 XOR-ed with the row (128-byte swizzle)
+      const int off = (s >> 4) * (QM_CODE_BYTES / 2) + (((((s >> 1) & 7) ^ g)) << 4) + ((s & 1) << 3);
+      const uint2 lo = *reinterpret_cast<const uint2*>(c_lo + off);
+      const uint2 hi = *reinterpret_cast<const uint2*>(c_hi + off);
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(t_base + __byte_perm(lo.x, 0u, sel));
+      a[1] = *reinterpret_cast<const uint32_t*>(t_base + __byte_perm(hi.x, 0u, sel));
+      a[2] = *reinterpret_cast<const uint32_t*>(t_base + __byte_perm(lo.y, 0u, sel));
+      a[3] = *reinterpret_cast<const uint32_t*>(t_base + __byte_perm(hi.y, 0u, sel));
+      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(x_base + s * 32);
+      const uint32_t b1 = *reinterpret_cast<const uint32_t*>(x_base + s * 32 + 16);
+      mma_bf16_16816(d, a, b0, b1);
+    };
+    auto fold = [&](const float (&d)[4], int gl) {
+      const float sc_lo = __bfloat162float(s_sc[g * gpc + gl]), sc_hi = __bfloat162float(s_sc[(g + 8) * gpc + gl]);
+      acc[0] = fmaf(sc_lo, d[0], acc[0]);
+      acc[1] = fmaf(sc_lo, d[1], acc[1]);
+      acc[2] = fmaf(sc_hi, d[2], acc[2]);
+      acc[3] = fmaf(sc_hi, d[3], acc[3]);
+      if (HAS_ZERO) {
+        const float z_lo = __bfloat162float(s_zr[g * gpc + gl]), z_hi = __bfloat162float(s_zr[(g + 8) * gpc + gl]);
+        const float2 xsum = *reinterpret_cast<const float2*>(s_xsum + (c * gpc + gl) * 8 + 2 * t);
+        acc[0] = fmaf(z_lo, xsum.x, acc[0]);
+        acc[1] = fmaf(z_lo, xsum.y, acc[1]);
+        acc[2] = fmaf(z_hi, xsum.x, acc[2]);
+        acc[3] = fmaf(z_hi, xsum.y, acc[3]);
+      }
+    };
+    // two groups at a time: their mma chains are independent (gpc is a multiple of 8)
+    for (int gl = 0; gl < gpc; gl += 2) {
+      float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+      for (int q = 0; q < gsteps; ++q) {
+        step(d0, gl * gsteps + q);
+        step(d1, (gl + 1) * gsteps + q);
+      }
+      fold(d0, gl);
+      fold(d1, gl + 1);
+    }
+    __syncwarp();
+    if (lane == 0 && it + QS_SLOTS < items) {
+      fence_proxy_async_smem();
+      issue(it + QS_SLOTS);
+    }
+    if (c == chunks - 1) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int n = n0 + g + (i >> 1) * 8, m = 2 * t + (i & 1);
+        if (n < N && m < M) {
+          float v = acc[i];
+          if (bias) v += __bfloat162float(bias[n]);
+          out[m * ldo + n] = __float2bfloat16(v);
+        }
+      }
+    }
+  }
+  if (!ok && lane == 0) {
+    const int last = min(items, it + QS_SLOTS);
+    for (int u = it; u < last; ++u) {
+      const uint32_t bar = my_bar + (u % QS_SLOTS) * 8;
+      const long long t0 = clock64();
+      while (!mbar_try_wait(bar, (u / QS_SLOTS) & 1) && clock64() - t0 < 20000000LL) {
+      }
+    }
+  }
+}
+
 }  // namespace
 }  // namespace edl
 
@@ -457,6 +656,39 @@ EDL_HOST_API int edl_qgemv(const void* x, long long ldx, const void* codes, cons
     return -1;
   }
   cudaStream_t s = (cudaStream_t)stream;
+  // Tensor-core form: 4-bit codes, K a multiple of 512, whole 16-byte scale pieces per item, activations (as bf16,
+  // eight padded rows) small enough to sit in shared memory beside the table and the rings.
+  if (status && bits == 4 && K % (QM_CW * 8) == 0 && group >= 16 && (QM_CW * 8) % group == 0 &&
+      ((QM_CW * 8 / group) * 2) % 16 == 0 && ((K / group) % 8) == 0 && !getenv("EDL_QGEMV_DIRECT") &&
+      !getenv("EDL_QGEMV_NO_MMA") &&
+      ((((uintptr_t)codes | (uintptr_t)scales | (uintptr_t)(zeros ? zeros : codes)) & 15) == 0)) {
+    const int sc_pitch = (QM_CW * 8 / group) * 2;
+    const long long slot = (QM_CODE_BYTES + QM_ROWS * sc_pitch * (zeros ? 2 : 1) + 1023) & ~1023LL;
+    const long long smem_mma = QM_TABLE_BYTES + QM_WARPS * QS_SLOTS * 8 + 128 + 8LL * (K + 8) * 2 +
+                               (zeros ? (long long)(K / group) * 8 * 4 : 0) + 1024 + QM_WARPS * QS_SLOTS * slot;
+    CUtensorMap mc, ms, mz;
+    const int gpc = QM_CW * 8 / group;
+    if (smem_mma <= 227 * 1024 &&
+        make_tmap_2d(&mc, codes, N, K / 8, K / 8, QM_ROWS, QM_CW / 2, 4, 3) == 0 &&
+        make_tmap_2d(&ms, scales, N, K / group, K / group, QM_ROWS, gpc, 2, 0) == 0 &&
+        make_tmap_2d(&mz, zeros ? zeros : scales, N, K / group, K / group, QM_ROWS, gpc, 2, 0) == 0) {
+      const int tiles = (N + QM_ROWS - 1) / QM_ROWS;
+      int blocks = (tiles + QM_WARPS - 1) / QM_WARPS;
+      if (blocks > sm_count()) blocks = sm_count();
+      if (zeros) {
+        auto kern = qgemv_mma_kernel<true>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma);
+        kern<<<blocks, QM_THREADS, (size_t)smem_mma, s>>>((const float*)x, ldx, M, mc, ms, mz, lut, N, K, group,
+                                                          (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)bias, status);
+      } else {
+        auto kern = qgemv_mma_kernel<false>;
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma);
+        kern<<<blocks, QM_THREADS, (size_t)smem_mma, s>>>((const float*)x, ldx, M, mc, ms, mz, lut, N, K, group,
+                                                          (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)bias, status);
+      }
+      return check_cuda(cudaGetLastError(), "qgemv mma launch");
+    }
+  }
   // Staged form when the bulk copies can be issued: 16-byte aligned sources and whole 16-byte scale pieces. Small
   // activation blocks (M * K * 4 <= 64 KB) are staged in shared memory as well, with a shorter row chunk.
   if (status && !getenv("EDL_QGEMV_DIRECT")) {

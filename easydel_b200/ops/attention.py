@@ -130,6 +130,8 @@ def flash_attention(q, k, v, *, causal=True, scale=None, segment_ids=None, slidi
     if segment_ids is not None and cu_seqlens is None:
         cu_seqlens, max_seqlen = segment_ids_to_cu_seqlens(segment_ids)
     if cu_seqlens is not None:
+        if max_seqlen is None:
+            max_seqlen = int((cu_seqlens[1:] - cu_seqlens[:-1]).max().item())
         shape = q.shape
         q3 = q.reshape(-1, q.shape[-2], q.shape[-1]) if q.dim() == 4 else q
         k3 = k.reshape(-1, k.shape[-2], k.shape[-1]) if k.dim() == 4 else k

@@ -437,9 +437,11 @@ def attention(q, k, v, *, causal: bool = True, scale: float | None = None, segme
                 scale = scale if scale is not None else 1.0 / math.sqrt(D)
                 q, k, v = (torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v))
                 return flash_attention(q, k, v, causal=causal, scale=scale, segment_ids=segment_ids,
-                                       sliding_window=sliding_window, softcap=softcap, sinks=sinks)[..., :D]
+                                       sliding_window=sliding_window, softcap=softcap, sinks=sinks,
+                                       cu_seqlens=cu_seqlens)[..., :D]
             return flash_attention(q, k, v, causal=causal, scale=scale, segment_ids=segment_ids,
-                                   sliding_window=sliding_window, softcap=softcap, sinks=sinks)
+                                   sliding_window=sliding_window, softcap=softcap, sinks=sinks,
+                                   cu_seqlens=cu_seqlens)
         return _library_attention(q, k, v, causal, scale, segment_ids, sliding_window, softcap, sinks)
     return R.attention(q, k, v, causal=causal, scale=scale, segment_ids=segment_ids, sliding_window=sliding_window,
                        softcap=softcap, sinks=sinks)
