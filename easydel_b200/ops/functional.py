@@ -60,6 +60,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
     if _lib.use_kernels(x):
         if x.dtype != torch.bfloat16:
             raise TypeError(f"GPU linear expects bf16 activations, got {x.dtype}")
+        if (w.shape[0] % 8) or (w.shape[1] % 8):
+            # rows of the operands / the output would not start on 16-byte boundaries (a 4-way router, a 3-class
+            # head ...): a plain library product; such matrices are a few kilobytes
+            return torch.nn.functional.linear(x, w.to(x.dtype), None if bias is None else bias.to(x.dtype))
         return _LinearFn.apply(x, w, bias)
     return R.linear(x, w, bias)
 
