@@ -141,8 +141,9 @@ class PagedLayerView:
         T = q.shape[1]
         q3, k3, v3 = q[0], k[0], v[0]
         S.kv_append(k3, v3, self.k_pages, self.v_pages, meta.slot_mapping)
-        if getattr(attn, "chunk_size", None):
-            return self._attend_chunked(attn, q3, meta)[None]
+        if getattr(attn, "chunk_size", None) or (q3.is_cuda and q3.shape[-1] not in (64, 128)):
+            # block-diagonal attention, or a head size outside the paged kernel's (64 / 128)
+            return self._attend_gathered(attn, q3, meta)[None]
         if meta.num_splits > 1 and meta.max_q == 1 and not attn.sliding_window and q3.is_cuda:
             o = S.paged_attention_splitkv(q3, self.k_pages, self.v_pages, meta.kv_lens, meta.page_table,
                                           meta.num_splits, scale=attn.scale, softcap=attn.softcap, sinks=attn.sinks)
@@ -169,9 +170,10 @@ def _pad_queries(q, meta: PagedBatchMeta):
     return qb, qpos, lens, cu
 
 
-def _attend_chunked(self, attn, q3, meta: PagedBatchMeta):
-    """Block-diagonal causal attention (keys outside the query's block of ``chunk_size`` positions are masked): the
-    pages of the scheduled sequences are gathered and the dense form runs per sequence row."""
+def _attend_gathered(self, attn, q3, meta: PagedBatchMeta):
+    """Causal attention over the gathered pages of the scheduled sequences in the dense form, one padded row per
+    sequence: block-diagonal masks (keys outside the query's block of ``chunk_size`` positions), sliding windows and
+    head sizes the paged kernel does not cover."""
     from ..ops import reference as R
 
     B = meta.num_seqs
@@ -180,8 +182,11 @@ def _attend_chunked(self, attn, q3, meta: PagedBatchMeta):
     vv = self.v_pages[table].reshape(B, -1, *self.v_pages.shape[2:])
     qb, qpos, lens, cu = _pad_queries(q3, meta)
     kpos = torch.arange(kk.shape[1], device=q3.device)
-    ok = (kpos[None, None, :] <= qpos[:, :, None]) & (kpos[None, None, :] < meta.kv_lens[:B].long()[:, None, None]) \
-        & ((kpos[None, None, :] // attn.chunk_size) == (qpos[:, :, None] // attn.chunk_size))
+    ok = (kpos[None, None, :] <= qpos[:, :, None]) & (kpos[None, None, :] < meta.kv_lens[:B].long()[:, None, None])
+    if getattr(attn, "chunk_size", None):
+        ok = ok & ((kpos[None, None, :] // attn.chunk_size) == (qpos[:, :, None] // attn.chunk_size))
+    if attn.sliding_window:
+        ok = ok & (kpos[None, None, :] > qpos[:, :, None] - attn.sliding_window)
     bias = torch.where(ok, 0.0, float("-inf"))[:, None]
     o = R.attention(qb, kk, vv, causal=False, scale=attn.scale, softcap=attn.softcap, sinks=attn.sinks, bias=bias)
     out = q3.new_zeros(q3.shape[0], *o.shape[2:])
@@ -193,7 +198,7 @@ def _attend_chunked(self, attn, q3, meta: PagedBatchMeta):
     return out
 
 
-PagedLayerView._attend_chunked = _attend_chunked
+PagedLayerView._attend_gathered = _attend_gathered
 
 
 class PagedLatentView:

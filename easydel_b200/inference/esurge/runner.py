@@ -66,6 +66,8 @@ class ModelRunner:
         import os
 
         self.use_graphs = dev.type == "cuda" and os.environ.get("EDL_ESURGE_CUDA_GRAPHS", "1") != "0"
+        if cache.linear or cache.latent or model.spec.head_dim not in (64, 128):
+            self.use_graphs = False     # these serving paths are tensor code with host-side steps: run eagerly
         self._seq_slots = torch.zeros(max_num_seqs, dtype=torch.int64, device=dev)
         self._graphs: dict[int, tuple[tp.Any, torch.Tensor]] = {}
         self._graph_pool = None
