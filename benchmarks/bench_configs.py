@@ -2,10 +2,10 @@
 
     # DPO on the Llama-3-8B architecture, tensor parallel x FSDP (frozen reference copy, sigmoid loss, beta 0.1)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29520 \
-        -m easydel_b200.trainers.bench_configs dpo --tp 2 [--layers 32] [--pairs-per-rank 4]
+        -m benchmarks.bench_configs dpo --tp 2 [--layers 32] [--pairs-per-rank 4]
 
     # SFT on the Qwen3-MoE-30B-A3B architecture with expert parallelism over all ranks (dropless top-8 of 128)
-    python -m torch.distributed.run ... -m easydel_b200.trainers.bench_configs moe [--layers 48] [--seqs-per-rank 4]
+    python -m torch.distributed.run ... -m benchmarks.bench_configs moe [--layers 48] [--seqs-per-rank 4]
 
 Synthetic data of the shapes the baseline names (preference pairs: prompt 128-512, completions 64-512 tokens; MoE:
 sequences of 4096 tokens), random-initialised bf16 weights, fp32 master AdamW, full activation recompute.
@@ -56,8 +56,8 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
-    from ..ops import _lib
-    from ..parallel.mesh import init_distributed
+    from easydel_b200.ops import _lib
+    from easydel_b200.parallel.mesh import init_distributed
 
     rank, local, world = init_distributed()
     dev = torch.device("cuda", local)
@@ -68,8 +68,8 @@ def main():
                   resume_if_possible=False, use_wandb=False, report_metrics=False, progress_bar_type="none",
                   log_grad_norms=False, extra_optimizer_kwargs={"b1": 0.9, "b2": 0.95, "eps": 1e-8})
     if a.what == "dpo":
-        from ..modules.llama import LlamaConfig, LlamaForCausalLM
-        from . import DPOConfig, DPOTrainer
+        from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+        from easydel_b200.trainers import DPOConfig, DPOTrainer
 
         V = 128256
         tp = min(a.tp, world)
@@ -110,8 +110,8 @@ def main():
                           "beta": 0.1, "loss": "sigmoid", "reference": "frozen copy, forward every step"},
                "final_loss": loss}
     else:
-        from ..modules.families import Qwen3MoeConfig, Qwen3MoeForCausalLM
-        from . import Trainer, TrainingArguments
+        from easydel_b200.modules.families import Qwen3MoeConfig, Qwen3MoeForCausalLM
+        from easydel_b200.trainers import Trainer, TrainingArguments
 
         V, S = 151936, 4096
         L = a.layers or 48

@@ -3,7 +3,7 @@
 Run under torchrun, one rank per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29511 \
-        -m easydel_b200.parallel.bench_fused [--tokens 8192] [--hidden 8192] [--ffn 28672] [--iters 20]
+        -m benchmarks.bench_fused [--tokens 8192] [--hidden 8192] [--ffn 28672] [--iters 20]
 
 Shapes are the tensor-parallel linears of a Llama-70B layer at ``tokens`` rows. Every number is the maximum
 over ranks of a CUDA-event time averaged over ``iters`` launches after 5 warm-up launches; operands are larger
@@ -54,9 +54,9 @@ def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
-    from ..ops import _lib
-    from ..ops import kernels as K
-    from .fused import AllGatherGemm, GemmReduceScatter
+    from easydel_b200.ops import _lib
+    from easydel_b200.ops import kernels as K
+    from easydel_b200.parallel.fused import AllGatherGemm, GemmReduceScatter
 
     group = dist.group.WORLD
     flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)

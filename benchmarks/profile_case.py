@@ -1,14 +1,14 @@
 """Runs one kernel a handful of times on a small, L2-exceeding case so that it can be captured by a profiler.
 
-    python -m easydel_b200.ops.profile_case gemm          # 4096 x 6144 x 4096 bf16 (151 MB of operands + output)
-    python -m easydel_b200.ops.profile_case gemm_wgrad    # fp32-accumulating weight gradient, MN-major operands
-    python -m easydel_b200.ops.profile_case attn_fwd      # 8192 tokens, 32 / 8 heads, D = 128, causal
-    python -m easydel_b200.ops.profile_case attn_bwd
-    python -m easydel_b200.ops.profile_case gemm_rs       # one-rank form of the GEMM -> reduce-scatter kernel
-    python -m easydel_b200.ops.profile_case ag_gemm       # one-rank form of the all-gather -> GEMM kernel
-    python -m easydel_b200.ops.profile_case qgemv         # 4-bit fused dequant-GEMV, 4 rows x 14336 x 4096
-    python -m easydel_b200.ops.profile_case qgemv_plain   # the same kernel as single launches (profiler captures)
-    python -m easydel_b200.ops.profile_case adamw         # fused AdamW over 256M parameters
+    python -m benchmarks.profile_case gemm          # 4096 x 6144 x 4096 bf16 (151 MB of operands + output)
+    python -m benchmarks.profile_case gemm_wgrad    # fp32-accumulating weight gradient, MN-major operands
+    python -m benchmarks.profile_case attn_fwd      # 8192 tokens, 32 / 8 heads, D = 128, causal
+    python -m benchmarks.profile_case attn_bwd
+    python -m benchmarks.profile_case gemm_rs       # one-rank form of the GEMM -> reduce-scatter kernel
+    python -m benchmarks.profile_case ag_gemm       # one-rank form of the all-gather -> GEMM kernel
+    python -m benchmarks.profile_case qgemv         # 4-bit fused dequant-GEMV, 4 rows x 14336 x 4096
+    python -m benchmarks.profile_case qgemv_plain   # the same kernel as single launches (profiler captures)
+    python -m benchmarks.profile_case adamw         # fused AdamW over 256M parameters
 
 Prints the CUDA-event time of the last launch. Everything held on the device stays below 4 GB.
 """
@@ -24,7 +24,7 @@ def main() -> None:
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
-    from . import kernels as K
+    from easydel_b200.ops import kernels as K
 
     bf = lambda *s: torch.randn(*s, device=dev, dtype=torch.bfloat16)  # noqa: E731
     if what == "gemm":
@@ -38,7 +38,7 @@ def main() -> None:
         fn = lambda: K.gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True)  # noqa: E731
         work = 2.0 * 8192 * 4096 * 4096
     elif what in ("attn_fwd", "attn_bwd"):
-        from . import attention as A
+        from easydel_b200.ops import attention as A
 
         q, k, v = bf(1, 8192, 32, 128), bf(1, 8192, 8, 128), bf(1, 8192, 8, 128)
         o, lse = A.attn_fwd(q, k, v, causal=True)
@@ -50,28 +50,28 @@ def main() -> None:
             fn = lambda: A.attn_bwd(q, k, v, o, lse, do, causal=True)  # noqa: E731
             work = 10.0 * 8192 * 8192 * 32 * 128 / 2
     elif what == "gemm_rs":
-        from ..parallel.fused import GemmReduceScatter
+        from easydel_b200.parallel.fused import GemmReduceScatter
 
         a, w = bf(4096, 4096), bf(4096, 4096)
         op = GemmReduceScatter(None, 4096, 4096, dev)
         fn = lambda: op(a, w)  # noqa: E731
         work = 2.0 * 4096 * 4096 * 4096
     elif what == "ag_gemm":
-        from ..parallel.fused import AllGatherGemm
+        from easydel_b200.parallel.fused import AllGatherGemm
 
         a, w = bf(4096, 4096), bf(4096, 4096)
         op = AllGatherGemm(None, 4096, 4096, dev)
         fn = lambda: op(a, w)  # noqa: E731
         work = 2.0 * 4096 * 4096 * 4096
     elif what == "qgemv_plain":      # single launches (for a profiler capture); timing is host-bound, see "qgemv"
-        from ..layers.quantization import quantize, quantized_matmul
+        from easydel_b200.layers.quantization import quantize, quantized_matmul
 
         q1 = quantize(bf(14336, 4096) * 0.05, "nf4")
         x = bf(4, 4096)
         fn = lambda: quantized_matmul(x, q1)  # noqa: E731
         work = 14336 * 4096 * 0.5 + 14336 * 64 * 2
     elif what == "qgemv":
-        from ..layers.quantization import quantize, quantized_matmul
+        from easydel_b200.layers.quantization import quantize, quantized_matmul
 
         # a launch is a few microseconds: 32 launches over 8 different weight matrices (250 MB, twice the L2) are
         # captured in one CUDA graph, so that neither the host nor the L2 decides the number
@@ -111,7 +111,7 @@ def main() -> None:
     ms = e0.elapsed_time(e1)
     unit = "GB/s" if what in ("qgemv", "qgemv_plain", "adamw") else "TFLOP/s"
     rate = work / ms / 1e6 if unit == "GB/s" else work / ms / 1e9
-    from . import _lib
+    from easydel_b200.ops import _lib
 
     _lib.check_status(dev)
     print(f"{what}: {ms:.3f} ms, {rate:.1f} {unit}")

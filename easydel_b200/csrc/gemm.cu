@@ -15,6 +15,8 @@
 #include "common.cuh"
 #include "tmem_ops.cuh"
 
+#include <stdlib.h>
+
 namespace edl {
 
 namespace {
@@ -97,6 +99,145 @@ __device__ __forceinline__ TileInfo decode_tile(int tile, int tiles_m, int tiles
   t.m0 = tm * BM;
   t.n0 = tn * BN;
   return t;
+}
+
+// Epilogue of one 128-row x BN-column accumulator: the calling warp owns tensor-memory lane quadrant `q`
+// (32 rows), reads its rows with tcgen05.ld, applies bias / accumulation / cast and writes global memory.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile(void* __restrict__ Cout, const __nv_bfloat16* __restrict__ bias,
+                                              uint32_t tmem_base, int acc, uint8_t* epi_stage, int q, int lane,
+                                              int m0, int n0, long long c_off, int M, int N, long long ldc,
+                                              bool out_f32, bool accum, bool has_bias) {
+  const int row = m0 + q * 32 + lane;
+  const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
+  uint8_t* my_stage = epi_stage + q * 4096;
+  const int valid_rows = M - (m0 + q * 32);  // may be <= 0 or > 32
+  if (!out_f32 && !accum) {
+    // bf16 output: 64 columns per step, staged so that stores cover whole 128-byte row segments
+    __nv_bfloat16* gbase = reinterpret_cast<__nv_bfloat16*>(Cout) + c_off + (long long)(m0 + q * 32) * ldc;
+#pragma unroll 1
+    for (int c = 0; c < BN / 64; ++c) {
+      uint32_t r[64];
+      tmem_ld_32x32b_x64(t_row + c * 64, r);
+      tc_wait_ld();
+      const int col0 = n0 + c * 64;
+      if (col0 < N && valid_rows > 0) {
+        uint4 pk[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j * 8 + e]);
+          if (has_bias) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              if (col0 + j * 8 + e < N) v[e] += __bfloat162float(bias[col0 + j * 8 + e]);
+          }
+          pk[j] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                             pack_bf16x2(v[6], v[7]));
+        }
+        store_rows_coalesced<false>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ldc * 2, valid_rows,
+                                    min(8, (N - col0) >> 3), lane);
+      }
+    }
+  } else if (out_f32 && (N & 3) == 0) {
+    // fp32 output (weight gradients, optionally accumulated in place): 32 columns = 128 bytes per row per step
+    float* gbase = reinterpret_cast<float*>(Cout) + c_off + (long long)(m0 + q * 32) * ldc;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_row + c * 32, r);
+      tc_wait_ld();
+      const int col0 = n0 + c * 32;
+      if (col0 < N && valid_rows > 0) {
+        uint4 pk[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (has_bias) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (col0 + j * 4 + e < N)
+                r[j * 4 + e] = __float_as_uint(__uint_as_float(r[j * 4 + e]) + __bfloat162float(bias[col0 + j * 4 + e]));
+          }
+          pk[j] = make_uint4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
+        }
+        if (accum)
+          store_rows_coalesced<true>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ldc * 4, valid_rows,
+                                     min(8, (N - col0) >> 2), lane);
+        else
+          store_rows_coalesced<false>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ldc * 4, valid_rows,
+                                      min(8, (N - col0) >> 2), lane);
+      }
+    }
+  } else {
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_row + c * 32, r);
+    tc_wait_ld();
+    const int col0 = n0 + c * 32;
+    if (row < M && col0 < N) {
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      if (has_bias) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < N) v[j] += __bfloat162float(bias[col0 + j]);
+      }
+      const bool full_chunk = (col0 + 32 <= N);
+      if (out_f32) {
+        float* cp = reinterpret_cast<float*>(Cout) + c_off + (long long)row * ldc + col0;
+        if (full_chunk) {
+          if (accum) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = *reinterpret_cast<const float4*>(cp + j);
+              v[j] += o.x;
+              v[j + 1] += o.y;
+              v[j + 2] += o.z;
+              v[j + 3] += o.w;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(cp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+          for (int j = 0; j < 32 && col0 + j < N; ++j) cp[j] = accum ? cp[j] + v[j] : v[j];
+        }
+      } else {
+        __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(Cout) + c_off + (long long)row * ldc + col0;
+        if (full_chunk) {
+          if (accum) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 o = *reinterpret_cast<const uint4*>(cp + j);
+              float2 f;
+              f = unpack_bf16x2(o.x); v[j] += f.x; v[j + 1] += f.y;
+              f = unpack_bf16x2(o.y); v[j + 2] += f.x; v[j + 3] += f.y;
+              f = unpack_bf16x2(o.z); v[j + 4] += f.x; v[j + 5] += f.y;
+              f = unpack_bf16x2(o.w); v[j + 6] += f.x; v[j + 7] += f.y;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(v[j], v[j + 1]);
+            o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+            o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+            o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+            *reinterpret_cast<uint4*>(cp + j) = o;
+          }
+        } else {
+          for (int j = 0; j < 32 && col0 + j < N; ++j) {
+            float o = accum ? __bfloat162float(cp[j]) + v[j] : v[j];
+            cp[j] = __float2bfloat16(o);
+          }
+        }
+      }
+    }
+  }
+  }
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -241,136 +382,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int m0 = ti.m0, n0 = ti.n0;
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, status, EDL_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
-      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16) + acc * BN;
-      uint8_t* my_stage = epi_stage + q * 4096;
-      const int valid_rows = M - (m0 + q * 32);  // may be <= 0 or > 32
-      if (!out_f32 && !accum) {
-        // bf16 output: 64 columns per step, staged so that stores cover whole 128-byte row segments
-        __nv_bfloat16* gbase = reinterpret_cast<__nv_bfloat16*>(Cout) + ti.c_off + (long long)(m0 + q * 32) * ldc;
-#pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          uint32_t r[64];
-          tmem_ld_32x32b_x64(t_row + c * 64, r);
-          tc_wait_ld();
-          const int col0 = n0 + c * 64;
-          if (col0 < N && valid_rows > 0) {
-            uint4 pk[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float v[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j * 8 + e]);
-              if (has_bias) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e)
-                  if (col0 + j * 8 + e < N) v[e] += __bfloat162float(bias[col0 + j * 8 + e]);
-              }
-              pk[j] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                                 pack_bf16x2(v[6], v[7]));
-            }
-            store_rows_coalesced<false>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ldc * 2, valid_rows,
-                                        min(8, (N - col0) >> 3), lane);
-          }
-        }
-      } else if (out_f32 && (N & 3) == 0) {
-        // fp32 output (weight gradients, optionally accumulated in place): 32 columns = 128 bytes per row per step
-        float* gbase = reinterpret_cast<float*>(Cout) + ti.c_off + (long long)(m0 + q * 32) * ldc;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_row + c * 32, r);
-          tc_wait_ld();
-          const int col0 = n0 + c * 32;
-          if (col0 < N && valid_rows > 0) {
-            uint4 pk[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (has_bias) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                  if (col0 + j * 4 + e < N)
-                    r[j * 4 + e] = __float_as_uint(__uint_as_float(r[j * 4 + e]) + __bfloat162float(bias[col0 + j * 4 + e]));
-              }
-              pk[j] = make_uint4(r[j * 4], r[j * 4 + 1], r[j * 4 + 2], r[j * 4 + 3]);
-            }
-            if (accum)
-              store_rows_coalesced<true>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ldc * 4, valid_rows,
-                                         min(8, (N - col0) >> 2), lane);
-            else
-              store_rows_coalesced<false>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ldc * 4, valid_rows,
-                                          min(8, (N - col0) >> 2), lane);
-          }
-        }
-      } else {
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(t_row + c * 32, r);
-        tc_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (row < M && col0 < N) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (has_bias) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < N) v[j] += __bfloat162float(bias[col0 + j]);
-          }
-          const bool full_chunk = (col0 + 32 <= N);
-          if (out_f32) {
-            float* cp = reinterpret_cast<float*>(Cout) + ti.c_off + (long long)row * ldc + col0;
-            if (full_chunk) {
-              if (accum) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                  float4 o = *reinterpret_cast<const float4*>(cp + j);
-                  v[j] += o.x;
-                  v[j + 1] += o.y;
-                  v[j + 2] += o.z;
-                  v[j + 3] += o.w;
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(cp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) cp[j] = accum ? cp[j] + v[j] : v[j];
-            }
-          } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(Cout) + ti.c_off + (long long)row * ldc + col0;
-            if (full_chunk) {
-              if (accum) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  uint4 o = *reinterpret_cast<const uint4*>(cp + j);
-                  float2 f;
-                  f = unpack_bf16x2(o.x); v[j] += f.x; v[j + 1] += f.y;
-                  f = unpack_bf16x2(o.y); v[j + 2] += f.x; v[j + 3] += f.y;
-                  f = unpack_bf16x2(o.z); v[j + 4] += f.x; v[j + 5] += f.y;
-                  f = unpack_bf16x2(o.w); v[j + 6] += f.x; v[j + 7] += f.y;
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 o;
-                o.x = pack_bf16x2(v[j], v[j + 1]);
-                o.y = pack_bf16x2(v[j + 2], v[j + 3]);
-                o.z = pack_bf16x2(v[j + 4], v[j + 5]);
-                o.w = pack_bf16x2(v[j + 6], v[j + 7]);
-                *reinterpret_cast<uint4*>(cp + j) = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) {
-                float o = accum ? __bfloat162float(cp[j]) + v[j] : v[j];
-                cp[j] = __float2bfloat16(o);
-              }
-            }
-          }
-        }
-      }
-      }
+      epilogue_tile<BN>(Cout, bias, tmem_base, acc, epi_stage, q, lane, m0, n0, ti.c_off, M, N, ldc, out_f32, accum,
+                        has_bias);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
@@ -389,6 +402,193 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// CTA-pair form: a cluster of two CTAs computes one 256 x 256 tile with tcgen05.mma.cta_group::2. Each CTA loads
+// its own 128 rows of A and its own 128-column half of B (plain, non-multicast TMA loads whose completion bytes are
+// counted on the leader's barrier), the leader's MMA thread issues one instruction that reads both CTAs' shared
+// memory and writes both CTAs' tensor memory, and each CTA runs the epilogue of its own 128 rows. Against the
+// single-CTA tile this halves the B bytes every SM reads from shared memory per MMA and makes a stage 32 KB instead
+// of 48 KB, so six stages of look-ahead fit.
+struct Cfg2 {
+  static constexpr int BN = 256;
+  static constexpr int A_BYTES = 128 * BK * 2;
+  static constexpr int B_BYTES = 128 * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int EPI_BYTES = 4 * 4096;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES + 1024;
+  static constexpr int TMEM_COLS = 512;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                  void* __restrict__ Cout, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc,
+                  int flags, int* status) {
+  using C = Cfg2;
+  constexpr int BN = C::BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  const uint32_t full0 = smem_u32(bars);
+  const uint32_t empty0 = full0 + 8 * C::STAGES;
+  const uint32_t tfull0 = empty0 + 8 * C::STAGES;
+  const uint32_t tempty0 = tfull0 + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES + C::BAR_BYTES;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader of the pair
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);   // leader: its own arrive.expect_tx; both CTAs' copies complete bytes on it
+      mbar_init(empty0 + 8 * s, 1);  // one multicast commit from the leader's MMA thread
+    }
+    mbar_init(tfull0, 1);
+    mbar_init(tfull0 + 8, 1);
+    mbar_init(tempty0, 8);  // four epilogue warps in each CTA of the pair (used in the leader only)
+    mbar_init(tempty0 + 8, 8);
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tma_a);
+    prefetch_tmap(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), C::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_m = (M + 255) / 256;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  const uint32_t smem_base = smem_u32(smem);
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t lead_full0 = mapa_shared(full0, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * 256 + (int)rank * 128;  // this CTA's rows of A and of the output
+        const int nb0 = tn * BN + (int)rank * 128;  // this CTA's half of the B tile
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const int kc = kb * BK;
+          if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, status, EDL_TIMEOUT_PRODUCER)) {
+            ok = false;
+            break;
+          }
+          if (leader) mbar_expect_tx(full0 + 8 * stage, 2 * C::STAGE_BYTES);
+          const uint32_t fb = lead_full0 + 8 * stage;
+          const uint32_t a_dst = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + C::A_BYTES;
+          if (!A_MN) {
+            tma_load_2d_pair(a_dst, &tma_a, fb, kc, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_2d_pair(a_dst + j * 8192, &tma_a, fb, m0 + j * 64, kc);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(b_dst, &tma_b, fb, kc, nb0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_2d_pair(b_dst + j * 8192, &tma_b, fb, nb0 + j * 64, kc);
+          }
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(256, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, status, EDL_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, status, EDL_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * C::STAGE_BYTES;
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? umma_smem_desc_sw128(a_addr + k * 2048, 8192, 1024)
+                                        : umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
+                                        : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit_pair(empty0 + 8 * stage, 3);  // the stage is free in both CTAs
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit_pair(tfull0 + 8 * acc, 3);  // both epilogues may read this accumulator
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool out_f32 = flags & GEMM_OUT_F32;
+    const bool accum = flags & GEMM_ACCUMULATE;
+    const bool has_bias = (flags & GEMM_BIAS) && bias != nullptr;
+    const uint32_t lead_tempty0 = mapa_shared(tempty0, 0);
+    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * 256 + (int)rank * 128, n0 = tn * BN;
+      if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, status, EDL_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      epilogue_tile<BN>(Cout, bias, tmem_base, acc, epi_stage, q, lane, m0, n0, 0, M, N, ldc, out_f32, accum, has_bias);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8 * acc);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  if (*abort_flag) {
+    long long t0 = clock64();
+    while (clock64() - t0 < 400000) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still signal it
+  if (warp == 1) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
 }
 
 // a_rows / b_rows: extents of the row (outer) dimension of the A / B tensors in memory, which for grouped
@@ -412,12 +612,15 @@ int launch(const void* A, const void* B, void* Cout, const void* bias, int M, in
     rc = make_tmap_2d_16b(&tb, B, b_rows >= 0 ? b_rows : K, N, ldb, BK, 64);
   if (rc) return rc;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {false};  // the opt-in is a per-device attribute of the function
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
     if (check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
                    "cudaFuncSetAttribute(gemm)"))
       return -1;
-    attr_set = true;
+    attr_set[dev] = true;
   }
   int tiles = max_tiles >= 0 ? max_tiles : ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int ctas = sm_count();
@@ -426,6 +629,59 @@ int launch(const void* A, const void* B, void* Cout, const void* bias, int M, in
   kern<<<ctas, GEMM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, Cout, reinterpret_cast<const __nv_bfloat16*>(bias), M,
                                                        N, K, ldc, flags, status, grp);
   return check_cuda(cudaGetLastError(), "gemm launch");
+}
+
+// Number of CTA pairs that can be resident at once (queried once per device and kernel).
+template <bool A_MN, bool B_MN>
+int launch_pair(const void* A, const void* B, void* Cout, const void* bias, int M, int N, int K, long long lda,
+                long long ldb, long long ldc, int flags, int* status, cudaStream_t stream, int max_ctas) {
+  using C = Cfg2;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!A_MN)
+    rc = make_tmap_2d_16b(&ta, A, M, K, lda, 128, BK);
+  else
+    rc = make_tmap_2d_16b(&ta, A, K, M, lda, BK, 64);
+  if (rc) return rc;
+  if (!B_MN)
+    rc = make_tmap_2d_16b(&tb, B, N, K, ldb, 128, BK);
+  else
+    rc = make_tmap_2d_16b(&tb, B, K, N, ldb, BK, 64);
+  if (rc) return rc;
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
+  static int pairs_on_device[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (pairs_on_device[dev] == 0) {
+    if (check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
+                   "cudaFuncSetAttribute(gemm pair)"))
+      return -1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count() & ~1, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count() / 2;
+    }
+    pairs_on_device[dev] = n;
+  }
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  int pairs = pairs_on_device[dev];
+  if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<2 * pairs, GEMM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, Cout, reinterpret_cast<const __nv_bfloat16*>(bias),
+                                                            M, N, K, ldc, flags, status);
+  return check_cuda(cudaGetLastError(), "gemm pair launch");
 }
 
 }  // namespace
@@ -452,6 +708,20 @@ EDL_HOST_API int edl_gemm_bf16(const void* A, const void* B, void* C, const void
     return -1;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // force_bn: 0 = choose, 128 / 256 = single-CTA tile width, 512 = CTA-pair (256 x 256) kernel, -1 = never the pair
+  const int pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  static const bool pair_default = [] {
+    const char* e = getenv("EDL_GEMM_PAIR");
+    return e ? (e[0] != '0') : true;
+  }();
+  const bool want_pair =
+      force_bn == 512 || (force_bn == 0 && pair_default && pair_tiles >= sm_count() / 2 && M >= 256 && N >= 256);
+  if (want_pair) {
+    if (!a_mn && !b_mn) return launch_pair<false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, status, s, max_ctas);
+    if (!a_mn && b_mn) return launch_pair<false, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, status, s, max_ctas);
+    if (a_mn && !b_mn) return launch_pair<true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, status, s, max_ctas);
+    return launch_pair<true, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, status, s, max_ctas);
+  }
   int tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
   bool bn128 = (N <= 128) || (tiles256 < sm_count());
   if (force_bn == 128) bn128 = true;

@@ -37,6 +37,49 @@ def test_gemm_layouts(a_mn, b_mn, bn):
     _close(out, _ref(a, b, a_mn, b_mn), K)
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(384, 512, 320), (256, 256, 64), (1000, 1000, 1000), (2048, 4096, 1024)])
+def test_gemm_cta_pair(a_mn, b_mn, M, N, K):
+    """The 256 x 256 cta_group::2 kernel (two CTAs per tile) on every operand layout, ragged edges included."""
+    from easydel_b200.ops import kernels as K_
+
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a 16-byte aligned leading dimension")
+    a, b = _mk(M, N, K, a_mn, b_mn, seed=M + K)
+    out = K_.gemm(a, b, a_mn=a_mn, b_mn=b_mn, force_bn=512)
+    _close(out, _ref(a, b, a_mn, b_mn), K)
+
+
+def test_gemm_cta_pair_fp32_accumulate_bias():
+    from easydel_b200.ops import kernels as K_
+
+    M, N, K = 512, 768, 512
+    a, b = _mk(M, N, K, True, True, seed=5)
+    ref = _ref(a, b, True, True)
+    acc = torch.ones((M, N), device="cuda", dtype=torch.float32)
+    K_.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True, force_bn=512)
+    K_.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True, force_bn=512)
+    assert torch.allclose(acc, 1 + 2 * ref, atol=2e-2, rtol=1e-3)
+    a, b = _mk(M, N, K, False, False, seed=6)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    out = K_.gemm(a, b, bias=bias, force_bn=512)
+    _close(out, _ref(a, b, False, False) + bias.float(), K)
+
+
+def test_gemm_benchmarked_shape_against_oracle():
+    """The largest benchmarked forward shape (gate_up of Llama-3-8B at 8192 tokens) against fp32 matmul."""
+    from easydel_b200.ops import kernels as K_
+
+    M, N, K = 8192, 28672, 4096
+    a, b = _mk(M, N, K, False, False, seed=11)
+    for bn in (0, 512):
+        out = K_.gemm(a, b, force_bn=bn)
+        for r0 in (0, 4096, 8192 - 256):  # compare row bands (the fp32 reference of the whole product is 940 MB)
+            ref = a[r0:r0 + 256].float() @ b.float().t()
+            _close(out[r0:r0 + 256], ref, K)
+        del out
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 264, 72), (1, 8, 8), (1000, 1000, 1000), (4096, 4096, 4096),
                                    (130, 40, 4104)])
 def test_gemm_shapes(M, N, K):
