@@ -47,6 +47,7 @@ struct AttnBwdParams {
   int causal;
   int window;
   int* status;
+  int nx, ny;           // launch geometry: tiles and heads (the grids are one-dimensional, tile index slowest)
 };
 
 template <int D>
@@ -104,8 +105,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // query tile slowest and reversed: the long causal tiles of every head start first
+  const int per_t = p.ny * p.B;
+  const int qt = p.nx - 1 - (int)(blockIdx.x / per_t);
+  const int rem_id = (int)(blockIdx.x % per_t);
+  const int h = rem_id % p.ny, b = rem_id / p.ny;
   const int hk = h / (p.Hq / p.Hkv);
   const int q_start = p.cu_q ? p.cu_q[b] : b * p.Tq;
   const int k_start = p.cu_k ? p.cu_k[b] : b * p.Tk;
@@ -266,7 +270,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       float pd[64];
       if (!capped) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) pd[i] = exp2f(fmaf(__uint_as_float(s[i]), scale_log2, neg_lse2));
+        for (int i = 0; i < 64; i += 4) {
+          float x0, x1, x2, x3;
+          fma2(x0, x1, __uint_as_float(s[i]), __uint_as_float(s[i + 1]), scale_log2, scale_log2, neg_lse2, neg_lse2);
+          fma2(x2, x3, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]), scale_log2, scale_log2, neg_lse2,
+               neg_lse2);
+          pd[i] = exp2f(x0);
+          pd[i + 1] = exp2f(x1);
+          pd[i + 2] = exp2f(x2);
+          pd[i + 3] = exp2_poly(x3);  // one exponential in four off the MUFU
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
@@ -291,9 +304,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       tmem_ld_32x32b_x64(tDP + lane_sel + cb, s);
       tc_wait_ld();
       uint32_t pk[32];
+      const float ndl = -dl;
 #pragma unroll
-      for (int i = 0; i < 64; i += 2)
-        pk[i >> 1] = pack_bf16x2(pd[i] * (__uint_as_float(s[i]) - dl), pd[i + 1] * (__uint_as_float(s[i + 1]) - dl));
+      for (int i = 0; i < 64; i += 2) {
+        float g0 = __uint_as_float(s[i]), g1 = __uint_as_float(s[i + 1]);
+        add2(g0, g1, ndl, ndl);
+        mul2(g0, g1, g0, g1, pd[i], pd[i + 1]);
+        pk[i >> 1] = pack_bf16x2(g0, g1);
+      }
       tmem_st_32x32b_x32(tDP + lane_sel + cb, pk);
       tc_wait_st();
       tc_fence_before();
@@ -358,7 +376,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  // key tile slowest: under a causal mask the early key tiles see the most query tiles, so they start first
+  const int per_t = p.ny * p.B;
+  const int jt = (int)(blockIdx.x / per_t);
+  const int rem_id = (int)(blockIdx.x % per_t);
+  const int hk = rem_id % p.ny, b = rem_id / p.ny;
   const int G = p.Hq / p.Hkv;
   const int q_start = p.cu_q ? p.cu_q[b] : b * p.Tq;
   const int k_start = p.cu_k ? p.cu_k[b] : b * p.Tk;
@@ -512,7 +534,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       const int qr = i * BT + (sidx & 127);
       if (qr >= len_q) return 0.f;
       const long long idx = (long long)hq * p.total_q + q_start + qr;
-      return sidx < 128 ? p.lse[idx] * LOG2E : p.delta[idx];
+      return sidx < 128 ? -p.lse[idx] * LOG2E : -p.delta[idx];  // both are only ever subtracted
     };
     // Bounded rendezvous (an mbarrier instead of bar.sync, so that an abandoned wait cannot hang the CTA).
     int stat_phase = 0;
@@ -552,11 +574,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       if (!capped && !tile_mask) {
 #pragma unroll
         for (int x = 0; x < 64; x += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(st_lse + cb + x);
-          pkp[x >> 1] = pack_bf16x2(exp2f(fmaf(__uint_as_float(s[x]), scale_log2, -l4.x)),
-                                    exp2f(fmaf(__uint_as_float(s[x + 1]), scale_log2, -l4.y)));
-          pkp[(x >> 1) + 1] = pack_bf16x2(exp2f(fmaf(__uint_as_float(s[x + 2]), scale_log2, -l4.z)),
-                                          exp2f(fmaf(__uint_as_float(s[x + 3]), scale_log2, -l4.w)));
+          const float4 l4 = *reinterpret_cast<const float4*>(st_lse + cb + x);  // -lse in log2 units
+          float x0, x1, x2, x3;
+          fma2(x0, x1, __uint_as_float(s[x]), __uint_as_float(s[x + 1]), scale_log2, scale_log2, l4.x, l4.y);
+          fma2(x2, x3, __uint_as_float(s[x + 2]), __uint_as_float(s[x + 3]), scale_log2, scale_log2, l4.z, l4.w);
+          pkp[x >> 1] = pack_bf16x2(exp2f(x0), exp2f(x1));
+          pkp[(x >> 1) + 1] = pack_bf16x2(exp2f(x2), exp2_poly(x3));  // one exponential in four off the MUFU
         }
       } else {
 #pragma unroll
@@ -572,7 +595,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
               s2 = cap2 * th;
               dcap = 1.f - th * th;
             }
-            float pe = exp2f(s2 - st_lse[col]);
+            float pe = exp2f(s2 + st_lse[col]);
             const int qpos = q0 + col + off;
             const bool okm = (kpos < len_k) && (q0 + col < len_q) && (!p.causal || kpos <= qpos) &&
                              (p.window <= 0 || kpos > qpos - p.window);
@@ -603,9 +626,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
           const float2 c0 = unpack_bf16x2(dcp[x >> 1]), c1 = unpack_bf16x2(dcp[(x >> 1) + 1]);
           p0.x *= c0.x; p0.y *= c0.y; p1.x *= c1.x; p1.y *= c1.y;
         }
-        pkd[x >> 1] = pack_bf16x2(p0.x * (__uint_as_float(s[x]) - d4.x), p0.y * (__uint_as_float(s[x + 1]) - d4.y));
-        pkd[(x >> 1) + 1] =
-            pack_bf16x2(p1.x * (__uint_as_float(s[x + 2]) - d4.z), p1.y * (__uint_as_float(s[x + 3]) - d4.w));
+        float g0 = __uint_as_float(s[x]), g1 = __uint_as_float(s[x + 1]);
+        float g2 = __uint_as_float(s[x + 2]), g3 = __uint_as_float(s[x + 3]);
+        add2(g0, g1, d4.x, d4.y);  // d4 holds -delta
+        add2(g2, g3, d4.z, d4.w);
+        mul2(g0, g1, g0, g1, p0.x, p0.y);
+        mul2(g2, g3, g2, g3, p1.x, p1.y);
+        pkd[x >> 1] = pack_bf16x2(g0, g1);
+        pkd[(x >> 1) + 1] = pack_bf16x2(g2, g3);
       }
       tmem_st_32x32b_x32(tDP + lane_sel + cb, pkp);        // P^T piece of this half
       tmem_st_32x32b_x32(tDP + lane_sel + cb + 32, pkd);   // dS^T piece of this half
@@ -683,20 +711,28 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dout, lo
   if (make_tmap_3d_16b(&tk, k, D, p.Hkv, total_k, D, ldk, 64, 1, BT, 3)) return -1;
   if (make_tmap_3d_16b(&tv, v, D, p.Hkv, total_k, D, ldv, 64, 1, BT, 3)) return -1;
   if (make_tmap_3d_16b(&tdo, dout, D, p.Hq, total_q, D, lddo, 64, 1, BT, 3)) return -1;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {false};  // per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
     if (check_cuda(cudaFuncSetAttribute(attn_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM),
                    "cudaFuncSetAttribute(attn_bwd_dq)") ||
         check_cuda(cudaFuncSetAttribute(attn_bwd_dkv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM),
                    "cudaFuncSetAttribute(attn_bwd_dkv)"))
       return -1;
-    attr_set = true;
+    attr_set[dev] = true;
   }
-  dim3 grid_kv((p.Tk + BT - 1) / BT, p.Hkv, p.B);
-  attn_bwd_dkv_kernel<D><<<grid_kv, BWD_THREADS, C::SMEM, stream>>>(tq, tk, tv, tdo, p);
+  AttnBwdParams pk = p, pq = p;
+  pk.nx = (p.Tk + BT - 1) / BT;
+  pk.ny = p.Hkv;
+  attn_bwd_dkv_kernel<D><<<(unsigned)((long long)pk.nx * pk.ny * p.B), BWD_THREADS, C::SMEM, stream>>>(tq, tk, tv, tdo,
+                                                                                                      pk);
   if (check_cuda(cudaGetLastError(), "attn_bwd_dkv launch")) return -1;
-  dim3 grid_q((p.Tq + BT - 1) / BT, p.Hq, p.B);
-  attn_bwd_dq_kernel<D><<<grid_q, BWD_THREADS, C::SMEM, stream>>>(tq, tk, tv, tdo, p);
+  pq.nx = (p.Tq + BT - 1) / BT;
+  pq.ny = p.Hq;
+  attn_bwd_dq_kernel<D><<<(unsigned)((long long)pq.nx * pq.ny * p.B), BWD_THREADS, C::SMEM, stream>>>(tq, tk, tv, tdo,
+                                                                                                     pq);
   return check_cuda(cudaGetLastError(), "attn_bwd_dq launch");
 }
 

@@ -54,6 +54,7 @@ struct AttnFwdParams {
   const int* kv_lens;    // [B] keys per sequence (context length including the new tokens), paged mode
   int pt_stride;
   int pack;              // query heads per tile row group (1 = one head per CTA)
+  int nx, ny;            // launch geometry: query blocks and heads (the grid itself is one-dimensional)
 };
 
 template <int D>
@@ -109,12 +110,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;  // heavy (late) causal blocks first
-  const int b = blockIdx.z;
+  // One-dimensional grid, query block slowest and reversed: blocks are handed to SMs in index order, so the
+  // long (late) causal blocks of every head and sequence start first and the short ones fill the tail.
+  const int per_qb = p.ny * p.B;
+  const int qb = p.nx - 1 - (int)(blockIdx.x / per_qb);
+  const int rem_id = (int)(blockIdx.x % per_qb);
+  const int b = rem_id / p.ny;
   const int pack = p.pack;                       // power of two, divides BQ
   const int pshift = 31 - __clz(pack);
   const int TQ = BQ >> pshift;                   // query tokens per tile
-  const int h = blockIdx.y;                      // query head (pack == 1) or KV head (packed)
+  const int h = rem_id % p.ny;                   // query head (pack == 1) or KV head (packed)
   const int hk = pack == 1 ? h / (p.Hq / p.Hkv) : h;
   const int h_first = pack == 1 ? h : hk * pack; // first query head of this CTA's rows
 
@@ -291,30 +296,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tc_fence_after();
       uint32_t a[64], c2[64];
       tmem_ld_32x32b_x64(tS, a);
-      tmem_ld_32x32b_x64(tS + 64, c2);
       tc_wait_ld();
+      tmem_ld_32x32b_x64(tS + 64, c2);  // in flight while the first half is masked and reduced
       const bool tile_mask = (kv0 + BKV > len_k) || (p.causal && kv0 + BKV - 1 > q0 + off) ||
                              (p.window > 0 && kv0 < q0 + TQ - 1 + off - p.window + 1);
-      if (capped) {
+      auto prep = [&](uint32_t (&v)[64], int kbase) {
+        if (capped) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          a[i] = __float_as_uint(cap2 * tanhf(__uint_as_float(a[i]) * scale_nat * inv_cap));
-          c2[i] = __float_as_uint(cap2 * tanhf(__uint_as_float(c2[i]) * scale_nat * inv_cap));
+          for (int i = 0; i < 64; ++i) v[i] = __float_as_uint(cap2 * tanhf(__uint_as_float(v[i]) * scale_nat * inv_cap));
         }
-      }
-      if (tile_mask) {
+        if (tile_mask) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const int k0 = kv0 + i, k1 = kv0 + 64 + i;
-          const bool ok0 = (k0 < len_k) && (!p.causal || k0 <= qpos) && (p.window <= 0 || k0 > qpos - p.window);
-          const bool ok1 = (k1 < len_k) && (!p.causal || k1 <= qpos) && (p.window <= 0 || k1 > qpos - p.window);
-          if (!ok0) a[i] = 0xff800000u;   // -inf
-          if (!ok1) c2[i] = 0xff800000u;
+          for (int i = 0; i < 64; ++i) {
+            const int k0 = kbase + i;
+            const bool ok0 = (k0 < len_k) && (!p.causal || k0 <= qpos) && (p.window <= 0 || k0 > qpos - p.window);
+            if (!ok0) v[i] = 0xff800000u;  // -inf
+          }
         }
-      }
-      float mx = -INFINITY;
+      };
+      auto row_max = [&](const uint32_t (&v)[64]) {
+        float m0 = fmax3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
+        float m1 = fmax3(__uint_as_float(v[3]), __uint_as_float(v[4]), __uint_as_float(v[5]));
 #pragma unroll
-      for (int i = 0; i < 64; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(a[i]), __uint_as_float(c2[i])));
+        for (int i = 6; i < 62; i += 4) {
+          m0 = fmax3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+          m1 = fmax3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+        }
+        return fmax3(m0, m1, fmaxf(__uint_as_float(v[62]), __uint_as_float(v[63])));
+      };
+      prep(a, kv0);
+      float mx = row_max(a);
+      tc_wait_ld();
+      prep(c2, kv0 + 64);
+      mx = fmaxf(mx, row_max(c2));
       mx *= mul;  // mul > 0, so scaling commutes with the maximum
       // lazy rescale (warp-uniform decision: tcgen05.ld/st are warp-wide). The QK^T product of this
       // step was issued after the PV product of the previous one, so O is quiescent here.
@@ -336,28 +350,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         m_used = m_new;
       }
       const float neg_m = -m_used;
-      float l0 = 0.f, l1 = 0.f;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      // Four scores per step: packed FMAs form x = s * mul - m, three exponentials go to the MUFU and one to the
+      // polynomial on the FMA pipe, the row sum is accumulated with packed adds.
+      auto exp_pack = [&](const uint32_t (&v)[64], uint32_t (&pk)[32]) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          float x0, x1, x2, x3;
+          fma2(x0, x1, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), mul, mul, neg_m, neg_m);
+          fma2(x2, x3, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]), mul, mul, neg_m, neg_m);
+          const float e0 = exp2f(x0), e1 = exp2f(x1), e2 = exp2f(x2);
+          const float e3 = exp2_poly(x3);
+          add2(l0, l1, e0, e1);
+          add2(l2, l3, e2, e3);
+          pk[i >> 1] = pack_bf16x2(e0, e1);
+          pk[(i >> 1) + 1] = pack_bf16x2(e2, e3);
+        }
+      };
       {
         uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float e0 = exp2f(fmaf(__uint_as_float(a[i]), mul, neg_m));
-          const float e1 = exp2f(fmaf(__uint_as_float(a[i + 1]), mul, neg_m));
-          l0 += e0;
-          l1 += e1;
-          pk[i >> 1] = pack_bf16x2(e0, e1);
-        }
+        exp_pack(a, pk);
         tmem_st_32x32b_x32(tS, pk);
-#pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float e0 = exp2f(fmaf(__uint_as_float(c2[i]), mul, neg_m));
-          const float e1 = exp2f(fmaf(__uint_as_float(c2[i + 1]), mul, neg_m));
-          l0 += e0;
-          l1 += e1;
-          pk[i >> 1] = pack_bf16x2(e0, e1);
-        }
+        exp_pack(c2, pk);
         tmem_st_32x32b_x32(tS + 32, pk);
       }
+      l0 += l2;
+      l1 += l3;
       l += l0 + l1;
       tc_wait_st();
       tc_fence_before();
@@ -421,16 +439,22 @@ int launch_fwd(const void* q, const void* k, const void* v, long long ldq, long 
   if (make_tmap_3d_16b(&tk, k, D, p.Hkv, total_k, D, ldk, 64, 1, BKV, 3)) return -1;
   if (make_tmap_3d_16b(&tv, v, D, p.Hkv, total_k, D, ldv, 64, 1, BKV, 3)) return -1;
   auto kern = attn_fwd_kernel<D>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {false};  // per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
     if (check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM),
                    "cudaFuncSetAttribute(attn_fwd)"))
       return -1;
-    attr_set = true;
+    attr_set[dev] = true;
   }
   const int tq_block = 2 * BQ / p.pack;  // query tokens per CTA
-  dim3 grid((p.Tq + tq_block - 1) / tq_block, p.pack == 1 ? p.Hq : p.Hkv, p.B);
-  kern<<<grid, ATT_THREADS, C::SMEM, stream>>>(tq, tk, tv, p);
+  AttnFwdParams pl = p;
+  pl.nx = (p.Tq + tq_block - 1) / tq_block;
+  pl.ny = p.pack == 1 ? p.Hq : p.Hkv;
+  const long long blocks = (long long)pl.nx * pl.ny * p.B;
+  kern<<<(unsigned)blocks, ATT_THREADS, C::SMEM, stream>>>(tq, tk, tv, pl);
   return check_cuda(cudaGetLastError(), "attn_fwd launch");
 }
 

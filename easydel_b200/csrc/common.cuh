@@ -303,6 +303,49 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   return __bfloat1622float2(v);
 }
 
+// ---- packed fp32 arithmetic and a software exp2 for the softmax loops ----------------------------------------
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float m;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+  return m;
+}
+// (d0, d1) = (a0, a1) * (b0, b1) + (c0, c1) as one packed instruction.
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0,
+                                     float c1) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1) {
+  asm("{\n\t.reg .b64 ra, rd;\n\t"
+      "mov.b64 rd, {%0, %1};\n\tmov.b64 ra, {%2, %3};\n\t"
+      "add.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "+f"(d0), "+f"(d1)
+      : "f"(a0), "f"(a1));
+}
+__device__ __forceinline__ void mul2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// 2^x on the FMA and integer pipes (no MUFU): round x to the nearest integer n with the 1.5 * 2^23 trick, a cubic
+// for 2^f on f = x - n in [-0.5, 0.5] (relative error 1.0e-4, well under bf16 rounding), then n added to the
+// exponent field. Used for a share of the softmax exponentials, whose MUFU throughput (16 per clock and SM)
+// otherwise bounds attention. x <= -126 (masked scores included) gives a value below 1e-37.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(0.05592204f, f, 0.24264008f);
+  p = fmaf(p, f, 0.69312102f);
+  p = fmaf(p, f, 0.99992448f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 // Epilogue helper: a warp holds a 32-row block one row per lane, each row 128 bytes as eight 16-byte chunks
 // (64 bf16 or 32 fp32 values). Writing it straight out would make every store instruction touch 32 different rows
 // with 16 bytes each; instead the block goes through a swizzled 4 KB shared-memory stage and leaves as four whole

@@ -497,13 +497,16 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
 
 int launch_collective(const CUtensorMap& ta, const CUtensorMap& tg, const CUtensorMap& tb, void* C, int N, int K,
                       long long ldc, int* status, const CollInfo& ci, int counters_n, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  static bool attr_set[64] = {false};  // per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_set[dev]) {
     if (check_cuda(cudaFuncSetAttribute(gemm_collective_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         SMEM_BYTES),
                    "cudaFuncSetAttribute(gemm_collective)"))
       return -1;
-    attr_set = true;
+    attr_set[dev] = true;
   }
   if (check_cuda(cudaMemsetAsync(ci.counters, 0, sizeof(int) * counters_n, stream), "memset(counters)")) return -1;
   // One CTA per SM, all resident at once: the copier CTAs and the flag waits rely on it.

@@ -389,7 +389,12 @@ class EasyDeLBaseConfig(PretrainedConfig):
 
     # ------------------------------------------------------------------ serialisation
     def to_dict(self) -> dict:
-        d = super().to_dict()
+        # the mesh holds process groups, which cannot be deep-copied: take it out while the base class copies
+        mesh = self.__dict__.pop("_mesh", None)
+        try:
+            d = super().to_dict()
+        finally:
+            self.__dict__["_mesh"] = mesh
         d.pop("_mesh", None)
         for f in _DTYPE_FIELDS:
             if f in d:

@@ -104,18 +104,12 @@ class EasyDeLState:
                 self._sumsq = torch.zeros(1, dtype=torch.float32, device=g.device)
             self._sumsq.zero_()
             K.sumsq_(self._sumsq, g)
-            if ep > 1:   # every rank must clip with the same global norm: add the other ranks' expert gradients
-                import torch.distributed as dist
-
-                rep = torch.zeros_like(self._sumsq)
-                for lo, hi in flat.replicated_ranges():
-                    K.sumsq_(rep, flat.grad[lo:hi])
-                local_experts = self._sumsq - rep
-                dist.all_reduce(local_experts, group=ep_group)
-                self._sumsq.copy_(rep + local_experts)
+            # every rank of the tensor- / expert-parallel groups must clip with the same global norm
+            self._sumsq.copy_(flat.global_sumsq(self._sumsq, g, flat.shard_lo, self._model_mesh()))
             norm, coef, skip = K.clip_coef(self._sumsq, grad_scale, tx.clip_grad or 0.0)
         else:
-            norm = g.float().norm() * grad_scale
+            sq = flat.global_sumsq(g.float().pow(2).sum().reshape(1), g, flat.shard_lo, self._model_mesh())
+            norm = sq.sqrt().reshape(()) * grad_scale
             skip = (~torch.isfinite(norm)).to(torch.int32).reshape(1)
             if tx.clip_grad:
                 coef = torch.clamp(tx.clip_grad / (norm + 1e-6), max=1.0).reshape(1)
@@ -126,6 +120,10 @@ class EasyDeLState:
                       gscale_tensor=coef, skip_tensor=skip, decay=decay, zero_grad=zero_grad)
         self.last_grad_norm = norm
         return norm
+
+    def _model_mesh(self):
+        mesh = getattr(getattr(self.model, "config", None), "mesh", None)
+        return mesh if (mesh is not None and getattr(mesh, "is_distributed", False)) else None
 
     def _expert_parallel(self):
         mesh = getattr(getattr(self.model, "config", None), "mesh", None)

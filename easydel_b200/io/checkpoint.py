@@ -76,6 +76,9 @@ def save_model(model, save_directory: str, float_dtype=None, step: int | None = 
                write_card: bool = True, **_) -> str:
     """``save_pretrained``: config, generation config, model card, index and parameter arrays."""
     float_dtype = coerce_dtype(float_dtype)
+    # Tensor- / expert-parallel shards are all-gathered into full tensors first (a collective over those groups,
+    # so every rank takes part); only the writer rank touches the disk.
+    ed_state = PT.model_to_easydel_state(model) if (PT.is_model_parallel(model) or _is_writer()) else None
     if not _is_writer():
         return save_directory
     os.makedirs(save_directory, exist_ok=True)
@@ -90,7 +93,6 @@ def save_model(model, save_directory: str, float_dtype=None, step: int | None = 
     if write_card:
         with open(os.path.join(save_directory, "README.md"), "w", encoding="utf-8") as f:
             f.write(_model_card(model, step))
-    ed_state = PT.model_to_easydel_state(model)
     entries = write_tree(save_directory, MODEL_PREFIX, ed_state, float_dtype)
     index_path = os.path.join(save_directory, TENSORSTORE_INDEX_NAME)
     index = {"format": "tensorstore", "version": "easydel", "prefixes": {}}
@@ -114,8 +116,12 @@ def save_optimizer_state(state, save_directory: str) -> None:
         return
     tensors: dict[str, torch.Tensor] = {}
     gathered = _gather_flat_state(state)
-    for sname, buf in gathered.items():
-        for pname, view in flat.named_views(buf):
+    model_parallel = PT.is_model_parallel(state.model)
+    mods = dict(state.model.named_modules()) if model_parallel else None
+    for sname in sorted(gathered):
+        for pname, view in flat.named_views(gathered[sname]):
+            if model_parallel:  # same assembly as the parameter itself (a collective over the tp / ep group)
+                view = PT.gather_tensor_from_ranks(state.model, pname, view, mods)
             tensors[f"{sname}.{pname}"] = view
     if not _is_writer():
         return
@@ -282,6 +288,8 @@ def load_optimizer_state(state, path: str, tx_template=None) -> None:
     tree = read_tree(path, OPTIMIZER_PREFIX)
     names = {"master": flat.master, **flat.opt_state}
     lo, hi = flat.shard_lo, flat.shard_hi
+    model_parallel = PT.is_model_parallel(state.model)
+    mods = dict(state.model.named_modules()) if model_parallel else None
     for sname, buf in names.items():
         for pname, off, sz, shape, _ in flat.entries:
             key = f"{sname}.{pname}"
@@ -290,7 +298,10 @@ def load_optimizer_state(state, path: str, tx_template=None) -> None:
             a, b = max(off, lo), min(off + sz, hi)
             if a >= b:
                 continue
-            src = tree[key].reshape(-1)[a - off:b - off]
+            full = tree[key]
+            if model_parallel:  # the checkpoint holds full tensors; keep this rank's tensor-/expert-parallel piece
+                full = PT.shard_tensor_for_rank(state.model, pname, full, mods).contiguous()
+            src = full.reshape(-1)[a - off:b - off]
             buf[a - lo:b - lo].copy_(src.to(buf.dtype))
     sp = os.path.join(path, TX_STRUCTURE_NAME)
     if os.path.exists(sp):

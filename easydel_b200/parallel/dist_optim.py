@@ -108,6 +108,8 @@ class DistributedFlat:
                 dist.reduce_scatter_tensor(g, flat.grad, op=dist.ReduceOp.SUM, group=self.group)
             self._sumsq += g.float().pow(2).sum()
         dist.all_reduce(self._sumsq, group=self.group)
+        # tensor- / expert-parallel shards: add the other ranks' pieces so that every rank clips with one norm
+        self._sumsq.copy_(flat.global_sumsq(self._sumsq, g, flat.shard_lo, self.mesh, dp_group=self.group))
         if g.is_cuda and _lib.available():
             from ..ops import kernels as K
 

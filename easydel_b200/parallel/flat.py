@@ -119,6 +119,62 @@ class FlatParams:
                 runs.append((o, end))
         return runs
 
+    def model_parallel_ranges(self) -> dict[str, list[tuple[int, int]]]:
+        """Flat ranges (element offsets, without padding) of the parameters that differ across the model-parallel
+        groups: ``"tp"`` = column / row shards of tensor-parallel linears, ``"ep"`` = per-rank expert weights.
+        Everything else is replicated over those groups."""
+        if getattr(self, "_mp_ranges", None) is not None:
+            return self._mp_ranges
+        owner = {}
+        for mod_name, mod in self.model.named_modules():
+            style = getattr(mod, "parallel_style", None)
+            if getattr(mod, "tp_size", 1) > 1 and style in ("column", "row"):
+                for leaf, p in mod.named_parameters(recurse=False):
+                    if not (style == "row" and leaf == "bias"):
+                        owner[id(p)] = "tp"
+        out: dict[str, list[tuple[int, int]]] = {"tp": [], "ep": []}
+        for n, o, sz, _, _ in self.entries:
+            p = self.params[n]
+            kind = "ep" if getattr(p, "_ep_local", False) else owner.get(id(p))
+            if kind is None:
+                continue
+            runs = out[kind]
+            if runs and runs[-1][1] == o:
+                runs[-1] = (runs[-1][0], o + sz)
+            else:
+                runs.append((o, o + sz))
+        self._mp_ranges = out
+        return out
+
+    def global_sumsq(self, sumsq: torch.Tensor, grad: torch.Tensor, grad_lo: int, mesh, dp_group=None) -> torch.Tensor:
+        """Sum of squared gradients over the whole model from the sum over this rank's flat buffer.
+
+        ``sumsq`` (1-element tensor) already covers the local flat buffer (summed over the data-parallel group when
+        the buffer is sharded over it); ``grad`` is the slice of the gradient buffer this rank reduced, starting at
+        flat offset ``grad_lo``. Parameters sharded over the tensor- or expert-parallel group contribute every
+        rank's piece, replicated parameters count once, so every rank of those groups ends up with the same norm
+        (and the same clip coefficient and skip decision)."""
+        import torch.distributed as dist
+
+        ranges = self.model_parallel_ranges()
+        if mesh is None or not (ranges["tp"] or ranges["ep"]):
+            return sumsq
+        parts = torch.zeros(2, dtype=torch.float32, device=sumsq.device)
+        hi_lim = grad_lo + grad.numel()
+        for i, kind in enumerate(("tp", "ep")):
+            for lo, hi in ranges[kind]:
+                a, b = max(lo, grad_lo), min(hi, hi_lim)
+                if a < b:
+                    parts[i] += grad[a - grad_lo:b - grad_lo].float().pow(2).sum()
+        if dp_group is not None and self.world_size > 1:
+            dist.all_reduce(parts, group=dp_group)
+        local = parts.clone()
+        if ranges["tp"]:
+            dist.all_reduce(parts[0:1], group=mesh.get_group("tp"))
+        if ranges["ep"]:
+            dist.all_reduce(parts[1:2], group=mesh.get_group("ep"))
+        return sumsq + (parts - local).sum()
+
     def sync_replicated_grads(self, group) -> None:
         """Sums the gradients of the replicated parameters over the expert-parallel group (each rank saw different
         tokens); expert weights already received every token's contribution through the token exchange."""

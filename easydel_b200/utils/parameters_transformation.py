@@ -34,8 +34,11 @@ def _module_of(model, name: str):
 
 
 # ----------------------------------------------------------------------------- internal <-> hf
-def internal_to_hf(model, state: dict[str, torch.Tensor] | None = None) -> dict[str, torch.Tensor]:
-    """Splits fused projections and unstacks experts; applies the family's ``hf_rename_out`` hook if present."""
+def internal_to_hf(model, state: dict[str, torch.Tensor] | None = None,
+                   full_shapes: bool = False) -> dict[str, torch.Tensor]:
+    """Splits fused projections and unstacks experts; applies the family's ``hf_rename_out`` hook if present.
+    ``full_shapes``: ``state`` holds gathered (tensor-parallel size 1) tensors, so merged outputs are split at
+    their global widths rather than at this rank's."""
     state = state if state is not None else {k: v for k, v in model.state_dict().items()}
     out: dict[str, torch.Tensor] = {}
     for name, t in state.items():
@@ -51,7 +54,7 @@ def internal_to_hf(model, state: dict[str, torch.Tensor] | None = None) -> dict[
         if mod_name in FUSED_SPLITS and t.dim() <= 2 and not kept and \
                 hasattr(_module_of(model, ".".join(parts[:-1])), "local_out_splits"):
             mod = _module_of(model, ".".join(parts[:-1]))
-            widths = mod.local_out_splits()
+            widths = (mod.out_splits or (t.shape[0],)) if full_shapes else mod.local_out_splits()
             for sub, chunk in zip(FUSED_SPLITS[mod_name], torch.split(t, list(widths), dim=0)):
                 out[f"{pre}{sub}.{leaf}"] = chunk
         elif t.dim() == 3 and mod_name in ("gate_up_proj", "down_proj") and leaf == "weight" and \
@@ -97,7 +100,12 @@ def hf_to_internal(model, hf_state: dict[str, torch.Tensor], strict: bool = True
             else:
                 missing.append(name)
         elif ref.dim() == 3 and mod_name in ("gate_up_proj", "down_proj"):
-            E = ref.shape[0]
+            # all experts are assembled here; an expert-parallel model keeps its own slice afterwards
+            try:
+                block = _module_of(model, prefix) if prefix else model
+            except (AttributeError, IndexError):
+                block = None
+            E = ref.shape[0] * max(1, getattr(block, "ep_size", 1))
             try:
                 if mod_name == "gate_up_proj":
                     out[name] = torch.stack([torch.cat([hf_state[f"{pre}experts.{e}.gate_proj.weight"],
@@ -112,7 +120,7 @@ def hf_to_internal(model, hf_state: dict[str, torch.Tensor], strict: bool = True
                     t = hf_state[fused_key]
                     transposed = getattr(model, "hf_fused_experts_transposed", None)
                     if transposed is None:
-                        transposed = tuple(t.shape) != tuple(ref.shape)
+                        transposed = tuple(t.shape[1:]) != tuple(ref.shape[1:])
                     out[name] = t.transpose(1, 2) if transposed else t
                 else:
                     missing.append(name)
@@ -194,6 +202,9 @@ def easydel_to_hf(ed_state: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
 def model_to_easydel_state(model) -> dict[str, torch.Tensor]:
     """Internal module tree -> reference checkpoint leaves (what ``save_pretrained`` writes)."""
     reg_ln = _layernorm_names(model)
+    if is_model_parallel(model):  # a collective: every rank assembles the full tensors
+        return hf_to_easydel(internal_to_hf(model, gather_internal_state(model), full_shapes=True),
+                             layernorm_names=reg_ln)
     return hf_to_easydel(internal_to_hf(model), layernorm_names=reg_ln)
 
 
@@ -203,6 +214,8 @@ def load_easydel_state(model, ed_state: dict[str, torch.Tensor], strict: bool = 
 
 def load_hf_state(model, hf_state: dict[str, torch.Tensor], strict: bool = True) -> None:
     internal = hf_to_internal(model, hf_state, strict=strict)
+    if is_model_parallel(model):
+        internal = shard_internal_state_for_tp(model, internal)
     with torch.no_grad():
         own = dict(model.named_parameters())
         own.update(dict(model.named_buffers()))
@@ -334,51 +347,114 @@ class TensorConverter:
         return t.detach().cpu().numpy()
 
 
+def _parallel_owner(model, name: str, mods: dict | None = None):
+    """(module, leaf, kind) for a parameter name: kind is "column" / "row" (tensor-parallel linear of size > 1),
+    "ep" (per-rank expert weights) or None (replicated)."""
+    mods = mods if mods is not None else dict(model.named_modules())
+    mod_name, _, leaf = name.rpartition(".")
+    mod = mods.get(mod_name)
+    if mod is None:
+        return None, leaf, None
+    style = getattr(mod, "parallel_style", None)
+    if getattr(mod, "tp_size", 1) > 1 and style in ("column", "row"):
+        return mod, leaf, style
+    param = getattr(mod, leaf, None)
+    if getattr(param, "_ep_local", False):
+        block = mods.get(mod_name.rpartition(".")[0])
+        if block is not None and getattr(block, "ep_size", 1) > 1:
+            return block, leaf, "ep"
+    return mod, leaf, None
+
+
+def shard_tensor_for_rank(model, name: str, t: torch.Tensor, mods: dict | None = None) -> torch.Tensor:
+    """The piece of a full (tp = ep = 1) tensor that this rank's parameter ``name`` holds."""
+    mod, leaf, kind = _parallel_owner(model, name, mods)
+    if kind is None:
+        return t
+    if kind == "ep":
+        n = mod.num_local_experts
+        return t[mod.ep_rank * n:(mod.ep_rank + 1) * n]
+    tp_size, r = mod.tp_size, mod.tp_rank
+    if kind == "row":
+        if leaf == "weight":
+            c = t.shape[1] // tp_size
+            return t[:, r * c:(r + 1) * c]
+        return t
+    local = mod.local_out_splits()
+    if len(local) == 1:
+        c = t.shape[0] // tp_size
+        return t[r * c:(r + 1) * c]
+    # merged outputs: infer the full widths from the tensor (q is exact; k / v may be replicated)
+    q_full = local[0] * tp_size
+    rest = (t.shape[0] - q_full) // (len(local) - 1)
+    full_widths = [q_full] + [rest] * (len(local) - 1)
+    pieces, o = [], 0
+    for lw, fw in zip(local, full_widths):
+        chunk = t[o:o + fw]
+        if fw == lw * tp_size:
+            pieces.append(chunk[r * lw:(r + 1) * lw])
+        else:  # fewer KV heads than ranks: pick the head group this rank's queries use
+            n_groups = fw // lw
+            gi = r * n_groups // tp_size
+            pieces.append(chunk[gi * lw:(gi + 1) * lw])
+        o += fw
+    out = torch.cat(pieces, dim=0)
+    assert out.shape[0] == sum(local)
+    return out
+
+
+def gather_tensor_from_ranks(model, name: str, t: torch.Tensor, mods: dict | None = None) -> torch.Tensor:
+    """Inverse of :func:`shard_tensor_for_rank`: the full tensor, assembled from the tensor- / expert-parallel
+    group's shards. A collective: every rank of that group must call it for the same names in the same order."""
+    import torch.distributed as dist
+
+    mod, leaf, kind = _parallel_owner(model, name, mods)
+    if kind is None or (kind == "row" and leaf != "weight"):
+        return t
+    group = mod.ep_group if kind == "ep" else mod.tp_group
+    world = mod.ep_size if kind == "ep" else mod.tp_size
+    parts = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(parts, t.contiguous(), group=group)
+    if kind == "ep":
+        return torch.cat(parts, dim=0)
+    if kind == "row":
+        return torch.cat(parts, dim=1)
+    local = mod.local_out_splits()
+    if len(local) == 1:
+        return torch.cat(parts, dim=0)
+    pieces, o = [], 0
+    for lw in local:  # each merged output is contiguous over the ranks in the full tensor
+        pieces.extend(part[o:o + lw] for part in parts)
+        o += lw
+    return torch.cat(pieces, dim=0)
+
+
+def is_model_parallel(model) -> bool:
+    """True when some parameter of the model is a tensor- or expert-parallel shard."""
+    for mod in model.modules():
+        if getattr(mod, "tp_size", 1) > 1 and getattr(mod, "parallel_style", None) in ("column", "row"):
+            return True
+        if getattr(mod, "ep_size", 1) > 1:
+            return True
+    return False
+
+
+def gather_internal_state(model, state: dict[str, torch.Tensor] | None = None) -> dict[str, torch.Tensor]:
+    """The model's state dict with every tensor- / expert-parallel shard replaced by the full tensor
+    (a collective over those groups; the result is identical on every rank)."""
+    state = state if state is not None else dict(model.state_dict())
+    if not is_model_parallel(model):
+        return state
+    mods = dict(model.named_modules())
+    return {k: gather_tensor_from_ranks(model, k, v, mods) for k, v in state.items()}
+
+
 def shard_internal_state_for_tp(model, full_state: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
-    """Cuts a full (tensor-parallel size 1) internal state dict down to what this rank's model holds.
+    """Cuts a full (tensor- and expert-parallel size 1) internal state dict down to what this rank's model holds.
 
     Column-parallel weights keep this rank's rows of every merged output (q / k / v, gate / up), row-parallel
-    weights keep this rank's input columns. When there are fewer KV heads than ranks, every rank keeps the
-    KV head its query heads belong to.
+    weights keep this rank's input columns, expert stacks keep this rank's experts. When there are fewer KV
+    heads than ranks, every rank keeps the KV head its query heads belong to.
     """
-    out = {}
     mods = dict(model.named_modules())
-    for name, t in full_state.items():
-        mod_name, _, leaf = name.rpartition(".")
-        mod = mods.get(mod_name)
-        style = getattr(mod, "parallel_style", None)
-        tp_size = getattr(mod, "tp_size", 1)
-        if mod is None or tp_size == 1 or style not in ("column", "row"):
-            out[name] = t
-            continue
-        r = mod.tp_rank
-        if style == "row":
-            if leaf == "weight":
-                c = t.shape[1] // tp_size
-                out[name] = t[:, r * c:(r + 1) * c]
-            else:
-                out[name] = t
-            continue
-        local = mod.local_out_splits()
-        if len(local) == 1:
-            c = t.shape[0] // tp_size
-            out[name] = t[r * c:(r + 1) * c]
-            continue
-        # merged outputs: infer the full widths from the tensor (q is exact; k / v may be replicated)
-        total_local = sum(local)
-        q_full = local[0] * tp_size
-        rest = (t.shape[0] - q_full) // (len(local) - 1)
-        full_widths = [q_full] + [rest] * (len(local) - 1)
-        pieces, o = [], 0
-        for lw, fw in zip(local, full_widths):
-            chunk = t[o:o + fw]
-            if fw == lw * tp_size:
-                pieces.append(chunk[r * lw:(r + 1) * lw])
-            else:  # fewer KV heads than ranks: pick the head group this rank's queries use
-                n_groups = fw // lw
-                gi = r * n_groups // tp_size
-                pieces.append(chunk[gi * lw:(gi + 1) * lw])
-            o += fw
-        out[name] = torch.cat(pieces, dim=0)
-        assert out[name].shape[0] == total_local
-    return out
+    return {name: shard_tensor_for_rank(model, name, t, mods) for name, t in full_state.items()}

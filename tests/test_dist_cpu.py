@@ -195,3 +195,110 @@ def _ep_step_worker(rank, world):
 
 def test_expert_parallel_training_step_matches_single_rank():
     _run(_ep_step_worker, 2)
+
+
+def _tp_checkpoint_worker(rank, world, tmp):
+    """A tensor-parallel model (and its optimizer state) saves full tensors; a tp = 1 model loads them and gives
+    the same logits as the tp = 2 forward; loading the same files back at tp = 2 restores every shard."""
+    from easydel_b200.infra.base_state import EasyDeLState
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+    from easydel_b200.optimizers import OptimizerFactory, SchedulerConfig
+    from easydel_b200.parallel.mesh import DeviceMesh
+
+    kw = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=32)
+    torch.manual_seed(3)
+    cfg = LlamaConfig(sharding_axis_dims=(1, 1, 1, world, 1), **kw)
+    model = LlamaForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32)
+    model.shard_model()
+    tx, _ = OptimizerFactory.create("adamw", SchedulerConfig(None, learning_rate=1e-2), weight_decay=0.0)
+    state = EasyDeLState.create(model=model, tx=tx, init_opt_state=True)
+    ids = torch.randint(0, 128, (2, 16), generator=torch.Generator().manual_seed(1))
+    _, met = model.compute_loss(input_ids=ids, labels=ids)
+    met.loss.backward()
+    state.apply_gradients()
+    with torch.no_grad():
+        logits_tp = model(input_ids=ids).logits
+    state.save_state(tmp)
+    dist.barrier()
+    local_before = {k: v.clone() for k, v in model.state_dict().items()}
+    m_before = {k: v.clone() for k, v in state.flat.opt_state.items()}
+    # tp = 2 round trip of weights and optimizer state
+    for p in model.parameters():
+        p.data.zero_()
+    for v in state.flat.opt_state.values():
+        v.zero_()
+    from easydel_b200.io import checkpoint as CK
+
+    CK.load_state_into(state, tmp)
+    for k, v in model.state_dict().items():
+        assert torch.equal(v, local_before[k]), k
+    for k, v in state.flat.opt_state.items():
+        assert torch.equal(v, m_before[k]), k
+    if rank == 0:
+        import json
+
+        with open(os.path.join(tmp, "tensorstore_index.json")) as f:
+            idx = json.load(f)
+        shapes = {e["path"]: e["shape"] for e in idx["prefixes"]["model"]}
+        qk = [v for k, v in shapes.items() if k.endswith("self_attn/q_proj/kernel")][0]
+        assert qk == [32, 32], qk      # full (in, out), not the tp-local half
+        one = LlamaConfig(**kw)
+        one.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), one.sharding_axis_names, 0, 1))
+        ref = LlamaForCausalLM(one, dtype=torch.float32, param_dtype=torch.float32)
+        CK.load_weights_into(ref, tmp)
+        with torch.no_grad():
+            logits_one = ref(input_ids=ids).logits
+        assert torch.allclose(logits_one, logits_tp, atol=1e-5), (logits_one - logits_tp).abs().max()
+    dist.barrier()
+
+
+def test_tensor_parallel_checkpoint_roundtrip(tmp_path):
+    _run(_tp_checkpoint_worker, 2, str(tmp_path))
+
+
+def _tp_clip_worker(rank, world):
+    """A clipped optimizer step at tp = 2 uses one global gradient norm on both ranks (sharded parameters count
+    every rank's piece, replicated ones once) and matches the single-process step."""
+    from easydel_b200.infra.base_state import EasyDeLState
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+    from easydel_b200.optimizers import OptimizerFactory, SchedulerConfig
+    from easydel_b200.parallel.mesh import DeviceMesh
+    from easydel_b200.utils.parameters_transformation import shard_internal_state_for_tp
+
+    kw = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=32)
+    one = LlamaConfig(**kw)
+    one.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), one.sharding_axis_names, 0, 1))
+    torch.manual_seed(11)
+    full = LlamaForCausalLM(one, dtype=torch.float32, param_dtype=torch.float32)
+    cfg = LlamaConfig(sharding_axis_dims=(1, 1, 1, world, 1), **kw)
+    model = LlamaForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32)
+    model.load_state_dict(shard_internal_state_for_tp(model, full.state_dict()))
+    ids = torch.randint(0, 128, (2, 16), generator=torch.Generator().manual_seed(2))
+
+    def step(m):
+        tx, _ = OptimizerFactory.create("adamw", SchedulerConfig(None, learning_rate=1e-2), weight_decay=0.0,
+                                        clip_grad=0.05)
+        st = EasyDeLState.create(model=m, tx=tx, init_opt_state=True)
+        _, met = m.compute_loss(input_ids=ids, labels=ids)
+        met.loss.backward()
+        return st.apply_gradients()
+
+    n_full, n_tp = step(full), step(model)
+    assert float(n_full) > 0.05, "the step must actually clip"
+    assert abs(float(n_full) - float(n_tp)) < 1e-4 * max(1.0, float(n_full)), (float(n_full), float(n_tp))
+    norms = [torch.zeros(1) for _ in range(world)]
+    dist.all_gather(norms, n_tp.detach().reshape(1).float())
+    assert all(torch.equal(n, norms[0]) for n in norms)
+    want = shard_internal_state_for_tp(model, full.state_dict())
+    for k, v in model.state_dict().items():
+        assert torch.allclose(v, want[k], atol=2e-5), k
+    emb = model.state_dict()["model.embed_tokens.weight"].clone()
+    parts = [torch.empty_like(emb) for _ in range(world)]
+    dist.all_gather(parts, emb)
+    assert torch.equal(parts[0], parts[1]), "replicated weights diverged across the tensor-parallel ranks"
+
+
+def test_tensor_parallel_clip_uses_global_norm():
+    _run(_tp_clip_worker, 2)
