@@ -26,6 +26,8 @@
 #include "common.cuh"
 #include "tmem_ops.cuh"
 
+#include <stdlib.h>
+
 namespace edl {
 namespace {
 

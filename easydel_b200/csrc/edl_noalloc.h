@@ -28,8 +28,10 @@ extern "C" {
 //   dx = rstd * (g - xhat * mean(g * xhat)) [+ dres],  g = dy * (w + w_offset), xhat = x * rstd
 //   dw (+)= sum over rows of dy * xhat          (accumulate != 0 adds to dw)
 // x, dy, dx (and dres if given) are [rows, D] contiguous, D a multiple of 8 and at most
-// EDL_NOALLOC_RMSNORM_MAX_D; dres and dw may be null; dx may alias dy. The caller passes
-// every input and output; nothing is allocated and no allocating routine is called.
+// EDL_NOALLOC_RMSNORM_MAX_D; dres and dw may be null; dx may alias dy (or dres). x, w, dy,
+// dres and dx must be 16-byte aligned: a misaligned pointer is rejected with an error. The
+// caller passes every input and output; nothing is allocated and no allocating routine is
+// called.
 //
 // Set-up: the first call on each device looks up the device address of the scratch array
 // (with that device current) and keeps it. Make that first call outside any stream capture.

@@ -48,6 +48,7 @@ struct CollInfo {
   int mode, nranks, rank, epoch;
   int tiles_per_shard;   // 128-row tiles in one rank's row shard
   int flags;
+  int b_mn;              // 1: B is stored [K, N] (N contiguous) as in a data-gradient GEMM; 0: [N, K]
   long long spin_limit;  // clock cycles a wait on a peer may take
   void* peer[MAX_RANKS];  // RS: staging base on every rank (this call's slot). AG: A shard base on every rank
   int* flag[MAX_RANKS];   // RS: flag words on every rank (this call's slot), one per source rank
@@ -299,7 +300,13 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
           mbar_expect_tx(fb, STAGE_BYTES);
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
           tma_load_2d(a_dst, amap, fb, kb * BK, ti.a_row);
-          tma_load_2d(a_dst + A_BYTES, &tma_b, fb, kb * BK, ti.n0);
+          if (!ci.b_mn) {
+            tma_load_2d(a_dst + A_BYTES, &tma_b, fb, kb * BK, ti.n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(a_dst + A_BYTES + j * 8192, &tma_b, fb, ti.n0 + j * 64, kb * BK);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -309,7 +316,8 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, 0);
+      const uint32_t idesc = umma_idesc_bf16(BM, BN, 0, ci.b_mn);
+      const bool b_mn = ci.b_mn != 0;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -330,7 +338,9 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
             umma_f16_ss(d_tmem, umma_smem_desc_sw128(a_addr + k * 32, 16, 1024),
-                        umma_smem_desc_sw128(b_addr + k * 32, 16, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+                        b_mn ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
+                             : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024),
+                        idesc, (kb | k) != 0 ? 1u : 0u);
           tc_commit(empty0 + 8 * stage);
           if (++stage == STAGES) {
             stage = 0;
@@ -509,9 +519,15 @@ int launch_collective(const CUtensorMap& ta, const CUtensorMap& tg, const CUtens
     attr_set[dev] = true;
   }
   if (check_cuda(cudaMemsetAsync(ci.counters, 0, sizeof(int) * counters_n, stream), "memset(counters)")) return -1;
-  // One CTA per SM, all resident at once: the copier CTAs and the flag waits rely on it.
-  gemm_collective_kernel<<<sm_count(), THREADS, SMEM_BYTES, stream>>>(ta, tg, tb, reinterpret_cast<__nv_bfloat16*>(C),
-                                                                     N, K, ldc, status, ci);
+  // One CTA per SM, all resident at once: the copier CTAs and the flag waits rely on it. A cooperative launch
+  // makes the driver start the grid only when every CTA has an SM, even while another stream holds some.
+  __nv_bfloat16* cptr = reinterpret_cast<__nv_bfloat16*>(C);
+  CUtensorMap ta_ = ta, tg_ = tg, tb_ = tb;
+  CollInfo ci_ = ci;
+  void* args[] = {&ta_, &tg_, &tb_, &cptr, &N, &K, &ldc, &status, &ci_};
+  cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(gemm_collective_kernel), dim3(sm_count()),
+                                              dim3(THREADS), args, SMEM_BYTES, stream);
+  if (e != cudaSuccess) return check_cuda(e, "gemm_collective launch");
   return check_cuda(cudaGetLastError(), "gemm_collective launch");
 }
 
@@ -526,7 +542,7 @@ long long cycles_for_ms(int wait_ms) {
 }  // namespace
 
 // Row-parallel linear fused with the reduce-scatter of its output.
-//   A [M, K] (lda), W [N, K] (ldb): this rank's slices of the reduction dimension. M = nranks * rows_per_rank,
+//   A [M, K] (lda), W [N, K] (ldb; or [K, N] when b_mn != 0): this rank's slices of the reduction dimension. M = nranks * rows_per_rank,
 //   rows_per_rank a multiple of 128; N a multiple of 8.
 //   stage_ptrs[r]: on rank r, a buffer of nranks * rows_per_rank * N bf16 (this call's slot of a symmetric allocation);
 //   flag_ptrs[r]: on rank r, nranks ints (this call's slot), initially 0; `epoch` must grow with every call that
@@ -535,7 +551,7 @@ long long cycles_for_ms(int wait_ms) {
 EDL_HOST_API int edl_gemm_reduce_scatter(const void* A, const void* W, void* out, const void* residual,
                                          const void* bias, int M, int N, int K, long long lda, long long ldb,
                                          void* const* stage_ptrs, int* const* flag_ptrs, int* counters, int nranks,
-                                         int rank, int epoch, int wait_ms, int* status, void* stream) {
+                                         int rank, int epoch, int wait_ms, int* status, void* stream, int b_mn) {
   using namespace edl;
   if (nranks < 1 || nranks > MAX_RANKS || M % (nranks * BM) || (N & 7) || (lda & 7) || (ldb & 7) || (K & 7)) {
     set_last_error("edl_gemm_reduce_scatter: need M %% (nranks*128) == 0, N, K, lda, ldb multiples of 8 (M=%d N=%d K=%d)",
@@ -544,8 +560,9 @@ EDL_HOST_API int edl_gemm_reduce_scatter(const void* A, const void* W, void* out
   }
   CUtensorMap ta, tb;
   if (make_tmap_2d_16b(&ta, A, M, K, lda, BM, BK)) return -1;
-  if (make_tmap_2d_16b(&tb, W, N, K, ldb, BN, BK)) return -1;
+  if (b_mn ? make_tmap_2d_16b(&tb, W, K, N, ldb, BK, 64) : make_tmap_2d_16b(&tb, W, N, K, ldb, BN, BK)) return -1;
   CollInfo ci{};
+  ci.b_mn = b_mn ? 1 : 0;
   ci.mode = MODE_RS;
   ci.nranks = nranks;
   ci.rank = rank;
@@ -568,11 +585,12 @@ EDL_HOST_API int edl_gemm_reduce_scatter(const void* A, const void* W, void* out
 //   of 128. The peers' shards must be complete before the launch and stay unchanged until every rank's kernel has
 //   finished (callers bracket the call with a device barrier over the same symmetric allocation).
 //   gathered: local [nranks * Ms, K]; rows of rank r land at r * Ms (own rows only when copy_own != 0).
-//   C [nranks * Ms, N] (ldc) = gather(A) * W^T (+ bias). counters: nranks * Ms / 128 local ints.
+//   C [nranks * Ms, N] (ldc) = gather(A) * W^T (+ bias); with b_mn != 0 W is stored [K, N] and C = gather(A) * W. counters: nranks * Ms / 128 local ints.
 //   n_copy is ignored (kept for binary compatibility): every CTA copies with a spare warp.
 EDL_HOST_API int edl_allgather_gemm(void* const* shard_ptrs, const void* W, void* C, const void* bias, void* gathered,
                                     int Ms, int N, int K, long long ldb, long long ldc, int* counters, int nranks,
-                                    int rank, int n_copy, int copy_own, int wait_ms, int* status, void* stream) {
+                                    int rank, int n_copy, int copy_own, int wait_ms, int* status, void* stream,
+                                    int b_mn) {
   using namespace edl;
   if (nranks < 1 || nranks > MAX_RANKS || Ms % BM || (K % 128) || (N & 7) || (ldb & 7) || (ldc & 7)) {
     set_last_error("edl_allgather_gemm: need Ms %% 128 == 0, K %% 128 == 0, N, ldb, ldc multiples of 8 (Ms=%d N=%d K=%d)",
@@ -583,8 +601,9 @@ EDL_HOST_API int edl_allgather_gemm(void* const* shard_ptrs, const void* W, void
   CUtensorMap ta, tg, tb;
   if (make_tmap_2d_16b(&ta, shard_ptrs[rank], Ms, K, K, BM, BK)) return -1;
   if (make_tmap_2d_16b(&tg, gathered, (uint64_t)nranks * Ms, K, K, BM, BK)) return -1;
-  if (make_tmap_2d_16b(&tb, W, N, K, ldb, BN, BK)) return -1;
+  if (b_mn ? make_tmap_2d_16b(&tb, W, K, N, ldb, BK, 64) : make_tmap_2d_16b(&tb, W, N, K, ldb, BN, BK)) return -1;
   CollInfo ci{};
+  ci.b_mn = b_mn ? 1 : 0;
   ci.mode = MODE_AG;
   ci.nranks = nranks;
   ci.rank = rank;

@@ -38,10 +38,12 @@ __device__ __forceinline__ void na_store8(__nv_bfloat16* p, const float (&f)[8])
 
 // CTA b walks rows b, b + gridDim.x, ...; its weight-gradient partial goes to partial[b, 0:D].
 // Every CTA writes its whole partial row (zeros included), so stale scratch contents never leak in.
+// dy and dres carry no restrict qualifier: the contract lets dx alias either (each thread reads the eight
+// elements of a row it later writes, and nobody else touches them).
 template <int MAX_VEC>
 __global__ void __launch_bounds__(NA_THREADS)
 rmsnorm_bwd_noalloc_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                           const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd_in,
+                           const __nv_bfloat16* dy, const float* __restrict__ rstd_in,
                            const __nv_bfloat16* dres, __nv_bfloat16* dx, float* __restrict__ partial, int rows, int D,
                            float w_offset) {
   __shared__ float red[32];
@@ -159,6 +161,13 @@ extern "C" __attribute__((visibility("default"))) int edl_rmsnorm_bwd_noalloc(
   }
   if (!x || !w || !dy || !rstd || !dx) {
     set_last_error("edl_rmsnorm_bwd_noalloc: x, w, dy, rstd and dx are required");
+    return -1;
+  }
+  auto misaligned = [](const void* p) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+  if (misaligned(x) || misaligned(w) || misaligned(dy) || misaligned(dres) || misaligned(dx) ||
+      (dw && (reinterpret_cast<uintptr_t>(dw) & 3))) {
+    set_last_error("edl_rmsnorm_bwd_noalloc: x, w, dy, dres and dx are read and written 16 bytes at a time and "
+                   "must be 16-byte aligned (dw 4-byte aligned)");
     return -1;
   }
   float* scratch = nullptr;

@@ -85,6 +85,12 @@ class EasyDeLState:
         flat.fold_param_grads()
         self.step += 1
         lr = tx.lr_at(self.step - 1)
+        if getattr(self.model, "sp_partial_grads", False):
+            # the backward ran on sequence-sharded activations (see parallel.tp): complete the partial gradients
+            mesh = self._model_mesh()
+            if mesh is not None and mesh.tp > 1:
+                flat.sync_partial_grads_over_tp(mesh.get_group("tp"))
+            self.model.sp_partial_grads = False
         ep_group, ep = self._expert_parallel()
         if ep > 1:
             # replicated parameters: sum over the ranks' different tokens; then everything is the gradient of the

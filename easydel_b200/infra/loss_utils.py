@@ -102,13 +102,17 @@ def _normalizer(cfg: LossConfig, labels: torch.Tensor, n_valid: torch.Tensor):
 def causal_lm_loss_from_hidden(hidden: torch.Tensor, lm_head_weight: torch.Tensor, labels: torch.Tensor,
                                config: LossConfig | None = None, *, lm_head_bias=None, softcap: float = 0.0,
                                chunk_size: int | None = None, loss_scale: float = 1.0,
-                               want_accuracy: bool = True) -> LossMetrics:
+                               want_accuracy: bool = True, already_shifted: bool = False,
+                               count_group=None) -> LossMetrics:
     """Shifted next-token CE from final hidden states ``[B,T,H]`` and labels ``[B,T]``.
 
     ``loss_scale`` multiplies the result (the trainer passes ``1 / gradient_accumulation_steps``).
+    ``count_group``: ``hidden`` / ``labels`` are this rank's rows of a token axis sharded over that process
+    group; the token count that normalises the loss (and the accuracy) is then the group's, so the ranks' losses
+    add up to the loss of the whole batch. ``already_shifted``: row t of ``labels`` is the target of row t.
     """
     cfg = config or LossConfig()
-    if cfg.shift_tokens:
+    if cfg.shift_tokens and not already_shifted:
         # keep T rows (row t predicts label t+1; the last row is ignored) so no activation copy is needed
         shifted = torch.full_like(labels, cfg.ignore_index)
         shifted[..., :-1] = labels[..., 1:]
@@ -116,12 +120,22 @@ def causal_lm_loss_from_hidden(hidden: torch.Tensor, lm_head_weight: torch.Tenso
     norm = _normalizer(cfg, labels, None)
     red_scale = None
     if norm is not None:
+        if count_group is not None and str(getattr(cfg.loss_normalizing_factor, "name",
+                                                   cfg.loss_normalizing_factor)).upper() == "NUM_TOTAL_TARGET_TOKENS":
+            import torch.distributed as dist
+
+            norm = norm * dist.get_world_size(count_group)   # the labels seen here are one rank's rows
         red_scale = loss_scale / norm
     loss, n_valid, acc = F.linear_cross_entropy(
         hidden.reshape(-1, hidden.shape[-1]), lm_head_weight, labels.reshape(-1), bias=lm_head_bias,
         ignore_index=cfg.ignore_index, label_smoothing=cfg.label_smoothing, z_loss=cfg.z_loss, softcap=softcap,
         chunk_size=chunk_size or cfg.chunk_token_size or 2048, reduction_scale=red_scale,
-        loss_scale=loss_scale, want_accuracy=want_accuracy)
+        loss_scale=loss_scale, want_accuracy=want_accuracy, count_group=count_group)
+    if count_group is not None and want_accuracy:
+        import torch.distributed as dist
+
+        acc = acc.detach().clone()
+        dist.all_reduce(acc, group=count_group)   # each rank counted its correct rows over the group's total
     return LossMetrics(loss=loss, weight_sum=n_valid, accuracy=acc if want_accuracy else None)
 
 

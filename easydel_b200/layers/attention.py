@@ -145,8 +145,8 @@ class Attention(nn.Module):
     def forward(self, hidden: torch.Tensor, positions: torch.Tensor, *, segment_ids: torch.Tensor | None = None,
                 cache_view=None, attn_meta=None, cu_seqlens=None, max_seqlen=None) -> torch.Tensor:
         """hidden ``[B,T,H]``; positions ``[B,T]``. Returns ``[B,T,H]``."""
-        B, T, _ = hidden.shape
         qkv = self.qkv_proj(hidden)
+        B, T = qkv.shape[0], qkv.shape[1]   # a sequence-parallel block hands in row shards and gets [B, T] back
         if self.qk_norm == "l2_full":     # q and k are normalised over the whole projection (all heads together)
             Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
             q, k, v = qkv[..., : Hq * D].float(), qkv[..., Hq * D:(Hq + Hkv) * D].float(), qkv[..., (Hq + Hkv) * D:]

@@ -4,12 +4,15 @@ The reference's ``ParallelLinear`` family (easydel/layers/linears/_linear.py:78-
 einsum plus a sharding annotation. Here the style is metadata the runtime acts on:
 
 * ``column``: output features are split over the tensor-parallel group (each rank owns
-  ``out/tp`` rows of the ``[out, in]`` weight); the input is replicated or, under sequence
-  parallelism, all-gathered (fused into the GEMM's producer by ``parallel.tp``).
+  ``out/tp`` rows of the ``[out, in]`` weight). The input is replicated, or, while the model
+  runs a sequence-parallel block (``parallel.tp.SequenceParallelState``), row-sharded: then the
+  all-gather of the rows happens inside the GEMM (``csrc/gemm_collective.cu``, all-gather -> GEMM),
+  and the backward data-gradient product reduce-scatters its rows inside its GEMM.
 * ``row``: input features are split (each rank owns ``in/tp`` columns); partial outputs are
-  summed across the group (all-reduce, or reduce-scatter under sequence parallelism, fused
-  into the GEMM epilogue by ``parallel.tp``).
-* FSDP shards the flat parameter storage, not the module: see ``parallel.fsdp``.
+  summed across the group: an all-reduce (NCCL, or the one-shot peer kernel for decode-size
+  messages), or, in a sequence-parallel block, a reduce-scatter fused into the GEMM epilogue.
+* The data-parallel / FSDP axes shard the flat parameter storage, not the module:
+  see ``parallel.flat`` and ``parallel.dist_optim``.
 
 Weights use the torch layout ``[out, in]``; the checkpoint writer transposes them to the
 reference's ``kernel (in, out)`` on disk.
@@ -28,6 +31,8 @@ from ..ops import functional as F
 
 class ParallelLinear(nn.Module):
     parallel_style = "replicated"
+    # set by a model that can run its layers on sequence-sharded activations (``parallel.tp.SequenceParallelState``)
+    sp_state = None
 
     def __init__(self, in_features: int, out_features: int | tp.Sequence[int], bias: bool = False, *,
                  dtype: torch.dtype = torch.float32, init_std: float | None = 0.02, tp_size: int = 1,
@@ -99,6 +104,11 @@ class ColumnParallelLinear(ParallelLinear):
         if self.tp_size > 1:
             from ..parallel import tp as tpar
 
+            sp = self.sp_state
+            if sp is not None and sp.active:
+                # sequence-parallel block: ``x`` holds this rank's rows; the all-gather happens inside the GEMM
+                y = tpar.column_parallel_sp(sp, x, self.weight if w is None else w, self.bias)
+                return y if self.scale is None else y * self.scale
             x = tpar.copy_to_tp(x, self.tp_group)
         return super().forward(x, w)
 
@@ -113,6 +123,11 @@ class RowParallelLinear(ParallelLinear):
         if self.tp_size > 1:
             from ..parallel import tp as tpar
 
+            sp = self.sp_state
+            if sp is not None and sp.active:
+                # sequence-parallel block: the reduce-scatter of the output rows happens inside the GEMM
+                y = tpar.row_parallel_sp(sp, x, self.weight if w is None else w, self.bias)
+                return y if self.scale is None else y * self.scale
             return tpar.row_parallel_linear(x, self.weight if w is None else w, self.bias, self.tp_group,
                                             scale=self.scale, defer=self.defer_reduce)
         return super().forward(x, w)

@@ -377,6 +377,25 @@ class DecoderModel(EasyDeLBaseModule):
         self.layers = nn.ModuleList([DecoderLayer(config, layer_spec(i), i, pd) for i in range(spec.num_layers)])
         if spec.final_norm:
             self.norm = _norm(spec, pd)
+        self._setup_sequence_parallel(config)
+
+    def _setup_sequence_parallel(self, config) -> None:
+        """Dense attention + MLP stacks can keep the residual stream sharded by rows over the tensor-parallel
+        group between their linears (all-gather -> GEMM into the column layers, GEMM -> reduce-scatter out of the
+        row layers). The state object is shared with every tensor-parallel linear of the layers."""
+        from ...layers.linears import ParallelLinear
+        from ...parallel.tp import SequenceParallelState
+
+        self.sp = SequenceParallelState()
+        tp_size, _, tp_group = _tp_of(config)
+        self._sp_group = tp_group
+        plain = all(not l.is_moe and not l.is_linear and l.ltype != "lightning" and l.spec.mla is None
+                    and l.spec.ssm_branch is None and l.spec.normed_residual is None for l in self.layers)
+        self.sp_capable = bool(tp_size > 1 and plain and getattr(config, "tp_sequence_parallel", True))
+        if self.sp_capable:
+            for m in self.layers.modules():
+                if isinstance(m, ParallelLinear) and m.tp_size > 1:
+                    m.sp_state = self.sp
 
     def get_input_embeddings(self):
         return self.embed_tokens
@@ -390,9 +409,12 @@ class DecoderModel(EasyDeLBaseModule):
                 position_ids: torch.Tensor | None = None, segment_ids: torch.Tensor | None = None,
                 inputs_embeds: torch.Tensor | None = None, past_key_values=None, cache_metadata=None,
                 output_hidden_states: bool = False, output_router_logits: bool = False,
-                deepstack_embeds: tp.Sequence[torch.Tensor] | None = None, **_):
+                deepstack_embeds: tp.Sequence[torch.Tensor] | None = None, sequence_parallel: bool = False, **_):
         """``deepstack_embeds[i]`` ``[B, T, H]`` (zeros outside image positions) is added to the residual stream
-        after layer ``i`` (Qwen3-VL feeds intermediate vision features to the first decoder layers)."""
+        after layer ``i`` (Qwen3-VL feeds intermediate vision features to the first decoder layers).
+
+        ``sequence_parallel``: the caller takes ``last_hidden_state`` as this rank's row shard ``[1, B*T/tp, H]``
+        (rows of the flattened ``[B*T]`` token axis) when ``self.sp.active`` is set on return."""
         spec = self.spec
         if inputs_embeds is None:
             if input_ids.dim() == 1:
@@ -427,6 +449,15 @@ class DecoderModel(EasyDeLBaseModule):
             x = x + self.embed_positions(position_ids + spec.learned_pos_offset)
         if spec.embed_layernorm:
             x = self.embed_layernorm(x)
+        use_sp = bool(sequence_parallel and self.sp_capable and past_key_values is None and not output_hidden_states
+                      and deepstack_embeds is None and (B * T) % self.config.mesh.tp == 0)
+        if use_sp:
+            from ...parallel import tp as tpar
+
+            self.sp.begin(self._sp_group, B, T)
+            x = tpar.shard_rows(self.sp, x)
+        else:
+            self.sp.end()
         policy = self.gradient_checkpointing_policy() not in ("", "everything_saveable")
         pending = None
         all_hidden = [] if output_hidden_states else None
@@ -513,11 +544,13 @@ class DecoderForCausalLM(EasyDeLBaseModule):
 
     def forward(self, input_ids=None, attention_mask=None, position_ids=None, segment_ids=None, inputs_embeds=None,
                 past_key_values=None, cache_metadata=None, output_hidden_states=False, output_router_logits=False,
-                apply_lm_head: bool = True, labels: torch.Tensor | None = None, **kw):
+                apply_lm_head: bool = True, labels: torch.Tensor | None = None, sequence_parallel: bool = False,
+                **kw):
         out = self.model(input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
                          segment_ids=segment_ids, inputs_embeds=inputs_embeds, past_key_values=past_key_values,
                          cache_metadata=cache_metadata, output_hidden_states=output_hidden_states,
-                         output_router_logits=output_router_logits, deepstack_embeds=kw.get("deepstack_embeds"))
+                         output_router_logits=output_router_logits, deepstack_embeds=kw.get("deepstack_embeds"),
+                         sequence_parallel=sequence_parallel and not apply_lm_head)
         hidden = out.last_hidden_state
         logits = self.apply_lm_head(hidden) if apply_lm_head else None
         rl = getattr(out, "router_logits", None)
@@ -534,6 +567,8 @@ class DecoderForCausalLM(EasyDeLBaseModule):
     def _compute_task_loss(self, labels, loss_config: LossConfig, loss_scale, call, loss_kwargs):
         call = dict(call)
         call["apply_lm_head"] = False
+        if getattr(self.model, "sp_capable", False) and type(self).forward is DecoderForCausalLM.forward:
+            call["sequence_parallel"] = True   # tensor-parallel dense stacks keep the token rows sharded
         attention_mask = call.get("attention_mask")
         out = self(**call)
         if attention_mask is not None:
@@ -542,6 +577,27 @@ class DecoderForCausalLM(EasyDeLBaseModule):
         hidden = out.last_hidden_state
         if spec.logit_scale is not None:
             hidden = hidden * spec.logit_scale
+        sp = getattr(self.model, "sp", None)
+        if sp is not None and sp.active:
+            # Every rank holds the hidden states of its own rows: it computes the loss terms of those rows
+            # (normalised by the group-wide token count), so the loss is the sum over the group and every
+            # replicated parameter's gradient is a partial sum (``sp_partial_grads``, summed before the update).
+            from ...parallel import tp as tpar
+
+            shifted = labels
+            if loss_config.shift_tokens:
+                shifted = torch.full_like(labels, loss_config.ignore_index)
+                shifted[..., :-1] = labels[..., 1:]
+            metrics = causal_lm_loss_from_hidden(hidden, self.lm_head_weight(), tpar.shard_rows(sp, shifted),
+                                                 loss_config, lm_head_bias=self.lm_head_bias(),
+                                                 softcap=spec.logit_softcap,
+                                                 chunk_size=getattr(self.config, "lmhead_chunksize", None),
+                                                 loss_scale=loss_scale, already_shifted=True, count_group=sp.group,
+                                                 **loss_kwargs)
+            metrics.loss = tpar.sum_value_over_group(metrics.loss, sp.group)
+            if torch.is_grad_enabled():
+                self.sp_partial_grads = True
+            return out, metrics
         metrics = causal_lm_loss_from_hidden(hidden, self.lm_head_weight(), labels, loss_config,
                                              lm_head_bias=self.lm_head_bias(), softcap=spec.logit_softcap,
                                              chunk_size=getattr(self.config, "lmhead_chunksize", None),

@@ -16,7 +16,9 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libedl_b200.so"
+# EDL_LIB_PATH points at another build of the library (e.g. one compiled with bounds checks)
+_LIB_PATH = Path(os.environ.get("EDL_LIB_PATH") or
+                 Path(__file__).resolve().parent.parent / "lib" / "libedl_b200.so")
 _lib = None
 _lock = threading.Lock()
 _status: dict[int, torch.Tensor] = {}

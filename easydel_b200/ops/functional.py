@@ -215,12 +215,16 @@ class _LinearCEFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, h, w, labels, bias, ignore_index, label_smoothing, z_loss, softcap, chunk, reduction_scale,
-                want_acc, grad_enabled, loss_scale):
+                want_acc, grad_enabled, loss_scale, count_group=None):
         T, H = h.shape
         V = w.shape[0]
         dev = h.device
         valid = (labels != ignore_index)
         n_valid = valid.sum().to(torch.float32)
+        if count_group is not None:   # rows are sharded over this group: normalise by the group's token count
+            import torch.distributed as dist
+
+            dist.all_reduce(n_valid, group=count_group)
         # gscale tensor = 1/max(n_valid,1) * reduction_scale, consumed on-device by the CE kernel
         if reduction_scale is None:
             gs = (float(loss_scale) / n_valid.clamp_min(1.0)).reshape(1)
@@ -270,14 +274,14 @@ class _LinearCEFn(torch.autograd.Function):
             gh = dh * dloss.to(dh.dtype)
         if dw is not None:
             gw = (dw * dloss).to(ctx.w_dtype)
-        return gh, gw, None, None, None, None, None, None, None, None, None, None, None
+        return gh, gw, None, None, None, None, None, None, None, None, None, None, None, None
 
 
 def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, *, bias=None,
                          ignore_index: int = -100, label_smoothing: float = 0.0, z_loss: float = 0.0,
                          softcap: float = 0.0, chunk_size: int = 2048, reduction_scale: float | None = None,
                          loss_scale: float = 1.0,
-                         want_accuracy: bool = False):
+                         want_accuracy: bool = False, count_group=None):
     """Mean (over non-ignored labels) cross-entropy of ``h @ w.T`` without materialising the logits.
 
     ``h`` is ``[T, H]``, ``labels`` ``[T]`` (already shifted by the caller). Returns
@@ -295,7 +299,7 @@ def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
         if not h2.is_contiguous():
             h2 = h2.contiguous()
         return _LinearCEFn.apply(h2, w, lab, bias, ignore_index, label_smoothing, z_loss, softcap, chunk_size,
-                                 reduction_scale, want_accuracy, torch.is_grad_enabled(), loss_scale)
+                                 reduction_scale, want_accuracy, torch.is_grad_enabled(), loss_scale, count_group)
     total = h2.new_zeros((), dtype=torch.float32)
     correct = h2.new_zeros((), dtype=torch.float32)
     for s in range(0, h2.shape[0], chunk_size):
@@ -308,6 +312,10 @@ def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
             correct = correct + ((zc.argmax(-1) == lab[s:s + chunk_size]) & (lab[s:s + chunk_size] != ignore_index)
                                  ).sum()
     n_valid = (lab != ignore_index).sum().to(torch.float32)
+    if count_group is not None:
+        import torch.distributed as dist
+
+        dist.all_reduce(n_valid, group=count_group)
     scale = (loss_scale / n_valid.clamp_min(1.0)) if reduction_scale is None else reduction_scale
     return total * scale, n_valid, correct / n_valid.clamp_min(1.0)
 

@@ -175,6 +175,23 @@ class FlatParams:
             dist.all_reduce(parts[1:2], group=mesh.get_group("ep"))
         return sumsq + (parts - local).sum()
 
+    def sync_partial_grads_over_tp(self, group) -> None:
+        """After a sequence-parallel backward every rank of the tensor-parallel group has seen only its own token
+        rows, so the gradient of each parameter that is not a tensor-parallel shard (norm scales, embeddings, the
+        LM head, row-parallel biases) is a partial sum: add the group's pieces."""
+        import torch.distributed as dist
+
+        tp_runs = self.model_parallel_ranges()["tp"]
+        pos, runs = 0, []
+        for lo, hi in tp_runs:
+            if lo > pos:
+                runs.append((pos, lo))
+            pos = max(pos, hi)
+        if pos < self.numel:
+            runs.append((pos, self.numel))
+        for lo, hi in runs:
+            dist.all_reduce(self.grad[lo:hi], group=group)
+
     def sync_replicated_grads(self, group) -> None:
         """Sums the gradients of the replicated parameters over the expert-parallel group (each rank saw different
         tokens); expert weights already received every token's contribution through the token exchange."""

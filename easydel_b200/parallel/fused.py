@@ -23,10 +23,10 @@ from ..ops import _lib
 
 _lib.register("edl_gemm_reduce_scatter", _lib.i32,
               [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i64, _lib.i64,
-               _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.vp])
+               _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.vp, _lib.i32])
 _lib.register("edl_allgather_gemm", _lib.i32,
               [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i64, _lib.i64,
-               _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.vp])
+               _lib.vp, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.i32, _lib.vp, _lib.vp, _lib.i32])
 
 _FLAG_BYTES = 256
 
@@ -83,9 +83,10 @@ class GemmReduceScatter:
         self.epoch = 0
 
     def __call__(self, a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None,
-                 bias: torch.Tensor | None = None, wait_ms: int = 2000) -> torch.Tensor:
+                 bias: torch.Tensor | None = None, wait_ms: int = 2000, b_mn: bool = False) -> torch.Tensor:
+        """``b_mn``: ``w`` is stored ``[K, N]`` (the product is ``a @ w``, a data-gradient GEMM)."""
         M, K = a.shape
-        N = w.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
         if M != self.rows * self.world or N != self.n_out:
             raise ValueError(f"shape ({M},{N}) does not match the plan ({self.rows * self.world},{self.n_out})")
         self.epoch += 1
@@ -94,7 +95,7 @@ class GemmReduceScatter:
         _lib.call("edl_gemm_reduce_scatter", a.data_ptr(), w.data_ptr(), out.data_ptr(), _lib.ptr(residual),
                   _lib.ptr(bias), M, N, K, a.stride(0), w.stride(0), C.cast(self.stage_ptrs[s], C.c_void_p),
                   C.cast(self.flag_ptrs[s], C.c_void_p), self.counters.data_ptr(), self.world, self.rank,
-                  self.epoch, wait_ms, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+                  self.epoch, wait_ms, _lib.status_word(a.device).data_ptr(), _lib.stream_ptr(), int(b_mn))
         return out
 
 
@@ -112,17 +113,18 @@ class AllGatherGemm:
         self.counters = torch.zeros(self.world * (rows_per_rank // 128), dtype=torch.int32, device=device)
 
     def __call__(self, a_shard: torch.Tensor | None, w: torch.Tensor, bias: torch.Tensor | None = None,
-                 copy_own: bool = True, wait_ms: int = 2000):
-        """``a_shard=None`` means the caller already wrote its rows into ``self.shard``."""
+                 copy_own: bool = True, wait_ms: int = 2000, b_mn: bool = False):
+        """``a_shard=None`` means the caller already wrote its rows into ``self.shard``. ``b_mn``: ``w`` is
+        stored ``[K, N]`` (the product is ``gather(a) @ w``)."""
         if a_shard is not None:
             self.shard.copy_(a_shard)
-        N = w.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
         c = torch.empty(self.world * self.rows, N, dtype=torch.bfloat16, device=w.device)
         self.handle.barrier(channel=0)     # every rank's shard is in place
         _lib.call("edl_allgather_gemm", C.cast(self.shard_ptrs, C.c_void_p), w.data_ptr(), c.data_ptr(),
                   _lib.ptr(bias), self.gathered.data_ptr(), self.rows, N, self.k, w.stride(0), c.stride(0),
                   self.counters.data_ptr(), self.world, self.rank, self.n_copy, int(copy_own), wait_ms,
-                  _lib.status_word(w.device).data_ptr(), _lib.stream_ptr())
+                  _lib.status_word(w.device).data_ptr(), _lib.stream_ptr(), int(b_mn))
         self.handle.barrier(channel=1)     # nobody rewrites a shard that a peer is still reading
         return c, self.gathered
 

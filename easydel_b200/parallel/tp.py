@@ -210,3 +210,237 @@ def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, bias, group, scale=Non
     if bias is not None:
         y = y + bias
     return y if scale is None else y * scale
+
+
+# ------------------------------------------------------------------------------------------------
+# Sequence-parallel tensor parallelism: the residual stream between the linears is sharded by rows
+# (tokens) over the group; a column-parallel linear all-gathers its input inside the GEMM, a
+# row-parallel linear reduce-scatters its output inside the GEMM (csrc/gemm_collective.cu). The
+# backward products are the mirrored pair. On CPU ranks (gloo) and for shapes the kernels do not
+# take, the same algebra runs through torch.distributed collectives.
+# ------------------------------------------------------------------------------------------------
+class SequenceParallelState:
+    """What the linears need to know while a model runs with sequence-sharded activations.
+
+    Set by the model's forward before its layers run and left in place afterwards, because the
+    activation-checkpoint recompute of a layer happens during backward."""
+
+    def __init__(self):
+        self.active = False
+        self.group = None
+        self.world = 1
+        self.rank = 0
+        self.batch = 1
+        self.seq = 0
+
+    @property
+    def rows(self) -> int:
+        return self.batch * self.seq
+
+    @property
+    def rows_local(self) -> int:
+        return self.rows // self.world
+
+    def begin(self, group, batch: int, seq: int) -> None:
+        self.active, self.group = True, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.batch, self.seq = batch, seq
+
+    def end(self) -> None:
+        self.active = False
+
+
+_PLANS: dict[tuple, tp.Any] = {}
+
+
+def sequence_parallel_usable(group, batch: int, seq: int, hidden: int, device) -> bool:
+    """Rows must split evenly; the fused kernels additionally want 128-row shards and a hidden size that is a
+    multiple of 128 (other shapes take the collective + GEMM path, which has no such limits)."""
+    if group is None:
+        return False
+    world = dist.get_world_size(group)
+    return world > 1 and (batch * seq) % world == 0
+
+
+def _fused_ok(sp, x: torch.Tensor, rows_local: int, k: int, n: int) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and _lib.available() and rows_local % 128 == 0
+            and k % 128 == 0 and n % 8 == 0 and sp.world <= 8)
+
+
+def _plan(sp, kind: str, rows_local: int, width: int, device):
+    from . import fused
+
+    key = (kind, id(sp.group), rows_local, width, device.index)
+    p = _PLANS.get(key)
+    if p is None:
+        if kind == "ag":
+            p = fused.AllGatherGemm(sp.group, rows_local, width, device)
+        else:
+            p = fused.GemmReduceScatter(sp.group, rows_local, width, device)
+        _PLANS[key] = p
+    return p
+
+
+def _all_gather_rows(sp, x: torch.Tensor) -> torch.Tensor:
+    parts = [torch.empty_like(x) for _ in range(sp.world)]
+    dist.all_gather(parts, x.contiguous(), group=sp.group)
+    return torch.cat(parts, 0)
+
+
+def _reduce_scatter_rows(sp, y: torch.Tensor) -> torch.Tensor:
+    """Sum over the group, keep this rank's row block."""
+    rows = y.shape[0] // sp.world
+    if y.is_cuda and dist.get_backend(sp.group) != "gloo":
+        out = torch.empty(rows, y.shape[1], dtype=y.dtype, device=y.device)
+        dist.reduce_scatter_tensor(out, y.contiguous(), group=sp.group)
+        return out
+    y = y.contiguous().clone()
+    dist.all_reduce(y, group=sp.group)
+    return y[sp.rank * rows:(sp.rank + 1) * rows].clone()
+
+
+def _ag_gemm(sp, x_shard: torch.Tensor, w: torch.Tensor, b_mn: bool, keep_gathered: bool = False):
+    """``(all_gather_rows(x_shard) @ op(w), gathered x)``; ``op(w) = w.T`` for ``[N, K]`` weights, ``w`` itself
+    when ``b_mn`` (weights stored ``[K, N]``)."""
+    from ..ops import functional as F
+
+    k = x_shard.shape[1]
+    n = w.shape[1] if b_mn else w.shape[0]
+    if _fused_ok(sp, x_shard, x_shard.shape[0], k, n) and w.stride(-1) == 1:
+        c, g = _plan(sp, "ag", x_shard.shape[0], k, x_shard.device)(x_shard, w, b_mn=b_mn)
+        # the gathered rows live in a buffer of the plan that its next call overwrites
+        return c, (g.clone() if keep_gathered else g)
+    g = _all_gather_rows(sp, x_shard)
+    with torch.no_grad():
+        return (g @ w if b_mn else F.linear(g, w, None)), g
+
+
+def _gemm_rs(sp, x: torch.Tensor, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
+    """``reduce_scatter_rows(x @ op(w))``: every rank holds a slice of the reduction dimension."""
+    from ..ops import functional as F
+
+    n = w.shape[1] if b_mn else w.shape[0]
+    rows_local = x.shape[0] // sp.world
+    if _fused_ok(sp, x, rows_local, 128, n) and x.shape[1] % 8 == 0 and w.stride(-1) == 1 and x.stride(-1) == 1:
+        return _plan(sp, "rs", rows_local, n, x.device)(x, w, b_mn=b_mn)
+    with torch.no_grad():
+        y = x @ w if b_mn else F.linear(x, w, None)
+    return _reduce_scatter_rows(sp, y)
+
+
+def _weight_grad(w: torch.Tensor, dy: torch.Tensor, x: torch.Tensor):
+    """dW[N, K] = dy[T, N]^T x[T, K]: accumulated into ``w.main_grad`` when the flat gradient buffer exists."""
+    from ..ops import kernels as K
+
+    mg = getattr(w, "main_grad", None)
+    if dy.is_cuda and _lib.available() and dy.dtype == torch.bfloat16:
+        if mg is not None:
+            K.gemm(dy, x, a_mn=True, b_mn=True, out=mg, accumulate=True)
+            w.grad_added_to_main_grad = True
+            return None
+        return K.gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32).to(w.dtype)
+    return (dy.float().t() @ x.float()).to(w.dtype)
+
+
+class _ColumnSP(torch.autograd.Function):
+    """y[T, N_local] = all_gather_rows(x[T/n, K]) @ w[N_local, K]^T  (+ bias)."""
+
+    @staticmethod
+    def forward(ctx, sp, x_shard, w, bias):
+        ctx.sp = sp
+        y, g = _ag_gemm(sp, x_shard, w, b_mn=False, keep_gathered=True)   # the gathered input is needed for dW
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(g, w)
+        ctx.has_bias = bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        g, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = _gemm_rs(ctx.sp, dy, w, b_mn=True) if ctx.needs_input_grad[1] else None   # dY[T, N_l] @ W[N_l, K]
+        dw = _weight_grad(w, dy, g) if ctx.needs_input_grad[2] else None
+        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[3] else None
+        return None, dx, dw, db
+
+
+class _RowSP(torch.autograd.Function):
+    """y[T/n, N] = reduce_scatter_rows(x[T, K_local] @ w[N, K_local]^T)."""
+
+    @staticmethod
+    def forward(ctx, sp, x, w):
+        ctx.sp = sp
+        ctx.save_for_backward(x, w)
+        return _gemm_rs(sp, x.contiguous(), w, b_mn=False)
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        x, w = ctx.saved_tensors
+        dx, g = _ag_gemm(ctx.sp, dy_shard.contiguous(), w, b_mn=True)   # gather(dY)[T, N] @ W[N, K_l]
+        dw = _weight_grad(w, g, x.reshape(-1, x.shape[-1])) if ctx.needs_input_grad[2] else None
+        return None, (dx if ctx.needs_input_grad[1] else None), dw
+
+
+def column_parallel_sp(sp, x_shard: torch.Tensor, w: torch.Tensor, bias) -> torch.Tensor:
+    """Column-parallel linear on a row-sharded input; returns ``[batch, seq, N_local]``."""
+    x2 = x_shard.reshape(-1, x_shard.shape[-1])
+    y = _ColumnSP.apply(sp, x2, w, bias)
+    return y.view(sp.batch, sp.seq, y.shape[-1])
+
+
+def row_parallel_sp(sp, x: torch.Tensor, w: torch.Tensor, bias) -> torch.Tensor:
+    """Row-parallel linear whose output comes back row-sharded: ``[1, rows/n, N]``. The bias (replicated) is
+    added once per row, after the reduction."""
+    x2 = x.reshape(-1, x.shape[-1])
+    y = _RowSP.apply(sp, x2, w)
+    if bias is not None:
+        y = y + bias
+    return y.view(1, y.shape[0], y.shape[1])
+
+
+class _GatherRows(torch.autograd.Function):
+    """All-gather of row shards whose consumer is replicated on every rank (backward keeps this rank's rows)."""
+
+    @staticmethod
+    def forward(ctx, sp, x):
+        ctx.sp = sp
+        return _all_gather_rows(sp, x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        sp = ctx.sp
+        n = dy.shape[0] // sp.world
+        return None, dy[sp.rank * n:(sp.rank + 1) * n].contiguous()
+
+
+def gather_rows(sp, x: torch.Tensor) -> torch.Tensor:
+    """``[1, rows/n, H]`` shards -> ``[batch, seq, H]`` on every rank."""
+    y = _GatherRows.apply(sp, x.reshape(-1, x.shape[-1]))
+    return y.view(sp.batch, sp.seq, y.shape[-1])
+
+
+def shard_rows(sp, x: torch.Tensor) -> torch.Tensor:
+    """This rank's block of the flattened ``[batch * seq, ...]`` rows, as ``[1, rows/n, ...]``."""
+    flat = x.reshape(sp.rows, *x.shape[2:])
+    n = sp.rows_local
+    return flat[sp.rank * n:(sp.rank + 1) * n].unsqueeze(0)
+
+
+class _SumOverGroupValue(torch.autograd.Function):
+    """Forward: sum of a scalar over the group (for reporting); backward: identity (each rank differentiates
+    its own term of the sum)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        y = x.detach().clone()
+        dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        return dy, None
+
+
+def sum_value_over_group(x: torch.Tensor, group) -> torch.Tensor:
+    return _SumOverGroupValue.apply(x, group)

@@ -36,12 +36,20 @@ def token_logprobs(model, input_ids: torch.Tensor, attention_mask: torch.Tensor 
     spec = getattr(model, "spec", None)
     direct = w is not None and not (spec is not None and spec.logit_softcap)
     if direct:
-        out = model(input_ids=input_ids, attention_mask=attention_mask, apply_lm_head=False, **model_kwargs)
-        h = out.last_hidden_state[:, :-1]
-        if spec is not None and spec.logit_scale is not None:
-            h = h * spec.logit_scale
-        lp, ent = F.linear_token_logprob(h, w, labels, bias=b, temperature=temperature, chunk_size=chunk_size,
-                                         want_entropy=want_entropy)
+        sp_kw = {}
+        if getattr(getattr(model, "model", None), "sp_capable", False) and "sequence_parallel" not in model_kwargs:
+            sp_kw["sequence_parallel"] = True   # tensor-parallel dense stacks keep the token rows sharded
+        out = model(input_ids=input_ids, attention_mask=attention_mask, apply_lm_head=False, **sp_kw, **model_kwargs)
+        sp = getattr(getattr(model, "model", None), "sp", None)
+        if sp is not None and sp.active:
+            lp, ent = _token_logprobs_row_sharded(model, sp, out.last_hidden_state, labels, w, b, spec, temperature,
+                                                  chunk_size, want_entropy)
+        else:
+            h = out.last_hidden_state[:, :-1]
+            if spec is not None and spec.logit_scale is not None:
+                h = h * spec.logit_scale
+            lp, ent = F.linear_token_logprob(h, w, labels, bias=b, temperature=temperature, chunk_size=chunk_size,
+                                             want_entropy=want_entropy)
     else:
         out = model(input_ids=input_ids, attention_mask=attention_mask, **model_kwargs)
         logits = out.logits[:, :-1].float() / temperature
@@ -53,6 +61,34 @@ def token_logprobs(model, input_ids: torch.Tensor, attention_mask: torch.Tensor 
     if ent is not None:
         ent = ent * m
     return lp, m, ent, out
+
+
+def _token_logprobs_row_sharded(model, sp, h_shard, labels, w, b, spec, temperature, chunk_size, want_entropy):
+    """Log-probabilities when the backbone returned this rank's rows of the flattened token axis (sequence-parallel
+    tensor parallelism). Each rank scores its rows; the rows of all ranks are then summed into the full
+    ``[B, T-1]`` table on every rank. What follows is the same computation on every rank, so each rank
+    back-propagates only through its own rows and parameter gradients are partial sums over the group
+    (``sp_partial_grads``: completed before the optimizer update)."""
+    from ..parallel import tp as tpar
+
+    B, T = sp.batch, sp.seq
+    full_labels = torch.full((B, T), -100, dtype=labels.dtype, device=labels.device)
+    full_labels[:, :-1] = labels
+    lab = tpar.shard_rows(sp, full_labels).reshape(-1)
+    h = h_shard.reshape(-1, h_shard.shape[-1])
+    if spec is not None and spec.logit_scale is not None:
+        h = h * spec.logit_scale
+    lp, ent = F.linear_token_logprob(h[None], w, lab[None], bias=b, temperature=temperature, chunk_size=chunk_size,
+                                     want_entropy=want_entropy)
+    n, r = sp.rows_local, sp.rank
+
+    def spread(v):
+        v = torch.nn.functional.pad(v.reshape(-1), (r * n, (sp.world - 1 - r) * n))
+        return tpar.sum_value_over_group(v, sp.group).view(B, T)[:, :-1]
+
+    if torch.is_grad_enabled() and h.requires_grad:
+        model.sp_partial_grads = True
+    return spread(lp), (spread(ent) if ent is not None else None)
 
 
 def sequence_logprobs(model, input_ids, attention_mask=None, loss_mask=None, *, average: bool = False, **kw):

@@ -349,6 +349,12 @@ class BaseTrainer:
             metrics = self.step_metrics.calculate(lm, step, epoch, bsz * self._dp_world, seq,
                                                   state.tx.lr_at(step - 1))
             metrics.update(extra)
+            if self.device.type == "cuda":
+                # The loss read-back above synchronised the stream: a kernel whose bounded wait ran out has written
+                # its code by now. Stop here rather than train on the uninitialised output it left behind.
+                from ..ops import _lib
+
+                _lib.check_status(self.device)
             if not math.isfinite(metrics["train/loss"]) and self.loss_config.break_on_nan:
                 self._break_requested = True
             for w in a.watchers:

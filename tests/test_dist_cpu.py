@@ -286,6 +286,7 @@ def _tp_clip_worker(rank, world):
         return st.apply_gradients()
 
     n_full, n_tp = step(full), step(model)
+    assert model.model.sp.active and model.model.sp.rows_local == 16, "the tp model ran sequence-parallel"
     assert float(n_full) > 0.05, "the step must actually clip"
     assert abs(float(n_full) - float(n_tp)) < 1e-4 * max(1.0, float(n_full)), (float(n_full), float(n_tp))
     norms = [torch.zeros(1) for _ in range(world)]
@@ -302,3 +303,50 @@ def _tp_clip_worker(rank, world):
 
 def test_tensor_parallel_clip_uses_global_norm():
     _run(_tp_clip_worker, 2)
+
+
+def _tp_logprob_worker(rank, world):
+    """Sequence log-probabilities (the DPO / GRPO building block) of a tensor-parallel model running on
+    sequence-sharded activations equal the single-process ones, in value and in gradients."""
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+    from easydel_b200.parallel.mesh import DeviceMesh
+    from easydel_b200.trainers._logprob_utils import sequence_logprobs
+    from easydel_b200.utils.parameters_transformation import shard_internal_state_for_tp
+
+    kw = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=32)
+    one = LlamaConfig(**kw)
+    one.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), one.sharding_axis_names, 0, 1))
+    torch.manual_seed(5)
+    full = LlamaForCausalLM(one, dtype=torch.float32, param_dtype=torch.float32)
+    cfg = LlamaConfig(sharding_axis_dims=(1, 1, 1, world, 1), **kw)
+    model = LlamaForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32)
+    model.load_state_dict(shard_internal_state_for_tp(model, full.state_dict()))
+    ids = torch.randint(0, 128, (3, 12), generator=torch.Generator().manual_seed(4))
+    mask = torch.ones_like(ids)
+    mask[1, 9:] = 0
+    wts = torch.tensor([1.0, -2.0, 0.5])
+
+    def run(m):
+        s, n, _ = sequence_logprobs(m, ids, attention_mask=mask, loss_mask=mask)
+        (s * wts).sum().backward()
+        return s.detach(), n
+
+    s_full, n_full = run(full)
+    s_tp, n_tp = run(model)
+    assert model.model.sp.active and getattr(model, "sp_partial_grads", False)
+    assert torch.allclose(s_tp, s_full, atol=1e-5) and torch.equal(n_tp, n_full)
+    want = shard_internal_state_for_tp(model, {k: p.grad for k, p in full.named_parameters()})
+    mods = dict(model.named_modules())
+    for k, p in model.named_parameters():
+        g = p.grad.clone()
+        mod = mods[k.rpartition(".")[0]]
+        sharded = getattr(mod, "tp_size", 1) > 1 and getattr(mod, "parallel_style", "") in ("column", "row") \
+            and not (mod.parallel_style == "row" and k.endswith("bias"))
+        if not sharded:
+            dist.all_reduce(g)     # partial sums over the token shards
+        assert torch.allclose(g, want[k], atol=1e-5), k
+
+
+def test_tensor_parallel_sequence_logprobs_match():
+    _run(_tp_logprob_worker, 2)

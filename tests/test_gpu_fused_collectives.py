@@ -56,6 +56,22 @@ def test_allgather_gemm_one_rank(Ms, N, K):
     assert torch.equal(g, a)   # the copier ring moved every byte
 
 
+def test_fused_collectives_mn_major_weight_one_rank():
+    """The data-gradient forms: the second operand is stored [K, N] (a linear layer's weight read as dY @ W)."""
+    from easydel_b200.parallel.fused import AllGatherGemm, GemmReduceScatter
+
+    dev = torch.device("cuda:0")
+    torch.manual_seed(1)
+    M, N, K = 512, 768, 384
+    a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    w_kn = torch.randn(K, N, device=dev, dtype=torch.bfloat16) * 0.05
+    out = GemmReduceScatter(None, M, N, dev)(a, w_kn, b_mn=True)
+    assert _rel_err(out, a.float() @ w_kn.float()) < 1e-2
+    c, g = AllGatherGemm(None, M, K, dev)(a, w_kn, b_mn=True)
+    assert _rel_err(c, a.float() @ w_kn.float()) < 1e-2
+    assert torch.equal(g, a)
+
+
 def _worker(rank, world, port, out_q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
@@ -101,7 +117,7 @@ def _worker(rank, world, port, out_q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_fused_collectives_multi_gpu(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

@@ -91,35 +91,50 @@ def _allreduce_worker(rank, world):
 
 
 def _tp_forward_worker(rank, world):
+    """Tensor-parallel Llama against the single-GPU model: inference logits (all-reduce path), then a training
+    step on sequence-sharded activations (all-gather -> GEMM and GEMM -> reduce-scatter kernels in both
+    directions) whose loss and gradients must match."""
+    import torch.distributed as dist
+
     from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
     from easydel_b200.parallel.mesh import DeviceMesh
     from easydel_b200.utils.parameters_transformation import shard_internal_state_for_tp
 
-    kw = dict(vocab_size=2048, hidden_size=512, intermediate_size=1408, num_hidden_layers=2, num_attention_heads=8,
-              num_key_value_heads=2, head_dim=64, max_position_embeddings=512)
+    kw = dict(vocab_size=2048, hidden_size=512, intermediate_size=1536, num_hidden_layers=2, num_attention_heads=8,
+              num_key_value_heads=8, head_dim=64, max_position_embeddings=512)
     full_cfg = LlamaConfig(**kw)
     full_cfg.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), full_cfg.sharding_axis_names, 0, 1))
     torch.manual_seed(0)
     full = LlamaForCausalLM(full_cfg, dtype=torch.bfloat16, param_dtype=torch.bfloat16).cuda().eval()
-    cfg = LlamaConfig(sharding_axis_dims=(1, 1, 1, 2, 1), **kw)
+    cfg = LlamaConfig(sharding_axis_dims=(1, 1, 1, world, 1), **kw)
     model = LlamaForCausalLM(cfg, dtype=torch.bfloat16, param_dtype=torch.bfloat16).cuda().eval()
-    assert model.model.layers[0].self_attn.num_heads == 4
+    assert model.model.layers[0].self_attn.num_heads == 8 // world
     model.load_state_dict(shard_internal_state_for_tp(model, full.state_dict()))
-    ids = torch.randint(0, 2048, (2, 128), generator=torch.Generator().manual_seed(1)).cuda()
+    ids = torch.randint(0, 2048, (2, 512), generator=torch.Generator().manual_seed(1)).cuda()
     with torch.no_grad():
         a = full(input_ids=ids).logits.float()
         b = model(input_ids=ids).logits.float()
     assert (a - b).abs().max().item() < 0.125, (a - b).abs().max()
-    # training path: gradients of a replicated parameter agree with the single-GPU model
     model.train(), full.train()
     _, m1 = full.compute_loss(input_ids=ids, labels=ids)
     _, m2 = model.compute_loss(input_ids=ids, labels=ids)
+    assert model.model.sp.active and model.model.sp.rows_local == 1024 // world
     assert abs(float(m1.loss) - float(m2.loss)) < 2e-2
     m1.loss.backward()
     m2.loss.backward()
+    assert model.sp_partial_grads
+    # a replicated parameter: partial sums over the token shards
     g1 = full.model.norm.weight.grad.float()
-    g2 = model.model.norm.weight.grad.float()
+    g2 = model.model.norm.weight.grad.float().clone()
+    dist.all_reduce(g2)
     assert ((g1 - g2).norm() / g1.norm()).item() < 0.05
+    # sharded parameters: this rank's slice of the full gradient
+    want = shard_internal_state_for_tp(model, {k: p.grad for k, p in full.named_parameters()})
+    for name in ("model.layers.0.self_attn.qkv_proj.weight", "model.layers.1.mlp.down_proj.weight",
+                 "model.layers.0.self_attn.o_proj.weight", "model.layers.1.mlp.gate_up_proj.weight"):
+        g = dict(model.named_parameters())[name].grad.float()
+        w = want[name].float()
+        assert ((g - w).norm() / w.norm()).item() < 0.05, name
 
 
 def _dist_optim_worker(rank, world):
@@ -168,8 +183,9 @@ def test_peer_allreduce_matches_nccl():
     _run(_allreduce_worker)
 
 
-def test_tensor_parallel_forward_and_loss():
-    _run(_tp_forward_worker)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_forward_and_loss(world):
+    _run(_tp_forward_worker, world)
 
 
 def test_sharded_optimizer_peer_kernels():

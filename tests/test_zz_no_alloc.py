@@ -70,6 +70,45 @@ def test_noalloc_matches_regular_entry_point_twice():
         assert torch.allclose(dw, 2 * dw_ref, atol=0.3, rtol=2e-2)
 
 
+def _torch_reference(x, w, dy, rstd, dres):
+    """RMSNorm backward in plain fp32 PyTorch."""
+    xf, wf, dyf = x.float(), w.float(), dy.float()
+    xhat = xf * rstd[:, None]
+    g = dyf * wf
+    dx = rstd[:, None] * (g - xhat * (g * xhat).mean(-1, keepdim=True))
+    if dres is not None:
+        dx = dx + dres.float()
+    return dx, (dyf * xhat).sum(0)
+
+
+def test_noalloc_matches_fp32_reference_and_allows_aliasing():
+    """Against fp32 PyTorch math, twice in a row; the second call writes dx over dy (the aliasing the header allows)."""
+    fn, err = _sym()
+    stream = torch.cuda.current_stream().cuda_stream
+    for rows, D, seed, with_dres, alias in [(513, 4096, 11, False, False), (129, 1024, 12, True, True)]:
+        x, w, dy, rstd, dres = _case(rows, D, seed, with_dres)
+        dx_ref, dw_ref = _torch_reference(x, w, dy, rstd, dres)
+        dx = dy.clone() if alias else torch.empty_like(x)
+        dy_arg = dx if alias else dy
+        dw = torch.empty(D, device="cuda", dtype=torch.float32)
+        rc = fn(x.data_ptr(), w.data_ptr(), dy_arg.data_ptr(), rstd.data_ptr(),
+                dres.data_ptr() if with_dres else None, dx.data_ptr(), dw.data_ptr(), rows, D, 0.0, 0, stream)
+        assert rc == 0, err().decode()
+        torch.cuda.synchronize()
+        assert torch.allclose(dx.float(), dx_ref, atol=3e-2, rtol=2e-2)
+        assert torch.allclose(dw, dw_ref, atol=0.15, rtol=2e-2)
+
+
+def test_noalloc_rejects_misaligned_pointers():
+    fn, err = _sym()
+    x, w, dy, rstd, _ = _case(4, 1024, 13, False)
+    buf = torch.empty(4 * 1024 + 8, device="cuda", dtype=torch.bfloat16)
+    dx_misaligned = buf[1:1 + 4 * 1024]          # 2 bytes past a 16-byte boundary
+    rc = fn(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr(), None, dx_misaligned.data_ptr(), None, 4, 1024,
+            0.0, 0, torch.cuda.current_stream().cuda_stream)
+    assert rc != 0 and "16-byte aligned" in err().decode()
+
+
 def test_noalloc_rejects_oversize_rows():
     fn, err = _sym()
     D = 8192 + 8
