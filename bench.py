@@ -13,6 +13,10 @@ Two measurements, both through ``easydel_b200.trainers.Trainer``:
 * ``e2e``: the same K steps driven by ``Trainer.train()`` from pinned host batches; every step
   copies its batch host->device and reads the loss back device->host.
 
+At 8 GPUs (``--serving auto``; ``on`` forces it at any N) the same JSON line carries a ``serving`` key: eSurge
+output tokens/s and TTFT / TPOT percentiles for Llama-3-70B at TP = N on the Poisson workload of the baseline
+(``easydel_b200/inference/esurge/bench_serving.py``), measured after the training state has been freed.
+
 ``--impl reference`` reports whether the unmodified reference can run here.
 ``--impl library`` runs the same config through stock PyTorch parts only (cuBLAS linears, SDPA,
 FSDP2 over NCCL, unfused AdamW; ``benchmarks/library_llama.py``) and prints the same JSON line with
@@ -143,6 +147,37 @@ def library_arm(args) -> None:
     dist.destroy_process_group()
 
 
+def serving_arm(args, rank: int, world: int) -> dict | None:
+    """The serving half of the headline: eSurge on Llama-3-70B (random weights, bf16), tensor parallel over all
+    ranks, paged KV cache (page 128, prefix caching on, at most 256 running sequences), Poisson arrivals of
+    synthetic requests (prompts 128-4096 tokens, 30 % sharing a 1024-token prefix, outputs 128-1024 tokens, greedy,
+    EOS ignored). Returns output tokens/s and the TTFT / TPOT percentiles; a failure is reported, not raised, so
+    that the training number of this run survives it."""
+    from easydel_b200.inference.esurge import bench_serving as BS
+
+    sargs = BS.build_parser().parse_args([
+        "--model", args.serving_model, "--requests", str(args.serving_requests), "--rate", str(args.serving_rate),
+        "--time-limit", str(args.serving_seconds)] + (["--layers", str(args.serving_layers)]
+                                                      if args.serving_layers else []))
+    try:
+        res = BS.run(sargs)
+    except Exception as e:  # noqa: BLE001
+        res = {"error": f"{type(e).__name__}: {e}"[:300]} if rank == 0 else None
+    if res is not None and "error" not in res:
+        res = {"metric": "eSurge output tok/s + TTFT/TPOT, Llama-3-70B", "output_tok_s": res["value"],
+               "ttft_p50_ms": res["ttft_p50_ms"], "ttft_p99_ms": res["ttft_p99_ms"],
+               "tpot_p50_ms": res["tpot_p50_ms"], "tpot_p99_ms": res["tpot_p99_ms"],
+               "config": {"model": res["model"], "tp": res["tp"], "requests_offered": res["requests_offered"],
+                          "requests_finished": res["requests_finished"], "rate_rps": res["rate_rps"],
+                          "admission_window_s": args.serving_seconds, "duration_s": res["duration_s"],
+                          "max_num_seqs": res["max_num_seqs"], "page_size": res["page_size"],
+                          "prefix_cache_hit_rate": res["prefix_cache_hit_rate"], "kv_pages": res["kv_pages"],
+                          "async_scheduling": res["async_scheduling"], "graph_steps": res["graph_steps"],
+                          "steps": res["steps"], "d2h_wait_s": res["d2h_wait_s"], "host_prep_s": res["host_prep_s"]},
+               "dtype": "bf16", "data": "synthetic", "timing": res["timing"]}
+    return res
+
+
 class ClockSampler:
     """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -198,6 +233,15 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=32, help="debug only; the reported config requires 32")
     ap.add_argument("--doc-mask", action="store_true",
                     help="mask attention across packed documents (the reference attends across them)")
+    ap.add_argument("--serving", default="auto", choices=["auto", "on", "off"],
+                    help="also measure the serving half of the headline (eSurge, Llama-3-70B, TP = --gpus) and add "
+                         "it to the JSON line under 'serving'; auto = only at 8 GPUs")
+    ap.add_argument("--serving-model", default="llama-3-70b")
+    ap.add_argument("--serving-layers", type=int, default=None, help="debug only; the reported config uses all")
+    ap.add_argument("--serving-requests", type=int, default=2000)
+    ap.add_argument("--serving-rate", type=float, default=8.0, help="Poisson arrival rate, requests/s")
+    ap.add_argument("--serving-seconds", type=float, default=270.0,
+                    help="requests stop being admitted after this long; the ones admitted are finished")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -306,10 +350,12 @@ def main() -> None:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_tok_s = tokens_per_step * K / e2e_s.item()
     h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
+    d2h = 8   # per step: the loss (4 bytes) and the kernel status word (4 bytes) are read back
 
+    line = None
     if rank == 0:
         value = tokens_per_step / (ms_per_step / 1e3)
-        print(json.dumps({
+        line = {
             "metric": "SFT tokens/sec/box Llama-3-8B", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
@@ -322,9 +368,33 @@ def main() -> None:
                        "l2": "weights (16 GB) and activations stream through every step; working set >> 126 MB L2",
                        "final_loss": final_loss},
             "clocks": clocks,
-            "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+            "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
-        }))
+        }
+    if args.serving == "on" or (args.serving == "auto" and world == 8):
+        # free the training state first: the 70B weights and the KV pages take most of every GPU
+        import gc
+
+        trainer.model_state = None
+        del trainer, model, host_batches
+        gc.collect()
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+
+        def give_up():   # the training number must survive a serving run that does not come back
+            if rank == 0:
+                print(json.dumps({**line, "serving": {"error": "did not finish within its time budget"}}), flush=True)
+            os._exit(0)
+
+        watchdog = threading.Timer(args.serving_seconds + 300.0, give_up)
+        watchdog.daemon = True
+        watchdog.start()
+        serving = serving_arm(args, rank, world)
+        watchdog.cancel()
+        if rank == 0 and serving is not None:
+            line["serving"] = serving
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -144,3 +144,87 @@ EDL_HOST_API int edl_dist_adamw_bcast(float* p32, float* m, float* v, float* g, 
       zero_grad);
   return check_cuda(cudaGetLastError(), "dist_adamw_bcast launch");
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Parameter-sharded data parallelism (ZeRO-3 style): every rank keeps 1/N of each layer's bf16 weights; a layer's
+// full weights are assembled into a rotating buffer shortly before the layer runs, and a layer's fp32 gradients
+// are summed over the ranks into the owner's slice as soon as the layer's backward has finished.
+//   edl_fsdp_gather      dst[r * per + i] = shard_r[i]          (bf16; peer loads of every rank's shard)
+//   edl_fsdp_reduce_acc  acc[i] += sum over ranks of full_r[rank * per + i]   (fp32; peer loads of this rank's slice
+//                        of every rank's layer-gradient buffer)
+// Both are plain grid-stride kernels with few registers and no shared memory, so their CTAs share SMs with the
+// GEMM / attention CTAs of the compute stream while the data crosses NVLink. The caller orders them against the
+// peers with device barriers (weights: once per optimizer step; gradients: before and after every reduction).
+namespace edl {
+namespace {
+__global__ void fsdp_gather_kernel(PeerPtrs shards, int nranks, int rank, long long per_vec,
+                                   uint4* __restrict__ dst) {
+  const long long total = per_vec * nranks;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    // start at this rank's own shard, then walk the peers: every rank reads a different peer at a time
+    const int k = (int)(i / per_vec);
+    const long long j = i - (long long)k * per_vec;
+    const int r = (rank + k) % nranks;
+    dst[(long long)r * per_vec + j] = reinterpret_cast<const uint4*>(shards.p[r])[j];
+  }
+}
+
+__global__ void fsdp_reduce_acc_kernel(PeerPtrs fulls, int nranks, int rank, long long per_vec,
+                                       float4* __restrict__ acc) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < per_vec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 a = acc[i];
+    for (int k = 0; k < nranks; ++k) {
+      const int r = (rank + k) % nranks;
+      const float4 v = reinterpret_cast<const float4*>(fulls.p[r])[(long long)rank * per_vec + i];
+      a.x += v.x;
+      a.y += v.y;
+      a.z += v.z;
+      a.w += v.w;
+    }
+    acc[i] = a;
+  }
+}
+}  // namespace
+}  // namespace edl
+
+// shard_ptrs[r]: rank r's shard of one layer (`per` bf16 elements, a multiple of 8, 16-byte aligned);
+// dst: local buffer of nranks * per elements. max_ctas bounds the grid (0 = 2 per SM).
+EDL_HOST_API int edl_fsdp_gather(const unsigned long long* shard_ptrs, int nranks, int rank, long long per, void* dst,
+                                 int max_ctas, void* stream) {
+  if (per <= 0) return 0;
+  if (nranks < 1 || nranks > MAX_RANKS || (per & 7) || (reinterpret_cast<uintptr_t>(dst) & 15)) {
+    set_last_error("edl_fsdp_gather: nranks=%d (max %d), per=%lld must be a multiple of 8, dst 16-byte aligned",
+                   nranks, MAX_RANKS, per);
+    return -1;
+  }
+  PeerPtrs pp;
+  for (int r = 0; r < nranks; ++r) pp.p[r] = reinterpret_cast<void*>(shard_ptrs[r]);
+  const long long per_vec = per / 8;
+  long long blocks = (per_vec * nranks + 255) / 256;
+  long long cap = max_ctas > 0 ? max_ctas : (long long)sm_count() * 2;
+  fsdp_gather_kernel<<<(int)(blocks > cap ? cap : blocks), 256, 0, (cudaStream_t)stream>>>(
+      pp, nranks, rank, per_vec, reinterpret_cast<uint4*>(dst));
+  return check_cuda(cudaGetLastError(), "fsdp_gather launch");
+}
+
+// full_ptrs[r]: rank r's gradient buffer of one layer (nranks * per fp32 elements); acc: this rank's accumulator
+// slice of that layer (`per` fp32 elements, a multiple of 4).
+EDL_HOST_API int edl_fsdp_reduce_acc(const unsigned long long* full_ptrs, int nranks, int rank, long long per,
+                                     float* acc, int max_ctas, void* stream) {
+  if (per <= 0) return 0;
+  if (nranks < 1 || nranks > MAX_RANKS || (per & 3) || (reinterpret_cast<uintptr_t>(acc) & 15)) {
+    set_last_error("edl_fsdp_reduce_acc: nranks=%d (max %d), per=%lld must be a multiple of 4, acc 16-byte aligned",
+                   nranks, MAX_RANKS, per);
+    return -1;
+  }
+  PeerPtrs pp;
+  for (int r = 0; r < nranks; ++r) pp.p[r] = reinterpret_cast<void*>(full_ptrs[r]);
+  const long long per_vec = per / 4;
+  long long blocks = (per_vec + 255) / 256;
+  long long cap = max_ctas > 0 ? max_ctas : (long long)sm_count() * 2;
+  fsdp_reduce_acc_kernel<<<(int)(blocks > cap ? cap : blocks), 256, 0, (cudaStream_t)stream>>>(
+      pp, nranks, rank, per_vec, reinterpret_cast<float4*>(acc));
+  return check_cuda(cudaGetLastError(), "fsdp_reduce_acc launch");
+}

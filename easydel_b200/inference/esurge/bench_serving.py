@@ -56,7 +56,7 @@ def pct(x, q):
     return float(np.percentile(np.asarray(x), q)) if len(x) else float("nan")
 
 
-def main():
+def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama-3-8b", choices=sorted(MODELS))
     ap.add_argument("--layers", type=int, default=None, help="override the layer count (smoke runs)")
@@ -74,19 +74,23 @@ def main():
     ap.add_argument("--hbm-utilization", type=float, default=0.85)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-prefix-caching", action="store_true")
+    ap.add_argument("--sync-scheduling", action="store_true", help="read every step's tokens back before the next launch")
+    ap.add_argument("--tp-shape-of", type=int, default=0,
+                    help="one GPU, with the per-GPU layer shapes of this tensor-parallel degree (heads, KV heads and "
+                         "FFN width divided by it): the compute side of a TP run without the other GPUs")
     ap.add_argument("--time-limit", type=float, default=0.0, help="stop admitting and finish after this many seconds")
-    args = ap.parse_args()
+    return ap
+
+
+def run(args) -> dict | None:
+    """Runs the workload on the ranks of the current job (tensor parallel over all of them) and returns the
+    result dictionary on rank 0 (``None`` elsewhere). The caller owns the process group."""
+    import torch.distributed as dist
 
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    import torch.distributed as dist
-
-    if world > 1:
-        from ...parallel.mesh import init_distributed
-
-        init_distributed()
     from ...modules.llama import LlamaConfig, LlamaForCausalLM
     from ..sampling_params import SamplingParams
     from . import eSurge
@@ -94,89 +98,140 @@ def main():
     kw = dict(MODELS[args.model])
     if args.layers:
         kw["num_hidden_layers"] = args.layers
+    shape_note = ""
+    if args.tp_shape_of and world == 1:
+        d = args.tp_shape_of
+        kw.update(num_attention_heads=kw["num_attention_heads"] // d,
+                  num_key_value_heads=max(1, kw["num_key_value_heads"] // d),
+                  intermediate_size=kw["intermediate_size"] // d,
+                  head_dim=kw["hidden_size"] // kw["num_attention_heads"])
+        shape_note = f"-tp{d}shape"
     cfg = LlamaConfig(sharding_axis_dims=(1, 1, 1, world, 1), **kw)
     model = LlamaForCausalLM.sequential_init(cfg, dtype=torch.bfloat16, param_dtype=torch.bfloat16, device=dev,
                                              seed=1234).eval()
     engine = eSurge(model, max_model_len=args.max_model_len, max_num_seqs=args.max_num_seqs,
                     max_num_batched_tokens=args.max_num_batched_tokens, hbm_utilization=args.hbm_utilization,
-                    enable_prefix_caching=not args.no_prefix_caching)
+                    enable_prefix_caching=not args.no_prefix_caching, async_scheduling=not args.sync_scheduling)
     work = make_workload(args.requests, args.rate, kw["vocab_size"], args.seed, (args.prompt_min, args.prompt_max),
                          (args.output_min, args.output_max), args.shared_prefix_frac, args.shared_prefix_len)
-    # warm-up: a few requests through prefill and every decode bucket that the run will meet
-    for i in range(3):
+    # warm-up: a few requests through prefill and the first decode buckets
+    for i in range(min(3, len(work))):
         engine.generate(work[i][1][:256], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
     torch.cuda.synchronize()
+    # The arrival count travels over a host-side (gloo) group: a device-side broadcast read back with .item()
+    # would wait for the engine step that was just launched and serialise host and device again.
+    ctl = None
     if world > 1:
         dist.barrier()
-    counter = torch.zeros(1, dtype=torch.int64, device=dev)
+        ctl = dist.new_group(backend="gloo")
+    counter = torch.zeros(1, dtype=torch.int64)
     arrival_wall: dict[str, float] = {}
     first_wall: dict[str, float] = {}
     done_wall: dict[str, float] = {}
     n_out: dict[str, int] = {}
     admitted = 0
     t0 = time.perf_counter()
+    wall0 = time.time()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     stop_admitting = False
-    while True:
-        now = time.perf_counter() - t0
-        if rank == 0:
-            k = admitted
-            if not stop_admitting:
-                while k < len(work) and work[k][0] <= now:
-                    k += 1
-            if args.time_limit and now > args.time_limit:
-                stop_admitting = True
-            counter[0] = k if not stop_admitting else -k - 1
+    try:
+        while True:
+            now = time.perf_counter() - t0
+            if rank == 0:
+                k = admitted
+                if not stop_admitting:
+                    while k < len(work) and work[k][0] <= now:
+                        k += 1
+                if args.time_limit and now > args.time_limit:
+                    stop_admitting = True
+                counter[0] = k if not stop_admitting else -k - 1
+            if ctl is not None:
+                dist.broadcast(counter, src=0, group=ctl)
+            v = int(counter.item())
+            if v < 0:
+                stop_admitting, v = True, -v - 1
+            for i in range(admitted, v):
+                rid = engine.add_request(work[i][1], SamplingParams(max_tokens=work[i][2], temperature=0.0,
+                                                                    ignore_eos=True), request_id=f"r{i}")
+                arrival_wall[rid] = t0 + max(work[i][0], 0.0) if args.rate > 0 else time.perf_counter()
+            admitted = v
+            if not (engine.scheduler.has_unfinished() or engine._inflight is not None):
+                if admitted >= len(work) or stop_admitting:
+                    break
+                time.sleep(0.0005)
+                continue
+            engine.step()
+            t = time.perf_counter()
+            for rid, tr in list(engine._tracked.items()):
+                ft = tr.req.first_token_time        # set when the token reached the host
+                if ft is not None and rid not in first_wall:
+                    first_wall[rid] = t0 + (ft - wall0)
+                if tr.finished and rid not in done_wall:
+                    done_wall[rid] = t
+                    n_out[rid] = len(tr.req.output_token_ids)
+                    engine._tracked.pop(rid, None)
+        ev1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        dev_ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
         if world > 1:
-            dist.broadcast(counter, src=0)
-        v = int(counter.item())
-        if v < 0:
-            stop_admitting, v = True, -v - 1
-        for i in range(admitted, v):
-            rid = engine.add_request(work[i][1], SamplingParams(max_tokens=work[i][2], temperature=0.0,
-                                                                ignore_eos=True), request_id=f"r{i}")
-            arrival_wall[rid] = t0 + max(work[i][0], 0.0) if args.rate > 0 else time.perf_counter()
-        admitted = v
-        if not engine.scheduler.has_unfinished():
-            if admitted >= len(work) or stop_admitting:
-                break
-            time.sleep(0.0005)
-            continue
-        engine.step()
-        t = time.perf_counter()
-        for rid, tr in list(engine._tracked.items()):
-            n = len(tr.req.output_token_ids)
-            if n and rid not in first_wall:
-                first_wall[rid] = t
-            if tr.finished and rid not in done_wall:
-                done_wall[rid] = t
-                n_out[rid] = n
-                engine._tracked.pop(rid, None)
-    ev1.record()
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
-    dev_ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+            dist.all_reduce(dev_ms, op=dist.ReduceOp.MAX)
+        result = None
+        if rank == 0:
+            ttft = [first_wall[r] - arrival_wall[r] for r in done_wall if r in first_wall]
+            tpot = [(done_wall[r] - first_wall[r]) / max(1, n_out[r] - 1) for r in done_wall
+                    if n_out[r] > 1 and r in first_wall]
+            e2e = [done_wall[r] - arrival_wall[r] for r in done_wall]
+            total_out = sum(n_out.values())
+            span = float(dev_ms) / 1e3
+            tm = engine.runner.timings
+            result = {
+                "metric": "eSurge output tokens/s", "value": total_out / span, "unit": "tokens/s", "n_gpus": world,
+                "model": args.model + (f"-{args.layers}L" if args.layers else "") + shape_note, "tp": world,
+                "requests_finished": len(done_wall), "requests_offered": len(work), "rate_rps": args.rate,
+                "duration_s": span, "wall_s": wall, "ttft_p50_ms": pct(ttft, 50) * 1e3,
+                "ttft_p99_ms": pct(ttft, 99) * 1e3, "tpot_p50_ms": pct(tpot, 50) * 1e3,
+                "tpot_p99_ms": pct(tpot, 99) * 1e3, "e2e_p50_s": pct(e2e, 50),
+                "prefix_cache_hit_rate": engine.pool.stats.hit_rate, "kv_pages": engine.cache.num_pages,
+                "max_num_seqs": args.max_num_seqs, "page_size": 128, "async_scheduling": engine.async_scheduling,
+                "steps": tm["steps"], "graph_steps": tm["graph_steps"], "host_prep_s": tm["prep"],
+                "launch_s": tm["exec"], "sample_s": tm["sample"], "d2h_wait_s": tm["d2h"], "dtype": "bf16",
+                "data": "synthetic", "timing": "CUDA events around the whole run, max over ranks"}
+        return result
+    finally:
+        # Teardown order matters for a clean exit: stop the engine and drop its captured graphs (they hold the
+        # collectives of the tensor-parallel group) and the symmetric buffers before the caller destroys the groups.
+        engine.close()
+        from ...parallel import tp as tpar
+
+        tpar.release_peer_buffers()
+        del engine, model
+        import gc
+
+        gc.collect()
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        if world > 1:
+            dist.barrier()
+            if ctl is not None:
+                dist.destroy_process_group(ctl)
+
+
+def main():
+    args = build_parser().parse_args()
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", 1))
     if world > 1:
-        dist.all_reduce(dev_ms, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        ttft = [first_wall[r] - arrival_wall[r] for r in done_wall]
-        tpot = [(done_wall[r] - first_wall[r]) / max(1, n_out[r] - 1) for r in done_wall if n_out[r] > 1]
-        e2e = [done_wall[r] - arrival_wall[r] for r in done_wall]
-        total_out = sum(n_out.values())
-        span = float(dev_ms) / 1e3
-        tm = engine.runner.timings
-        print(json.dumps({
-            "metric": "eSurge output tokens/s", "value": total_out / span, "unit": "tokens/s", "n_gpus": world,
-            "model": args.model + (f"-{args.layers}L" if args.layers else ""), "tp": world,
-            "requests_finished": len(done_wall), "requests_offered": len(work), "rate_rps": args.rate,
-            "duration_s": span, "wall_s": wall, "ttft_p50_ms": pct(ttft, 50) * 1e3, "ttft_p99_ms": pct(ttft, 99) * 1e3,
-            "tpot_p50_ms": pct(tpot, 50) * 1e3, "tpot_p99_ms": pct(tpot, 99) * 1e3, "e2e_p50_s": pct(e2e, 50),
-            "prefix_cache_hit_rate": engine.pool.stats.hit_rate, "kv_pages": engine.cache.num_pages,
-            "steps": tm["steps"], "graph_steps": tm["graph_steps"],
-            "host_prep_s": tm["prep"], "launch_s": tm["exec"], "sample_s": tm["sample"], "d2h_wait_s": tm["d2h"],
-            "dtype": "bf16", "data": "synthetic", "timing": "CUDA events around the whole run, max over ranks"}))
+        from ...parallel.mesh import init_distributed
+
+        init_distributed()
+    result = run(args)
+    if result is not None:
+        print(json.dumps(result), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -99,15 +99,37 @@ class _Tracked:
         self.emitted_tokens = 0
 
 
+# Options of the reference engine that steer its ahead-of-time XLA compilation or its process layout; accepted so
+# that configurations written for it load, and without effect here.
+_COMPILE_ONLY_OPTIONS = frozenset({
+    "dtype", "min_input_pad", "min_token_pad", "max_num_seq_buckets", "use_aot_forward", "bind_graphstate_for_aot",
+    "auto_shard_model", "compile_runner", "runner_verbose", "sampler_metrics", "data_parallelism_axis",
+    "strict_context", "prefer_preserve_prompt", "decode_truncated_prompt", "destroy_pages_on_pause",
+    "detokenizer_max_states", "tokenizer_endpoint", "detokenizer_endpoint", "worker_startup_timeout",
+    "max_request_outputs", "idle_reset_seconds", "idle_reset_min_interval", "ignore_stop_strings_in_reasoning",
+    "resolution_buckets", "vision_cache_capacity_mb"})
+
+
 class eSurge:
     def __init__(self, model, tokenizer=None, processor=None, max_model_len: int = 8192, max_num_seqs: int = 256,
                  max_num_batched_tokens: int | None = None, hbm_utilization: float = 0.85, page_size: int = PAGE_SIZE,
                  enable_prefix_caching: bool = True, num_pages: int | None = None,
                  long_prefill_token_threshold: int | None = None, scheduling_policy: str = "fcfs",
-                 overlap_execution: bool = False, async_scheduling: bool = False, esurge_name: str | None = None,
-                 reserve_tokens: int | None = None, auto_truncate_prompt: bool = True,
-                 truncate_mode: str = "left", silent_mode: bool = True, sharding_axis_dims=(1, 1, 1, -1, 1),
-                 **unused):
+                 overlap_execution: bool | None = None, async_scheduling: bool | None = None,
+                 esurge_name: str | None = None, reserve_tokens: int | None = None,
+                 auto_truncate_prompt: bool = True, truncate_mode: str = "left", silent_mode: bool = True,
+                 sharding_axis_dims=(1, 1, 1, -1, 1), extra_eos_token_ids: tp.Sequence[int] | None = None,
+                 extra_stops: str | tp.Sequence[str] | None = None, auto_cap_new_tokens: bool = True,
+                 sampling_params_callback: tp.Callable | None = None, tool_parser: str | None = None,
+                 reasoning_parser: str | None = None, **compile_options):
+        """``async_scheduling`` / ``overlap_execution`` (either one; default on for CUDA models): step *t+1* is
+        scheduled and launched before the tokens of step *t* are read back, so host work overlaps device work.
+
+        ``compile_options`` takes only the reference's ahead-of-time compilation knobs, which have nothing to
+        act on here (kernels are launched eagerly or replayed from CUDA graphs); any other name is an error."""
+        unknown = set(compile_options) - _COMPILE_ONLY_OPTIONS
+        if unknown:
+            raise TypeError(f"eSurge got unexpected option(s) {sorted(unknown)}")
         self.model = model.eval() if hasattr(model, "eval") else model
         self.tokenizer = tokenizer if tokenizer is not None else getattr(processor, "tokenizer", processor)
         self.processor = processor
@@ -151,8 +173,20 @@ class eSurge:
         self._max_errors = int(os.environ.get("EASURGE_MAX_SCHEDULER_ERRORS", "3"))
         self.last_heartbeat = time.time()
         self.eos_token_id = getattr(model.config, "eos_token_id", None)
+        extra_eos = list(extra_eos_token_ids or [])
         if isinstance(self.eos_token_id, (list, tuple)):
+            extra_eos = list(self.eos_token_id[1:]) + extra_eos
             self.eos_token_id = self.eos_token_id[0] if self.eos_token_id else None
+        self.extra_eos_token_ids = [int(t) for t in extra_eos]
+        self.extra_stops = [extra_stops] if isinstance(extra_stops, str) else list(extra_stops or [])
+        self.auto_cap_new_tokens = auto_cap_new_tokens
+        self.sampling_params_callback = sampling_params_callback
+        self.tool_parser, self.reasoning_parser = tool_parser, reasoning_parser
+        want_async = async_scheduling if async_scheduling is not None else overlap_execution
+        if want_async is None:
+            want_async = self.runner.device.type == "cuda"
+        self.async_scheduling = bool(want_async)
+        self._inflight = None      # (SchedulerOutput, runner handle, launch time) of the step not read back yet
 
     # ------------------------------------------------------------------ lifecycle
     def initiate(self) -> "eSurge":
@@ -172,6 +206,21 @@ class eSurge:
         if self._thread is not None:
             self._thread.join(timeout=30)
             self._thread = None
+        self._drain()
+
+    def _drain(self) -> None:
+        """Reads back (and commits) a step that is still in flight."""
+        with self._lock:
+            prev, self._inflight = self._inflight, None
+            if prev is not None:
+                self._commit(*prev)
+
+    def close(self) -> None:
+        """Stops the scheduler thread, finishes the step in flight and drops the captured CUDA graphs and the
+        runner's device buffers, so that the process group can be destroyed and the process can exit."""
+        self.terminate()
+        self.stop_monitoring()
+        self.runner.release()
 
     def pause(self) -> None:
         with self._work:
@@ -224,7 +273,7 @@ class eSurge:
     def update_model_weights(self, model=None, state_dict: dict | None = None) -> None:
         """Swaps in new weights (RL trainers refresh the policy between rollouts). Cached prefixes are dropped."""
         with self._lock:
-            if self.scheduler.has_unfinished():
+            if self.scheduler.has_unfinished() or self._inflight is not None:
                 raise RuntimeError("cannot update weights while requests are in flight")
             if state_dict is not None:
                 self.model.load_state_dict(state_dict, strict=False)
@@ -255,6 +304,11 @@ class eSurge:
                     priority: int = 0, images: tp.Sequence[tp.Any] | None = None,
                     videos: tp.Sequence[tp.Any] | None = None) -> str:
         sp = sampling_params or SamplingParams()
+        if self.sampling_params_callback is not None:
+            sp = self.sampling_params_callback(sp, {"prompt": prompt, "request_id": request_id}) or sp
+        if self.extra_eos_token_ids or self.extra_stops:
+            sp = sp.clone(stop_token_ids=list(dict.fromkeys([*sp.stop_token_ids, *self.extra_eos_token_ids])),
+                          stop=list(dict.fromkeys([*(sp.stop or []), *self.extra_stops])))
         ids, text = self._tokenize(prompt)
         if not ids:
             raise ValueError("empty prompt")
@@ -308,22 +362,56 @@ class eSurge:
             req.slot = -1
 
     # ------------------------------------------------------------------ the step
+    def _assign_slots(self, out) -> None:
+        for s in out.scheduled:
+            if s.request.slot < 0:
+                s.request.slot = self._free_slots.pop()
+                self.runner._slot_npages[s.request.slot] = 0   # the slot's page mirror belongs to a new request
+                self.cache.reset_slot_state(s.request.slot)
+                if s.request.sampling_params.needs_penalties:
+                    self.runner._ensure_counts()
+                    self.runner.reset_slot(s.request.slot, s.request.all_token_ids)
+
+    def _commit(self, out, handle, t_launch) -> int:
+        sampled = self.runner.collect(handle)
+        finished = self.scheduler.commit_output(out, sampled)
+        self._publish(out, sampled, finished)
+        self.metrics.record_step(out.total_tokens, len(sampled), time.perf_counter() - t_launch,
+                                 self.scheduler.num_running, self.scheduler.num_waiting, self.pool.usage,
+                                 self.pool.stats.hit_rate)
+        self.last_heartbeat = time.time()
+        return out.total_tokens
+
+    def _step_async(self) -> int:
+        """schedule(t) -> launch(t) -> read back and commit(t-1) -> book(t): the host work of a step (scheduling,
+        batch metadata, detokenisation, stop checks) runs while the device executes the previous launch."""
+        with self._lock:
+            out = self.scheduler.schedule()
+            for r in out.preempted:
+                self._return_slot(r)
+            handle = None
+            if not out.is_empty:
+                self._assign_slots(out)
+                handle = self.runner.launch(out)
+            prev, self._inflight = self._inflight, None
+            done = self._commit(*prev) if prev is not None else 0
+            if handle is not None:
+                self.scheduler.advance_optimistic(out)
+                self._inflight = (out, handle, time.perf_counter())
+                done += out.total_tokens
+            return done
+
     def step(self) -> int:
         """One schedule -> execute -> update cycle. Returns the number of tokens processed."""
+        if self.async_scheduling:
+            return self._step_async()
         with self._lock:
             out = self.scheduler.schedule()
             for r in out.preempted:
                 self._return_slot(r)
             if out.is_empty:
                 return 0
-            for s in out.scheduled:
-                if s.request.slot < 0:
-                    s.request.slot = self._free_slots.pop()
-                    self.runner._slot_npages[s.request.slot] = 0   # the slot's page mirror belongs to a new request
-                    self.cache.reset_slot_state(s.request.slot)
-                    if s.request.sampling_params.needs_penalties:
-                        self.runner._ensure_counts()
-                        self.runner.reset_slot(s.request.slot, s.request.all_token_ids)
+            self._assign_slots(out)
             t0 = time.perf_counter()
             sampled = self.runner.execute(out)
             dt = time.perf_counter() - t0
@@ -380,7 +468,7 @@ class eSurge:
     def _loop(self) -> None:
         while True:
             with self._work:
-                while self._running and (self._paused or not self.scheduler.has_unfinished()):
+                while self._running and (self._paused or not (self.scheduler.has_unfinished() or self._inflight)):
                     self.last_heartbeat = time.time()
                     self._work.wait(timeout=0.5)
                 if not self._running:
@@ -442,7 +530,7 @@ class eSurge:
         while not done():
             if background:
                 time.sleep(0.001)
-            elif self.step() == 0 and not self.scheduler.has_unfinished():
+            elif self.step() == 0 and not self.scheduler.has_unfinished() and self._inflight is None:
                 break
 
     def stream(self, prompt, sampling_params: SamplingParams | None = None, request_id: str | None = None,

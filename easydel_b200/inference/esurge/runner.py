@@ -37,8 +37,9 @@ class ModelRunner:
         dev = self.device
         pin = dev.type == "cuda"
         B, T, MP = max_num_seqs, max_num_batched_tokens, self.max_pages_per_seq
-        # one packed int32 staging buffer: ids | pos | slots | cu_q | kv_lens | last_idx | page_table
-        self._sizes = [T, T, T, B + 1, B, B, B * MP]
+        # one packed int32 staging buffer: ids | pos | slots | cu_q | kv_lens | last_idx | page_table |
+        # slot of every sequence | (token row, slot) of the rows whose input token is still on the device
+        self._sizes = [T, T, T, B + 1, B, B, B * MP, B, B, B]
         total = sum(self._sizes)
         self._host = torch.zeros(total, dtype=torch.int32, pin_memory=pin)
         self._dev = torch.zeros(total, dtype=torch.int32, device=dev)
@@ -61,6 +62,13 @@ class ModelRunner:
         self.counts: torch.Tensor | None = None
         self.timings: dict[str, float] = {"prep": 0.0, "exec": 0.0, "sample": 0.0, "d2h": 0.0, "steps": 0,
                                           "graph_steps": 0}
+        # The last token sampled for every engine slot stays on the device: a step launched before the previous
+        # step's tokens were read back takes its decode inputs from here (asynchronous scheduling).
+        self._last_tokens = torch.zeros(B + 1, dtype=torch.int64, device=dev)
+        # two read-back buffers, used alternately: [tokens of up to B rows | kernel status word]
+        self._tok_host = [torch.zeros(B + 1, dtype=torch.int64, pin_memory=pin) for _ in range(2)]
+        self._tok_dev = torch.zeros(B + 1, dtype=torch.int64, device=dev)
+        self._launches = 0
         # Decode-only greedy steps are replayed from CUDA graphs, one per power-of-two batch bucket
         # (the reference compiles (tokens, requests) buckets ahead of time: runners/execution_manager.py:1291-1405).
         import os
@@ -77,6 +85,15 @@ class ModelRunner:
         mesh = getattr(model.config, "mesh", None)
         if mesh is not None and getattr(mesh, "tp", 1) > 1:
             self.tp_group = mesh.get_group("tp")
+
+    def release(self) -> None:
+        """Drops the captured graphs (and with them their private memory pool). Needed before the process group
+        is torn down: a graph that holds collectives keeps the communicator's resources alive."""
+        self._graphs.clear()
+        self._graph_pool = None
+        self._warm.clear()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
 
     def _split(self, buf: torch.Tensor) -> list[torch.Tensor]:
         out, o = [], 0
@@ -112,7 +129,7 @@ class ModelRunner:
     def _forward(self, B: int, T: int, max_q: int, num_decode: int, mm_rows=None) -> torch.Tensor:
         """Backbone over the first ``T`` staged tokens of ``B`` sequences, LM head on each sequence's last row.
         ``mm_rows``: ``[(first staged row, features [n, hidden])]`` to write over the token embeddings."""
-        d_ids, d_pos, d_slots, d_cu, d_kv, d_last, d_table = self._dviews
+        d_ids, d_pos, d_slots, d_cu, d_kv, d_last, d_table = self._dviews[:7]
         MP = self.max_pages_per_seq
         meta = PagedBatchMeta(cu_q=d_cu[:B + 1], kv_lens=d_kv[:B], page_table=d_table.view(self.max_num_seqs, MP)[:B],
                               slot_mapping=d_slots[:T], max_q=max_q, num_seqs=B, last_token_index=d_last[:B],
@@ -155,15 +172,40 @@ class ModelRunner:
     @torch.no_grad()
     def execute(self, out: SchedulerOutput) -> dict[str, int]:
         """Runs one engine step; returns ``{request_id: sampled token}`` for the requests that sampled."""
+        handle = self.launch(out)
+        return self.collect(handle) if handle is not None else {}
+
+    def collect(self, handle) -> dict[str, int]:
+        """Waits for a launched step and returns its tokens. Also the point where a kernel whose bounded wait ran
+        out is noticed: its status word travels with the tokens."""
+        t3 = time.perf_counter()
+        sched, B, buf, event = handle
+        if event is not None:
+            event.synchronize()
+        host = buf[:B + 1].tolist()
+        self.timings["d2h"] += time.perf_counter() - t3
+        if host[B] != 0:
+            from ...ops import _lib
+
+            _lib.status_word(self.device).zero_()
+            raise RuntimeError(f"a kernel of this engine step reported status {host[B]} (a bounded wait ran out); "
+                               "the step's output is not valid")
+        return {s.request.request_id: host[b] for b, s in enumerate(sched) if s.samples}
+
+    @torch.no_grad()
+    def launch(self, out: SchedulerOutput):
+        """Enqueues one engine step on the device and returns a handle for :meth:`collect`; does not wait for it."""
         t0 = time.perf_counter()
         sched = out.scheduled
         B = len(sched)
         T = out.total_tokens
         if B == 0:
-            return {}
+            return None
         if B > self.max_num_seqs or T > self.max_tokens:
             raise RuntimeError(f"batch of {B} sequences / {T} tokens exceeds the runner's buffers")
-        ids, pos, slots, cu_q, kv_lens, last_idx, table = self._hviews
+        ids, pos, slots, cu_q, kv_lens, last_idx, table, slot_of, fix_pos, fix_slot = self._hviews
+        slotof_np, fixpos_np, fixslot_np = slot_of.numpy(), fix_pos.numpy(), fix_slot.numpy()
+        nfix = 0
         MP = self.max_pages_per_seq
         ids_np, pos_np, slots_np = ids.numpy(), pos.numpy(), slots.numpy()
         table_np = table.numpy().reshape(self.max_num_seqs, MP)
@@ -191,6 +233,13 @@ class ModelRunner:
             p = np.fromiter((s.start for s in sched), dtype=np.int32, count=B)
             ids_np[:B] = np.fromiter((s.request.output_token_ids[-1] for s in sched), dtype=np.int32, count=B)
             pos_np[:B] = p
+            slotof_np[:B] = slot_idx
+            on_dev = np.nonzero(ids_np[:B] < 0)[0]          # tokens sampled by a step that was not read back yet
+            nfix = len(on_dev)
+            if nfix:
+                fixpos_np[:nfix] = on_dev
+                fixslot_np[:nfix] = slot_idx[on_dev]
+                ids_np[on_dev] = 0
             if self._native is not None:     # one C++ pass over the rows (csrc/host_native.cu)
                 self._native.edl_host_fill_decode(slot_idx.ctypes.data, p.ctypes.data, B, sp_pages.ctypes.data, MP,
                                                   PAGE_SIZE, slots_np.ctypes.data, table_np.ctypes.data,
@@ -214,6 +263,11 @@ class ModelRunner:
             else:
                 toks = req.prompt_token_ids[st:] + req.output_token_ids[:st + n - npt]
             ids_np[o:o + n] = toks
+            slotof_np[b] = req.slot if req.slot >= 0 else self.max_num_seqs
+            if toks[-1] < 0:       # the one token a decoding row feeds may still be on the device
+                fixpos_np[nfix], fixslot_np[nfix] = o + n - 1, req.slot
+                ids_np[o + n - 1] = 0
+                nfix += 1
             for off, feats in req.mm_embeds:
                 # the part of this image that falls inside [st, st + n): chunked prefill may split an image
                 a, z = max(off, st), min(off + feats.shape[0], st + n)
@@ -250,12 +304,16 @@ class ModelRunner:
                 kv_np[B:Bp] = 1
                 cu_np[B + 1:Bp + 1] = np.arange(B + 1, Bp + 1, dtype=np.int32)
                 last_np[B:Bp] = np.arange(B, Bp, dtype=np.int32)
+                slotof_np[B:Bp] = self.max_num_seqs
         if self.cache.linear:
             # recurrent-state rows of the scheduled sequences; padding rows of a batch bucket share the spare row
             sl = [s.request.slot for s in sched] + [self.max_num_seqs] * (Bp - B)
             self._seq_slots[:Bp].copy_(torch.tensor(sl, dtype=torch.int64), non_blocking=True)
         # one upload of the packed metadata
         self._dev.copy_(self._host, non_blocking=True)
+        if nfix:
+            d_fixpos, d_fixslot = self._dviews[8][:nfix].long(), self._dviews[9][:nfix].long()
+            self._dviews[0].index_copy_(0, d_fixpos, self._last_tokens.index_select(0, d_fixslot).to(torch.int32))
         t1 = time.perf_counter()
         if self.use_graphs and decode_only:
             tokens = self._decode_step_graphed(Bp)[:B]
@@ -290,12 +348,26 @@ class ModelRunner:
                 S.count_update(self.counts, tokens, torch.tensor([s.request.slot for s in sched], dtype=torch.int32,
                                                                   device=self.device))
         t3 = time.perf_counter()
-        host_tokens = tokens.cpu().tolist()  # the step's only device->host read
-        t4 = time.perf_counter()
+        # keep every slot's newest token on the device, and start the step's only device->host read
+        self._last_tokens.index_copy_(0, self._dviews[7][:B].long(), tokens[:B].to(torch.int64))
+        buf = self._tok_host[self._launches & 1]
+        self._launches += 1
+        event = None
+        if self.device.type == "cuda":
+            from ...ops import _lib
+
+            self._tok_dev[:B].copy_(tokens[:B])
+            self._tok_dev[B:B + 1].copy_(_lib.status_word(self.device)) if _lib.available() else \
+                self._tok_dev[B:B + 1].zero_()
+            buf[:B + 1].copy_(self._tok_dev[:B + 1], non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+        else:
+            buf[:B].copy_(tokens[:B])
+            buf[B] = 0
         tm = self.timings
         tm["prep"] += t1 - t0
         tm["exec"] += t2 - t1
         tm["sample"] += t3 - t2
-        tm["d2h"] += t4 - t3
         tm["steps"] += 1
-        return {s.request.request_id: host_tokens[b] for b, s in enumerate(sched) if s.samples}
+        return (sched, B, buf, event)

@@ -64,6 +64,9 @@ class EngineRequest:
     # images: (offset of the first placeholder token in the prompt, projected features [rows, hidden] on the device)
     mm_embeds: list = field(default_factory=list)
     mm_hash: tp.Any = None                # joins the page hashes: same tokens + other images = other pages
+    # asynchronous scheduling: the request reached its length limit with a token that is still on the device;
+    # it is not scheduled again and finishes when that token is committed
+    finishing: bool = False
 
     @property
     def all_token_ids(self) -> list[int]:
@@ -82,12 +85,17 @@ class EngineRequest:
         return self.num_prompt_tokens + (self.sampling_params.max_tokens or 0)
 
 
+#: stands in ``output_token_ids`` for a token that was sampled on the device and not read back yet
+PLACEHOLDER_TOKEN = -1
+
+
 @dataclass
 class ScheduledRequest:
     request: EngineRequest
     num_new_tokens: int            # tokens fed to the model this step
     start: int                     # index (in all_token_ids) of the first fed token
     samples: bool                  # True when this step produces the next token for the request
+    out_index: int = -1            # asynchronous scheduling: where in output_token_ids this step's token goes
 
 
 @dataclass
@@ -196,7 +204,10 @@ class Scheduler:
         """Publishes pages that became full (and whose tokens are final) for prefix reuse."""
         if not self.pool.enable_caching:
             return
-        full = req.num_computed_tokens // self.page_size
+        known = req.num_tokens
+        if req.output_token_ids and req.output_token_ids[-1] == PLACEHOLDER_TOKEN:
+            known -= 1          # that token is still on the device: its page cannot be hashed yet
+        full = min(req.num_computed_tokens, known) // self.page_size
         if full <= req.num_registered_pages:
             return
         tokens = req.all_token_ids
@@ -219,7 +230,7 @@ class Scheduler:
         running = sorted(self.running, key=lambda r: r.order)
         while i < len(running) and budget > 0:
             req = running[i]
-            if req.status != RequestStatus.RUNNING:
+            if req.status != RequestStatus.RUNNING or req.finishing:
                 i += 1
                 continue
             remaining = req.num_tokens - req.num_computed_tokens
@@ -229,7 +240,8 @@ class Scheduler:
                 continue
             while not self._try_allocate(req, req.num_computed_tokens + n):
                 # free pages by preempting the newest running request (possibly this one)
-                victim = max((r for r in self.running if r.status == RequestStatus.RUNNING), key=lambda r: r.order)
+                victim = max((r for r in self.running if r.status == RequestStatus.RUNNING and
+                              (not r.finishing or r is req)), key=lambda r: r.order)
                 self._preempt(victim)
                 preempted.append(victim)
                 scheduled = [s for s in scheduled if s.request is not victim]
@@ -273,6 +285,76 @@ class Scheduler:
         scheduled.sort(key=lambda s: (s.num_new_tokens > 1, s.request.order))
         num_decode = sum(1 for s in scheduled if s.num_new_tokens == 1)
         return SchedulerOutput(scheduled, preempted, sum(s.num_new_tokens for s in scheduled), num_decode)
+
+    # ------------------------------------------------------------------ asynchronous scheduling
+    # The engine launches step t before it has read the tokens of step t-1 (the reference's ``AsyncScheduler``,
+    # easydel/inference/esurge/scheduler/async_scheduler.py:68). Between launch and read-back a sampled token is a
+    # placeholder in ``output_token_ids``; the runner feeds the real value from its device-side token table.
+    def advance_optimistic(self, out: SchedulerOutput) -> None:
+        """Books a launched step: computed-token counts move on and every sampling row gets a placeholder token.
+        Length limits are known without the token, so a request that reaches one stops being scheduled now."""
+        for s in out.scheduled:
+            req = s.request
+            if req.status != RequestStatus.RUNNING:
+                continue
+            req.num_computed_tokens += s.num_new_tokens
+            if not s.samples:
+                continue
+            s.out_index = len(req.output_token_ids)
+            req.output_token_ids.append(PLACEHOLDER_TOKEN)
+            sp = req.sampling_params
+            if (sp.max_tokens is not None and len(req.output_token_ids) >= sp.max_tokens) or \
+                    req.num_tokens >= self.config.max_model_len:
+                req.finishing = True
+
+    def commit_output(self, out: SchedulerOutput, sampled: dict[str, int]) -> list[EngineRequest]:
+        """Fills in the tokens of a step booked by :meth:`advance_optimistic` and applies the stop conditions.
+        A request that stops on a token (EOS, stop id) may already be part of the next, launched step: that row's
+        result is dropped when its turn to be committed comes, because the request is no longer running."""
+        finished = []
+        now = time.time()
+        for s in out.scheduled:
+            req = s.request
+            if req.status.finished:
+                continue               # stopped or aborted meanwhile: the row's result is dropped
+            running = req.status == RequestStatus.RUNNING
+            if not s.samples or s.out_index < 0:
+                if running:
+                    self._register_full_pages(req)
+                continue
+            if req.request_id not in sampled or s.out_index >= len(req.output_token_ids):
+                continue
+            # a request preempted after the launch keeps its token: it was sampled from a complete context
+            tok = int(sampled[req.request_id])
+            req.output_token_ids[s.out_index] = tok
+            if req.first_token_time is None:
+                req.first_token_time = now
+            status = self._check_stop_at(req, tok, s.out_index + 1)
+            if status is not None:
+                del req.output_token_ids[s.out_index + 1:]
+                if running:
+                    self._register_full_pages(req)
+                self._finish(req, status)
+                finished.append(req)
+                continue
+            if running:
+                self._register_full_pages(req)
+        return finished
+
+    def _check_stop_at(self, req: EngineRequest, tok: int, n_out: int) -> RequestStatus | None:
+        sp = req.sampling_params
+        if n_out >= sp.min_tokens:
+            if not sp.ignore_eos and req.eos_token_id is not None and tok == req.eos_token_id:
+                req.stop_reason = "eos"
+                return RequestStatus.FINISHED_STOPPED
+            if tok in sp.stop_token_ids:
+                req.stop_reason = tok
+                return RequestStatus.FINISHED_STOPPED
+        if sp.max_tokens is not None and n_out >= sp.max_tokens:
+            return RequestStatus.FINISHED_LENGTH
+        if req.num_prompt_tokens + n_out >= self.config.max_model_len:
+            return RequestStatus.FINISHED_LENGTH
+        return None
 
     # ------------------------------------------------------------------ after the model ran
     def update_from_output(self, out: SchedulerOutput, sampled: dict[str, int]) -> list[EngineRequest]:

@@ -248,6 +248,8 @@ class EasyDeLBaseConfig(PretrainedConfig):
         fsdp_is_ep_bound: bool = True,
         sp_is_ep_bound: bool = True,
         operation_configs: dict | None = None,
+        fsdp_parameter_sharding: str = "auto",
+        tp_sequence_parallel: bool = True,
         **kwargs,
     ):
         self.sharding_axis_dims = tuple(getattr(self, "sharding_axis_dims", None) or sharding_axis_dims)
@@ -312,6 +314,14 @@ class EasyDeLBaseConfig(PretrainedConfig):
         self.fsdp_is_ep_bound = fsdp_is_ep_bound
         self.sp_is_ep_bound = sp_is_ep_bound
         self.operation_configs = operation_configs
+        # "sharded": every rank of the dp x fsdp group keeps 1/N of each decoder layer's parameters and layers are
+        # gathered one at a time (parallel.fsdp); "hoisted": full bf16 weights on every rank, only the optimizer
+        # state is sharded (parallel.dist_optim); "auto": hoisted while the replicas fit in device memory.
+        if str(fsdp_parameter_sharding).lower() not in ("auto", "sharded", "hoisted"):
+            raise ValueError(f"fsdp_parameter_sharding must be auto / sharded / hoisted, got {fsdp_parameter_sharding!r}")
+        self.fsdp_parameter_sharding = str(fsdp_parameter_sharding).lower()
+        # tensor-parallel dense stacks keep the residual stream sharded by token rows between their linears
+        self.tp_sequence_parallel = bool(tp_sequence_parallel)
         self.pretraining_tp = 1
         if self.kv_cache_quantization_config is not None and self.use_sharded_kv_caching:
             warnings.warn("`kv_cache_quantization_config` and `use_sharded_kv_caching` can't be used together "

@@ -150,6 +150,21 @@ class EasyDeLBaseModule(nn.Module, EasyBridgeMixin, EasyGenerationMixin):
     def gradient_checkpointing_policy(self) -> str:
         return str(getattr(self.config, "gradient_checkpointing", "") or "")
 
+    def remat_policy(self):
+        """The activation save policy of this model's layers (``ops.remat.SavePolicy``), from
+        ``config.gradient_checkpointing`` and, for the name-based policies, ``config.gradient_checkpointing_targets``
+        (the names to save, or to exclude for the ``..._except_these_names`` policies)."""
+        from ..ops import remat
+
+        key = (self.gradient_checkpointing_policy(), tuple(getattr(self.config, "gradient_checkpointing_targets",
+                                                                   None) or ()))
+        cached = getattr(self, "_remat_policy", None)
+        if cached is None or cached[0] != key:
+            targets = list(key[1]) or None
+            cached = (key, remat.get_policy(key[0], save_names=targets, exclude_names=targets))
+            object.__setattr__(self, "_remat_policy", cached)
+        return cached[1]
+
     # ------------------------------------------------------------------ parallel runtime hooks
     def shard_model(self, partition_rules=None, mesh=None, **_):
         """Places parameters according to the mesh. With one rank this is a no-op; with several the

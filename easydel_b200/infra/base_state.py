@@ -46,15 +46,48 @@ class EasyDeLState:
         self.tx = tx
         mesh = getattr(self.model.config, "mesh", None)
         world = mesh.axis_size(("dp", "fsdp")) if mesh is not None and mesh.is_distributed else 1
+        self._fsdp = None
         if world > 1:
             from ..parallel.dist_optim import DistributedFlat
 
-            self._dist = DistributedFlat(self.model, mesh, no_decay_patterns=no_decay_patterns)
+            param_filter = None
+            if self._wants_sharded_parameters(world):
+                # the decoder layers keep 1/world of their parameters per rank (parallel.fsdp); embeddings, final
+                # norm and LM head stay with the optimizer-sharded flat storage below
+                from ..parallel.fsdp import ShardedLayers
+
+                backbone = self.model.model
+                self._fsdp = ShardedLayers(backbone.layers, mesh, prefix="model.layers",
+                                           no_decay_patterns=no_decay_patterns)
+                backbone.fsdp_layers = self._fsdp
+                self._fsdp.opt_state = tx.init_state(self._fsdp.master)
+                param_filter = lambda n, p: not n.startswith("model.layers.")  # noqa: E731
+            self._dist = DistributedFlat(self.model, mesh, no_decay_patterns=no_decay_patterns,
+                                         param_filter=param_filter)
             self.flat = self._dist.flat
         else:
             self.flat = FlatParams(self.model, no_decay_patterns=no_decay_patterns)
         self.flat.opt_state = tx.init_state(self.flat.master)
         return self
+
+    def _wants_sharded_parameters(self, world: int) -> bool:
+        """``config.fsdp_parameter_sharding``: "sharded" keeps 1/N of every decoder layer per rank and gathers
+        layer by layer, "hoisted" keeps full bf16 weights and fp32 gradients on every rank and shards only the
+        optimizer state, "auto" (default) takes "hoisted" while those replicas fit comfortably in device memory."""
+        cfg = getattr(self.model, "config", None)
+        mode = str(getattr(cfg, "fsdp_parameter_sharding", "auto")).lower()
+        layers = getattr(getattr(self.model, "model", None), "layers", None)
+        if mode == "hoisted" or layers is None or len(layers) == 0 or not hasattr(self.model.model, "_run_layer"):
+            return False
+        if mode == "sharded":
+            return True
+        n = sum(p.numel() for p in self.model.parameters())
+        replicas = n * (2 + 4)                       # bf16 weights + fp32 gradient buffer on every rank
+        dev = next(self.model.parameters()).device
+        if dev.type != "cuda":
+            return False
+        total = torch.cuda.get_device_properties(dev).total_memory
+        return replicas + n * 12 // world > 0.6 * total
 
     @property
     def opt_state(self):
@@ -98,7 +131,14 @@ class EasyDeLState:
             flat.sync_replicated_grads(ep_group)
             grad_scale = grad_scale / ep
         if self._dist is not None:
-            norm = self._dist.step(tx, step=self.step, lr=lr, grad_scale=grad_scale, zero_grad=zero_grad)
+            extra = None
+            if self._fsdp is not None:
+                extra = self._sharded_layers_sumsq()
+            norm = self._dist.step(tx, step=self.step, lr=lr, grad_scale=grad_scale, zero_grad=zero_grad,
+                                   extra_sumsq=extra)
+            if self._fsdp is not None:
+                coef, skip, gscale = self._dist.last_clip
+                self._fsdp.update(tx, step=self.step, lr=lr, gscale=gscale, coef=coef, skip=skip)
             self.last_grad_norm = norm
             return norm
         g = flat.grad_shard
@@ -126,6 +166,18 @@ class EasyDeLState:
                       gscale_tensor=coef, skip_tensor=skip, decay=decay, zero_grad=zero_grad)
         self.last_grad_norm = norm
         return norm
+
+    def _sharded_layers_sumsq(self) -> torch.Tensor:
+        """Sum of squared gradients of the layer-sharded parameters over the whole model (one float, on device)."""
+        import torch.distributed as dist
+
+        rt = self._fsdp
+        parts = rt.finish_reduction().clone()          # [tensor-parallel shards, the rest] of this rank's slices
+        dist.all_reduce(parts, group=rt.group)         # the slices of all ranks make up the layers
+        mesh = self._model_mesh()
+        if mesh is not None and mesh.tp > 1 and rt._tp_mask_ranges():
+            dist.all_reduce(parts[0:1], group=mesh.get_group("tp"))
+        return parts.sum().reshape(1)
 
     def _model_mesh(self):
         mesh = getattr(getattr(self.model, "config", None), "mesh", None)

@@ -76,6 +76,15 @@ def save_model(model, save_directory: str, float_dtype=None, step: int | None = 
                write_card: bool = True, **_) -> str:
     """``save_pretrained``: config, generation config, model card, index and parameter arrays."""
     float_dtype = coerce_dtype(float_dtype)
+    fsdp = getattr(getattr(model, "model", None), "fsdp_layers", None)
+    if fsdp is not None:       # parameter-sharded layers: assemble them for the duration of the save (a collective)
+        fsdp.materialize()
+        try:
+            return save_model(_Unsharded(model), save_directory, float_dtype=float_dtype, step=step, gather=gather,
+                              write_card=write_card)
+        finally:
+            fsdp.dematerialize()
+    model = getattr(model, "_wrapped", model)
     # Tensor- / expert-parallel shards are all-gathered into full tensors first (a collective over those groups,
     # so every rank takes part); only the writer rank touches the disk.
     ed_state = PT.model_to_easydel_state(model) if (PT.is_model_parallel(model) or _is_writer()) else None
@@ -109,6 +118,18 @@ def save_model(model, save_directory: str, float_dtype=None, step: int | None = 
     return save_directory
 
 
+class _Unsharded:
+    """Marks a model whose parameter-sharded layers are currently materialised (see ``save_model``)."""
+
+    def __init__(self, model):
+        self._wrapped = model
+
+    def __getattr__(self, name):
+        if name == "model":      # hides ``model.fsdp_layers`` from the recursive call
+            return None
+        return getattr(self._wrapped, name)
+
+
 def save_optimizer_state(state, save_directory: str) -> None:
     """Optimizer moments + fp32 master weights, named like the parameters they belong to."""
     flat = state.flat
@@ -123,6 +144,10 @@ def save_optimizer_state(state, save_directory: str) -> None:
             if model_parallel:  # same assembly as the parameter itself (a collective over the tp / ep group)
                 view = PT.gather_tensor_from_ranks(state.model, pname, view, mods)
             tensors[f"{sname}.{pname}"] = view
+    fsdp = getattr(state, "_fsdp", None)
+    if fsdp is not None:       # master weights and moments of the parameter-sharded layers (a collective)
+        for key, full in fsdp.named_state():
+            tensors[key] = full.cpu() if _is_writer() else None
     if not _is_writer():
         return
     entries = write_tree(save_directory, OPTIMIZER_PREFIX, tensors)
@@ -244,6 +269,13 @@ def load_config(path: str, config_kwargs: dict | None = None, **overrides):
 
 
 def load_weights_into(model, path: str, strict: bool = True) -> None:
+    fsdp = getattr(getattr(model, "model", None), "fsdp_layers", None)
+    if fsdp is not None and fsdp._materialized is None:
+        fsdp.materialize()          # full parameters to load into, then back into the shards
+        try:
+            return load_weights_into(model, path, strict=strict)
+        finally:
+            fsdp.dematerialize(reshard=True)
     if os.path.exists(os.path.join(path, TENSORSTORE_INDEX_NAME)):
         PT.load_easydel_state(model, read_tree(path, MODEL_PREFIX), strict=strict)
         return
@@ -303,6 +335,9 @@ def load_optimizer_state(state, path: str, tx_template=None) -> None:
                 full = PT.shard_tensor_for_rank(state.model, pname, full, mods).contiguous()
             src = full.reshape(-1)[a - off:b - off]
             buf[a - lo:b - lo].copy_(src.to(buf.dtype))
+    fsdp = getattr(state, "_fsdp", None)
+    if fsdp is not None:
+        fsdp.load_named_state(tree)
     sp = os.path.join(path, TX_STRUCTURE_NAME)
     if os.path.exists(sp):
         with open(sp, encoding="utf-8") as f:

@@ -97,6 +97,7 @@ class Attention(nn.Module):
                                              tp_group=tp_group)
         self.o_proj = RowParallelLinear(num_heads * head_dim, hidden_size, bias=o_bias, dtype=dtype,
                                         init_std=init_std, tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group)
+        self.qkv_proj.remat_name, self.o_proj.remat_name = "attn_qkv", "attn_output"
         self.qk_norm, self.qk_norm_eps = qk_norm, qk_norm_eps
         if qk_norm == "rms_head":      # per-head RMSNorm over head_dim (Qwen3, Gemma3, OLMo... per-head flavour)
             self.q_norm = RMSNorm(head_dim, qk_norm_eps, dtype, offset=qk_norm_offset)

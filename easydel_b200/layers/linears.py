@@ -33,6 +33,8 @@ class ParallelLinear(nn.Module):
     parallel_style = "replicated"
     # set by a model that can run its layers on sequence-sharded activations (``parallel.tp.SequenceParallelState``)
     sp_state = None
+    # activation-checkpoint name of this product (``ops.remat``): set by the block that owns the layer
+    remat_name: str | None = None
 
     def __init__(self, in_features: int, out_features: int | tp.Sequence[int], bias: bool = False, *,
                  dtype: torch.dtype = torch.float32, init_std: float | None = 0.02, tp_size: int = 1,
@@ -87,7 +89,7 @@ class ParallelLinear(nn.Module):
 
     def forward(self, x: torch.Tensor, w: torch.Tensor | None = None) -> torch.Tensor:
         """``w`` overrides the weight (tied embeddings pass the embedding table here)."""
-        y = F.linear(x, self.weight if w is None else w, self.bias)
+        y = F.linear(x, self.weight if w is None else w, self.bias, name=self.remat_name)
         if self.scale is not None:
             y = y * self.scale
         return y

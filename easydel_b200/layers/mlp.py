@@ -24,6 +24,7 @@ class GatedMLP(nn.Module):
                                                  tp_group=tp_group)
         self.down_proj = RowParallelLinear(intermediate_size, hidden_size, bias=bias, dtype=dtype, init_std=init_std,
                                            tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group)
+        self.gate_up_proj.remat_name, self.down_proj.remat_name = "mlp_gate_up", "mlp_down"
 
     # fixed muP multipliers on the gate pre-activation and on the output (Falcon-H1); 1.0 elsewhere
     gate_multiplier: float = 1.0
@@ -50,6 +51,7 @@ class PlainMLP(nn.Module):
                                         tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group)
         self.fc2 = RowParallelLinear(intermediate_size, hidden_size, bias=bias, dtype=dtype, init_std=init_std,
                                      tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group)
+        self.fc1.remat_name, self.fc2.remat_name = "mlp_gate_up", "mlp_down"
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.fc2(ACT2FN[self.act](self.fc1(x)))

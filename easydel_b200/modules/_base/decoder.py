@@ -400,9 +400,20 @@ class DecoderModel(EasyDeLBaseModule):
     def get_input_embeddings(self):
         return self.embed_tokens
 
+    #: set by ``EasyDeLState.init_tx`` when the decoder layers are parameter-sharded (``parallel.fsdp``)
+    fsdp_layers = None
+
     def _run_layer(self, layer, x, pending, positions, segment_ids, cache_view, attn_meta, policy):
+        if self.fsdp_layers is not None and cache_view is None:
+            # the layer's weights are gathered for the call; under autograd the layer is a recompute unit
+            return self.fsdp_layers.run(layer.layer_idx, layer, x, _resolve(pending), positions, segment_ids,
+                                        self.remat_policy())
         if policy and self.training and torch.is_grad_enabled() and cache_view is None:
-            return checkpoint(layer, x, pending, positions, segment_ids, None, None, use_reentrant=False)
+            # recompute unit under the configured save policy (full recompute, saved dots, saved names ...)
+            from ...ops import remat
+
+            return remat.recompute_unit(lambda a, b, c, d: layer(a, b, c, d, None, None), self.remat_policy(),
+                                        (x, _resolve(pending), positions, segment_ids))
         return layer(x, pending, positions, segment_ids, cache_view, attn_meta)
 
     def forward(self, input_ids: torch.Tensor | None = None, attention_mask: torch.Tensor | None = None,

@@ -89,8 +89,15 @@ def attn_bwd(q, k, v, o, lse, do, *, causal=True, scale=None, window=0, softcap=
 class _FlashAttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, scale, window, softcap, sinks, cu, max_len):
-        o, lse = attn_fwd(q, k, v, causal=causal, scale=scale, window=window, softcap=softcap, sinks=sinks, cu_q=cu,
-                          cu_k=cu, max_q=max_len, max_k=max_len)
+        from . import remat
+
+        hit, kept = remat.saved_output("attn_core", "attn")   # recompute of a unit that kept the kernel's result
+        if hit:
+            o, lse = kept
+        else:
+            o, lse = attn_fwd(q, k, v, causal=causal, scale=scale, window=window, softcap=softcap, sinks=sinks,
+                              cu_q=cu, cu_k=cu, max_q=max_len, max_k=max_len)
+            remat.keep_output("attn_core", "attn", (o, lse))
         ctx.save_for_backward(q, k, v, o, lse, cu)
         ctx.args = (causal, scale, window, softcap, max_len)
         ctx.has_sinks = sinks is not None

@@ -13,7 +13,7 @@ import math
 
 import torch
 
-from . import _lib, kernels as K, reference as R
+from . import _lib, kernels as K, reference as R, remat
 
 
 def _as_2d(x: torch.Tensor) -> torch.Tensor:
@@ -26,10 +26,13 @@ def _as_2d(x: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------- linear
 class _LinearFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias):
+    def forward(ctx, x, w, bias, name=None):
         x2 = _as_2d(x)
-        y = torch.empty((*x.shape[:-1], w.shape[0]), dtype=x.dtype, device=x.device)
-        K.gemm(x2, w, bias=bias, out=y.view(-1, w.shape[0]))
+        hit, y = remat.saved_output(name, "dot")   # recompute of a unit that kept this product: no GEMM
+        if not hit:
+            y = torch.empty((*x.shape[:-1], w.shape[0]), dtype=x.dtype, device=x.device)
+            K.gemm(x2, w, bias=bias, out=y.view(-1, w.shape[0]))
+            remat.keep_output(name, "dot", y)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
         ctx.x_shape = x.shape
@@ -52,11 +55,13 @@ class _LinearFn(torch.autograd.Function):
                 dw = K.gemm(dy2, x2, a_mn=True, b_mn=True)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
-        return dx, dw, db
+        return dx, dw, db, None
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
-    """y = x @ w.T + bias with ``w`` in torch Linear layout ``[out, in]``."""
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+           name: str | None = None) -> torch.Tensor:
+    """y = x @ w.T + bias with ``w`` in torch Linear layout ``[out, in]``. ``name``: the activation-checkpoint
+    name of this product (see :mod:`.remat`)."""
     if _lib.use_kernels(x):
         if x.dtype != torch.bfloat16:
             raise TypeError(f"GPU linear expects bf16 activations, got {x.dtype}")
@@ -64,7 +69,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
             # rows of the operands / the output would not start on 16-byte boundaries (a 4-way router, a 3-class
             # head ...): a plain library product; such matrices are a few kilobytes
             return torch.nn.functional.linear(x, w.to(x.dtype), None if bias is None else bias.to(x.dtype))
-        return _LinearFn.apply(x, w, bias)
+        return _LinearFn.apply(x, w, bias, name)
     return R.linear(x, w, bias)
 
 

@@ -38,7 +38,8 @@ _lib.register("edl_dist_adamw_bcast", _lib.i32, [_lib.vp, _lib.vp, _lib.vp, _lib
 
 
 class DistributedFlat:
-    def __init__(self, model, mesh, no_decay_patterns: tp.Sequence[str] = (), use_peer_kernels: bool | None = None):
+    def __init__(self, model, mesh, no_decay_patterns: tp.Sequence[str] = (), use_peer_kernels: bool | None = None,
+                 param_filter=None):
         self.mesh = mesh
         axes = ("dp", "fsdp")
         self.group = mesh.get_group(axes)
@@ -57,7 +58,8 @@ class DistributedFlat:
                 return t
 
         self.flat = FlatParams(model, world_size=self.world, rank=self.rank, no_decay_patterns=no_decay_patterns,
-                               alloc=alloc)
+                               alloc=alloc, param_filter=param_filter)
+        self.last_clip = (None, None, 1.0)   # (clip coefficient, non-finite flag, gradient scale) of the last step
         flat = self.flat
         # identical starting weights everywhere: rank 0 of the group is the source
         src = dist.get_global_rank(self.group, 0) if self.group is not None else 0
@@ -84,8 +86,11 @@ class DistributedFlat:
             dist.barrier(group=self.group)
 
     @torch.no_grad()
-    def step(self, tx, *, step: int, lr: float, grad_scale: float = 1.0, zero_grad: bool = True) -> torch.Tensor:
-        """One sharded optimizer step. Returns the global gradient norm (device tensor)."""
+    def step(self, tx, *, step: int, lr: float, grad_scale: float = 1.0, zero_grad: bool = True,
+             extra_sumsq: torch.Tensor | None = None) -> torch.Tensor:
+        """One sharded optimizer step. Returns the global gradient norm (device tensor). ``extra_sumsq``: sum of
+        squared gradients of parameters kept elsewhere (already summed over every group), to be part of the norm;
+        the clip factor and the non-finite flag of the step are left in ``last_clip`` for that other runtime."""
         flat = self.flat
         n_shard = flat.shard_hi - flat.shard_lo
         # the mean over ranks is part of the gradient scale
@@ -110,6 +115,8 @@ class DistributedFlat:
         dist.all_reduce(self._sumsq, group=self.group)
         # tensor- / expert-parallel shards: add the other ranks' pieces so that every rank clips with one norm
         self._sumsq.copy_(flat.global_sumsq(self._sumsq, g, flat.shard_lo, self.mesh, dp_group=self.group))
+        if extra_sumsq is not None:
+            self._sumsq += extra_sumsq.reshape(-1)[:1].to(self._sumsq.dtype)
         if g.is_cuda and _lib.available():
             from ..ops import kernels as K
 
@@ -119,6 +126,7 @@ class DistributedFlat:
             skip = (~torch.isfinite(norm)).to(torch.int32).reshape(1)
             coef = torch.clamp((tx.clip_grad or float("inf")) / (norm + 1e-6), max=1.0).reshape(1) \
                 if tx.clip_grad else None
+        self.last_clip = (coef, skip, gscale)
         for lo, hi, decay in flat.decay_ranges():
             state = {k: v[lo:hi] for k, v in flat.opt_state.items()}
             if fused:

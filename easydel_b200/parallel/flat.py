@@ -31,10 +31,14 @@ def _round_up(n: int, a: int) -> int:
 
 class FlatParams:
     def __init__(self, model: nn.Module, *, world_size: int = 1, rank: int = 0, grad_dtype=torch.float32,
-                 no_decay_patterns: tp.Sequence[str] = (), alloc: tp.Callable | None = None):
+                 no_decay_patterns: tp.Sequence[str] = (), alloc: tp.Callable | None = None,
+                 param_filter: tp.Callable[[str, nn.Parameter], bool] | None = None):
+        """``param_filter(name, param)`` selects the parameters this storage owns (default: all trainable ones);
+        the rest belong to another runtime, e.g. the layer-sharded one of ``parallel.fsdp``."""
         self.model = model
         self.world_size, self.rank = world_size, rank
-        params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        params = [(n, p) for n, p in model.named_parameters()
+                  if p.requires_grad and (param_filter is None or param_filter(n, p))]
         # parameters shared under several names (tied embeddings) appear once
         seen: dict[int, str] = {}
         uniq = []

@@ -135,6 +135,13 @@ def _peer_ctx(group, device) -> _PeerAllReduce | None:
     return _CTX[key]
 
 
+def release_peer_buffers() -> None:
+    """Drops the symmetric buffers of the one-shot all-reduce and of the fused GEMM plans. Call with no kernel
+    in flight (after a synchronize) and before the process groups are destroyed."""
+    _CTX.clear()
+    _PLANS.clear()
+
+
 def all_reduce(x: torch.Tensor, group) -> torch.Tensor:
     """Sum over the tensor-parallel group (out of place)."""
     if group is None or dist.get_world_size(group) == 1:

@@ -66,9 +66,12 @@ def test_scheduler_budget_chunking_and_preemption():
     assert pool.num_free >= 0
 
 
-def test_engine_matches_generate_and_uses_prefix_cache():
+@pytest.mark.parametrize("async_scheduling", [False, True])
+def test_engine_matches_generate_and_uses_prefix_cache(async_scheduling):
     model = _model()
-    eng = eSurge(model, max_model_len=1024, max_num_seqs=8, max_num_batched_tokens=256, num_pages=32)
+    eng = eSurge(model, max_model_len=1024, max_num_seqs=8, max_num_batched_tokens=256, num_pages=32,
+                 async_scheduling=async_scheduling)
+    assert eng.async_scheduling == async_scheduling
     g = torch.Generator().manual_seed(1)
     shared = torch.randint(0, 198, (130,), generator=g).tolist()
     prompts = [shared + torch.randint(0, 198, (n,), generator=g).tolist() for n in (5, 40, 300)]
@@ -165,3 +168,32 @@ def test_hybrid_recurrent_models_are_served_with_per_slot_states(family):
     # a slot taken by a new request starts from a zero state
     again = eng.generate([prompts[1]], SamplingParams(max_tokens=5, temperature=0.0))[0]
     assert again.outputs[0].token_ids == outs[1].outputs[0].token_ids
+
+
+def test_async_scheduling_eos_stop_preemption_and_unknown_options():
+    """Step t+1 is launched before step t's tokens are read: a request that stops on a token (not on its length)
+    has one row too many in flight, whose result must be dropped; preempted requests keep the token sampled
+    before the preemption; outputs equal the synchronous engine's."""
+    model = _model()
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 198, (n,), generator=g).tolist() for n in (7, 150, 33, 260, 90)]
+    sync = eSurge(model, max_model_len=512, max_num_seqs=4, max_num_batched_tokens=128, num_pages=12,
+                  async_scheduling=False)
+    ref = sync.generate(prompts, SamplingParams(max_tokens=40, temperature=0.0, ignore_eos=True))
+    # stop on the 5th token of the longest-running request: a token-triggered stop
+    stop_tok = ref[0].outputs[0].token_ids[4]
+    sp = SamplingParams(max_tokens=40, temperature=0.0, ignore_eos=True, stop_token_ids=[stop_tok])
+    want = eSurge(model, max_model_len=512, max_num_seqs=4, max_num_batched_tokens=128, num_pages=12,
+                  async_scheduling=False).generate(prompts, sp)
+    eng = eSurge(model, max_model_len=512, max_num_seqs=4, max_num_batched_tokens=128, num_pages=12,
+                 async_scheduling=True)
+    got = eng.generate(prompts, sp)
+    for a, b in zip(got, want):
+        assert a.outputs[0].token_ids == b.outputs[0].token_ids
+        assert a.outputs[0].finish_reason == b.outputs[0].finish_reason
+    assert got[0].outputs[0].finish_reason == "stop" and len(got[0].outputs[0].token_ids) <= 5
+    assert eng._inflight is None and not eng.scheduler.has_unfinished()
+    assert eng.pool.num_free == eng.pool.num_pages - 1 or eng.pool.num_free > 0
+    with pytest.raises(TypeError):
+        eSurge(model, max_model_len=64, max_num_seqs=2, num_pages=4, overlap_executon=True)   # misspelt
+    eSurge(model, max_model_len=64, max_num_seqs=2, num_pages=4, compile_runner=True)         # reference AOT knob

@@ -109,3 +109,34 @@ def test_micro_batch_accumulation_matches_full_batch():
     for n in a:
         rel = ((a[n] - b[n]).norm() / (a[n].norm() + 1e-8)).item()
         assert rel < 0.03, f"{n}: {rel}"
+
+
+@pytest.mark.parametrize("policy,targets", [("dots_saveable", None), ("save_only_these_names", ["attn_core", "mlp_gate"]),
+                                            ("mlp_notsaveable", None), ("nothing_saveable", None)])
+def test_activation_save_policies_match_no_checkpointing(policy, targets):
+    """Every save policy gives the gradients of the un-checkpointed model; policies that keep op outputs launch
+    fewer kernels in the recompute than full recomputation does."""
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+    from easydel_b200.ops import _lib
+
+    def run(pol, tg):
+        cfg = LlamaConfig(vocab_size=2048, hidden_size=512, intermediate_size=1408, num_hidden_layers=2,
+                          num_attention_heads=8, num_key_value_heads=2, head_dim=64, max_position_embeddings=512,
+                          gradient_checkpointing=pol, gradient_checkpointing_targets=tg)
+        torch.manual_seed(0)
+        m = LlamaForCausalLM(cfg, dtype=torch.bfloat16, param_dtype=torch.bfloat16).cuda().train()
+        ids = torch.randint(0, 2048, (2, 256), generator=torch.Generator().manual_seed(1)).cuda()
+        n0 = _lib.launch_count
+        _, met = m.compute_loss(input_ids=ids, labels=ids)
+        met.loss.backward()
+        torch.cuda.synchronize()
+        return float(met.loss), {k: p.grad.float().clone() for k, p in m.named_parameters()}, _lib.launch_count - n0
+
+    loss0, g0, _ = run("everything_saveable", None)
+    loss1, g1, n1 = run(policy, targets)
+    assert abs(loss0 - loss1) < 1e-3
+    for k in g0:
+        assert torch.allclose(g0[k], g1[k], atol=2e-3, rtol=2e-2), k
+    if policy != "nothing_saveable":
+        _, _, n_full = run("nothing_saveable", None)
+        assert n1 < n_full, (n1, n_full)
