@@ -154,13 +154,53 @@ def bench_layer(args) -> None:
     print(f"layers={args.layers} tokens={args.tokens}: fwd+bwd micro-batch {s.elapsed_time(e):.2f} ms")
 
 
+def bench_decode(args) -> None:
+    """Decode-step kernels at the per-GPU shapes of Llama-3-70B under 8-way tensor parallelism (8 query heads on one
+    KV head, hidden 8192, FFN 3584) with 256 running sequences: the streaming decode-attention kernel against the
+    general paged kernel, and the four skinny GEMMs of a layer against the weight-streaming bound."""
+    from easydel_b200.ops import serving as S
+
+    pk = _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    B, Hq, Hkv, D = 256, 8, 1, 128
+    for ctx in (700, 2700):
+        pages_per = (ctx + 127) // 128
+        P = B * pages_per + 1
+        kp = torch.randn(P, 128, Hkv, D, device="cuda").to(torch.bfloat16)
+        vp = torch.randn(P, 128, Hkv, D, device="cuda").to(torch.bfloat16)
+        table = (torch.randperm(P - 1, device="cuda")[: B * pages_per] + 1).to(torch.int32).view(B, pages_per)
+        lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+        cu = torch.arange(B + 1, dtype=torch.int32, device="cuda")
+        q = torch.randn(B, Hq, D, device="cuda").to(torch.bfloat16)
+        kv_bytes = 2.0 * B * ctx * Hkv * D * 2
+        ms_new = time_cuda(lambda: S.decode_attention(q, kp, vp, lens, table), flush=flush)
+        ms_old = time_cuda(lambda: S.paged_attention(q, kp, vp, cu, lens, table, 1), flush=flush)
+        print(f"decode attention B={B} ctx={ctx} Hq/Hkv={Hq}/{Hkv}: streaming kernel {ms_new * 1e3:7.1f} us "
+              f"({kv_bytes / ms_new / 1e6:6.0f} GB/s, {kv_bytes / ms_new / 1e6 / pk['hbm_gbs']:.2f} of {pk['src']} copy "
+              f"bandwidth)   general paged kernel {ms_old * 1e3:7.1f} us", flush=True)
+    for name, M, N, Kd in (("qkv", B, 1280, 8192), ("o", B, 8192, 1024), ("gate_up", B, 7168, 8192),
+                           ("down", B, 8192, 3584)):
+        a = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
+        w = torch.randn(N, Kd, device="cuda").to(torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = time_cuda(lambda: K.gemm(a, w, out=out), flush=flush)
+        ms_lib = time_cuda(lambda: torch.matmul(a, w.t(), out=out), flush=flush)
+        wbytes = 2.0 * N * Kd
+        print(f"decode GEMM {name:8s} M={M} N={N:5d} K={Kd:5d}: ours {ms * 1e3:6.1f} us ({wbytes / ms / 1e6:5.0f} GB/s of "
+              f"weights, {wbytes / ms / 1e6 / pk['hbm_gbs']:.2f} of {pk['src']} copy bandwidth)   cuBLAS "
+              f"{ms_lib * 1e3:6.1f} us", flush=True)
+    from easydel_b200.ops import _lib
+
+    _lib.check_status()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("what", choices=["gemm", "attention", "layer"])
+    ap.add_argument("what", choices=["gemm", "attention", "layer", "decode"])
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=2)
     a = ap.parse_args()
-    {"gemm": bench_gemm, "attention": bench_attention, "layer": bench_layer}[a.what](a)
+    {"gemm": bench_gemm, "attention": bench_attention, "layer": bench_layer, "decode": bench_decode}[a.what](a)
 
 
 if __name__ == "__main__":

@@ -144,6 +144,12 @@ class PagedLayerView:
         if getattr(attn, "chunk_size", None) or (q3.is_cuda and q3.shape[-1] not in (64, 128)):
             # block-diagonal attention, or a head size outside the paged kernel's (64 / 128)
             return self._attend_gathered(attn, q3, meta)[None]
+        if meta.max_q == 1 and q3.shape[0] == meta.num_seqs and S.decode_kernel_supports(q3, self.k_pages,
+                                                                                           attn.softcap):
+            # a pure decode step: the streaming kernel (one CTA per sequence, KV head and key split)
+            o = S.decode_attention(q3, self.k_pages, self.v_pages, meta.kv_lens, meta.page_table, scale=attn.scale,
+                                   window=attn.sliding_window or 0, sinks=attn.sinks, num_splits=meta.num_splits)
+            return o[None]
         if meta.num_splits > 1 and meta.max_q == 1 and not attn.sliding_window and q3.is_cuda:
             o = S.paged_attention_splitkv(q3, self.k_pages, self.v_pages, meta.kv_lens, meta.page_table,
                                           meta.num_splits, scale=attn.scale, softcap=attn.softcap, sinks=attn.sinks)

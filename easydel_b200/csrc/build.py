@@ -7,7 +7,10 @@ and a stream handle) and is loaded with ``ctypes``; no Python headers are needed
 so a file compiles in seconds and cross-compiles on a machine without a GPU.
 
 Run ``python -m easydel_b200.csrc.build`` (add ``--force`` to rebuild everything,
-``--verbose`` for ptxas register/shared-memory reports).
+``--verbose`` for ptxas register/shared-memory reports). ``EDL_NVCC_EXTRA`` adds compiler flags, and
+``--out PATH`` links the result somewhere else, so that a checking build
+(``EDL_NVCC_EXTRA=-DEDL_BOUNDS_CHECK python -m easydel_b200.csrc.build --out /tmp/libedl_check.so``, loaded
+with ``EDL_LIB_PATH``) can sit beside the production library.
 """
 
 from __future__ import annotations
@@ -76,12 +79,21 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -> Path:
-    """Compiles what changed and links the shared library; returns its path."""
+def build(force: bool = False, verbose: bool = False, jobs: int | None = None, out: str | None = None) -> Path:
+    """Compiles what changed and links the shared library; returns its path. ``out``: link there instead of the
+    in-tree location, with the objects in a directory of their own (a build with other flags beside the main one)."""
+    global BUILD, LIB_PATH
     nvcc = _nvcc()
+    if out is not None:
+        LIB_PATH = Path(out).resolve()
+        BUILD = CSRC / "build" / ("alt-" + hashlib.sha256(str(LIB_PATH).encode()).hexdigest()[:8])
+        BUILD.mkdir(parents=True, exist_ok=True)
+        LIB_PATH.parent.mkdir(parents=True, exist_ok=True)
     BUILD.mkdir(exist_ok=True)
     LIB_DIR.mkdir(exist_ok=True)
     flags = list(NVCC_FLAGS)
+    extra = os.environ.get("EDL_NVCC_EXTRA", "").split()   # e.g. -DEDL_BOUNDS_CHECK for a checking build
+    flags += extra
     if verbose:
         flags += ["-Xptxas", "-v"]
     srcs = sources()
@@ -111,8 +123,9 @@ def main() -> None:
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("-j", "--jobs", type=int, default=None)
+    ap.add_argument("--out", default=None, help="link the library here instead of easydel_b200/lib/")
     a = ap.parse_args()
-    print(build(force=a.force, verbose=a.verbose, jobs=a.jobs))
+    print(build(force=a.force, verbose=a.verbose, jobs=a.jobs, out=a.out))
 
 
 if __name__ == "__main__":

@@ -21,9 +21,10 @@ from .base_config import EasyDeLBaseConfig, coerce_dtype
 from .loss_utils import LossConfig, LossMetrics
 from .mixins.bridge import EasyBridgeMixin
 from .mixins.generation import EasyGenerationMixin
+from .mixins.operation_cache import OperationCacheMixin
 
 
-class EasyDeLBaseModule(nn.Module, EasyBridgeMixin, EasyGenerationMixin):
+class EasyDeLBaseModule(nn.Module, EasyBridgeMixin, EasyGenerationMixin, OperationCacheMixin):
     config_class: type[EasyDeLBaseConfig] = EasyDeLBaseConfig
     base_model_prefix: str = "model"
     _model_task: str | None = None

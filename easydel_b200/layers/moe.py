@@ -68,6 +68,53 @@ def router_z_loss(router_logits: torch.Tensor) -> torch.Tensor:
     return torch.logsumexp(router_logits.float(), dim=-1).pow(2).mean()
 
 
+class MoeRoutingStrategy:
+    """Routing strategies of the reference (easydel/layers/moe/_communication_utils.py:1024-1078)."""
+
+    TOP_K = "top_k"                 # top-k experts per token, weights renormalised to sum to one
+    TOP_K_NDIV = "top_k_ndiv"       # top-k experts per token, raw probabilities as weights
+    SWITCH = "switch"               # one expert per token, weight exactly one
+    EMPTY_CHOICE = "expert_choice"  # every expert picks its own tokens (capacity = tokens * k / experts)
+    HASH = "hash"                   # token -> experts by token position, uniform weights (debugging / baselines)
+
+
+class MoeLoadBalancingStrategy:
+    """Auxiliary load-balancing losses (easydel/layers/moe/_moe_module.py:440-510)."""
+
+    STANDARD = "standard"
+    SWITCH_TRANSFORMER = "switch_transformer"
+    EMPTY_CHOICE = "expert_choice"
+    NONE = "none"
+
+
+def load_balancing_loss_by_strategy(router_probs: torch.Tensor, expert_loads: torch.Tensor, num_experts: int, top_k: int,
+                                    strategy: str = MoeLoadBalancingStrategy.STANDARD,
+                                    coef: float | None = 1.0) -> torch.Tensor | None:
+    """``router_probs`` ``[T, E]`` fp32, ``expert_loads`` ``[E]`` token counts per expert."""
+    if strategy == MoeLoadBalancingStrategy.NONE or coef is None:
+        return None
+    loads = expert_loads.to(torch.float32)
+    if strategy == MoeLoadBalancingStrategy.STANDARD:
+        return coef * ((loads * num_experts / top_k) * router_probs.mean(0)).sum()
+    if strategy == MoeLoadBalancingStrategy.SWITCH_TRANSFORMER:
+        return coef * num_experts * ((loads / router_probs.shape[0]) * router_probs.mean(0)).sum()
+    if strategy == MoeLoadBalancingStrategy.EMPTY_CHOICE:
+        return coef * loads.var(unbiased=False)
+    raise ValueError(f"Unknown load balancing strategy: {strategy}")
+
+
+def apply_capacity(idx: torch.Tensor, weights: torch.Tensor, num_experts: int, capacity: int):
+    """Token-choice routing with a per-expert capacity: of the tokens that chose an expert, the first ``capacity``
+    (in token order, first choices before second choices) keep it; the others lose that choice (weight zero).
+    Returns ``(weights with dropped choices zeroed, keep mask [T, k])``."""
+    T, k = idx.shape
+    flat = idx.t().reshape(-1)                       # choice-major: every token's first choice comes first
+    onehot = torch.nn.functional.one_hot(flat, num_experts)
+    rank_in_expert = (onehot.cumsum(0) - 1).gather(1, flat[:, None])[:, 0]
+    keep = (rank_in_expert < capacity).view(k, T).t()
+    return weights * keep.to(weights.dtype), keep
+
+
 class MoEBlock(nn.Module):
     """Router + routed experts (+ optional shared experts)."""
 
@@ -78,8 +125,17 @@ class MoEBlock(nn.Module):
                  shared_gate: bool = False, dtype=torch.float32, init_std: float = 0.02, expert_init_std: float = 0.01,
                  ep_size: int = 1, ep_rank: int = 0, ep_group=None, tp_size: int = 1, tp_rank: int = 0,
                  tp_group=None, router_dtype=None, expert_bias: bool = False, scale_input: bool = False,
-                 router_jitter_eps: float = 0.01):
+                 router_jitter_eps: float = 0.01, routing_strategy: str | None = None,
+                 capacity_factor: float | None = None,
+                 load_balancing_strategy: str = MoeLoadBalancingStrategy.STANDARD, lbl_coef: float | None = None,
+                 rzl_coef: float | None = None):
         super().__init__()
+        # None = top-k with (TOP_K) or without (TOP_K_NDIV) renormalisation, as ``norm_topk_prob`` says
+        self.routing_strategy = getattr(routing_strategy, "value", routing_strategy)
+        self.capacity_factor = capacity_factor     # None = dropless
+        self.load_balancing_strategy = getattr(load_balancing_strategy, "value", load_balancing_strategy)
+        self.lbl_coef, self.rzl_coef = lbl_coef, rzl_coef
+        self.last_aux_losses: dict[str, torch.Tensor] = {}
         self.router_jitter_eps = router_jitter_eps
         # Llama-4: the routing score multiplies the expert's input instead of its output
         self.scale_input = scale_input
@@ -131,9 +187,58 @@ class MoEBlock(nn.Module):
             scores = scores.scatter(-1, ind, float("-inf"))
         return torch.cat(ws, -1), torch.cat(ids, -1), torch.softmax(lf, dim=-1)
 
+    def _route_by_strategy(self, lf: torch.Tensor):
+        """SWITCH / EXPERT_CHOICE / HASH routing; returns None for the top-k strategies handled by :meth:`route`."""
+        st = self.routing_strategy
+        T, E = lf.shape
+        k = self.top_k
+        if st == MoeRoutingStrategy.SWITCH:
+            probs = torch.softmax(lf, dim=-1)
+            idx = probs.argmax(-1, keepdim=True)
+            w = torch.ones(T, 1, dtype=torch.float32, device=lf.device)
+            if k > 1:   # the kernels take k choices per token: the others are expert 0 with weight zero
+                idx = torch.cat([idx, idx.new_zeros(T, k - 1)], 1)
+                w = torch.cat([w, w.new_zeros(T, k - 1)], 1)
+            return w, idx, probs
+        if st == MoeRoutingStrategy.HASH:
+            probs = torch.softmax(lf, dim=-1)
+            base = torch.arange(T, device=lf.device)[:, None] * k + torch.arange(k, device=lf.device)[None]
+            idx = base % E
+            return torch.full((T, k), 1.0 / k, dtype=torch.float32, device=lf.device), idx, probs
+        if st == MoeRoutingStrategy.EMPTY_CHOICE:
+            # every expert takes its `cap` highest-scoring tokens; a token may be taken by 0..E experts. In the
+            # token-major form the kernels use, each token lists up to k of the experts that took it (the ones
+            # with its highest scores); choices beyond the experts that took it get weight zero.
+            probs = torch.softmax(lf, dim=-1)
+            cap = max(1, min(T, int(round(T * k / E * (self.capacity_factor or 1.0)))))
+            taken = torch.zeros(T, E, dtype=torch.bool, device=lf.device)
+            top_tok = probs.topk(cap, dim=0).indices                    # [cap, E]
+            taken.scatter_(0, top_tok, True)
+            score = torch.where(taken, probs, probs.new_full((), -1.0))
+            val, idx = score.topk(k, dim=-1)
+            w = torch.where(val >= 0, torch.full_like(val, 1.0 / k), torch.zeros_like(val))
+            return w, idx, probs
+        return None
+
+    def aux_losses(self, logits: torch.Tensor, probs: torch.Tensor, idx: torch.Tensor, weights: torch.Tensor) -> dict:
+        """Load-balancing loss and router z-loss of this call, when their coefficients are set (the reference's
+        ``lbl_coef`` / ``rzl_coef``, easydel/layers/moe/_moe_module.py:440-560)."""
+        out = {}
+        if self.lbl_coef is not None and self.load_balancing_strategy != MoeLoadBalancingStrategy.NONE:
+            used = idx[weights > 0] if weights is not None else idx.reshape(-1)
+            loads = torch.bincount(used.reshape(-1), minlength=self.num_experts)
+            out["load_balancing_loss"] = load_balancing_loss_by_strategy(
+                probs, loads, self.num_experts, self.top_k, self.load_balancing_strategy, self.lbl_coef)
+        if self.rzl_coef is not None:
+            out["router_z_loss"] = self.rzl_coef * router_z_loss(logits)
+        return out
+
     def route(self, logits: torch.Tensor):
         """Returns (weights [T,k] fp32, idx [T,k] int64, probs [T,E] fp32)."""
         lf = logits.float()
+        if self.routing_strategy in (MoeRoutingStrategy.SWITCH, MoeRoutingStrategy.HASH,
+                                     MoeRoutingStrategy.EMPTY_CHOICE):
+            return self._route_by_strategy(lf)
         if self.scoring == "sparsemixer":
             return self._route_sparsemixer(lf)
         probs = torch.softmax(lf, dim=-1) if self.scoring == "softmax" else torch.sigmoid(lf)
@@ -155,9 +260,15 @@ class MoEBlock(nn.Module):
             scores = torch.where(gmask[..., None] > 0, g, torch.full_like(g, fill)).view(T, E)
         idx = scores.topk(self.top_k, dim=-1).indices
         w = probs.gather(-1, idx)
-        if self.norm_topk_prob:
+        renorm = self.norm_topk_prob if self.routing_strategy is None else \
+            self.routing_strategy == MoeRoutingStrategy.TOP_K
+        if renorm:
             w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
         w = w * self.routed_scaling_factor
+        if self.capacity_factor is not None:       # capacity path: choices beyond an expert's capacity are dropped
+            T = idx.shape[0]
+            cap = max(1, int(self.capacity_factor * T * self.top_k / self.num_experts + 0.999))
+            w, _ = apply_capacity(idx, w, self.num_experts, cap)
         return w, idx, probs
 
     # ------------------------------------------------------------------ forward
@@ -166,7 +277,9 @@ class MoEBlock(nn.Module):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         logits = self.gate(x2)
-        w, idx, _ = self.route(logits)
+        w, idx, probs = self.route(logits)
+        if self.lbl_coef is not None or self.rzl_coef is not None:
+            self.last_aux_losses = self.aux_losses(logits, probs, idx, w)
         if self.scale_input:
             T, k = idx.shape
             x_in = (x2[:, None, :] * w[..., None].to(x2.dtype)).reshape(T * k, -1)

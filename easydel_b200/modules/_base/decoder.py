@@ -55,6 +55,15 @@ class MoESpec:
     expert_act: str | None = None     # gated activation of the experts when it differs from the dense MLP's
     scale_input: bool = False         # routing score applied to the experts' input (Llama-4)
     router_jitter_eps: float = 0.01   # margin of the sparsemixer routing (Phi-3.5-MoE)
+    routing_strategy: str | None = None          # top_k | top_k_ndiv | switch | expert_choice | hash; None = by scoring
+    capacity_factor: float | None = None         # None = dropless
+    load_balancing_strategy: str = "standard"    # standard | switch_transformer | expert_choice | none
+    lbl_coef: float | None = None                # per-block load-balancing loss (added to the training loss)
+    rzl_coef: float | None = None                # per-block router z-loss
+
+
+def _first_set(*values):
+    return next((v for v in values if v is not None), None)
 
 
 @dataclass
@@ -229,6 +238,12 @@ class DecoderLayer(nn.Module):
             self.mlp = MoEBlock(spec.hidden_size, moe.intermediate_size, moe.num_experts, moe.top_k,
                                 act=moe.expert_act or spec.act, expert_bias=moe.expert_bias,
                                 scale_input=moe.scale_input, router_jitter_eps=moe.router_jitter_eps,
+                                routing_strategy=getattr(config, "moe_routing_strategy", None) or moe.routing_strategy,
+                                capacity_factor=getattr(config, "moe_capacity_factor", None) or moe.capacity_factor,
+                                load_balancing_strategy=getattr(config, "moe_load_balancing_strategy", None)
+                                or moe.load_balancing_strategy,
+                                lbl_coef=_first_set(getattr(config, "moe_lbl_coef", None), moe.lbl_coef),
+                                rzl_coef=_first_set(getattr(config, "moe_rzl_coef", None), moe.rzl_coef),
                                 norm_topk_prob=moe.norm_topk_prob, scoring=moe.scoring,
                                 routed_scaling_factor=moe.routed_scaling_factor, n_group=moe.n_group,
                                 topk_group=moe.topk_group, use_score_bias=moe.use_score_bias,
@@ -618,6 +633,15 @@ class DecoderForCausalLM(EasyDeLBaseModule):
             # the auxiliary loss is added to the training loss (easydel/infra/base_module.py:2791-2793)
             metrics.loss = metrics.loss + spec.moe.aux_loss_coef * aux * loss_scale
             metrics.other_metrics = {"aux_loss": aux.detach()}
+        if spec.moe is not None and torch.is_grad_enabled():
+            # per-block losses the blocks computed themselves (lbl_coef / rzl_coef carry their weights)
+            extra: dict[str, torch.Tensor] = {}
+            for layer in self.model.layers:
+                for k, v in getattr(getattr(layer, "mlp", None), "last_aux_losses", {}).items():
+                    extra[k] = extra[k] + v if k in extra else v
+            if extra:
+                metrics.loss = metrics.loss + sum(extra.values()) * loss_scale
+                metrics.other_metrics = {**(metrics.other_metrics or {}), **{k: v.detach() for k, v in extra.items()}}
         return out, metrics
 
 

@@ -18,6 +18,8 @@ _lib.register("edl_paged_kv_append", i32, [vp, vp, vp, vp, vp, i32, i32, i64, i6
 _lib.register("edl_sample", i32, [vp, i32, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i64, vp, vp, vp, vp, vp])
 _lib.register("edl_count_update", i32, [vp, i64, vp, vp, i32, i32, vp])
 _lib.register("edl_gather_rows", i32, [vp, vp, vp, i32, i32, i64, vp])
+_lib.register("edl_attn_decode", i32, [vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, i32, i32, i64, i32, i32, i32, f32,
+                                       i32, i32, vp, vp, vp])
 
 PAGE_SIZE = 128
 
@@ -68,6 +70,34 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         return out
     return paged_attention_reference(q, k_pages, v_pages, cu_q, kv_lens, page_table, scale=scale, causal=causal,
                                      window=window, softcap=softcap, sinks=sinks)
+
+
+def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_lens: torch.Tensor,
+                     page_table: torch.Tensor, *, scale: float | None = None, window: int = 0, sinks=None,
+                     num_splits: int = 1) -> torch.Tensor:
+    """Decode-step attention (one query token per sequence) with the streaming kernel of
+    ``csrc/attention_decode.cu``. q ``[B, Hq, D]``; pages ``[P, 128, Hkv, D]``; ``num_splits`` cuts every
+    sequence's keys into that many parts that run as separate CTAs and are merged by :func:`attn_combine`."""
+    B, Hq, D = q.shape
+    Hkv = k_pages.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    S_ = max(1, int(num_splits))
+    out = torch.empty((S_, B, Hq, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((S_, Hq, B), dtype=torch.float32, device=q.device) if S_ > 1 else None
+    _lib.call("edl_attn_decode", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), _lib.ptr(lse),
+              q.stride(0), k_pages.stride(1), Hq * D, kv_lens.data_ptr(), page_table.data_ptr(),
+              page_table.stride(0), B, k_pages.shape[0], Hq, Hkv, D, float(scale), int(window or 0), S_,
+              _lib.ptr(sinks) if S_ == 1 else None, _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
+    if S_ == 1:
+        return out[0]
+    return attn_combine(out, lse, sinks=sinks)
+
+
+def decode_kernel_supports(q: torch.Tensor, k_pages: torch.Tensor, softcap: float) -> bool:
+    Hq, D = q.shape[-2], q.shape[-1]
+    Hkv = k_pages.shape[2]
+    return (q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and Hq % Hkv == 0 and Hq // Hkv <= 16
+            and not softcap and k_pages.shape[1] == PAGE_SIZE and q.stride(-1) == 1 and q.stride(-2) == D)
 
 
 def attn_combine(o_parts: torch.Tensor, lse_parts: torch.Tensor, sinks=None, want_lse: bool = False):

@@ -152,3 +152,32 @@ def test_greedy_sampler_fast_path_matches_argmax():
     assert torch.equal(tok.long(), ref)
     ref_lp = torch.log_softmax(logits.float(), -1).gather(-1, ref[:, None])[:, 0]
     assert (lp - ref_lp).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 1, 128), (32, 8, 128), (4, 4, 64), (16, 1, 128), (12, 4, 64)])
+@pytest.mark.parametrize("splits,window", [(1, 0), (3, 0), (1, 200)])
+def test_streaming_decode_attention(Hq, Hkv, D, splits, window):
+    """The decode kernel (one query token per sequence, 32-key tiles streamed per warp) against the reference, with
+    ragged key counts (1 key, a count inside a tile, several pages), key splits and a sliding window."""
+    from easydel_b200.ops import serving as S
+
+    P = 48
+    kp, vp = _pool(P, Hkv, D, 5)
+    kv_lens = [1, 31, 33, 128, 129, 777, 1500, 5]
+    B = len(kv_lens)
+    perm = torch.randperm(P, generator=torch.Generator().manual_seed(8)).tolist()
+    maxp = max((L + 127) // 128 for L in kv_lens)
+    table = torch.zeros(B, maxp, dtype=torch.int32)
+    nxt = 0
+    for b, L in enumerate(kv_lens):
+        n = (L + 127) // 128
+        table[b, :n] = torch.tensor(perm[nxt:nxt + n], dtype=torch.int32)
+        nxt += n
+    q = torch.randn(B, Hq, D, device="cuda").to(torch.bfloat16)
+    sinks = torch.randn(Hq, device="cuda") if window == 0 and splits == 1 else None
+    lens = torch.tensor(kv_lens, dtype=torch.int32)
+    o = S.decode_attention(q, kp, vp, lens.cuda(), table.cuda(), window=window, sinks=sinks, num_splits=splits)
+    ref = S.paged_attention_reference(q.cpu(), kp.cpu(), vp.cpu(), torch.arange(B + 1, dtype=torch.int32), lens, table,
+                                      window=window, sinks=None if sinks is None else sinks.cpu())
+    err = (o.float().cpu() - ref.float()).abs().max().item()
+    assert torch.allclose(o.float().cpu(), ref.float(), atol=2e-2, rtol=2e-2), err
