@@ -189,6 +189,14 @@ def bench_decode(args) -> None:
         print(f"decode GEMM {name:8s} M={M} N={N:5d} K={Kd:5d}: ours {ms * 1e3:6.1f} us ({wbytes / ms / 1e6:5.0f} GB/s of "
               f"weights, {wbytes / ms / 1e6 / pk['hbm_gbs']:.2f} of {pk['src']} copy bandwidth)   cuBLAS "
               f"{ms_lib * 1e3:6.1f} us", flush=True)
+        ref = torch.matmul(a.float(), w.float().t())
+        sweep = []
+        for sp in (1, 2, 3, 4, 5, 6, 8):
+            t = time_cuda(lambda: K.gemm(a, w, out=out, pair_splits=sp), flush=flush)
+            err = float((out.float() - ref).abs().max() / ref.abs().max())
+            sweep.append(f"{sp}:{t * 1e3:.1f}us" + ("" if err < 1e-2 else f"(ERR {err:.3f})"))
+        print(f"    CTA-pair split-K by slices  {'  '.join(sweep)}   planned slices "
+              f"{K._pair_splitk_plan(M, N, Kd, a.device)}", flush=True)
     from easydel_b200.ops import _lib
 
     _lib.check_status()

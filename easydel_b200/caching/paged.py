@@ -34,23 +34,75 @@ class PagedBatchMeta:
     request_distribution: tuple[int, int, int] | None = None  # (#decode, #decode+#prefill, #total)
     num_splits: int = 1          # decode-only steps: cut every sequence's keys into this many page ranges
     seq_slots: torch.Tensor | None = None   # int64 [B] engine slot of every sequence (recurrent-state pools)
+    # cache groups beyond the first (sliding-window / chunked-local layers with their own pools): per group the page
+    # table [B, maxP] and the slot mapping [T]; entry g - 1 belongs to group g
+    group_tables: list | None = None
+    group_slots: list | None = None
+
+    def table_of(self, group: int) -> torch.Tensor:
+        return self.page_table if group == 0 or not self.group_tables else self.group_tables[group - 1]
+
+    def slots_of(self, group: int) -> torch.Tensor:
+        return self.slot_mapping if group == 0 or not self.group_slots else self.group_slots[group - 1]
 
 
 class PagedKVCache:
+    """Key / value pages of every layer. Layers that retain keys under the same rule (full context, a sliding window,
+    a block of chunked-local attention) form a *group* with its own page count and page tables
+    (:mod:`easydel_b200.caching.specs`); one group of all layers is the plain case."""
+
     def __init__(self, num_layers: int, num_pages: int, num_kv_heads: int, head_dim: int, dtype=torch.bfloat16,
-                 device=None, page_size: int = PAGE_SIZE, latent: bool = False):
+                 device=None, page_size: int = PAGE_SIZE, latent: bool = False, groups=None):
         if page_size != PAGE_SIZE:
             raise ValueError(f"the paged attention kernels use pages of {PAGE_SIZE} tokens, got {page_size}")
-        self.num_layers, self.num_pages, self.page_size = num_layers, num_pages, page_size
+        from .specs import FullAttentionSpec, KVCacheGroup, MLAAttentionSpec
+
+        self.num_layers, self.page_size = num_layers, page_size
         self.num_kv_heads, self.head_dim, self.dtype = num_kv_heads, head_dim, dtype
-        shape = (num_layers, num_pages, page_size, num_kv_heads, head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
         # latent attention stores one row per token (compressed keys/values + the shared rotary key): no value pool
         self.latent = latent
-        self.v = self.k if latent else torch.zeros(shape, dtype=dtype, device=device)
+        if groups is None:
+            es = torch.empty(0, dtype=dtype).element_size()
+            spec_cls = MLAAttentionSpec if latent else FullAttentionSpec
+            groups = [KVCacheGroup(spec_cls(page_size=page_size, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                                            element_size=es), list(range(num_layers)), int(num_pages))]
+        self.groups = list(groups)
+        self.layer_slot: dict[int, tuple[int, int]] = {}
+        self._k, self._v = [], []
+        for g, grp in enumerate(self.groups):
+            shape = (len(grp.layers), int(grp.num_pages), page_size, grp.spec.num_kv_heads, grp.spec.head_dim)
+            k = torch.zeros(shape, dtype=dtype, device=device)      # zeros: the null page must hold finite numbers
+            self._k.append(k)
+            self._v.append(k if grp.kind == "latent" else torch.zeros(shape, dtype=dtype, device=device))
+            for j, layer in enumerate(grp.layers):
+                self.layer_slot[layer] = (g, j)
         # hybrids: layer -> recurrent state with one row per engine slot; ``step_meta`` is the running step's batch
         self.linear: dict[int, object] = {}
         self.step_meta: PagedBatchMeta | None = None
+
+    @property
+    def k(self) -> torch.Tensor:
+        return self._k[0]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self._v[0]
+
+    @property
+    def num_pages(self) -> int:
+        return int(self.groups[0].num_pages)
+
+    @property
+    def num_groups(self) -> int:
+        return len(self.groups)
+
+    def memory_bytes(self) -> int:
+        seen, n = set(), 0
+        for t in (*self._k, *self._v):
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                n += t.numel() * t.element_size()
+        return n
 
     def add_state_pools(self, model, num_slots: int) -> None:
         layers = getattr(getattr(model, "model", model), "layers", ())
@@ -75,31 +127,55 @@ class PagedKVCache:
     @classmethod
     def init_for_model(cls, model, num_pages: int | None = None, page_size: int = PAGE_SIZE,
                        hbm_utilization: float = 0.85, max_model_length: int | None = None, dtype=None, device=None,
-                       max_pages: int | None = None):
+                       max_pages: int | None = None, max_num_seqs: int | None = None,
+                       max_num_batched_tokens: int | None = None):
+        """Groups the model's layers by retention rule and sizes every group's pool. ``num_pages`` fixes the page
+        count of every group; otherwise free HBM x ``hbm_utilization`` is divided by
+        :func:`easydel_b200.caching.specs.plan_pages` (window-bounded groups get what ``max_num_seqs`` sequences can
+        hold, the rest goes to the full-attention layers)."""
+        from . import specs as SP
+
         spec = model.spec
         device = device or model.device
         dtype = dtype or getattr(model.config, "kvdtype", None) or model.dtype
-        tp_size = getattr(model.config.mesh, "tp", 1)
-        kvh = max(1, spec.num_kv_heads // tp_size)
+        es = torch.empty(0, dtype=dtype).element_size()
         latent = getattr(spec, "mla", None) is not None
-        head_dim = spec.head_dim
-        if latent:
-            kvh, head_dim = 1, spec.mla["kv_lora_rank"] + spec.mla["qk_rope_head_dim"]
-        if num_pages is None:
-            per_page = cls.bytes_per_page(spec.num_layers, kvh, head_dim, dtype, page_size) // (2 if latent else 1)
+        lm = getattr(model, "language_model", model)
+        groups = SP.build_groups(lm, element_size=es, page_size=page_size) \
+            if hasattr(lm, "get_operations_cache_info") else []
+        if not groups:      # a model of recurrent layers only still gets a (tiny) pool: the scheduler counts pages
+            tp_size = getattr(model.config.mesh, "tp", 1)
+            groups = [SP.KVCacheGroup(SP.FullAttentionSpec(page_size=page_size,
+                                                           num_kv_heads=max(1, spec.num_kv_heads // tp_size),
+                                                           head_dim=spec.head_dim, element_size=es), [], 2)]
+        if num_pages is not None:
+            counts = [int(num_pages)] * len(groups)
+        else:
             if torch.device(device).type == "cuda":
                 free, total = torch.cuda.mem_get_info(device)
                 budget = max(0, int(free - (1.0 - hbm_utilization) * total))
             else:
                 budget = 256 << 20
-            num_pages = max(2, budget // per_page)
-        if max_pages is not None:
-            # never more than max_num_seqs * pages-per-sequence would need
-            num_pages = min(int(num_pages), int(max_pages))
-        return cls(spec.num_layers, int(num_pages), kvh, head_dim, dtype, device, page_size, latent=latent)
+            seqs = max_num_seqs or 256
+            mlen = max_model_length or spec.max_position
+            counts = SP.plan_pages(groups, budget, seqs, mlen, max_num_batched_tokens or 2048)
+            if max_pages is not None:
+                # never more than max_num_seqs * pages-per-sequence would need
+                counts = [min(int(c), int(max_pages)) for c in counts]
+        for g, n in zip(groups, counts):
+            g.num_pages = max(2, int(n))
+        head = groups[0].spec
+        return cls(spec.num_layers, groups[0].num_pages, head.num_kv_heads, head.head_dim, dtype, device, page_size,
+                   latent=latent, groups=groups)
 
     def view(self, layer: int):
-        view = PagedLatentView(self.k[layer]) if self.latent else PagedLayerView(self.k[layer], self.v[layer])
+        slot = self.layer_slot.get(layer)
+        if slot is None:
+            view = PagedLayerView(None, None)        # a layer without keys / values (recurrent mixer only)
+        else:
+            g, j = slot
+            view = PagedLatentView(self._k[g][j]) if self.groups[g].kind == "latent" else \
+                PagedLayerView(self._k[g][j], self._v[g][j], group=g)
         pool = self.linear.get(layer)
         view.linear_state = None if pool is None else PagedLinearState(pool, self.step_meta)
         return view
@@ -130,8 +206,8 @@ class PagedLinearState:
 class PagedLayerView:
     linear_state = None
 
-    def __init__(self, k_pages: torch.Tensor, v_pages: torch.Tensor):
-        self.k_pages, self.v_pages = k_pages, v_pages
+    def __init__(self, k_pages: torch.Tensor, v_pages: torch.Tensor, group: int = 0):
+        self.k_pages, self.v_pages, self.group = k_pages, v_pages, group
 
     def attend(self, attn, q, k, v, positions=None, attn_meta: PagedBatchMeta | None = None):
         """Appends this step's keys/values to their pages, then runs paged attention.
@@ -140,21 +216,22 @@ class PagedLayerView:
         meta = attn_meta
         T = q.shape[1]
         q3, k3, v3 = q[0], k[0], v[0]
-        S.kv_append(k3, v3, self.k_pages, self.v_pages, meta.slot_mapping)
+        table = meta.table_of(self.group)
+        S.kv_append(k3, v3, self.k_pages, self.v_pages, meta.slots_of(self.group))
         if getattr(attn, "chunk_size", None) or (q3.is_cuda and q3.shape[-1] not in (64, 128)):
             # block-diagonal attention, or a head size outside the paged kernel's (64 / 128)
             return self._attend_gathered(attn, q3, meta)[None]
         if meta.max_q == 1 and q3.shape[0] == meta.num_seqs and S.decode_kernel_supports(q3, self.k_pages,
                                                                                            attn.softcap):
             # a pure decode step: the streaming kernel (one CTA per sequence, KV head and key split)
-            o = S.decode_attention(q3, self.k_pages, self.v_pages, meta.kv_lens, meta.page_table, scale=attn.scale,
+            o = S.decode_attention(q3, self.k_pages, self.v_pages, meta.kv_lens, table, scale=attn.scale,
                                    window=attn.sliding_window or 0, sinks=attn.sinks, num_splits=meta.num_splits)
             return o[None]
         if meta.num_splits > 1 and meta.max_q == 1 and not attn.sliding_window and q3.is_cuda:
-            o = S.paged_attention_splitkv(q3, self.k_pages, self.v_pages, meta.kv_lens, meta.page_table,
+            o = S.paged_attention_splitkv(q3, self.k_pages, self.v_pages, meta.kv_lens, table,
                                           meta.num_splits, scale=attn.scale, softcap=attn.softcap, sinks=attn.sinks)
             return o[None]
-        o = S.paged_attention(q3, self.k_pages, self.v_pages, meta.cu_q, meta.kv_lens, meta.page_table, meta.max_q,
+        o = S.paged_attention(q3, self.k_pages, self.v_pages, meta.cu_q, meta.kv_lens, table, meta.max_q,
                               scale=attn.scale, causal=True, window=attn.sliding_window or 0, softcap=attn.softcap,
                               sinks=attn.sinks)
         return o[None]
@@ -183,7 +260,7 @@ def _attend_gathered(self, attn, q3, meta: PagedBatchMeta):
     from ..ops import reference as R
 
     B = meta.num_seqs
-    table = meta.page_table[:B].long().clamp_min(0)
+    table = meta.table_of(getattr(self, "group", 0))[:B].long().clamp_min(0)
     kk = self.k_pages[table].reshape(B, -1, *self.k_pages.shape[2:])
     vv = self.v_pages[table].reshape(B, -1, *self.v_pages.shape[2:])
     qb, qpos, lens, cu = _pad_queries(q3, meta)

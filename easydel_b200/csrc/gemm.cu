@@ -404,6 +404,70 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
+// Split-K epilogue of one warp's 32 rows x 256 columns (see gemm2_bf16_kernel). Every slice adds its partial into
+// the strip's fp32 accumulator in `ws` with vector reductions that complete in L2 (they leave the SM on its store
+// path, which a weight-streaming kernel does not otherwise use, instead of coming back through its load path),
+// then counts itself; the warp that arrives last reads the sums, writes bf16 and puts the zeros back. Layout of a
+// strip, private to this function: float4 number (v * 32 + lane) holds columns [4v, 4v + 4) of the lane's row.
+// With two slices the result does not depend on arrival order (0 + a + b == 0 + b + a); with more it can differ
+// in the last bit of the fp32 sum from run to run.
+__device__ __forceinline__ void splitk_partial_epilogue(void* __restrict__ Cout, const __nv_bfloat16* __restrict__ bias,
+                                                        uint32_t tmem_acc, uint8_t* epi_stage, int q, int lane, int m0,
+                                                        int n0, int M, int N, long long ldc, bool has_bias, int sp,
+                                                        int splits, int region, float* ws, int* counters) {
+  const uint32_t t_row = tmem_acc + (uint32_t(q * 32) << 16);
+  float4* strip = reinterpret_cast<float4*>(ws + (long long)region * 8192);
+#pragma unroll 1
+  for (int c = 0; c < 8; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_row + c * 32, r);
+    tc_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(strip + (c * 8 + j) * 32 + lane),
+                   "f"(__uint_as_float(r[4 * j])), "f"(__uint_as_float(r[4 * j + 1])),
+                   "f"(__uint_as_float(r[4 * j + 2])), "f"(__uint_as_float(r[4 * j + 3]))
+                   : "memory");
+  }
+  __threadfence();
+  __syncwarp();
+  int old = 0;
+  if (lane == 0) old = atomicAdd(counters + region, 1);
+  old = __shfl_sync(0xffffffffu, old, 0);
+  if (old != splits - 1) return;
+  __threadfence();
+  if (lane == 0) counters[region] = 0;  // every slice has arrived: nobody touches this counter again in this launch
+  const int valid_rows = M - (m0 + q * 32);
+  uint8_t* my_stage = epi_stage + q * 4096;
+  __nv_bfloat16* gbase = reinterpret_cast<__nv_bfloat16*>(Cout) + (long long)(m0 + q * 32) * ldc;
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    const int col0 = n0 + c * 64;
+    float4* p = strip + (c * 16) * 32 + lane;
+    float4 x[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) x[j] = __ldcg(p + j * 32);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) __stcg(p + j * 32, make_float4(0.f, 0.f, 0.f, 0.f));
+    if (col0 >= N || valid_rows <= 0) continue;
+    uint4 pk[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v[8] = {x[2 * j].x, x[2 * j].y, x[2 * j].z, x[2 * j].w, x[2 * j + 1].x, x[2 * j + 1].y, x[2 * j + 1].z,
+                    x[2 * j + 1].w};
+      if (has_bias) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (col0 + j * 8 + e < N) v[e] += __bfloat162float(bias[col0 + j * 8 + e]);
+      }
+      pk[j] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                         pack_bf16x2(v[6], v[7]));
+    }
+    store_rows_coalesced<false>(my_stage, pk, reinterpret_cast<uint8_t*>(gbase + col0), ldc * 2, valid_rows,
+                                min(8, (N - col0) >> 3), lane);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // CTA-pair form: a cluster of two CTAs computes one 256 x 256 tile with tcgen05.mma.cta_group::2. Each CTA loads
 // its own 128 rows of A and its own 128-column half of B (plain, non-multicast TMA loads whose completion bytes are
@@ -423,11 +487,16 @@ struct Cfg2 {
   static constexpr int TMEM_COLS = 512;
 };
 
-template <bool A_MN, bool B_MN>
+//
+// SPLITK (skinny products: a decode step's few hundred rows against a large weight matrix): a unit of work is one
+// (tile, slice of the reduction dimension); every epilogue warp adds its 32 x 256 fp32 partial into the strip's
+// accumulator in `ws`, counts itself on `counters[region]`, and the warp that arrives last adds the bias and
+// writes bf16. `ws` and `counters` must be zero on entry and are zero again on exit.
+template <bool A_MN, bool B_MN, bool SPLITK>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                   void* __restrict__ Cout, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc,
-                  int flags, int* status) {
+                  int flags, int* status, int splits, float* __restrict__ ws, int* __restrict__ counters) {
   using C = Cfg2;
   constexpr int BN = C::BN;
   extern __shared__ uint8_t smem_raw[];
@@ -477,6 +546,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
   const uint32_t smem_base = smem_u32(smem);
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
+  const int num_items = SPLITK ? num_tiles * splits : num_tiles;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -484,12 +554,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      for (int item = pair; item < num_items && ok; item += num_pairs) {
+        const int tile = SPLITK ? item / splits : item;
+        const int sp = SPLITK ? item - tile * splits : 0;
+        const int kb0 = SPLITK ? (sp * num_kb) / splits : 0;
+        const int kb1 = SPLITK ? ((sp + 1) * num_kb) / splits : num_kb;
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * 256 + (int)rank * 128;  // this CTA's rows of A and of the output
         const int nb0 = tn * BN + (int)rank * 128;  // this CTA's half of the B tile
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           const int kc = kb * BK;
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, status, EDL_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -526,11 +600,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      for (int item = pair; item < num_items && ok; item += num_pairs) {
+        const int sp = SPLITK ? item % splits : 0;
+        const int kb0 = SPLITK ? (sp * num_kb) / splits : 0;
+        const int kb1 = SPLITK ? ((sp + 1) * num_kb) / splits : num_kb;
         if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1, abort_flag, status, EDL_TIMEOUT_MMA)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full0 + 8 * stage, phase, abort_flag, status, EDL_TIMEOUT_MMA)) {
             ok = false;
             break;
@@ -544,7 +621,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                                         : umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
                                         : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
-            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           tc_commit_pair(empty0 + 8 * stage, 3);  // the stage is free in both CTAs
           if (++stage == C::STAGES) {
@@ -565,13 +642,20 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     const bool accum = flags & GEMM_ACCUMULATE;
     const bool has_bias = (flags & GEMM_BIAS) && bias != nullptr;
     const uint32_t lead_tempty0 = mapa_shared(tempty0, 0);
-    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+    for (int item = pair; item < num_items; item += num_pairs) {
+      const int tile = SPLITK ? item / splits : item;
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
       const int m0 = tm * 256 + (int)rank * 128, n0 = tn * BN;
       if (!mbar_wait(tfull0 + 8 * acc, acc_phase, abort_flag, status, EDL_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
-      epilogue_tile<BN>(Cout, bias, tmem_base, acc, epi_stage, q, lane, m0, n0, 0, M, N, ldc, out_f32, accum, has_bias);
+      if (SPLITK && splits > 1) {
+        splitk_partial_epilogue(Cout, bias, tmem_base + acc * BN, epi_stage, q, lane, m0, n0, M, N, ldc, has_bias,
+                                item - tile * splits, splits, (tile * 2 + (int)rank) * 4 + q, ws, counters);
+      } else {
+        epilogue_tile<BN>(Cout, bias, tmem_base, acc, epi_stage, q, lane, m0, n0, 0, M, N, ldc, out_f32, accum,
+                          has_bias);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(lead_tempty0 + 8 * acc);
@@ -632,9 +716,10 @@ int launch(const void* A, const void* B, void* Cout, const void* bias, int M, in
 }
 
 // Number of CTA pairs that can be resident at once (queried once per device and kernel).
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool SPLITK = false>
 int launch_pair(const void* A, const void* B, void* Cout, const void* bias, int M, int N, int K, long long lda,
-                long long ldb, long long ldc, int flags, int* status, cudaStream_t stream, int max_ctas) {
+                long long ldb, long long ldc, int flags, int* status, cudaStream_t stream, int max_ctas,
+                int splits = 1, float* ws = nullptr, int* counters = nullptr) {
   using C = Cfg2;
   CUtensorMap ta, tb;
   int rc;
@@ -648,7 +733,7 @@ int launch_pair(const void* A, const void* B, void* Cout, const void* bias, int 
   else
     rc = make_tmap_2d_16b(&tb, B, K, N, ldb, BK, 64);
   if (rc) return rc;
-  auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN, SPLITK>;
   static int pairs_on_device[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -675,12 +760,12 @@ int launch_pair(const void* A, const void* B, void* Cout, const void* bias, int 
     }
     pairs_on_device[dev] = n;
   }
-  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256) * (SPLITK ? splits : 1);
   int pairs = pairs_on_device[dev];
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (tiles < pairs) pairs = tiles;
   kern<<<2 * pairs, GEMM_THREADS, C::SMEM_BYTES, stream>>>(ta, tb, Cout, reinterpret_cast<const __nv_bfloat16*>(bias),
-                                                            M, N, K, ldc, flags, status);
+                                                            M, N, K, ldc, flags, status, splits, ws, counters);
   return check_cuda(cudaGetLastError(), "gemm pair launch");
 }
 
@@ -843,4 +928,31 @@ EDL_HOST_API int edl_gemm_splitk(const void* A, const void* B, void* C, const vo
                                               reinterpret_cast<__nv_bfloat16*>(C),
                                               reinterpret_cast<const __nv_bfloat16*>(bias), M, N, ldc, splits);
   return check_cuda(cudaGetLastError(), "splitk_reduce launch");
+}
+
+// Split-K on the CTA-pair kernel: C[M,N] = A[M,K] * B[N,K]^T (+ bias), bf16 in and out, for products whose 256 x 256
+// output tiles are too few to occupy every SM. (tile, K-slice) units are spread over all CTA pairs; the partial sums
+// meet in `workspace` (fp32, edl_gemm_pair_splitk_workspace() bytes, ZERO on entry and left zero) and the last warp
+// to arrive on a 32-row strip writes the result. `counters`: int32, one per strip (8 per tile), zero on entry, left
+// zero. With splits <= 2 results are bit-reproducible; with more slices the fp32 sum depends on arrival order.
+EDL_HOST_API long long edl_gemm_pair_splitk_workspace(int M, int N) {
+  const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
+  return tiles * 8 * 8192 * 4;
+}
+
+EDL_HOST_API int edl_gemm_pair_splitk(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                                      long long lda, long long ldb, long long ldc, int splits, void* workspace,
+                                      int* counters, int* status, void* stream) {
+  using namespace edl;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int num_kb = (K + BK - 1) / BK;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7) || splits < 1 || splits > num_kb ||
+      (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 15)) {
+    set_last_error("edl_gemm_pair_splitk: lda, ldb, ldc, N must be multiples of 8, 1 <= splits <= K/64, "
+                   "C and workspace 16-byte aligned");
+    return -1;
+  }
+  return launch_pair<false, false, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, bias ? GEMM_BIAS : 0, status,
+                                         reinterpret_cast<cudaStream_t>(stream), 0, splits,
+                                         reinterpret_cast<float*>(workspace), counters);
 }

@@ -22,6 +22,7 @@ import torch
 from ...caching.paged import PAGE_SIZE, PagedKVCache
 from ..sampling_params import SamplingParams
 from .metrics import MetricsCollector
+from .kv_manager import KVCacheCoordinator
 from .page_pool import PagePool
 from .runner import ModelRunner
 from .scheduler import EngineRequest, RequestStatus, Scheduler, SchedulerConfig
@@ -147,18 +148,22 @@ class eSurge:
         # the page count is settled before anything is allocated: two caches never exist at once
         self.cache = PagedKVCache.init_for_model(model, num_pages=num_pages, page_size=page_size,
                                                  hbm_utilization=hbm_utilization, max_model_length=max_model_len,
-                                                 max_pages=pages_cap if num_pages is None else None)
+                                                 max_pages=pages_cap if num_pages is None else None,
+                                                 max_num_seqs=max_num_seqs,
+                                                 max_num_batched_tokens=self.max_num_batched_tokens)
         # hybrids: one recurrent-state row per engine slot (the last row belongs to the padding rows of a batch
         # bucket). A cached prefix has no recurrent state to resume from, so prefix caching is off for them.
         self.cache.add_state_pools(getattr(model, "language_model", model), max_num_seqs + 1)
         if self.cache.linear:
             enable_prefix_caching = False
-        self.pool = PagePool(self.cache.num_pages, enable_caching=enable_prefix_caching)
+        # one page pool per cache group (full attention / each sliding window / each chunked-local block size)
+        self.kv = KVCacheCoordinator(self.cache.groups, enable_caching=enable_prefix_caching)
+        self.pool = self.kv.pool
         self.scheduler = Scheduler(SchedulerConfig(max_num_seqs=max_num_seqs,
                                                    max_num_batched_tokens=self.max_num_batched_tokens,
                                                    max_model_len=max_model_len,
                                                    long_prefill_token_threshold=long_prefill_token_threshold,
-                                                   policy=scheduling_policy), self.pool, page_size)
+                                                   policy=scheduling_policy), self.kv, page_size)
         self.runner = ModelRunner(model, self.cache, max_num_seqs, self.max_num_batched_tokens, max_model_len)
         self.metrics = MetricsCollector()
         self._tracked: dict[str, _Tracked] = {}
@@ -279,7 +284,8 @@ class eSurge:
                 self.model.load_state_dict(state_dict, strict=False)
             elif model is not None and model is not self.model:
                 self.model.load_state_dict(model.state_dict(), strict=False)
-            self.pool.reset_cache()
+            for m in self.kv.managers:
+                m.pool.reset_cache()
 
     # ------------------------------------------------------------------ requests
     def _tokenize(self, prompt) -> tuple[list[int], str | None]:

@@ -40,6 +40,10 @@ class ModelRunner:
         # one packed int32 staging buffer: ids | pos | slots | cu_q | kv_lens | last_idx | page_table |
         # slot of every sequence | (token row, slot) of the rows whose input token is still on the device
         self._sizes = [T, T, T, B + 1, B, B, B * MP, B, B, B]
+        # cache groups beyond the first (window-bounded layers with their own pools): slot mapping + page table each
+        self.num_groups = getattr(cache, "num_groups", 1)
+        for _ in range(self.num_groups - 1):
+            self._sizes += [T, B * MP]
         total = sum(self._sizes)
         self._host = torch.zeros(total, dtype=torch.int32, pin_memory=pin)
         self._dev = torch.zeros(total, dtype=torch.int32, device=dev)
@@ -53,6 +57,7 @@ class ModelRunner:
         # host mirror of every slot's page list, so that decode steps are filled without per-request slicing
         self._slot_pages = np.zeros((B, MP), dtype=np.int32)
         self._slot_npages = np.zeros(B, dtype=np.int32)
+        self._slot_epoch = np.full(B, -1, dtype=np.int64)
         try:
             from ...data import _native
 
@@ -136,6 +141,10 @@ class ModelRunner:
                               request_distribution=(num_decode, B, B),
                               num_splits=self._decode_splits(B) if (max_q == 1 and T == B) else 1,
                               seq_slots=self._seq_slots[:B] if self.cache.linear else None)
+        if self.num_groups > 1:
+            extra = self._dviews[10:]
+            meta.group_slots = [extra[2 * g][:T] for g in range(self.num_groups - 1)]
+            meta.group_tables = [extra[2 * g + 1].view(self.max_num_seqs, MP)[:B] for g in range(self.num_groups - 1)]
         self.cache.step_meta = meta
         model = self._lm
         if mm_rows:
@@ -149,6 +158,25 @@ class ModelRunner:
                         cache_metadata=meta, apply_lm_head=False)
         rows = S.gather_rows(res.last_hidden_state[0], d_last[:B])
         return model.apply_lm_head(rows)
+
+    def _fill_extra_groups(self, sched, B: int) -> None:
+        """Slot mapping and page table of the cache groups beyond the first, from every request's per-group page
+        list (same indexing by position as group 0; pages a window no longer reaches are the null page)."""
+        MP = self.max_pages_per_seq
+        for g in range(self.num_groups - 1):
+            slots_np = self._hviews[10 + 2 * g].numpy()
+            table_np = self._hviews[11 + 2 * g].numpy().reshape(self.max_num_seqs, MP)
+            o = 0
+            for b, s in enumerate(sched):
+                pg = np.asarray(s.request.group_pages[g], dtype=np.int32)
+                n, st = s.num_new_tokens, s.start
+                if n == 1:
+                    slots_np[o] = pg[st >> 7] * PAGE_SIZE + (st & (PAGE_SIZE - 1))
+                else:
+                    p = np.arange(st, st + n, dtype=np.int32)
+                    slots_np[o:o + n] = pg[p // PAGE_SIZE] * PAGE_SIZE + p % PAGE_SIZE
+                table_np[b, :len(pg)] = pg
+                o += n
 
     def _decode_step_graphed(self, Bp: int) -> torch.Tensor:
         """Greedy decode step for ``Bp`` rows: eager the first time (warm-up), captured the second, replayed after."""
@@ -203,7 +231,7 @@ class ModelRunner:
             return None
         if B > self.max_num_seqs or T > self.max_tokens:
             raise RuntimeError(f"batch of {B} sequences / {T} tokens exceeds the runner's buffers")
-        ids, pos, slots, cu_q, kv_lens, last_idx, table, slot_of, fix_pos, fix_slot = self._hviews
+        ids, pos, slots, cu_q, kv_lens, last_idx, table, slot_of, fix_pos, fix_slot = self._hviews[:10]
         slotof_np, fixpos_np, fixslot_np = slot_of.numpy(), fix_pos.numpy(), fix_slot.numpy()
         nfix = 0
         MP = self.max_pages_per_seq
@@ -224,9 +252,10 @@ class ModelRunner:
             for s in sched:   # pages only grow by one every 128 tokens: this loop rarely copies anything
                 req = s.request
                 n_pg = len(req.pages)
-                if sp_n[req.slot] != n_pg:
+                if sp_n[req.slot] != n_pg or self._slot_epoch[req.slot] != req.pages_epoch:
                     sp_pages[req.slot, :n_pg] = req.pages
                     sp_n[req.slot] = n_pg
+                    self._slot_epoch[req.slot] = req.pages_epoch
                 sp = req.sampling_params
                 any_pen |= sp.needs_penalties
                 any_random |= not sp.is_greedy
@@ -281,6 +310,7 @@ class ModelRunner:
             if req.slot >= 0:
                 self._slot_pages[req.slot, :len(pg)] = pg
                 self._slot_npages[req.slot] = len(pg)
+                self._slot_epoch[req.slot] = req.pages_epoch
             kv_np[b] = st + n
             o += n
             cu_np[b + 1] = o
@@ -289,6 +319,8 @@ class ModelRunner:
             sp = req.sampling_params
             any_pen |= sp.needs_penalties
             any_random |= not sp.is_greedy
+        if self.num_groups > 1:
+            self._fill_extra_groups(sched, B)
         decode_only = max_q == 1 and not any_pen and not any_random
         Bp = B
         if self.use_graphs and decode_only:
@@ -305,6 +337,9 @@ class ModelRunner:
                 cu_np[B + 1:Bp + 1] = np.arange(B + 1, Bp + 1, dtype=np.int32)
                 last_np[B:Bp] = np.arange(B, Bp, dtype=np.int32)
                 slotof_np[B:Bp] = self.max_num_seqs
+                for g in range(self.num_groups - 1):
+                    self._hviews[10 + 2 * g].numpy()[B:Bp] = 0
+                    self._hviews[11 + 2 * g].numpy().reshape(self.max_num_seqs, MP)[B:Bp, :] = 0
         if self.cache.linear:
             # recurrent-state rows of the scheduled sequences; padding rows of a batch bucket share the spare row
             sl = [s.request.slot for s in sched] + [self.max_num_seqs] * (Bp - B)

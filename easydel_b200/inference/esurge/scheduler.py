@@ -20,6 +20,7 @@ import typing as tp
 from dataclasses import dataclass, field
 
 from ..sampling_params import SamplingParams
+from .kv_manager import KVCacheCoordinator
 from .page_pool import PagePool, hash_request_pages
 
 
@@ -52,9 +53,11 @@ class EngineRequest:
     output_token_ids: list[int] = field(default_factory=list)
     num_computed_tokens: int = 0          # tokens whose KV is in the cache
     num_cached_tokens: int = 0            # prefix-cache hit length at (last) admission
-    pages: list[int] = field(default_factory=list)
+    pages: list[int] = field(default_factory=list)              # page list of cache group 0
+    group_pages: list[list[int]] = field(default_factory=list)  # page lists of the other cache groups, same indexing
     page_hashes: list[bytes] = field(default_factory=list)
     num_registered_pages: int = 0
+    pages_epoch: int = 0                  # bumped whenever entries of a page list change in place (window release)
     slot: int = -1                        # row in the runner's persistent per-sequence buffers
     order: int = field(default_factory=lambda: next(_arrival))
     first_token_time: float | None = None
@@ -121,8 +124,10 @@ class SchedulerConfig:
 
 
 class Scheduler:
-    def __init__(self, config: SchedulerConfig, pool: PagePool, page_size: int = 128):
-        self.config, self.pool, self.page_size = config, pool, page_size
+    def __init__(self, config: SchedulerConfig, pool: "PagePool | KVCacheCoordinator", page_size: int = 128):
+        # one pool = one full-attention group; a coordinator carries one pool per cache group
+        self.kv = pool if isinstance(pool, KVCacheCoordinator) else KVCacheCoordinator.single(pool, page_size)
+        self.config, self.pool, self.page_size = config, self.kv.pool, page_size
         self.waiting: collections.deque[EngineRequest] = collections.deque()
         self.running: list[EngineRequest] = []
         self.requests: dict[str, EngineRequest] = {}
@@ -160,22 +165,16 @@ class Scheduler:
         return len(self.waiting)
 
     # ------------------------------------------------------------------ pages
-    def _pages_needed(self, req: EngineRequest, upto_tokens: int) -> int:
-        need = (upto_tokens + self.page_size - 1) // self.page_size
-        return max(0, need - len(req.pages))
-
     def _try_allocate(self, req: EngineRequest, upto_tokens: int) -> bool:
-        n = self._pages_needed(req, upto_tokens)
-        if n == 0:
-            return True
-        if n > self.pool.num_free:
-            return False
-        req.pages.extend(self.pool.allocate(n))
-        return True
+        """Pages for ``upto_tokens`` tokens in every cache group, or nothing. Window-bounded groups first give back
+        the pages no later query of this request can reach (every launched step is ahead of the next one on the
+        stream, so a page freed here is not read again before its new owner writes it)."""
+        if self.kv.remove_skipped(req):
+            req.pages_epoch += 1
+        return self.kv.try_allocate(req, upto_tokens)
 
     def _release(self, req: EngineRequest) -> None:
-        self.pool.release(req.pages)
-        req.pages = []
+        self.kv.release(req)
         req.num_registered_pages = 0
 
     def _preempt(self, req: EngineRequest) -> None:
@@ -192,12 +191,9 @@ class Scheduler:
         req.page_hashes = hash_request_pages(tokens, self.page_size, req.mm_hash)
         # never serve the whole request from cache: the last token must be recomputed to produce logits
         usable = req.page_hashes[: max(0, (len(tokens) - 1) // self.page_size)]
-        hit = self.pool.lookup(usable)
-        if hit:
-            self.pool.touch(hit)
-            req.pages = list(hit)
-            req.num_registered_pages = len(hit)
-        req.num_cached_tokens = len(hit) * self.page_size
+        n_hit = self.kv.admit_with_prefix(req, usable)
+        req.num_registered_pages = n_hit
+        req.num_cached_tokens = n_hit * self.page_size
         req.num_computed_tokens = req.num_cached_tokens
 
     def _register_full_pages(self, req: EngineRequest) -> None:
@@ -214,7 +210,7 @@ class Scheduler:
         if len(req.page_hashes) < full:
             req.page_hashes = hash_request_pages(tokens[: full * self.page_size], self.page_size, req.mm_hash)
         for i in range(req.num_registered_pages, full):
-            self.pool.register(req.pages[i], req.page_hashes[i])
+            self.kv.register(req, i, req.page_hashes[i])
         req.num_registered_pages = full
 
     # ------------------------------------------------------------------ the step

@@ -34,6 +34,8 @@ _SIGS = {
     "edl_abi_version": (i32, []),
     "edl_gemm_bf16": (i32, [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i32, i32, vp, vp, i32, i32]),
     "edl_gemm_splitk": (i32, [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, vp, vp, vp, vp]),
+    "edl_gemm_pair_splitk": (i32, [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, vp, vp, vp, vp]),
+    "edl_gemm_pair_splitk_workspace": (i64, [i32, i32]),
     "edl_rmsnorm_fwd": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32, f32, vp]),
     "edl_rmsnorm_bwd_workspace": (i64, [i32, i32]),
     "edl_rmsnorm_bwd": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, i32, vp]),

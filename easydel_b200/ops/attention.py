@@ -55,8 +55,9 @@ def attn_fwd(q, k, v, *, causal=True, scale=None, window=0, softcap=0.0, sinks=N
 
 
 def attn_bwd(q, k, v, o, lse, do, *, causal=True, scale=None, window=0, softcap=0.0, cu_q=None, cu_k=None,
-             max_q=None, max_k=None, dq=None, dk=None, dv=None):
-    """Gradients of :func:`attn_fwd`. Returns (dq, dk, dv) in the layouts of q, k, v."""
+             max_q=None, max_k=None, dq=None, dk=None, dv=None, want_delta=False):
+    """Gradients of :func:`attn_fwd`. Returns (dq, dk, dv) in the layouts of q, k, v (and ``delta = rowsum(o * do)``,
+    ``[Hq, total_q]`` fp32, when ``want_delta``)."""
     varlen = cu_q is not None
     if varlen:
         total_q, Hq, D = q.shape
@@ -83,6 +84,8 @@ def attn_bwd(q, k, v, o, lse, do, *, causal=True, scale=None, window=0, softcap=
               v.stride(-3), o.stride(-3), do.stride(-3), dq.stride(-3), dk.stride(-3), dv.stride(-3), _lib.ptr(cu_q),
               _lib.ptr(cu_k), B, Tq, Tk, total_q, total_k, Hq, Hkv, D, float(scale), int(causal), int(window or 0),
               float(softcap or 0.0), _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
+    if want_delta:
+        return dq, dk, dv, delta
     return dq, dk, dv
 
 
@@ -98,20 +101,23 @@ class _FlashAttnFn(torch.autograd.Function):
             o, lse = attn_fwd(q, k, v, causal=causal, scale=scale, window=window, softcap=softcap, sinks=sinks,
                               cu_q=cu, cu_k=cu, max_q=max_len, max_k=max_len)
             remat.keep_output("attn_core", "attn", (o, lse))
-        ctx.save_for_backward(q, k, v, o, lse, cu)
+        ctx.save_for_backward(q, k, v, o, lse, cu, sinks)
         ctx.args = (causal, scale, window, softcap, max_len)
-        ctx.has_sinks = sinks is not None
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, o, lse, cu = ctx.saved_tensors
+        q, k, v, o, lse, cu, sinks = ctx.saved_tensors
         causal, scale, window, softcap, max_len = ctx.args
-        if ctx.has_sinks:
-            raise NotImplementedError("attention sinks are forward-only (serving) in the GPU kernels")
-        dq, dk, dv = attn_bwd(q, k, v, o, lse, do, causal=causal, scale=scale, window=window, softcap=softcap,
-                              cu_q=cu, cu_k=cu, max_q=max_len, max_k=max_len)
-        return dq, dk, dv, None, None, None, None, None, None, None
+        # With sinks the forward's log-sum-exp already counts the sink logit, so P = exp(S - lse) recomputed by the
+        # backward kernels is the true probability and dq / dk / dv need nothing else. The sink itself has a zero
+        # value row, hence dP_sink = 0 and d sink[h] = sum_rows P_sink * (0 - delta) = -sum exp(sink - lse) * delta.
+        dq, dk, dv, delta = attn_bwd(q, k, v, o, lse, do, causal=causal, scale=scale, window=window, softcap=softcap,
+                                     cu_q=cu, cu_k=cu, max_q=max_len, max_k=max_len, want_delta=True)
+        dsinks = None
+        if sinks is not None and ctx.needs_input_grad[7]:
+            dsinks = -(torch.exp(sinks.float()[:, None] - lse) * delta).sum(1).to(sinks.dtype)
+        return dq, dk, dv, None, None, None, None, dsinks, None, None
 
 
 def segment_ids_to_cu_seqlens(segment_ids: torch.Tensor):

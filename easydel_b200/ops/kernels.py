@@ -54,6 +54,43 @@ def _splitk_plan(M: int, N: int, K: int, device) -> int:
     return best
 
 
+def _pair_splitk_plan(M: int, N: int, K: int, device) -> int:
+    """K slices for the CTA-pair split-K kernel (0 = use the other kernels).
+
+    Measured on the decode shapes of a 70B model under 8-way tensor parallelism (256 rows; hidden 8192, FFN 3584 per
+    GPU), the pair kernel does not beat the 128-wide kernel: with one slice too few CTAs stream (the weight bytes in
+    flight per CTA are bounded by its six 32 KB stages), and every extra slice pays ~8 us for the fp32 partial sums
+    that meet in L2. So nothing is planned by default; ``gemm(..., pair_splits=n)`` runs it explicitly and
+    ``EDL_GEMM_PAIR_SPLITK=1`` enables the two-slice plan for products with fewer than half as many 256 x 256 tiles
+    as CTA pairs.
+    """
+    if not _PAIR_SPLITK_ENV[0] or M <= 128 or M > 512 or N % 8 or K % 64 or N < 512:
+        return 0
+    idx = device.index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(device).multi_processor_count
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    return 2 if 4 * tiles <= _SM_COUNT[idx] and K >= 2048 else 0
+
+
+_PAIR_SPLITK_ENV = [__import__("os").environ.get("EDL_GEMM_PAIR_SPLITK", "0") not in ("", "0")]
+
+
+_PAIR_WS: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _pair_workspace(strips: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """Zeroed fp32 strip accumulators and strip counters (the kernel leaves both zero), one set per (device,
+    stream), grown on demand."""
+    key = (device.index or 0, torch.cuda.current_stream(device).cuda_stream)
+    cur = _PAIR_WS.get(key)
+    if cur is None or cur[1].numel() < strips:
+        n = max(strips, 512)
+        cur = _PAIR_WS[key] = (torch.zeros(n * 8192, dtype=torch.float32, device=device),
+                               torch.zeros(n, dtype=torch.int32, device=device))
+    return cur
+
+
 def _splitk_offsets(K: int, splits: int, device) -> torch.Tensor:
     key = (K, splits, device.index or 0)
     t = _SPLITK_OFFSETS.get(key)
@@ -66,7 +103,7 @@ def _splitk_offsets(K: int, splits: int, device) -> torch.Tensor:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
          out_dtype: torch.dtype | None = None, accumulate: bool = False, bias: torch.Tensor | None = None,
-         max_ctas: int = 0, force_bn: int = 0) -> torch.Tensor:
+         max_ctas: int = 0, force_bn: int = 0, pair_splits: int = 0) -> torch.Tensor:
     """C[M,N] (+)= op(A) op(B) on tcgen05 tensor cores.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``); ``b`` is ``[N,K]`` (or ``[K,N]`` when ``b_mn``).
@@ -96,6 +133,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     lda = a.stride(0) if a.shape[0] > 1 else a.shape[1]
     ldb = b.stride(0) if b.shape[0] > 1 else b.shape[1]
     ldc = out.stride(0) if out.shape[0] > 1 else out.shape[1]
+    if not (a_mn or b_mn or accumulate or max_ctas) and out.dtype == torch.bfloat16 and force_bn in (0, 512):
+        ps = pair_splits or (_pair_splitk_plan(M, N, K, a.device) if not force_bn else 0)
+        if ps > 1 or (ps == 1 and pair_splits):
+            # one 32-row strip per epilogue warp
+            ws, counters = _pair_workspace(8 * ((M + 255) // 256) * ((N + 255) // 256), a.device)
+            _lib.call("edl_gemm_pair_splitk", a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K, lda,
+                      ldb, ldc, ps, ws.data_ptr(), counters.data_ptr(), _lib.status_word(a.device).data_ptr(),
+                      _lib.stream_ptr())
+            return out
     if not (a_mn or b_mn or accumulate or max_ctas or force_bn) and out.dtype == torch.bfloat16:
         splits = _splitk_plan(M, N, K, a.device)
         if splits > 1:

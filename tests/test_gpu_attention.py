@@ -133,6 +133,25 @@ def test_flash_attention_autograd():
     _check_grad("dv", v.grad, rv)
 
 
+def test_attention_sinks_backward():
+    """Sliding window + sinks (the gpt-oss layer form): gradients of q, k, v and of the sink logits against autograd
+    through the dense fp32 attention."""
+    from easydel_b200.ops import attention as A, reference as R
+
+    q, k, v = _qkv(2, 320, 4, 2, 64, seed=21, packed=False)
+    sinks = torch.randn(4, device="cuda")
+    w = torch.randn(2, 320, 4, 64, device="cuda")
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, sinks)]
+    o = A.flash_attention(*leaves[:3], causal=True, sliding_window=96, sinks=leaves[3])
+    (o.float() * w).sum().backward()
+    ref_leaves = [t.float().clone().requires_grad_(True) for t in (q, k, v, sinks)]
+    ro = R.attention(*ref_leaves[:3], causal=True, sliding_window=96, sinks=ref_leaves[3])
+    (ro.float() * w).sum().backward()
+    for name, a, b in zip(("dq", "dk", "dv"), leaves[:3], ref_leaves[:3]):
+        _check_grad(name, a.grad, b.grad)
+    assert torch.allclose(leaves[3].grad, ref_leaves[3].grad, rtol=3e-2, atol=3e-2 * float(ref_leaves[3].grad.abs().max()))
+
+
 def test_attn_benchmarked_shape_against_oracle():
     """The shape the training benchmark runs (8192 tokens, 32 query / 8 KV heads, D = 128, causal), forward and
     backward, against dense fp32 attention. The reference is formed one GQA group at a time (1 GB of scores)."""

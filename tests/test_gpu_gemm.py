@@ -145,3 +145,27 @@ def test_gemm_skinny_uses_split_k(M, N, K):
         ref = a.float() @ w.float().t() + (b.float() if b is not None else 0)
         err = (out.float() - ref).abs().max() / ref.abs().max()
         assert err < 1e-2, err
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K,splits", [(256, 1280, 8192, 4), (200, 7168, 4096, 2), (64, 520, 1024, 3),
+                                          (256, 8192, 1024, 1), (384, 768, 2048, 5)])
+def test_pair_splitk_matches_fp32(M, N, K, splits):
+    """Split-K on the CTA-pair kernel (decode-sized products), with bias, against an fp32 product; with at most two
+    slices repeated calls give bit-identical results; the accumulators and strip counters are left at zero."""
+    from easydel_b200.ops import kernels as K_
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    ref = a.float() @ w.float().t() + bias.float()
+    out = K_.gemm(a, w, bias=bias, pair_splits=splits)
+    assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+    again = K_.gemm(a, w, bias=bias, pair_splits=splits)
+    if splits <= 2:
+        assert torch.equal(out, again)
+    else:
+        assert (out.float() - again.float()).abs().max() <= 1e-2 * ref.abs().max()
+    for ws, counters in K_._PAIR_WS.values():
+        assert int(counters.abs().sum()) == 0 and float(ws.abs().max()) == 0.0
