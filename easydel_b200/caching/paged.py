@@ -307,6 +307,11 @@ class PagedLatentView:
         w_uk, w_uv = w[:, : mla.nope], w[:, mla.nope:]
         q = torch.cat([torch.einsum("thn,hnl->thl", q_nope[0], w_uk.to(q_nope.dtype)), q_rope[0]], -1)   # [T,H,L+R]
         B = meta.num_seqs
+        if meta.max_q == 1 and T == B and mla.rope_dim == 64 and L == 512 and S.mla_decode_kernel_supports(q, self.pages):
+            # a pure decode step of the 512 + 64 layout: the streaming kernel walks the page table itself
+            o_lat = S.mla_decode_attention(q.contiguous(), self.pages, meta.kv_lens, meta.page_table, scale=mla.scale,
+                                           num_splits=meta.num_splits)
+            return torch.einsum("bhl,hvl->bhv", o_lat, w_uv.to(o_lat.dtype))[None]
         table = meta.page_table[:B].long().clamp_min(0)
         kv = self.pages[table].reshape(B, -1, self.pages.shape[-1])                                       # [B,Tk,L+R]
         Tk = kv.shape[1]

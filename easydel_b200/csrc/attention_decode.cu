@@ -20,9 +20,15 @@
 namespace edl {
 namespace {
 
-constexpr int DEC_WARPS = 4;
+#ifndef EDL_DEC_WARPS
+#define EDL_DEC_WARPS 4
+#endif
+#ifndef EDL_DEC_TK
+#define EDL_DEC_TK 32
+#endif
+constexpr int DEC_WARPS = EDL_DEC_WARPS;
 constexpr int DEC_THREADS = DEC_WARPS * 32;
-constexpr int TK = 32;        // keys per tile
+constexpr int TK = EDL_DEC_TK;        // keys per tile (16 or 32)
 constexpr int DEC_STAGES = 3;
 constexpr int PAGE = 128;
 constexpr float LOG2E_F = 1.4426950408889634f;

@@ -354,3 +354,180 @@ EDL_HOST_API int edl_allreduce_add_rmsnorm(const unsigned long long* data_ptrs, 
       (__nv_bfloat16*)x_out, (__nv_bfloat16*)h_out, rows, width, spin, status);
   return check_cuda(cudaGetLastError(), "allreduce_add_rmsnorm launch");
 }
+
+// ---- two-shot all-reduce (+ residual add + RMSNorm) for messages of a few megabytes --------------------------------
+// The one-shot form makes every rank read every rank's whole partial: (n - 1) x message bytes over NVLink per rank,
+// fine for a few hundred kilobytes and 35 us for a 4 MB decode step of 256 rows. Here rank r owns rows
+// [r * rows / n, (r + 1) * rows / n): it sums the peers' partials of ITS rows (reads (n - 1) / n of one message),
+// adds the residual stream, normalises, and stores the new residual rows and the normalised rows into every rank's
+// output buffers (writes 2 (n - 1) / n of one message); a second flag round tells the peers that the rows have
+// landed. Flags [0, 16) of a rank's flag array carry "partials written" (shared with the one-shot kernels, same call
+// counter), flags [16, 32) carry "rows stored". weight == null: no normalisation, only the summed rows are gathered.
+namespace edl {
+namespace {
+
+__global__ void __launch_bounds__(ARN_THREADS)
+allreduce_twoshot_kernel(PeerPtrs data, PeerPtrs flags, PeerPtrs x_outs, PeerPtrs h_outs, int nranks, int rank,
+                         int* sync, const __nv_bfloat16* __restrict__ residual,
+                         const __nv_bfloat16* __restrict__ weight, float eps, float w_offset, int rows, int width,
+                         long long spin_limit, int* status) {
+  __shared__ int s_ok;
+  __shared__ float red[32];
+  const int epoch = *reinterpret_cast<volatile int*>(sync) + 1;
+  if (blockIdx.x == 0 && threadIdx.x < nranks)
+    st_release_sys(reinterpret_cast<int*>(flags.p[threadIdx.x]) + rank, epoch);
+  const int* mine = reinterpret_cast<const int*>(flags.p[rank]);
+  const long long t0 = clock64();
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int r = 0; r < nranks && ok; ++r) {
+      while (ld_acquire_sys(mine + r) < epoch) {
+        if (clock64() - t0 > spin_limit) {
+          ok = 0;
+          if (status) atomicCAS(status, 0, EDL_TIMEOUT_PEER_FLAG);
+          break;
+        }
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  const int vec_per_row = width / 8;
+  const int rows_per = rows / nranks;
+  if (s_ok) {
+    for (int lr = blockIdx.x; lr < rows_per; lr += gridDim.x) {
+      const int row = rank * rows_per + lr;
+      float v[ARN_MAX_VEC][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < ARN_MAX_VEC; ++j) {
+        const int c = threadIdx.x + j * ARN_THREADS;
+        if (c >= vec_per_row) break;
+        const long long off = (long long)row * vec_per_row + c;
+        uint4 part[MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < nranks) part[r] = reinterpret_cast<const uint4*>(data.p[r])[off];
+        float2 f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[j][e] = 0.f;
+        if (residual) {
+          const uint4 rs = reinterpret_cast<const uint4*>(residual)[off];
+          f = unpack_bf16x2(rs.x); v[j][0] = f.x; v[j][1] = f.y;
+          f = unpack_bf16x2(rs.y); v[j][2] = f.x; v[j][3] = f.y;
+          f = unpack_bf16x2(rs.z); v[j][4] = f.x; v[j][5] = f.y;
+          f = unpack_bf16x2(rs.w); v[j][6] = f.x; v[j][7] = f.y;
+        }
+        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) {
+          if (r >= nranks) break;
+          f = unpack_bf16x2(part[r].x); a[0] += f.x; a[1] += f.y;
+          f = unpack_bf16x2(part[r].y); a[2] += f.x; a[3] += f.y;
+          f = unpack_bf16x2(part[r].z); a[4] += f.x; a[5] += f.y;
+          f = unpack_bf16x2(part[r].w); a[6] += f.x; a[7] += f.y;
+        }
+        uint4 o;
+        uint32_t* ow = &o.x;
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          // the sum is rounded to bf16 before it joins the residual stream, as the unfused sequence does
+          const float2 y = unpack_bf16x2(pack_bf16x2(a[e], a[e + 1]));
+          const uint32_t packed = pack_bf16x2(v[j][e] + y.x, v[j][e + 1] + y.y);
+          ow[e >> 1] = packed;
+          const float2 z = unpack_bf16x2(packed);
+          v[j][e] = z.x;
+          v[j][e + 1] = z.y;
+          ss += z.x * z.x + z.y * z.y;
+        }
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < nranks) reinterpret_cast<uint4*>(x_outs.p[r])[off] = o;
+      }
+      if (weight) {
+        ss = block_sum(ss, red);
+        const float rstd = rsqrtf(ss / (float)width + eps);
+#pragma unroll
+        for (int j = 0; j < ARN_MAX_VEC; ++j) {
+          const int c = threadIdx.x + j * ARN_THREADS;
+          if (c >= vec_per_row) break;
+          const uint4 wv = reinterpret_cast<const uint4*>(weight)[c];
+          const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+          uint4 o;
+          uint32_t* ow = &o.x;
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            const float2 w2 = unpack_bf16x2(ww[e >> 1]);
+            ow[e >> 1] = pack_bf16x2(v[j][e] * rstd * (w2.x + w_offset), v[j][e + 1] * rstd * (w2.y + w_offset));
+          }
+          const long long off = (long long)row * vec_per_row + c;
+#pragma unroll
+          for (int r = 0; r < MAX_RANKS; ++r)
+            if (r < nranks) reinterpret_cast<uint4*>(h_outs.p[r])[off] = o;
+        }
+        __syncthreads();
+      }
+    }
+  }
+  // second round: this rank's rows are in every peer's buffers once ALL its blocks have fenced their stores
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(sync + 2, 1) == (int)gridDim.x - 1) {
+      sync[2] = 0;
+      __threadfence_system();
+      for (int r = 0; r < nranks; ++r) st_release_sys(reinterpret_cast<int*>(flags.p[r]) + 16 + rank, epoch);
+    }
+    for (int r = 0; r < nranks; ++r) {
+      while (ld_acquire_sys(mine + 16 + r) < epoch) {
+        if (clock64() - t0 > 2 * spin_limit) {
+          if (status) atomicCAS(status, 0, EDL_TIMEOUT_PEER_FLAG);
+          r = nranks;
+          break;
+        }
+      }
+    }
+    __threadfence();
+    if (atomicAdd(sync + 1, 1) == (int)gridDim.x - 1) {
+      sync[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile int*>(sync) = epoch;
+    }
+  }
+}
+
+}  // namespace
+}  // namespace edl
+
+// data_ptrs[r]: rank r's partial [rows, width] bf16; flag_ptrs[r]: rank r's flag array (int[32]); x_out_ptrs[r] /
+// h_out_ptrs[r]: rank r's output buffers in symmetric memory ([rows, width] bf16 each): x_out receives
+// residual + sum (or the sum alone when residual is null), h_out the RMSNorm of it times (weight + w_offset) when
+// weight is given. rows must be a multiple of nranks, width a multiple of 8 and <= 16384. sync: int[4] per group.
+// `residual` may be this rank's own x_out buffer (each rank reads and rewrites only its own rows of it).
+EDL_HOST_API int edl_allreduce_twoshot(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs,
+                                       const unsigned long long* x_out_ptrs, const unsigned long long* h_out_ptrs,
+                                       int nranks, int rank, int* sync, const void* residual, const void* weight,
+                                       float eps, float w_offset, int rows, int width, int wait_ms, int* status,
+                                       void* stream) {
+  if (rows <= 0) return 0;
+  if (nranks < 1 || nranks > MAX_RANKS || (width & 7) || width > ARN_THREADS * ARN_MAX_VEC * 8 || rows % nranks ||
+      (weight && !h_out_ptrs)) {
+    set_last_error("edl_allreduce_twoshot: nranks=%d, rows=%d (multiple of nranks), width=%d (multiple of 8, <= %d)",
+                   nranks, rows, width, ARN_THREADS * ARN_MAX_VEC * 8);
+    return -1;
+  }
+  PeerPtrs d, f, xo, ho;
+  for (int r = 0; r < MAX_RANKS; ++r) {
+    d.p[r] = reinterpret_cast<void*>(r < nranks ? data_ptrs[r] : 0ull);
+    f.p[r] = reinterpret_cast<void*>(r < nranks ? flag_ptrs[r] : 0ull);
+    xo.p[r] = reinterpret_cast<void*>(r < nranks ? x_out_ptrs[r] : 0ull);
+    ho.p[r] = reinterpret_cast<void*>(r < nranks && h_out_ptrs ? h_out_ptrs[r] : 0ull);
+  }
+  int blocks = rows / nranks;
+  if (blocks > sm_count()) blocks = sm_count();
+  const long long spin = (long long)(wait_ms > 0 ? wait_ms : 2000) * 2000000LL;
+  allreduce_twoshot_kernel<<<blocks, ARN_THREADS, 0, (cudaStream_t)stream>>>(
+      d, f, xo, ho, nranks, rank, sync, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)weight, eps, w_offset,
+      rows, width, spin, status);
+  return check_cuda(cudaGetLastError(), "allreduce_twoshot launch");
+}

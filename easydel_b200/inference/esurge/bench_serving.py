@@ -118,6 +118,7 @@ def run(args) -> dict | None:
     for i in range(min(3, len(work))):
         engine.generate(work[i][1][:256], SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True))
     torch.cuda.synchronize()
+    engine.runner.time_decode_steps = True      # CUDA events around every replayed decode step
     # The arrival count travels over a host-side (gloo) group: a device-side broadcast read back with .item()
     # would wait for the engine step that was just launched and serialise host and device again.
     ctl = None
@@ -186,6 +187,9 @@ def run(args) -> dict | None:
             total_out = sum(n_out.values())
             span = float(dev_ms) / 1e3
             tm = engine.runner.timings
+            steps_ms = engine.runner.decode_step_times()
+            decode_ms = {str(bp): {"n": len(v), "p50_ms": pct(v, 50), "p90_ms": pct(v, 90)}
+                         for bp, v in sorted(steps_ms.items())}
             result = {
                 "metric": "eSurge output tokens/s", "value": total_out / span, "unit": "tokens/s", "n_gpus": world,
                 "model": args.model + (f"-{args.layers}L" if args.layers else "") + shape_note, "tp": world,
@@ -196,7 +200,8 @@ def run(args) -> dict | None:
                 "prefix_cache_hit_rate": engine.pool.stats.hit_rate, "kv_pages": engine.cache.num_pages,
                 "max_num_seqs": args.max_num_seqs, "page_size": 128, "async_scheduling": engine.async_scheduling,
                 "steps": tm["steps"], "graph_steps": tm["graph_steps"], "host_prep_s": tm["prep"],
-                "launch_s": tm["exec"], "sample_s": tm["sample"], "d2h_wait_s": tm["d2h"], "dtype": "bf16",
+                "launch_s": tm["exec"], "sample_s": tm["sample"], "d2h_wait_s": tm["d2h"],
+                "decode_step_device_ms_by_rows": decode_ms, "dtype": "bf16",
                 "data": "synthetic", "timing": "CUDA events around the whole run, max over ranks"}
         return result
     finally:

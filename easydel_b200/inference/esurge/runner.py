@@ -79,10 +79,15 @@ class ModelRunner:
         import os
 
         self.use_graphs = dev.type == "cuda" and os.environ.get("EDL_ESURGE_CUDA_GRAPHS", "1") != "0"
-        if cache.linear or cache.latent or model.spec.head_dim not in (64, 128):
+        latent_kernel = bool(cache.latent and cache.k.shape[-1] == 576)    # the 512 + 64 layout has a decode kernel
+        if cache.linear or (cache.latent and not latent_kernel) or \
+                (not cache.latent and model.spec.head_dim not in (64, 128)):
             self.use_graphs = False     # these serving paths are tensor code with host-side steps: run eagerly
         self._seq_slots = torch.zeros(max_num_seqs, dtype=torch.int64, device=dev)
         self._graphs: dict[int, tuple[tp.Any, torch.Tensor]] = {}
+        # device time of replayed decode steps (CUDA events around the graph launch), read by decode_step_times()
+        self.time_decode_steps = False
+        self._step_events: list = []
         self._graph_pool = None
         self._warm: set[int] = set()
         self._sms = torch.cuda.get_device_properties(dev).multi_processor_count if dev.type == "cuda" else 1
@@ -90,6 +95,17 @@ class ModelRunner:
         mesh = getattr(model.config, "mesh", None)
         if mesh is not None and getattr(mesh, "tp", 1) > 1:
             self.tp_group = mesh.get_group("tp")
+
+    def decode_step_times(self) -> dict[int, list[float]]:
+        """Milliseconds on the device of every replayed decode step recorded since the last call, by batch bucket
+        (``time_decode_steps`` must be on). Synchronises the device."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        out: dict[int, list[float]] = {}
+        for bp, e0, e1 in self._step_events:
+            out.setdefault(bp, []).append(e0.elapsed_time(e1))
+        self._step_events = []
+        return out
 
     def release(self) -> None:
         """Drops the captured graphs (and with them their private memory pool). Needed before the process group
@@ -157,6 +173,8 @@ class ModelRunner:
             res = model(input_ids=d_ids[:T][None].long(), position_ids=d_pos[:T][None], past_key_values=self.cache,
                         cache_metadata=meta, apply_lm_head=False)
         rows = S.gather_rows(res.last_hidden_state[0], d_last[:B])
+        if self.tp_group is not None and hasattr(model, "apply_lm_head_vocab_parallel"):
+            return model.apply_lm_head_vocab_parallel(rows, self.tp_group)
         return model.apply_lm_head(rows)
 
     def _fill_extra_groups(self, sched, B: int) -> None:
@@ -351,7 +369,14 @@ class ModelRunner:
             self._dviews[0].index_copy_(0, d_fixpos, self._last_tokens.index_select(0, d_fixslot).to(torch.int32))
         t1 = time.perf_counter()
         if self.use_graphs and decode_only:
-            tokens = self._decode_step_graphed(Bp)[:B]
+            if self.time_decode_steps and Bp in self._graphs:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                tokens = self._decode_step_graphed(Bp)[:B]
+                e1.record()
+                self._step_events.append((Bp, e0, e1))
+            else:
+                tokens = self._decode_step_graphed(Bp)[:B]
             self.timings["graph_steps"] += 1
             t2 = time.perf_counter()
         else:

@@ -250,6 +250,8 @@ class EasyDeLBaseConfig(PretrainedConfig):
         operation_configs: dict | None = None,
         fsdp_parameter_sharding: str = "auto",
         tp_sequence_parallel: bool = True,
+        ring_attention_layout: str = "zigzag",
+        ring_attention_impl: str = "auto",
         **kwargs,
     ):
         self.sharding_axis_dims = tuple(getattr(self, "sharding_axis_dims", None) or sharding_axis_dims)
@@ -322,6 +324,14 @@ class EasyDeLBaseConfig(PretrainedConfig):
         self.fsdp_parameter_sharding = str(fsdp_parameter_sharding).lower()
         # tensor-parallel dense stacks keep the residual stream sharded by token rows between their linears
         self.tp_sequence_parallel = bool(tp_sequence_parallel)
+        # attn_mechanism="ring" with sp > 1: how the sequence is laid over the sp ranks (zigzag balances causal work,
+        # contiguous keeps rank r's tokens adjacent) and which exchange serves it (gather = all keys / values
+        # gathered, peer = remote key blocks read in place by the flash kernel, auto = peer when it applies)
+        if ring_attention_layout not in ("zigzag", "contiguous"):
+            raise ValueError(f"ring_attention_layout must be zigzag or contiguous, got {ring_attention_layout!r}")
+        if ring_attention_impl not in ("auto", "gather", "peer"):
+            raise ValueError(f"ring_attention_impl must be auto, gather or peer, got {ring_attention_impl!r}")
+        self.ring_attention_layout, self.ring_attention_impl = ring_attention_layout, ring_attention_impl
         self.pretraining_tp = 1
         if self.kv_cache_quantization_config is not None and self.use_sharded_kv_caching:
             warnings.warn("`kv_cache_quantization_config` and `use_sharded_kv_caching` can't be used together "

@@ -124,6 +124,16 @@ class EasyDeLState:
             if mesh is not None and mesh.tp > 1:
                 flat.sync_partial_grads_over_tp(mesh.get_group("tp"))
             self.model.sp_partial_grads = False
+        if getattr(self.model, "cp_partial_grads", False):
+            # the batch's sequence dimension was sharded over the ``sp`` axis: every gradient is a partial sum
+            mesh = self._model_mesh()
+            if mesh is not None and mesh.sp > 1:
+                if self._fsdp is not None:
+                    raise NotImplementedError("sequence-sharded batches with parameter-sharded layers")
+                import torch.distributed as dist
+
+                dist.all_reduce(flat.grad, group=mesh.get_group("sp"))
+            self.model.cp_partial_grads = False
         ep_group, ep = self._expert_parallel()
         if ep > 1:
             # replicated parameters: sum over the ranks' different tokens; then everything is the gradient of the

@@ -123,6 +123,11 @@ class Attention(nn.Module):
             self.alibi = None
 
     # ------------------------------------------------------------------
+    #: set by the decoder when the sequence is sharded over the ``sp`` mesh axis (``attn_mechanism="ring"``)
+    cp_group = None
+    cp_layout = "zigzag"
+    cp_impl = "auto"
+
     def _split(self, qkv: torch.Tensor):
         B, T, _ = qkv.shape
         Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
@@ -171,7 +176,9 @@ class Attention(nn.Module):
             positions = positions[0]
         else:
             if self.rotary is not None:
-                qkv = self.rotary.rotate_packed(qkv, positions, self.num_heads + self.num_kv_heads)
+                # serving: the projection's output is consumed here only, so it is rotated where it lies
+                qkv = self.rotary.rotate_packed(qkv, positions, self.num_heads + self.num_kv_heads,
+                                                inplace=cache_view is not None and not torch.is_grad_enabled())
             q, k, v = self._split(qkv)
         if self.head_scale is not None:
             q = (q * self.head_scale.to(q.dtype)[None, None, :, None])
@@ -190,6 +197,16 @@ class Attention(nn.Module):
                 segment_ids = (base * (int(blocks.max()) + 1) + blocks).to(torch.int32) * (base != 0)
         if cache_view is not None:
             o = cache_view.attend(self, q, k, v, positions=positions, attn_meta=attn_meta)
+        elif self.cp_group is not None:
+            if segment_ids is not None or self.sliding_window or self.sinks is not None or self.alibi is not None \
+                    or self.chunk_size:
+                raise NotImplementedError("sequence-parallel (ring) attention covers plain causal / full attention: "
+                                          "no packed segments, windows, sinks or position biases")
+            from ..parallel import context_parallel as CP
+
+            o = CP.ring_attention(q.contiguous(), k.contiguous(), v.contiguous(), self.cp_group,
+                                  layout=self.cp_layout, causal=self.causal, scale=self.scale,
+                                  softcap=self.softcap or 0.0, impl=self.cp_impl)
         elif self.alibi is not None:
             o = self._alibi_attention(q, k, v, segment_ids)
         else:

@@ -188,14 +188,16 @@ class RotaryEmbedding(torch.nn.Module):
             self.sin = self.sin.to(device)
         return self.cos, self.sin
 
-    def rotate_packed(self, qkv: torch.Tensor, positions: torch.Tensor, n_heads: int, col0: int = 0) -> torch.Tensor:
-        """Rotates ``n_heads`` consecutive heads of a packed projection ``[..., width]`` starting at ``col0``."""
+    def rotate_packed(self, qkv: torch.Tensor, positions: torch.Tensor, n_heads: int, col0: int = 0,
+                      inplace: bool = False) -> torch.Tensor:
+        """Rotates ``n_heads`` consecutive heads of a packed projection ``[..., width]`` starting at ``col0``
+        (``inplace``: in the projection's own memory when no gradient is needed)."""
         from ..ops import functional as F
 
         cos, sin = self.tables(qkv.device)
         shape = qkv.shape
         out = F.rope_packed(qkv.reshape(-1, shape[-1]), positions.reshape(-1), cos, sin, n_heads, self.head_size,
-                            col0=col0, rot_dim=self.rotary_dim, interleaved=not self.is_neox_style)
+                            col0=col0, rot_dim=self.rotary_dim, interleaved=not self.is_neox_style, inplace=inplace)
         return out.view(shape)
 
     def forward(self, positions: torch.Tensor, q: torch.Tensor, k: torch.Tensor):

@@ -393,6 +393,28 @@ class DecoderModel(EasyDeLBaseModule):
         if spec.final_norm:
             self.norm = _norm(spec, pd)
         self._setup_sequence_parallel(config)
+        self._setup_context_parallel(config)
+
+    #: process group over which the sequence dimension of a batch is sharded (``attn_mechanism="ring"``), or None
+    cp_group = None
+    cp_layout = "zigzag"
+
+    def _setup_context_parallel(self, config) -> None:
+        """``attn_mechanism="ring"`` on a mesh whose ``sp`` axis is larger than one: every rank of the ``sp`` group
+        runs the layers on its slice of the sequence and the attention layers see the whole sequence's keys
+        (parallel.context_parallel). The reference selects its ring attention the same way
+        (easydel/operations/kernels/ring_attention.py:84-260) with the batch sharded ``P(("dp", "fsdp"), "sp")``."""
+        mesh = getattr(config, "mesh", None)
+        mech = str(getattr(getattr(config, "attn_mechanism", None), "value", getattr(config, "attn_mechanism", "")))
+        if mesh is None or getattr(mesh, "sp", 1) <= 1 or mech != "ring":
+            return
+        self.cp_group = mesh.get_group("sp")
+        self.cp_layout = getattr(config, "ring_attention_layout", None) or "zigzag"
+        impl = getattr(config, "ring_attention_impl", None) or "auto"
+        for layer in self.layers:
+            attn = getattr(layer, "self_attn", None)
+            if attn is not None and hasattr(attn, "cp_group"):
+                attn.cp_group, attn.cp_layout, attn.cp_impl = self.cp_group, self.cp_layout, impl
 
     def _setup_sequence_parallel(self, config) -> None:
         """Dense attention + MLP stacks can keep the residual stream sharded by rows over the tensor-parallel
@@ -565,6 +587,30 @@ class DecoderForCausalLM(EasyDeLBaseModule):
             logits = torch.tanh(logits.float() / spec.logit_softcap).mul_(spec.logit_softcap).to(logits.dtype)
         return logits
 
+    def apply_lm_head_vocab_parallel(self, hidden: torch.Tensor, group) -> torch.Tensor:
+        """Serving under tensor parallelism: every rank multiplies by its slice of the (replicated) head's rows and
+        the slices of the logits are gathered, so a decode step streams ``vocab / tp`` rows of the head per GPU
+        instead of all of them. Same values as :meth:`apply_lm_head` (each logit is one dot product either way)."""
+        import torch.distributed as dist
+
+        n, r = dist.get_world_size(group), dist.get_rank(group)
+        W = self.lm_head_weight()
+        V = W.shape[0]
+        if n == 1 or V % (8 * n) or hidden.dim() != 2 or torch.is_grad_enabled():
+            return self.apply_lm_head(hidden)
+        vs = V // n
+        bias = self.lm_head_bias()
+        part = F.linear(hidden, W[r * vs:(r + 1) * vs], None if bias is None else bias[r * vs:(r + 1) * vs])
+        full = torch.empty(n * hidden.shape[0], vs, dtype=part.dtype, device=part.device)
+        dist.all_gather_into_tensor(full, part.contiguous(), group=group)
+        logits = full.view(n, hidden.shape[0], vs).permute(1, 0, 2).reshape(hidden.shape[0], V)
+        spec = self.spec
+        if spec.logit_scale is not None:
+            logits = logits * spec.logit_scale
+        if spec.logit_softcap:
+            logits = torch.tanh(logits.float() / spec.logit_softcap).mul_(spec.logit_softcap).to(logits.dtype)
+        return logits
+
     def make_lm_head_fn(self):
         return self.apply_lm_head
 
@@ -595,6 +641,22 @@ class DecoderForCausalLM(EasyDeLBaseModule):
         call["apply_lm_head"] = False
         if getattr(self.model, "sp_capable", False) and type(self).forward is DecoderForCausalLM.forward:
             call["sequence_parallel"] = True   # tensor-parallel dense stacks keep the token rows sharded
+        cp_group = getattr(self.model, "cp_group", None)
+        if cp_group is not None:
+            import torch.distributed as dist
+
+            from ...parallel import context_parallel as CP
+
+            if not call.pop("labels_shifted", False):
+                # the whole sequence came in: keep this rank's slice (labels shifted before the cut)
+                keys = set(call) | {"position_ids"}
+                b = CP.shard_batch({**call, "labels": labels}, dist.get_rank(cp_group), dist.get_world_size(cp_group),
+                                   self.model.cp_layout)
+                labels = b["labels"]
+                call = {k: v for k, v in b.items() if k in keys}
+            call.pop("attention_mask", None)        # folded into the labels; the layers see every token
+        else:
+            call.pop("labels_shifted", None)
         attention_mask = call.get("attention_mask")
         out = self(**call)
         if attention_mask is not None:
@@ -603,6 +665,21 @@ class DecoderForCausalLM(EasyDeLBaseModule):
         hidden = out.last_hidden_state
         if spec.logit_scale is not None:
             hidden = hidden * spec.logit_scale
+        if cp_group is not None:
+            # Sequence sharded over the ``sp`` axis: this rank computes the loss terms of its own tokens, normalised
+            # by the group-wide token count; the loss is the sum over the group and EVERY parameter's gradient is a
+            # partial sum (``cp_partial_grads``, summed over the group before the update).
+            from ...parallel import tp as tpar
+
+            metrics = causal_lm_loss_from_hidden(hidden, self.lm_head_weight(), labels, loss_config,
+                                                 lm_head_bias=self.lm_head_bias(), softcap=spec.logit_softcap,
+                                                 chunk_size=getattr(self.config, "lmhead_chunksize", None),
+                                                 loss_scale=loss_scale, already_shifted=True, count_group=cp_group,
+                                                 **loss_kwargs)
+            metrics.loss = tpar.sum_value_over_group(metrics.loss, cp_group)
+            if torch.is_grad_enabled():
+                self.cp_partial_grads = True
+            return out, metrics
         sp = getattr(self.model, "sp", None)
         if sp is not None and sp.active:
             # Every rank holds the hidden states of its own rows: it computes the loss terms of those rows

@@ -166,12 +166,18 @@ class _RopeFn(torch.autograd.Function):
 
 
 def rope_packed(qkv: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, nheads: int,
-                head_dim: int, col0: int = 0, rot_dim: int | None = None, interleaved: bool = False):
+                head_dim: int, col0: int = 0, rot_dim: int | None = None, interleaved: bool = False,
+                inplace: bool = False):
     """Rotates the first ``nheads`` heads (starting at column ``col0``) of a packed ``[T, width]`` projection.
 
-    Returns a new tensor; the input is left untouched.
+    Returns a new tensor and leaves the input untouched, except with ``inplace=True`` (inference: the projection's
+    output has no other reader), where the rotation is done in the input's memory and no copy is made.
     """
     if _lib.use_kernels(qkv):
+        if inplace and not (torch.is_grad_enabled() and qkv.requires_grad) and qkv.is_contiguous():
+            K.rope_(qkv.view(-1, qkv.shape[-1]), pos.reshape(-1), cos, sin, nheads, head_dim, col0=col0,
+                    rot_dim=rot_dim, interleaved=interleaved)
+            return qkv
         return _RopeFn.apply(qkv, pos.reshape(-1), cos, sin, nheads, head_dim, col0, rot_dim, interleaved)
     T = qkv.reshape(-1, qkv.shape[-1]).shape[0]
     flat = qkv.reshape(T, -1)

@@ -21,6 +21,8 @@ _lib.register("edl_gather_rows", i32, [vp, vp, vp, i32, i32, i64, vp])
 _lib.register("edl_attn_decode", i32, [vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, i32, i32, i64, i32, i32, i32, f32,
                                        i32, i32, vp, vp, vp])
 
+_lib.register("edl_attn_mla_decode", i32, [vp, vp, vp, vp, i64, i64, vp, vp, i32, i32, i64, i32, f32, i32, vp, vp])
+
 PAGE_SIZE = 128
 
 
@@ -91,6 +93,31 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     if S_ == 1:
         return out[0]
     return attn_combine(out, lse, sinks=sinks)
+
+
+def mla_decode_attention(q: torch.Tensor, pages: torch.Tensor, kv_lens: torch.Tensor, page_table: torch.Tensor, *,
+                         scale: float, num_splits: int = 1) -> torch.Tensor:
+    """Decode-step latent attention in the absorbed form (``csrc/attention_mla_decode.cu``).
+
+    q ``[B, H, 576]`` = (query folded through the key up-projection (512) | rotated rotary query (64)); pages
+    ``[P, 128, 1, 576]`` rows (compressed key/value | rotated rotary key). Returns ``[B, H, 512]``: the
+    softmax-weighted sums of the rows' compressed part, to be sent through the value up-projection."""
+    B, H, W = q.shape
+    assert W == 576 and pages.shape[-1] == 576 and pages.shape[1] == PAGE_SIZE and q.is_contiguous()
+    S_ = max(1, int(num_splits))
+    out = torch.empty((S_, B, H, 512), dtype=q.dtype, device=q.device)
+    lse = torch.empty((S_, H, B), dtype=torch.float32, device=q.device) if S_ > 1 else None
+    _lib.call("edl_attn_mla_decode", q.data_ptr(), pages.data_ptr(), out.data_ptr(), _lib.ptr(lse), H * 576, H * 512,
+              kv_lens.data_ptr(), page_table.data_ptr(), page_table.stride(0), B, pages.shape[0], H, float(scale), S_,
+              _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
+    if S_ == 1:
+        return out[0]
+    return attn_combine(out, lse)
+
+
+def mla_decode_kernel_supports(q: torch.Tensor, pages: torch.Tensor) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and q.shape[-1] == 576
+            and pages.shape[-1] == 576 and pages.shape[1] == PAGE_SIZE and pages.is_contiguous())
 
 
 def decode_kernel_supports(q: torch.Tensor, k_pages: torch.Tensor, softcap: float) -> bool:

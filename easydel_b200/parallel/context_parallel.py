@@ -119,3 +119,127 @@ def context_parallel_attention_reference(q, k, v, group, causal=True, scale=None
     if causal:
         kf, vf = kf[: (me + 1) * T], vf[: (me + 1) * T]
     return R.attention(q[None], kf[None], vf[None], causal=causal, scale=scale)[0]
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Sequence sharding of a batch and the attention that goes with it on the model path (``attn_mechanism="ring"`` with
+# an ``sp`` mesh axis > 1; the reference shards the batch ``P(("dp", "fsdp"), "sp")``,
+# easydel/trainers/training_utils.py:763-765, and runs ring attention, easydel/operations/kernels/ring_attention.py:84-260).
+#
+# Layouts of the sequence over the ``n`` ranks of the group:
+#   contiguous  rank r holds tokens [r * T/n, (r + 1) * T/n)
+#   zigzag      the sequence is cut into 2n chunks and rank r holds chunks r and 2n - 1 - r, so that under a causal
+#               mask every rank has the same number of (query, key) pairs to compute
+# Keys and values are small next to the queries under grouped-query attention, so every rank gathers all of them
+# (the gather's backward is the reduce-scatter that sums the key / value gradients on their owners) and runs the flash
+# kernel once per local chunk against the keys in front of that chunk's end; the "fewer queries than keys" causal
+# form of the kernel puts the diagonal where it belongs.
+LAYOUTS = ("contiguous", "zigzag")
+
+
+def shard_positions(total: int, rank: int, world: int, layout: str = "zigzag") -> torch.Tensor:
+    """Global positions of the tokens rank ``rank`` holds, in the order it holds them."""
+    if layout not in LAYOUTS:
+        raise ValueError(f"sequence layout {layout!r}: expected one of {LAYOUTS}")
+    parts = world if layout == "contiguous" else 2 * world
+    if total % parts:
+        raise ValueError(f"sequence length {total} is not a multiple of {parts} ({layout} over {world} ranks)")
+    c = total // parts
+    if layout == "contiguous":
+        return torch.arange(rank * c, (rank + 1) * c)
+    return torch.cat([torch.arange(rank * c, (rank + 1) * c),
+                      torch.arange((2 * world - 1 - rank) * c, (2 * world - rank) * c)])
+
+
+def shard_sequence(t: torch.Tensor, rank: int, world: int, layout: str = "zigzag", dim: int = 1) -> torch.Tensor:
+    idx = shard_positions(t.shape[dim], rank, world, layout).to(t.device)
+    return t.index_select(dim, idx)
+
+
+def shard_batch(batch: dict, rank: int, world: int, layout: str = "zigzag") -> dict:
+    """This rank's slice of a causal-LM batch. Labels are shifted to the next token on the whole sequence first (the
+    token after a shard's last one lives on another rank), so the result carries ``labels_shifted=True``;
+    ``position_ids`` hold the global positions."""
+    ids = batch["input_ids"]
+    B, T = ids.shape
+    labels = batch.get("labels", ids)
+    shifted = torch.full_like(labels, -100)
+    shifted[:, :-1] = labels[:, 1:]
+    if batch.get("attention_mask") is not None:
+        shifted = torch.where(torch.nn.functional.pad(batch["attention_mask"][:, 1:], (0, 1)).bool(), shifted,
+                              torch.full_like(shifted, -100))
+    pos = batch.get("position_ids")
+    if pos is None:
+        pos = torch.arange(T, device=ids.device)[None].expand(B, T)
+    out = dict(batch)
+    for name, t in (("input_ids", ids), ("labels", shifted), ("position_ids", pos)):
+        out[name] = shard_sequence(t, rank, world, layout)
+    for name in ("attention_mask", "segment_ids"):
+        if batch.get(name) is not None:
+            out[name] = shard_sequence(batch[name], rank, world, layout)
+    out["labels_shifted"] = True
+    return out
+
+
+def gathered_kv_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, group, *, layout: str = "zigzag",
+                          causal: bool = True, scale: float | None = None, softcap: float = 0.0) -> torch.Tensor:
+    """Attention of this rank's query shard ``[B, Tl, Hq, D]`` over the keys / values of the whole sequence, whose
+    shards ``[B, Tl, Hkv, D]`` are spread over ``group`` in ``layout``. Differentiable."""
+    from ..ops import functional as F
+    from .ep import all_gather_tokens
+
+    n, r = dist.get_world_size(group), dist.get_rank(group)
+    B, Tl, Hkv, D = k.shape
+    kv = torch.stack([k, v], 0).reshape(2 * B * Tl, Hkv * D)              # one exchange for both
+    kv_all = all_gather_tokens(kv.contiguous(), group).view(n, 2, B, Tl, Hkv, D)
+    if layout == "contiguous":
+        k_all = kv_all[:, 0].permute(1, 0, 2, 3, 4).reshape(B, n * Tl, Hkv, D)
+        v_all = kv_all[:, 1].permute(1, 0, 2, 3, 4).reshape(B, n * Tl, Hkv, D)
+        if not causal:
+            return F.attention(q, k_all, v_all, causal=False, scale=scale, softcap=softcap)
+        end = (r + 1) * Tl
+        return F.attention(q, k_all[:, :end], v_all[:, :end], causal=True, scale=scale, softcap=softcap)
+    c = Tl // 2
+    # global order: chunk s is the first half of rank s, chunk 2n - 1 - s the second half of rank s
+    halves = kv_all.view(n, 2, B, 2, c, Hkv, D)
+    early = halves[:, :, :, 0]                                             # [n, 2, B, c, Hkv, D] chunks 0 .. n-1
+    late = halves[:, :, :, 1].flip(0)                                      # chunks n .. 2n-1
+    full = torch.cat([early, late], 0)                                     # [2n, 2, B, c, Hkv, D] in global order
+    k_all = full[:, 0].permute(1, 0, 2, 3, 4).reshape(B, 2 * n * c, Hkv, D)
+    v_all = full[:, 1].permute(1, 0, 2, 3, 4).reshape(B, 2 * n * c, Hkv, D)
+    if not causal:
+        return F.attention(q, k_all, v_all, causal=False, scale=scale, softcap=softcap)
+    e0, e1 = (r + 1) * c, (2 * n - r) * c
+    o0 = F.attention(q[:, :c], k_all[:, :e0], v_all[:, :e0], causal=True, scale=scale, softcap=softcap)
+    o1 = F.attention(q[:, c:], k_all[:, :e1], v_all[:, :e1], causal=True, scale=scale, softcap=softcap)
+    return torch.cat([o0, o1], 1)
+
+
+_PEER_CP: dict[tuple, ContextParallelAttention] = {}
+
+
+def ring_attention(q, k, v, group, *, layout: str = "zigzag", causal: bool = True, scale: float | None = None,
+                   softcap: float = 0.0, impl: str = "auto") -> torch.Tensor:
+    """Sequence-parallel attention for the model path. ``impl``: ``gather`` = all keys / values gathered, flash
+    kernel per local chunk (any layout, any device); ``peer`` = remote key blocks read in place over NVLink by the
+    flash kernel's own loads (contiguous layout, CUDA, no soft-cap, batch 1); ``auto`` picks ``peer`` when it
+    applies and the layout is contiguous."""
+    from ..ops import _lib
+
+    peer_ok = (layout == "contiguous" and q.is_cuda and _lib.available() and not softcap and q.shape[0] == 1 and
+               q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128))
+    if impl == "peer" and not peer_ok:
+        raise ValueError("the peer-memory form needs the contiguous layout, one bf16 sequence per rank on CUDA, "
+                         "head size 64 or 128 and no soft-cap")
+    if impl == "peer" or (impl == "auto" and peer_ok):
+        T, Hkv, D = k.shape[1], k.shape[2], k.shape[3]
+        key = (id(group), T, Hkv, D, q.device.index)
+        cp = _PEER_CP.get(key)
+        if cp is None:
+            cp = _PEER_CP[key] = ContextParallelAttention(group, T, Hkv, D, q.device, q.dtype)
+        return cp(q[0], k[0], v[0], causal=causal, scale=scale)[None]
+    return gathered_kv_attention(q, k, v, group, layout=layout, causal=causal, scale=scale, softcap=softcap)
+
+
+def release_peer_buffers() -> None:
+    _PEER_CP.clear()

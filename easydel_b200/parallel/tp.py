@@ -28,21 +28,26 @@ _lib.register("edl_allreduce_add_rmsnorm", _lib.i32, [_lib.vp, _lib.vp, _lib.i32
                                                       _lib.f32, _lib.f32, _lib.vp, _lib.vp, _lib.i32, _lib.i32,
                                                       _lib.i32, _lib.vp, _lib.vp])
 
-ONE_SHOT_MAX_BYTES = 1 << 20
+ONE_SHOT_MAX_BYTES = 1 << 20     # up to here every rank reads every rank's whole partial (one flag round)
+TWO_SHOT_MAX_BYTES = 8 << 20     # up to here rank r reduces its own rows and stores them to every rank (two rounds)
 _FLAG_BYTES = 256
+_lib.register("edl_allreduce_twoshot", _lib.i32, [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.vp,
+                                                  _lib.vp, _lib.vp, _lib.f32, _lib.f32, _lib.i32, _lib.i32, _lib.i32,
+                                                  _lib.vp, _lib.vp])
 
 
 class _PeerAllReduce:
     """Symmetric buffers + flags of one process group."""
 
-    def __init__(self, group, device, max_bytes: int = ONE_SHOT_MAX_BYTES):
+    def __init__(self, group, device, max_bytes: int = TWO_SHOT_MAX_BYTES):
         import torch.distributed._symmetric_memory as symm
 
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.max_bytes = max_bytes
-        total = 2 * max_bytes + _FLAG_BYTES
+        # [partial slot 0 | partial slot 1 | flags | gathered residual rows | gathered normalised rows]
+        total = 4 * max_bytes + _FLAG_BYTES
         self.buf = symm.empty(total, dtype=torch.uint8, device=device)
         self.buf.zero_()
         self.handle = symm.rendezvous(self.buf, group)
@@ -52,8 +57,10 @@ class _PeerAllReduce:
             raise RuntimeError("symmetric-memory handle does not address this rank's own buffer")
         self.slot_ptrs = [(C.c_ulonglong * self.world)(*[b + s * max_bytes for b in base]) for s in range(2)]
         self.flag_ptrs = (C.c_ulonglong * self.world)(*[b + 2 * max_bytes for b in base])
+        self.out_off = [2 * max_bytes + _FLAG_BYTES, 3 * max_bytes + _FLAG_BYTES]
+        self.out_ptrs = [(C.c_ulonglong * self.world)(*[b + o for b in base]) for o in self.out_off]
         self.epoch = 0          # host-side call count: selects the slot; the kernel keeps its own count in `sync`
-        self.sync = torch.zeros(2, dtype=torch.int32, device=device)
+        self.sync = torch.zeros(4, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
 
@@ -77,6 +84,35 @@ class _PeerAllReduce:
         return out
 
 
+    def out_tensor(self, which: int, shape, dtype) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= d
+        off = self.out_off[which]
+        return self.buf[off:off + n * 2].view(dtype).view(shape)
+
+    def two_shot_ok(self, rows: int, width: int) -> bool:
+        return rows % self.world == 0 and width % 8 == 0 and width <= 16384 and rows * width * 2 <= self.max_bytes
+
+    def reduce_two_shot(self, rows: int, width: int, residual=None, weight=None, eps: float = 0.0,
+                        w_offset: float = 0.0, sum_into: int = 0, wait_ms: int = 2000):
+        """Two-shot all-reduce of the partial in the next slot. Returns views of this rank's gathered outputs:
+        ``(residual + sum, rmsnorm(...) * (weight + w_offset))`` (the second is None without ``weight``). The views
+        live in the symmetric buffer and are overwritten by a later call; ``sum_into`` selects which of the two
+        output regions receives the summed rows."""
+        self.epoch += 1
+        s = self.epoch & 1
+        x_ptrs = self.out_ptrs[sum_into]
+        h_ptrs = self.out_ptrs[1 - sum_into] if weight is not None else None
+        _lib.call("edl_allreduce_twoshot", C.cast(self.slot_ptrs[s], C.c_void_p), C.cast(self.flag_ptrs, C.c_void_p),
+                  C.cast(x_ptrs, C.c_void_p), C.cast(h_ptrs, C.c_void_p) if h_ptrs is not None else None, self.world,
+                  self.rank, self.sync.data_ptr(), _lib.ptr(residual), _lib.ptr(weight), float(eps), float(w_offset),
+                  rows, width, wait_ms, _lib.status_word(self.buf.device).data_ptr(), _lib.stream_ptr())
+        x = self.out_tensor(sum_into, (rows, width), torch.bfloat16)
+        h = self.out_tensor(1 - sum_into, (rows, width), torch.bfloat16) if weight is not None else None
+        return x, h
+
+
 class PendingReduce:
     """A row-parallel product whose partial sums still sit in the symmetric slot.
 
@@ -89,8 +125,20 @@ class PendingReduce:
         self.ctx, self.slot, self.shape, self.bias, self.scale = ctx, slot, tuple(shape), bias, scale
         self.dtype, self.device = slot.dtype, slot.device
 
+    def _big(self) -> bool:
+        width = self.shape[-1]
+        rows = self.slot.numel() // width
+        return self.slot.numel() * 2 > ONE_SHOT_MAX_BYTES and self.ctx.two_shot_ok(rows, width)
+
     def resolve(self) -> torch.Tensor:
-        y = self.ctx.reduce(self.slot).view(self.shape)
+        if self._big():
+            width = self.shape[-1]
+            # the sum goes to the region of the normalised rows (whose last content has been consumed) and is copied
+            # out: the residual rows in the other region may still be needed by the caller
+            y, _ = self.ctx.reduce_two_shot(self.slot.numel() // width, width, sum_into=1)
+            y = y.clone().view(self.shape)
+        else:
+            y = self.ctx.reduce(self.slot).view(self.shape)
         if self.bias is not None:
             y = y + self.bias
         return y if self.scale is None else y * self.scale
@@ -104,6 +152,15 @@ class PendingReduce:
 
             return F.add_rms_norm(y, residual, weight, eps, w_offset)
         c = self.ctx
+        if self._big():
+            # rank r reduces, normalises and stores its own rows to everybody; the results are views of the
+            # symmetric buffer (the next all-reduce of this group overwrites them, after its own flag round)
+            width = self.shape[-1]
+            res = residual.reshape(-1, width)
+            if not res.is_contiguous():
+                res = res.contiguous()
+            x_new, h_new = c.reduce_two_shot(res.shape[0], width, res, weight, eps, w_offset)
+            return h_new.view(residual.shape), x_new.view(residual.shape)
         c.epoch += 1
         s = c.epoch & 1
         res = residual.contiguous()
@@ -198,20 +255,17 @@ def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, bias, group, scale=Non
     from ..ops import kernels as K
 
     nbytes = x.numel() // x.shape[-1] * w.shape[0] * 2
-    if (not torch.is_grad_enabled()) and x.is_cuda and x.dtype == torch.bfloat16 and nbytes <= ONE_SHOT_MAX_BYTES:
+    if (not torch.is_grad_enabled()) and x.is_cuda and x.dtype == torch.bfloat16 and nbytes <= TWO_SHOT_MAX_BYTES:
         ctx = _peer_ctx(group, x.device)
-        if ctx is not None:
+        rows_ = x.numel() // x.shape[-1]
+        if ctx is not None and (nbytes <= ONE_SHOT_MAX_BYTES or ctx.two_shot_ok(rows_, w.shape[0])):
             x2 = x.reshape(-1, x.shape[-1])
             if x2.stride(1) != 1 or (x2.shape[0] > 1 and x2.stride(0) % 8):
                 x2 = x2.contiguous()
             slot = ctx.slot_tensor((x2.shape[0], w.shape[0]), x.dtype)
             K.gemm(x2, w, out=slot)
-            if defer:
-                return PendingReduce(ctx, slot, (*x.shape[:-1], w.shape[0]), bias, scale)
-            y = ctx.reduce(slot).view(*x.shape[:-1], w.shape[0])
-            if bias is not None:
-                y = y + bias
-            return y if scale is None else y * scale
+            pend = PendingReduce(ctx, slot, (*x.shape[:-1], w.shape[0]), bias, scale)
+            return pend if defer else pend.resolve()
     y = F.linear(x, w, None)
     y = _ReduceFromTP.apply(y, group) if torch.is_grad_enabled() else all_reduce(y, group)
     if bias is not None:

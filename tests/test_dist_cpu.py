@@ -119,13 +119,16 @@ def test_sharded_optimizer_matches_single_process():
     _run(_sharded_step_worker, 2)
 
 
-def _ep_worker(rank, world):
-    """Expert-parallel MoE block (2 ranks x 2 local experts) equals the single-rank block on each rank's tokens,
-    in outputs and in gradients of inputs, router weights and expert weights."""
+def _ep_worker(rank, world, mode="alltoall"):
+    """Expert-parallel MoE block (2 local experts per rank) equals the single-rank block on each rank's tokens,
+    in outputs and in gradients of inputs, router weights and expert weights, for both token-exchange forms."""
+    import os
+
     from easydel_b200.layers.moe import MoEBlock
 
+    os.environ["EP_DISPATCH"] = mode
     torch.manual_seed(0)
-    H, F, E, k, T = 16, 32, 4, 2, 6
+    H, F, E, k, T = 16, 32, 2 * world, 2, 6
     full = MoEBlock(H, F, E, k, dtype=torch.float32)
     ep = MoEBlock(H, F, E, k, dtype=torch.float32, ep_size=world, ep_rank=rank, ep_group=dist.group.WORLD)
     El = E // world
@@ -149,8 +152,9 @@ def _ep_worker(rank, world):
     assert torch.allclose(g, full.gate.weight.grad, atol=1e-5)
 
 
-def test_expert_parallel_block_matches_single_rank():
-    _run(_ep_worker, 2)
+@pytest.mark.parametrize("mode,world", [("alltoall", 2), ("allgather", 2), ("alltoall", 4)])
+def test_expert_parallel_block_matches_single_rank(mode, world):
+    _run(_ep_worker, world, mode)
 
 
 def _ep_step_worker(rank, world):
@@ -428,3 +432,88 @@ def _fsdp_sharded_worker(rank, world, tmp):
 
 def test_fsdp_parameter_sharded_layers_match_single_process(tmp_path):
     _run(_fsdp_sharded_worker, 2, str(tmp_path))
+
+
+def _ring_worker(rank, world, layout):
+    """Sequence sharded over the sp axis (attn_mechanism="ring"): loss, gradient norm and the updated weights of a
+    clipped optimizer step equal the single-process step on the whole sequences; every rank ends with the same
+    weights. Also the sharding helpers' bookkeeping."""
+    from easydel_b200.infra.base_state import EasyDeLState
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+    from easydel_b200.optimizers import OptimizerFactory, SchedulerConfig
+    from easydel_b200.parallel import context_parallel as CP
+    from easydel_b200.parallel.mesh import DeviceMesh
+
+    pos = torch.cat([CP.shard_positions(32, r, world, layout) for r in range(world)])
+    assert sorted(pos.tolist()) == list(range(32))
+    if layout == "zigzag":
+        assert CP.shard_positions(32, 0, 2, "zigzag").tolist() == list(range(0, 8)) + list(range(24, 32))
+    kw = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=64)
+    one = LlamaConfig(**kw)
+    one.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), one.sharding_axis_names, 0, 1))
+    torch.manual_seed(5)
+    full = LlamaForCausalLM(one, dtype=torch.float32, param_dtype=torch.float32)
+    cfg = LlamaConfig(sharding_axis_dims=(1, 1, 1, 1, world), attn_mechanism="ring", ring_attention_layout=layout, **kw)
+    model = LlamaForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32)
+    model.load_state_dict(full.state_dict())
+    assert model.model.cp_group is not None and model.model.layers[0].self_attn.cp_layout == layout
+    ids = torch.randint(0, 128, (2, 32), generator=torch.Generator().manual_seed(2))
+    labels = ids.clone()
+    labels[0, :5] = -100
+
+    def step(m):
+        tx, _ = OptimizerFactory.create("adamw", SchedulerConfig(None, learning_rate=1e-2), weight_decay=0.0,
+                                        clip_grad=0.05)
+        st = EasyDeLState.create(model=m, tx=tx, init_opt_state=True)
+        _, met = m.compute_loss(input_ids=ids, labels=labels)
+        met.loss.backward()
+        return met.loss.detach(), st.apply_gradients()
+
+    (l_full, n_full), (l_cp, n_cp) = step(full), step(model)
+    assert abs(float(l_full) - float(l_cp)) < 1e-5 * max(1.0, float(l_full)), (float(l_full), float(l_cp))
+    assert abs(float(n_full) - float(n_cp)) < 1e-4 * max(1.0, float(n_full)), (float(n_full), float(n_cp))
+    for k, v in model.state_dict().items():
+        assert torch.allclose(v, full.state_dict()[k], atol=2e-5), k
+    w = model.state_dict()["model.layers.1.mlp.down_proj.weight"].clone()
+    parts = [torch.empty_like(w) for _ in range(world)]
+    dist.all_gather(parts, w)
+    assert all(torch.equal(p, parts[0]) for p in parts)
+
+
+@pytest.mark.parametrize("layout,world", [("zigzag", 2), ("contiguous", 2), ("zigzag", 4)])
+def test_ring_attention_sequence_sharded_step_matches_single_process(layout, world):
+    _run(_ring_worker, world, layout)
+
+
+def _tp_esurge_worker(rank, world):
+    """An eSurge engine over a tensor-parallel model (every rank runs the same scheduler on the same requests; the
+    LM head is evaluated vocabulary-parallel) produces the tokens of the unsharded model's greedy generation."""
+    from easydel_b200.inference import SamplingParams
+    from easydel_b200.inference.esurge import eSurge
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+    from easydel_b200.parallel.mesh import DeviceMesh
+    from easydel_b200.utils.parameters_transformation import shard_internal_state_for_tp
+
+    kw = dict(vocab_size=256, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, max_position_embeddings=512, eos_token_id=255)
+    one = LlamaConfig(**kw)
+    one.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), one.sharding_axis_names, 0, 1))
+    torch.manual_seed(4)
+    full = LlamaForCausalLM(one, dtype=torch.float32, param_dtype=torch.float32).eval()
+    cfg = LlamaConfig(sharding_axis_dims=(1, 1, 1, world, 1), **kw)
+    model = LlamaForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    model.load_state_dict(shard_internal_state_for_tp(model, full.state_dict()))
+    eng = eSurge(model, max_model_len=512, max_num_seqs=4, max_num_batched_tokens=64, num_pages=12)
+    assert eng.runner.tp_group is not None
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 250, (n,), generator=g).tolist() for n in (150, 9)]
+    outs = eng.generate(prompts, SamplingParams(max_tokens=10, temperature=0.0, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        ref = full.generate(torch.tensor([p]), max_new_tokens=10, eos_token_id=-1).sequences[0, len(p):].tolist()
+        assert o.outputs[0].token_ids == ref, (rank, o.outputs[0].token_ids, ref)
+    eng.close()
+
+
+def test_esurge_tensor_parallel_matches_unsharded_generate():
+    _run(_tp_esurge_worker, 2)

@@ -90,6 +90,45 @@ def _allreduce_worker(rank, world):
             assert (plain.float() - y).abs().max() < 6e-2 * y.abs().max()
 
 
+def _twoshot_worker(rank, world):
+    """Messages of a few megabytes (decode steps of a few hundred rows): rank r reduces, normalises and stores its
+    own rows to every rank. The residual stream is carried from call to call through the returned view, as the
+    decoder layers do, and the plain (no norm) form is checked as well."""
+    import torch.distributed as dist
+
+    from easydel_b200.parallel import tp
+
+    g = dist.group.WORLD
+    torch.manual_seed(7)
+    H, Kf, R = 2048, 256 * world, 512          # 512 x 2048 bf16 = 2 MiB per message
+    x_full = torch.randn(R, Kf, device="cuda").to(torch.bfloat16)
+    w_full = (torch.randn(H, Kf, device="cuda") * 0.03).to(torch.bfloat16)
+    nw = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16)
+    res = torch.randn(R, H, device="cuda").to(torch.bfloat16)
+    ks = Kf // world
+    xs, ws = x_full[:, rank * ks:(rank + 1) * ks].contiguous(), w_full[:, rank * ks:(rank + 1) * ks].contiguous()
+    y = x_full.float() @ w_full.float().t()
+    with torch.no_grad():
+        xr = res.float()
+        cur = res
+        for it in range(4):
+            pend = tp.row_parallel_linear(xs, ws, None, g, defer=True)
+            assert isinstance(pend, tp.PendingReduce) and pend._big()
+            h, cur = pend.add_rms_norm(cur, nw, 1e-5)
+            xr = (xr + y).to(torch.bfloat16).float()
+            hr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * nw.float()
+            assert (cur.float() - xr).abs().max() < 6e-2 * xr.abs().max(), it
+            assert (h.float() - hr).abs().max() < 6e-2 * hr.abs().max(), it
+        plain = tp.row_parallel_linear(xs, ws, None, g)
+        assert (plain.float() - y).abs().max() < 6e-2 * y.abs().max()
+        assert (cur.float() - xr).abs().max() < 6e-2 * xr.abs().max(), "the residual rows survived the plain reduce"
+        # every rank holds bit-identical results
+        mine = torch.cat([cur.reshape(-1), h.reshape(-1), plain.reshape(-1)]).view(torch.int16)
+        other = mine.clone()
+        dist.broadcast(other, src=0)
+        assert torch.equal(mine, other)
+
+
 def _tp_forward_worker(rank, world):
     """Tensor-parallel Llama against the single-GPU model: inference logits (all-reduce path), then a training
     step on sequence-sharded activations (all-gather -> GEMM and GEMM -> reduce-scatter kernels in both
@@ -239,6 +278,11 @@ def test_peer_allreduce_matches_nccl():
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
+def test_two_shot_allreduce_add_rmsnorm(world):
+    _run(_twoshot_worker, world)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_tensor_parallel_forward_and_loss(world):
     _run(_tp_forward_worker, world)
 
@@ -250,3 +294,55 @@ def test_sharded_optimizer_peer_kernels():
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_fsdp_parameter_sharded_layers(world):
     _run(_fsdp_sharded_worker, world)
+
+
+def _tp_esurge_worker(rank, world):
+    """eSurge over a tensor-parallel bf16 model (graph-replayed decode steps, peer-memory all-reduces, vocabulary-
+    parallel LM head): same greedy tokens on every rank, and nearly all of them equal to the unsharded engine's
+    (bf16 reductions in another order may flip a near-tie late in a sequence)."""
+    import torch.distributed as dist
+
+    from easydel_b200.inference import SamplingParams
+    from easydel_b200.inference.esurge import eSurge
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+    from easydel_b200.parallel import tp as tpar
+    from easydel_b200.parallel.mesh import DeviceMesh
+    from easydel_b200.utils.parameters_transformation import shard_internal_state_for_tp
+
+    dev = torch.device("cuda", rank)
+    kw = dict(vocab_size=1024, hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
+              num_key_value_heads=2 * world if world <= 4 else 8, head_dim=64, max_position_embeddings=1024,
+              eos_token_id=1023)
+    one = LlamaConfig(**kw)
+    one.set_model_mesh(DeviceMesh((1, 1, 1, 1, 1), one.sharding_axis_names, 0, 1))
+    torch.manual_seed(4)
+    full = LlamaForCausalLM(one, dtype=torch.bfloat16, param_dtype=torch.bfloat16).to(dev).eval()
+    for p in full.parameters():
+        dist.broadcast(p.data, src=0)
+    cfg = LlamaConfig(sharding_axis_dims=(1, 1, 1, world, 1), **kw)
+    model = LlamaForCausalLM(cfg, dtype=torch.bfloat16, param_dtype=torch.bfloat16).to(dev).eval()
+    model.load_state_dict(shard_internal_state_for_tp(model, full.state_dict()))
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (200, 9, 77, 130)]
+    sp = SamplingParams(max_tokens=24, temperature=0.0, ignore_eos=True)
+    ref_eng = eSurge(full, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=256, num_pages=16)
+    ref = [o.outputs[0].token_ids for o in ref_eng.generate(prompts, sp)]
+    ref_eng.close()
+    eng = eSurge(model, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=256, num_pages=16)
+    assert eng.runner.tp_group is not None
+    got = [o.outputs[0].token_ids for o in eng.generate(prompts, sp)]
+    assert eng.runner.timings["graph_steps"] > 0
+    eng.close()
+    tpar.release_peer_buffers()
+    mine = torch.tensor(got, device=dev)
+    others = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(others, mine)
+    assert all(torch.equal(o, others[0]) for o in others), "ranks diverged"
+    same = sum(a == b for r, gt in zip(ref, got) for a, b in zip(r, gt))
+    assert same >= 0.8 * sum(len(r) for r in ref), (ref, got)
+    assert all(r[:4] == gt[:4] for r, gt in zip(ref, got)), (ref, got)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_esurge_tensor_parallel_engine(world):
+    _run(_tp_esurge_worker, world)

@@ -181,3 +181,29 @@ def test_streaming_decode_attention(Hq, Hkv, D, splits, window):
                                       window=window, sinks=None if sinks is None else sinks.cpu())
     err = (o.float().cpu() - ref.float()).abs().max().item()
     assert torch.allclose(o.float().cpu(), ref.float(), atol=2e-2, rtol=2e-2), err
+
+
+@pytest.mark.parametrize("B,H,ctx,splits", [(5, 16, [1, 31, 128, 700, 2049], 1), (3, 40, [513, 64, 900], 1),
+                                            (2, 16, [3000, 33], 4)])
+def test_latent_decode_attention_kernel(B, H, ctx, splits):
+    """Absorbed-form latent attention for decode steps: 576-wide scores and 512-wide value sums over the same paged
+    rows, against fp32 softmax attention over the gathered rows."""
+    from easydel_b200.ops import serving as S
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    pages_per = (max(ctx) + 127) // 128
+    P = B * pages_per + 1
+    pages = (torch.randn(P, 128, 1, 576, device=dev) * 0.5).to(torch.bfloat16)
+    perm = torch.randperm(P - 1, device=dev)[: B * pages_per] + 1
+    table = perm.view(B, pages_per).to(torch.int32)
+    lens = torch.tensor(ctx, dtype=torch.int32, device=dev)
+    q = (torch.randn(B, H, 576, device=dev) * 0.5).to(torch.bfloat16)
+    scale = 0.07
+    o = S.mla_decode_attention(q, pages, lens, table, scale=scale, num_splits=splits)
+    for b in range(B):
+        rows = pages[table[b].long()].reshape(-1, 576)[: ctx[b]].float()
+        s = (q[b].float() @ rows.t()) * scale
+        ref = torch.softmax(s, -1) @ rows[:, :512]
+        err = (o[b].float() - ref).abs().max() / ref.abs().max()
+        assert err < 2e-2, (b, float(err))

@@ -134,3 +134,39 @@ def test_engine_sliding_layers_hold_bounded_pages_and_match_generate(async_sched
         assert out == ref
     for m in eng.kv.managers:
         assert m.pool.num_free == m.pool.num_pages - 1    # everything was given back
+
+
+def test_data_parallel_router_keeps_pages_local_and_follows_cached_prefixes():
+    """Two engine replicas behind the data-parallel front: requests spread by load, a request whose prompt shares a
+    cached prefix goes to the replica that holds those pages, outputs equal plain generate()."""
+    from easydel_b200.inference.esurge.dp_router import DataParallelEngine, pages_per_dp_shard
+    from easydel_b200.modules.llama import LlamaConfig, LlamaForCausalLM
+
+    assert pages_per_dp_shard(64, 4) == 16 and pages_per_dp_shard(5, 4) is None
+    cfg = LlamaConfig(vocab_size=200, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=1024, eos_token_id=199)
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    engines = [eSurge(model, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=256, num_pages=16)
+               for _ in range(2)]
+    dp = DataParallelEngine(engines)
+    g = torch.Generator().manual_seed(5)
+    shared = torch.randint(0, 198, (260,), generator=g).tolist()
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    first = [shared + [1, 2, 3], torch.randint(0, 198, (40,), generator=g).tolist()]
+    rids = [dp.add_request(p, sp) for p in first]
+    assert {dp.shard_of(r) for r in rids} == {0, 1}               # spread by load
+    while dp.has_unfinished():
+        dp.step()
+    home = dp.shard_of(rids[0])
+    # the same 256-token prefix again: routed to the replica that cached it, and served from its pages
+    out = dp.generate([shared + [9, 8, 7, 6]], sp)[0]
+    rid = max(dp.owner, key=lambda r: int(r.split("-")[1]))
+    assert dp.shard_of(rid) == home and out.num_cached_tokens == 256
+    ref = model.generate(torch.tensor([shared + [9, 8, 7, 6]]), max_new_tokens=6, eos_token_id=-1).sequences[0, 264:]
+    assert out.outputs[0].token_ids == ref.tolist()
+    m = dp.get_metrics_summary()
+    assert m["replicas"] == 2 and sum(m["requests_routed"]) == 3 and m["requests_completed"] == 3
+    for e in engines:
+        assert e.pool.num_free == e.pool.num_pages - 1
+    dp.close()
