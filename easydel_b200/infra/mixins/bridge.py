@@ -47,4 +47,17 @@ class EasyBridgeMixin:
         return cls.from_pretrained(path, **kw)
 
     def can_generate(self) -> bool:
-        return False
+        """True for models with a language-model head and a ``generate`` method (causal LMs, sequence-to-sequence
+        and vision-language wrappers); such models get a ``generation_config.json`` next to their weights."""
+        if not callable(getattr(self, "generate", None)):
+            return False
+        lm = getattr(self, "language_model", self)
+        return any(hasattr(m, a) for m in (self, lm) for a in ("apply_lm_head", "lm_head", "proj_out"))
+
+    @staticmethod
+    def convert_hf_checkpoint_streaming(source: str, out: str, dtype=None, task=None, verbose: bool = False) -> dict:
+        """Hugging Face safetensors -> EasyDeL layout tensor by tensor, without building the model
+        (:func:`easydel_b200.io.streaming_convert.stream_hf_to_easydel`)."""
+        from ...io.streaming_convert import stream_hf_to_easydel
+
+        return stream_hf_to_easydel(source, out, dtype=dtype, task=task, verbose=verbose)

@@ -29,7 +29,9 @@ _lib.register("edl_allreduce_add_rmsnorm", _lib.i32, [_lib.vp, _lib.vp, _lib.i32
                                                       _lib.i32, _lib.vp, _lib.vp])
 
 ONE_SHOT_MAX_BYTES = 1 << 20     # up to here every rank reads every rank's whole partial (one flag round)
-TWO_SHOT_MAX_BYTES = 8 << 20     # up to here rank r reduces its own rows and stores them to every rank (two rounds)
+# up to here rank r reduces its own rows and stores them to every rank (two rounds); EDL_TP_TWO_SHOT=0 leaves
+# messages above the one-shot limit to NCCL
+TWO_SHOT_MAX_BYTES = (8 << 20) if __import__("os").environ.get("EDL_TP_TWO_SHOT", "1") != "0" else ONE_SHOT_MAX_BYTES
 _FLAG_BYTES = 256
 _lib.register("edl_allreduce_twoshot", _lib.i32, [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.vp,
                                                   _lib.vp, _lib.vp, _lib.f32, _lib.f32, _lib.i32, _lib.i32, _lib.i32,

@@ -26,8 +26,21 @@ _TOKENIZER_FILES = ("tokenizer.json", "tokenizer.model", "tokenizer_config.json"
 
 
 def convert(source: str, out: str, to: str = "easydel", dtype: str = "bf16", task: str = "causal-language-model",
-            quantize: str | None = None) -> str:
+            quantize: str | None = None, stream: bool = False) -> str:
     from ..infra.factory import TaskType
+
+    if stream:
+        # tensor by tensor, never holding the model: for checkpoints larger than host memory
+        if to != "easydel" or quantize:
+            raise ValueError("--stream converts Hugging Face safetensors to the EasyDeL layout, without quantisation")
+        from ..io.streaming_convert import stream_hf_to_easydel
+
+        os.makedirs(out, exist_ok=True)
+        stream_hf_to_easydel(source, out, dtype=_DTYPES[dtype], task=task)
+        for name in _TOKENIZER_FILES:
+            for src in glob.glob(os.path.join(source, name)):
+                shutil.copy2(src, os.path.join(out, os.path.basename(src)))
+        return out
     from ..modules.auto import auto_modeling as A
     from ..utils.parameters_transformation import internal_to_hf
 
@@ -65,6 +78,8 @@ def main(argv=None) -> int:
     ap.add_argument("--task", default="causal-language-model")
     ap.add_argument("--quantize", default=None)
     ap.add_argument("--batch", default=None, help="text file with one 'source out' pair per line")
+    ap.add_argument("--stream", action="store_true",
+                    help="convert tensor by tensor without building the model (checkpoints larger than host memory)")
     a = ap.parse_args(argv)
     jobs = []
     if a.batch:
@@ -77,7 +92,7 @@ def main(argv=None) -> int:
     failed = 0
     for src, dst in jobs:
         try:
-            print("converted", src, "->", convert(src, dst, a.to, a.dtype, a.task, a.quantize))
+            print("converted", src, "->", convert(src, dst, a.to, a.dtype, a.task, a.quantize, a.stream))
         except Exception as e:  # noqa: BLE001
             failed += 1
             print(f"FAILED {src}: {type(e).__name__}: {e}", file=sys.stderr)

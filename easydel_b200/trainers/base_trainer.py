@@ -86,7 +86,10 @@ class BaseTrainer:
         self.finetune = finetune
         self.mesh = getattr(self.model.config, "mesh", None)
         self.device = self.model.device
-        self._hooks: dict[str, list[tp.Callable]] = {"on_step_start": [], "on_step_end": []}
+        self._hooks: dict[str, list[tp.Callable]] = {"on_step_start": [], "on_step_end": [],
+                                                     "on_generation_preview": [], "on_benchmark": []}
+        self.last_previews: list[str] = []
+        self.last_benchmarks: dict = {}
         self._break_requested = False
         self._resumed_from: str | None = None
         self.loss_config = arguments.loss_config or LossConfig()
@@ -272,6 +275,7 @@ class BaseTrainer:
         pbar.update(start_step)
         interrupted = False
         last_saved = None
+        restore_signals = self._install_preemption_handlers()
         try:
             epoch = start_step // max(1, self.steps_per_epoch)
             while state.step < self.max_training_steps:
@@ -287,19 +291,31 @@ class BaseTrainer:
                     if a.evaluation_steps and self.dataloader_eval is not None and \
                             state.step % a.evaluation_steps == 0:
                         self.eval()
+                    if a.generation_interval and a.generation_prompts and state.step % a.generation_interval == 0:
+                        self.generate_previews(state.step)
+                    if a.benchmark_interval and state.step % a.benchmark_interval == 0:
+                        self.run_benchmarks(state.step)
                     limit = a.training_time_seconds
                     if limit is not None and time.time() - t_begin > limit:
                         raise EasyDeLTimerError("training_time_limit reached")
+                    if self._preempt_signal is not None:
+                        # a preemption notice (SIGTERM from the scheduler, or a signal named in the arguments):
+                        # the state of the step that just finished is written before the process is taken away
+                        # (easydel/trainers/base_trainer.py:5477-5522)
+                        if a.save_tpu_preemption_checkpoints and a.save_directory:
+                            last_saved = self._save_checkpoint(state.step)
+                        raise EasyDeLPreemptionSignal(f"signal {self._preempt_signal}")
                     if self._break_requested:
                         raise EasyDeLBreakRequest("break requested")
                 if not ran:
                     break
                 epoch += 1
-        except (EasyDeLTimerError, EasyDeLBreakRequest, KeyboardInterrupt) as e:
+        except (EasyDeLTimerError, EasyDeLBreakRequest, EasyDeLPreemptionSignal, KeyboardInterrupt) as e:
             interrupted = True
             if a.verbose and a.is_process_zero:
                 print(f"[trainer] stopping early at step {state.step}: {type(e).__name__}: {e}")
         finally:
+            restore_signals()
             pbar.close()
         if a.do_last_save and a.save_directory and (last_saved is None or not last_saved.endswith(f"run-{state.step}")):
             last_saved = self._save_checkpoint(state.step)
@@ -308,6 +324,114 @@ class BaseTrainer:
         self.logger.close()
         return TrainerOutput(state=state, mesh=self.mesh, last_save_file_name=last_saved, checkpoint_path=last_saved,
                              metrics_history=self.logger.history, interrupted=interrupted)
+
+    # ------------------------------------------------------------------ preemption, previews, benchmarks
+    _preempt_signal = None
+
+    def _install_preemption_handlers(self):
+        """SIGTERM (what cluster schedulers send before they take a node away) and SIGUSR1 set a flag that the loop
+        reads at the next step boundary. Returns a function that puts the previous handlers back. Only the main
+        thread can install handlers; elsewhere this is a no-op."""
+        import signal
+        import threading
+
+        self._preempt_signal = None
+        if threading.current_thread() is not threading.main_thread():
+            return lambda: None
+        previous = {}
+
+        def on_signal(signum, _frame):
+            self._preempt_signal = signal.Signals(signum).name
+
+        for name in getattr(self.arguments, "preemption_signals", None) or ("SIGTERM", "SIGUSR1"):
+            sig = getattr(signal, name, None)
+            if sig is None:
+                continue
+            try:
+                previous[sig] = signal.signal(sig, on_signal)
+            except (ValueError, OSError):
+                pass
+
+        def restore():
+            for sig, h in previous.items():
+                try:
+                    signal.signal(sig, h)
+                except (ValueError, OSError):
+                    pass
+
+        return restore
+
+    @torch.no_grad()
+    def generate_previews(self, step: int) -> list[str]:
+        """Greedy / sampled continuations of ``arguments.generation_prompts`` from the model being trained, logged
+        with the step (the reference's training-time generation previews,
+        easydel/trainers/base_trainer.py ``maybe_generate``)."""
+        a = self.arguments
+        tok = self.processing_class
+        if tok is None or not a.generation_prompts:
+            return []
+        was_training = self.model.training
+        self.model.eval()
+        texts = []
+        try:
+            for prompt in a.generation_prompts:
+                ids = tok(prompt, return_tensors="pt")["input_ids"] if isinstance(prompt, str) else \
+                    torch.tensor([list(prompt)])
+                kw = {}
+                if a.generation_do_sample:
+                    kw.update(do_sample=True, temperature=a.generation_temperature or 1.0,
+                              top_p=a.generation_top_p or 1.0, top_k=a.generation_top_k or 0,
+                              seed=a.generation_seed)
+                out = self.model.generate(ids.to(self.device), max_new_tokens=a.generation_max_new_tokens or 32, **kw)
+                new = out.sequences[0, ids.shape[1]:].tolist()
+                texts.append(tok.decode(new, skip_special_tokens=True) if hasattr(tok, "decode") else str(new))
+        finally:
+            self.model.train(was_training)
+        self.last_previews = texts
+        if a.can_log_metrics and hasattr(self.logger, "log_text"):
+            self.logger.log_text("generation_preview", texts, step)
+        for fn in self._hooks["on_generation_preview"]:
+            fn(self, step, texts)
+        return texts
+
+    def run_benchmarks(self, step: int) -> dict:
+        """lm-eval tasks named in ``arguments.benchmark_tasks`` through the eSurge adapter, when ``lm_eval`` is
+        installed (easydel/infra/elarge/benchmarking.py:40-615 drives the same harness); otherwise the
+        ``on_benchmark`` hooks alone run."""
+        a = self.arguments
+        results: dict = {}
+        tasks = getattr(a, "benchmark_tasks", None)
+        if tasks:
+            try:
+                import lm_eval  # noqa: F401
+
+                from ..inference.esurge import eSurge
+                from ..inference.evaluations.esurge_eval import eSurgeLMEvalAdapter, run_lm_eval
+
+                was_training = self.model.training
+                self.model.eval()
+                eng = eSurge(self.model, tokenizer=self.processing_class, max_model_len=a.max_length or 2048,
+                             max_num_seqs=a.esurge_max_num_seqs or 16,
+                             hbm_utilization=a.esurge_hbm_utilization or 0.3)
+                try:
+                    results = run_lm_eval(eSurgeLMEvalAdapter(eng, self.processing_class), tasks,
+                                          limit=getattr(a, "benchmark_limit", None))
+                finally:
+                    eng.close()
+                    self.model.train(was_training)
+            except ImportError:
+                if a.verbose and a.is_process_zero:
+                    print("[trainer] lm_eval is not installed: benchmark tasks skipped")
+        for fn in self._hooks["on_benchmark"]:
+            out = fn(self, step)
+            if isinstance(out, dict):
+                results.update(out)
+        if results and a.can_log_metrics:
+            flat = {f"benchmark/{k}": v for k, v in results.items() if isinstance(v, (int, float))}
+            if flat:
+                self.logger.log(flat, step)
+        self.last_benchmarks = results
+        return results
 
     def _epoch_iterator(self, epoch: int, skip: int = 0):
         loader = self.dataloader_train

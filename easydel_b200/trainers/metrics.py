@@ -199,6 +199,16 @@ class MetricsLogger:
         if self._wandb is not None:
             self._wandb.log(metrics, step=step)
 
+    def log_text(self, key: str, texts: list[str], step: int) -> None:
+        """Free text (generation previews) beside the scalar metrics."""
+        self.history.append({"step": step, key: list(texts)})
+        if self._jsonl is not None:
+            self._jsonl.write(json.dumps({"step": step, key: list(texts)}) + "\n")
+            self._jsonl.flush()
+        if self._tb is not None:
+            for i, t in enumerate(texts):
+                self._tb.add_text(f"{key}/{i}", t, step)
+
     def close(self) -> None:
         if self._jsonl is not None:
             self._jsonl.close()

@@ -114,6 +114,9 @@ class TrainingArguments:
     generation_prompts: list = field(default_factory=list)
     generation_seed: int | None = None
     benchmark_interval: int | None = None
+    benchmark_tasks: list | None = None          # lm-eval task names run every ``benchmark_interval`` steps
+    benchmark_limit: int | None = None
+    preemption_signals: tuple = ("SIGTERM", "SIGUSR1")   # signals that trigger a checkpoint and a clean stop
     use_esurge_generation: bool = True
     esurge_hbm_utilization: float | None = None
     esurge_max_num_seqs: int | None = None

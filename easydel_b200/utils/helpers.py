@@ -63,6 +63,8 @@ ENV_FLAGS: dict[str, EnvFlag] = {f.name: f for f in (
     EnvFlag("EDL_GEMM_PAIR", True, "bool", "use the two-CTA (cta_group::2) GEMM for large products"),
     EnvFlag("EDL_GEMM_PAIR_SPLITK", False, "bool", "plan the two-slice split-K form of the CTA-pair GEMM for skinny "
             "products (off: measured no faster than the 128-wide kernel)"),
+    EnvFlag("EDL_TP_TWO_SHOT", True, "bool", "tensor-parallel decode all-reduces of 1-8 MiB run the two-shot peer-memory "
+            "kernel (off: NCCL)"),
     EnvFlag("EDL_ESURGE_CUDA_GRAPHS", True, "bool", "replay decode steps from CUDA graphs"),
     EnvFlag("EDL_NVTX", False, "bool", "emit NVTX ranges around trainer steps, engine steps and layers"),
     EnvFlag("EASURGE_MAX_SCHEDULER_ERRORS", 3, "int", "consecutive engine-step errors before in-flight requests fail"),

@@ -131,3 +131,51 @@ def test_hf_safetensors_import(tmp_path):
     ids = torch.randint(0, 256, (1, 8))
     with torch.no_grad():
         assert torch.allclose(m(input_ids=ids).logits, m2(input_ids=ids).logits, atol=1e-6)
+
+
+def test_streaming_hf_conversion_matches_in_memory_load(tmp_path):
+    """A sharded Hugging Face safetensors checkpoint (dense and MoE) converted tensor by tensor: the EasyDeL
+    directory loads into the same logits as loading the safetensors directly, and no more than one stacked expert
+    projection was ever held."""
+    import json
+    import os
+
+    from safetensors.torch import save_file
+
+    from easydel_b200.infra.factory import TaskType, registry
+    from easydel_b200.io.streaming_convert import LazySafetensors, stream_hf_to_easydel
+    from easydel_b200.utils.parameters_transformation import internal_to_hf
+    import easydel_b200.modules  # noqa: F401
+
+    for mtype, extra in (("llama", {}), ("qwen3_moe", dict(num_experts=4, num_experts_per_tok=2,
+                                                          moe_intermediate_size=32, head_dim=16))):
+        cfg = registry.get_config(mtype)(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                         num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64,
+                                         **extra)
+        reg = registry.get_module_registration(TaskType.CAUSAL_LM, mtype)
+        torch.manual_seed(0)
+        model = reg.module(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+        assert model.can_generate()
+        src = tmp_path / f"{mtype}_hf"
+        os.makedirs(src)
+        sd = {k: v.detach().contiguous().clone() for k, v in internal_to_hf(model).items()}
+        keys = sorted(sd)
+        half = len(keys) // 2
+        shards = {"model-00001-of-00002.safetensors": keys[:half], "model-00002-of-00002.safetensors": keys[half:]}
+        for fn, ks in shards.items():
+            save_file({k: sd[k] for k in ks}, str(src / fn), metadata={"format": "pt"})
+        with open(src / "model.safetensors.index.json", "w") as f:
+            json.dump({"metadata": {}, "weight_map": {k: fn for fn, ks in shards.items() for k in ks}}, f)
+        model.config.save_pretrained(str(src))
+        lazy = LazySafetensors(str(src))
+        assert len(lazy) == len(sd) and lazy.reads == 0
+        lazy.close()
+        out = tmp_path / f"{mtype}_ed"
+        stats = stream_hf_to_easydel(str(src), str(out), dtype=torch.float32)
+        biggest = max(v.numel() * 4 for v in model.state_dict().values())
+        assert stats["tensors"] > 0 and stats["peak_tensor_bytes"] <= biggest
+        assert os.path.exists(out / "tensorstore_index.json") and os.path.exists(out / "config.json")
+        back = reg.module.from_pretrained(str(out), dtype=torch.float32, device="cpu")
+        ids = torch.randint(0, 128, (1, 12), generator=torch.Generator().manual_seed(1))
+        with torch.no_grad():
+            assert torch.allclose(back(input_ids=ids).logits, model(input_ids=ids).logits, atol=1e-5)
