@@ -309,3 +309,115 @@ def quantize_kv_int8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
 
 def dequantize_kv_int8(codes: torch.Tensor, scales: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
     return (codes.float() * scales.float()).to(dtype)
+
+
+# ------------------------------------------------------------------------------------------------- QAT
+class _StraightThrough(torch.autograd.Function):
+    """Forward: the weight as it comes back from quantise -> dequantise; backward: identity."""
+
+    @staticmethod
+    def forward(ctx, w, cfg):
+        w2 = w.reshape(-1, w.shape[-1])
+        return dequantize_reference(quantize(w2.detach(), cfg)).to(w.dtype).view(w.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def straight_through(w: torch.Tensor, dtype: str | QuantizationType | EasyDeLQuantizationConfig = "nf4",
+                     block_size: int | None = None) -> torch.Tensor:
+    """Fake-quantised weight for quantisation-aware training: the value the quantised format would hold, with the
+    gradient passed through unchanged (the reference's ``straight_through``,
+    easydel/layers/quantization/_straight_through.py)."""
+    if isinstance(dtype, EasyDeLQuantizationConfig):
+        cfg = dtype
+    else:
+        cfg = EasyDeLQuantizationConfig(getattr(dtype, "value", dtype), block_size=block_size)
+    return _StraightThrough.apply(w, cfg)
+
+
+def straight_through_nf4(w, block_size: int | None = None):
+    return straight_through(w, "nf4", block_size)
+
+
+def straight_through_8bit(w, block_size: int | None = None):
+    return straight_through(w, "int8", block_size)
+
+
+def straight_through_mxfp4(w):
+    return straight_through(w, "mxfp4")
+
+
+def straight_through_mxfp8(w):
+    return straight_through(w, "mxfp8")
+
+
+def straight_through_nvfp8(w):
+    return straight_through(w, "nvfp8")
+
+
+def straight_through_1bit(w: torch.Tensor) -> torch.Tensor:
+    """sign(w) scaled by the mean magnitude of each row, gradient passed through."""
+    q = torch.sign(w) * w.abs().mean(-1, keepdim=True)
+    return w + (q - w).detach()
+
+
+class QATLinear(nn.Module):
+    """Wraps a linear layer for quantisation-aware training: the forward product uses the fake-quantised weight, the
+    optimizer keeps updating the full-precision one. ``EasyQuantizer.apply_qat`` installs it; ``convert`` turns the
+    trained layer into a :class:`QuantizedLinear`."""
+
+    def __init__(self, inner: nn.Module, config: EasyDeLQuantizationConfig):
+        super().__init__()
+        self.inner, self.config = inner, config
+
+    @property
+    def weight(self):
+        return self.inner.weight
+
+    @property
+    def bias(self):
+        return getattr(self.inner, "bias", None)
+
+    def forward(self, x, *args, **kw):
+        from ..ops import functional as F
+
+        w = straight_through(self.inner.weight, self.config)
+        y = F.linear(x, w, getattr(self.inner, "bias", None))
+        return y
+
+    def convert(self) -> QuantizedLinear:
+        return QuantizedLinear(quantize(self.inner.weight.detach(), self.config), getattr(self.inner, "bias", None),
+                               self.inner)
+
+
+def _apply_qat(self, model: nn.Module) -> nn.Module:
+    """Replaces every linear the quantiser would quantise by a :class:`QATLinear` around it (plain, non-parallel
+    linears: a tensor-parallel layer keeps its own forward)."""
+    n = 0
+    for name, mod in list(model.named_modules()):
+        if not self._wanted(name, mod) or isinstance(mod, QATLinear) or getattr(mod, "tp_size", 1) > 1:
+            continue
+        parent_name, _, leaf = name.rpartition(".")
+        parent = model.get_submodule(parent_name) if parent_name else model
+        if isinstance(parent, QATLinear):
+            continue
+        setattr(parent, leaf, QATLinear(mod, self.config))
+        n += 1
+    model.qat_summary = {"modules": n, "format": self.config.dtype}
+    return model
+
+
+def _finalize_qat(self, model: nn.Module) -> nn.Module:
+    """Turns the :class:`QATLinear` wrappers of a trained model into quantised linears."""
+    for name, mod in list(model.named_modules()):
+        if isinstance(mod, QATLinear):
+            parent_name, _, leaf = name.rpartition(".")
+            parent = model.get_submodule(parent_name) if parent_name else model
+            setattr(parent, leaf, mod.convert())
+    return model
+
+
+EasyQuantizer.apply_qat = _apply_qat
+EasyQuantizer.finalize_qat = _finalize_qat

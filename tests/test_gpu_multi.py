@@ -123,7 +123,7 @@ def _twoshot_worker(rank, world):
         assert (plain.float() - y).abs().max() < 6e-2 * y.abs().max()
         assert (cur.float() - xr).abs().max() < 6e-2 * xr.abs().max(), "the residual rows survived the plain reduce"
         # every rank holds bit-identical results
-        mine = torch.cat([cur.reshape(-1), h.reshape(-1), plain.reshape(-1)]).view(torch.int16)
+        mine = torch.cat([cur.reshape(-1), h.reshape(-1), plain.reshape(-1)]).view(torch.uint8)
         other = mine.clone()
         dist.broadcast(other, src=0)
         assert torch.equal(mine, other)

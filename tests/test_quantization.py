@@ -60,3 +60,40 @@ def test_cuda_kernels_match_reference(fmt, M):
     y = quantized_matmul(x, q, bias)
     ref = x.float() @ ref_w.t() + bias.float()
     assert (y.float() - ref).abs().max() < 2e-2 * ref.abs().max().clamp_min(1.0)
+
+
+def test_straight_through_and_qat_linear():
+    """Fake quantisation for training: forward value = quantise -> dequantise, gradient = identity; a wrapped model
+    trains its full-precision weights and converts to quantised linears whose output it already produced."""
+    import torch
+    from torch import nn
+
+    from easydel_b200.layers import quantization as Q
+
+    torch.manual_seed(0)
+    w = torch.randn(8, 256, requires_grad=True)
+    wq = Q.straight_through(w, "nf4")
+    ref = Q.dequantize_reference(Q.quantize(w.detach(), "nf4"))
+    assert torch.allclose(wq, ref) and not torch.equal(wq, w)
+    (wq * torch.arange(256.0)).sum().backward()
+    assert torch.allclose(w.grad, torch.arange(256.0).expand(8, 256))
+    for fn in (Q.straight_through_8bit, Q.straight_through_mxfp4, Q.straight_through_mxfp8, Q.straight_through_nvfp8):
+        assert fn(w).shape == w.shape
+    b = Q.straight_through_1bit(w)
+    assert torch.allclose(b.abs(), w.detach().abs().mean(-1, keepdim=True).expand_as(w))
+
+    model = nn.Sequential(nn.Linear(256, 128), nn.ReLU(), nn.Linear(128, 8))
+    quantizer = Q.EasyQuantizer("nf4", pattern=r".*")
+    quantizer.apply_qat(model)
+    assert model.qat_summary["modules"] == 2 and isinstance(model[0], Q.QATLinear)
+    x = torch.randn(16, 256)
+    before = model[0].inner.weight.detach().clone()
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    loss = model(x).pow(2).mean()
+    loss.backward()
+    opt.step()
+    assert not torch.equal(model[0].inner.weight, before)          # the full-precision weight moved
+    y_qat = model(x)
+    quantizer.finalize_qat(model)
+    assert isinstance(model[0], Q.QuantizedLinear)
+    assert torch.allclose(model(x), y_qat, atol=1e-4)
