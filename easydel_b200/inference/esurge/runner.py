@@ -368,6 +368,13 @@ class ModelRunner:
             d_fixpos, d_fixslot = self._dviews[8][:nfix].long(), self._dviews[9][:nfix].long()
             self._dviews[0].index_copy_(0, d_fixpos, self._last_tokens.index_select(0, d_fixslot).to(torch.int32))
         t1 = time.perf_counter()
+        from ...utils.helpers import nvtx_range
+
+        with nvtx_range(f"esurge_step_B{B}_T{T}"):
+            tokens, t2, t3 = self._run_model(out, sched, B, Bp, T, max_q, decode_only, any_pen, any_random, mm_rows)
+        return self._finish_launch(sched, B, tokens, t0, t1, t2, t3)
+
+    def _run_model(self, out, sched, B, Bp, T, max_q, decode_only, any_pen, any_random, mm_rows):
         if self.use_graphs and decode_only:
             if self.time_decode_steps and Bp in self._graphs:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -408,6 +415,9 @@ class ModelRunner:
                 S.count_update(self.counts, tokens, torch.tensor([s.request.slot for s in sched], dtype=torch.int32,
                                                                   device=self.device))
         t3 = time.perf_counter()
+        return tokens, t2, t3
+
+    def _finish_launch(self, sched, B, tokens, t0, t1, t2, t3):
         # keep every slot's newest token on the device, and start the step's only device->host read
         self._last_tokens.index_copy_(0, self._dviews[7][:B].long(), tokens[:B].to(torch.int64))
         buf = self._tok_host[self._launches & 1]

@@ -228,3 +228,14 @@ LOSS_MAPPING = {
     "ForQuestionAnswering": ForQuestionAnsweringLoss,
     "ForTokenClassification": ForTokenClassification,
 }
+
+
+# the functional variants and the strategy objects live in their own module and are part of this one's surface
+from .loss_functions import (SLNF, BaseLossStrategy, CausalLMLossStrategy, FunctionalLossStrategy,  # noqa: E402,F401
+                             LossForwardPlan, compute_weighted_cross_entropy,
+                             compute_weighted_cross_entropy_and_accuracy,
+                             convert_special_loss_normalizing_factor_to_enum, cross_entropy_blockwise_logits,
+                             cross_entropy_loss_and_accuracy, cross_entropy_with_logits, dynamic_cross_entropy_loss,
+                             fixed_cross_entropy, get_factor_and_weight, onehot, resolve_loss_strategy,
+                             sigmoid_cross_entropy_with_logits, sparse_cross_entropy_chunked_tokens,
+                             sparse_cross_entropy_chunked_vocab)

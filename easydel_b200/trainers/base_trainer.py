@@ -456,8 +456,11 @@ class BaseTrainer:
         if a.ids_to_pop_from_dataset:
             for k in a.ids_to_pop_from_dataset:
                 batch.pop(k, None)
-        dev_batch = _to_device(batch, self.device)
-        loss, grad_norm, aux = self.training_step(dev_batch)
+        from ..utils.helpers import nvtx_range
+
+        with nvtx_range(f"train_step_{state.step + 1}"):
+            dev_batch = _to_device(batch, self.device)
+            loss, grad_norm, aux = self.training_step(dev_batch)
         step = state.step
         need_report = (step % max(1, a.report_steps) == 0) or step == self.max_training_steps or \
             a.progress_bar_type == "json"
