@@ -170,3 +170,155 @@ class SampleOutput(ModelOutput):
 class BeamSearchOutput(ModelOutput):
     sequences: torch.Tensor | None = None
     scores: torch.Tensor | None = None
+
+
+# ---- the remaining output types of the reference's module (same field names; only the fields differ) ----------------
+@dataclass
+class EmbeddingInfo(ModelOutput):
+    """What ``get_embedding_info`` reports about a model's embedding tables."""
+
+    vocab_size: int | None = None
+    hidden_size: int | None = None
+    tie_word_embeddings: bool | None = None
+    embedding_names: tuple | None = None
+
+
+@dataclass
+class AttentionLayerOutput(ModelOutput):
+    attention_output: torch.Tensor | None = None
+    attention_weight: torch.Tensor | None = None
+    cache_view: tp.Any = None
+
+
+@dataclass
+class EncoderLayerOutput(ModelOutput):
+    hidden_states: torch.Tensor | None = None
+    residual_states: torch.Tensor | None = None
+    attention_weight: torch.Tensor | None = None
+
+
+@dataclass
+class DecoderLayerOutput(ModelOutput):
+    hidden_states: torch.Tensor | None = None
+    residual_states: torch.Tensor | None = None
+    attention_weight: torch.Tensor | None = None
+    cross_attention_weight: torch.Tensor | None = None
+    router_logits: torch.Tensor | None = None
+    gate_loss: torch.Tensor | None = None
+    cache_view: tp.Any = None
+
+
+@dataclass
+class BaseModelOutputWithNoAttention(ModelOutput):
+    last_hidden_state: torch.Tensor | None = None
+    hidden_states: tuple | None = None
+
+
+@dataclass
+class BaseModelOutputWithPoolingAndNoAttention(BaseModelOutputWithNoAttention):
+    pooler_output: torch.Tensor | None = None
+
+
+@dataclass
+class ImageClassifierOutputWithNoAttention(ModelOutput):
+    loss: torch.Tensor | None = None
+    logits: torch.Tensor | None = None
+    hidden_states: tuple | None = None
+
+
+@dataclass
+class BaseModelOutputWithPoolingAndCrossAttentions(BaseModelOutput):
+    pooler_output: torch.Tensor | None = None
+    cross_attentions: tuple | None = None
+
+
+@dataclass
+class BaseModelOutputWithPastAndCrossAttentions(BaseModelOutput):
+    cross_attentions: tuple | None = None
+
+
+@dataclass
+class CausalLMOutputWithCrossAttentions(ModelOutput):
+    loss: torch.Tensor | None = None
+    logits: torch.Tensor | None = None
+    last_hidden_state: torch.Tensor | None = None
+    hidden_states: tuple | None = None
+    attentions: tuple | None = None
+    cross_attentions: tuple | None = None
+    past_key_values: tp.Any = None
+
+
+@dataclass
+class MaskedLMOutput(ModelOutput):
+    loss: torch.Tensor | None = None
+    logits: torch.Tensor | None = None
+    last_hidden_state: torch.Tensor | None = None
+    hidden_states: tuple | None = None
+    attentions: tuple | None = None
+
+
+@dataclass
+class NextSentencePredictorOutput(ModelOutput):
+    loss: torch.Tensor | None = None
+    logits: torch.Tensor | None = None
+    hidden_states: tuple | None = None
+    attentions: tuple | None = None
+
+
+@dataclass
+class Seq2SeqSequenceClassifierOutput(ModelOutput):
+    loss: torch.Tensor | None = None
+    logits: torch.Tensor | None = None
+    past_key_values: tp.Any = None
+    decoder_hidden_states: tuple | None = None
+    decoder_attentions: tuple | None = None
+    cross_attentions: tuple | None = None
+    encoder_last_hidden_state: torch.Tensor | None = None
+    encoder_hidden_states: tuple | None = None
+    encoder_attentions: tuple | None = None
+
+
+@dataclass
+class MultipleChoiceModelOutput(ModelOutput):
+    loss: torch.Tensor | None = None
+    logits: torch.Tensor | None = None
+    hidden_states: tuple | None = None
+    attentions: tuple | None = None
+
+
+@dataclass
+class Seq2SeqQuestionAnsweringModelOutput(ModelOutput):
+    loss: torch.Tensor | None = None
+    start_logits: torch.Tensor | None = None
+    end_logits: torch.Tensor | None = None
+    past_key_values: tp.Any = None
+    decoder_hidden_states: tuple | None = None
+    decoder_attentions: tuple | None = None
+    cross_attentions: tuple | None = None
+    encoder_last_hidden_state: torch.Tensor | None = None
+    encoder_hidden_states: tuple | None = None
+    encoder_attentions: tuple | None = None
+
+
+@dataclass
+class MambaOutput(ModelOutput):
+    last_hidden_state: torch.Tensor | None = None
+    cache_params: tp.Any = None
+    hidden_states: tuple | None = None
+
+
+@dataclass
+class MambaCausalLMOutput(ModelOutput):
+    loss: torch.Tensor | None = None
+    logits: torch.Tensor | None = None
+    cache_params: tp.Any = None
+    last_hidden_state: torch.Tensor | None = None
+    hidden_states: tuple | None = None
+
+
+@dataclass
+class CLIPTextModelOutput(ModelOutput):
+    text_embeds: torch.Tensor | None = None
+    last_hidden_state: torch.Tensor | None = None
+    hidden_states: tuple | None = None
+    attentions: tuple | None = None

@@ -128,8 +128,15 @@ class MoEBlock(nn.Module):
                  router_jitter_eps: float = 0.01, routing_strategy: str | None = None,
                  capacity_factor: float | None = None,
                  load_balancing_strategy: str = MoeLoadBalancingStrategy.STANDARD, lbl_coef: float | None = None,
-                 rzl_coef: float | None = None):
+                 rzl_coef: float | None = None, expert_tensor_mode: bool = False):
         super().__init__()
+        # Expert tensor mode (the reference's ``use_expert_tensor_mode``, easydel/layers/linears/_linear_moe.py:113,
+        # :330): the experts are spread over the TENSOR-parallel group instead of an expert-parallel one. Every rank
+        # of that group sees the same tokens, so nothing is exchanged: a rank runs its own experts on all tokens and
+        # the partial outputs are summed over the group.
+        self.expert_tensor_mode = bool(expert_tensor_mode and tp_size > 1 and ep_size == 1)
+        if self.expert_tensor_mode:
+            ep_size, ep_rank, ep_group = tp_size, tp_rank, tp_group
         # None = top-k with (TOP_K) or without (TOP_K_NDIV) renormalisation, as ``norm_topk_prob`` says
         self.routing_strategy = getattr(routing_strategy, "value", routing_strategy)
         self.capacity_factor = capacity_factor     # None = dropless
@@ -157,9 +164,10 @@ class MoEBlock(nn.Module):
                                    expert_init_std, "row", bias=expert_bias)
         if ep_size > 1:   # these weights differ per rank: their gradients are not summed over the group
             for lin in (self.gate_up_proj, self.down_proj):
-                lin.weight._ep_local = True
-                if lin.bias is not None:
-                    lin.bias._ep_local = True
+                for p in (lin.weight, lin.bias):
+                    if p is not None:
+                        p._ep_local = True
+                        p._ep_over_tp = self.expert_tensor_mode   # the group they differ over is the tp group
         self.shared_experts = None
         self.shared_expert_gate = None
         if shared_intermediate_size > 0:
@@ -292,6 +300,24 @@ class MoEBlock(nn.Module):
                 y = G.moe_ffn(x_in, self.gate_up_proj.weight, self.down_proj.weight, one, idx.reshape(T * k, 1),
                               self.act, b_gate_up=self.gate_up_proj.bias, b_down=self.down_proj.bias)
             y = y.view(T, k, -1).sum(1)
+        elif self.expert_tensor_mode:
+            from ..parallel import tp as tpar
+
+            # same tokens on every rank: local experts on all of them, partial outputs summed over the group; the
+            # input and routing-weight gradients are the sums of the ranks' contributions
+            xin, win = tpar.copy_to_tp(x2, self.ep_group), tpar.copy_to_tp(w, self.ep_group)
+            off = self.ep_rank * self.num_local_experts
+            if x2.is_cuda:
+                part = G.moe_ffn(xin, self.gate_up_proj.weight, self.down_proj.weight, win, idx, self.act,
+                                 b_gate_up=self.gate_up_proj.bias, b_down=self.down_proj.bias, expert_offset=off)
+            else:   # reference path: local indices, pairs owned by other ranks get weight zero
+                local = idx - off
+                mine = (local >= 0) & (local < self.num_local_experts)
+                part = G.moe_ffn(xin, self.gate_up_proj.weight, self.down_proj.weight, win * mine.to(win.dtype),
+                                 local.clamp(0, self.num_local_experts - 1), self.act,
+                                 b_gate_up=self.gate_up_proj.bias, b_down=self.down_proj.bias)
+            y = tpar._ReduceFromTP.apply(part, self.ep_group) if torch.is_grad_enabled() else \
+                tpar.all_reduce(part, self.ep_group)
         elif self.ep_size > 1:
             from ..parallel import ep as epar
 

@@ -250,7 +250,8 @@ class DecoderLayer(nn.Module):
                                 router_bias=moe.router_bias, shared_intermediate_size=moe.shared_intermediate_size,
                                 shared_gate=moe.shared_gate, dtype=dtype, init_std=spec.init_std,
                                 expert_init_std=moe.expert_init_std, ep_size=ep_size, ep_rank=ep_rank,
-                                ep_group=ep_group, tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group)
+                                ep_group=ep_group, tp_size=tp_size, tp_rank=tp_rank, tp_group=tp_group,
+                                expert_tensor_mode=bool(getattr(config, "use_expert_tensor_mode", False)))
         elif spec.mlp == "gated":
             self.mlp = GatedMLP(spec.hidden_size, spec.intermediate_size, spec.act, spec.mlp_bias, dtype,
                                 spec.init_std, tp_size, tp_rank, tp_group)

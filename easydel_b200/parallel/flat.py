@@ -139,7 +139,10 @@ class FlatParams:
         out: dict[str, list[tuple[int, int]]] = {"tp": [], "ep": []}
         for n, o, sz, _, _ in self.entries:
             p = self.params[n]
-            kind = "ep" if getattr(p, "_ep_local", False) else owner.get(id(p))
+            if getattr(p, "_ep_local", False):
+                kind = "tp" if getattr(p, "_ep_over_tp", False) else "ep"    # expert tensor mode: spread over tp
+            else:
+                kind = owner.get(id(p))
             if kind is None:
                 continue
             runs = out[kind]

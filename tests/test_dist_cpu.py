@@ -517,3 +517,37 @@ def _tp_esurge_worker(rank, world):
 
 def test_esurge_tensor_parallel_matches_unsharded_generate():
     _run(_tp_esurge_worker, 2)
+
+
+def _expert_tensor_worker(rank, world):
+    """Expert tensor mode: experts spread over the tensor-parallel group, identical tokens on every rank, partial
+    outputs summed. Output, input gradient, router gradient and the local experts' gradients equal the unsharded
+    block's."""
+    from easydel_b200.layers.moe import MoEBlock
+
+    torch.manual_seed(0)
+    H, F, E, k, T = 16, 32, 2 * world, 2, 10
+    full = MoEBlock(H, F, E, k, dtype=torch.float32)
+    etm = MoEBlock(H, F, E, k, dtype=torch.float32, tp_size=world, tp_rank=rank, tp_group=dist.group.WORLD,
+                   expert_tensor_mode=True)
+    assert etm.expert_tensor_mode and etm.num_local_experts == 2 and etm.gate_up_proj.weight._ep_over_tp
+    El = E // world
+    with torch.no_grad():
+        etm.gate.weight.copy_(full.gate.weight)
+        etm.gate_up_proj.weight.copy_(full.gate_up_proj.weight[rank * El:(rank + 1) * El])
+        etm.down_proj.weight.copy_(full.down_proj.weight[rank * El:(rank + 1) * El])
+    x0 = torch.randn(1, T, H)
+    xa = x0.clone().requires_grad_(True)
+    ya, _ = full(xa)
+    ya.square().sum().backward()
+    xb = x0.clone().requires_grad_(True)
+    yb, _ = etm(xb)
+    yb.square().sum().backward()
+    assert torch.allclose(yb, ya, atol=1e-5)
+    assert torch.allclose(xb.grad, xa.grad, atol=1e-5)
+    assert torch.allclose(etm.gate.weight.grad, full.gate.weight.grad, atol=1e-5)
+    assert torch.allclose(etm.down_proj.weight.grad, full.down_proj.weight.grad[rank * El:(rank + 1) * El], atol=1e-5)
+
+
+def test_expert_tensor_mode_matches_unsharded_block():
+    _run(_expert_tensor_worker, 2)
