@@ -3,9 +3,10 @@
 //   edl_gemm_reduce_scatter : every rank holds A[M, K_r] and W[N, K_r] (the reduction dimension is sharded, a
 //       row-parallel linear). Each rank computes its partial product tile by tile on the tensor cores and the
 //       epilogue stores every finished tile straight into the staging area of the rank that owns those rows
-//       (peer stores over NVLink while the next tile's MMAs run). When the last tile for a destination is out,
-//       a release flag is written to it. The same kernel then waits (bounded) for the flags of all sources and
-//       sums the staged partials of its own row shard: out[M/n, N] = sum_r partial_r (+ residual).
+//       (peer stores over NVLink while the next tile's MMAs run). When the last tile of a 128-row block is out, a
+//       release flag for that block is written to its owner. The owner sums the staged partials of a block as soon
+//       as every source has published it (a work queue served by one spare warp per CTA from the start and by the
+//       epilogue warps once their tiles are done): out[M/n, N] = sum_r partial_r (+ residual).
 //
 //   edl_allgather_gemm : A is sharded by rows across ranks (sequence parallel activations or FSDP weight rows);
 //       C[n*Ms, N] = gather(A) * W^T. One extra warp in every CTA pulls its share of the peers' shards into a local
@@ -49,10 +50,13 @@ struct CollInfo {
   int tiles_per_shard;   // 128-row tiles in one rank's row shard
   int flags;
   int b_mn;              // 1: B is stored [K, N] (N contiguous) as in a data-gradient GEMM; 0: [N, K]
+  int rs_pieces;         // RS: column pieces per 128-row block in the reduction work queue
+  int rs_piece_vecs;     // RS: 16-byte vectors per row in one piece
   long long spin_limit;  // clock cycles a wait on a peer may take
   void* peer[MAX_RANKS];  // RS: staging base on every rank (this call's slot). AG: A shard base on every rank
-  int* flag[MAX_RANKS];   // RS: flag words on every rank (this call's slot), one per source rank
-  int* counters;          // local, zeroed before launch. RS: [nranks]; AG: [nranks * tiles_per_shard]
+  int* flag[MAX_RANKS];   // RS: flag words on every rank (this call's slot): [source rank][row block]
+  int* counters;          // local, zeroed before launch. RS: [nranks * tiles_per_shard] arrivals + 1 queue head;
+                          // AG: [nranks * tiles_per_shard]
   void* gathered;         // AG: local [nranks * Ms, K]
   const __nv_bfloat16* residual;  // RS: optional [Ms, N]
   const __nv_bfloat16* bias;      // optional [N]
@@ -162,6 +166,108 @@ __device__ __forceinline__ Tile decode(int t, int tiles_n, const CollInfo& ci) {
   return o;
 }
 
+// Reduce-scatter side of MODE_RS. The rows of this rank's shard are cut into units of (128-row block, column
+// piece); any warp may take the next unit from a grid-wide counter, waits (bounded) until every source rank has
+// published that row block (one flag per source and row block, raised when all of the block's tiles are stored),
+// and sums the sources' staged partials in rank order (+ residual, + bias). The spare warp of every CTA starts on
+// the queue at once, so the blocks that arrive early are reduced while the tensor cores are still busy; the
+// epilogue warps join when their tiles are done.
+__device__ __forceinline__ void rs_reduce_units(const CollInfo& ci, __nv_bfloat16* __restrict__ Cout, int N, int lane,
+                                                volatile int* abort_flag, int* status) {
+  const int tps = ci.tiles_per_shard;
+  const int pieces = ci.rs_pieces;
+  const int piece_vecs = ci.rs_piece_vecs;          // 16-byte vectors per row in one piece
+  const long long vec_per_row = N / 8;
+  const long long slot_elems = (long long)tps * BM * N;
+  const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(ci.peer[ci.rank]);
+  const bool has_res = (ci.flags & CF_RESIDUAL) && ci.residual != nullptr;
+  const bool rs_bias = (ci.flags & CF_BIAS) && ci.bias != nullptr;
+  int* queue = ci.counters + ci.nranks * tps;
+  const int* mine = ci.flag[ci.rank];
+  const int total_units = tps * pieces;
+  while (true) {
+    int unit = 0;
+    if (lane == 0) unit = atomicAdd(queue, 1);
+    unit = __shfl_sync(0xffffffffu, unit, 0);
+    if (unit >= total_units) return;
+    const int tm = unit / pieces, pc = unit - tm * pieces;
+    bool ready = true;
+    if (lane == 0) {
+      for (int s = 0; s < ci.nranks && ready; ++s) {
+        const long long t0 = clock64();
+        uint32_t it = 0;
+        while (ld_acquire_sys(mine + s * tps + tm) < ci.epoch) {
+          __nanosleep(100);
+          if ((++it & 0x3f) == 0 && (*abort_flag || clock64() - t0 > ci.spin_limit)) {
+            if (!*abort_flag) {
+              *abort_flag = 1;
+              if (status) atomicCAS(status, 0, EDL_TIMEOUT_PEER_FLAG);
+            }
+            ready = false;
+            break;
+          }
+        }
+      }
+    }
+    ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+    if (!ready) return;
+    const long long v_lo = (long long)pc * piece_vecs;
+    const int nv = (int)min((long long)piece_vecs, vec_per_row - v_lo);   // vectors of this piece in a row
+    if (nv <= 0) continue;
+    const int total = BM * nv;
+    // two independent vectors per lane and source keep enough loads in flight for one warp to stream
+    for (int i0 = lane; i0 < total; i0 += 64) {
+      uint4 x[2][MAX_RANKS];
+      long long off[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = i0 + u * 32;
+        const int r = i / nv, c = i - r * nv;
+        off[u] = ((long long)(tm * BM + r) * vec_per_row + v_lo + c) * 8;
+        if (i < total) {
+#pragma unroll
+          for (int sidx = 0; sidx < MAX_RANKS; ++sidx)
+            if (sidx < ci.nranks) x[u][sidx] = __ldcg(reinterpret_cast<const uint4*>(stage + sidx * slot_elems + off[u]));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (i0 + u * 32 >= total) break;
+        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int sidx = 0; sidx < MAX_RANKS; ++sidx) {
+          if (sidx < ci.nranks) {
+            float2 f;
+            f = unpack_bf16x2(x[u][sidx].x); a[0] += f.x; a[1] += f.y;
+            f = unpack_bf16x2(x[u][sidx].y); a[2] += f.x; a[3] += f.y;
+            f = unpack_bf16x2(x[u][sidx].z); a[4] += f.x; a[5] += f.y;
+            f = unpack_bf16x2(x[u][sidx].w); a[6] += f.x; a[7] += f.y;
+          }
+        }
+        if (has_res) {
+          const uint4 r4 = *reinterpret_cast<const uint4*>(ci.residual + off[u]);
+          float2 f;
+          f = unpack_bf16x2(r4.x); a[0] += f.x; a[1] += f.y;
+          f = unpack_bf16x2(r4.y); a[2] += f.x; a[3] += f.y;
+          f = unpack_bf16x2(r4.z); a[4] += f.x; a[5] += f.y;
+          f = unpack_bf16x2(r4.w); a[6] += f.x; a[7] += f.y;
+        }
+        if (rs_bias) {
+          const int col = (int)((off[u] / 8) % vec_per_row) * 8;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[j] += __bfloat162float(ci.bias[col + j]);
+        }
+        uint4 o;
+        o.x = pack_bf16x2(a[0], a[1]);
+        o.y = pack_bf16x2(a[2], a[3]);
+        o.z = pack_bf16x2(a[4], a[5]);
+        o.w = pack_bf16x2(a[6], a[7]);
+        *reinterpret_cast<uint4*>(Cout + off[u]) = o;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_g,
                        const __grid_constant__ CUtensorMap tma_b, __nv_bfloat16* __restrict__ Cout, int N, int K,
@@ -216,6 +322,7 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   const int ppc = (BM * K * 2) / PIECE;  // pieces per 128-row chunk
 
   if (warp == 6) {
+    if (ci.mode == MODE_RS) rs_reduce_units(ci, Cout, N, lane, abort_flag, status);
     // ---- all-gather copier: every CTA moves its share of the peers' rows while its other warps multiply -------
     if (ci.mode == MODE_AG && lane == 0) {
       const int tps = ci.tiles_per_shard;
@@ -359,7 +466,7 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     uint32_t acc_phase = 0;
     const bool ag = ci.mode == MODE_AG;
     const bool has_bias = ag && (ci.flags & CF_BIAS) && ci.bias != nullptr;
-    const int arrivals_per_dst = 4 * ci.tiles_per_shard * tiles_n;
+    const int arrivals_per_block = 4 * tiles_n;   // four epilogue warps per tile, tiles_n tiles per row block
     bool ok = true;
     for (int tile = cta; tile < num_tiles; tile += ncta) {
       const Tile ti = decode(tile, tiles_n, ci);
@@ -403,96 +510,20 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       if (lane == 0) {
         mbar_arrive(tempty0 + 8 * acc);
         if (!ag) {
-          // Publish: when the last warp of the last tile for this destination has stored, raise its flag.
+          // Publish: when the last warp of the last tile of this row block has stored, raise the block's flag
+          // on its destination.
           __threadfence_system();
-          const int old = atom_add_acq_rel_gpu(ci.counters + ti.dst, 1);
-          if (old == arrivals_per_dst - 1) st_release_sys(ci.flag[ti.dst] + ci.rank, ci.epoch);
+          const int blk = (int)(ti.out_row / BM) - ci.rank * ci.tiles_per_shard;
+          const int old = atom_add_acq_rel_gpu(ci.counters + ti.dst * ci.tiles_per_shard + blk, 1);
+          if (old == arrivals_per_block - 1)
+            st_release_sys(ci.flag[ti.dst] + ci.rank * ci.tiles_per_shard + blk, ci.epoch);
         }
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
 
-    if (!ag && __all_sync(0xffffffffu, ok && !*abort_flag)) {
-      // ---- reduce this rank's row shard over the partials staged by every source -------------------------
-      bool ready = true;
-      if (lane == 0) {
-        const int* mine = ci.flag[ci.rank];
-        for (int s = 0; s < ci.nranks && ready; ++s) {
-          long long t0 = clock64();
-          uint32_t it = 0;
-          while (ld_acquire_sys(mine + s) < ci.epoch) {
-            if ((++it & 0x3f) == 0 && (*abort_flag || clock64() - t0 > ci.spin_limit)) {
-              if (!*abort_flag) {
-                *abort_flag = 1;
-                if (status) atomicCAS(status, 0, EDL_TIMEOUT_PEER_FLAG);
-              }
-              ready = false;
-              break;
-            }
-          }
-        }
-      }
-      ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
-      if (ready) {
-        const long long rows = (long long)ci.tiles_per_shard * BM;
-        const long long vec_per_row = N / 8;
-        const long long total = rows * vec_per_row;
-        const long long slot_elems = rows * N;
-        const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(ci.peer[ci.rank]);
-        const bool has_res = (ci.flags & CF_RESIDUAL) && ci.residual != nullptr;
-        const bool rs_bias = (ci.flags & CF_BIAS) && ci.bias != nullptr;
-        // four independent 16-byte vectors per thread and step keep enough loads in flight to stream from HBM
-        const long long step = (long long)ncta * 128;
-        for (long long v0 = (long long)cta * 128 + (warp - 2) * 32 + lane; v0 < total; v0 += 4 * step) {
-          uint4 x[4][MAX_RANKS];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const long long v = v0 + u * step;
-            if (v < total) {
-#pragma unroll
-              for (int s = 0; s < MAX_RANKS; ++s)
-                if (s < ci.nranks) x[u][s] = __ldcg(reinterpret_cast<const uint4*>(stage + s * slot_elems + v * 8));
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const long long v = v0 + u * step;
-            if (v >= total) break;
-            float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int s = 0; s < MAX_RANKS; ++s) {
-              if (s < ci.nranks) {
-                float2 f;
-                f = unpack_bf16x2(x[u][s].x); a[0] += f.x; a[1] += f.y;
-                f = unpack_bf16x2(x[u][s].y); a[2] += f.x; a[3] += f.y;
-                f = unpack_bf16x2(x[u][s].z); a[4] += f.x; a[5] += f.y;
-                f = unpack_bf16x2(x[u][s].w); a[6] += f.x; a[7] += f.y;
-              }
-            }
-            if (has_res) {
-              const uint4 r4 = *reinterpret_cast<const uint4*>(ci.residual + v * 8);
-              float2 f;
-              f = unpack_bf16x2(r4.x); a[0] += f.x; a[1] += f.y;
-              f = unpack_bf16x2(r4.y); a[2] += f.x; a[3] += f.y;
-              f = unpack_bf16x2(r4.z); a[4] += f.x; a[5] += f.y;
-              f = unpack_bf16x2(r4.w); a[6] += f.x; a[7] += f.y;
-            }
-            if (rs_bias) {
-              const int col = (int)((v % vec_per_row) * 8);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) a[j] += __bfloat162float(ci.bias[col + j]);
-            }
-            uint4 o;
-            o.x = pack_bf16x2(a[0], a[1]);
-            o.y = pack_bf16x2(a[2], a[3]);
-            o.z = pack_bf16x2(a[4], a[5]);
-            o.w = pack_bf16x2(a[6], a[7]);
-            *reinterpret_cast<uint4*>(Cout + v * 8) = o;
-          }
-        }
-      }
-    }
+    if (!ag && __all_sync(0xffffffffu, ok && !*abort_flag)) rs_reduce_units(ci, Cout, N, lane, abort_flag, status);
   }
 
   if (*abort_flag) {
@@ -545,8 +576,9 @@ long long cycles_for_ms(int wait_ms) {
 //   A [M, K] (lda), W [N, K] (ldb; or [K, N] when b_mn != 0): this rank's slices of the reduction dimension. M = nranks * rows_per_rank,
 //   rows_per_rank a multiple of 128; N a multiple of 8.
 //   stage_ptrs[r]: on rank r, a buffer of nranks * rows_per_rank * N bf16 (this call's slot of a symmetric allocation);
-//   flag_ptrs[r]: on rank r, nranks ints (this call's slot), initially 0; `epoch` must grow with every call that
-//   uses the same slot. counters: nranks local ints. out [rows_per_rank, N] = sum over ranks (+ residual, + bias).
+//   flag_ptrs[r]: on rank r, nranks * (rows_per_rank / 128) ints (this call's slot: one flag per source rank and
+//   128-row block), initially 0; `epoch` must grow with every call that uses the same slot. counters:
+//   nranks * (rows_per_rank / 128) + 1 local ints. out [rows_per_rank, N] = sum over ranks (+ residual, + bias).
 //   Callers alternate between two slots so that a rank still reducing call e is not overwritten by call e+1.
 EDL_HOST_API int edl_gemm_reduce_scatter(const void* A, const void* W, void* out, const void* residual,
                                          const void* bias, int M, int N, int K, long long lda, long long ldb,
@@ -577,7 +609,16 @@ EDL_HOST_API int edl_gemm_reduce_scatter(const void* A, const void* W, void* out
   ci.counters = counters;
   ci.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   ci.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
-  return launch_collective(ta, ta, tb, out, N, K, N, status, ci, nranks, reinterpret_cast<cudaStream_t>(stream));
+  {  // reduction work queue: about two units per SM, each a (row block, column piece)
+    const int vec_per_row = N / 8;
+    int pieces = (2 * sm_count() + ci.tiles_per_shard - 1) / ci.tiles_per_shard;
+    if (pieces < 1) pieces = 1;
+    if (pieces > vec_per_row) pieces = vec_per_row;
+    ci.rs_piece_vecs = (vec_per_row + pieces - 1) / pieces;
+    ci.rs_pieces = (vec_per_row + ci.rs_piece_vecs - 1) / ci.rs_piece_vecs;
+  }
+  return launch_collective(ta, ta, tb, out, N, K, N, status, ci, nranks * ci.tiles_per_shard + 1,
+                           reinterpret_cast<cudaStream_t>(stream));
 }
 
 // All-gather of row shards fused with the GEMM that consumes them.

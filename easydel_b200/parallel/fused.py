@@ -74,12 +74,15 @@ class GemmReduceScatter:
         self.world, self.rank = _world(group)
         self.rows, self.n_out = rows_per_rank, n_out
         self.slot_bytes = self.world * rows_per_rank * n_out * 2
-        self.buf, self.handle, base = _rendezvous(2 * self.slot_bytes + 2 * _FLAG_BYTES, group, device)
         w = self.world
+        blocks = rows_per_rank // 128
+        # one flag per (source rank, 128-row block) and slot
+        flag_bytes = max(_FLAG_BYTES, (4 * w * blocks + 255) // 256 * 256)
+        self.buf, self.handle, base = _rendezvous(2 * self.slot_bytes + 2 * flag_bytes, group, device)
         self.stage_ptrs = [(C.c_ulonglong * w)(*[b + s * self.slot_bytes for b in base]) for s in range(2)]
-        self.flag_ptrs = [(C.c_ulonglong * w)(*[b + 2 * self.slot_bytes + s * _FLAG_BYTES for b in base])
+        self.flag_ptrs = [(C.c_ulonglong * w)(*[b + 2 * self.slot_bytes + s * flag_bytes for b in base])
                           for s in range(2)]
-        self.counters = torch.zeros(w, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(w * blocks + 1, dtype=torch.int32, device=device)
         self.epoch = 0
 
     def __call__(self, a: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None,

@@ -100,7 +100,7 @@ def test_gemm_reduce_scatter_gives_up_on_missing_peer():
     w = torch.randn(N, K, device=dev).to(torch.bfloat16)
     stage = [torch.zeros(2 * rows * N, device=dev, dtype=torch.bfloat16) for _ in range(2)]
     flags = [torch.zeros(64, device=dev, dtype=torch.int32) for _ in range(2)]
-    counters = torch.zeros(2, device=dev, dtype=torch.int32)
+    counters = torch.zeros(2 * (rows // 128) + 1, device=dev, dtype=torch.int32)   # arrivals per block + queue head
     out = torch.zeros(rows, N, device=dev, dtype=torch.bfloat16)
     stage_ptrs = (C.c_ulonglong * 2)(*[t.data_ptr() for t in stage])
     flag_ptrs = (C.c_ulonglong * 2)(*[t.data_ptr() for t in flags])
