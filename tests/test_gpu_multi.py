@@ -298,8 +298,8 @@ def test_fsdp_parameter_sharded_layers(world):
 
 def _tp_esurge_worker(rank, world):
     """eSurge over a tensor-parallel bf16 model (graph-replayed decode steps, peer-memory all-reduces, vocabulary-
-    parallel LM head): same greedy tokens on every rank, and nearly all of them equal to the unsharded engine's
-    (bf16 reductions in another order may flip a near-tie late in a sequence)."""
+    parallel LM head): same greedy tokens on every rank, each of them the unsharded model's arg-max (up to bf16
+    near-ties) given the same history."""
     import torch.distributed as dist
 
     from easydel_b200.inference import SamplingParams
@@ -338,9 +338,19 @@ def _tp_esurge_worker(rank, world):
     others = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather(others, mine)
     assert all(torch.equal(o, others[0]) for o in others), "ranks diverged"
-    same = sum(a == b for r, gt in zip(ref, got) for a, b in zip(r, gt))
-    assert same >= 0.8 * sum(len(r) for r in ref), (ref, got)
-    assert all(r[:4] == gt[:4] for r, gt in zip(ref, got)), (ref, got)
+    # Greedy decoding of a random-initialised model has many near-ties, and bf16 sums in another order may break one
+    # differently; what must hold is that every token the sharded engine chose is (nearly) the unsharded model's
+    # arg-max given the same history.
+    worst = 0.0
+    for p, gt in zip(prompts, got):
+        ids = torch.tensor([p + gt], device=dev)
+        with torch.no_grad():
+            logits = full(input_ids=ids).logits[0, len(p) - 1:-1].float()
+        chosen = logits.gather(-1, torch.tensor(gt, device=dev)[:, None])[:, 0]
+        worst = max(worst, float((logits.max(-1).values - chosen).max()))
+    spread = float(logits.max(-1).values.mean() - logits.mean())
+    assert worst <= 0.05 * max(1.0, spread) + 0.1, (worst, spread, ref, got)
+    assert sum(r[0] == gt[0] for r, gt in zip(ref, got)) >= len(ref) - 1, (ref, got)
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
