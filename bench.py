@@ -173,7 +173,8 @@ def serving_arm(args, rank: int, world: int) -> dict | None:
                           "max_num_seqs": res["max_num_seqs"], "page_size": res["page_size"],
                           "prefix_cache_hit_rate": res["prefix_cache_hit_rate"], "kv_pages": res["kv_pages"],
                           "async_scheduling": res["async_scheduling"], "graph_steps": res["graph_steps"],
-                          "steps": res["steps"], "d2h_wait_s": res["d2h_wait_s"], "host_prep_s": res["host_prep_s"]},
+                          "steps": res["steps"], "d2h_wait_s": res["d2h_wait_s"], "host_prep_s": res["host_prep_s"],
+                          "decode_step_device_ms_by_rows": res.get("decode_step_device_ms_by_rows")},
                "dtype": "bf16", "data": "synthetic", "timing": res["timing"]}
     return res
 

@@ -141,10 +141,28 @@ def main():
 
         trainer = Trainer(arguments=args, model=model, dataset_train=_B())
         ms, loss = _time_steps(trainer, batches, a.warmup, a.steps, dev, world)
+        # one more (untimed) step with the exchange's row counter on: rows a rank stores into other ranks per
+        # dispatch, against what an all-gather of the tokens would move ((world - 1) x tokens per rank)
+        traffic = None
+        if world > 1:
+            from easydel_b200.parallel import ep as EP
+
+            for ex in EP._TOKEN_EXCHANGES.values():
+                ex.track = True
+            _time_steps(trainer, batches[-1:], 0, 1, dev, world)
+            exs = [ex for ex in EP._TOKEN_EXCHANGES.values() if ex.dispatches]
+            if exs:
+                ex = exs[0]
+                per = float(ex.rows_remote) / ex.dispatches
+                traffic = {"token_exchange": EP.ep_dispatch_mode(), "remote_rows_per_dispatch": per,
+                           "all_gather_rows": (world - 1) * S, "fraction_of_all_gather": per / ((world - 1) * S),
+                           "row_bytes": ex.x_bytes, "dispatches_per_step": ex.dispatches}
+                ex.track = False
         res = {"metric": "SFT tokens/s (Qwen3-MoE-30B-A3B architecture)", "value": n * world * S / (ms / 1e3),
                "unit": "tokens/s", "ms_per_step": ms, "n_gpus": world,
                "config": {"layers": L, "parallelism": f"ep{world}", "global_batch": n * world, "seq_len": S,
-                          "experts": 128, "top_k": 8, "aux_loss_coef": 0.001}, "final_loss": loss}
+                          "experts": 128, "top_k": 8, "aux_loss_coef": 0.001}, "final_loss": loss,
+               "nvlink_traffic": traffic}
     torch.cuda.synchronize()
     _lib.check_status()
     if rank == 0:

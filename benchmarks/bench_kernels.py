@@ -190,6 +190,12 @@ def bench_decode(args) -> None:
               f"weights, {wbytes / ms / 1e6 / pk['hbm_gbs']:.2f} of {pk['src']} copy bandwidth)   cuBLAS "
               f"{ms_lib * 1e3:6.1f} us", flush=True)
         ref = torch.matmul(a.float(), w.float().t())
+        t1 = time_cuda(lambda: K.gemm(a, w, out=out, force_bn=-1), flush=flush)
+        t384 = time_cuda(lambda: K.gemm(a, w, out=out, force_bn=384), flush=flush)
+        e384 = float((out.float() - ref).abs().max() / ref.abs().max())
+        print(f"    128-wide single-CTA kernel {t1 * 1e3:.1f} us   CTA pair, 256 x 128 tiles {t384 * 1e3:.1f} us"
+              + ("" if e384 < 1e-2 else f" (ERR {e384:.3f})") + f"   planned: "
+              f"{'pair 256x128' if K._pair128_plan(M, N, Kd, a.device) else 'other'}", flush=True)
         sweep = []
         for sp in (1, 2, 3, 4, 5, 6, 8):
             t = time_cuda(lambda: K.gemm(a, w, out=out, pair_splits=sp), flush=flush)

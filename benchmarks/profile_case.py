@@ -1,6 +1,7 @@
 """Runs one kernel a handful of times on a small, L2-exceeding case so that it can be captured by a profiler.
 
     python -m benchmarks.profile_case gemm          # 4096 x 6144 x 4096 bf16 (151 MB of operands + output)
+    python -m benchmarks.profile_case gemm_decode   # 256 x 7168 x 8192: a decode step's weight-streaming product
     python -m benchmarks.profile_case gemm_wgrad    # fp32-accumulating weight gradient, MN-major operands
     python -m benchmarks.profile_case attn_fwd      # 8192 tokens, 32 / 8 heads, D = 128, causal
     python -m benchmarks.profile_case attn_bwd
@@ -32,6 +33,20 @@ def main() -> None:
         out = torch.empty(4096, 6144, device=dev, dtype=torch.bfloat16)
         fn = lambda: K.gemm(a, w, out=out)  # noqa: E731
         work = 2.0 * 4096 * 6144 * 4096
+    elif what == "gemm_decode":
+        # a decode step's gate / up projection at the per-GPU shape of a 70B model under 8-way tensor parallelism:
+        # 256 rows against a 7168 x 8192 weight (117 MB streamed once); two weight copies alternate so that the
+        # second launch does not find its weights in L2
+        a = bf(256, 8192)
+        ws = [bf(7168, 8192), bf(7168, 8192)]
+        out = torch.empty(256, 7168, device=dev, dtype=torch.bfloat16)
+        state = {"i": 0}
+
+        def fn():
+            state["i"] ^= 1
+            K.gemm(a, ws[state["i"]], out=out, force_bn=-1)
+
+        work = 2.0 * 7168 * 8192        # bytes of weights: the roofline of this product is HBM
     elif what == "gemm_wgrad":
         dy, x = bf(8192, 4096), bf(8192, 4096)
         out = torch.zeros(4096, 4096, device=dev, dtype=torch.float32)
@@ -109,7 +124,7 @@ def main() -> None:
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
-    unit = "GB/s" if what in ("qgemv", "qgemv_plain", "adamw") else "TFLOP/s"
+    unit = "GB/s" if what in ("qgemv", "qgemv_plain", "adamw", "gemm_decode") else "TFLOP/s"
     rate = work / ms / 1e6 if unit == "GB/s" else work / ms / 1e9
     from easydel_b200.ops import _lib
 

@@ -475,16 +475,20 @@ __device__ __forceinline__ void splitk_partial_epilogue(void* __restrict__ Cout,
 // memory and writes both CTAs' tensor memory, and each CTA runs the epilogue of its own 128 rows. Against the
 // single-CTA tile this halves the B bytes every SM reads from shared memory per MMA and makes a stage 32 KB instead
 // of 48 KB, so six stages of look-ahead fit.
+// BN2 = 128 is the skinny form (a decode step's few hundred rows): 256 x 128 pair tiles give twice as many CTAs for
+// the same weight matrix, each CTA streaming 16 KB of activations and 8 KB of weights per reduction block through
+// eight stages.
+template <int BN2>
 struct Cfg2 {
-  static constexpr int BN = 256;
+  static constexpr int BN = BN2;
   static constexpr int A_BYTES = 128 * BK * 2;
-  static constexpr int B_BYTES = 128 * BK * 2;
+  static constexpr int B_BYTES = (BN2 / 2) * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = 6;
+  static constexpr int STAGES = BN2 == 256 ? 6 : 8;
   static constexpr int BAR_BYTES = 256;
   static constexpr int EPI_BYTES = 4 * 4096;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + EPI_BYTES + 1024;
-  static constexpr int TMEM_COLS = 512;
+  static constexpr int TMEM_COLS = 2 * BN2;
 };
 
 //
@@ -492,13 +496,14 @@ struct Cfg2 {
 // (tile, slice of the reduction dimension); every epilogue warp adds its 32 x 256 fp32 partial into the strip's
 // accumulator in `ws`, counts itself on `counters[region]`, and the warp that arrives last adds the bias and
 // writes bf16. `ws` and `counters` must be zero on entry and are zero again on exit.
-template <bool A_MN, bool B_MN, bool SPLITK>
+template <bool A_MN, bool B_MN, bool SPLITK, int BN2 = 256>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                   void* __restrict__ Cout, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, long long ldc,
                   int flags, int* status, int splits, float* __restrict__ ws, int* __restrict__ counters) {
-  using C = Cfg2;
+  using C = Cfg2<BN2>;
   constexpr int BN = C::BN;
+  constexpr int HALF = BN / 2;   // rows of the B tile each CTA of the pair loads
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
@@ -562,7 +567,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * 256 + (int)rank * 128;  // this CTA's rows of A and of the output
-        const int nb0 = tn * BN + (int)rank * 128;  // this CTA's half of the B tile
+        const int nb0 = tn * BN + (int)rank * HALF;  // this CTA's half of the B tile
         for (int kb = kb0; kb < kb1; ++kb) {
           const int kc = kb * BK;
           if (!mbar_wait(empty0 + 8 * stage, phase ^ 1, abort_flag, status, EDL_TIMEOUT_PRODUCER)) {
@@ -716,11 +721,11 @@ int launch(const void* A, const void* B, void* Cout, const void* bias, int M, in
 }
 
 // Number of CTA pairs that can be resident at once (queried once per device and kernel).
-template <bool A_MN, bool B_MN, bool SPLITK = false>
+template <bool A_MN, bool B_MN, bool SPLITK = false, int BN2 = 256>
 int launch_pair(const void* A, const void* B, void* Cout, const void* bias, int M, int N, int K, long long lda,
                 long long ldb, long long ldc, int flags, int* status, cudaStream_t stream, int max_ctas,
                 int splits = 1, float* ws = nullptr, int* counters = nullptr) {
-  using C = Cfg2;
+  using C = Cfg2<BN2>;
   CUtensorMap ta, tb;
   int rc;
   if (!A_MN)
@@ -729,11 +734,11 @@ int launch_pair(const void* A, const void* B, void* Cout, const void* bias, int 
     rc = make_tmap_2d_16b(&ta, A, K, M, lda, BK, 64);
   if (rc) return rc;
   if (!B_MN)
-    rc = make_tmap_2d_16b(&tb, B, N, K, ldb, 128, BK);
+    rc = make_tmap_2d_16b(&tb, B, N, K, ldb, BN2 / 2, BK);
   else
     rc = make_tmap_2d_16b(&tb, B, K, N, ldb, BK, 64);
   if (rc) return rc;
-  auto kern = gemm2_bf16_kernel<A_MN, B_MN, SPLITK>;
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN, SPLITK, BN2>;
   static int pairs_on_device[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -760,7 +765,7 @@ int launch_pair(const void* A, const void* B, void* Cout, const void* bias, int 
     }
     pairs_on_device[dev] = n;
   }
-  const int tiles = ((M + 255) / 256) * ((N + 255) / 256) * (SPLITK ? splits : 1);
+  const int tiles = ((M + 255) / 256) * ((N + BN2 - 1) / BN2) * (SPLITK ? splits : 1);
   int pairs = pairs_on_device[dev];
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (tiles < pairs) pairs = tiles;
@@ -793,12 +798,20 @@ EDL_HOST_API int edl_gemm_bf16(const void* A, const void* B, void* C, const void
     return -1;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // force_bn: 0 = choose, 128 / 256 = single-CTA tile width, 512 = CTA-pair (256 x 256) kernel, -1 = never the pair
+  // force_bn: 0 = choose, 128 / 256 = single-CTA tile width, 512 = CTA-pair (256 x 256) kernel, 384 = CTA-pair with
+  // 256 x 128 tiles (skinny products), -1 = never the pair
   const int pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
   static const bool pair_default = [] {
     const char* e = getenv("EDL_GEMM_PAIR");
     return e ? (e[0] != '0') : true;
   }();
+  if (force_bn == 384) {
+    if (a_mn || b_mn) {
+      set_last_error("edl_gemm_bf16: the 256 x 128 pair tile takes K-major operands only");
+      return -1;
+    }
+    return launch_pair<false, false, false, 128>(A, B, C, bias, M, N, K, lda, ldb, ldc, flags, status, s, max_ctas);
+  }
   const bool want_pair =
       force_bn == 512 || (force_bn == 0 && pair_default && pair_tiles >= sm_count() / 2 && M >= 256 && N >= 256);
   if (want_pair) {

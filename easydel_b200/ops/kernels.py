@@ -73,6 +73,22 @@ def _pair_splitk_plan(M: int, N: int, K: int, device) -> int:
     return 2 if 4 * tiles <= _SM_COUNT[idx] and K >= 2048 else 0
 
 
+def _pair128_plan(M: int, N: int, K: int, device) -> bool:
+    """Skinny products (a decode step's few hundred rows): the CTA-pair kernel with 256 x 128 tiles when it gives
+    more streaming CTAs than the 128-wide single-CTA kernel has row-tile pairs to spare. Each CTA of a pair loads 16 KB
+    of activations and 8 KB of weights per reduction block (24 KB against the single-CTA kernel's 32 KB), and what
+    bounds these products is what one SM pulls through its L2 port."""
+    if not _PAIR128_ENV[0] or M <= 128 or M > 512 or N % 8 or K % 64 or K < 1024:
+        return False
+    idx = device.index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(device).multi_processor_count
+    pairs = _SM_COUNT[idx] // 2
+    tiles = ((M + 255) // 256) * ((N + 127) // 128)
+    return 0.6 * pairs <= tiles <= 4 * pairs
+
+
+_PAIR128_ENV = [__import__("os").environ.get("EDL_GEMM_PAIR128", "0") not in ("", "0")]
 _PAIR_SPLITK_ENV = [__import__("os").environ.get("EDL_GEMM_PAIR_SPLITK", "0") not in ("", "0")]
 
 
@@ -142,6 +158,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                       ldb, ldc, ps, ws.data_ptr(), counters.data_ptr(), _lib.status_word(a.device).data_ptr(),
                       _lib.stream_ptr())
             return out
+    if not (a_mn or b_mn or accumulate or max_ctas or force_bn) and out.dtype == torch.bfloat16 \
+            and _pair128_plan(M, N, K, a.device):
+        force_bn = 384
     if not (a_mn or b_mn or accumulate or max_ctas or force_bn) and out.dtype == torch.bfloat16:
         splits = _splitk_plan(M, N, K, a.device)
         if splits > 1:

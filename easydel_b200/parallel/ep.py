@@ -189,7 +189,10 @@ class TokenExchange:
         self.a_bytes = (8 * k + 15) // 16 * 16          # k fp32 routing weights | k int32 expert ids
         self.ra_bytes = (4 * k + 15) // 16 * 16         # k fp32 routing-weight gradients
         self.native = device.type == "cuda" and _lib.available()
-        self.bytes_sent = 0                             # rows x row bytes this rank stored into OTHER ranks, cumulative
+        # with ``track`` on, every dispatch adds the rows it stores into OTHER ranks to a device counter (reporting)
+        self.track = False
+        self.rows_remote = torch.zeros((), dtype=torch.int64, device=device)
+        self.dispatches = 0
         if self.native:
             import torch.distributed._symmetric_memory as symm
 
@@ -250,6 +253,9 @@ class TokenExchange:
         """``x [T, H]`` bf16 (+ ``aux [T, a_bytes / 4]`` as 32-bit words) -> ``(x_recv [W * cap, H], aux_recv)``.
         On the GPU the results are VIEWS of this rank's arena: they are valid until the next dispatch."""
         W, cap = self.world, self.cap
+        if self.track:
+            self.rows_remote += p.send_count.sum() - p.send_count[self.rank]
+            self.dispatches += 1
         if self.native:
             if x.dtype != torch.bfloat16 or x.stride(-1) != 1 or x.shape[1] != self.hidden:
                 raise ValueError("exchange rows must be bf16 [T, hidden] with unit inner stride")

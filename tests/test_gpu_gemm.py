@@ -169,3 +169,17 @@ def test_pair_splitk_matches_fp32(M, N, K, splits):
         assert (out.float() - again.float()).abs().max() <= 1e-2 * ref.abs().max()
     for ws, counters in K_._PAIR_WS.values():
         assert int(counters.abs().sum()) == 0 and float(ws.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 7168, 2048), (200, 520, 1024), (384, 1000, 512)])
+def test_pair_kernel_128_wide_tiles(M, N, K):
+    """The CTA-pair kernel with 256 x 128 tiles (skinny products), ragged M and N, with bias, against fp32."""
+    from easydel_b200.ops import kernels as K_
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda") / K ** 0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device="cuda").to(torch.bfloat16)
+    ref = a.float() @ w.float().t() + bias.float()
+    out = K_.gemm(a, w, bias=bias, force_bn=384)
+    assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
