@@ -8,11 +8,15 @@
 //   warp 1      MMA issuer, software pipelined per key tile j:
 //                   O_A += P_A(j) V(j);  S_A = Q_A K(j+1)^T;  O_B += P_B(j) V(j);  S_B = Q_B K(j+1)^T
 //               so that the softmax of one tile always runs under the two products of the other
-//   warps 2..5  softmax of tile A, warps 6..9 softmax of tile B: thread i owns query row i,
-//               pulls its whole S row (128 fp32) out of tensor memory in one go, finds the row
-//               maximum, exponentiates in registers and writes P back as packed bf16 over the
-//               same tensor-memory columns (the A operand of the PV product). O is rescaled in
-//               tensor memory only when the running maximum moved by more than 2^8.
+//   warps 2..9  softmax of tile A, warps 10..17 softmax of tile B. Two threads share a query row
+//               (warps w and w + 4 of a group sit on the same tensor-memory lane quadrant and take
+//               the left and the right 64 score columns): with one warp per scheduler the softmax of
+//               a tile was bound by the latency of its own instruction stream and took longer than
+//               the other tile's two products, which left the tensor pipe idle a fifth of the time.
+//               Each thread pulls its 64 scores out of tensor memory, the two halves exchange their
+//               maxima through shared memory, exponentiate in registers and write P back as packed
+//               bf16 over the same tensor-memory columns (the A operand of the PV product). O is
+//               rescaled in tensor memory only when the running maximum moved by more than 2^8.
 // Tensor memory map (512 columns): S_A/P_A [0,128)  S_B/P_B [128,256)  O_A [256,384)  O_B [384,512).
 //
 // Queries, keys and values are read straight out of the packed projection output
@@ -31,11 +35,18 @@
 namespace edl {
 namespace {
 
-constexpr int ATT_THREADS = 320;
+constexpr int ATT_THREADS = 576;   // producer, MMA issuer, 2 x 8 softmax warps
 constexpr int BQ = 128;
 constexpr int BKV = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
+
+#ifdef EDL_ATTN_TRACE
+__device__ long long g_trace[4 * 64 * 8];
+#define TRACE(role, n, slot) do { if (trace_on && (n) < 64) g_trace[((role) * 64 + (n)) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(role, n, slot) do { } while (0)
+#endif
 
 struct AttnFwdParams {
   __nv_bfloat16* o;      // [tokens, ldo], head h at columns h*D
@@ -67,7 +78,8 @@ struct ACfg {
   static constexpr int OFF_K = 2 * Q_BYTES;
   static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
   static constexpr int OFF_BAR = OFF_V + 2 * KV_BYTES;
-  static constexpr int SMEM = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_XCH = OFF_BAR + 256;   // float [tile][parity][half][row]: row maxima / sums of a half
+  static constexpr int SMEM = OFF_XCH + 2 * 2 * 2 * BQ * 4 + 1024;
 };
 
 struct TileRange {
@@ -108,6 +120,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const uint32_t b_sfull = b_vempty + 16;      // [2] per query tile
   const uint32_t b_pfull = b_sfull + 16;       // [2] per query tile
   const uint32_t b_ofinal = b_pfull + 16;      // [2] per query tile
+  const uint32_t b_xch = smem_u32(bars + 16);  // [2 tiles][4 quadrants]: the two halves of a row block meet here
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -157,9 +170,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       mbar_init(b_kempty + 8 * s, 1);
       mbar_init(b_vempty + 8 * s, 1);
       mbar_init(b_sfull + 8 * s, 1);
-      mbar_init(b_pfull + 8 * s, 128);
+      mbar_init(b_pfull + 8 * s, 256);
       mbar_init(b_ofinal + 8 * s, 1);
     }
+    for (int i = 0; i < 8; ++i) mbar_init(b_xch + 8 * i, 64);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -204,7 +218,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && jmax > jmin) {
+    if (jmax > jmin) {
+      // The whole warp runs the role (waits, loop control, descriptor arithmetic); one elected lane issues.
+      const bool leader = elect_one();
       constexpr uint32_t idesc_qk = umma_idesc_bf16(BQ, BKV, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(BQ, D, 0, 1);
       bool ok = mbar_wait(b_qfull, 0, abort_flag, p.status, EDL_TIMEOUT_MMA);
@@ -220,9 +236,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           for (int k = 0; k < 4; ++k) {
             uint64_t ad = umma_smem_desc_sw128(qbase + c * (BQ * 128) + k * 32, 16, 1024);
             uint64_t bd = umma_smem_desc_sw128(kb + c * (BKV * 128) + k * 32, 16, 1024);
-            umma_f16_ss(tmem_base + t * 128, ad, bd, idesc_qk, (c | k) != 0 ? 1u : 0u);
+            if (leader) umma_f16_ss(tmem_base + t * 128, ad, bd, idesc_qk, (c | k) != 0 ? 1u : 0u);
           }
-        tc_commit(b_sfull + 8 * t);
+        if (leader) tc_commit(b_sfull + 8 * t);
       };
       auto issue_pv = [&](int t, int j) -> bool {
         const int s = (j - jmin) & 1;
@@ -232,12 +248,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k) {
           uint64_t bd = umma_smem_desc_sw128(vb + k * 2048, BKV * 128, 1024);
-          umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, bd, idesc_pv,
-                      (pv_cnt[t] | k) != 0 ? 1u : 0u);
+          if (leader)
+            umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, bd, idesc_pv,
+                        (pv_cnt[t] | k) != 0 ? 1u : 0u);
         }
         ++pv_cnt[t];
         const bool last = t == 0 ? (j == rgA.hi - 1) : (j == rgB.hi - 1);
-        if (last) tc_commit(b_ofinal + 8 * t);
+        if (last && leader) tc_commit(b_ofinal + 8 * t);
         return true;
       };
       if (ok) {
@@ -246,29 +263,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           tc_fence_after();
           if (valid(0, jmin)) issue_qk(0, jmin);
           if (valid(1, jmin)) issue_qk(1, jmin);
-          tc_commit(b_kempty);
+          if (leader) tc_commit(b_kempty);
         }
       }
+#ifdef EDL_ATTN_TRACE
+      const bool trace_on = blockIdx.x == 0 && leader;
+#endif
       for (int j = jmin; j < jmax && ok; ++j) {
         const int it = j - jmin;
         const int s = it & 1;
         const bool more = j + 1 < jmax;
+        TRACE(2, it, 0);
         if (!mbar_wait(b_vfull + 8 * s, (it >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA)) break;
         if (more && !mbar_wait(b_kfull + 8 * (s ^ 1), ((it + 1) >> 1) & 1, abort_flag, p.status, EDL_TIMEOUT_MMA))
           break;
         tc_fence_after();
+        TRACE(2, it, 1);
         if (valid(0, j) && !issue_pv(0, j)) break;
+        TRACE(2, it, 2);
         if (more && valid(0, j + 1)) issue_qk(0, j + 1);
+        TRACE(2, it, 3);
         if (valid(1, j) && !issue_pv(1, j)) break;
-        tc_commit(b_vempty + 8 * s);
+        TRACE(2, it, 4);
+        if (leader) tc_commit(b_vempty + 8 * s);
         if (more) {
           if (valid(1, j + 1)) issue_qk(1, j + 1);
-          tc_commit(b_kempty + 8 * (s ^ 1));
+          if (leader) tc_commit(b_kempty + 8 * (s ^ 1));
         }
+        TRACE(2, it, 5);
       }
     }
   } else {
-    const int t = (warp - 2) >> 2;          // query tile handled by this softmax group
+    const int t = (warp - 2) >> 3;          // query tile handled by this softmax group
+    const int half = ((warp - 2) >> 2) & 1; // score columns [64 * half, 64 * half + 64) of every key tile
     const int q = warp & 3;                 // tensor-memory lane quadrant of this warp
     const int r = q * 32 + lane;            // query row within the tile
     const int q0 = qblock0 + t * TQ;        // first query token of the tile
@@ -280,8 +307,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const uint32_t tS = tmem_base + t * 128 + lane_sel;
     const uint32_t tO = tmem_base + 256 + t * 128 + lane_sel;
     const uint32_t bs = b_sfull + 8 * t, bp = b_pfull + 8 * t, bo = b_ofinal + 8 * t;
+    const uint32_t bx = b_xch + 8 * (t * 4 + q);
+    float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH) + t * (2 * 2 * BQ);   // [parity][half][row]
     float m_used = -1e30f;
-    float l = 0.f;
+    float l = 0.f;                          // sum over this thread's columns only
     const float cap2 = p.softcap * LOG2E;   // soft-cap in log2 units
     const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
     const float scale_nat = p.scale_log2 * LN2;
@@ -289,50 +318,65 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const float mul = capped ? 1.f : p.scale_log2;
     bool alive = true;
     int n = 0;
+    // One value per thread to the other half of the row and back (shared memory, 64-thread barrier, bounded).
+    auto exchange = [&](float mine, float& other) -> bool {
+      const int par = n & 1;
+      xch[(par * 2 + half) * BQ + r] = mine;
+      mbar_arrive(bx);
+      if (!mbar_wait(bx, par, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) return false;
+      other = xch[(par * 2 + (half ^ 1)) * BQ + r];
+      return true;
+    };
+#ifdef EDL_ATTN_TRACE
+    const bool trace_on = blockIdx.x == 0 && q == 0 && lane == 0 && half == 0;
+#endif
     for (int j = rg.lo; j < rg.hi && alive; ++j, ++n) {
       const int kv0 = j * BKV;
+      const int kbase = kv0 + half * 64;
+      TRACE(t, n, 0);
       if (!mbar_wait(bs, n & 1, abort_flag, p.status, EDL_TIMEOUT_SOFTMAX)) {
         alive = false;
         break;
       }
       tc_fence_after();
-      uint32_t a[64], c2[64];
-      tmem_ld_32x32b_x64(tS, a);
-      tc_wait_ld();
-      tmem_ld_32x32b_x64(tS + 64, c2);  // in flight while the first half is masked and reduced
+      TRACE(t, n, 1);
+      uint32_t a[64];
+      tmem_ld_32x32b_x64(tS + half * 64, a);
       const bool tile_mask = (kv0 + BKV > len_k) || (p.causal && kv0 + BKV - 1 > q0 + off) ||
                              (p.window > 0 && kv0 < q0 + TQ - 1 + off - p.window + 1);
-      auto prep = [&](uint32_t (&v)[64], int kbase) {
-        if (capped) {
+      tc_wait_ld();
+      if (capped) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) v[i] = __float_as_uint(cap2 * tanhf(__uint_as_float(v[i]) * scale_nat * inv_cap));
-        }
-        if (tile_mask) {
+        for (int i = 0; i < 64; ++i) a[i] = __float_as_uint(cap2 * tanhf(__uint_as_float(a[i]) * scale_nat * inv_cap));
+      }
+      if (tile_mask) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
-            const int k0 = kbase + i;
-            const bool ok0 = (k0 < len_k) && (!p.causal || k0 <= qpos) && (p.window <= 0 || k0 > qpos - p.window);
-            if (!ok0) v[i] = 0xff800000u;  // -inf
-          }
+        for (int i = 0; i < 64; ++i) {
+          const int k0 = kbase + i;
+          const bool ok0 = (k0 < len_k) && (!p.causal || k0 <= qpos) && (p.window <= 0 || k0 > qpos - p.window);
+          if (!ok0) a[i] = 0xff800000u;  // -inf
         }
-      };
-      auto row_max = [&](const uint32_t (&v)[64]) {
-        float m0 = fmax3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
-        float m1 = fmax3(__uint_as_float(v[3]), __uint_as_float(v[4]), __uint_as_float(v[5]));
+      }
+      float mx;
+      {
+        float m0 = fmax3(__uint_as_float(a[0]), __uint_as_float(a[1]), __uint_as_float(a[2]));
+        float m1 = fmax3(__uint_as_float(a[3]), __uint_as_float(a[4]), __uint_as_float(a[5]));
 #pragma unroll
         for (int i = 6; i < 62; i += 4) {
-          m0 = fmax3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-          m1 = fmax3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+          m0 = fmax3(m0, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
+          m1 = fmax3(m1, __uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]));
         }
-        return fmax3(m0, m1, fmaxf(__uint_as_float(v[62]), __uint_as_float(v[63])));
-      };
-      prep(a, kv0);
-      float mx = row_max(a);
-      tc_wait_ld();
-      prep(c2, kv0 + 64);
-      mx = fmaxf(mx, row_max(c2));
-      mx *= mul;  // mul > 0, so scaling commutes with the maximum
-      // lazy rescale (warp-uniform decision: tcgen05.ld/st are warp-wide). The QK^T product of this
+        mx = fmax3(m0, m1, fmaxf(__uint_as_float(a[62]), __uint_as_float(a[63])));
+      }
+      float mx_other;
+      TRACE(t, n, 2);
+      if (!exchange(mx, mx_other)) {
+        alive = false;
+        break;
+      }
+      mx = fmaxf(mx, mx_other) * mul;  // mul > 0, so scaling commutes with the maximum
+      // lazy rescale. Both halves of a row see the same maxima, so they take the same decision (warp-uniform,
+      // as tcgen05.ld/st are warp-wide) and each rescales its own 64 columns of O. The QK^T product of this
       // step was issued after the PV product of the previous one, so O is quiescent here.
       const float m_new = fmaxf(m_used, mx);
       if (__any_sync(0xffffffffu, m_new > m_used + 8.f)) {
@@ -340,52 +384,54 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         l *= alpha;
         if (n > 0) {
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
+          for (int c = 0; c < D / 64; ++c) {
             uint32_t rr[32];
-            tmem_ld_32x32b_x32(tO + c * 32, rr);
+            tmem_ld_32x32b_x32(tO + half * (D / 2) + c * 32, rr);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
-            tmem_st_32x32b_x32(tO + c * 32, rr);
+            tmem_st_32x32b_x32(tO + half * (D / 2) + c * 32, rr);
           }
         }
         m_used = m_new;
       }
       const float neg_m = -m_used;
+      TRACE(t, n, 3);
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
       // Four scores per step: packed FMAs form x = s * mul - m, three exponentials go to the MUFU and one to the
       // polynomial on the FMA pipe, the row sum is accumulated with packed adds.
-      auto exp_pack = [&](const uint32_t (&v)[64], uint32_t (&pk)[32]) {
+      uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          float x0, x1, x2, x3;
-          fma2(x0, x1, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), mul, mul, neg_m, neg_m);
-          fma2(x2, x3, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]), mul, mul, neg_m, neg_m);
-          const float e0 = exp2f(x0), e1 = exp2f(x1), e2 = exp2f(x2);
-          const float e3 = exp2_poly(x3);
-          add2(l0, l1, e0, e1);
-          add2(l2, l3, e2, e3);
-          pk[i >> 1] = pack_bf16x2(e0, e1);
-          pk[(i >> 1) + 1] = pack_bf16x2(e2, e3);
-        }
-      };
-      {
-        uint32_t pk[32];
-        exp_pack(a, pk);
-        tmem_st_32x32b_x32(tS, pk);
-        exp_pack(c2, pk);
-        tmem_st_32x32b_x32(tS + 32, pk);
+      for (int i = 0; i < 64; i += 4) {
+        float x0, x1, x2, x3;
+        fma2(x0, x1, __uint_as_float(a[i]), __uint_as_float(a[i + 1]), mul, mul, neg_m, neg_m);
+        fma2(x2, x3, __uint_as_float(a[i + 2]), __uint_as_float(a[i + 3]), mul, mul, neg_m, neg_m);
+        const float e0 = exp2f(x0), e1 = exp2f(x1), e2 = exp2f(x2);
+        const float e3 = exp2_poly(x3);
+        add2(l0, l1, e0, e1);
+        add2(l2, l3, e2, e3);
+        pk[i >> 1] = pack_bf16x2(e0, e1);
+        pk[(i >> 1) + 1] = pack_bf16x2(e2, e3);
       }
+      tmem_st_32x32b_x32(tS + half * 32, pk);
       l0 += l2;
       l1 += l3;
       l += l0 + l1;
+      TRACE(t, n, 4);
       tc_wait_st();
+      TRACE(t, n, 5);
       tc_fence_before();
       mbar_arrive(bp);
+      TRACE(t, n, 6);
     }
 
-    // epilogue: O / l -> bf16, plus LSE
+    // epilogue: O / l -> bf16, plus LSE. Each half writes its own D / 2 columns; the row sum is the two halves'.
     const bool any = rg.hi > rg.lo;
+    if (any && alive) {
+      float l_other;
+      if (!exchange(l, l_other)) alive = false;
+      l += l_other;
+    }
     if (any && alive) {
       if (!mbar_wait(bo, 0, abort_flag, p.status, EDL_TIMEOUT_EPILOGUE)) alive = false;
       tc_fence_after();
@@ -394,12 +440,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       if (p.sinks) l += exp2f(p.sinks[qhead] * LOG2E - m_used);
       const float inv_l = l > 0.f ? 1.f / l : 0.f;
       const bool row_ok = qrow < len_q;
-      __nv_bfloat16* op = p.o + (long long)(q_start + qrow) * p.ldo + (long long)qhead * D;
+      __nv_bfloat16* op = p.o + (long long)(q_start + qrow) * p.ldo + (long long)qhead * D + half * (D / 2);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t rr[32];
         if (any) {
-          tmem_ld_32x32b_x32(tO + c * 32, rr);
+          tmem_ld_32x32b_x32(tO + half * (D / 2) + c * 32, rr);
           tc_wait_ld();
         } else {
 #pragma unroll
@@ -417,7 +463,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           }
         }
       }
-      if (row_ok && p.lse)
+      if (row_ok && p.lse && half == 0)
         p.lse[(long long)qhead * p.total_q + q_start + qrow] = l > 0.f ? (m_used + log2f(l)) * LN2 : -INFINITY;
     }
   }
@@ -462,6 +508,12 @@ int launch_fwd(const void* q, const void* k, const void* v, long long ldq, long 
 
 }  // namespace
 }  // namespace edl
+
+#ifdef EDL_ATTN_TRACE
+EDL_HOST_API int edl_attn_trace_read(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, edl::g_trace, sizeof(long long) * 4 * 64 * 8);
+}
+#endif
 
 // q: [total_q, ldq] with head h at columns h*D (bf16); k, v likewise with Hkv heads.
 // Fixed-length batches: cu_q = cu_k = null, total_q = B*Tq, total_k = B*Tk. Variable
