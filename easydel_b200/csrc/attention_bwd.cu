@@ -181,7 +181,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n > 0) {
+    if (n > 0) {
+      // the warp stays converged through waits and operand arithmetic; one elected lane issues
+      const bool leader = elect_one();
       constexpr uint32_t id_kk = umma_idesc_bf16(BT, BT, 0, 0);
       constexpr uint32_t id_tn = umma_idesc_bf16(BT, D, 0, 1);
       bool ok = mbar_wait(b_qfull, 0, abort_flag, p.status, EDL_TIMEOUT_MMA);
@@ -194,9 +196,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         for (int c = 0; c < C::DCH; ++c)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_f16_ss(tS + (it & 1) * 128, umma_smem_desc_sw128(sQ + c * (BT * 128) + k * 32, 16, 1024),
+            if (leader) umma_f16_ss(tS + (it & 1) * 128, umma_smem_desc_sw128(sQ + c * (BT * 128) + k * 32, 16, 1024),
                         umma_smem_desc_sw128(kb + c * (BT * 128) + k * 32, 16, 1024), id_kk, (c | k) != 0 ? 1u : 0u);
-        tc_commit(b_sfull + 8 * (it & 1));
+        if (leader) tc_commit(b_sfull + 8 * (it & 1));
         return true;
       };
       auto issue_dp = [&](int it) -> bool {
@@ -208,10 +210,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         for (int c = 0; c < C::DCH; ++c)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_f16_ss(tDP, umma_smem_desc_sw128(sDO + c * (BT * 128) + k * 32, 16, 1024),
+            if (leader) umma_f16_ss(tDP, umma_smem_desc_sw128(sDO + c * (BT * 128) + k * 32, 16, 1024),
                         umma_smem_desc_sw128(vb + c * (BT * 128) + k * 32, 16, 1024), id_kk, (c | k) != 0 ? 1u : 0u);
-        tc_commit(b_dpfull);
-        tc_commit(b_vempty + 8 * vs);
+        if (leader) tc_commit(b_dpfull);
+        if (leader) tc_commit(b_vempty + 8 * vs);
         return true;
       };
       auto issue_dq = [&](int it) -> bool {
@@ -220,10 +222,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
         const uint32_t kb = sK0 + (it % 3) * C::TILE;
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)
-          umma_f16_ts(tDQ, split_a(tDP, kk), umma_smem_desc_sw128(kb + kk * 2048, BT * 128, 1024), id_tn,
+          if (leader) umma_f16_ts(tDQ, split_a(tDP, kk), umma_smem_desc_sw128(kb + kk * 2048, BT * 128, 1024), id_tn,
                       (it | kk) != 0 ? 1u : 0u);
-        tc_commit(b_kempty + 8 * (it % 3));
-        if (it == n - 1) tc_commit(b_final);
+        if (leader) tc_commit(b_kempty + 8 * (it % 3));
+        if (it == n - 1 && leader) tc_commit(b_final);
         return true;
       };
       if (ok) ok = issue_s(0) && issue_dp(0);
@@ -455,7 +457,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n > 0) {
+    if (n > 0) {
+      // the warp stays converged through waits and operand arithmetic; one elected lane issues
+      const bool leader = elect_one();
       constexpr uint32_t id_kk = umma_idesc_bf16(BT, BT, 0, 0);
       constexpr uint32_t id_tn = umma_idesc_bf16(BT, D, 0, 1);
       bool ok = mbar_wait(b_kvfull, 0, abort_flag, p.status, EDL_TIMEOUT_MMA);
@@ -469,9 +473,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         for (int c = 0; c < C::DCH; ++c)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_f16_ss(tS, umma_smem_desc_sw128(sK + c * (BT * 128) + k * 32, 16, 1024),
+            if (leader) umma_f16_ss(tS, umma_smem_desc_sw128(sK + c * (BT * 128) + k * 32, 16, 1024),
                         umma_smem_desc_sw128(qb + c * (BT * 128) + k * 32, 16, 1024), id_kk, (c | k) != 0 ? 1u : 0u);
-        tc_commit(b_sfull);
+        if (leader) tc_commit(b_sfull);
         return true;
       };
       auto issue_dpt = [&](int t) -> bool {
@@ -483,9 +487,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         for (int c = 0; c < C::DCH; ++c)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_f16_ss(tDP, umma_smem_desc_sw128(sV + c * (BT * 128) + k * 32, 16, 1024),
+            if (leader) umma_f16_ss(tDP, umma_smem_desc_sw128(sV + c * (BT * 128) + k * 32, 16, 1024),
                         umma_smem_desc_sw128(db + c * (BT * 128) + k * 32, 16, 1024), id_kk, (c | k) != 0 ? 1u : 0u);
-        tc_commit(b_dpfull);
+        if (leader) tc_commit(b_dpfull);
         return true;
       };
       auto issue_dvdk = [&](int t) -> bool {
@@ -495,15 +499,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         const uint32_t qb = sQ0 + (t % 3) * C::TILE;
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)
-          umma_f16_ts(tDV, split_a(tDP, kk), umma_smem_desc_sw128(db + kk * 2048, BT * 128, 1024), id_tn,
+          if (leader) umma_f16_ts(tDV, split_a(tDP, kk), umma_smem_desc_sw128(db + kk * 2048, BT * 128, 1024), id_tn,
                       (t | kk) != 0 ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)
-          umma_f16_ts(tDK, split_a(tDP + 32, kk), umma_smem_desc_sw128(qb + kk * 2048, BT * 128, 1024), id_tn,
+          if (leader) umma_f16_ts(tDK, split_a(tDP + 32, kk), umma_smem_desc_sw128(qb + kk * 2048, BT * 128, 1024), id_tn,
                       (t | kk) != 0 ? 1u : 0u);
-        tc_commit(b_qempty + 8 * (t % 3));
-        tc_commit(b_doempty + 8 * (t & 1));
-        if (t == n - 1) tc_commit(b_final);
+        if (leader) tc_commit(b_qempty + 8 * (t % 3));
+        if (leader) tc_commit(b_doempty + 8 * (t & 1));
+        if (t == n - 1 && leader) tc_commit(b_final);
         return true;
       };
       if (ok) ok = issue_st(0) && issue_dpt(0);

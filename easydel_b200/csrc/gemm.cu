@@ -329,7 +329,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // The whole warp runs this role and stays converged (waits, tile decoding, descriptor arithmetic); one
+      // elected lane issues the MMAs and their commits.
+      const bool leader = elect_one();
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
@@ -356,15 +359,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                                         : umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
                                         : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (leader) umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit(empty0 + 8 * stage);
+          if (leader) tc_commit(empty0 + 8 * stage);
           if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) tc_commit(tfull0 + 8 * acc);
+        if (ok && leader) tc_commit(tfull0 + 8 * acc);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
@@ -598,7 +601,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && leader) {
+    if (leader) {
+      const bool issuer = elect_one();   // the warp stays converged; one lane issues MMAs and commits
       constexpr uint32_t idesc = umma_idesc_bf16(256, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
@@ -626,15 +630,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
                                         : umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
                                         : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
-            umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            if (issuer) umma_f16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
-          tc_commit_pair(empty0 + 8 * stage, 3);  // the stage is free in both CTAs
+          if (issuer) tc_commit_pair(empty0 + 8 * stage, 3);  // the stage is free in both CTAs
           if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) tc_commit_pair(tfull0 + 8 * acc, 3);  // both epilogues may read this accumulator
+        if (ok && issuer) tc_commit_pair(tfull0 + 8 * acc, 3);  // both epilogues may read this accumulator
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }

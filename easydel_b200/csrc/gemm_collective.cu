@@ -422,7 +422,8 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();   // the warp stays converged; one lane issues MMAs and commits
       const uint32_t idesc = umma_idesc_bf16(BM, BN, 0, ci.b_mn);
       const bool b_mn = ci.b_mn != 0;
       int stage = 0;
@@ -443,18 +444,19 @@ gemm_collective_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
           const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_f16_ss(d_tmem, umma_smem_desc_sw128(a_addr + k * 32, 16, 1024),
-                        b_mn ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
-                             : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024),
-                        idesc, (kb | k) != 0 ? 1u : 0u);
-          tc_commit(empty0 + 8 * stage);
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t ad = umma_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t bd = b_mn ? umma_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
+                                     : umma_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+            if (leader) umma_f16_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          if (leader) tc_commit(empty0 + 8 * stage);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) tc_commit(tfull0 + 8 * acc);
+        if (ok && leader) tc_commit(tfull0 + 8 * acc);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
