@@ -41,9 +41,13 @@ constexpr int BKV = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
+// Optional cycle trace (-DEDL_ATTN_TRACE): CTA 0 stamps clock64 at the phase boundaries of its MMA-issuing lane and
+// of one softmax thread per query tile, 64 steps x 8 slots per role; `edl_attn_trace_read` copies the table out
+// (read by benchmarks/trace_attention.py).
 #ifdef EDL_ATTN_TRACE
 __device__ long long g_trace[4 * 64 * 8];
-#define TRACE(role, n, slot) do { if (trace_on && (n) < 64) g_trace[((role) * 64 + (n)) * 8 + (slot)] = clock64(); } while (0)
+#define TRACE(role, n, slot) \
+  do { if (trace_on && (n) < 64) g_trace[((role) * 64 + (n)) * 8 + (slot)] = clock64(); } while (0)
 #else
 #define TRACE(role, n, slot) do { } while (0)
 #endif
@@ -221,6 +225,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     if (jmax > jmin) {
       // The whole warp runs the role (waits, loop control, descriptor arithmetic); one elected lane issues.
       const bool leader = elect_one();
+#ifdef EDL_ATTN_TRACE
+      const bool trace_on = blockIdx.x == 0 && leader;
+#endif
       constexpr uint32_t idesc_qk = umma_idesc_bf16(BQ, BKV, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(BQ, D, 0, 1);
       bool ok = mbar_wait(b_qfull, 0, abort_flag, p.status, EDL_TIMEOUT_MMA);
@@ -261,14 +268,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         ok = mbar_wait(b_kfull, 0, abort_flag, p.status, EDL_TIMEOUT_MMA);
         if (ok) {
           tc_fence_after();
+          TRACE(3, 0, 0);
           if (valid(0, jmin)) issue_qk(0, jmin);
+          TRACE(3, 0, 1);
           if (valid(1, jmin)) issue_qk(1, jmin);
+          TRACE(3, 0, 2);
           if (leader) tc_commit(b_kempty);
         }
       }
-#ifdef EDL_ATTN_TRACE
-      const bool trace_on = blockIdx.x == 0 && leader;
-#endif
       for (int j = jmin; j < jmax && ok; ++j) {
         const int it = j - jmin;
         const int s = it & 1;
