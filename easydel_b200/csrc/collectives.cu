@@ -366,7 +366,10 @@ EDL_HOST_API int edl_allreduce_add_rmsnorm(const unsigned long long* data_ptrs, 
 namespace edl {
 namespace {
 
-__global__ void __launch_bounds__(ARN_THREADS)
+// THREADS x MAXV uint4 vectors cover a row. Peer loads are latency bound (one NVLink round trip each), so the wide
+// form (1024 threads, one or two vectors per thread) keeps every load of a row in flight at once.
+template <int THREADS, int MAXV>
+__global__ void __launch_bounds__(THREADS, 1)
 allreduce_twoshot_kernel(PeerPtrs data, PeerPtrs flags, PeerPtrs x_outs, PeerPtrs h_outs, int nranks, int rank,
                          int* sync, const __nv_bfloat16* __restrict__ residual,
                          const __nv_bfloat16* __restrict__ weight, float eps, float w_offset, int rows, int width,
@@ -397,17 +400,48 @@ allreduce_twoshot_kernel(PeerPtrs data, PeerPtrs flags, PeerPtrs x_outs, PeerPtr
   if (s_ok) {
     for (int lr = blockIdx.x; lr < rows_per; lr += gridDim.x) {
       const int row = rank * rows_per + lr;
-      float v[ARN_MAX_VEC][8];
+      float v[MAXV][8];
       float ss = 0.f;
+      // every peer load of the row first (eight ranks at a time), then the sums: a load is one NVLink round trip
+      float a[MAXV][8];
 #pragma unroll
-      for (int j = 0; j < ARN_MAX_VEC; ++j) {
-        const int c = threadIdx.x + j * ARN_THREADS;
+      for (int j = 0; j < MAXV; ++j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[j][e] = 0.f;
+      for (int g = 0; g < nranks; g += 8) {
+        uint4 part[MAXV][8];
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+          const int c = threadIdx.x + j * THREADS;
+          if (c < vec_per_row) {
+            const long long off = (long long)row * vec_per_row + c;
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (g + r < nranks) part[j][r] = reinterpret_cast<const uint4*>(data.p[g + r])[off];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+          const int c = threadIdx.x + j * THREADS;
+          if (c < vec_per_row) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              if (g + r < nranks) {
+                float2 f;
+                f = unpack_bf16x2(part[j][r].x); a[j][0] += f.x; a[j][1] += f.y;
+                f = unpack_bf16x2(part[j][r].y); a[j][2] += f.x; a[j][3] += f.y;
+                f = unpack_bf16x2(part[j][r].z); a[j][4] += f.x; a[j][5] += f.y;
+                f = unpack_bf16x2(part[j][r].w); a[j][6] += f.x; a[j][7] += f.y;
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j) {
+        const int c = threadIdx.x + j * THREADS;
         if (c >= vec_per_row) break;
         const long long off = (long long)row * vec_per_row + c;
-        uint4 part[MAX_RANKS];
-#pragma unroll
-        for (int r = 0; r < MAX_RANKS; ++r)
-          if (r < nranks) part[r] = reinterpret_cast<const uint4*>(data.p[r])[off];
         float2 f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[j][e] = 0.f;
@@ -418,21 +452,12 @@ allreduce_twoshot_kernel(PeerPtrs data, PeerPtrs flags, PeerPtrs x_outs, PeerPtr
           f = unpack_bf16x2(rs.z); v[j][4] = f.x; v[j][5] = f.y;
           f = unpack_bf16x2(rs.w); v[j][6] = f.x; v[j][7] = f.y;
         }
-        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int r = 0; r < MAX_RANKS; ++r) {
-          if (r >= nranks) break;
-          f = unpack_bf16x2(part[r].x); a[0] += f.x; a[1] += f.y;
-          f = unpack_bf16x2(part[r].y); a[2] += f.x; a[3] += f.y;
-          f = unpack_bf16x2(part[r].z); a[4] += f.x; a[5] += f.y;
-          f = unpack_bf16x2(part[r].w); a[6] += f.x; a[7] += f.y;
-        }
         uint4 o;
         uint32_t* ow = &o.x;
 #pragma unroll
         for (int e = 0; e < 8; e += 2) {
           // the sum is rounded to bf16 before it joins the residual stream, as the unfused sequence does
-          const float2 y = unpack_bf16x2(pack_bf16x2(a[e], a[e + 1]));
+          const float2 y = unpack_bf16x2(pack_bf16x2(a[j][e], a[j][e + 1]));
           const uint32_t packed = pack_bf16x2(v[j][e] + y.x, v[j][e + 1] + y.y);
           ow[e >> 1] = packed;
           const float2 z = unpack_bf16x2(packed);
@@ -448,8 +473,8 @@ allreduce_twoshot_kernel(PeerPtrs data, PeerPtrs flags, PeerPtrs x_outs, PeerPtr
         ss = block_sum(ss, red);
         const float rstd = rsqrtf(ss / (float)width + eps);
 #pragma unroll
-        for (int j = 0; j < ARN_MAX_VEC; ++j) {
-          const int c = threadIdx.x + j * ARN_THREADS;
+        for (int j = 0; j < MAXV; ++j) {
+          const int c = threadIdx.x + j * THREADS;
           if (c >= vec_per_row) break;
           const uint4 wv = reinterpret_cast<const uint4*>(weight)[c];
           const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
@@ -510,10 +535,10 @@ EDL_HOST_API int edl_allreduce_twoshot(const unsigned long long* data_ptrs, cons
                                        float eps, float w_offset, int rows, int width, int wait_ms, int* status,
                                        void* stream) {
   if (rows <= 0) return 0;
-  if (nranks < 1 || nranks > MAX_RANKS || (width & 7) || width > ARN_THREADS * ARN_MAX_VEC * 8 || rows % nranks ||
+  if (nranks < 1 || nranks > MAX_RANKS || (width & 7) || width > 16384 || rows % nranks ||
       (weight && !h_out_ptrs)) {
     set_last_error("edl_allreduce_twoshot: nranks=%d, rows=%d (multiple of nranks), width=%d (multiple of 8, <= %d)",
-                   nranks, rows, width, ARN_THREADS * ARN_MAX_VEC * 8);
+                   nranks, rows, width, 16384);
     return -1;
   }
   PeerPtrs d, f, xo, ho;
@@ -526,8 +551,19 @@ EDL_HOST_API int edl_allreduce_twoshot(const unsigned long long* data_ptrs, cons
   int blocks = rows / nranks;
   if (blocks > sm_count()) blocks = sm_count();
   const long long spin = (long long)(wait_ms > 0 ? wait_ms : 2000) * 2000000LL;
-  allreduce_twoshot_kernel<<<blocks, ARN_THREADS, 0, (cudaStream_t)stream>>>(
-      d, f, xo, ho, nranks, rank, sync, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)weight, eps, w_offset,
-      rows, width, spin, status);
+  const int vecs = width / 8;
+#define EDL_TWOSHOT_LAUNCH(T, V)                                                                                  \
+  allreduce_twoshot_kernel<T, V><<<blocks, T, 0, (cudaStream_t)stream>>>(                                         \
+      d, f, xo, ho, nranks, rank, sync, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)weight, eps, w_offset, \
+      rows, width, spin, status)
+  if (vecs <= 256)
+    EDL_TWOSHOT_LAUNCH(256, 1);
+  else if (vecs <= 512)
+    EDL_TWOSHOT_LAUNCH(512, 1);
+  else if (vecs <= 1024)
+    EDL_TWOSHOT_LAUNCH(512, 2);
+  else
+    EDL_TWOSHOT_LAUNCH(512, 4);
+#undef EDL_TWOSHOT_LAUNCH
   return check_cuda(cudaGetLastError(), "allreduce_twoshot launch");
 }
