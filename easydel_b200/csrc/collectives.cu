@@ -366,6 +366,26 @@ EDL_HOST_API int edl_allreduce_add_rmsnorm(const unsigned long long* data_ptrs, 
 namespace edl {
 namespace {
 
+// Multicast (NVLink switch) addresses of the same three regions, or zeros: with them the sum over ranks is one
+// `multimem.ld_reduce` (the switch adds the eight partials, fp32 accumulation, bf16 result) instead of one load per
+// peer, and a row is handed to every rank by one `multimem.st` instead of one store per peer.
+struct McPtrs {
+  unsigned long long data, x_out, h_out;
+};
+__device__ __forceinline__ uint4 multimem_sum_bf16x8(unsigned long long addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_store16(unsigned long long addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 // THREADS x MAXV uint4 vectors cover a row. Peer loads are latency bound (one NVLink round trip each), so the wide
 // form (1024 threads, one or two vectors per thread) keeps every load of a row in flight at once.
 template <int THREADS, int MAXV>
@@ -373,7 +393,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 allreduce_twoshot_kernel(PeerPtrs data, PeerPtrs flags, PeerPtrs x_outs, PeerPtrs h_outs, int nranks, int rank,
                          int* sync, const __nv_bfloat16* __restrict__ residual,
                          const __nv_bfloat16* __restrict__ weight, float eps, float w_offset, int rows, int width,
-                         long long spin_limit, int* status) {
+                         long long spin_limit, int* status, McPtrs mc) {
   __shared__ int s_ok;
   __shared__ float red[32];
   const int epoch = *reinterpret_cast<volatile int*>(sync) + 1;
@@ -408,7 +428,21 @@ allreduce_twoshot_kernel(PeerPtrs data, PeerPtrs flags, PeerPtrs x_outs, PeerPtr
       for (int j = 0; j < MAXV; ++j)
 #pragma unroll
         for (int e = 0; e < 8; ++e) a[j][e] = 0.f;
-      for (int g = 0; g < nranks; g += 8) {
+      if (mc.data) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+          const int c = threadIdx.x + j * THREADS;
+          if (c < vec_per_row) {
+            const uint4 sum = multimem_sum_bf16x8(mc.data + ((long long)row * vec_per_row + c) * 16);
+            float2 f;
+            f = unpack_bf16x2(sum.x); a[j][0] = f.x; a[j][1] = f.y;
+            f = unpack_bf16x2(sum.y); a[j][2] = f.x; a[j][3] = f.y;
+            f = unpack_bf16x2(sum.z); a[j][4] = f.x; a[j][5] = f.y;
+            f = unpack_bf16x2(sum.w); a[j][6] = f.x; a[j][7] = f.y;
+          }
+        }
+      }
+      for (int g = 0; g < (mc.data ? 0 : nranks); g += 8) {
         uint4 part[MAXV][8];
 #pragma unroll
         for (int j = 0; j < MAXV; ++j) {
@@ -465,9 +499,13 @@ allreduce_twoshot_kernel(PeerPtrs data, PeerPtrs flags, PeerPtrs x_outs, PeerPtr
           v[j][e + 1] = z.y;
           ss += z.x * z.x + z.y * z.y;
         }
+        if (mc.x_out) {
+          multimem_store16(mc.x_out + off * 16, o);
+        } else {
 #pragma unroll
-        for (int r = 0; r < MAX_RANKS; ++r)
-          if (r < nranks) reinterpret_cast<uint4*>(x_outs.p[r])[off] = o;
+          for (int r = 0; r < MAX_RANKS; ++r)
+            if (r < nranks) reinterpret_cast<uint4*>(x_outs.p[r])[off] = o;
+        }
       }
       if (weight) {
         ss = block_sum(ss, red);
@@ -486,9 +524,13 @@ allreduce_twoshot_kernel(PeerPtrs data, PeerPtrs flags, PeerPtrs x_outs, PeerPtr
             ow[e >> 1] = pack_bf16x2(v[j][e] * rstd * (w2.x + w_offset), v[j][e + 1] * rstd * (w2.y + w_offset));
           }
           const long long off = (long long)row * vec_per_row + c;
+          if (mc.h_out) {
+            multimem_store16(mc.h_out + off * 16, o);
+          } else {
 #pragma unroll
-          for (int r = 0; r < MAX_RANKS; ++r)
-            if (r < nranks) reinterpret_cast<uint4*>(h_outs.p[r])[off] = o;
+            for (int r = 0; r < MAX_RANKS; ++r)
+              if (r < nranks) reinterpret_cast<uint4*>(h_outs.p[r])[off] = o;
+          }
         }
         __syncthreads();
       }
@@ -529,11 +571,16 @@ allreduce_twoshot_kernel(PeerPtrs data, PeerPtrs flags, PeerPtrs x_outs, PeerPtr
 // residual + sum (or the sum alone when residual is null), h_out the RMSNorm of it times (weight + w_offset) when
 // weight is given. rows must be a multiple of nranks, width a multiple of 8 and <= 16384. sync: int[4] per group.
 // `residual` may be this rank's own x_out buffer (each rank reads and rewrites only its own rows of it).
-EDL_HOST_API int edl_allreduce_twoshot(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs,
-                                       const unsigned long long* x_out_ptrs, const unsigned long long* h_out_ptrs,
-                                       int nranks, int rank, int* sync, const void* residual, const void* weight,
-                                       float eps, float w_offset, int rows, int width, int wait_ms, int* status,
-                                       void* stream) {
+// mc_data / mc_x_out / mc_h_out: multicast addresses of the partial and of the two output regions (0 = use the
+// per-peer pointers for that step).
+EDL_HOST_API int edl_allreduce_twoshot_mc(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs,
+                                          const unsigned long long* x_out_ptrs,
+                                          const unsigned long long* h_out_ptrs, int nranks, int rank, int* sync,
+                                          const void* residual, const void* weight, float eps, float w_offset,
+                                          int rows, int width, int wait_ms, int* status, void* stream,
+                                          unsigned long long mc_data, unsigned long long mc_x_out,
+                                          unsigned long long mc_h_out) {
+  using namespace edl;
   if (rows <= 0) return 0;
   if (nranks < 1 || nranks > MAX_RANKS || (width & 7) || width > 16384 || rows % nranks ||
       (weight && !h_out_ptrs)) {
@@ -552,10 +599,15 @@ EDL_HOST_API int edl_allreduce_twoshot(const unsigned long long* data_ptrs, cons
   if (blocks > sm_count()) blocks = sm_count();
   const long long spin = (long long)(wait_ms > 0 ? wait_ms : 2000) * 2000000LL;
   const int vecs = width / 8;
+  if ((mc_data | mc_x_out | mc_h_out) & 15) {
+    set_last_error("edl_allreduce_twoshot: multicast addresses must be 16-byte aligned");
+    return -1;
+  }
+  const McPtrs mc{mc_data, mc_x_out, mc_h_out && weight ? mc_h_out : 0ull};
 #define EDL_TWOSHOT_LAUNCH(T, V)                                                                                  \
   allreduce_twoshot_kernel<T, V><<<blocks, T, 0, (cudaStream_t)stream>>>(                                         \
       d, f, xo, ho, nranks, rank, sync, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)weight, eps, w_offset, \
-      rows, width, spin, status)
+      rows, width, spin, status, mc)
   if (vecs <= 256)
     EDL_TWOSHOT_LAUNCH(256, 1);
   else if (vecs <= 512)
@@ -566,4 +618,13 @@ EDL_HOST_API int edl_allreduce_twoshot(const unsigned long long* data_ptrs, cons
     EDL_TWOSHOT_LAUNCH(512, 4);
 #undef EDL_TWOSHOT_LAUNCH
   return check_cuda(cudaGetLastError(), "allreduce_twoshot launch");
+}
+
+EDL_HOST_API int edl_allreduce_twoshot(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs,
+                                       const unsigned long long* x_out_ptrs, const unsigned long long* h_out_ptrs,
+                                       int nranks, int rank, int* sync, const void* residual, const void* weight,
+                                       float eps, float w_offset, int rows, int width, int wait_ms, int* status,
+                                       void* stream) {
+  return edl_allreduce_twoshot_mc(data_ptrs, flag_ptrs, x_out_ptrs, h_out_ptrs, nranks, rank, sync, residual, weight,
+                                  eps, w_offset, rows, width, wait_ms, status, stream, 0ull, 0ull, 0ull);
 }

@@ -26,7 +26,7 @@ _status: dict[int, torch.Tensor] = {}
 #: number of kernel-library launches issued by this process (for benchmarks)
 launch_count = 0
 
-vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+vp, i32, i64, f32, u64 = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulonglong
 
 _SIGS = {
     "edl_last_error": (C.c_char_p, []),

@@ -282,6 +282,19 @@ def test_two_shot_allreduce_add_rmsnorm(world):
     _run(_twoshot_worker, world)
 
 
+def _twoshot_multimem_worker(rank, world):
+    """The same checks with the sums and the broadcasts going through the NVLink switch (multimem) at any rank count."""
+    from easydel_b200.parallel import tp
+
+    tp._MULTIMEM_MODE = "1"
+    _twoshot_worker(rank, world)   # falls back to per-peer loads and stores where the buffer has no multicast mapping
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_two_shot_allreduce_multimem(world):
+    _run(_twoshot_multimem_worker, world)
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_tensor_parallel_forward_and_loss(world):
     _run(_tp_forward_worker, world)
