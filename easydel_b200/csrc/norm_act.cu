@@ -282,6 +282,74 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const int* __restrict
   }
 }
 
+// Vector form for full-width rotation (rot_dim == head_dim, head_dim a multiple of 16, 16-byte aligned rows): a thread
+// rotates eight pairs with 16-byte accesses. With dst != src the result goes to dst and the columns outside the rotated
+// heads are copied along, so that one pass replaces a copy of the tensor plus the in-place rotation.
+__global__ void rope_vec_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                const int* __restrict__ pos, const float* __restrict__ cos_t,
+                                const float* __restrict__ sin_t, long long T, int nheads, int head_dim,
+                                long long ld_src, long long ld_dst, int width, int col0, int interleaved, float sign,
+                                int max_pos) {
+  const int half = head_dim / 2;
+  const int hv = half / 8;
+  const int rot_items = nheads * hv;
+  const int rot_w = nheads * head_dim;
+  const int pass_vecs = src != dst ? (width - rot_w) / 8 : 0;
+  const int items = rot_items + pass_vecs;
+  const long long total = T * items;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / items;
+    const int k = (int)(i - t * items);
+    const __nv_bfloat16* srow = src + t * ld_src;
+    __nv_bfloat16* drow = dst + t * ld_dst;
+    if (k >= rot_items) {
+      int col = (k - rot_items) * 8;
+      if (col >= col0) col += rot_w;
+      *reinterpret_cast<uint4*>(drow + col) = *reinterpret_cast<const uint4*>(srow + col);
+      continue;
+    }
+    const int hh = k / hv, p = (k - hh * hv) * 8;
+    int ps = pos ? pos[t] : (int)t;
+    ps = min(max(ps, 0), max_pos - 1);
+    float c[8], sn[8];
+    {
+      const float4* cp = reinterpret_cast<const float4*>(cos_t + (size_t)ps * half + p);
+      const float4* sp = reinterpret_cast<const float4*>(sin_t + (size_t)ps * half + p);
+      const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+      c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    const int base = col0 + hh * head_dim;
+    float a[8], b[8], oa[8], ob[8];
+    if (!interleaved) {
+      load8(srow + base + p, a);
+      load8(srow + base + half + p, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float s = sign * sn[e];
+        oa[e] = a[e] * c[e] - b[e] * s;
+        ob[e] = b[e] * c[e] + a[e] * s;
+      }
+      store8(drow + base + p, oa);
+      store8(drow + base + half + p, ob);
+    } else {
+      load8(srow + base + 2 * p, a);        // pairs p .. p+3 as (even, odd) neighbours
+      load8(srow + base + 2 * p + 8, b);    // pairs p+4 .. p+7
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float s0 = sign * sn[e], s1 = sign * sn[e + 4];
+        oa[2 * e] = a[2 * e] * c[e] - a[2 * e + 1] * s0;
+        oa[2 * e + 1] = a[2 * e + 1] * c[e] + a[2 * e] * s0;
+        ob[2 * e] = b[2 * e] * c[e + 4] - b[2 * e + 1] * s1;
+        ob[2 * e + 1] = b[2 * e + 1] * c[e + 4] + b[2 * e] * s1;
+      }
+      store8(drow + base + 2 * p, oa);
+      store8(drow + base + 2 * p + 8, ob);
+    }
+  }
+}
+
 // Embedding gather: out[t,:] = table[ids[t],:]  (ids outside [0,V) give zeros)
 __global__ void embed_fwd_kernel(const __nv_bfloat16* __restrict__ table, const long long* __restrict__ ids,
                                  __nv_bfloat16* __restrict__ out, long long T, int D, int V) {
@@ -435,6 +503,26 @@ EDL_HOST_API int edl_rope(void* x, const int* pos, const float* cos_t, const flo
                                                                      head_dim, rot_dim, ld, col0, interleaved,
                                                                      backward ? -1.f : 1.f, max_pos);
   return check_cuda(cudaGetLastError(), "rope launch");
+}
+
+// Rotation of full heads from src [T, ld_src] into dst [T, ld_dst] (may be the same memory), `width` columns per row
+// of which nheads * head_dim starting at col0 are rotated and the rest copied (skipped when dst == src).
+EDL_HOST_API int edl_rope_copy(const void* src, void* dst, const int* pos, const float* cos_t, const float* sin_t,
+                               long long T, int nheads, int head_dim, long long ld_src, long long ld_dst, int width,
+                               int col0, int interleaved, int backward, int max_pos, void* stream) {
+  if (T <= 0 || nheads <= 0) return 0;
+  const uintptr_t al = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) |
+                       reinterpret_cast<uintptr_t>(cos_t) | reinterpret_cast<uintptr_t>(sin_t);
+  if ((head_dim % 16) || (col0 % 8) || (width % 8) || (ld_src % 8) || (ld_dst % 8) || (al & 15) ||
+      col0 + nheads * head_dim > width) {
+    set_last_error("edl_rope_copy: head_dim %% 16, col0 / width / row pitch %% 8 and 16-byte aligned pointers required");
+    return -1;
+  }
+  const int items = nheads * (head_dim / 16) + (src != dst ? (width - nheads * head_dim) / 8 : 0);
+  rope_vec_kernel<<<grid_for(T * items, 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, pos, cos_t, sin_t, T, nheads, head_dim, ld_src, ld_dst, width,
+      col0, interleaved, backward ? -1.f : 1.f, max_pos);
+  return check_cuda(cudaGetLastError(), "rope_copy launch");
 }
 
 EDL_HOST_API int edl_embed_fwd(const void* table, const long long* ids, void* out, long long T, int D, int V,

@@ -42,6 +42,7 @@ _SIGS = {
     "edl_gated_act_fwd": (i32, [vp, vp, i64, i32, i64, i32, vp]),
     "edl_gated_act_bwd": (i32, [vp, vp, vp, i64, i32, i64, i32, vp]),
     "edl_rope": (i32, [vp, vp, vp, vp, i64, i32, i32, i32, i64, i32, i32, i32, i32, vp]),
+    "edl_rope_copy": (i32, [vp, vp, vp, vp, vp, i64, i32, i32, i64, i64, i32, i32, i32, i32, i32, vp]),
     "edl_embed_fwd": (i32, [vp, vp, vp, i64, i32, i32, vp]),
     "edl_embed_bwd": (i32, [vp, vp, vp, i64, i32, i32, vp]),
     "edl_cross_entropy": (i32, [vp, vp, vp, vp, vp, i32, i32, i64, i32, f32, f32, f32, vp, f32, i32, vp]),

@@ -150,6 +150,12 @@ class _RopeFn(torch.autograd.Function):
     def forward(ctx, x, pos, cos, sin, nheads, head_dim, col0, rot_dim, interleaved):
         ctx.save_for_backward(pos, cos, sin)
         ctx.args = (nheads, head_dim, col0, rot_dim, interleaved)
+        x2 = x.reshape(-1, x.shape[-1]) if x.is_contiguous() else None
+        if x2 is not None and K.rope_copy_supported(x2, cos, sin, nheads, head_dim, col0, rot_dim):
+            y = torch.empty_like(x, memory_format=torch.contiguous_format)   # one pass: rotate and copy the rest
+            K.rope_copy(x2, y.view(-1, y.shape[-1]), pos, cos, sin, nheads, head_dim, col0=col0,
+                        interleaved=interleaved)
+            return y
         y = x.clone(memory_format=torch.contiguous_format)
         K.rope_(y.view(-1, y.shape[-1]), pos, cos, sin, nheads, head_dim, col0=col0, rot_dim=rot_dim,
                 interleaved=interleaved)
@@ -159,6 +165,12 @@ class _RopeFn(torch.autograd.Function):
     def backward(ctx, dx):
         pos, cos, sin = ctx.saved_tensors
         nheads, head_dim, col0, rot_dim, interleaved = ctx.args
+        d2 = dx.reshape(-1, dx.shape[-1]) if dx.is_contiguous() else None
+        if d2 is not None and K.rope_copy_supported(d2, cos, sin, nheads, head_dim, col0, rot_dim):
+            out = torch.empty_like(dx, memory_format=torch.contiguous_format)
+            K.rope_copy(d2, out.view(-1, out.shape[-1]), pos, cos, sin, nheads, head_dim, col0=col0,
+                        interleaved=interleaved, backward=True)
+            return out, None, None, None, None, None, None, None, None
         dx = dx.contiguous() if not dx.is_contiguous() else dx.clone()
         K.rope_(dx.view(-1, dx.shape[-1]), pos, cos, sin, nheads, head_dim, col0=col0, rot_dim=rot_dim,
                 interleaved=interleaved, backward=True)
@@ -175,8 +187,12 @@ def rope_packed(qkv: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: to
     """
     if _lib.use_kernels(qkv):
         if inplace and not (torch.is_grad_enabled() and qkv.requires_grad) and qkv.is_contiguous():
-            K.rope_(qkv.view(-1, qkv.shape[-1]), pos.reshape(-1), cos, sin, nheads, head_dim, col0=col0,
-                    rot_dim=rot_dim, interleaved=interleaved)
+            q2 = qkv.view(-1, qkv.shape[-1])
+            if K.rope_copy_supported(q2, cos, sin, nheads, head_dim, col0, rot_dim):
+                K.rope_copy(q2, q2, pos.reshape(-1), cos, sin, nheads, head_dim, col0=col0, interleaved=interleaved)
+            else:
+                K.rope_(q2, pos.reshape(-1), cos, sin, nheads, head_dim, col0=col0, rot_dim=rot_dim,
+                        interleaved=interleaved)
             return qkv
         return _RopeFn.apply(qkv, pos.reshape(-1), cos, sin, nheads, head_dim, col0, rot_dim, interleaved)
     T = qkv.reshape(-1, qkv.shape[-1]).shape[0]

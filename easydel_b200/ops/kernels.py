@@ -268,6 +268,33 @@ def rope_(x: torch.Tensor, pos: torch.Tensor | None, cos: torch.Tensor, sin: tor
     return x
 
 
+def rope_copy_supported(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, nheads: int, head_dim: int, col0: int,
+                        rot_dim: int | None) -> bool:
+    """Whether :func:`rope_copy` takes this layout (full-width rotation, 16-byte aligned rows and tables)."""
+    return (x.dim() == 2 and x.stride(1) == 1 and x.dtype == torch.bfloat16 and (rot_dim or head_dim) == head_dim
+            and head_dim % 16 == 0 and col0 % 8 == 0 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and cos.data_ptr() % 16 == 0 and sin.data_ptr() % 16 == 0
+            and col0 + nheads * head_dim <= x.shape[1])
+
+
+def rope_copy(x: torch.Tensor, out: torch.Tensor, pos: torch.Tensor | None, cos: torch.Tensor, sin: torch.Tensor,
+              nheads: int, head_dim: int, col0: int = 0, interleaved: bool = False,
+              backward: bool = False) -> torch.Tensor:
+    """Rotary embedding of ``nheads`` full heads from ``x`` into ``out`` (same shape; may be ``x`` itself) in one
+    vectorised pass; columns outside the rotated heads are copied. Layout rules: :func:`rope_copy_supported`."""
+    assert out.shape == x.shape and out.dtype == x.dtype and out.stride(1) == 1 and out.stride(0) % 8 == 0
+    assert out.data_ptr() % 16 == 0
+    assert cos.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+    assert cos.shape[-1] == head_dim // 2, (cos.shape, head_dim)
+    if pos is not None:
+        pos = pos.reshape(-1).to(torch.int32)
+        assert pos.numel() == x.shape[0]
+    _lib.call("edl_rope_copy", x.data_ptr(), out.data_ptr(), _lib.ptr(pos), cos.data_ptr(), sin.data_ptr(),
+              x.shape[0], nheads, head_dim, x.stride(0), out.stride(0), x.shape[1], col0, int(interleaved),
+              int(backward), cos.shape[0], _lib.stream_ptr())
+    return out
+
+
 def embed_fwd(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     ids1 = ids.reshape(-1).to(torch.int64).contiguous()
     V, D = table.shape

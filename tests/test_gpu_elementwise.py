@@ -80,6 +80,53 @@ def test_rope(interleaved):
     assert torch.allclose(out.float(), qkv.float(), atol=6e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("col0", [0, 128])
+def test_rope_vector_copy(interleaved, col0):
+    """The one-pass vector form (rotate the heads, copy the other columns) against the scalar in-place kernel, out of
+    place and in place, forward and transpose, and through autograd."""
+    from easydel_b200.ops import functional as F
+    from easydel_b200.ops import kernels as K
+
+    T, H, Hkv, D = 203, 8, 2, 128
+    width = col0 + (H + 2 * Hkv) * D
+    qkv = _bf(T, width, seed=17)
+    pos = torch.randint(0, 1024, (T,), device="cuda")
+    inv = 1.0 / (500000 ** (torch.arange(0, D, 2, device="cuda").float() / D))
+    ang = torch.arange(1024, device="cuda").float()[:, None] * inv[None]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    assert K.rope_copy_supported(qkv, cos, sin, H + Hkv, D, col0, None)
+    rot = slice(col0, col0 + (H + Hkv) * D)
+
+    def same(a, b):
+        # rotated columns: the two kernels may contract their multiply-adds differently (one bf16 ulp); the copied
+        # columns are bit-identical
+        keep = torch.ones(width, dtype=torch.bool, device="cuda")
+        keep[rot] = False
+        return (torch.allclose(a[:, rot].float(), b[:, rot].float(), atol=4e-2, rtol=2e-2)
+                and torch.equal(a[:, keep], b[:, keep]))
+
+    for backward in (False, True):
+        ref = qkv.clone()
+        K.rope_(ref, pos, cos, sin, H + Hkv, D, col0=col0, interleaved=interleaved, backward=backward)
+        out = torch.full_like(qkv, float("nan"))
+        K.rope_copy(qkv, out, pos, cos, sin, H + Hkv, D, col0=col0, interleaved=interleaved, backward=backward)
+        assert same(out, ref)
+        inplace = qkv.clone()
+        K.rope_copy(inplace, inplace, pos, cos, sin, H + Hkv, D, col0=col0, interleaved=interleaved, backward=backward)
+        assert same(inplace, ref)
+    x = qkv.clone().requires_grad_(True)
+    y = F.rope_packed(x, pos, cos, sin, H + Hkv, D, col0=col0, interleaved=interleaved)
+    ref = qkv.clone()
+    K.rope_(ref, pos, cos, sin, H + Hkv, D, col0=col0, interleaved=interleaved)
+    assert same(y.detach(), ref)
+    dy = _bf(T, width, seed=18)
+    y.backward(dy)
+    dref = dy.clone()
+    K.rope_(dref, pos, cos, sin, H + Hkv, D, col0=col0, interleaved=interleaved, backward=True)
+    assert same(x.grad, dref)
+
+
 def test_embedding():
     from easydel_b200.ops import kernels as K
 
