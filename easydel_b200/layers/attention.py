@@ -131,10 +131,7 @@ class Attention(nn.Module):
     def _split(self, qkv: torch.Tensor):
         B, T, _ = qkv.shape
         Hq, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
-        q = qkv[..., : Hq * D].view(B, T, Hq, D)
-        k = qkv[..., Hq * D:(Hq + Hkv) * D].view(B, T, Hkv, D)
-        v = qkv[..., (Hq + Hkv) * D:].view(B, T, Hkv, D)
-        return q, k, v
+        return F.split_qkv(qkv, Hq, Hkv, D)
 
     def _apply_qk_norm(self, qkv: torch.Tensor) -> torch.Tensor:
         B, T, W = qkv.shape

@@ -112,8 +112,15 @@ class _FlashAttnFn(torch.autograd.Function):
         # With sinks the forward's log-sum-exp already counts the sink logit, so P = exp(S - lse) recomputed by the
         # backward kernels is the true probability and dq / dk / dv need nothing else. The sink itself has a zero
         # value row, hence dP_sink = 0 and d sink[h] = sum_rows P_sink * (0 - delta) = -sum exp(sink - lse) * delta.
+        bufs = {}
+        if q.dim() == 4 and k.shape[:2] == q.shape[:2] and k.dtype == q.dtype and v.dtype == q.dtype:
+            # the three gradients as slices of one packed buffer: a packed projection's backward takes it as it is
+            from .functional import packed_qkv_buffers
+
+            _, bufs["dq"], bufs["dk"], bufs["dv"] = packed_qkv_buffers(q.shape[0], q.shape[1], q.shape[2], k.shape[2],
+                                                                       q.shape[3], q.dtype, q.device)
         dq, dk, dv, delta = attn_bwd(q, k, v, o, lse, do, causal=causal, scale=scale, window=window, softcap=softcap,
-                                     cu_q=cu, cu_k=cu, max_q=max_len, max_k=max_len, want_delta=True)
+                                     cu_q=cu, cu_k=cu, max_q=max_len, max_k=max_len, want_delta=True, **bufs)
         dsinks = None
         if sinks is not None and ctx.needs_input_grad[7]:
             dsinks = -(torch.exp(sinks.float()[:, None] - lse) * delta).sum(1).to(sinks.dtype)

@@ -177,6 +177,78 @@ class _RopeFn(torch.autograd.Function):
         return dx, None, None, None, None, None, None, None, None
 
 
+class _SplitQKVFn(torch.autograd.Function):
+    """``[B, T, (Hq + 2 Hkv) D]`` -> views ``q [B, T, Hq, D]``, ``k``, ``v [B, T, Hkv, D]``.
+
+    Autograd's own backward of three slices fills three zero tensors of the packed size, copies a slice into each
+    and adds them up (eight passes over the packed gradient). Here the three incoming gradients are either already
+    the slices of one packed buffer (the attention backward allocates them that way: nothing is copied) or are
+    concatenated in one pass."""
+
+    @staticmethod
+    def forward(ctx, qkv, Hq, Hkv, D):
+        ctx.dims = (Hq, Hkv, D, qkv.shape, qkv.dtype, qkv.device)
+        ctx.set_materialize_grads(False)
+        B, T, _ = qkv.shape
+        q = qkv[..., : Hq * D].view(B, T, Hq, D)
+        k = qkv[..., Hq * D:(Hq + Hkv) * D].view(B, T, Hkv, D)
+        v = qkv[..., (Hq + Hkv) * D:].view(B, T, Hkv, D)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        Hq, Hkv, D, shape, dtype, device = ctx.dims
+        B, T, W = shape
+        if dq is not None and dk is not None and dv is not None:
+            packed = packed_qkv_base(dq, dk, dv, B, T, Hq, Hkv, D)
+            if packed is not None:
+                return packed, None, None, None
+        parts = []
+        for g, H in ((dq, Hq), (dk, Hkv), (dv, Hkv)):
+            parts.append(torch.zeros(B, T, H * D, dtype=dtype, device=device) if g is None
+                         else g.reshape(B, T, H * D).to(dtype))
+        return torch.cat(parts, dim=-1), None, None, None
+
+
+def packed_qkv_buffers(B: int, T: int, Hq: int, Hkv: int, D: int, dtype, device):
+    """One ``[B, T, (Hq + 2 Hkv) D]`` buffer and its three head-shaped views (see :class:`_SplitQKVFn`)."""
+    base = torch.empty(B, T, (Hq + 2 * Hkv) * D, dtype=dtype, device=device)
+    q = base[..., : Hq * D].view(B, T, Hq, D)
+    k = base[..., Hq * D:(Hq + Hkv) * D].view(B, T, Hkv, D)
+    v = base[..., (Hq + Hkv) * D:].view(B, T, Hkv, D)
+    return base, q, k, v
+
+
+def packed_qkv_base(q, k, v, B, T, Hq, Hkv, D):
+    """The packed tensor whose slices ``q``, ``k``, ``v`` are, or None when they do not lie that way in memory."""
+    W = (Hq + 2 * Hkv) * D
+    want = (T * W, W, D, 1)
+    try:
+        same = (q.untyped_storage().data_ptr() == k.untyped_storage().data_ptr() == v.untyped_storage().data_ptr())
+    except Exception:
+        return None
+    if not same or q.dtype != k.dtype or q.dtype != v.dtype:
+        return None
+    o = q.storage_offset()
+    if k.storage_offset() != o + Hq * D or v.storage_offset() != o + (Hq + Hkv) * D:
+        return None
+    for t, H in ((q, Hq), (k, Hkv), (v, Hkv)):
+        if tuple(t.shape) != (B, T, H, D):
+            return None
+        if any(st != w for st, w, n in zip(t.stride(), want, t.shape) if n > 1):
+            return None
+    return q.as_strided((B, T, W), (T * W, W, 1), o)
+
+
+def split_qkv(qkv: torch.Tensor, Hq: int, Hkv: int, D: int):
+    """Head-shaped views of a packed projection output; differentiable without the zero-fill / add passes."""
+    if qkv.dim() == 3 and qkv.is_contiguous() and torch.is_grad_enabled() and qkv.requires_grad:
+        return _SplitQKVFn.apply(qkv, Hq, Hkv, D)
+    B, T, _ = qkv.shape
+    return (qkv[..., : Hq * D].view(B, T, Hq, D), qkv[..., Hq * D:(Hq + Hkv) * D].view(B, T, Hkv, D),
+            qkv[..., (Hq + Hkv) * D:].view(B, T, Hkv, D))
+
+
 def rope_packed(qkv: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, nheads: int,
                 head_dim: int, col0: int = 0, rot_dim: int | None = None, interleaved: bool = False,
                 inplace: bool = False):
