@@ -318,11 +318,11 @@ class eSurge:
         ids, text = self._tokenize(prompt)
         if not ids:
             raise ValueError("empty prompt")
-        mm_embeds, mm_hash = [], None
+        mm_embeds, mm_hash, rope = [], None, None
         if images or videos:
             if self.multimodal is None:
                 raise ValueError("this model has no vision tower: images cannot be served")
-            ids, mm_embeds, mm_hash = self.multimodal.prepare(ids, images, videos)
+            ids, mm_embeds, mm_hash, rope = self.multimodal.prepare(ids, images, videos, with_rope=True)
             if len(ids) > self.max_model_len - self.reserve_tokens:
                 raise ValueError(f"prompt with images has {len(ids)} tokens; max_model_len is {self.max_model_len}")
         limit = self.max_model_len - self.reserve_tokens
@@ -331,6 +331,7 @@ class eSurge:
             if len(ids) > limit:
                 if not self.auto_truncate_prompt:
                     raise ValueError(f"prompt has {len(ids)} tokens; max_model_len is {self.max_model_len}")
+                rope = None     # a truncated prompt keeps consecutive positions
                 keep = limit
                 if self.truncate_mode == "left":
                     ids = ids[-keep:]
@@ -343,6 +344,8 @@ class eSurge:
         rid = request_id or f"req-{next(self._ids)}"
         req = EngineRequest(rid, ids, sp, eos_token_id=self.eos_token_id, priority=priority, mm_embeds=mm_embeds,
                             mm_hash=mm_hash)
+        if rope is not None:
+            req.rope_positions, req.rope_delta = rope
         tr = _Tracked(req, text, IncrementalDetokenizer(self.tokenizer if sp.detokenize else None,
                                                         sp.skip_special_tokens))
         with self._work:
@@ -514,9 +517,9 @@ class eSurge:
 
     def generate(self, prompts, sampling_params: SamplingParams | list[SamplingParams] | None = None,
                  request_id: str | list[str] | None = None, use_tqdm: bool = False,
-                 images: list | None = None) -> list[RequestOutput]:
-        """Blocking batch generation. Works with or without the background thread. ``images``: the images of the
-        prompt (or one list per prompt), one per image placeholder token."""
+                 images: list | None = None, videos: list | None = None) -> list[RequestOutput]:
+        """Blocking batch generation. Works with or without the background thread. ``images`` / ``videos``: the
+        images / frame stacks of the prompt (or one list per prompt), one per placeholder token."""
         single = isinstance(prompts, str) or (isinstance(prompts, (list, tuple)) and prompts
                                               and isinstance(prompts[0], int))
         plist = [prompts] if single else list(prompts)
@@ -526,7 +529,9 @@ class eSurge:
             imgs = [None] * len(plist)
         else:
             imgs = [images] if single else list(images)
-        ids = [self.add_request(p, sp, rid, images=im) for p, sp, rid, im in zip(plist, sps, rids, imgs)]
+        vids = [None] * len(plist) if videos is None else ([videos] if single else list(videos))
+        ids = [self.add_request(p, sp, rid, images=im, videos=vd)
+               for p, sp, rid, im, vd in zip(plist, sps, rids, imgs, vids)]
         self._drive(lambda: all(self._tracked[i].finished for i in ids))
         outs = [self._snapshot(self._tracked.pop(i), True) for i in ids]
         return outs
@@ -540,9 +545,9 @@ class eSurge:
                 break
 
     def stream(self, prompt, sampling_params: SamplingParams | None = None, request_id: str | None = None,
-               images: list | None = None) -> tp.Iterator[RequestOutput]:
+               images: list | None = None, videos: list | None = None) -> tp.Iterator[RequestOutput]:
         """Yields a ``RequestOutput`` whenever new tokens arrive (``delta_text`` holds the increment)."""
-        rid = self.add_request(prompt, sampling_params, request_id, images=images)
+        rid = self.add_request(prompt, sampling_params, request_id, images=images, videos=videos)
         tr = self._tracked[rid]
         background = self._thread is not None and self._thread.is_alive()
         try:

@@ -45,6 +45,7 @@ class MultiModalFeature:
     pixel_values: torch.Tensor | None = None           # [3, H, W], dropped once the embeddings exist
     embeddings: torch.Tensor | None = None             # [rows, hidden] on the model's device
     placeholder: PlaceholderRange | None = None
+    grid: tuple | None = None                          # (t, h, w) in patches, towers that take flattened patches
 
     @classmethod
     def from_image(cls, pixel_values: torch.Tensor) -> "MultiModalFeature":
@@ -337,12 +338,14 @@ class MultiModalManager:
         for f in feats:
             if f.embeddings is None:
                 f.embeddings = todo[f.mm_hash].embeddings
+            self.grid_of(f)
             f.clear_pixel_values()
         return feats
 
     def _encode_flat(self, f: MultiModalFeature, dev) -> None:
         frames = f.pixel_values if f.pixel_values.dim() == 4 else f.pixel_values[None]
         rows, grid = self.patchify(frames)
+        f.grid = tuple(int(g) for g in grid)
         grid_t = torch.tensor([grid], device=dev)
         fn = self.model.get_video_features if (f.modality == "video" and hasattr(self.model, "get_video_features")) \
             else self.model.get_image_features
@@ -364,6 +367,7 @@ class MultiModalManager:
                 f.embeddings = hit
             else:
                 self._encode_flat(f, dev)
+            self.grid_of(f)
             f.clear_pixel_values()
             feats.append(f)
         return feats
@@ -407,23 +411,72 @@ class MultiModalManager:
                 raise ValueError(f"{len(feats)} media items for {used[ph]} placeholders of token {ph} in the prompt")
         return out
 
-    def prepare(self, token_ids: tp.Sequence[int], images: tp.Sequence[tp.Any] | None = None,
-                videos: tp.Sequence[tp.Any] | None = None):
-        """-> (expanded token ids, [(offset, embeddings)], extra hash key) for ``eSurge.add_request``.
+    def grid_of(self, f: MultiModalFeature) -> tuple | None:
+        """(t, h, w) patch grid of a feature of a flattened-patch tower (kept on the feature; recomputed from the
+        number of rows and the frame shape when the embeddings came from the cache)."""
+        if f.grid is None and self.flat_patch and f.pixel_values is not None:
+            frames = f.pixel_values if f.pixel_values.dim() == 4 else f.pixel_values[None]
+            vc = self.model.config.vision_config
+            t = -(-frames.shape[0] // vc.temporal_patch_size)
+            f.grid = (int(t), int(frames.shape[-2] // vc.patch_size), int(frames.shape[-1] // vc.patch_size))
+        return f.grid
 
-        The engine numbers all tokens of a request consecutively; models whose rotary embedding gives vision tokens
-        grid positions (three position streams) therefore see the text after an image later than in
-        ``model.generate``, which computes the grid positions."""
+    def rope_positions(self, num_tokens: int, feats: tp.Sequence[MultiModalFeature]):
+        """Three-stream rotary positions of a prompt whose vision placeholders are ``feats``: text advances all three
+        streams together, a vision run takes (temporal, row, column) indices from where the text stopped and the
+        text after it continues from the largest of them (the arithmetic of ``mrope_positions`` in
+        ``modules/qwen2_vl``). -> (``[3, num_tokens]`` int32, offset of generated tokens from their index)."""
+        import numpy as np
+
+        m = int(self.model.config.vision_config.spatial_merge_size)
+        pos = np.zeros((3, num_tokens), dtype=np.int32)
+        cur, i = 0, 0
+        for f in sorted(feats, key=lambda f: f.placeholder.offset):
+            a = f.placeholder.offset
+            if a > i:
+                pos[:, i:a] = cur + np.arange(a - i, dtype=np.int32)
+                cur += a - i
+            t, h, w = f.grid
+            gh, gw = h // m, w // m
+            n = t * gh * gw
+            if n != f.placeholder.length:
+                raise ValueError(f"vision run of {f.placeholder.length} tokens does not match its grid {f.grid}")
+            ti, hi, wi = np.meshgrid(np.arange(t), np.arange(gh), np.arange(gw), indexing="ij")
+            pos[:, a:a + n] = cur + np.stack([ti.reshape(-1), hi.reshape(-1), wi.reshape(-1)]).astype(np.int32)
+            cur += max(t, gh, gw)
+            i = a + n
+        if i < num_tokens:
+            pos[:, i:] = cur + np.arange(num_tokens - i, dtype=np.int32)
+            cur += num_tokens - i
+        return pos, int(cur - num_tokens)
+
+    @property
+    def three_stream_rotary(self) -> bool:
+        """Whether the language model rotates with three position streams (vision tokens at grid coordinates)."""
+        cfg = getattr(self.model.config, "text_config", None) or self.model.config
+        rs = getattr(cfg, "rope_scaling", None) or getattr(self.model.config, "rope_scaling", None) or {}
+        return self.flat_patch and isinstance(rs, dict) and "mrope_section" in rs
+
+    def prepare(self, token_ids: tp.Sequence[int], images: tp.Sequence[tp.Any] | None = None,
+                videos: tp.Sequence[tp.Any] | None = None, with_rope: bool = False):
+        """-> (expanded token ids, [(offset, embeddings)], extra hash key) for ``eSurge.add_request``; with
+        ``with_rope`` a fourth item: ``(positions [3, tokens], delta)`` for three-stream rotary models (None for
+        the others), so that the engine rotates vision tokens at their grid coordinates as ``model.generate`` does."""
         feats = self.process_images_to_features(images) if images else []
         vfeats = self.process_videos_to_features(videos) if videos else []
         by_token = {}
+        want_rope = with_rope and self.three_stream_rotary
         if feats:
             by_token[self.image_token_id] = feats
         if vfeats:
             by_token[self.video_token_id] = vfeats
         ids = self._expand(list(token_ids), by_token) if by_token else list(token_ids)
         allf = sorted(feats + vfeats, key=lambda f: f.placeholder.offset)
-        return ids, [(f.placeholder.offset, f.embeddings) for f in allf], tuple(f.mm_hash for f in allf)
+        out = (ids, [(f.placeholder.offset, f.embeddings) for f in allf], tuple(f.mm_hash for f in allf))
+        if not with_rope:
+            return out
+        rope = self.rope_positions(len(ids), allf) if want_rope and all(f.grid is not None for f in allf) else None
+        return (*out, rope)
 
     def tokenize_multimodal(self, messages: list[dict], images: tp.Sequence[tp.Any] | None = None, **template_kw):
         if self.tokenizer is None:

@@ -44,6 +44,14 @@ class ModelRunner:
         self.num_groups = getattr(cache, "num_groups", 1)
         for _ in range(self.num_groups - 1):
             self._sizes += [T, B * MP]
+        # models that rotate with three position streams (vision tokens at grid coordinates): [3, T] rotary positions
+        # beside the token indices, which keep addressing the cache
+        cfg = getattr(model.config, "text_config", None) or model.config
+        rs = getattr(cfg, "rope_scaling", None) or getattr(model.config, "rope_scaling", None) or {}
+        self.rope3 = isinstance(rs, dict) and "mrope_section" in rs
+        self._rope_idx = len(self._sizes) if self.rope3 else -1
+        if self.rope3:
+            self._sizes.append(3 * T)
         total = sum(self._sizes)
         self._host = torch.zeros(total, dtype=torch.int32, pin_memory=pin)
         self._dev = torch.zeros(total, dtype=torch.int32, device=dev)
@@ -163,14 +171,18 @@ class ModelRunner:
             meta.group_tables = [extra[2 * g + 1].view(self.max_num_seqs, MP)[:B] for g in range(self.num_groups - 1)]
         self.cache.step_meta = meta
         model = self._lm
+        if self.rope3:
+            d_pos = self._dviews[self._rope_idx].view(3, self.max_tokens)[:, :T][:, None, :]   # [3, 1, T]
+        else:
+            d_pos = d_pos[:T][None]
         if mm_rows:
             emb = model.get_input_embeddings()(d_ids[:T].long())
             for row0, feats in mm_rows:
                 emb[row0:row0 + feats.shape[0]] = feats.to(emb.dtype)
-            res = model(inputs_embeds=emb[None], position_ids=d_pos[:T][None], past_key_values=self.cache,
+            res = model(inputs_embeds=emb[None], position_ids=d_pos, past_key_values=self.cache,
                         cache_metadata=meta, apply_lm_head=False)
         else:
-            res = model(input_ids=d_ids[:T][None].long(), position_ids=d_pos[:T][None], past_key_values=self.cache,
+            res = model(input_ids=d_ids[:T][None].long(), position_ids=d_pos, past_key_values=self.cache,
                         cache_metadata=meta, apply_lm_head=False)
         rows = S.gather_rows(res.last_hidden_state[0], d_last[:B])
         if self.tp_group is not None and hasattr(model, "apply_lm_head_vocab_parallel"):
@@ -256,6 +268,7 @@ class ModelRunner:
         ids_np, pos_np, slots_np = ids.numpy(), pos.numpy(), slots.numpy()
         table_np = table.numpy().reshape(self.max_num_seqs, MP)
         cu_np, kv_np, last_np = cu_q.numpy(), kv_lens.numpy(), last_idx.numpy()
+        rope_np = self._hviews[self._rope_idx].numpy().reshape(3, self.max_tokens) if self.rope3 else None
         o = 0
         max_q = 0
         cu_np[0] = 0
@@ -280,6 +293,8 @@ class ModelRunner:
             p = np.fromiter((s.start for s in sched), dtype=np.int32, count=B)
             ids_np[:B] = np.fromiter((s.request.output_token_ids[-1] for s in sched), dtype=np.int32, count=B)
             pos_np[:B] = p
+            if rope_np is not None:
+                rope_np[:, :B] = p + np.fromiter((s.request.rope_delta for s in sched), dtype=np.int32, count=B)
             slotof_np[:B] = slot_idx
             on_dev = np.nonzero(ids_np[:B] < 0)[0]          # tokens sampled by a step that was not read back yet
             nfix = len(on_dev)
@@ -322,6 +337,11 @@ class ModelRunner:
                     mm_rows.append((o + a - st, feats[a - off:z - off]))
             p = np.arange(st, st + n, dtype=np.int32)
             pos_np[o:o + n] = p
+            if rope_np is not None:
+                rope_np[:, o:o + n] = p + req.rope_delta
+                if req.rope_positions is not None and st < npt:       # prompt tokens carry their grid positions
+                    z = min(st + n, npt)
+                    rope_np[:, o:o + z - st] = req.rope_positions[:, st:z]
             pg = np.asarray(req.pages, dtype=np.int32)
             slots_np[o:o + n] = pg[p // PAGE_SIZE] * PAGE_SIZE + p % PAGE_SIZE
             table_np[b, :len(pg)] = pg
@@ -349,6 +369,8 @@ class ModelRunner:
             if Bp > B:   # pad rows: token 0 at position 0 written to the null page, attending to one key
                 ids_np[B:Bp] = 0
                 pos_np[B:Bp] = 0
+                if rope_np is not None:
+                    rope_np[:, B:Bp] = 0
                 slots_np[B:Bp] = 0
                 table_np[B:Bp, :] = 0
                 kv_np[B:Bp] = 1

@@ -67,6 +67,10 @@ class EngineRequest:
     # images: (offset of the first placeholder token in the prompt, projected features [rows, hidden] on the device)
     mm_embeds: list = field(default_factory=list)
     mm_hash: tp.Any = None                # joins the page hashes: same tokens + other images = other pages
+    # three-stream rotary models: [3, prompt length] int32 rotary positions of the prompt (vision tokens carry grid
+    # coordinates) and the offset a generated token's rotary position has from its index; None = index everywhere
+    rope_positions: tp.Any = None
+    rope_delta: int = 0
     # asynchronous scheduling: the request reached its length limit with a token that is still on the device;
     # it is not scheduled again and finishes when that token is committed
     finishing: bool = False

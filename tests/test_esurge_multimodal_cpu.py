@@ -125,3 +125,75 @@ def test_flat_patch_tower_images_and_videos_expand_in_one_pass():
         direct = model.get_video_features(rows, video_grid_thw=torch.tensor([grid]))
     torch.testing.assert_close(embeds[0][1], direct)
     assert len(key) == 2
+
+
+def test_three_stream_rotary_positions_through_the_engine():
+    """Qwen2-VL style rotary: vision tokens sit at (temporal, row, column) coordinates and the text after them
+    continues from the largest. The manager computes the same positions as the model's own routine, the runner
+    stages them beside the token indices (chunked prefill across the vision runs included), and the engine's greedy
+    tokens equal a plain forward loop of the model that is handed those positions."""
+    from easydel_b200.modules.qwen2_vl import Qwen2VLConfig, Qwen2VLForConditionalGeneration, mrope_positions
+
+    V = dict(depth=1, embed_dim=32, hidden_size=32, num_heads=4, in_channels=3, patch_size=4, spatial_merge_size=2,
+             temporal_patch_size=2, mlp_ratio=2)
+    T = dict(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, max_position_embeddings=512, eos_token_id=125,
+             rope_scaling={"type": "mrope", "mrope_section": [2, 1, 1]})
+    NTOK = 24
+    torch.manual_seed(0)
+    model = Qwen2VLForConditionalGeneration(Qwen2VLConfig(vision_config=V, text_config=T, image_token_id=127,
+                                                          video_token_id=126), dtype=torch.float32).eval()
+    rng = np.random.default_rng(1)
+    image = rng.integers(0, 255, (16, 24, 3), dtype=np.uint8)
+    video = rng.integers(0, 255, (4, 16, 16, 3), dtype=np.uint8)
+    prompt = [5, 9, 126, 6, 11, 127, 7, 8]
+    eng = eSurge(model, max_model_len=256, max_num_seqs=2, max_num_batched_tokens=8, hbm_utilization=0.05,
+                 enable_prefix_caching=False)
+    try:
+        mgr = eng.multimodal
+        mgr.resolution_buckets = [(16, 16), (24, 16)]
+        ids, embeds, _, rope = mgr.prepare(prompt, images=[image], videos=[video], with_rope=True)
+        assert rope is not None
+        pos, delta = rope
+        # the model's own routine on the expanded ids and the grids of the two runs
+        grids = {o: None for o, _ in embeds}
+        _, vg = mgr.patchify(torch.stack(mgr.process_images(list(video))))
+        _, ig = mgr.patchify(mgr.process_images([image])[0][None])
+        vid_grid, img_grid = torch.tensor([list(vg)]), torch.tensor([list(ig)])
+        assert vg[0] == 2 and ig[0] == 1
+        want, want_delta = mrope_positions(torch.tensor([ids]), 127, img_grid, 2, video_token_id=126,
+                                           video_grid_thw=vid_grid)
+        assert np.array_equal(pos, want[:, 0].numpy()) and delta == int(want_delta[0])
+        assert delta < 0 and len(grids) == 2          # vision runs advance the position by less than their length
+        out = eng.generate(prompt, SamplingParams(max_tokens=NTOK, temperature=0.0, ignore_eos=True), images=[image],
+                           videos=[video])[0]
+        got = list(out.outputs[0].token_ids)
+    finally:
+        eng.close()
+    # reference: full forward passes of the language model on the spliced embeddings with those positions
+    lm = model.language_model
+    toks = list(ids)
+    ref = []
+    with torch.no_grad():
+        for _ in range(NTOK):
+            n = len(toks)
+            emb = lm.get_input_embeddings()(torch.tensor([toks]))
+            for off, feats in embeds:
+                emb[0, off:off + feats.shape[0]] = feats
+            p = torch.zeros(3, 1, n, dtype=torch.long)
+            p[:, 0, :len(ids)] = torch.from_numpy(pos).long()
+            if n > len(ids):
+                p[:, 0, len(ids):] = torch.arange(len(ids), n) + delta
+            logits = lm(inputs_embeds=emb, position_ids=p).logits
+            nxt = int(logits[0, -1].argmax())
+            ref.append(nxt)
+            toks.append(nxt)
+    assert got == ref
+    # the positions matter to this model: consecutive numbering changes the logits of the first generated token
+    with torch.no_grad():
+        emb = lm.get_input_embeddings()(torch.tensor([ids]))
+        for off, feats in embeds:
+            emb[0, off:off + feats.shape[0]] = feats
+        a = lm(inputs_embeds=emb, position_ids=torch.from_numpy(pos).long()[:, None]).logits[0, -1]
+        b = lm(inputs_embeds=emb, position_ids=torch.arange(len(ids))[None]).logits[0, -1]
+    assert (a - b).abs().max() > 1e-4
