@@ -134,6 +134,7 @@ class Scheduler:
         self.config, self.pool, self.page_size = config, self.kv.pool, page_size
         self.waiting: collections.deque[EngineRequest] = collections.deque()
         self.running: list[EngineRequest] = []
+        self.num_preemptions = 0          # requests pushed back to the waiting queue since the scheduler was built
         self.requests: dict[str, EngineRequest] = {}
         self.finished_ids: list[str] = []
 
@@ -186,6 +187,7 @@ class Scheduler:
         req.status = RequestStatus.PREEMPTED
         req.num_computed_tokens = 0
         req.num_preemptions += 1
+        self.num_preemptions += 1
         self.running.remove(req)
         self.waiting.appendleft(req)
 

@@ -71,3 +71,59 @@ def test_engine_runs_mixed_batches_and_prefix_cache():
     assert a == b and len(a) == 8
     m = eng.get_metrics_summary()
     assert m["requests_completed"] == 7 and m["ttft_p50"] is not None
+
+
+def test_preemption_chunked_prefix_hit_and_bucket_padding_on_the_gpu():
+    """Three scheduler situations on the kernels: (a) a page pool too small for all requests, so that the newest is
+    preempted and recomputed; (b) a prompt that hits the prefix cache and is then prefilled in chunks smaller than
+    the rest of it; (c) three decode rows replayed from the four-row graph bucket (one padding row). In each, greedy
+    continuations must agree with the same request served alone by a roomy engine (first tokens exactly; later
+    ones may flip on bf16 near-ties, so agreement of most positions is asked for)."""
+    from easydel_b200.inference import SamplingParams
+    from easydel_b200.inference.esurge import eSurge
+
+    model = _model()
+    g = torch.Generator().manual_seed(11)
+    shared = torch.randint(0, 4000, (384,), generator=g).tolist()
+    prompts = [shared + torch.randint(0, 4000, (n,), generator=g).tolist() for n in (116, 121, 126)]   # 500, 505, 510 tokens
+    sp = SamplingParams(max_tokens=40, temperature=0.0, ignore_eos=True)
+
+    def alone(prompt):
+        eng = eSurge(model, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=1024, num_pages=32,
+                     enable_prefix_caching=False)
+        try:
+            return eng.generate([prompt], sp)[0].outputs[0].token_ids
+        finally:
+            eng.close()
+
+    want = [alone(p) for p in prompts]
+
+    def agree(a, b):
+        assert len(a) == len(b) == 40 and a[:2] == b[:2], (a[:4], b[:4])
+        assert sum(x == y for x, y in zip(a, b)) >= 30 or a[:8] == b[:8]
+
+    # (a) all three fit at admission (4 pages of 128 tokens each, 13 usable pages) and each crosses into a fifth page
+    # while decoding, which the pool cannot give to all of them
+    tight = eSurge(model, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=1024, num_pages=14,
+                   enable_prefix_caching=False)
+    try:
+        outs = tight.generate(prompts, sp)
+        assert tight.scheduler.num_preemptions >= 1
+        for o, w in zip(outs, want):
+            agree(o.outputs[0].token_ids, w)
+    finally:
+        tight.close()
+    # (b) prefix hit of three pages, then the rest of the prompt in chunks of 64 tokens; (c) three rows -> bucket 4
+    eng = eSurge(model, max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=64, num_pages=48)
+    try:
+        first = eng.generate([prompts[0]], sp)[0]
+        agree(first.outputs[0].token_ids, want[0])
+        hit = eng.generate([prompts[1]], sp)[0]
+        assert hit.num_cached_tokens == 384
+        agree(hit.outputs[0].token_ids, want[1])
+        outs = eng.generate(prompts, sp)
+        assert eng.runner.timings["graph_steps"] > 0 and 4 in eng.runner._graphs
+        for o, w in zip(outs, want):
+            agree(o.outputs[0].token_ids, w)
+    finally:
+        eng.close()
