@@ -226,12 +226,35 @@ namespace {
 constexpr int ARN_THREADS = 256;
 constexpr int ARN_MAX_VEC = 8;   // uint4 vectors per thread: width <= 256 * 8 * 8 = 16384
 
-__global__ void __launch_bounds__(ARN_THREADS)
+// Multicast (NVLink switch) addresses of the partial and of the two output regions of the kernels below, or zeros: with them the sum over ranks is one
+// `multimem.ld_reduce` (the switch adds the eight partials, fp32 accumulation, bf16 result) instead of one load per
+// peer, and a row is handed to every rank by one `multimem.st` instead of one store per peer.
+struct McPtrs {
+  unsigned long long data, x_out, h_out;
+};
+__device__ __forceinline__ uint4 multimem_sum_bf16x8(unsigned long long addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_store16(unsigned long long addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// THREADS x MAXV uint4 vectors cover a row; every peer load of a row is issued before the first sum (a load is one
+// NVLink round trip), or the sum is one `multimem.ld_reduce` when `mc_data` is given.
+template <int THREADS, int MAXV>
+__global__ void __launch_bounds__(THREADS, 1)
 allreduce_add_rmsnorm_kernel(PeerPtrs data, PeerPtrs flags, int nranks, int rank, int* sync,
                              const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ weight,
                              float eps, float w_offset, __nv_bfloat16* __restrict__ x_out,
                              __nv_bfloat16* __restrict__ h_out, int rows, int width, long long spin_limit,
-                             int* status) {
+                             int* status, unsigned long long mc_data) {
   __shared__ int s_ok;
   __shared__ float red[32];
   const int epoch = *reinterpret_cast<volatile int*>(sync) + 1;
@@ -256,39 +279,74 @@ allreduce_add_rmsnorm_kernel(PeerPtrs data, PeerPtrs flags, int nranks, int rank
   const int vec_per_row = width / 8;
   if (s_ok) {
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-      float v[ARN_MAX_VEC][8];
+      float v[MAXV][8];
       float ss = 0.f;
+      float a[MAXV][8];
 #pragma unroll
-      for (int j = 0; j < ARN_MAX_VEC; ++j) {
-        const int c = threadIdx.x + j * ARN_THREADS;
+      for (int j = 0; j < MAXV; ++j)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[j][e] = 0.f;
+      if (mc_data) {
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+          const int c = threadIdx.x + j * THREADS;
+          if (c < vec_per_row) {
+            const uint4 sum = multimem_sum_bf16x8(mc_data + ((long long)row * vec_per_row + c) * 16);
+            float2 f;
+            f = unpack_bf16x2(sum.x); a[j][0] = f.x; a[j][1] = f.y;
+            f = unpack_bf16x2(sum.y); a[j][2] = f.x; a[j][3] = f.y;
+            f = unpack_bf16x2(sum.z); a[j][4] = f.x; a[j][5] = f.y;
+            f = unpack_bf16x2(sum.w); a[j][6] = f.x; a[j][7] = f.y;
+          }
+        }
+      }
+      for (int g = 0; g < (mc_data ? 0 : nranks); g += 8) {
+        uint4 part[MAXV][8];
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+          const int c = threadIdx.x + j * THREADS;
+          if (c < vec_per_row) {
+            const long long off = (long long)row * vec_per_row + c;
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (g + r < nranks) part[j][r] = reinterpret_cast<const uint4*>(data.p[g + r])[off];
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+          const int c = threadIdx.x + j * THREADS;
+          if (c < vec_per_row) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+              if (g + r < nranks) {
+                float2 f;
+                f = unpack_bf16x2(part[j][r].x); a[j][0] += f.x; a[j][1] += f.y;
+                f = unpack_bf16x2(part[j][r].y); a[j][2] += f.x; a[j][3] += f.y;
+                f = unpack_bf16x2(part[j][r].z); a[j][4] += f.x; a[j][5] += f.y;
+                f = unpack_bf16x2(part[j][r].w); a[j][6] += f.x; a[j][7] += f.y;
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j) {
+        const int c = threadIdx.x + j * THREADS;
         if (c >= vec_per_row) break;
         const long long off = (long long)row * vec_per_row + c;
-        uint4 part[MAX_RANKS];
-#pragma unroll
-        for (int r = 0; r < MAX_RANKS; ++r)
-          if (r < nranks) part[r] = reinterpret_cast<const uint4*>(data.p[r])[off];
         const uint4 rs = reinterpret_cast<const uint4*>(residual)[off];
         float2 f;
         f = unpack_bf16x2(rs.x); v[j][0] = f.x; v[j][1] = f.y;
         f = unpack_bf16x2(rs.y); v[j][2] = f.x; v[j][3] = f.y;
         f = unpack_bf16x2(rs.z); v[j][4] = f.x; v[j][5] = f.y;
         f = unpack_bf16x2(rs.w); v[j][6] = f.x; v[j][7] = f.y;
-        float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int r = 0; r < MAX_RANKS; ++r) {
-          if (r >= nranks) break;
-          f = unpack_bf16x2(part[r].x); a[0] += f.x; a[1] += f.y;
-          f = unpack_bf16x2(part[r].y); a[2] += f.x; a[3] += f.y;
-          f = unpack_bf16x2(part[r].z); a[4] += f.x; a[5] += f.y;
-          f = unpack_bf16x2(part[r].w); a[6] += f.x; a[7] += f.y;
-        }
         // the sum of the partials is rounded to bf16 before it joins the residual stream, as the unfused
         // sequence (all-reduce to bf16, then add) does
         uint4 o;
         uint32_t* ow = &o.x;
 #pragma unroll
         for (int e = 0; e < 8; e += 2) {
-          const float2 y = unpack_bf16x2(pack_bf16x2(a[e], a[e + 1]));
+          const float2 y = unpack_bf16x2(pack_bf16x2(a[j][e], a[j][e + 1]));
           const uint32_t packed = pack_bf16x2(v[j][e] + y.x, v[j][e + 1] + y.y);
           ow[e >> 1] = packed;
           const float2 z = unpack_bf16x2(packed);
@@ -301,8 +359,8 @@ allreduce_add_rmsnorm_kernel(PeerPtrs data, PeerPtrs flags, int nranks, int rank
       ss = block_sum(ss, red);
       const float rstd = rsqrtf(ss / (float)width + eps);
 #pragma unroll
-      for (int j = 0; j < ARN_MAX_VEC; ++j) {
-        const int c = threadIdx.x + j * ARN_THREADS;
+      for (int j = 0; j < MAXV; ++j) {
+        const int c = threadIdx.x + j * THREADS;
         if (c >= vec_per_row) break;
         const uint4 wv = reinterpret_cast<const uint4*>(weight)[c];
         const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
@@ -332,14 +390,17 @@ allreduce_add_rmsnorm_kernel(PeerPtrs data, PeerPtrs flags, int nranks, int rank
 }  // namespace
 }  // namespace edl
 
-EDL_HOST_API int edl_allreduce_add_rmsnorm(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs,
-                                           int nranks, int rank, int* sync, const void* residual, const void* weight,
-                                           float eps, float w_offset, void* x_out, void* h_out, int rows, int width,
-                                           int wait_ms, int* status, void* stream) {
+// mc_data: multicast address of the partial (0 = one load per peer).
+EDL_HOST_API int edl_allreduce_add_rmsnorm_mc(const unsigned long long* data_ptrs,
+                                              const unsigned long long* flag_ptrs, int nranks, int rank, int* sync,
+                                              const void* residual, const void* weight, float eps, float w_offset,
+                                              void* x_out, void* h_out, int rows, int width, int wait_ms, int* status,
+                                              void* stream, unsigned long long mc_data) {
+  using namespace edl;
   if (rows <= 0) return 0;
-  if (nranks < 1 || nranks > MAX_RANKS || (width & 7) || width > ARN_THREADS * ARN_MAX_VEC * 8) {
+  if (nranks < 1 || nranks > MAX_RANKS || (width & 7) || width > 16384) {
     set_last_error("edl_allreduce_add_rmsnorm: nranks=%d, width=%d must be a multiple of 8 and <= %d", nranks, width,
-                   ARN_THREADS * ARN_MAX_VEC * 8);
+                   16384);
     return -1;
   }
   PeerPtrs d, f;
@@ -349,10 +410,33 @@ EDL_HOST_API int edl_allreduce_add_rmsnorm(const unsigned long long* data_ptrs, 
   }
   int blocks = rows < sm_count() * 2 ? rows : sm_count() * 2;
   const long long spin = (long long)(wait_ms > 0 ? wait_ms : 2000) * 2000000LL;
-  allreduce_add_rmsnorm_kernel<<<blocks, ARN_THREADS, 0, (cudaStream_t)stream>>>(
-      d, f, nranks, rank, sync, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)weight, eps, w_offset,
-      (__nv_bfloat16*)x_out, (__nv_bfloat16*)h_out, rows, width, spin, status);
+  if (mc_data & 15) {
+    set_last_error("edl_allreduce_add_rmsnorm: the multicast address must be 16-byte aligned");
+    return -1;
+  }
+  const int vecs = width / 8;
+#define EDL_ONESHOT_LAUNCH(T, V)                                                                                 \
+  allreduce_add_rmsnorm_kernel<T, V><<<blocks, T, 0, (cudaStream_t)stream>>>(                                    \
+      d, f, nranks, rank, sync, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)weight, eps, w_offset,     \
+      (__nv_bfloat16*)x_out, (__nv_bfloat16*)h_out, rows, width, spin, status, mc_data)
+  if (vecs <= 256)
+    EDL_ONESHOT_LAUNCH(256, 1);
+  else if (vecs <= 512)
+    EDL_ONESHOT_LAUNCH(512, 1);
+  else if (vecs <= 1024)
+    EDL_ONESHOT_LAUNCH(512, 2);
+  else
+    EDL_ONESHOT_LAUNCH(512, 4);
+#undef EDL_ONESHOT_LAUNCH
   return check_cuda(cudaGetLastError(), "allreduce_add_rmsnorm launch");
+}
+
+EDL_HOST_API int edl_allreduce_add_rmsnorm(const unsigned long long* data_ptrs, const unsigned long long* flag_ptrs,
+                                           int nranks, int rank, int* sync, const void* residual, const void* weight,
+                                           float eps, float w_offset, void* x_out, void* h_out, int rows, int width,
+                                           int wait_ms, int* status, void* stream) {
+  return edl_allreduce_add_rmsnorm_mc(data_ptrs, flag_ptrs, nranks, rank, sync, residual, weight, eps, w_offset,
+                                      x_out, h_out, rows, width, wait_ms, status, stream, 0ull);
 }
 
 // ---- two-shot all-reduce (+ residual add + RMSNorm) for messages of a few megabytes --------------------------------
@@ -365,26 +449,6 @@ EDL_HOST_API int edl_allreduce_add_rmsnorm(const unsigned long long* data_ptrs, 
 // counter), flags [16, 32) carry "rows stored". weight == null: no normalisation, only the summed rows are gathered.
 namespace edl {
 namespace {
-
-// Multicast (NVLink switch) addresses of the same three regions, or zeros: with them the sum over ranks is one
-// `multimem.ld_reduce` (the switch adds the eight partials, fp32 accumulation, bf16 result) instead of one load per
-// peer, and a row is handed to every rank by one `multimem.st` instead of one store per peer.
-struct McPtrs {
-  unsigned long long data, x_out, h_out;
-};
-__device__ __forceinline__ uint4 multimem_sum_bf16x8(unsigned long long addr) {
-  uint4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(addr)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ void multimem_store16(unsigned long long addr, const uint4& v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y),
-               "r"(v.z), "r"(v.w)
-               : "memory");
-}
 
 // THREADS x MAXV uint4 vectors cover a row. Peer loads are latency bound (one NVLink round trip each), so the wide
 // form (1024 threads, one or two vectors per thread) keeps every load of a row in flight at once.

@@ -38,6 +38,9 @@ _lib.register("edl_allreduce_twoshot", _lib.i32, [_lib.vp, _lib.vp, _lib.vp, _li
                                                   _lib.vp, _lib.vp])
 
 
+_lib.register("edl_allreduce_add_rmsnorm_mc", _lib.i32, [_lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.vp, _lib.vp, _lib.vp,
+                                                         _lib.f32, _lib.f32, _lib.vp, _lib.vp, _lib.i32, _lib.i32,
+                                                         _lib.i32, _lib.vp, _lib.vp, _lib.u64])
 _lib.register("edl_allreduce_twoshot_mc", _lib.i32, [_lib.vp, _lib.vp, _lib.vp, _lib.vp, _lib.i32, _lib.i32, _lib.vp,
                                                      _lib.vp, _lib.vp, _lib.f32, _lib.f32, _lib.i32, _lib.i32,
                                                      _lib.i32, _lib.vp, _lib.vp, _lib.u64, _lib.u64, _lib.u64])
@@ -186,10 +189,11 @@ class PendingReduce:
         h_out = torch.empty_like(res)
         width = self.shape[-1]
         rows = res.numel() // width
-        _lib.call("edl_allreduce_add_rmsnorm", C.cast(c.slot_ptrs[s], C.c_void_p), C.cast(c.flag_ptrs, C.c_void_p),
-                  c.world, c.rank, c.sync.data_ptr(), res.data_ptr(), weight.data_ptr(), float(eps), float(w_offset),
-                  x_out.data_ptr(), h_out.data_ptr(), rows, width, 2000, _lib.status_word(res.device).data_ptr(),
-                  _lib.stream_ptr())
+        _lib.call("edl_allreduce_add_rmsnorm_mc", C.cast(c.slot_ptrs[s], C.c_void_p),
+                  C.cast(c.flag_ptrs, C.c_void_p), c.world, c.rank, c.sync.data_ptr(), res.data_ptr(),
+                  weight.data_ptr(), float(eps), float(w_offset), x_out.data_ptr(), h_out.data_ptr(), rows, width, 2000,
+                  _lib.status_word(res.device).data_ptr(), _lib.stream_ptr(),
+                  c.mc_base + s * c.max_bytes if c.mc_base else 0)
         return h_out.view(residual.shape), x_out.view(residual.shape)
 
 

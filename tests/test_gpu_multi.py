@@ -295,6 +295,18 @@ def test_two_shot_allreduce_multimem(world):
     _run(_twoshot_multimem_worker, world)
 
 
+def _oneshot_multimem_worker(rank, world):
+    """Small messages (one flag round, every rank sums everything) with the sum taken in the NVLink switch."""
+    from easydel_b200.parallel import tp
+
+    tp._MULTIMEM_MODE = "1"
+    _allreduce_worker(rank, world)
+
+
+def test_one_shot_allreduce_add_rmsnorm_multimem():
+    _run(_oneshot_multimem_worker)
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_tensor_parallel_forward_and_loss(world):
     _run(_tp_forward_worker, world)
