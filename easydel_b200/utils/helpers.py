@@ -61,11 +61,14 @@ ENV_FLAGS: dict[str, EnvFlag] = {f.name: f for f in (
     EnvFlag("EDL_FORCE_BUILD", False, "bool", "rebuild the kernel library in-tree on import even if it exists"),
     EnvFlag("EDL_NVCC_EXTRA", "", "str", "extra nvcc flags for csrc/build.py (e.g. -DEDL_BOUNDS_CHECK)"),
     EnvFlag("EDL_GEMM_PAIR", True, "bool", "use the two-CTA (cta_group::2) GEMM for large products"),
-    EnvFlag("EDL_GEMM_PAIR128", True, "bool", "skinny products (129-512 rows) may use the CTA-pair GEMM with 256 x 128 tiles"),
+    EnvFlag("EDL_GEMM_PAIR128", False, "bool", "skinny products (129-512 rows) may use the CTA-pair GEMM with 256 x 128 "
+            "tiles (off: measured the same as the 128-wide kernel)"),
     EnvFlag("EDL_GEMM_PAIR_SPLITK", False, "bool", "plan the two-slice split-K form of the CTA-pair GEMM for skinny "
             "products (off: measured no faster than the 128-wide kernel)"),
     EnvFlag("EDL_TP_TWO_SHOT", True, "bool", "tensor-parallel decode all-reduces of 1-8 MiB run the two-shot peer-memory "
             "kernel (off: NCCL)"),
+    EnvFlag("EDL_TP_MULTIMEM", "auto", "str", "peer all-reduce kernels sum and broadcast through the NVLink switch "
+            "(multimem): auto = from four ranks up | 1 | 0"),
     EnvFlag("EDL_ESURGE_CUDA_GRAPHS", True, "bool", "replay decode steps from CUDA graphs"),
     EnvFlag("EDL_NVTX", False, "bool", "emit NVTX ranges around trainer steps, engine steps and layers"),
     EnvFlag("EASURGE_MAX_SCHEDULER_ERRORS", 3, "int", "consecutive engine-step errors before in-flight requests fail"),
