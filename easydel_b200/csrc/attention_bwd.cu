@@ -705,6 +705,36 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   if (lane == 0) delta[(long long)h * total_q + row] = s;
 }
 
+// The same with 16-byte loads: D / 8 lanes share a (row, head), a warp covers 256 / D of them.
+__global__ void attn_delta_vec_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                      float* __restrict__ delta, long long total_q, int Hq, int D, long long ldo,
+                                      long long lddo) {
+  const int lanes = D / 8;                      // 8, 16 or 32
+  const int per_warp = 32 / lanes;
+  const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long item = warp * per_warp + lane / lanes;
+  const int sub = lane % lanes;
+  float s = 0.f;
+  const bool live = item < total_q * Hq;
+  long long row = 0;
+  int h = 0;
+  if (live) {
+    row = item / Hq;
+    h = (int)(item - row * Hq);
+    const uint4 a = *reinterpret_cast<const uint4*>(o + row * ldo + (long long)h * D + sub * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(dout + row * lddo + (long long)h * D + sub * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = unpack_bf16x2(aw[j]), y = unpack_bf16x2(bw[j]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+  for (int off = lanes >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (live && sub == 0) delta[(long long)h * total_q + row] = s;
+}
+
 template <int D>
 int launch_bwd(const void* q, const void* k, const void* v, const void* dout, long long ldq, long long ldk,
                long long ldv, long long lddo, long long total_q, long long total_k, const AttnBwdParams& p,
@@ -763,10 +793,19 @@ EDL_HOST_API int edl_attn_bwd(const void* q, const void* k, const void* v, const
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   {
-    long long warps = total_q * Hq;
-    long long blocks = (warps * 32 + 255) / 256;
-    attn_delta_kernel<<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta,
-                                                       total_q, Hq, D, ldo, lddo);
+    const bool vec = (D == 64 || D == 128 || D == 256) && !(ldo & 7) && !(lddo & 7) &&
+                     !((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(dout)) & 15);
+    if (vec) {
+      const long long warps = (total_q * Hq + (256 / D) - 1) / (256 / D);
+      const long long blocks = (warps * 32 + 255) / 256;
+      attn_delta_vec_kernel<<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout,
+                                                             delta, total_q, Hq, D, ldo, lddo);
+    } else {
+      long long warps = total_q * Hq;
+      long long blocks = (warps * 32 + 255) / 256;
+      attn_delta_kernel<<<(unsigned)blocks, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta,
+                                                         total_q, Hq, D, ldo, lddo);
+    }
     if (check_cuda(cudaGetLastError(), "attn_delta launch")) return -1;
   }
   AttnBwdParams p;
