@@ -463,7 +463,7 @@ class Gemma4Config(VLMConfig):
             text_config = dict(text_config, model_type="gemma4_text")
         kw.setdefault("tie_word_embeddings", True)
         kw = self._init_parts(vision_config, text_config, image_token_id, kw)
-        self.audio_config = audio_config          # kept for round trips; the audio tower is not built
+        self.audio_config = audio_config          # an opaque payload kept for round trips, as in the reference
         self.boi_token_id, self.eoi_token_id, self.image_token_id = boi_token_id, eoi_token_id, image_token_id
         self.video_token_id, self.boa_token_id, self.eoa_token_index = video_token_id, boa_token_id, eoa_token_index
         self.audio_token_id = audio_token_id
