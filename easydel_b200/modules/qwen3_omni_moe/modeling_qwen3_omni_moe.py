@@ -182,24 +182,41 @@ class Qwen3OmniMoeThinkerConfig(VLMConfig):
 
 @register_config("qwen3_omni_moe")
 class Qwen3OmniMoeConfig(EasyDeLBaseConfig):
-    """Top-level checkpoint configuration: only the thinker part is modelled; the talker and code-to-waveform
-    sections are carried through unchanged."""
+    """Top-level checkpoint configuration: thinker, talker (with its code predictor) and code-to-waveform decoder,
+    plus the chat-template and text-to-speech marker ids the hand-over between them needs."""
 
     model_type = "qwen3_omni_moe"
 
-    def __init__(self, thinker_config=None, talker_config=None, code2wav_config=None, enable_audio_output=False, **kw):
+    def __init__(self, thinker_config=None, talker_config=None, code2wav_config=None, enable_audio_output=False,
+                 im_start_token_id=151644, im_end_token_id=151645, tts_pad_token_id=151671, tts_bos_token_id=151672,
+                 tts_eos_token_id=151673, system_token_id=8948, user_token_id=872, assistant_token_id=77091, **kw):
+        from .speech import Qwen3OmniMoeCode2WavConfig, Qwen3OmniMoeTalkerConfig
+
         if thinker_config is None:
             thinker_config = {}
         if isinstance(thinker_config, dict):
             thinker_config = Qwen3OmniMoeThinkerConfig(**{k: v for k, v in thinker_config.items()
                                                           if k != "model_type"})
+        if isinstance(talker_config, dict):
+            talker_config = Qwen3OmniMoeTalkerConfig(**{k: v for k, v in talker_config.items() if k != "model_type"})
+        if isinstance(code2wav_config, dict):
+            code2wav_config = Qwen3OmniMoeCode2WavConfig(**{k: v for k, v in code2wav_config.items()
+                                                            if k != "model_type"})
         self.thinker_config, self.talker_config, self.code2wav_config = thinker_config, talker_config, code2wav_config
         self.enable_audio_output = enable_audio_output
+        self.im_start_token_id, self.im_end_token_id = im_start_token_id, im_end_token_id
+        self.tts_pad_token_id, self.tts_bos_token_id, self.tts_eos_token_id = tts_pad_token_id, tts_bos_token_id, \
+            tts_eos_token_id
+        self.system_token_id, self.user_token_id, self.assistant_token_id = system_token_id, user_token_id, \
+            assistant_token_id
         super().__init__(**kw)
 
     def to_dict(self):
         d = super().to_dict()
         d["thinker_config"] = self.thinker_config.to_dict()
+        for k in ("talker_config", "code2wav_config"):
+            v = getattr(self, k)
+            d[k] = v.to_dict() if hasattr(v, "to_dict") else v
         return d
 
 
@@ -299,11 +316,93 @@ class Qwen3OmniMoeThinkerForConditionalGeneration(Qwen3VLForConditionalGeneratio
 
 @register_module(TaskType.ANY_TO_ANY, config=Qwen3OmniMoeConfig, model_type="qwen3_omni_moe")
 class Qwen3OmniMoeForConditionalGeneration(Qwen3OmniMoeThinkerForConditionalGeneration):
-    """The full checkpoint's entry point, restricted to text output: loads the ``thinker.*`` tensors."""
+    """The full checkpoint's entry point. The module itself is the thinker (text output; ``thinker.*`` tensors go
+    through the regular checkpoint path). With ``enable_audio_output`` (or after :meth:`enable_talker`) it also owns
+    the talker and the code-to-waveform decoder (``speech.py``), loaded with :meth:`load_speech_hf_state`, and
+    :meth:`generate_speech` runs thinker -> talker -> waveform."""
 
     def __init__(self, config, dtype=torch.bfloat16, param_dtype=None, precision=None, rngs=None):
         super().__init__(config.thinker_config if hasattr(config, "thinker_config") else config, dtype, param_dtype,
                          precision, rngs)
+        self.omni_config = config if hasattr(config, "thinker_config") else None
+        self.talker = self.code2wav = None
+        if self.omni_config is not None and getattr(config, "enable_audio_output", False) \
+                and config.talker_config is not None and config.code2wav_config is not None:
+            self.enable_talker()
 
     def hf_rename_out(self, sd):
-        return {"thinker." + k: v for k, v in super().hf_rename_out(sd).items()}
+        return {"thinker." + k: v for k, v in super().hf_rename_out(sd).items()
+                if not k.startswith(("talker.", "code2wav."))}
+
+    # ------------------------------------------------------------------ speech
+    def enable_talker(self) -> None:
+        from .speech import Qwen3OmniMoeCode2Wav, Qwen3OmniMoeTalkerForConditionalGeneration
+
+        c = self.omni_config
+        if c is None or c.talker_config is None or c.code2wav_config is None:
+            raise ValueError("the configuration has no talker / code2wav sections")
+        dev = next(self.parameters()).device
+        self.talker = Qwen3OmniMoeTalkerForConditionalGeneration(c.talker_config, dtype=self.dtype,
+                                                                 param_dtype=self.param_dtype).to(dev).eval()
+        self.code2wav = Qwen3OmniMoeCode2Wav(c.code2wav_config, dtype=torch.float32).to(dev).eval()
+
+    def disable_talker(self) -> None:
+        self.talker = self.code2wav = None
+
+    def load_speech_hf_state(self, sd: dict) -> None:
+        """``talker.*`` and ``code2wav.*`` tensors of a Hugging Face Qwen3-Omni checkpoint."""
+        if self.talker is None:
+            self.enable_talker()
+        self.talker.load_hf_state(sd, prefix="talker.")
+        self.code2wav.load_hf_state(sd, prefix="code2wav.")
+
+    def state_dict(self, *a, **kw):
+        sd = super().state_dict(*a, **kw)
+        return type(sd)((k, v) for k, v in sd.items() if not k.startswith(("talker.", "code2wav.")))
+
+    @torch.no_grad()
+    def generate_speech(self, input_ids: torch.Tensor, speaker: str | int = 0, thinker_max_new_tokens: int = 256,
+                        talker_max_new_tokens: int = 1024, do_sample: bool = True, temperature: float = 0.9,
+                        top_k: int = 50, top_p: float = 1.0, seed: int | None = None, **thinker_inputs):
+        """One conversation (batch 1) -> (token sequence ``[1, T]``, waveform ``[1, 1, samples]``). ``speaker``: a
+        name from ``talker_config.speaker_id`` or a codec token id. ``thinker_inputs``: the multimodal tensors of the
+        prompt (``pixel_values``, ``image_grid_thw``, ``input_features`` ...)."""
+        from ..qwen2_vl import mrope_positions
+        from .speech import SpeechTokenIds, talker_inputs, top_k_top_p_sampler
+
+        if self.talker is None:
+            raise ValueError("speech output needs the talker: enable_talker() and load_speech_hf_state()")
+        if input_ids.shape[0] != 1:
+            raise NotImplementedError("speech output is generated one conversation at a time")
+        c, tc = self.omni_config, self.omni_config.talker_config
+        if isinstance(speaker, str):
+            table = {k.lower(): v for k, v in (tc.speaker_id or {}).items()}
+            if speaker.lower() not in table:
+                raise ValueError(f"unknown speaker {speaker!r}; known: {sorted(table)}")
+            speaker = table[speaker.lower()]
+        seqs = self.generate(input_ids, max_new_tokens=thinker_max_new_tokens, eos_token_id=c.im_end_token_id,
+                             **thinker_inputs).sequences
+        # one pass over prompt + reply for the two things the talker is conditioned on
+        out = self(input_ids=seqs, output_hidden_states=True, **thinker_inputs)
+        hs = out.hidden_states
+        ids = SpeechTokenIds(im_start=c.im_start_token_id, system=c.system_token_id, user=c.user_token_id,
+                             assistant=c.assistant_token_id, tts_pad=c.tts_pad_token_id, tts_bos=c.tts_bos_token_id,
+                             tts_eos=c.tts_eos_token_id, audio=self.config.audio_token_id,
+                             image=self.config.image_token_id, video=self.config.video_token_id)
+        emb, tids, trailing, pad_e = talker_inputs(self.talker, seqs, input_ids, hs[0], hs[tc.accept_hidden_layer],
+                                                   self.get_input_embeddings(), ids, int(speaker))
+        grid = thinker_inputs.get("image_grid_thw")
+        pos, delta = mrope_positions(tids, self.config.image_token_id, grid,
+                                     self.config.vision_config.spatial_merge_size,
+                                     video_token_id=self.config.video_token_id,
+                                     video_grid_thw=thinker_inputs.get("video_grid_thw"))
+        V = tc.text_config.vocab_size
+        banned = [i for i in range(V - 1024, V) if i != tc.codec_eos_token_id and i >= 0]
+        sampler = top_k_top_p_sampler(temperature, top_k, top_p, seed) if do_sample else None
+        residual = top_k_top_p_sampler(1.0, 50, 0.8, seed) if do_sample else None
+        codes = self.talker.generate_codes(emb, trailing, pad_e, max_new_tokens=talker_max_new_tokens,
+                                           position_ids=pos, rope_delta=int(delta[0]), sample=sampler,
+                                           residual_sample=residual, suppress_tokens=banned)
+        if codes.shape[-1] == 0:
+            return seqs, torch.zeros(1, 1, 0)
+        return seqs, self.code2wav.chunked_decode(codes.clamp_max(self.code2wav.config.codebook_size - 1)).float()
