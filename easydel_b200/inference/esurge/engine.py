@@ -122,7 +122,7 @@ class eSurge:
                  sharding_axis_dims=(1, 1, 1, -1, 1), extra_eos_token_ids: tp.Sequence[int] | None = None,
                  extra_stops: str | tp.Sequence[str] | None = None, auto_cap_new_tokens: bool = True,
                  sampling_params_callback: tp.Callable | None = None, tool_parser: str | None = None,
-                 reasoning_parser: str | None = None, **compile_options):
+                 reasoning_parser: str | None = None, kv_quantization=None, **compile_options):
         """``async_scheduling`` / ``overlap_execution`` (either one; default on for CUDA models): step *t+1* is
         scheduled and launched before the tokens of step *t* are read back, so host work overlaps device work.
 
@@ -146,11 +146,21 @@ class eSurge:
         self.name = esurge_name or f"esurge-{id(self) & 0xffff:x}"
         pages_cap = max_num_seqs * ((max_model_len + page_size - 1) // page_size) + 1
         # the page count is settled before anything is allocated: two caches never exist at once
-        self.cache = PagedKVCache.init_for_model(model, num_pages=num_pages, page_size=page_size,
-                                                 hbm_utilization=hbm_utilization, max_model_length=max_model_len,
-                                                 max_pages=pages_cap if num_pages is None else None,
-                                                 max_num_seqs=max_num_seqs,
-                                                 max_num_batched_tokens=self.max_num_batched_tokens)
+        if kv_quantization is not None:
+            # ``kv_quantization``: a ``TurboQuantConfig``; keys and values are stored compressed and attention runs
+            # as tensor code over them (no decode graphs)
+            from ...caching.turboquant_paged import TurboQuantPagedKVCache
+
+            self.cache = TurboQuantPagedKVCache.init_for_model(getattr(model, "language_model", model),
+                                                               kv_quantization, num_pages=num_pages,
+                                                               hbm_utilization=hbm_utilization,
+                                                               max_pages=pages_cap if num_pages is None else None)
+        else:
+            self.cache = PagedKVCache.init_for_model(model, num_pages=num_pages, page_size=page_size,
+                                                     hbm_utilization=hbm_utilization, max_model_length=max_model_len,
+                                                     max_pages=pages_cap if num_pages is None else None,
+                                                     max_num_seqs=max_num_seqs,
+                                                     max_num_batched_tokens=self.max_num_batched_tokens)
         # hybrids: one recurrent-state row per engine slot (the last row belongs to the padding rows of a batch
         # bucket). A cached prefix has no recurrent state to resume from, so prefix caching is off for them.
         self.cache.add_state_pools(getattr(model, "language_model", model), max_num_seqs + 1)

@@ -88,7 +88,7 @@ class ModelRunner:
 
         self.use_graphs = dev.type == "cuda" and os.environ.get("EDL_ESURGE_CUDA_GRAPHS", "1") != "0"
         latent_kernel = bool(cache.latent and cache.k.shape[-1] == 576)    # the 512 + 64 layout has a decode kernel
-        if cache.linear or (cache.latent and not latent_kernel) or \
+        if cache.linear or getattr(cache, "compressed", False) or (cache.latent and not latent_kernel) or \
                 (not cache.latent and model.spec.head_dim not in (64, 128)):
             self.use_graphs = False     # these serving paths are tensor code with host-side steps: run eagerly
         self._seq_slots = torch.zeros(max_num_seqs, dtype=torch.int64, device=dev)
