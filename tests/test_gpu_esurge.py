@@ -127,3 +127,49 @@ def test_preemption_chunked_prefix_hit_and_bucket_padding_on_the_gpu():
             agree(o.outputs[0].token_ids, w)
     finally:
         eng.close()
+
+
+def test_engine_on_the_compressed_cache_on_the_gpu():
+    """The TurboQuant page pools and their tensor-code attention with CUDA tensors (eager steps): 8-bit codes keep the
+    first greedy tokens of the exact cache."""
+    from easydel_b200.caching.turboquant_paged import TurboQuantPagedKVCache
+    from easydel_b200.inference import SamplingParams
+    from easydel_b200.inference.esurge import eSurge
+    from easydel_b200.layers.turboquant import TurboQuantConfig
+
+    model = _model()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 4000, (n,), generator=g).tolist() for n in (200, 33)]
+    sp = SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True)
+    plain = eSurge(model, max_model_len=512, max_num_seqs=2, max_num_batched_tokens=256, num_pages=16)
+    try:
+        want = [o.outputs[0].token_ids for o in plain.generate(prompts, sp)]
+    finally:
+        plain.close()
+    eng = eSurge(model, max_model_len=512, max_num_seqs=2, max_num_batched_tokens=256, num_pages=16,
+                 kv_quantization=TurboQuantConfig(bits=8))
+    try:
+        assert isinstance(eng.cache, TurboQuantPagedKVCache) and eng.cache.k_codes.is_cuda
+        got = [o.outputs[0].token_ids for o in eng.generate(prompts, sp)]
+    finally:
+        eng.close()
+    # random bf16 weights put many logits within the quantisation noise of one another: only the short prompt's
+    # first token is required to agree
+    assert all(len(t) == 6 for t in got) and got[1][0] == want[1][0]
+    # the cache's own arithmetic on the GPU equals the same arithmetic on the CPU
+    import types
+
+    from easydel_b200.caching.paged import PagedBatchMeta
+
+    torch.manual_seed(0)
+    attn = types.SimpleNamespace(scale=128 ** -0.5, softcap=None, sliding_window=None, sinks=None)
+    q, k, v = torch.randn(1, 70, 8, 128), torch.randn(1, 70, 2, 128), torch.randn(1, 70, 2, 128)
+    outs = []
+    for dev in ("cpu", "cuda"):
+        cache = TurboQuantPagedKVCache(1, 4, 2, 128, TurboQuantConfig(bits=4), device=dev)
+        meta = PagedBatchMeta(cu_q=torch.tensor([0, 70], dtype=torch.int32, device=dev),
+                              kv_lens=torch.tensor([70], dtype=torch.int32, device=dev),
+                              page_table=torch.tensor([[1, 0]], dtype=torch.int32, device=dev),
+                              slot_mapping=(128 + torch.arange(70, dtype=torch.int32)).to(dev), max_q=70, num_seqs=1)
+        outs.append(cache.view(0).attend(attn, q.to(dev), k.to(dev), v.to(dev), attn_meta=meta).cpu())
+    assert torch.allclose(outs[0], outs[1], atol=2e-3, rtol=2e-3)
