@@ -62,6 +62,64 @@ def selective_scan_reference(u, delta, A, B, C, D=None, z=None, dt_bias=None, so
     return torch.stack(ys).to(u.dtype)
 
 
+def _scan_chunk(a, b, h0):
+    """h_t = a_t * h_{t-1} + b_t over the leading axis (``a``, ``b`` ``[Q, ...]``, ``h0`` ``[...]``) by recursive
+    doubling: log2(Q) vectorised steps instead of Q sequential ones; every intermediate stays bounded because the
+    decays ``a`` are in (0, 1]."""
+    Q = a.shape[0]
+    k = 1
+    while k < Q:
+        a_prev = torch.cat([torch.ones_like(a[:k]), a[:-k]], 0)
+        b_prev = torch.cat([torch.zeros_like(b[:k]), b[:-k]], 0)
+        b = a * b_prev + b
+        a = a * a_prev
+        k *= 2
+    return a * h0[None] + b
+
+
+def selective_scan_chunked(u, delta, A, B, C, D=None, z=None, dt_bias=None, softplus=True, cu_seqlens=None,
+                           state=None, chunk: int = 256):
+    """The recurrence of :func:`selective_scan_reference` evaluated chunk by chunk with a parallel scan inside each
+    chunk; differentiable, and every chunk is recomputed in the backward pass (``torch.utils.checkpoint``) so that
+    only the states at chunk boundaries are kept. This is what training runs: the sequential reference needs one
+    small launch per token."""
+    from torch.utils.checkpoint import checkpoint
+
+    total, Dm = u.shape
+    cu = _cu(total, cu_seqlens, u.device).tolist()
+    Af = A.float()
+
+    def run(u_c, d_c, B_c, C_c, z_c, h0):
+        dt = d_c.float() + (dt_bias.float() if dt_bias is not None else 0.0)
+        if softplus:
+            dt = tF.softplus(dt)
+        a = torch.exp(dt[:, :, None] * Af[None])                                     # [Q, D, N]
+        b = (dt * u_c.float())[:, :, None] * B_c.float()[:, None, :]
+        h = _scan_chunk(a, b, h0)
+        y = (h * C_c.float()[:, None, :]).sum(-1)
+        if D is not None:
+            y = y + D.float()[None] * u_c.float()
+        if z_c is not None:
+            y = y * tF.silu(z_c.float())
+        return y, h[-1]
+
+    need_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad
+                                                for t in (u, delta, A, B, C, D, z, dt_bias))
+    ys, finals = [], []
+    for bi in range(len(cu) - 1):
+        h = state[bi].float().clone() if state is not None else torch.zeros(Dm, A.shape[1], device=u.device)
+        for lo in range(cu[bi], cu[bi + 1], chunk):
+            hi = min(lo + chunk, cu[bi + 1])
+            args = (u[lo:hi], delta[lo:hi], B[lo:hi], C[lo:hi], None if z is None else z[lo:hi], h)
+            y, h = checkpoint(run, *args, use_reentrant=False) if need_grad else run(*args)
+            ys.append(y)
+        finals.append(h)
+    if state is not None:
+        with torch.no_grad():
+            state.copy_(torch.stack([f.detach() for f in finals]))
+    return torch.cat(ys).to(u.dtype) if ys else u.new_zeros(0, Dm)
+
+
 def selective_scan(u, delta, A, B, C, D=None, z=None, dt_bias=None, softplus=True, cu_seqlens=None, state=None):
     """u, delta, z ``[total, D]``; A ``[D, N]`` (negative); B, C ``[total, N]``; state ``[nseq, D, N]`` fp32."""
     if _use_kernel(u, delta, A, B, C, D, z) and A.shape[1] in (8, 16, 32, 64) and u.dtype == torch.bfloat16:
@@ -74,6 +132,8 @@ def selective_scan(u, delta, A, B, C, D=None, z=None, dt_bias=None, softplus=Tru
                   _lib.ptr(c(z)), _lib.ptr(None if dt_bias is None else dt_bias.float().contiguous()), int(softplus),
                   cu.data_ptr(), cu.numel() - 1, Dm, A.shape[1], _lib.ptr(state), y.data_ptr(), _lib.stream_ptr())
         return y
+    if u.shape[0] > 16:
+        return selective_scan_chunked(u, delta, A, B, C, D, z, dt_bias, softplus, cu_seqlens, state)
     return selective_scan_reference(u, delta, A, B, C, D, z, dt_bias, softplus, cu_seqlens, state)
 
 
@@ -105,6 +165,70 @@ def ssd_scan_reference(x, dt, A, B, C, D=None, dt_bias=None, softplus=True, cu_s
     return torch.stack(ys).to(x.dtype)
 
 
+def ssd_scan_chunked(x, dt, A, B, C, D=None, dt_bias=None, softplus=True, cu_seqlens=None, state=None,
+                     chunk: int = 64):
+    """The recurrence of :func:`ssd_scan_reference` in its chunked matrix form (state-space duality): inside a chunk
+    the output is a masked, decay-weighted ``(C B^T)`` product applied to the inputs, chunks hand a ``[H, P, N]``
+    state to one another, and the state's contribution is one more product. Batched matrix products instead of one
+    launch per token; differentiable."""
+    total, H, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    rep = H // G
+    cu = _cu(total, cu_seqlens, x.device).tolist()
+    d = dt.float() + (dt_bias.float() if dt_bias is not None else 0.0)
+    if softplus:
+        d = tF.softplus(d)
+    Af = A.float()
+    ys, finals = [], []
+    for bi in range(len(cu) - 1):
+        lo, hi = cu[bi], cu[bi + 1]
+        T = hi - lo
+        s_in = state[bi].float().clone() if state is not None else torch.zeros(H, P, N, device=x.device)
+        if T == 0:
+            finals.append(s_in)
+            continue
+        pad = (-T) % chunk
+        nc = (T + pad) // chunk
+
+        def chunks(t, fill=0.0):
+            t = t[lo:hi].float()
+            if pad:
+                t = torch.cat([t, t.new_full((pad, *t.shape[1:]), fill)], 0)
+            return t.view(nc, chunk, *t.shape[1:])
+
+        xc, dc = chunks(x), chunks(d)                               # [nc, Q, H, P], [nc, Q, H]  (padded steps: dt = 0)
+        Bc = chunks(B).repeat_interleave(rep, 2)                    # [nc, Q, H, N]
+        Cc = chunks(C).repeat_interleave(rep, 2)
+        la = dc * Af[None, None]                                    # log decay per step, <= 0
+        cs = la.cumsum(1)                                           # [nc, Q, H]
+        # inside a chunk: y_t = sum_{s <= t} exp(cs_t - cs_s) (C_t . B_s) dt_s x_s
+        seg = cs[:, :, None, :] - cs[:, None, :, :]                 # [nc, t, s, H]
+        causal = torch.ones(chunk, chunk, dtype=torch.bool, device=x.device).tril()
+        L = torch.exp(seg.masked_fill(~causal[None, :, :, None], float("-inf")))
+        cb = torch.einsum("cthn,cshn->ctsh", Cc, Bc)
+        xd = xc * dc[..., None]
+        y = torch.einsum("ctsh,cshp->cthp", cb * L, xd)
+        # what every chunk adds to the state, decayed to the chunk's end
+        to_end = torch.exp(cs[:, -1:, :] - cs)                      # [nc, Q, H]
+        add = torch.einsum("cshn,cshp->chpn", Bc * to_end[..., None], xd)
+        total_decay = torch.exp(cs[:, -1, :])                       # [nc, H]
+        states = []
+        for c in range(nc):                                         # the only sequential part: one step per chunk
+            states.append(s_in)
+            s_in = total_decay[c][:, None, None] * s_in + add[c]
+        st = torch.stack(states)                                    # state entering each chunk [nc, H, P, N]
+        y = y + torch.einsum("cthn,chpn->cthp", Cc * torch.exp(cs)[..., None], st)
+        y = y.reshape(nc * chunk, H, P)[:T]
+        if D is not None:
+            y = y + D.float()[None, :, None] * x[lo:hi].float()
+        ys.append(y)
+        finals.append(s_in)
+    if state is not None:
+        with torch.no_grad():
+            state.copy_(torch.stack([f.detach() for f in finals]))
+    return torch.cat(ys).to(x.dtype) if ys else x.new_zeros(0, H, P)
+
+
 def ssd_scan(x, dt, A, B, C, D=None, dt_bias=None, softplus=True, cu_seqlens=None, state=None):
     """x ``[total, H, P]``; dt ``[total, H]``; A ``[H]``; B, C ``[total, G, N]``; state ``[nseq, H, P, N]`` fp32."""
     if _use_kernel(x, dt, A, B, C, D) and B.shape[2] in (16, 32, 64, 128) and x.dtype == torch.bfloat16 \
@@ -118,6 +242,8 @@ def ssd_scan(x, dt, A, B, C, D=None, dt_bias=None, softplus=True, cu_seqlens=Non
                   _lib.ptr(None if dt_bias is None else dt_bias.float().contiguous()), int(softplus), cu.data_ptr(),
                   cu.numel() - 1, H, P, B.shape[1], B.shape[2], _lib.ptr(state), y.data_ptr(), _lib.stream_ptr())
         return y
+    if x.shape[0] > 16:
+        return ssd_scan_chunked(x, dt, A, B, C, D, dt_bias, softplus, cu_seqlens, state)
     return ssd_scan_reference(x, dt, A, B, C, D, dt_bias, softplus, cu_seqlens, state)
 
 

@@ -115,3 +115,81 @@ def test_wkv4_kernel_matches_reference_with_state():
     out2 = ssm.wkv4(decay, first, k, v, cu, st)
     ref2 = ssm.wkv4_reference(decay, first, k.float(), v.float(), cu, st_ref)
     assert (out2.float() - ref2).abs().max() < 2e-2
+
+
+def test_chunked_selective_scan_and_ssd_match_the_sequential_references_with_gradients():
+    """The forms training runs (parallel scan per chunk / chunked matrix form) against the one-token-at-a-time
+    references: outputs, final states and every input gradient, on two packed sequences with initial states."""
+    import torch
+
+    from easydel_b200.ops import ssm
+
+    torch.manual_seed(0)
+
+    def mk(*s):
+        return (torch.randn(*s) * 0.5).requires_grad_(True)
+
+    cu = torch.tensor([0, 70, 150], dtype=torch.int32)
+    T, Dm, N = 150, 12, 8
+    u, delta, B, C, z = mk(T, Dm), mk(T, Dm), mk(T, N), mk(T, N), mk(T, Dm)
+    A = (-torch.rand(Dm, N) - 0.1).requires_grad_(True)
+    D, dtb = mk(Dm), mk(Dm)
+    ins = [u, delta, A, B, C, D, z, dtb]
+    s1 = torch.randn(2, Dm, N)
+    s2 = s1.clone()
+    y1 = ssm.selective_scan_reference(u, delta, A, B, C, D, z, dtb, True, cu, s1)
+    y2 = ssm.selective_scan_chunked(u, delta, A, B, C, D, z, dtb, True, cu, s2, chunk=32)
+    g1 = torch.autograd.grad(y1.square().sum(), ins)
+    g2 = torch.autograd.grad(y2.square().sum(), ins)
+    assert torch.allclose(y1, y2, atol=1e-5) and torch.allclose(s1, s2, atol=1e-5)
+    assert all(torch.allclose(a, b, atol=2e-4, rtol=1e-4) for a, b in zip(g1, g2))
+
+    T, H, P, G, N = 150, 4, 6, 2, 8
+    x, dt, B, C = mk(T, H, P), mk(T, H), mk(T, G, N), mk(T, G, N)
+    A = (-torch.rand(H) - 0.1).requires_grad_(True)
+    D, dtb = mk(H), mk(H)
+    ins = [x, dt, A, B, C, D, dtb]
+    s1 = torch.randn(2, H, P, N)
+    s2 = s1.clone()
+    y1 = ssm.ssd_scan_reference(x, dt, A, B, C, D, dtb, True, cu, s1)
+    y2 = ssm.ssd_scan_chunked(x, dt, A, B, C, D, dtb, True, cu, s2, chunk=32)
+    g1 = torch.autograd.grad(y1.square().sum(), ins)
+    g2 = torch.autograd.grad(y2.square().sum(), ins)
+    assert torch.allclose(y1, y2, atol=2e-5) and torch.allclose(s1, s2, atol=2e-5)
+    assert all(torch.allclose(a, b, atol=5e-4, rtol=1e-3) for a, b in zip(g1, g2))
+
+
+@pytest.mark.gpu
+def test_chunked_scans_on_the_gpu_match_the_recurrent_kernels():
+    """Training's chunked forms (autograd on, CUDA tensors) against the inference kernels on the same inputs."""
+    import torch
+
+    from easydel_b200.ops import ssm
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    T, Dm, N = 700, 256, 16
+    bf = lambda *s: (torch.randn(*s, device=dev) * 0.5).to(torch.bfloat16)   # noqa: E731
+    u, delta, B, C, z = bf(T, Dm), bf(T, Dm), bf(T, N), bf(T, N), bf(T, Dm)
+    A = -torch.rand(Dm, N, device=dev) - 0.1
+    D, dtb = torch.randn(Dm, device=dev), torch.randn(Dm, device=dev) * 0.1
+    cu = torch.tensor([0, 300, 700], dtype=torch.int32, device=dev)
+    with torch.no_grad():
+        want = ssm.selective_scan(u, delta, A, B, C, D, z, dtb, True, cu)
+    ug = u.clone().requires_grad_(True)
+    got = ssm.selective_scan(ug, delta, A, B, C, D, z, dtb, True, cu)          # gradients wanted: chunked form
+    got.float().square().sum().backward()
+    assert ug.grad is not None and torch.isfinite(ug.grad).all()
+    assert (got.float() - want.float()).abs().max() < 0.06 * want.float().abs().max() + 0.02
+
+    H, P, G, N = 8, 64, 2, 32
+    x, dt, Bm, Cm = bf(T, H, P), bf(T, H), bf(T, G, N), bf(T, G, N)
+    A2 = -torch.rand(H, device=dev) - 0.1
+    D2, dtb2 = torch.randn(H, device=dev), torch.randn(H, device=dev) * 0.1
+    with torch.no_grad():
+        want = ssm.ssd_scan(x, dt, A2, Bm, Cm, D2, dtb2, True, cu)
+    xg = x.clone().requires_grad_(True)
+    got = ssm.ssd_scan(xg, dt, A2, Bm, Cm, D2, dtb2, True, cu)
+    got.float().square().sum().backward()
+    assert xg.grad is not None and torch.isfinite(xg.grad).all()
+    assert (got.float() - want.float()).abs().max() < 0.06 * want.float().abs().max() + 0.02
