@@ -74,20 +74,25 @@ class DelimitedReasoningParser(ReasoningParser):
         return None, self._clean_content(text) or None
 
     def _split_partial(self, text, final):
-        hold = 0 if final else _hold_back(text, [self.start, self.end] + [m for m in (self.cs, self.ce) if m])
-        safe = text[:len(text) - hold] if hold else text
-        body = safe
-        if self.start in body:
-            pre, body = body.split(self.start, 1)
+        # Markers are located in the whole text first; only the open stream's tail is held back while it could be
+        # the beginning of a marker. Trimming the text before the search would cut a complete marker whose last
+        # characters begin another one ("\n</think>\n" ends in the first character of "\n</answer>").
+        def trim(s, markers):
+            n = 0 if final else _hold_back(s, markers)
+            return s[:len(s) - n] if n else s
+
+        cm = [m for m in (self.cs, self.ce) if m]
+        if self.start in text:
+            pre, body = text.split(self.start, 1)
             in_reasoning = True
         else:
-            pre, in_reasoning = "", self.implicit
+            pre, body, in_reasoning = "", text, self.implicit
         if not in_reasoning:
-            return "", self._clean_content(body)
+            return "", trim(self._clean_content(body), [self.start] + cm)
         if self.end in body:
             r, c = body.split(self.end, 1)
-            return r, self._clean_content(pre + c).lstrip("\n")
-        return body, pre
+            return r, trim(self._clean_content(pre + c).lstrip("\n"), cm)
+        return trim(body, [self.end] if pre or self.start in text else [self.end, self.start]), pre
 
 
 class HarmonyReasoningParser(ReasoningParser):
@@ -104,6 +109,21 @@ class HarmonyReasoningParser(ReasoningParser):
         if a is None and "<|channel|>" not in text:
             return None, text or None
         return a, None
+
+    _MARKS = ("<|channel|>", "<|message|>", "<|end|>", "<|start|>", "<|return|>", "<|call|>")
+
+    def _split_partial(self, text, final):
+        # no trailing strip while streaming: what was sent must stay a prefix of what is sent next
+        if not final:
+            n = _hold_back(text, self._MARKS)
+            text = text[:len(text) - n] if n else text
+        a = "\n".join(m.lstrip() for m in self._ana.findall(text))
+        f = self._fin.search(text)
+        if f:
+            return a, f.group(1).lstrip()
+        if not a and not any(m in text for m in self._MARKS):
+            return "", text
+        return a, ""
 
 
 class IdentityReasoningParser(ReasoningParser):

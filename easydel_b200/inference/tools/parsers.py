@@ -260,6 +260,35 @@ class HarmonyParser(ToolParser):
         content = fin.group(1).strip() if fin else (None if calls else text)
         return ExtractedToolCalls(bool(calls), calls, content)
 
+    _done = re.compile(r"to=functions\.(?P<name>[\w\-\.]+).*?<\|message\|>(?P<args>.*?)(?:<\|call\|>|<\|end\|>)", re.S)
+
+    def extract_tool_calls_streaming(self, current_text, final=False):
+        # Channel markup is never content: only the text of the final channel streams out, and a call is reported
+        # once its closing marker has arrived (or the generation ended).
+        text = current_text
+        if not final:
+            hold = 0
+            for m in ("<|channel|>", "<|message|>", "<|return|>", "<|end|>", "<|call|>", "<|start|>", "<|constrain|>"):
+                for n in range(min(len(m) - 1, len(text)), 0, -1):
+                    if text.endswith(m[:n]):
+                        hold = max(hold, n)
+                        break
+            text = text[:len(text) - hold] if hold else text
+        fin = self._final.search(text)
+        if fin:
+            content = fin.group(1).lstrip()
+        else:
+            content = "" if "<|" in text else text
+        delta = content[self._sent_content:]
+        self._sent_content = max(self._sent_content, len(content))
+        rx = self._rx if final else self._done
+        calls = [_call(m.group("name"), m.group("args").strip()) for m in rx.finditer(text)]
+        new = calls[self._sent_calls:]
+        for i, c in enumerate(new, start=self._sent_calls):
+            c["index"] = i
+        self._sent_calls = max(self._sent_calls, len(calls))
+        return delta, new
+
 
 class FunctionGemmaParser(ToolParser):
     """``<start_function_call>call:NAME{key:<escape>text<escape>,n:3}<end_function_call>``."""
