@@ -398,7 +398,7 @@ def wkv4_reference(time_decay, time_first, k, v, cu_seqlens=None, state=None):
     outs, new_states = [], []
     for b in range(len(cu) - 1):
         if state is not None:
-            num, den, mx = state[b, 0].float(), state[b, 1].float(), state[b, 2].float()
+            num, den, mx = state[b].float().clone().unbind(0)     # not views: the state is overwritten below
         else:
             num = torch.zeros(Cn, device=k.device)
             den = torch.zeros(Cn, device=k.device)
@@ -418,6 +418,58 @@ def wkv4_reference(time_decay, time_first, k, v, cu_seqlens=None, state=None):
     return torch.stack(outs).to(k.dtype) if outs else k.new_zeros(0, Cn)
 
 
+def wkv4_chunked(time_decay, time_first, k, v, cu_seqlens=None, state=None, chunk: int = 32):
+    """The recurrence of :func:`wkv4_reference` in a chunked matrix form: inside a chunk of ``Q`` tokens every output
+    is a ratio of two sums over the earlier tokens with log-weights ``(t-1-s) w + k_s`` (a ``[Q, Q, C]`` tensor), the
+    chunk's incoming state with ``mx + t w`` and the token itself with ``u + k_t``, all taken relative to their
+    row maximum. The carried ``(num, den, mx)`` is the same triple the sequential form keeps (``mx`` is a maximum over
+    the same set of exponents), so states interchange with the kernel's. Differentiable; chunks are recomputed in the
+    backward pass."""
+    from torch.utils.checkpoint import checkpoint
+
+    total, Cn = k.shape
+    cu = _cu(total, cu_seqlens, k.device).tolist()
+
+    def run(td, tf_, k_c, v_c, num0, den0, mx0):
+        w, u = -torch.exp(td.float()), tf_.float()
+        kf, vf = k_c.float(), v_c.float()
+        Q = kf.shape[0]
+        t = torch.arange(Q + 1, device=kf.device, dtype=torch.float32)
+        # rows 0..Q-1 give the outputs, row Q the state handed to the next chunk
+        gap = (t[:, None] - 1 - t[None, :Q])                                       # [Q+1, Q]
+        a_in = gap[:, :, None] * w[None, None] + kf[None]                          # [Q+1, Q, C]
+        a_in = a_in.masked_fill((gap < 0)[:, :, None], -float("inf"))
+        a_car = mx0[None] + t[:, None] * w[None]                                   # [Q+1, C]
+        a_cur = u[None] + kf                                                       # [Q, C]
+        m_past = torch.maximum(a_in.amax(1), a_car)                                # [Q+1, C]
+        m_out = torch.maximum(m_past[:Q], a_cur)
+        e_in, e_car, e_cur = torch.exp(a_in[:Q] - m_out[:, None]), torch.exp(a_car[:Q] - m_out), torch.exp(a_cur - m_out)
+        top = e_car * num0[None] + (e_in * vf[None]).sum(1) + e_cur * vf
+        bot = e_car * den0[None] + e_in.sum(1) + e_cur
+        mx1 = m_past[Q]
+        s_in, s_car = torch.exp(a_in[Q] - mx1[None]), torch.exp(a_car[Q] - mx1)
+        return top / bot, s_car * num0 + (s_in * vf).sum(0), s_car * den0 + s_in.sum(0), mx1
+
+    need_grad = torch.is_grad_enabled() and any(x.requires_grad for x in (time_decay, time_first, k, v))
+    outs, finals = [], []
+    for b in range(len(cu) - 1):
+        if state is not None:
+            num, den, mx = state[b].float().clone().unbind(0)     # not views: the state is overwritten below
+        else:
+            num, den = torch.zeros(Cn, device=k.device), torch.zeros(Cn, device=k.device)
+            mx = torch.full((Cn,), -1e38, device=k.device)
+        for lo in range(cu[b], cu[b + 1], chunk):
+            hi = min(lo + chunk, cu[b + 1])
+            args = (time_decay, time_first, k[lo:hi], v[lo:hi], num, den, mx)
+            y, num, den, mx = checkpoint(run, *args, use_reentrant=False) if need_grad else run(*args)
+            outs.append(y)
+        finals.append(torch.stack([num, den, mx]))
+    if state is not None:
+        with torch.no_grad():
+            state.copy_(torch.stack([f.detach() for f in finals]))
+    return torch.cat(outs).to(k.dtype) if outs else k.new_zeros(0, Cn)
+
+
 def wkv4(time_decay, time_first, k, v, cu_seqlens=None, state=None):
     """RWKV-4 time mixing. k, v ``[total, C]``; time_decay / time_first ``[C]``; state ``[nseq, 3, C]`` fp32
     (numerator, denominator, running max exponent), updated in place. Returns ``[total, C]``."""
@@ -429,4 +481,6 @@ def wkv4(time_decay, time_first, k, v, cu_seqlens=None, state=None):
                   k.contiguous().data_ptr(), v.contiguous().data_ptr(), cu.data_ptr(), cu.numel() - 1, Cn,
                   _lib.ptr(state), out.data_ptr(), _lib.stream_ptr())
         return out
+    if k.is_cuda and k.shape[0] > 16:      # launch-bound on a GPU; on the host the per-token loop does less arithmetic
+        return wkv4_chunked(time_decay, time_first, k, v, cu_seqlens, state)
     return wkv4_reference(time_decay, time_first, k, v, cu_seqlens, state)

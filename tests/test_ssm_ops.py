@@ -193,3 +193,49 @@ def test_chunked_scans_on_the_gpu_match_the_recurrent_kernels():
     got.float().square().sum().backward()
     assert xg.grad is not None and torch.isfinite(xg.grad).all()
     assert (got.float() - want.float()).abs().max() < 0.06 * want.float().abs().max() + 0.02
+
+    Cn = 256
+    k, v = bf(T, Cn), bf(T, Cn)
+    decay, first = torch.randn(Cn, device=dev) * 0.5 - 1.0, torch.randn(Cn, device=dev) * 0.5
+    with torch.no_grad():
+        want = ssm.wkv4(decay, first, k, v, cu)                                  # the recurrent kernel
+    kg = k.clone().requires_grad_(True)
+    got = ssm.wkv4(decay, first, kg, v, cu)                                      # gradients wanted: chunked form
+    got.float().square().sum().backward()
+    assert kg.grad is not None and torch.isfinite(kg.grad).all()
+    assert (got.float() - want.float()).abs().max() < 0.03
+
+
+def test_chunked_wkv4_matches_the_sequential_reference_with_gradients():
+    """RWKV-4's chunked matrix form against the per-token recurrence: outputs, the carried (num, den, max) triple
+    and the gradients of decay, bonus, keys and values, on two packed sequences that start from a state."""
+    import torch
+
+    from easydel_b200.ops import ssm
+
+    torch.manual_seed(0)
+    T, C = 150, 24
+    cu = torch.tensor([0, 70, 150], dtype=torch.int32)
+    k = (torch.randn(T, C) * 2.0).requires_grad_(True)              # wide keys exercise the running maximum
+    v = torch.randn(T, C).requires_grad_(True)
+    decay = (torch.randn(C) * 0.5 - 1.0).requires_grad_(True)
+    first = (torch.randn(C) * 0.5).requires_grad_(True)
+    ins = [decay, first, k, v]
+    s1 = torch.zeros(2, 3, C)
+    s1[:, 2] = -1e38
+    with torch.no_grad():                                           # a state that has already seen tokens
+        ssm.wkv4_reference(decay, first, torch.randn(40, C), torch.randn(40, C), torch.tensor([0, 15, 40]), s1)
+    s2 = s1.clone()
+    y1 = ssm.wkv4_reference(decay, first, k, v, cu, s1)
+    y2 = ssm.wkv4_chunked(decay, first, k, v, cu, s2, chunk=32)
+    g1 = torch.autograd.grad(y1.square().sum(), ins)
+    g2 = torch.autograd.grad(y2.square().sum(), ins)
+    assert torch.allclose(y1, y2, atol=1e-5)
+    assert torch.allclose(s1[:, 2], s2[:, 2], atol=1e-5)                                   # same maximum
+    assert torch.allclose(s1[:, :2], s2[:, :2], atol=1e-5, rtol=1e-5)
+    assert all(torch.allclose(a, b, atol=2e-4, rtol=1e-4) for a, b in zip(g1, g2))
+    # the dispatcher agrees with the reference, and a fresh state and a ragged last chunk work too
+    with torch.no_grad():
+        assert torch.allclose(ssm.wkv4(decay, first, k, v, cu), ssm.wkv4_reference(decay, first, k, v, cu), atol=1e-5)
+        assert torch.allclose(ssm.wkv4_chunked(decay, first, k[:7], v[:7], chunk=4),
+                              ssm.wkv4_reference(decay, first, k[:7], v[:7]), atol=1e-5)
