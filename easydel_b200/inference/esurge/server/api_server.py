@@ -26,6 +26,7 @@ from ...openai_api_modules import (ChatCompletionRequest, ChatCompletionResponse
                                    ModelCard, ModelList, ResponsesRequest, ResponsesResponse, ToolCall,
                                    ToolExecuteRequest, UsageInfo, sse)
 from ...reasoning import DelegatingParser, ReasoningParserManager, detect_reasoning_parser
+from ...stream_protocol import ResponsesStreamBuilder, sse_frame
 from ...tools import ToolParserManager, detect_tool_parser
 
 
@@ -265,7 +266,7 @@ class eSurgeApiServer:
             if req.max_output_tokens:
                 req.max_tokens = req.max_output_tokens
             sp = req.to_sampling_params(server.default_max_tokens)
-            rec = authorize(request, "/v1/responses", name, sp.max_tokens or 0, False, bool(req.tools))
+            rec = authorize(request, "/v1/responses", name, sp.max_tokens or 0, req.stream, bool(req.tools))
             history: list[dict] = []
             if req.previous_response_id:
                 prev = server.store.get(req.previous_response_id)
@@ -283,6 +284,33 @@ class eSurgeApiServer:
                         content = "".join(p.get("text", "") for p in content if isinstance(p, dict))
                     history.append({"role": item.get("role", "user"), "content": content})
             prompt = engine.tokenizer.apply_chat_template(history, tokenize=False, add_generation_prompt=True)
+            if req.stream:
+                parser = server._parser(engine, bool(req.tools))
+                builder = ResponsesStreamBuilder(model=name, previous_response_id=req.previous_response_id)
+
+                async def gen():
+                    for ev, payload in builder.start():
+                        yield sse_frame(ev, payload)
+                    last, text = None, ""
+                    async for out in pump(request, engine, engine.stream(prompt, sp)):
+                        last = out
+                        text += out.delta_text
+                        d = parser.parse_streaming(text, final=out.finished)
+                        for ev, payload in builder.feed(d["reasoning_content"], d["content"], d["tool_calls"]):
+                            yield sse_frame(ev, payload)
+                    if last is None:      # the client went away before the first token
+                        return
+                    n_in, n_out = len(last.prompt_token_ids), last.num_generated_tokens
+                    server.auth.record_usage(rec, n_in, n_out)
+                    events, final = builder.finish({"input_tokens": n_in, "output_tokens": n_out,
+                                                    "total_tokens": n_in + n_out})
+                    if req.store:
+                        server.store.put(final["id"], {"messages": history + [
+                            {"role": "assistant", "content": final["output_text"]}]})
+                    for ev, payload in events:
+                        yield sse_frame(ev, payload)
+
+                return StreamingResponse(gen(), media_type="text/event-stream")
             loop = asyncio.get_running_loop()
             out = (await loop.run_in_executor(None, engine.generate, prompt, sp))[0]
             parsed = server._parser(engine, bool(req.tools)).parse(out.get_text())

@@ -85,6 +85,17 @@ class Registry:
             known = sorted(self._modules.get(task, {}))
             raise KeyError(f"no {task} module registered for model_type {model_type!r}; known: {known}") from None
 
+    def alias(self, alias: str, target: str) -> None:
+        """Makes ``alias`` resolve to everything registered as ``target``: composite checkpoints name their halves
+        with their own model types (``qwen3_vl_text``, ``glm4v_moe_vision``...) although the classes are shared."""
+        cfgs = self._configs[ConfigType.MODULE_CONFIG.value]
+        if target not in cfgs:
+            raise KeyError(f"cannot alias {alias!r}: config type {target!r} is not registered")
+        cfgs.setdefault(alias, cfgs[target])
+        for table in self._modules.values():
+            if target in table:
+                table.setdefault(alias, table[target])
+
     @property
     def task_registry(self) -> dict[str, dict[str, ModuleRegistration]]:
         return self._modules

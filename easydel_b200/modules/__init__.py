@@ -38,3 +38,15 @@ from . import qwen3_omni_moe  # noqa: F401
 from .qwen3_omni_moe import *  # noqa: F401,F403
 from . import kimi_vl  # noqa: F401
 from .kimi_vl import *  # noqa: F401,F403
+from . import llama4  # noqa: F401
+from .llama4 import *  # noqa: F401,F403
+
+# The halves of composite checkpoints under the model types their own configs carry.
+from ..infra.factory import registry as _registry  # noqa: E402
+
+for _alias, _target in {
+    "qwen2_vl_text": "qwen2", "qwen3_vl_text": "qwen3", "qwen3_vl_moe_text": "qwen3_moe",
+    "qwen3_vl_moe_vision": "qwen3_vl_vision", "glm4v_moe_text": "glm4_moe", "glm4v_moe_vision": "glm4v_vision",
+    "qwen3_omni_moe_text": "qwen3_moe", "qwen3_omni_moe_vision_encoder": "qwen3_vl_vision",
+}.items():
+    _registry.alias(_alias, _target)

@@ -23,6 +23,7 @@ import torch.nn.functional as tF
 from torch import nn
 
 from ...infra.base_config import EasyDeLBaseConfig
+from ...infra.factory import register_config
 from ...ops import functional as F
 from .._base.families import base_spec, define_family, moe_spec
 
@@ -77,6 +78,7 @@ Qwen3OmniMoeTalkerTextConfig = _TEXT["Qwen3OmniMoeTalkerTextConfig"]
 Qwen3OmniMoeTalkerTextForCausalLM = _TEXT["Qwen3OmniMoeTalkerTextForCausalLM"]
 
 
+@register_config("qwen3_omni_moe_talker")
 class Qwen3OmniMoeTalkerConfig(EasyDeLBaseConfig):
     model_type = "qwen3_omni_moe_talker"
 
@@ -112,6 +114,7 @@ class Qwen3OmniMoeTalkerConfig(EasyDeLBaseConfig):
         return d
 
 
+@register_config("qwen3_omni_moe_code2wav")
 class Qwen3OmniMoeCode2WavConfig(EasyDeLBaseConfig):
     model_type = "qwen3_omni_moe_code2wav"
 

@@ -35,13 +35,17 @@ class Tok:
         return {}
 
 
-@pytest.fixture(scope="module")
-def engine():
+def make_engine():
     cfg = LlamaConfig(vocab_size=V, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
                       num_key_value_heads=2, max_position_embeddings=512, eos_token_id=2)
     torch.manual_seed(0)
     model = LlamaForCausalLM(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
     return eSurge(model, tokenizer=Tok(), max_model_len=256, max_num_seqs=4, esurge_name="tiny")
+
+
+@pytest.fixture(scope="module")
+def engine():
+    return make_engine()
 
 
 def test_completions_and_chat(engine):

@@ -38,6 +38,7 @@ def _entry(rank, fn, world, port, args):
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
     try:
         fn(rank, world, *args)
+        dist.barrier()      # nobody tears its sockets down while a peer still has transfers in flight
     finally:
         dist.destroy_process_group()
 

@@ -484,3 +484,75 @@ def test_qwen3_vl_video_frames_match_hf():
         a = m(**kw).logits
         b = hf(mm_token_type_ids=2 * (ids == 126).long(), **kw).logits
     assert (a - b).abs().max() < 1e-3, (a - b).abs().max()
+
+
+L4V = dict(hidden_size=32, num_hidden_layers=2, num_attention_heads=2, intermediate_size=128, image_size=28,
+           patch_size=7, vision_output_dim=48, projector_input_dim=48, projector_output_dim=48,
+           pixel_shuffle_ratio=0.5)
+L4T = dict(vocab_size=128, hidden_size=32, intermediate_size=48, intermediate_size_mlp=96, num_hidden_layers=4,
+           num_attention_heads=2, num_key_value_heads=1, head_dim=16, num_local_experts=4, num_experts_per_tok=1,
+           attention_chunk_size=32, floor_scale=16, attn_scale=0.3, no_rope_layers=[1, 1, 1, 0],
+           moe_layers=[0, 2, 3], max_position_embeddings=64, rope_theta=10000.0,
+           layer_types=["chunked_attention", "chunked_attention", "chunked_attention", "full_attention"])
+
+
+def test_llama4_vision_tower_matches_hf():
+    from easydel_b200.modules.llama4 import Llama4VisionConfig, Llama4VisionModel, pixel_shuffle
+
+    torch.manual_seed(0)
+    m = Llama4VisionModel(Llama4VisionConfig(**L4V), dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf = transformers.Llama4VisionModel(transformers.Llama4VisionConfig(
+        **L4V, rope_parameters=dict(rope_theta=10000.0, rope_type="default"))).float().eval()
+    missing, unexpected = hf.load_state_dict(internal_to_hf(m), strict=False)
+    assert not missing and not unexpected
+    pix = torch.randn(3, 3, 28, 28)
+    with torch.no_grad():
+        a, b = m(pix).last_hidden_state, hf(pix).last_hidden_state
+    assert a.shape == (3, 4, 48) and (a - b).abs().max() < 1e-5          # 16 patches fold into 4 rows
+    back = hf_to_internal(m, hf.state_dict())
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    # the shuffle folds a 2 x 2 neighbourhood of the grid into the channel axis
+    grid = torch.arange(16.0).view(1, 16, 1).expand(1, 16, 2).contiguous()
+    out = pixel_shuffle(grid, 0.5)
+    assert out.shape == (1, 4, 8) and sorted(out[0, 0, ::2].tolist()) == [0.0, 1.0, 4.0, 5.0]
+
+
+def test_llama4_multimodal_matches_hf_trains_and_decodes():
+    from easydel_b200.modules.llama4 import Llama4Config, Llama4ForConditionalGeneration
+
+    cfg = Llama4Config(vision_config=dict(L4V), text_config=dict(L4T), image_token_index=127)
+    assert cfg.vision_config.model_type == "llama4_vision_model" and cfg.text_config.model_type == "llama4_text"
+    torch.manual_seed(0)
+    m = Llama4ForConditionalGeneration(cfg, dtype=torch.float32, param_dtype=torch.float32).eval()
+    _jitter(m)
+    hf_cfg = transformers.Llama4Config(
+        vision_config=dict(L4V, rope_parameters=dict(rope_theta=10000.0, rope_type="default")),
+        text_config=dict({k: v for k, v in L4T.items() if k != "rope_theta"},
+                         rope_parameters=dict(rope_theta=10000.0, rope_type="default")),
+        image_token_index=127)
+    hf_cfg._attn_implementation = "eager"
+    hf = transformers.Llama4ForConditionalGeneration(hf_cfg).float().eval()
+    missing, unexpected = hf.load_state_dict(internal_to_hf(m), strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    ids = torch.randint(0, 120, (2, 14))
+    ids[:, 2:6] = 127                                              # one tile -> four feature rows per sequence
+    pix = torch.randn(2, 3, 28, 28)
+    with torch.no_grad():
+        a, b = m(input_ids=ids, pixel_values=pix).logits, hf(input_ids=ids, pixel_values=pix).logits
+        t1, t2 = m(input_ids=ids).logits, hf(input_ids=ids).logits
+    assert (t1 - t2).abs().max() < 3e-4 and (a - b).abs().max() < 3e-4
+    assert (a - t1).abs().max() > 1e-3                             # the image changed something
+    back = hf_to_internal(m, hf.state_dict())
+    assert all(torch.equal(back[k], v) for k, v in m.state_dict().items())
+    _, met = m.compute_loss(input_ids=ids, pixel_values=pix, labels=ids)
+    met.loss.backward()
+    assert torch.isfinite(met.loss) and m.vision_model.patch_embedding.linear.weight.grad.abs().sum() > 0
+    cache = m.init_cache(2, 16)
+    with torch.no_grad():
+        o1 = m(input_ids=ids[:, :10], pixel_values=pix, past_key_values=cache).logits
+        cache.advance(10)
+        o2 = m(input_ids=ids[:, 10:11], past_key_values=cache).logits
+    assert (o2[:, 0] - a[:, 10]).abs().max() < 3e-4 and (o1 - a[:, :10]).abs().max() < 3e-4
+    with pytest.raises(ValueError):                                # placeholders and feature rows must agree
+        m(input_ids=ids[:, :4], pixel_values=pix)
