@@ -16,6 +16,13 @@ _LAZY: dict[str, str] = {
     "get_modules_by_type": "easydel_b200.infra.factory",
     "EasyDeLOptimizers": "easydel_b200.infra.etils", "EasyDeLSchedulers": "easydel_b200.infra.etils",
     "EasyDeLGradientCheckPointers": "easydel_b200.infra.etils", "AttentionMechanisms": "easydel_b200.infra.etils",
+    "EasyDeLRuntimeError": "easydel_b200.infra.errors", "EasyDeLSyntaxRuntimeError": "easydel_b200.infra.errors",
+    "EasyDeLTimerError": "easydel_b200.infra.errors", "EasyDeLBackends": "easydel_b200.infra.etils",
+    "EasyDeLPlatforms": "easydel_b200.infra.etils", "MoEMethods": "easydel_b200.infra.etils",
+    "Registry": "easydel_b200.infra.factory",
+    "ModelConverter": "easydel_b200.utils.parameters_transformation",
+    "StateDictConverter": "easydel_b200.utils.parameters_transformation",
+    "TensorConverter": "easydel_b200.utils.parameters_transformation",
     # trainers
     "TrainingArguments": "easydel_b200.trainers", "Trainer": "easydel_b200.trainers",
     "BaseTrainer": "easydel_b200.trainers", "TrainerOutput": "easydel_b200.trainers",
@@ -28,6 +35,10 @@ _LAZY: dict[str, str] = {
     "eSurge": "easydel_b200.inference.esurge", "eSurgeApiServer": "easydel_b200.inference.esurge.server",
     "InferenceApiRouter": "easydel_b200.inference.oai_proxies",
     "ToolParserManager": "easydel_b200.inference.tools.parsers",
+    "ToolParser": "easydel_b200.inference.tools.parsers",
+    "EngineRequest": "easydel_b200.inference.esurge.scheduler",
+    "EngineRequestStatus": "easydel_b200.inference.esurge.scheduler",
+    "ResponsesStreamBuilder": "easydel_b200.inference.stream_protocol",
     "eSurgeLMEvalAdapter": "easydel_b200.inference.evaluations.esurge_eval",
     "MultiModalManager": "easydel_b200.inference.esurge.multimodal",
     # quantisation

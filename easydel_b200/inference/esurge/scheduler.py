@@ -41,6 +41,9 @@ class RequestStatus(enum.Enum):
 _arrival = itertools.count()
 
 
+EngineRequestStatus = RequestStatus      # the name the public namespace uses
+
+
 @dataclass
 class EngineRequest:
     request_id: str

@@ -50,3 +50,6 @@ for _alias, _target in {
     "qwen3_omni_moe_text": "qwen3_moe", "qwen3_omni_moe_vision_encoder": "qwen3_vl_vision",
 }.items():
     _registry.alias(_alias, _target)
+
+from . import aliases  # noqa: E402,F401
+from .aliases import *  # noqa: E402,F401,F403
