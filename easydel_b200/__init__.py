@@ -36,6 +36,7 @@ _LAZY: dict[str, str] = {
     "InferenceApiRouter": "easydel_b200.inference.oai_proxies",
     "ToolParserManager": "easydel_b200.inference.tools.parsers",
     "ToolParser": "easydel_b200.inference.tools.parsers",
+    "AttentionModule": "easydel_b200.layers.attention",
     "EngineRequest": "easydel_b200.inference.esurge.scheduler",
     "EngineRequestStatus": "easydel_b200.inference.esurge.scheduler",
     "ResponsesStreamBuilder": "easydel_b200.inference.stream_protocol",
@@ -49,6 +50,15 @@ _LAZY: dict[str, str] = {
     "vWhisperInference": "easydel_b200.inference.vwhisper",
     "vWhisperInferenceConfig": "easydel_b200.inference.vwhisper",
 }
+
+
+_LAZY.update({_n: "easydel_b200.ops.registry" for _n in (
+    "OperationMetadata", "BaseOperationConfig", "AttentionConfig", "FlashAttentionConfig",
+    "BlockSparseAttentionConfig", "ScaledDotProductAttentionConfig", "RingAttentionConfig", "RaggedPageAttentionv2Config",
+    "RaggedPageAttentionv3Config", "AttentionOutput", "OperationRegistry", "OperationImpl",
+    "FlashAttn", "BlockSparseAttn", "VanillaAttn", "ScaledDotProductAttn",
+    "RingAttn", "RaggedPageAttnV2", "RaggedPageAttnV3", "PagedFlashAttn",
+    "AutoRegressiveDecodeAttn", "FlexibleAttentionModule")})
 
 
 def _register_lazy(names: dict[str, str]) -> None:

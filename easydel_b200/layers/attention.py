@@ -224,3 +224,6 @@ class Attention(nn.Module):
         rel = (torch.arange(Tk, device=q.device)[None, :] - torch.arange(Tq, device=q.device)[:, None] - (Tk - Tq))
         bias = self.alibi.to(q.device)[None, :, None, None] * rel[None, None].float()
         return R.attention(q, k, v, causal=self.causal, scale=self.scale, segment_ids=segment_ids, bias=bias)
+
+
+AttentionModule = Attention      # the name model code uses for its attention base class
