@@ -26,4 +26,7 @@ from .ray_dist import RayDistributedConfig, RayDistributedTrainer  # noqa: E402
 
 register_trainer("ray_dist")(RayDistributedTrainer)
 
+from . import prompt_transforms  # noqa: E402,F401
+from .prompt_transforms import *  # noqa: E402,F401,F403
+
 __all__ = [n for n in dir() if not n.startswith("_")]
